@@ -1,0 +1,85 @@
+"""ctypes loader for ``libomni_kernels.so`` (the hand-written sm_100a kernels).
+
+The kernels export a plain C ABI that takes raw device pointers and a ``cudaStream_t``; this
+module turns tensors into those arguments.  On a machine with a GPU a missing library is an
+error (there is no silent PyTorch fallback for CUDA tensors); on CPU-only machines the library
+is optional and the fp32 reference implementations in :mod:`omni_infer_b200.ops` are used.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libomni_kernels.so"
+_lib = None
+_status = {}
+
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_void_p = ctypes.c_void_p
+c_int64 = ctypes.c_int64
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def lib():
+    """Load the kernel library once.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: run `python -m omni_infer_b200.build` "
+                "(CUDA tensors never fall back to PyTorch ops)")
+        _lib = ctypes.CDLL(str(_LIB_PATH), mode=ctypes.RTLD_GLOBAL)
+    return _lib
+
+
+def ptr(t):
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr())
+
+
+def stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def status_buffer(device=None) -> torch.Tensor:
+    """Per-device int32[4] word {code, site, block, detail} that kernels write when a bounded
+    wait gives up.  Zero means every launch so far completed its protocol."""
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    if dev.type != "cuda":
+        dev = torch.device("cuda", torch.cuda.current_device())
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status[key]
+
+
+class KernelProtocolError(RuntimeError):
+    """A kernel gave up on a bounded wait (code, site, block, detail)."""
+
+
+def check_status(device=None, reset: bool = True) -> None:
+    """Synchronise and raise :class:`KernelProtocolError` if any kernel reported a failed wait."""
+    buf = status_buffer(device)
+    vals = buf.tolist()
+    if vals[0] != 0:
+        if reset:
+            buf.zero_()
+        raise KernelProtocolError(
+            f"kernel wait gave up: code={vals[0]} site={vals[1]} block={vals[2]} detail={vals[3]}")
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
