@@ -52,6 +52,8 @@ struct GemmParams {
   float* out_scale;      // EPI 2: [n_out/128, out_scale_ld]
   int out_scale_ld;
   const float* row_scale;  // optional [rows]
+  int x_group_col;       // head-batched mode: group g reads X columns [g*x_group_col, +K) ...
+  int out_group_col;     // ... and writes out columns [g*out_group_col, +n_out)
   OmniStatus* status;
 };
 
@@ -178,7 +180,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * BK_ELEMS, wrow, pol_w);
           if (NACC == 2)
             tma_load_2d_hint(st + L::A_BYTES, &tmap_w, &full_bar[s], kb * BK_ELEMS, wrow + p.n_out, pol_w);
-          tma_load_2d_hint(st + NACC * L::A_BYTES, &tmap_x, &full_bar[s], kb * BK_ELEMS, row0, pol_x);
+          tma_load_2d_hint(st + NACC * L::A_BYTES, &tmap_x, &full_bar[s], kb * BK_ELEMS + g * p.x_group_col, row0, pol_x);
         }
       }
     }
@@ -247,8 +249,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       int g, mt, row0, rows;
       decode_tile(tile, g, mt, row0, rows);
-      const int n = mt * 128 + r;
-      const bool n_ok = n < p.n_out;
+      const int n_in = mt * 128 + r;
+      const bool n_ok = n_in < p.n_out;
+      const int n = n_in + g * p.out_group_col;  // output column
 
       float acc[(KIND == 1) ? NACC * BN : 1];
       if (KIND == 1) {
@@ -441,8 +444,8 @@ using namespace omni;
 extern "C" int omni_gemm(int kind, int epi, const void* w, const void* x, void* out, int G, int n_out, int K,
                          int x_rows, int T, const int* seg_start, const int* seg_len, const float* w_scale,
                          const float* x_scale, int x_scale_ld, int out_ld, int out_f32, float* out_scale,
-                         int out_scale_ld, const float* row_scale, int bn, int t_hint, void* status,
-                         cudaStream_t stream) {
+                         int out_scale_ld, const float* row_scale, int x_group_col, int out_group_col, int x_ld,
+                         int bn, int t_hint, void* status, cudaStream_t stream) {
   if (G < 1 || G > MAX_GROUPS || n_out < 1 || K < 1) return -1;
   const int nacc = (epi == 0) ? 1 : 2;
   const int esz = (kind == 0) ? 2 : 1;
@@ -460,12 +463,16 @@ extern "C" int omni_gemm(int kind, int epi, const void* w, const void* x, void* 
   p.G = G; p.n_out = n_out; p.K = K; p.T = T; p.seg_start = seg_start; p.seg_len = seg_len;
   p.w_rows_per_group = n_out * nacc; p.w_scale = w_scale; p.x_scale = x_scale; p.x_scale_ld = x_scale_ld;
   p.out = out; p.out_ld = out_ld; p.out_f32 = out_f32; p.out_scale = out_scale; p.out_scale_ld = out_scale_ld;
-  p.row_scale = row_scale; p.status = (OmniStatus*)status;
+  p.row_scale = row_scale; p.x_group_col = x_group_col; p.out_group_col = out_group_col;
+  p.status = (OmniStatus*)status;
+  if (x_ld <= 0) x_ld = K;
+  const uint64_t x_cols = x_group_col > 0 ? (uint64_t)x_ld : (uint64_t)K;
 
   const int bk = (kind == 0) ? 64 : 128;
   CUtensorMap tw, tx;
   if (make_tmap_2d(&tw, w, esz, (uint64_t)G * p.w_rows_per_group, K, K, 128, bk, true)) return -10;
-  if (make_tmap_2d(&tx, x, esz, (uint64_t)x_rows, K, K, bn, bk, true)) return -11;
+  if (x_group_col > 0 && (K % bk) != 0) return -6;  // a K tail would read the next group's columns
+  if (make_tmap_2d(&tx, x, esz, (uint64_t)x_rows, x_cols, x_ld, bn, bk, true)) return -11;
   const int grid = sm_count();
 
 #define OMNI_GEMM_CASE(KIND_, BN_, NACC_, EPI_) \

@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(128) mla_kv_rope_cache_kernel(
     const __nv_bfloat16* __restrict__ latent, int latent_ld, const __nv_bfloat16* __restrict__ kv_weight, float eps,
     const float* __restrict__ cos_sin, const int64_t* __restrict__ positions, const int64_t* __restrict__ slots,
     __nv_bfloat16* cache, int cache_ld, __nv_bfloat16* q, int heads, int q_head_dim, int q_rope_off,
-    __nv_bfloat16* latent_out) {
+    __nv_bfloat16* q_out, int q_out_head_dim, int q_out_off, __nv_bfloat16* latent_out) {
   const int t = blockIdx.x;
   const int64_t pos = positions[t];
   const int64_t slot = slots[t];
@@ -178,7 +178,11 @@ __global__ void __launch_bounds__(128) mla_kv_rope_cache_kernel(
           reinterpret_cast<__nv_bfloat162*>(q + ((size_t)t * heads + hd) * q_head_dim + q_rope_off + 2 * i);
       const float2 ab = __bfloat1622float2(*p2);
       const float cth = cs[i], sth = cs[32 + i];
-      *p2 = __floats2bfloat162_rn(ab.x * cth - ab.y * sth, ab.x * sth + ab.y * cth);
+      const __nv_bfloat162 rot = __floats2bfloat162_rn(ab.x * cth - ab.y * sth, ab.x * sth + ab.y * cth);
+      if (q_out != nullptr)  // decode: rotated rope slice goes straight into the absorbed-q buffer
+        *reinterpret_cast<__nv_bfloat162*>(q_out + ((size_t)t * heads + hd) * q_out_head_dim + q_out_off + 2 * i) = rot;
+      else
+        *p2 = rot;
     }
   }
 }
@@ -287,12 +291,14 @@ extern "C" int omni_quant_fp8_block(const void* x, void* q, float* scale, int sc
 extern "C" int omni_mla_kv_rope_cache(const void* latent, int latent_ld, const void* kv_weight, float eps,
                                       const float* cos_sin, const int64_t* positions, const int64_t* slots,
                                       void* cache, int cache_ld, void* q, int heads, int q_head_dim, int q_rope_off,
-                                      void* latent_out, int T, cudaStream_t stream) {
+                                      void* q_out, int q_out_head_dim, int q_out_off, void* latent_out, int T,
+                                      cudaStream_t stream) {
   if (T <= 0) return 0;
   mla_kv_rope_cache_kernel<<<T, 128, 0, stream>>>((const __nv_bfloat16*)latent, latent_ld,
                                                   (const __nv_bfloat16*)kv_weight, eps, cos_sin, positions, slots,
                                                   (__nv_bfloat16*)cache, cache_ld, (__nv_bfloat16*)q, heads,
-                                                  q_head_dim, q_rope_off, (__nv_bfloat16*)latent_out);
+                                                  q_head_dim, q_rope_off, (__nv_bfloat16*)q_out, q_out_head_dim,
+                                                  q_out_off, (__nv_bfloat16*)latent_out);
   return (int)cudaGetLastError();
 }
 

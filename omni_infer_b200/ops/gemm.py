@@ -93,7 +93,7 @@ def gemm_ref(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, 
 
 
 def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi="store",
-         row_scale=None, out_dtype=torch.bfloat16, out=None, out_scale=None, bn=0, t_hint=0):
+         row_scale=None, out_dtype=None, out=None, out_scale=None, bn=0, t_hint=0):
     """``out[t] = epi(x[t] @ w[g(t)].T)``.
 
     x: [T, K] bf16 or e4m3 (then ``x_scale`` is [K/128, ld] fp32, K-block major).
@@ -101,6 +101,8 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
     seg_start/seg_len: int32 [G] row segments per group (grouped GEMM).
     epi: "store" | "swiglu" (w holds gate rows then up rows) | "swiglu_quant" (returns (q, scale_t)).
     """
+    if out_dtype is None:
+        out_dtype = torch.bfloat16 if (x.dtype == FP8 or x.is_cuda) else x.dtype
     if not x.is_cuda:
         return gemm_ref(x, w, w_scale=w_scale, x_scale=x_scale, seg_start=seg_start, seg_len=seg_len,
                         epi=epi, row_scale=row_scale, out_dtype=out_dtype)
@@ -109,7 +111,7 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
         w = w.unsqueeze(0)
     G, n_w, K = w.shape
     T = x.shape[0]
-    assert x.shape[1] == K and x.is_contiguous() and w.is_contiguous()
+    assert x.shape[1] == K and x.stride(1) == 1 and w.is_contiguous()
     kind = 1 if x.dtype == FP8 else 0
     assert (w.dtype == FP8) == (kind == 1), "x and w must both be bf16 or both e4m3"
     if kind == 0:
@@ -132,8 +134,44 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
         nat.ptr(x_scale), nat.c_int(x_scale.shape[1] if x_scale is not None else 0),
         nat.c_int(out.stride(0)), nat.c_int(out_f32), nat.ptr(out_scale),
         nat.c_int(out_scale.shape[1] if out_scale is not None else 0), nat.ptr(row_scale),
-        nat.c_int(bn), nat.c_int(t_hint), nat.ptr(nat.status_buffer(x.device)), nat.stream())
+        nat.c_int(0), nat.c_int(0), nat.c_int(x.stride(0)), nat.c_int(bn), nat.c_int(t_hint), nat.ptr(nat.status_buffer(x.device)), nat.stream())
     nat.check_rc(rc, "omni_gemm")
     if e == 2:
         return out, out_scale
+    return out
+
+
+def bmm_heads_ref(x, w):
+    """x [T, H, K], w [H, N, K] -> [T, H, N] (fp32 accumulate)."""
+    return torch.einsum("thk,hnk->thn", x.float(), w.float()).to(x.dtype)
+
+
+def bmm_heads(x, w, out=None, out_col_offset=0):
+    """Per-head GEMM without transposes: ``out[t, h, :N] = x[t, h, :K] @ w[h].T``.
+
+    ``x`` may be a strided view [T, H, K] of a wider [T, H, Dx] buffer (last dim contiguous) and ``out``
+    a wider [T, H, Do] buffer: heads are addressed as column offsets of one 2-D tensor map, so the
+    absorbed MLA projections (q_nope @ W_UK, o_latent @ W_UV) read and write the attention layouts
+    directly (omni/models/common/layers/attention/deepseek_mla.py:209-235, 440-560)."""
+    T, H, K = x.shape
+    N = w.shape[1]
+    if not x.is_cuda:
+        y = bmm_heads_ref(x, w)
+        if out is None:
+            return y
+        out[:, :, out_col_offset:out_col_offset + N] = y
+        return out
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()
+    assert x.stride(2) == 1 and x.stride(0) == H * x.stride(1), "x must be a [T, H, Dx] buffer view"
+    if out is None:
+        out = torch.empty(T, H, N, dtype=x.dtype, device=x.device)
+    assert out.stride(2) == 1 and out.stride(0) == H * out.stride(1)
+    base_out = out[:, :, out_col_offset:] if out_col_offset else out
+    rc = nat.lib().omni_gemm(
+        nat.c_int(0), nat.c_int(0), nat.ptr(w), nat.ptr(x), nat.ptr(base_out), nat.c_int(H), nat.c_int(N), nat.c_int(K),
+        nat.c_int(T), nat.c_int(T), nat.ptr(None), nat.ptr(None), nat.ptr(None), nat.ptr(None), nat.c_int(0),
+        nat.c_int(out.stride(0)), nat.c_int(0), nat.ptr(None), nat.c_int(0), nat.ptr(None),
+        nat.c_int(x.stride(1)), nat.c_int(out.stride(1)), nat.c_int(x.stride(0)), nat.c_int(0), nat.c_int(T),
+        nat.ptr(nat.status_buffer(x.device)), nat.stream())
+    nat.check_rc(rc, "omni_gemm(bmm_heads)")
     return out
