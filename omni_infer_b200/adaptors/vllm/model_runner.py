@@ -1,0 +1,385 @@
+"""Model runner: turns a SchedulerOutput into device work.
+
+Counterpart of the reference's NPUModelRunner (omni/adaptors/vllm/worker/npu_model_runner.py:120-995):
+``_prepare_inputs`` (positions, slot mapping, attention state, padding the decode batch to a "gear"),
+the multi-step loop with on-device input advance, logits -> sampler or MTP verification -> ``run_mtp``
+drafting, KV-connector hooks, the OmniPlacement hook between steps, ``load_model`` (main model + up to
+three MTP drafters sharing embedding and LM head), ``initialize_kv_cache``, ``capture_model`` and
+``_get_closest_gear``.  The vendor graph compiler's gears become CUDA-graph buckets
+(:mod:`omni_infer_b200.adaptors.vllm.cuda_graphs`).
+"""
+from __future__ import annotations
+
+import logging
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ... import ops
+from ...engine.request import ModelRunnerOutput, SchedulerOutput
+from ...layers.common import AttnMetadata
+from ...models import build_model
+from ...models.config import ModelConfig
+from ...parallel import get_parallel_state
+
+logger = logging.getLogger("omni_infer_b200.runner")
+
+
+@dataclass
+class RunnerConfig:
+    block_size: int = 128
+    num_kv_blocks: int = 0                     # 0 = size from free memory
+    gpu_memory_utilization: float = 0.9
+    max_num_seqs: int = 256
+    max_model_len: int = 4096
+    max_num_batched_tokens: int = 8192
+    num_speculative_tokens: int = 0
+    decode_gear_list: list = field(default_factory=list)   # CUDA-graph batch buckets; [] = powers of two
+    use_cuda_graph: bool = True
+    enforce_eager: bool = False
+    seed: int = 0
+    kv_cache_dtype: str = "auto"
+    control_accept_rate: float = -1.0          # test knob of the MTP verifier (reference: model_extra_config)
+
+
+class ModelRunner:
+    def __init__(self, model_cfg: ModelConfig, cfg: RunnerConfig, device: torch.device, planner=None,
+                 kv_connector=None):
+        self.model_cfg, self.cfg, self.device = model_cfg, cfg, device
+        self.planner = planner
+        self.kv_connector = kv_connector
+        self.model = None
+        self.drafters: list = []
+        self.kv_caches: list = []
+        self.drafter_kv: list = []
+        self.graphs = None
+        self.rng = torch.Generator(device=device)
+        self.rng.manual_seed(cfg.seed)
+        self.tpr = 1 + cfg.num_speculative_tokens
+        self._bt_width = (cfg.max_model_len + cfg.block_size - 1) // cfg.block_size + 1
+        self.step_times: list = []
+
+    # ------------------------------------------------------------------ model / cache set-up
+    def load_model(self, weights=None, seed: Optional[int] = 0) -> None:
+        cfg = self.model_cfg
+        t0 = time.time()
+        self.model = build_model(cfg, device=self.device, planner=self.planner,
+                                 seed=seed if weights is None else None)
+        from ...models.deepseek_mtp import DeepseekV3MTP
+        n_draft = min(self.cfg.num_speculative_tokens, max(cfg.num_nextn_predict_layers, 0), 3)
+        if self.cfg.num_speculative_tokens and n_draft == 0:
+            raise ValueError("speculative decoding needs num_nextn_predict_layers > 0 in the model config")
+        for i in range(n_draft):
+            d = DeepseekV3MTP(cfg, self.model, mtp_index=i, device=self.device)
+            if weights is None:
+                from ...quantization.loader import init_random_weights
+                init_random_weights(d, (seed or 0) + 1000 + i)
+            self.drafters.append(d)
+        if weights is not None:
+            wl = list(weights) if self.drafters else weights
+            self.model.load_weights(wl, planner=self.planner)
+            for d in self.drafters:
+                d.load_weights(wl, planner=self.planner)
+        if self.planner is not None:
+            self.planner.init_dram_weights(self.model)
+        logger.info("model %s loaded in %.1fs", cfg.name or cfg.architecture, time.time() - t0)
+
+    def kv_bytes_per_block(self) -> int:
+        cfg = self.model_cfg
+        layers = self.model.num_kv_layers + len(self.drafters)
+        esz = 4 if cfg.dtype == "float32" else 2
+        return layers * self.cfg.block_size * cfg.kv_bytes_per_token(esz)
+
+    def determine_num_blocks(self) -> int:
+        if self.cfg.num_kv_blocks:
+            return self.cfg.num_kv_blocks
+        if self.device.type != "cuda":
+            return 256
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = free - int(total * (1.0 - self.cfg.gpu_memory_utilization))
+        return max(16, int(budget // self.kv_bytes_per_block()))
+
+    def initialize_kv_cache(self, num_blocks: int) -> None:
+        cfg, bs = self.model_cfg, self.cfg.block_size
+        dt = self.model.model.dtype if hasattr(self.model, "model") else torch.bfloat16
+        self.num_blocks = num_blocks
+
+        def one():
+            if cfg.use_mla:
+                return torch.zeros(num_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim, dtype=dt, device=self.device)
+            return (torch.zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim, dtype=dt, device=self.device),
+                    torch.zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim, dtype=dt, device=self.device))
+
+        self.kv_caches = [one() for _ in range(self.model.num_kv_layers)]
+        self.drafter_kv = [[one()] for _ in self.drafters]
+        if self.kv_connector is not None:
+            self.kv_connector.register_kv_caches(self.kv_caches + [k[0] for k in self.drafter_kv])
+
+    # ------------------------------------------------------------------ gears / graphs
+    def gear_list(self) -> list:
+        if self.cfg.decode_gear_list:
+            return sorted(set(int(g) for g in self.cfg.decode_gear_list))
+        gears, g = [], 1
+        while g < self.cfg.max_num_seqs:
+            gears.append(g)
+            g *= 2
+        gears.append(self.cfg.max_num_seqs)
+        return gears
+
+    def _get_closest_gear(self, n: int) -> int:
+        for g in self.gear_list():
+            if g >= n:
+                return g
+        return n
+
+    def capture_model(self) -> None:
+        """Capture one CUDA graph per decode bucket, largest first so smaller ones reuse its memory pool."""
+        if self.device.type != "cuda" or not self.cfg.use_cuda_graph or self.cfg.enforce_eager:
+            return
+        from .cuda_graphs import DecodeGraphs
+        self.graphs = DecodeGraphs(self)
+        t0 = time.time()
+        for g in reversed(self.gear_list()):
+            self.graphs.capture(g)
+        logger.info("captured %d decode graphs in %.1fs", len(self.gear_list()), time.time() - t0)
+
+    # ------------------------------------------------------------------ input preparation
+    def _slots(self, block_ids: list, start: int, n: int) -> list:
+        bs = self.cfg.block_size
+        return [block_ids[p // bs] * bs + p % bs for p in range(start, start + n)]
+
+    def _to_dev(self, data, dtype) -> torch.Tensor:
+        t = torch.tensor(data, dtype=dtype)
+        if self.device.type == "cuda":
+            return t.pin_memory().to(self.device, non_blocking=True)
+        return t
+
+    def _prepare_prefill(self, so: SchedulerOutput):
+        ids, pos, slots, cu_q, cu_k, qlens, ctx, sample_idx, seq_lens = [], [], [], [0], [0], [], [], [], []
+        gather, need_gather = [], False
+        bt_rows = []
+        for s in so.scheduled:
+            r = s.request
+            st, n = r.num_computed_tokens, s.num_scheduled_tokens
+            toks = r.all_token_ids[st:st + n]
+            ids += toks
+            pos += list(range(st, st + n))
+            slots += self._slots(r.block_ids, st, n)
+            cu_q.append(cu_q[-1] + n)
+            cu_k.append(cu_k[-1] + st + n)
+            qlens.append(n)
+            ctx.append(st)
+            seq_lens.append(st + n)
+            need_gather |= st > 0
+            gather += self._slots(r.block_ids, 0, st + n)
+            sample_idx.append(cu_q[-1] - 1)
+            bt_rows.append(r.block_ids + [0] * (self._bt_width - len(r.block_ids)))
+        md = AttnMetadata(
+            is_prefill=True, positions=self._to_dev(pos, torch.int64), slot_mapping=self._to_dev(slots, torch.int64),
+            block_table=self._to_dev(bt_rows, torch.int32), seq_lens=self._to_dev(seq_lens, torch.int32),
+            cu_q=self._to_dev(cu_q, torch.int32), cu_k=self._to_dev(cu_k, torch.int32), query_lens=qlens,
+            context_lens=ctx, max_q=max(qlens), max_k=max(seq_lens),
+            kv_gather_slots=self._to_dev(gather, torch.int64) if need_gather else None,
+            sample_indices=self._to_dev(sample_idx, torch.int64))
+        return self._to_dev(ids, torch.int64), md
+
+    def _prepare_decode(self, so: SchedulerOutput, padded: int):
+        tpr = self.tpr
+        B = len(so.scheduled)
+        ids, pos, slots, qlens, seq_lens, bt_rows = [], [], [], [], [], []
+        for s in so.scheduled:
+            r = s.request
+            st = r.num_computed_tokens
+            drafts = list(s.spec_token_ids) + [0] * (tpr - 1 - len(s.spec_token_ids))
+            ids += [r.all_token_ids[st]] + drafts[: tpr - 1]
+            pos += list(range(st, st + tpr))
+            slots += self._slots(r.block_ids, st, tpr)
+            qlens += [st + j + 1 for j in range(tpr)]
+            seq_lens.append(st + tpr)
+            bt_rows.append(r.block_ids + [0] * (self._bt_width - len(r.block_ids)))
+        for _ in range(padded - B):     # padding rows: no cache write, zero-length attention
+            ids += [0] * tpr
+            pos += [0] * tpr
+            slots += [-1] * tpr
+            qlens += [0] * tpr
+            seq_lens.append(0)
+            bt_rows.append([0] * self._bt_width)
+        q_to_seq = [b for b in range(padded) for _ in range(tpr)]
+        md = AttnMetadata(
+            is_prefill=False, positions=self._to_dev(pos, torch.int64), slot_mapping=self._to_dev(slots, torch.int64),
+            block_table=self._to_dev(bt_rows, torch.int32), seq_lens=self._to_dev(seq_lens, torch.int32),
+            tokens_per_req=tpr, q_seq_lens=self._to_dev(qlens, torch.int32), q_to_seq=self._to_dev(q_to_seq, torch.int32),
+            max_seq_len=max(seq_lens) if seq_lens else 0,
+            num_valid=self._to_dev([B * tpr], torch.int32) if padded != B else None)
+        return self._to_dev(ids, torch.int64), md
+
+    # ------------------------------------------------------------------ sampling
+    def _sample(self, logits: torch.Tensor, reqs: list, rows_per_req: int) -> torch.Tensor:
+        """logits [len(reqs) * rows_per_req (+ padding), V] -> token ids (padding rows included)."""
+        if all(r.sampling.greedy for r in reqs):
+            return ops.argmax(logits)
+        n = logits.shape[0]
+        temp = torch.zeros(n)
+        tk = torch.zeros(n, dtype=torch.int32)
+        tp = torch.ones(n)
+        for i, r in enumerate(reqs):
+            sl = slice(i * rows_per_req, (i + 1) * rows_per_req)
+            temp[sl], tk[sl], tp[sl] = r.sampling.temperature, r.sampling.top_k, r.sampling.top_p
+        u = torch.rand(n, device=self.device, generator=self.rng)
+        return ops.sample_topk_topp(logits, temp.to(self.device), tk.to(self.device), tp.to(self.device), u)
+
+    # ------------------------------------------------------------------ execution
+    @torch.inference_mode()
+    def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+        t0 = time.perf_counter()
+        fin_send, fin_recv = set(), set()
+        if self.kv_connector is not None:
+            self.kv_connector.bind_connector_metadata(so.kv_connector_metadata)
+            self.kv_connector.start_load_kv()
+        if so.empty:
+            if self.kv_connector is not None:
+                fin_send, fin_recv = self.kv_connector.get_finished(so.finished_req_ids)
+            return ModelRunnerOutput([], [[]], None, fin_send, fin_recv)
+        if self.planner is not None:
+            self.planner.place_experts()
+        reqs = [s.request for s in so.scheduled]
+        if so.is_prefill:
+            out = self._run_prefill(so, reqs)
+        else:
+            out = self._run_decode(so, reqs)
+        if self.kv_connector is not None:
+            self.kv_connector.wait_for_save()
+            fin_send, fin_recv = self.kv_connector.get_finished(so.finished_req_ids)
+            out.finished_sending, out.finished_recving = fin_send, fin_recv
+        out.step_time_s = time.perf_counter() - t0
+        self.step_times.append(out.step_time_s)
+        return out
+
+    def _run_prefill(self, so, reqs) -> ModelRunnerOutput:
+        ids, md = self._prepare_prefill(so)
+        hidden = self.model(ids, md, self.kv_caches)
+        last_h = hidden[md.sample_indices]
+        logits = self.model.compute_logits(last_h)
+        toks = self._sample(logits, reqs, 1)
+        spec = None
+        if self.drafters:
+            # drafter prefill: tokens shifted left, the sampled token closes each request's row
+            mtp_in = torch.empty_like(ids)
+            mtp_in[:-1] = ids[1:]
+            mtp_in[md.sample_indices] = toks
+            spec_cols, h, cur = [], hidden, mtp_in
+            for di, d in enumerate(self.drafters):
+                h = d(cur, md, self.drafter_kv[di], h)
+                dl = d.compute_logits(h[md.sample_indices])
+                draft = ops.argmax(dl)
+                spec_cols.append(draft)
+                if di + 1 < len(self.drafters):
+                    nxt = torch.empty_like(cur)
+                    nxt[:-1] = cur[1:]
+                    nxt[md.sample_indices] = draft
+                    cur = nxt
+            spec_t = torch.stack(spec_cols, dim=1).tolist()
+            pad = self.cfg.num_speculative_tokens - len(self.drafters)
+            spec = [row + [0] * pad for row in spec_t]
+        tl = toks.tolist()
+        return ModelRunnerOutput([r.request_id for r in reqs], [[[t] for t in tl]], spec)
+
+    def _forward_decode(self, ids, md, padded):
+        """hidden, logits and greedy tokens for one decode step (CUDA graph replay when available)."""
+        if self.graphs is not None and self.graphs.has(padded):
+            return self.graphs.replay(padded, ids, md)
+        hidden = self.model(ids, md, self.kv_caches)
+        logits = self.model.compute_logits(hidden)
+        return hidden, logits
+
+    def _run_decode(self, so, reqs) -> ModelRunnerOutput:
+        tpr, B = self.tpr, len(reqs)
+        padded = self._get_closest_gear(B) if (self.graphs is not None) else B
+        ids, md = self._prepare_decode(so, padded)
+        steps_out: list = []
+        spec_final = None
+        for step in range(so.num_step):
+            hidden, logits = self._forward_decode(ids, md, padded)
+            toks = self._sample(logits, reqs, tpr) if not all(r.sampling.greedy for r in reqs) else ops.argmax(logits)
+            if tpr == 1:
+                steps_out.append(toks[:B])
+                if step + 1 < so.num_step:
+                    ops.step_advance(md.positions, md.seq_lens, md.slot_mapping, md.block_table, self.cfg.block_size, 1)
+                    md.q_seq_lens = md.seq_lens
+                    md.max_seq_len += 1
+                    ids = toks
+                continue
+            # ---- MTP: verify the drafts, then draft again from the last accepted position
+            fwd = toks.view(padded, tpr)
+            u = None
+            if 0.0 <= self.cfg.control_accept_rate <= 1.0:
+                u = torch.rand(padded * (tpr - 1), device=self.device, generator=self.rng)
+            out_tok, acc, last_idx, mtp_in = ops.mtp_verify(ids.view(padded, tpr), fwd, u, self.cfg.control_accept_rate)
+            steps_out.append(out_tok[:B])
+            drafts, h, cur = [], hidden, mtp_in.view(-1)
+            for di, d in enumerate(self.drafters):
+                h = d(cur, md, self.drafter_kv[di], h)
+                dl = d.compute_logits(h[last_idx.long()])
+                draft = ops.argmax(dl)
+                drafts.append(draft)
+                if di + 1 < len(self.drafters):
+                    nxt = torch.roll(cur, -1)
+                    nxt[last_idx.long()] = draft
+                    cur = nxt
+            draft_t = torch.stack(drafts, dim=1)                       # [padded, n_drafters]
+            if draft_t.shape[1] < tpr - 1:
+                draft_t = torch.nn.functional.pad(draft_t, (0, tpr - 1 - draft_t.shape[1]))
+            spec_final = draft_t
+            if step + 1 < so.num_step:
+                adv = (acc + 1).int()
+                ops.step_advance(md.positions, md.seq_lens, md.slot_mapping, md.block_table, self.cfg.block_size, tpr, adv)
+                # visible kv tokens per q row: seq_len - tpr + j + 1
+                base = (md.seq_lens - tpr).repeat_interleave(tpr)
+                md.q_seq_lens = torch.where(base >= 0, base + torch.arange(1, tpr + 1, device=self.device, dtype=torch.int32).repeat(padded), torch.zeros_like(base)).int()
+                md.max_seq_len += tpr
+                last_tok = fwd.gather(1, acc.long().unsqueeze(1))
+                ids = torch.cat([last_tok, draft_t], dim=1).reshape(-1)
+        # ---- one host sync for the whole round
+        if tpr == 1:
+            stacked = torch.stack(steps_out, dim=0).tolist()           # [steps][B]
+            sampled = [[[t] for t in row] for row in stacked]
+            return ModelRunnerOutput([r.request_id for r in reqs], sampled, None)
+        stacked = torch.stack(steps_out, dim=0).tolist()               # [steps][B][tpr]
+        spec = spec_final[:B].tolist() if spec_final is not None else None
+        return ModelRunnerOutput([r.request_id for r in reqs], stacked, spec)
+
+    # ------------------------------------------------------------------ warm-up / dummy batches
+    @torch.inference_mode()
+    def execute_dummy_batch(self, num_tokens: int = 1) -> None:
+        """Idle data-parallel ranks still run one padded decode step so that collectives match
+        (omni/adaptors/vllm/worker/npu_worker.py:285)."""
+        tpr = self.tpr
+        padded = self._get_closest_gear(1) if self.graphs is not None else 1
+        so = SchedulerOutput([], False)
+        ids, md = self._prepare_decode(so, padded)
+        md.num_valid = self._to_dev([0], torch.int32)
+        self._forward_decode(ids, md, padded)
+
+    @torch.inference_mode()
+    def profile_run(self) -> None:
+        """One worst-case prefill to measure peak activation memory before sizing the KV cache."""
+        n = min(self.cfg.max_num_batched_tokens, self.cfg.max_model_len - 1)
+        cfg = self.model_cfg
+        bs = self.cfg.block_size
+        nblk = (n + bs - 1) // bs + 1
+        self.initialize_kv_cache(nblk + 1)
+        ids = torch.zeros(n, dtype=torch.int64, device=self.device)
+        blocks = list(range(1, nblk + 1))
+        md = AttnMetadata(True, torch.arange(n, device=self.device), self._to_dev(self._slots(blocks, 0, n), torch.int64),
+                          self._to_dev([blocks], torch.int32), self._to_dev([n], torch.int32),
+                          cu_q=self._to_dev([0, n], torch.int32), cu_k=self._to_dev([0, n], torch.int32),
+                          query_lens=[n], context_lens=[0], max_q=n, max_k=n,
+                          sample_indices=self._to_dev([n - 1], torch.int64))
+        h = self.model(ids, md, self.kv_caches)
+        self.model.compute_logits(h[md.sample_indices])
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        self.kv_caches, self.drafter_kv = [], []

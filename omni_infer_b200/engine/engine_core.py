@@ -1,0 +1,169 @@
+"""Engine core: request intake -> scheduler -> worker -> outputs, with multi-step and asynchronous
+scheduling (the reference patches these into its host engine: async_schedule_update_output.patch,
+multi_step.patch, manual_apiserver_scaleout.patch)."""
+from __future__ import annotations
+
+import itertools
+import logging
+import os
+import time
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ..adaptors.vllm.model_runner import RunnerConfig
+from ..adaptors.vllm.worker import B200Worker
+from ..models.config import ModelConfig, get_config
+from .kv_manager import KVCacheManager
+from .request import Request, RequestOutput, SamplingParams
+from .scheduler import Scheduler, SchedulerConfig
+
+logger = logging.getLogger("omni_infer_b200.engine")
+
+
+@dataclass
+class EngineConfig:
+    model: str = "tiny-deepseek-v3"
+    model_overrides: dict = field(default_factory=dict)
+    device: Optional[str] = None
+    tp_size: int = 1
+    block_size: int = 128
+    num_kv_blocks: int = 0
+    gpu_memory_utilization: float = 0.9
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 8192
+    max_model_len: int = 4096
+    num_speculative_tokens: int = 0
+    num_step: int = 1
+    async_schedule: bool = False
+    enable_prefix_caching: bool = False
+    enable_chunked_prefill: bool = os.environ.get("FORCE_ENABLE_CHUNK_PREFILL", "0") == "1"
+    decode_gear_list: list = field(default_factory=list)
+    enforce_eager: bool = False
+    seed: int = 0
+    kv_transfer_config: Optional[dict] = None    # {"kv_role": "kv_producer"|"kv_consumer", ...}
+    enable_omni_attn: bool = False
+    omni_attn_config: Optional[dict] = None
+    placement_config: Optional[dict] = None
+    eos_token_id: Optional[int] = None
+
+
+class EngineCore:
+    def __init__(self, cfg: EngineConfig, model_cfg: Optional[ModelConfig] = None, weights=None, planner=None,
+                 kv_connector_pair=None):
+        self.cfg = cfg
+        self.model_cfg = model_cfg or get_config(cfg.model, **cfg.model_overrides)
+        rc = RunnerConfig(block_size=cfg.block_size, num_kv_blocks=cfg.num_kv_blocks,
+                          gpu_memory_utilization=cfg.gpu_memory_utilization, max_num_seqs=cfg.max_num_seqs,
+                          max_model_len=cfg.max_model_len, max_num_batched_tokens=cfg.max_num_batched_tokens,
+                          num_speculative_tokens=cfg.num_speculative_tokens, decode_gear_list=cfg.decode_gear_list,
+                          enforce_eager=cfg.enforce_eager, seed=cfg.seed)
+        sched_conn = worker_conn = None
+        if kv_connector_pair is not None:
+            sched_conn, worker_conn = kv_connector_pair
+        elif cfg.kv_transfer_config:
+            from ..accelerators.pd import create_connectors
+            sched_conn, worker_conn = create_connectors(cfg.kv_transfer_config, block_size=cfg.block_size)
+        if planner is None and cfg.placement_config:
+            from ..accelerators.placement import OmniPlanner
+            planner = OmniPlanner.from_config(cfg.placement_config, self.model_cfg)
+        self.worker = B200Worker(self.model_cfg, rc, tp_size=cfg.tp_size, device=cfg.device, planner=planner,
+                                 kv_connector=worker_conn)
+        self.worker.init_device()
+        self.worker.load_model(weights, seed=cfg.seed)
+        n_blocks = self.worker.determine_available_memory()
+        self.worker.initialize_cache(n_blocks)
+        self.worker.compile_or_warm_up_model()
+        self.kv = KVCacheManager(n_blocks, cfg.block_size, cfg.enable_prefix_caching)
+        if cfg.enable_omni_attn:
+            from ..accelerators.cache import apply_omni_attn_patch
+            apply_omni_attn_patch(self, cfg.omni_attn_config or {})
+        sc = SchedulerConfig(max_num_seqs=cfg.max_num_seqs, max_num_batched_tokens=cfg.max_num_batched_tokens,
+                             max_model_len=cfg.max_model_len, num_speculative_tokens=cfg.num_speculative_tokens,
+                             num_step=cfg.num_step, async_schedule=cfg.async_schedule,
+                             enable_chunked_prefill=cfg.enable_chunked_prefill)
+        self.scheduler = Scheduler(sc, self.kv, connector=sched_conn)
+        self._ids = itertools.count()
+        self._pool = ThreadPoolExecutor(max_workers=1) if cfg.async_schedule else None
+        self._inflight = None
+        self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "generated_tokens": 0}
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, prompt_token_ids, sampling: Optional[SamplingParams] = None, request_id: Optional[str] = None,
+                    kv_transfer_params: Optional[dict] = None, priority: int = 0) -> str:
+        rid = request_id or f"req-{next(self._ids)}"
+        req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), priority=priority,
+                      eos_token_id=self.cfg.eos_token_id, kv_transfer_params=kv_transfer_params)
+        if not self.scheduler.try_pull_kv_fast_path(req):
+            self.scheduler.add_request(req)
+        else:
+            self.scheduler.requests[rid] = req
+            self.scheduler.waiting.append(req)
+        return rid
+
+    def abort(self, request_id: str) -> None:
+        self.scheduler.abort_request(request_id)
+
+    @property
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished or self._inflight is not None
+
+    # ------------------------------------------------------------------ stepping
+    def step(self) -> list:
+        if self.cfg.async_schedule:
+            return self.step_async()
+        so = self.scheduler.schedule()
+        out = self.worker.execute_model(so)
+        res = self.scheduler.update_from_output(so, out)
+        self._account(so, res)
+        return res
+
+    def step_async(self) -> list:
+        """Overlap: while the worker executes round N, apply round N-1's results and schedule round N+1.
+        A request scheduled twice in flight would need tokens the host has not seen yet, so a request
+        takes part in at most one in-flight round; with enough running requests the device never idles."""
+        results: list = []
+        if self._inflight is None:
+            so = self.scheduler.schedule()
+            self._inflight = (so, self._pool.submit(self.worker.execute_model, so))
+            return results
+        so, fut = self._inflight
+        out = fut.result()
+        res = self.scheduler.update_from_output(so, out)
+        self._account(so, res)
+        nxt = self.scheduler.schedule()
+        if not nxt.empty or nxt.kv_connector_metadata is not None and self.scheduler.has_unfinished:
+            self._inflight = (nxt, self._pool.submit(self.worker.execute_model, nxt))
+        else:
+            self._inflight = None
+        return res
+
+    def _account(self, so, res) -> None:
+        self.metrics["steps"] += 1
+        self.metrics["prefill_steps" if so.is_prefill else "decode_steps"] += 0 if so.empty else 1
+        self.metrics["generated_tokens"] += sum(len(r.new_token_ids) for r in res)
+
+    def run_until_done(self, max_steps: int = 1_000_000) -> dict:
+        outs: dict = {}
+        for _ in range(max_steps):
+            if not self.has_unfinished:
+                break
+            for r in self.step():
+                outs.setdefault(r.request_id, []).extend(r.new_token_ids)
+        return outs
+
+
+class LLM:
+    """Offline front end: ``LLM(...).generate(list_of_token_id_lists, SamplingParams)``."""
+
+    def __init__(self, model: str = "tiny-deepseek-v3", **kw):
+        model_cfg = kw.pop("model_config", None)
+        weights = kw.pop("weights", None)
+        self.engine = EngineCore(EngineConfig(model=model, **kw), model_cfg=model_cfg, weights=weights)
+
+    def generate(self, prompts: list, sampling: Optional[SamplingParams] = None) -> list:
+        ids = [self.engine.add_request(p, sampling) for p in prompts]
+        outs = self.engine.run_until_done()
+        return [outs.get(i, []) for i in ids]

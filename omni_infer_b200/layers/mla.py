@@ -1,0 +1,102 @@
+"""Multi-head Latent Attention (DeepSeek-V2/V3).
+
+Prefill runs the non-absorbed form (q 192-wide, k = [k_nope | k_pe], v 128-wide, causal varlen); decode
+runs the absorbed form over the paged latent cache: ``q_abs = q_nope @ W_UK``, scores against the
+576-wide cache rows, output in latent space, then ``@ W_UV`` and o_proj
+(omni/models/common/layers/attention/deepseek_mla.py:209-235, 269-410, 412-661).
+The latent cache of a layer is one tensor [blocks, block_size, kv_lora + rope]."""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .. import ops
+
+from .common import AttnMetadata, Linear, RMSNorm
+
+
+class MLAAttention(nn.Module):
+    def __init__(self, cfg, layer_idx: int, *, dtype, device=None, cos_sin=None):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        H = cfg.num_attention_heads
+        self.H = H
+        self.nope, self.rope, self.vd = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        self.kvl = cfg.kv_lora_rank
+        self.qk = self.nope + self.rope
+        self.scale = cfg.softmax_scale
+        quant = cfg.quantization if cfg.quantization == "fp8_block" else "none"
+        self.quant = quant
+        hs = cfg.hidden_size
+        self.q_lora = cfg.q_lora_rank
+        if self.q_lora:
+            # merged q_a + kv_a projection: both read the same normalised hidden state
+            self.fused_qkv_a_proj = Linear(hs, self.q_lora + self.kvl + self.rope, dtype=dtype, quant=quant, device=device)
+            self.q_a_layernorm = RMSNorm(self.q_lora, cfg.rms_norm_eps, dtype, device)
+            self.q_b_proj = Linear(self.q_lora, H * self.qk, dtype=dtype, quant=quant, device=device)
+        else:
+            self.fused_qkv_a_proj = Linear(hs, H * self.qk + self.kvl + self.rope, dtype=dtype, quant=quant, device=device)
+        self.kv_a_layernorm = RMSNorm(self.kvl, cfg.rms_norm_eps, dtype, device)
+        # kept unquantised: the absorbed decode path multiplies activations by slices of it
+        self.kv_b_proj = Linear(self.kvl, H * (self.nope + self.vd), dtype=dtype, quant="none", device=device)
+        self.o_proj = Linear(H * self.vd, hs, dtype=dtype, quant=quant, device=device)
+        self.cos_sin = cos_sin
+        self.w_uk = None   # [H, kvl, nope]   (N = kvl, K = nope)
+        self.w_uv = None   # [H, vd, kvl]     (N = vd,  K = kvl)
+
+    def process_weights_after_loading(self):
+        w = self.kv_b_proj.weight.view(self.H, self.nope + self.vd, self.kvl)
+        self.w_uk = w[:, : self.nope, :].transpose(1, 2).contiguous()
+        self.w_uv = w[:, self.nope:, :].contiguous()
+
+    # ------------------------------------------------------------------ projections
+    def _project(self, x, xq, md: AttnMetadata, kv_cache, decode: bool):
+        T = x.shape[0]
+        H = self.H
+        a = self.fused_qkv_a_proj(x, xq=xq)
+        if self.q_lora:
+            q_a = a[:, : self.q_lora]
+            latent = a[:, self.q_lora:]
+            if self.quant == "fp8_block":
+                _, qa_q, qa_s = self.q_a_layernorm(q_a, quant=True)
+                q = self.q_b_proj(None, xq=(qa_q, qa_s))
+            else:
+                q = self.q_b_proj(self.q_a_layernorm(q_a))
+        else:
+            q = a[:, : H * self.qk].contiguous()
+            latent = a[:, H * self.qk:]
+        q = q.view(T, H, self.qk)
+        return q, latent
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x, md: AttnMetadata, kv_cache, xq=None):
+        if md.is_prefill:
+            return self._forward_prefill(x, xq, md, kv_cache)
+        return self._forward_decode(x, xq, md, kv_cache)
+
+    def _forward_prefill(self, x, xq, md, kv_cache):
+        T, H = x.shape[0], self.H
+        q, latent = self._project(x, xq, md, kv_cache, decode=False)
+        lat = ops.mla_kv_rope_cache(latent, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, self.cos_sin,
+                                    md.positions, md.slot_mapping, kv_cache, q=q, q_rope_off=self.nope,
+                                    want_latent=True)
+        if md.kv_gather_slots is not None:
+            # prefix-cache / chunked prefill: attend over the whole cached context of each request
+            lat = kv_cache.view(-1, kv_cache.shape[-1])[md.kv_gather_slots, : self.kvl + self.rope]
+        kv = self.kv_b_proj(lat[:, : self.kvl].contiguous() if not lat.is_cuda else lat[:, : self.kvl])
+        o = ops.attention.mla_prefill(q, kv, lat, H, self.nope, self.rope, self.vd, md.cu_q, md.cu_k, self.scale,
+                                      md.max_q, md.max_k)
+        return self.o_proj(o.reshape(T, H * self.vd))
+
+    def _forward_decode(self, x, xq, md, kv_cache):
+        T, H = x.shape[0], self.H
+        q, latent = self._project(x, xq, md, kv_cache, decode=True)
+        q_abs = torch.empty(T, H, self.kvl + self.rope, dtype=x.dtype, device=x.device)
+        ops.bmm_heads(q[:, :, : self.nope], self.w_uk, out=q_abs)
+        ops.mla_kv_rope_cache(latent, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, self.cos_sin, md.positions,
+                              md.slot_mapping, kv_cache, q=q, q_rope_off=self.nope, q_out=q_abs, q_out_off=self.kvl)
+        o_lat = ops.mla_decode(q_abs, kv_cache, md.block_table, md.q_seq_lens, self.scale, q_to_seq=md.q_to_seq,
+                               max_seq_len=md.max_seq_len, kv_lora=self.kvl)
+        o = ops.bmm_heads(o_lat, self.w_uv)
+        return self.o_proj(o.reshape(T, H * self.vd))

@@ -1,0 +1,120 @@
+"""Mixture-of-experts layer: fp32 gate, (grouped) top-k routing with logical->physical remap,
+expert-parallel dispatch, grouped expert GEMMs with fused SwiGLU(+quant), combine, shared experts.
+
+Mirrors DeepseekMoE / FusedMoE of the reference (omni/models/common/layers/moe/deepseek_moe.py:121-541,
+omni/models/common/layers/moe/fused_moe/layer.py:169-365).  Expert-parallel data paths:
+
+* ``ep_size == 1``  local permutation (csrc/kernels/moe_route.cu)
+* ``nccl``          all-to-all over NCCL: the unfused baseline
+* ``fused``         one dispatch kernel (quantise + NVLink peer stores + counts) and a combine whose reduce
+                    reads peer memory (csrc/kernels/ep_dispatch_combine.cu)
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..ops import FP8
+from ..parallel import get_parallel_state
+from .common import Linear, SwiGLUMLP
+
+
+class MoEGate(nn.Module):
+    def __init__(self, cfg, dtype, device=None):
+        super().__init__()
+        self.cfg = cfg
+        E = cfg.n_routed_experts
+        # gate weights stay in the activation dtype; logits come out of the GEMM in fp32
+        self.weight = nn.Parameter(torch.empty(E, cfg.hidden_size, dtype=dtype, device=device), requires_grad=False)
+        self.e_score_correction_bias = (
+            nn.Parameter(torch.zeros(E, dtype=torch.float32, device=device), requires_grad=False)
+            if cfg.topk_method == "noaux_tc" else None)
+
+    def logits(self, x):
+        return ops.gemm(x, self.weight, out_dtype=torch.float32)
+
+
+class MoELayer(nn.Module):
+    def __init__(self, cfg, layer_idx: int, *, dtype, device=None, planner=None, ep_backend: str = "auto"):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        self.moe_index = layer_idx - cfg.first_k_dense_replace
+        ps = get_parallel_state()
+        self.ep_size, self.ep_rank = ps.ep_size, ps.ep_rank
+        self.planner = planner
+        E = cfg.n_routed_experts
+        redundant = planner.num_redundant_per_rank if planner is not None else 0
+        assert E % self.ep_size == 0
+        self.slots_per_rank = E // self.ep_size + redundant
+        self.num_physical = self.slots_per_rank * self.ep_size
+        self.e_lo = self.ep_rank * self.slots_per_rank
+        quant = cfg.quantization if cfg.quantization == "fp8_block" else "none"
+        self.quant = quant
+        H, I = cfg.hidden_size, cfg.moe_intermediate_size
+        self.gate = MoEGate(cfg, dtype, device)
+        wdt = FP8 if quant == "fp8_block" else dtype
+        S = self.slots_per_rank
+        self.w13 = nn.Parameter(torch.empty(S, 2 * I, H, dtype=wdt, device=device), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(S, H, I, dtype=wdt, device=device), requires_grad=False)
+        if quant == "fp8_block":
+            self.w13_scale = nn.Parameter(torch.ones(S, 2 * I // 128, H // 128, dtype=torch.float32, device=device),
+                                          requires_grad=False)
+            self.w2_scale = nn.Parameter(torch.ones(S, H // 128, (I + 127) // 128, dtype=torch.float32, device=device),
+                                         requires_grad=False)
+        else:
+            self.w13_scale = self.w2_scale = None
+        self.shared_experts = (SwiGLUMLP(H, I * cfg.n_shared_experts, dtype=dtype, quant=quant, device=device)
+                               if cfg.n_shared_experts > 0 else None)
+        self.ep_backend = ep_backend
+        self.ep_ctx = None          # set by the model runner when the fused NVLink path is enabled
+        self.forced_balance = False
+        self.routing_bias_override = None   # benchmark aid: fixed per-layer logit bias (load-skew stress)
+
+    # ------------------------------------------------------------------ routing
+    def route(self, x, num_valid=None):
+        cfg = self.cfg
+        logits = self.gate.logits(x)
+        if self.routing_bias_override is not None:
+            logits = logits + self.routing_bias_override
+        selector = counts = None
+        if self.planner is not None:
+            selector = self.planner.selector(self.moe_index)
+            counts = self.planner.activation_counts(self.moe_index)
+        if cfg.topk_method == "noaux_tc":
+            kw = dict(mode="sigmoid", bias=self.gate.e_score_correction_bias, n_group=cfg.n_group,
+                      topk_group=cfg.topk_group, group_mode="top2sum", renorm=cfg.norm_topk_prob,
+                      scale=cfg.routed_scaling_factor)
+        elif cfg.topk_method == "group_limited_greedy":
+            kw = dict(mode=cfg.scoring_func, n_group=cfg.n_group, topk_group=cfg.topk_group, group_mode="max",
+                      renorm=cfg.norm_topk_prob, scale=cfg.routed_scaling_factor)
+        else:
+            kw = dict(mode=cfg.scoring_func, renorm=cfg.norm_topk_prob, scale=cfg.routed_scaling_factor)
+        return ops.router_topk(logits, cfg.num_experts_per_tok, selector=selector, counts=counts,
+                               forced_balance=self.forced_balance, num_valid=num_valid, **kw)
+
+    # ------------------------------------------------------------------ expert compute on sorted rows
+    def experts(self, xs, x_scale, seg_start, seg_len, row_w, t_hint):
+        if self.quant == "fp8_block":
+            aq, ascale = ops.gemm(xs, self.w13, w_scale=self.w13_scale, x_scale=x_scale, seg_start=seg_start,
+                                  seg_len=seg_len, epi="swiglu_quant", t_hint=t_hint)
+            return ops.gemm(aq, self.w2, w_scale=self.w2_scale, x_scale=ascale, seg_start=seg_start, seg_len=seg_len,
+                            row_scale=row_w, t_hint=t_hint)
+        act = ops.gemm(xs, self.w13, seg_start=seg_start, seg_len=seg_len, epi="swiglu", t_hint=t_hint)
+        return ops.gemm(act, self.w2, seg_start=seg_start, seg_len=seg_len, row_scale=row_w, t_hint=t_hint)
+
+    def forward(self, x, xq=None, num_valid=None):
+        T = x.shape[0]
+        k = self.cfg.num_experts_per_tok
+        ids, w = self.route(x, num_valid)
+        shared = self.shared_experts(x, xq=xq) if self.shared_experts is not None else None
+        if self.ep_size == 1:
+            perm = ops.moe_permute(x, ids, w, self.e_lo, self.slots_per_rank, quant=self.quant == "fp8_block")
+            t_hint = max(16, (T * k + self.slots_per_rank - 1) // self.slots_per_rank)
+            y = self.experts(perm.x, perm.x_scale, perm.seg_start, perm.seg_len, perm.row_w, t_hint)
+            return ops.moe_combine(y, perm.row_of, T, k, shared=shared)
+        if self.ep_ctx is not None:
+            return self.ep_ctx.moe_forward(self, x, ids, w, shared)
+        from ..parallel.ep_nccl import moe_forward_nccl
+        return moe_forward_nccl(self, x, ids, w, shared)

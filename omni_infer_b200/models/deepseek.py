@@ -1,0 +1,120 @@
+"""DeepSeek-V2 / V3 / R1 (MLA + MoE) decoder stack.
+
+Counterpart of the reference's DeepseekDecoderLayer / DeepseekV3Model / DeepseekV3ForCausalLM
+(omni/models/deepseek/deepseek_v3.py:139-460, 698-895) and CustomDeepseekV2ForCausalLM
+(omni/models/deepseek/deepseek_v2.py:78-685).  One class serves both generations: V2-Lite has no q LoRA
+and softmax routing, V3 has q LoRA, sigmoid + bias group-limited routing and block-scaled e4m3 weights.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..layers.common import AttnMetadata, Linear, RMSNorm, SwiGLUMLP, _dtype
+from ..layers.mla import MLAAttention
+from ..layers.moe import MoELayer
+from .config import ModelConfig
+
+
+class DeepseekDecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, *, dtype, device, cos_sin, planner=None, force_moe=None):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.quant = cfg.quantization == "fp8_block"
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.self_attn = MLAAttention(cfg, layer_idx, dtype=dtype, device=device, cos_sin=cos_sin)
+        is_moe = cfg.layer_is_moe(layer_idx) if force_moe is None else force_moe
+        if is_moe:
+            self.mlp = MoELayer(cfg, layer_idx, dtype=dtype, device=device, planner=planner)
+        else:
+            q = cfg.quantization if self.quant else "none"
+            self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, quant=q, device=device)
+        self.is_moe = is_moe
+
+    def forward(self, h, residual, md: AttnMetadata, kv_cache):
+        if residual is None:
+            residual = h.clone()
+            n = self.input_layernorm(h, quant=self.quant)
+        else:
+            n = self.input_layernorm(h, residual=residual, quant=self.quant)
+        x, xq = (n[0], (n[1], n[2])) if self.quant else (n, None)
+        a = self.self_attn(x, md, kv_cache, xq=xq)
+        n = self.post_attention_layernorm(a, residual=residual, quant=self.quant)
+        x, xq = (n[0], (n[1], n[2])) if self.quant else (n, None)
+        if self.is_moe:
+            out = self.mlp(x, xq=xq, num_valid=md.num_valid)
+        else:
+            out = self.mlp(x, xq=xq)
+        return out, residual
+
+
+class DeepseekModel(nn.Module):
+    def __init__(self, cfg: ModelConfig, *, device=None, planner=None, num_layers: Optional[int] = None):
+        super().__init__()
+        self.cfg = cfg
+        dtype = _dtype(cfg.dtype)
+        self.dtype = dtype
+        self.cos_sin = ops.rope_cos_sin_table(cfg.qk_rope_head_dim, min(cfg.max_position_embeddings, 163840),
+                                              cfg.rope_theta, cfg.rope_scaling, device=device or "cpu")
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        self.embed_tokens.weight.requires_grad_(False)
+        n = cfg.num_hidden_layers if num_layers is None else num_layers
+        self.layers = nn.ModuleList([
+            DeepseekDecoderLayer(cfg, i, dtype=dtype, device=device, cos_sin=self.cos_sin, planner=planner)
+            for i in range(n)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+
+    def forward(self, input_ids, md: AttnMetadata, kv_caches, inputs_embeds=None):
+        h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
+        residual = None
+        for i, layer in enumerate(self.layers):
+            h, residual = layer(h, residual, md, kv_caches[i])
+        return self.norm(h, residual=residual)
+
+
+class DeepseekV3ForCausalLM(nn.Module):
+    """Returns hidden states from ``forward`` and logits from ``compute_logits`` (the model runner keeps
+    the hidden states for the MTP drafters)."""
+    is_mla = True
+
+    def __init__(self, cfg: ModelConfig, *, device=None, planner=None):
+        super().__init__()
+        self.cfg = cfg
+        self.model = DeepseekModel(cfg, device=device, planner=planner)
+        dtype = self.model.dtype
+        if cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
+
+    @property
+    def num_kv_layers(self) -> int:
+        return len(self.model.layers)
+
+    def forward(self, input_ids, md: AttnMetadata, kv_caches, inputs_embeds=None):
+        return self.model(input_ids, md, kv_caches, inputs_embeds)
+
+    def compute_logits(self, hidden):
+        w = self.lm_head.weight if self.lm_head is not None else self.model.embed_tokens.weight
+        return ops.gemm(hidden, w, out_dtype=torch.float32)
+
+    def process_weights_after_loading(self):
+        for layer in self.model.layers:
+            layer.self_attn.process_weights_after_loading()
+
+    def should_use_eager_mode(self, md: AttnMetadata) -> bool:
+        """Prefill runs eagerly, decode-only steps replay CUDA graphs
+        (omni/models/deepseek/deepseek_v3.py:897-908)."""
+        return md.is_prefill
+
+    # ------------------------------------------------------------------ checkpoint loading
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]], planner=None) -> set:
+        from ..quantization.loader import WeightLoader
+        return WeightLoader(self, self.cfg, planner=planner).load(weights)
+
+
+DeepseekV2ForCausalLM = DeepseekV3ForCausalLM

@@ -1,0 +1,96 @@
+"""Qwen2 (dense GQA, omni/models/qwen/qwen2.py:60-566) and Qwen3-MoE-style GQA MoE models."""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..layers.common import AttnMetadata, Linear, RMSNorm, SwiGLUMLP, _dtype
+from ..layers.gqa import GQAAttention
+from ..layers.moe import MoELayer
+from .config import ModelConfig
+
+
+class QwenDecoderLayer(nn.Module):
+    def __init__(self, cfg, layer_idx, *, dtype, device, cos_sin, planner=None):
+        super().__init__()
+        self.quant = cfg.quantization == "fp8_block"
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.self_attn = GQAAttention(cfg, layer_idx, dtype=dtype, device=device, cos_sin=cos_sin)
+        self.is_moe = cfg.layer_is_moe(layer_idx)
+        if self.is_moe:
+            self.mlp = MoELayer(cfg, layer_idx, dtype=dtype, device=device, planner=planner)
+        else:
+            self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype=dtype,
+                                 quant=cfg.quantization if self.quant else "none", device=device)
+
+    def forward(self, h, residual, md, kv_cache):
+        if residual is None:
+            residual = h.clone()
+            n = self.input_layernorm(h, quant=self.quant)
+        else:
+            n = self.input_layernorm(h, residual=residual, quant=self.quant)
+        x, xq = (n[0], (n[1], n[2])) if self.quant else (n, None)
+        a = self.self_attn(x, md, kv_cache, xq=xq)
+        n = self.post_attention_layernorm(a, residual=residual, quant=self.quant)
+        x, xq = (n[0], (n[1], n[2])) if self.quant else (n, None)
+        out = self.mlp(x, xq=xq, num_valid=md.num_valid) if self.is_moe else self.mlp(x, xq=xq)
+        return out, residual
+
+
+class QwenModel(nn.Module):
+    def __init__(self, cfg: ModelConfig, *, device=None, planner=None):
+        super().__init__()
+        self.cfg = cfg
+        dtype = _dtype(cfg.dtype)
+        self.dtype = dtype
+        self.cos_sin = ops.rope_cos_sin_table(cfg.head_dim, min(cfg.max_position_embeddings, 131072), cfg.rope_theta,
+                                              cfg.rope_scaling, device=device or "cpu")
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        self.embed_tokens.weight.requires_grad_(False)
+        self.layers = nn.ModuleList([QwenDecoderLayer(cfg, i, dtype=dtype, device=device, cos_sin=self.cos_sin,
+                                                      planner=planner) for i in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+
+    def forward(self, input_ids, md, kv_caches, inputs_embeds=None):
+        h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
+        residual = None
+        for i, layer in enumerate(self.layers):
+            h, residual = layer(h, residual, md, kv_caches[i])
+        return self.norm(h, residual=residual)
+
+
+class Qwen2ForCausalLM(nn.Module):
+    is_mla = False
+
+    def __init__(self, cfg: ModelConfig, *, device=None, planner=None):
+        super().__init__()
+        self.cfg = cfg
+        self.model = QwenModel(cfg, device=device, planner=planner)
+        self.lm_head = None if cfg.tie_word_embeddings else Linear(cfg.hidden_size, cfg.vocab_size,
+                                                                   dtype=self.model.dtype, device=device)
+
+    @property
+    def num_kv_layers(self):
+        return len(self.model.layers)
+
+    def forward(self, input_ids, md, kv_caches, inputs_embeds=None):
+        return self.model(input_ids, md, kv_caches, inputs_embeds)
+
+    def compute_logits(self, hidden):
+        w = self.lm_head.weight if self.lm_head is not None else self.model.embed_tokens.weight
+        return ops.gemm(hidden, w, out_dtype=torch.float32)
+
+    def process_weights_after_loading(self):
+        pass
+
+    def should_use_eager_mode(self, md):
+        return md.is_prefill
+
+    def load_weights(self, weights, planner=None) -> set:
+        from ..quantization.loader import WeightLoader
+        return WeightLoader(self, self.cfg, planner=planner).load(weights)
+
+
+Qwen3MoeForCausalLM = Qwen2ForCausalLM

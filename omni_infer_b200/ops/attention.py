@@ -8,12 +8,12 @@ from . import _native as nat
 
 
 # ----------------------------------------------------------------------------- MLA decode
-def mla_decode_ref(q, cache, block_table, seq_lens, scale, q_to_seq=None):
-    """q [Bq, H, 576]; cache [blocks, block, >=576]; returns [Bq, H, 512] (latent space)."""
-    Bq, H, _ = q.shape
+def mla_decode_ref(q, cache, block_table, seq_lens, scale, q_to_seq=None, kv_lora=512):
+    """q [Bq, H, kv_lora+rope]; cache [blocks, block, >=kv_lora+rope]; returns [Bq, H, kv_lora] (latent space)."""
+    Bq, H, D = q.shape
     bs = cache.shape[1]
-    out = torch.zeros(Bq, H, 512, dtype=torch.float32, device=q.device)
-    flat = cache.reshape(-1, cache.shape[-1])[:, :576].float()
+    out = torch.zeros(Bq, H, kv_lora, dtype=torch.float32, device=q.device)
+    flat = cache.reshape(-1, cache.shape[-1])[:, :D].float()
     for b in range(Bq):
         L = int(seq_lens[b])
         if L == 0:
@@ -24,7 +24,7 @@ def mla_decode_ref(q, cache, block_table, seq_lens, scale, q_to_seq=None):
         kv = flat[slots]
         s = (q[b].float() @ kv.t()) * scale
         p = torch.softmax(s, dim=-1)
-        out[b] = p @ kv[:, :512]
+        out[b] = p @ kv[:, :kv_lora]
     return out.to(q.dtype)
 
 
@@ -41,12 +41,13 @@ def _mla_scratch(dev, n_o, n_l):
     return buf
 
 
-def mla_decode(q, cache, block_table, seq_lens, scale, q_to_seq=None, num_splits=0, max_seq_len=None):
+def mla_decode(q, cache, block_table, seq_lens, scale, q_to_seq=None, num_splits=0, max_seq_len=None, kv_lora=512):
     """Absorbed MLA decode attention.  ``seq_lens[b]`` is the number of cache tokens q row b attends to
     (MTP rows of one request get consecutive lengths); ``q_to_seq`` maps q rows to block-table rows."""
     if not q.is_cuda:
-        return mla_decode_ref(q, cache, block_table, seq_lens, scale, q_to_seq)
+        return mla_decode_ref(q, cache, block_table, seq_lens, scale, q_to_seq, kv_lora)
     Bq, H, D = q.shape
+    assert D == 576 and kv_lora == 512, "the sm_100a kernel is specialised for kv_lora 512 + rope 64"
     assert D == 576 and q.is_contiguous() and q.dtype == torch.bfloat16
     bs = cache.shape[1]
     cache2 = cache.view(-1, cache.shape[-1])
@@ -118,3 +119,43 @@ def gqa_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale):
         p = torch.softmax(s, dim=-1)
         out[b] = torch.einsum("hl,hld->hd", p, vv)
     return out.to(q.dtype)
+
+
+def mla_prefill_ref(q, kv, lat, H, nope, rope, vd, cu_q, cu_k, scale):
+    """Non-absorbed MLA prefill: q [Tq, H, nope+rope] (rope already applied), kv [Tk, H*(nope+vd)] = per head
+    k_nope | v, lat [Tk, kv_lora+rope] whose last ``rope`` columns are the shared roped k_pe."""
+    Tk = kv.shape[0]
+    kvh = kv.view(Tk, H, nope + vd)
+    k_pe = lat[:, -rope:].unsqueeze(1).expand(Tk, H, rope)
+    k = torch.cat([kvh[:, :, :nope], k_pe.to(kv.dtype)], dim=-1)
+    v = kvh[:, :, nope:]
+    return attn_prefill_ref(q, k, v, cu_q, cu_k, scale, causal=True)
+
+
+def mla_prefill(q, kv, lat, H, nope, rope, vd, cu_q, cu_k, scale, max_q, max_k):
+    if not q.is_cuda:
+        return mla_prefill_ref(q, kv, lat, H, nope, rope, vd, cu_q, cu_k, scale)
+    from .fmha import fmha_varlen
+    kvl = lat.shape[1] - rope
+    return fmha_varlen(q.view(q.shape[0], H * (nope + rope)), kv, kv, cu_q, cu_k, scale, Hq=H, Hkv=H,
+                       q_head_stride=nope + rope, k_head_stride=nope + vd, v_head_stride=nope + vd, v_col0=nope,
+                       d_k1=nope, k2=lat, k2_col0=kvl, d_k2=rope, d_v=vd, max_q=max_q, max_k=max_k, causal=True)
+
+
+def gqa_prefill(q, k, v, cu_q, cu_k, scale, max_q, max_k):
+    """q [Tq, Hq, D], k/v [Tk, Hkv, D] (views allowed), causal varlen."""
+    if not q.is_cuda:
+        return attn_prefill_ref(q, k, v, cu_q, cu_k, scale, causal=True)
+    from .fmha import fmha_varlen
+    Tq, Hq, D = q.shape
+    Hkv = k.shape[1]
+    return fmha_varlen(q, k, v, cu_q, cu_k, scale, Hq=Hq, Hkv=Hkv, q_head_stride=q.stride(1), k_head_stride=k.stride(1),
+                       v_head_stride=v.stride(1), v_col0=0, d_k1=D, k2=None, k2_col0=0, d_k2=0, d_v=D, max_q=max_q,
+                       max_k=max_k, causal=True)
+
+
+def gqa_decode(q, k_cache, v_cache, block_table, seq_lens, scale, max_seq_len=None):
+    if not q.is_cuda:
+        return gqa_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale)
+    from .fmha import gqa_paged_decode
+    return gqa_paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale, max_seq_len)

@@ -145,18 +145,20 @@ def rope_neox_ref(x, cos_sin, positions):
 # ----------------------------------------------------------------------------- MLA latent write
 def mla_kv_rope_cache_ref(latent, kv_weight, eps, cos_sin, positions, slots, cache, q=None, q_rope_off=0,
                           q_out=None, q_out_off=0):
-    ckv = rmsnorm_ref(latent[:, :512], kv_weight, eps)
-    kpe = rope_interleaved_ref(latent[:, 512:576], cos_sin, positions)
+    kvl = kv_weight.shape[0]
+    rd = cos_sin.shape[1]
+    ckv = rmsnorm_ref(latent[:, :kvl], kv_weight, eps)
+    kpe = rope_interleaved_ref(latent[:, kvl:kvl + rd], cos_sin, positions)
     row = torch.cat([ckv, kpe], dim=-1)
     ok = slots >= 0
     if cache is not None:
-        cache.view(-1, cache.shape[-1])[slots[ok], :576] = row[ok].to(cache.dtype)
+        cache.view(-1, cache.shape[-1])[slots[ok], :kvl + rd] = row[ok].to(cache.dtype)
     if q is not None:
-        rot = rope_interleaved_ref(q[..., q_rope_off:q_rope_off + 64], cos_sin, positions)
+        rot = rope_interleaved_ref(q[..., q_rope_off:q_rope_off + rd], cos_sin, positions)
         if q_out is not None:
-            q_out[..., q_out_off:q_out_off + 64] = rot
+            q_out[..., q_out_off:q_out_off + rd] = rot
         else:
-            q[..., q_rope_off:q_rope_off + 64] = rot
+            q[..., q_rope_off:q_rope_off + rd] = rot
     return row
 
 
@@ -170,6 +172,7 @@ def mla_kv_rope_cache(latent, kv_weight, eps, cos_sin, positions, slots, cache, 
         return mla_kv_rope_cache_ref(latent, kv_weight, eps, cos_sin, positions, slots, cache, q, q_rope_off,
                                      q_out, q_out_off)
     T = latent.shape[0]
+    assert kv_weight.shape[0] == 512 and cos_sin.shape[1] == 64, "the sm_100a kernel is specialised for 512 + 64"
     out = torch.empty(T, 576, dtype=latent.dtype, device=latent.device) if want_latent else None
     heads = q.shape[1] if q is not None else 0
     qhd = q.shape[2] if q is not None else 0

@@ -1,0 +1,69 @@
+"""End-to-end on CPU: the engine (scheduler + paged latent cache + absorbed decode + fused-layout ops)
+must reproduce the naive fp32 oracle token for token (tiny DeepSeek-V3-style MLA+MoE, 4 prompts of 32
+tokens, 16 greedy tokens)."""
+import torch
+
+from omni_infer_b200.engine.engine_core import LLM, EngineConfig, EngineCore
+from omni_infer_b200.engine.request import SamplingParams
+from omni_infer_b200.models.reference_fp32 import ReferenceDeepseek
+
+
+def _prompts(n=4, length=32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 1024, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _oracle(llm, prompts, n):
+    ref = ReferenceDeepseek(llm.engine.model_cfg, llm.engine.worker.runner.model.state_dict())
+    return [ref.greedy(p, n) for p in prompts]
+
+
+def test_tiny_deepseek_token_exact():
+    llm = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu")
+    prompts = _prompts()
+    outs = llm.generate(prompts, SamplingParams(max_tokens=16))
+    assert outs == _oracle(llm, prompts, 16)
+
+
+def test_multi_step_and_chunked_prefill_match():
+    prompts = _prompts(3, 40, seed=1)
+    base = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu")
+    want = base.generate(prompts, SamplingParams(max_tokens=12))
+    multi = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu", num_step=4)
+    assert multi.generate(prompts, SamplingParams(max_tokens=12)) == want
+    chunk = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu",
+                enable_chunked_prefill=True, max_num_batched_tokens=24)
+    assert chunk.generate(prompts, SamplingParams(max_tokens=12)) == want
+    asyn = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu",
+               async_schedule=True)
+    assert asyn.generate(prompts, SamplingParams(max_tokens=12)) == want
+
+
+def test_prefix_caching_and_preemption_match():
+    prompts = _prompts(2, 48, seed=2)
+    prompts.append(prompts[0][:32] + [5, 6, 7, 8])       # shares two full blocks with prompt 0
+    base = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu")
+    want = base.generate(prompts, SamplingParams(max_tokens=10))
+    pc = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu",
+             enable_prefix_caching=True, max_num_seqs=2)
+    assert pc.generate(prompts, SamplingParams(max_tokens=10)) == want
+    assert any(r.num_cached_tokens > 0 for r in pc.engine.scheduler.requests.values())
+    # 10 usable blocks: the three prompts fit (9 blocks), growth forces a preemption and a recompute
+    tight = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=11, max_model_len=128, device="cpu")
+    assert tight.generate(prompts, SamplingParams(max_tokens=10)) == want
+    assert tight.engine.scheduler.stats["preemptions"] > 0
+
+
+def test_mtp_greedy_equivalence():
+    """Speculative decoding with the MTP drafter never changes greedy output, whatever is accepted."""
+    prompts = _prompts(3, 24, seed=3)
+    over = {"num_nextn_predict_layers": 1}
+    base = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu",
+               model_overrides=over)
+    want = base.generate(prompts, SamplingParams(max_tokens=14))
+    mtp = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu",
+              model_overrides=over, num_speculative_tokens=1)
+    assert mtp.generate(prompts, SamplingParams(max_tokens=14)) == want
+    mtp2 = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu",
+               model_overrides=over, num_speculative_tokens=1, num_step=3)
+    assert mtp2.generate(prompts, SamplingParams(max_tokens=14)) == want
