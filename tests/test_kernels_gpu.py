@@ -240,3 +240,53 @@ def test_mla_decode(H, lens, bs, splits):
     out = A.mla_decode(q, cache, bt, sl, scale, num_splits=splits, max_seq_len=max(lens))
     ref = A.mla_decode_ref(q, cache, bt, sl, scale)
     _close(out, ref, 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("qlens,ctx", [([5, 130, 64], [0, 0, 0]), ([256], [0]), ([17, 100], [40, 0]), ([1, 1], [300, 5])])
+def test_fmha_mla_prefill(qlens, ctx):
+    """Non-absorbed MLA prefill: q 192 wide, k = kv_b slice | shared roped k_pe, v = kv_b slice."""
+    torch.manual_seed(9)
+    H, nope, rope, vd = 4, 128, 64, 128
+    klens = [q + c for q, c in zip(qlens, ctx)]
+    Tq, Tk = sum(qlens), sum(klens)
+    q = (torch.randn(Tq, H, nope + rope, device=DEV) * 0.5).bfloat16()
+    kv = (torch.randn(Tk, H * (nope + vd), device=DEV) * 0.5).bfloat16()
+    lat = (torch.randn(Tk, 576, device=DEV) * 0.5).bfloat16()
+    cu_q = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(klens).cumsum(0)), dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(192)
+    out = A.mla_prefill(q, kv, lat, H, nope, rope, vd, cu_q, cu_k, scale, max(qlens), max(klens))
+    ref = A.mla_prefill_ref(q, kv, lat, H, nope, rope, vd, cu_q, cu_k, scale)
+    _close(out, ref, 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("qlens", [[9, 200], [128, 1, 77]])
+def test_fmha_gqa_prefill(qlens):
+    torch.manual_seed(10)
+    Hq, Hkv, D = 8, 2, 128
+    T = sum(qlens)
+    qkv = (torch.randn(T, Hq + 2 * Hkv, D, device=DEV) * 0.5).bfloat16()
+    q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:]
+    cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    out = A.gqa_prefill(q, k, v, cu, cu, scale, max(qlens), max(qlens))
+    ref = A.attn_prefill_ref(q, k, v, cu, cu, scale)
+    _close(out, ref, 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("lens,splits", [([1, 33, 500], 1), ([2000, 64], 4), ([0, 77], 0)])
+def test_gqa_paged_decode(lens, splits):
+    torch.manual_seed(11)
+    B_, Hq, Hkv, D, bs = len(lens), 32, 4, 128, 16
+    max_blocks = (max(lens) + bs - 1) // bs + 1
+    nb = B_ * max_blocks + 1
+    kc = (torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5).bfloat16()
+    vc = (torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5).bfloat16()
+    bt = (torch.randperm(nb - 1, device=DEV)[: B_ * max_blocks].int() + 1).view(B_, max_blocks).contiguous()
+    q = (torch.randn(B_, Hq, D, device=DEV) * 0.5).bfloat16()
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    from omni_infer_b200.ops.fmha import gqa_paged_decode
+    out = gqa_paged_decode(q, kc, vc, bt, sl, scale, max(lens), num_splits=splits)
+    ref = A.gqa_decode_ref(q, kc, vc, bt, sl, scale)
+    _close(out, ref, 3e-2, 2e-2)
