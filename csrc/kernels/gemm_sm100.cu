@@ -11,7 +11,8 @@
 // One persistent CTA per SM, three roles:
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocation + MMA issue (one lane)
-//   warps 2..5  epilogue: tcgen05.ld of the accumulator lanes, scaling, activation, stores
+//   warps 2..9  epilogue (two groups of four, each group owns half of the token columns): tcgen05.ld of the
+//               accumulator lanes, scaling, activation, stores
 //
 // Variants (template parameters):
 //   KIND  0 = bf16 operands (accumulate the whole K range in TMEM)
@@ -57,22 +58,42 @@ struct GemmParams {
   OmniStatus* status;
 };
 
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two groups of four)
 constexpr int MAX_GROUPS = 1024;
 constexpr int SMEM_BUDGET = 225 * 1024;
+constexpr int MAX_STAGES = 10;
 
 template <int BN, int NACC>
 struct GemmSmem {
   static constexpr int A_BYTES = 128 * 128;          // 128 weight rows x 128 B
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = NACC * A_BYTES + B_BYTES;
-  static constexpr int AUX_BYTES = 1024 /*barriers*/ + (MAX_GROUPS + 1) * 4 + 4 * 256 * 4 /*amax exchange*/;
+  static constexpr int SC_BYTES = MAX_STAGES * BN * 4;   // activation-scale ring (fp8 kind)
+  static constexpr int PREFIX_BYTES = (MAX_GROUPS + 4) * 4;   // G+1 ints, padded so what follows stays 16-byte aligned
+  static constexpr int AUX_BYTES = 1024 /*barriers*/ + PREFIX_BYTES + 1024 /*amax exchange*/ + SC_BYTES;
   static constexpr int STAGES_RAW = (SMEM_BUDGET - AUX_BYTES - 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+  static constexpr int STAGES = STAGES_RAW > MAX_STAGES ? MAX_STAGES : STAGES_RAW;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
 };
 
 enum { SITE_PROD_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_TMEM_EMPTY = 3, SITE_EPI_TMEM_FULL = 4 };
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// packed fp32 pair arithmetic (two lanes per instruction)
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
+  return d;
+}
+__device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(reinterpret_cast<uint64_t&>(acc))
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
+}
 
 template <int KIND, int BN, int NACC, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -82,24 +103,27 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   constexpr int STAGES = L::STAGES;
   constexpr int BK_ELEMS = (KIND == 0) ? 64 : 128;       // one 128-byte swizzle span
   constexpr int ACC_COLS = NACC * BN;                    // TMEM columns of one accumulator buffer
+  constexpr int CW = BN / 2;                             // token columns owned by one epilogue group
   constexpr int TMEM_COLS_RAW = 2 * ACC_COLS;
   constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128
                             : TMEM_COLS_RAW <= 256 ? 256 : 512;
   static_assert(TMEM_COLS_RAW <= 512, "accumulators exceed TMEM");
-  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "invalid UMMA N");
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "invalid token tile");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* aux = smem + STAGES * L::STAGE_BYTES;
   uint64_t* full_bar = (uint64_t*)aux;                   // [STAGES]
-  uint64_t* empty_bar = full_bar + STAGES;               // [STAGES]
-  uint64_t* tfull_bar = empty_bar + STAGES;              // [2]
+  uint64_t* empty_bar = full_bar + MAX_STAGES;           // [STAGES]
+  uint64_t* tfull_bar = empty_bar + MAX_STAGES;          // [2]
   uint64_t* tempty_bar = tfull_bar + 2;                  // [2]
   uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* epi_counter = (int*)(tmem_slot + 2);              // [2] one per epilogue group
   int* tile_prefix = (int*)(aux + 1024);                 // [G + 1]
-  float* amax_x = (float*)(aux + 1024 + (MAX_GROUPS + 1) * 4);  // [2][4][16]
-  int* epi_counter = (int*)(amax_x + 128);
+  float* amax_x = (float*)(aux + 1024 + L::PREFIX_BYTES);  // [2 groups][2 slabs][4 warps][16]
+  float* sc_ring = amax_x + 256;                         // [STAGES][BN], 16-byte aligned (bulk copies, float4 reads)
+  static_assert((1024 + L::PREFIX_BYTES + 1024) % 16 == 0, "scale ring must be 16-byte aligned");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -109,14 +133,15 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], (KIND == 1) ? 9 : 1);     // MMA commit (+ 8 epilogue warps that read the scale ring)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 4);
+      mbar_init(&tempty_bar[b], 8);
     }
     *abort_flag = 0;
-    *epi_counter = 0;
+    epi_counter[0] = 0;
+    epi_counter[1] = 0;
     mbar_fence_init();
     // tiles per group: ceil(len / BN) * m_tiles, token tile fastest
     int acc = 0;
@@ -171,16 +196,20 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         int g, mt, row0, rows;
         decode_tile(tile, g, mt, row0, rows);
         const int wrow = g * p.w_rows_per_group + mt * 128;
+        // activation scales of this tile's rows: [kb][row0 .. row0+BN), clipped to the allocation
+        const int sc_n = (KIND == 1) ? max(0, min(BN, p.x_scale_ld - row0)) : 0;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, SITE_PROD_EMPTY, s)) { ok = false; break; }
           uint8_t* st = smem + s * L::STAGE_BYTES;
-          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES + sc_n * 4);
           tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * BK_ELEMS, wrow, pol_w);
           if (NACC == 2)
             tma_load_2d_hint(st + L::A_BYTES, &tmap_w, &full_bar[s], kb * BK_ELEMS, wrow + p.n_out, pol_w);
           tma_load_2d_hint(st + NACC * L::A_BYTES, &tmap_x, &full_bar[s], kb * BK_ELEMS + g * p.x_group_col, row0, pol_x);
+          if (KIND == 1 && sc_n > 0)
+            bulk_load_1d(sc_ring + s * BN, p.x_scale + (size_t)kb * p.x_scale_ld + row0, sc_n * 4, &full_bar[s]);
         }
       }
     }
@@ -226,7 +255,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 umma_fp8(d0 + BN, umma_desc_kmajor_sw128(sa + L::A_BYTES) + 2 * k, bdesc + 2 * k, idesc, accum);
             }
           }
-          umma_commit(&empty_bar[s]);  // the stage is free once these MMAs retire
+          umma_commit(&empty_bar[s]);  // operands consumed once these MMAs retire
           if (KIND == 1) {
             umma_commit(&tfull_bar[buf]);
             ++acc_it;
@@ -241,9 +270,12 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int grp = (warp - 2) >> 2;        // column half owned by this warp's group
     const int r = q * 32 + lane;            // accumulator lane = weight row inside the tile
+    const int c_lo = grp * CW;              // first token column of this group
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     int acc_it = 0;
+    int it = 0;
     int epi_sync = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -253,39 +285,55 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const bool n_ok = n_in < p.n_out;
       const int n = n_in + g * p.out_group_col;  // output column
 
-      float acc[(KIND == 1) ? NACC * BN : 1];
+      float2 acc[(KIND == 1) ? NACC * CW / 2 : 1];
       if (KIND == 1) {
 #pragma unroll
-        for (int j = 0; j < NACC * BN; ++j) acc[j] = 0.f;
+        for (int j = 0; j < NACC * CW / 2; ++j) acc[j] = make_float2(0.f, 0.f);
         const int sb_per_group = p.w_rows_per_group / 128;
         const float* wsc0 = p.w_scale + ((size_t)g * sb_per_group + mt) * num_kb;
         const float* wsc1 = p.w_scale + ((size_t)g * sb_per_group + mt + p.n_out / 128) * num_kb;
-        for (int kb = 0; kb < num_kb; ++kb, ++acc_it) {
+        for (int kb = 0; kb < num_kb; ++kb, ++acc_it, ++it) {
           const int buf = acc_it & 1;
+          const int s = it % STAGES;
           if (!mbar_wait(&tfull_bar[buf], (acc_it >> 1) & 1, abort_flag, p.status, SITE_EPI_TMEM_FULL, buf)) {
             ok = false; break;
           }
           tc_fence_after();
-          const float sw0 = __ldg(wsc0 + kb);
-          const float sw1 = (NACC == 2) ? __ldg(wsc1 + kb) : 0.f;
-          const float* xs = p.x_scale + (size_t)kb * p.x_scale_ld + row0;
+          // pull this group's columns of the fresh partial product out of TMEM in one round trip
+          uint32_t t[NACC][CW];
 #pragma unroll
           for (int a = 0; a < NACC; ++a) {
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = 0; c0 < CW; c0 += 16) {
               uint32_t v[16];
-              tmem_ld_x16(lane_addr + buf * ACC_COLS + a * BN + c0, v);
-              tmem_ld_wait();
+              tmem_ld_x16(lane_addr + buf * ACC_COLS + a * BN + c_lo + c0, v);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float sx = (c0 + j < rows) ? __ldg(xs + c0 + j) : 0.f;
-                acc[a * BN + c0 + j] = fmaf(__uint_as_float(v[j]), sx * (a == 0 ? sw0 : sw1), acc[a * BN + c0 + j]);
-              }
+              for (int j = 0; j < 16; ++j) t[a][c0 + j] = v[j];
             }
           }
+          const float sw0 = __ldg(wsc0 + kb);
+          const float sw1 = (NACC == 2) ? __ldg(wsc1 + kb) : 0.f;
+          tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+          if (lane == 0) mbar_arrive(&tempty_bar[buf]);   // the MMA may overwrite this buffer now
+          const float4* sc4 = reinterpret_cast<const float4*>(sc_ring + s * BN + c_lo);
+          const float2 w0 = make_float2(sw0, sw0), w1 = make_float2(sw1, sw1);
+#pragma unroll
+          for (int j4 = 0; j4 < CW / 4; ++j4) {
+            const float4 sx = sc4[j4];
+            const float2 sxa = make_float2(sx.x, sx.y), sxb = make_float2(sx.z, sx.w);
+#pragma unroll
+            for (int a = 0; a < NACC; ++a) {
+              const float2 wa = (a == 0) ? w0 : w1;
+              fma2(acc[a * CW / 2 + 2 * j4], make_float2(__uint_as_float(t[a][4 * j4]), __uint_as_float(t[a][4 * j4 + 1])),
+                   mul2(sxa, wa));
+              fma2(acc[a * CW / 2 + 2 * j4 + 1],
+                   make_float2(__uint_as_float(t[a][4 * j4 + 2]), __uint_as_float(t[a][4 * j4 + 3])), mul2(sxb, wa));
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[s]);      // scale ring slot read
         }
         if (!ok) break;
       } else {
@@ -296,27 +344,31 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         tc_fence_after();
       }
 
-      // ---- per-tile output.  `val(a, j)` = accumulator a, token column j ----
+      // ---- per-tile output: this thread owns weight row r and token columns [c_lo, c_lo + CW)
       const int bufc = acc_it & 1;  // bf16 path: buffer holding this tile
+      auto accv = [&](int a, int j) -> float {   // fp8 path: accumulator a, local column j
+        const float2 v = acc[(KIND == 1) ? (a * CW / 2 + (j >> 1)) : 0];
+        return (j & 1) ? v.y : v.x;
+      };
       if (EPI == 0) {
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 16) {
+        for (int c0 = 0; c0 < CW; c0 += 16) {
           float vals[16];
           if (KIND == 0) {
             uint32_t v[16];
-            tmem_ld_x16(lane_addr + bufc * ACC_COLS + c0, v);
+            tmem_ld_x16(lane_addr + bufc * ACC_COLS + c_lo + c0, v);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) vals[j] = __uint_as_float(v[j]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) vals[j] = acc[(KIND == 1) ? (c0 + j) : 0];
+            for (int j = 0; j < 16; ++j) vals[j] = accv(0, c0 + j);
           }
-          if (c0 < rows && n_ok) {
+          if (c_lo + c0 < rows && n_ok) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              if (c0 + j < rows) {
-                const size_t row = (size_t)(row0 + c0 + j);
+              if (c_lo + c0 + j < rows) {
+                const size_t row = (size_t)(row0 + c_lo + c0 + j);
                 float y = vals[j];
                 if (p.row_scale) y *= __ldg(p.row_scale + row);
                 if (p.out_f32) ((float*)p.out)[row * p.out_ld + n] = y;
@@ -328,33 +380,32 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       } else {
         // SwiGLU on (gate, up) held by the same lane
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 16) {
+        for (int c0 = 0; c0 < CW; c0 += 16) {
           float act[16];
           if (KIND == 0) {
             uint32_t vg[16], vu[16];
-            tmem_ld_x16(lane_addr + bufc * ACC_COLS + c0, vg);
-            tmem_ld_x16(lane_addr + bufc * ACC_COLS + BN + c0, vu);
+            tmem_ld_x16(lane_addr + bufc * ACC_COLS + c_lo + c0, vg);
+            tmem_ld_x16(lane_addr + bufc * ACC_COLS + BN + c_lo + c0, vu);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) act[j] = silu_f(__uint_as_float(vg[j])) * __uint_as_float(vu[j]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              act[j] = silu_f(acc[(KIND == 1) ? (c0 + j) : 0]) * acc[(KIND == 1 && NACC == 2) ? (BN + c0 + j) : 0];
+            for (int j = 0; j < 16; ++j) act[j] = silu_f(accv(0, c0 + j)) * accv(NACC - 1, c0 + j);
           }
           if (EPI == 1) {
-            if (c0 < rows && n_ok) {
+            if (c_lo + c0 < rows && n_ok) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c0 + j < rows)
-                  ((__nv_bfloat16*)p.out)[(size_t)(row0 + c0 + j) * p.out_ld + n] = __float2bfloat16(act[j]);
+                if (c_lo + c0 + j < rows)
+                  ((__nv_bfloat16*)p.out)[(size_t)(row0 + c_lo + c0 + j) * p.out_ld + n] = __float2bfloat16(act[j]);
             }
           } else {
-            // amax over the 128 lanes of the tile for each of the 16 token columns.  The four
-            // warps exchange their partial maxima through a double-buffered slab and a counter
+            // amax over the 128 lanes of the tile for each of the 16 token columns.  The four warps of
+            // this group exchange their partial maxima through a double-buffered slab and a counter
             // that only grows; the wait on the counter also watches the abort flag, so a warp
             // that left early can never strand the others (a bar.sync could).
-            float* slab = amax_x + (epi_sync & 1) * 64;
+            float* slab = amax_x + grp * 128 + (epi_sync & 1) * 64;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               float m = warp_max(n_ok ? fabsf(act[j]) : 0.f);
@@ -363,12 +414,12 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             __syncwarp();
             if (lane == 0) {
               __threadfence_block();
-              atomicAdd(epi_counter, 1);
+              atomicAdd(&epi_counter[grp], 1);
             }
             ++epi_sync;
             {
               uint32_t spins = 0;
-              while (*(volatile int*)epi_counter < 4 * epi_sync) {
+              while (*(volatile int*)&epi_counter[grp] < 4 * epi_sync) {
                 if (((++spins) & 0xff) == 0 && *abort_flag) { ok = false; break; }
               }
               __syncwarp();
@@ -380,11 +431,11 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
               float m = fmaxf(fmaxf(slab[j], slab[16 + j]), fmaxf(slab[32 + j], slab[48 + j]));
               scl[j] = fmaxf(m, 1e-10f) * (1.0f / 448.0f);
             }
-            if (c0 < rows) {
+            if (c_lo + c0 < rows) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                if (c0 + j < rows) {
-                  const size_t row = (size_t)(row0 + c0 + j);
+                if (c_lo + c0 + j < rows) {
+                  const size_t row = (size_t)(row0 + c_lo + c0 + j);
                   if (n_ok) ((uint8_t*)p.out)[row * p.out_ld + n] = f32_to_e4m3(act[j] / scl[j]);
                   if (r == 0) p.out_scale[(size_t)mt * p.out_scale_ld + row] = scl[j];
                 }
@@ -452,13 +503,15 @@ extern "C" int omni_gemm(int kind, int epi, const void* w, const void* x, void* 
   if ((K * esz) % 16 != 0) return -2;
   if (nacc == 2 && (n_out % 128) != 0) return -3;
   if (kind == 1 && (w_scale == nullptr || x_scale == nullptr)) return -4;
+  if (kind == 1 && ((x_scale_ld % 4) != 0 || ((uintptr_t)x_scale % 16) != 0)) return -7;  // bulk copies of scale rows
   if (epi == 2 && out_scale == nullptr) return -5;
   if (bn == 0) {
     int t = t_hint > 0 ? t_hint : T;
     const int cap = (kind == 1) ? (nacc == 2 ? 64 : 128) : (nacc == 2 ? 128 : 256);
-    bn = t <= 16 ? 16 : t <= 32 ? 32 : t <= 64 ? 64 : t <= 128 ? 128 : 256;
+    bn = t <= 32 ? 32 : t <= 64 ? 64 : t <= 128 ? 128 : 256;
     if (bn > cap) bn = cap;
   }
+  if (bn == 16) bn = 32;   // smallest instantiated token tile
   GemmParams p;
   p.G = G; p.n_out = n_out; p.K = K; p.T = T; p.seg_start = seg_start; p.seg_len = seg_len;
   p.w_rows_per_group = n_out * nacc; p.w_scale = w_scale; p.x_scale = x_scale; p.x_scale_ld = x_scale_ld;
@@ -477,12 +530,11 @@ extern "C" int omni_gemm(int kind, int epi, const void* w, const void* x, void* 
 
 #define OMNI_GEMM_CASE(KIND_, BN_, NACC_, EPI_) \
   if (kind == KIND_ && bn == BN_ && epi == EPI_) return launch_gemm<KIND_, BN_, NACC_, EPI_>(tw, tx, p, grid, stream);
-  OMNI_GEMM_CASE(0, 16, 1, 0) OMNI_GEMM_CASE(0, 32, 1, 0) OMNI_GEMM_CASE(0, 64, 1, 0)
-  OMNI_GEMM_CASE(0, 128, 1, 0) OMNI_GEMM_CASE(0, 256, 1, 0)
-  OMNI_GEMM_CASE(0, 16, 2, 1) OMNI_GEMM_CASE(0, 32, 2, 1) OMNI_GEMM_CASE(0, 64, 2, 1) OMNI_GEMM_CASE(0, 128, 2, 1)
-  OMNI_GEMM_CASE(1, 16, 1, 0) OMNI_GEMM_CASE(1, 32, 1, 0) OMNI_GEMM_CASE(1, 64, 1, 0) OMNI_GEMM_CASE(1, 128, 1, 0)
-  OMNI_GEMM_CASE(1, 16, 2, 1) OMNI_GEMM_CASE(1, 32, 2, 1) OMNI_GEMM_CASE(1, 64, 2, 1)
-  OMNI_GEMM_CASE(1, 16, 2, 2) OMNI_GEMM_CASE(1, 32, 2, 2) OMNI_GEMM_CASE(1, 64, 2, 2)
+  OMNI_GEMM_CASE(0, 32, 1, 0) OMNI_GEMM_CASE(0, 64, 1, 0) OMNI_GEMM_CASE(0, 128, 1, 0) OMNI_GEMM_CASE(0, 256, 1, 0)
+  OMNI_GEMM_CASE(0, 32, 2, 1) OMNI_GEMM_CASE(0, 64, 2, 1) OMNI_GEMM_CASE(0, 128, 2, 1)
+  OMNI_GEMM_CASE(1, 32, 1, 0) OMNI_GEMM_CASE(1, 64, 1, 0) OMNI_GEMM_CASE(1, 128, 1, 0)
+  OMNI_GEMM_CASE(1, 32, 2, 1) OMNI_GEMM_CASE(1, 64, 2, 1)
+  OMNI_GEMM_CASE(1, 32, 2, 2) OMNI_GEMM_CASE(1, 64, 2, 2)
 #undef OMNI_GEMM_CASE
   return -20;
 }

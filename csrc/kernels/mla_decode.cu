@@ -14,7 +14,8 @@
 //   S = Q K^T     A = Q  (smem, K-major, 9 chunks of 64 dims)   B = KV tile (smem, K-major)      -> TMEM
 //   P = softmax   written back to TMEM as packed bf16 (A operand of the second MMA)
 //   O += P V      A = P  (TMEM)                                  B = KV tile (same smem, MN-major) -> TMEM
-// KV tiles are 32 tokens, double buffered; the chunks that only the score MMA reads (the other CTA's
+// Four of the nine 64-dim q chunks sit in shared memory, the other five in TMEM (as A operands), which
+// leaves room for four KV stages.  KV tiles are 32 tokens; the chunks that only the score MMA reads (the other CTA's
 // value dims and the rope dims) are released as soon as S is issued, the value chunks after P V.
 // The running max is only raised when it grows by more than 2^8 (lazy rescale), so the O accumulator is
 // rarely read back.
@@ -33,6 +34,7 @@ struct MlaDecodeParams {
   int bt_ld;
   const int* seq_lens;   // [Bq] visible kv tokens of each q row
   const int* q_to_seq;   // [Bq] block-table row of each q row, or null (identity)
+  const __nv_bfloat16* q; // [Bq, H, 576] (also read directly for the chunks kept in TMEM)
   float scale_log2;      // softmax scale * log2(e)
   int num_splits;
   __nv_bfloat16* out;    // [Bq, H, 512]
@@ -46,12 +48,15 @@ constexpr int MLA_CHUNK_BYTES = MLA_TILE * 128;       // 32 tokens x 64 dims bf1
 constexpr int MLA_STAGE_BYTES = 9 * MLA_CHUNK_BYTES;  // 36 KB
 constexpr int MLA_Q_CHUNK = 128 * 128;                // 128 heads x 64 dims bf16
 constexpr int MLA_Q_BYTES = 9 * MLA_Q_CHUNK;          // 144 KB
-constexpr int MLA_SMEM = MLA_Q_BYTES + 2 * MLA_STAGE_BYTES + 1024 /*barriers*/ + 1024 /*align*/;
+constexpr int MLA_QS = 4;                             // q chunks 0..3 live in shared memory,
+constexpr int MLA_QT = 5;                             // chunks 4..8 (latent dims 256..511 + rope) in TMEM
+constexpr int MLA_STAGES = 4;
+constexpr int MLA_SMEM = MLA_QS * MLA_Q_CHUNK + MLA_STAGES * MLA_STAGE_BYTES + 1024 /*barriers*/ + 1024 /*align*/;
 constexpr int MLA_THREADS = 192;
-// TMEM columns
-constexpr int TM_O = 0, TM_S = 256, TM_P = 320, TM_COLS = 512;
+// TMEM columns: O accumulator | two S tiles | two packed-bf16 P tiles | five packed-bf16 q chunks
+constexpr int TM_O = 0, TM_S = 256, TM_P = 320, TM_Q = 352, TM_COLS = 512;
 
-enum { MS_Q = 1, MS_KA_EMPTY, MS_KB_EMPTY, MS_KA_FULL, MS_KB_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE };
+enum { MS_Q = 1, MS_KA_EMPTY, MS_KB_EMPTY, MS_KA_FULL, MS_KB_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT };
 
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -76,18 +81,19 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sq = smem;
-  uint8_t* skv = smem + MLA_Q_BYTES;
-  uint64_t* bars = (uint64_t*)(skv + 2 * MLA_STAGE_BYTES);
-  uint64_t* q_full = bars;            // 1
-  uint64_t* ka_full = bars + 1;       // 2
-  uint64_t* ka_empty = bars + 3;      // 2
-  uint64_t* kb_full = bars + 5;       // 2
-  uint64_t* kb_empty = bars + 7;      // 2
-  uint64_t* s_full = bars + 9;        // 2
-  uint64_t* p_full = bars + 11;       // 2
-  uint64_t* o_done = bars + 13;       // 1
-  uint64_t* o_final = bars + 14;      // 1: all P V of this CTA retired
-  uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+  uint8_t* skv = smem + MLA_QS * MLA_Q_CHUNK;
+  uint64_t* bars = (uint64_t*)(skv + MLA_STAGES * MLA_STAGE_BYTES);
+  uint64_t* q_full = bars;                          // 1
+  uint64_t* ka_full = bars + 1;                     // STAGES
+  uint64_t* ka_empty = ka_full + MLA_STAGES;
+  uint64_t* kb_full = ka_empty + MLA_STAGES;
+  uint64_t* kb_empty = kb_full + MLA_STAGES;
+  uint64_t* s_full = kb_empty + MLA_STAGES;         // 2
+  uint64_t* p_full = s_full + 2;                    // 2
+  uint64_t* o_done = p_full + 2;                    // 1
+  uint64_t* o_final = o_done + 1;                   // 1: all P V of this CTA retired
+  uint64_t* qt_full = o_final + 1;                  // 1: q chunks written to TMEM
+  uint32_t* tmem_slot = (uint32_t*)(qt_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,16 +110,19 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < MLA_STAGES; ++s) {
       mbar_init(&ka_full[s], 1);
       mbar_init(&ka_empty[s], 1);
       mbar_init(&kb_full[s], 1);
       mbar_init(&kb_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 4);
     }
     mbar_init(o_done, 1);
     mbar_init(o_final, 1);
+    mbar_init(qt_full, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -134,13 +143,13 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (lane == 0) {
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_kv);
-        mbar_expect_tx(q_full, MLA_Q_BYTES);
-        for (int c = 0; c < 9; ++c) tma_load_2d(sq + c * MLA_Q_CHUNK, &tmap_q, q_full, c * 64, bq * p.H);
+        mbar_expect_tx(q_full, MLA_QS * MLA_Q_CHUNK);
+        for (int c = 0; c < MLA_QS; ++c) tma_load_2d(sq + c * MLA_Q_CHUNK, &tmap_q, q_full, c * 64, bq * p.H);
         const int seq = p.q_to_seq ? p.q_to_seq[bq] : bq;
         const int* bt = p.block_table + (size_t)seq * p.bt_ld;
         for (int i = 0; i < n; ++i) {
-          const int st = i & 1;
-          const uint32_t ph = (i >> 1) & 1;
+          const int st = i % MLA_STAGES;
+          const uint32_t ph = (i / MLA_STAGES) & 1;
           const int tok0 = (tile_begin + i) * MLA_TILE;
           const int page = bt[tok0 / p.block_size];
           const int row = page * p.block_size + tok0 % p.block_size;
@@ -160,48 +169,52 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         constexpr uint32_t idesc_qk = umma_idesc(128, MLA_TILE, 1, 1, 0, 0);
         constexpr uint32_t idesc_pv = umma_idesc(128, 256, 1, 1, 0, 1);
         bool ok = mbar_wait(q_full, 0, abort_flag, p.status, MS_Q, 0);
+        if (ok) ok = mbar_wait(qt_full, 0, abort_flag, p.status, MS_QT, 0);
+        tc_fence_after();
+        // q chunk c times kv chunk c of the staged tile; q comes from shared memory or from TMEM
+        auto qk_chunk = [&](uint32_t d, uint32_t kbase, int c, uint32_t& accum) {
+          const uint64_t bd = umma_desc_kmajor_sw128(kbase + c * MLA_CHUNK_BYTES);
+          if (c < MLA_QS) {
+            const uint64_t ad = umma_desc_kmajor_sw128(smem_u32(sq) + c * MLA_Q_CHUNK);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { umma_bf16(d, ad + 2 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
+          } else {
+            const uint32_t at = tmem_base + TM_Q + (c - MLA_QS) * 32;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { umma_bf16_ts(d, at + 8 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
+          }
+        };
         auto issue_qk = [&](int j) -> bool {
-          const int st = j & 1;
-          const uint32_t ph = (j >> 1) & 1;
+          const int st = j % MLA_STAGES;
+          const uint32_t ph = (j / MLA_STAGES) & 1;
           const uint32_t kbase = smem_u32(skv + st * MLA_STAGE_BYTES);
-          const uint32_t d = tmem_base + TM_S + st * MLA_TILE;
+          const uint32_t d = tmem_base + TM_S + (j & 1) * MLA_TILE;
           uint32_t accum = 0;
           if (!mbar_wait(&ka_full[st], ph, abort_flag, p.status, MS_KA_FULL, j)) return false;
           tc_fence_after();
           for (int c = 0; c < 9; ++c) {
             if (c >= vb && c < vb + 4) continue;
-            const uint64_t ad = umma_desc_kmajor_sw128(smem_u32(sq) + c * MLA_Q_CHUNK);
-            const uint64_t bd = umma_desc_kmajor_sw128(kbase + c * MLA_CHUNK_BYTES);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              umma_bf16(d, ad + 2 * k, bd + 2 * k, idesc_qk, accum);
-              accum = 1;
-            }
+            qk_chunk(d, kbase, c, accum);
           }
           umma_commit(&ka_empty[st]);
           if (!mbar_wait(&kb_full[st], ph, abort_flag, p.status, MS_KB_FULL, j)) return false;
           tc_fence_after();
-          for (int c = vb; c < vb + 4; ++c) {
-            const uint64_t ad = umma_desc_kmajor_sw128(smem_u32(sq) + c * MLA_Q_CHUNK);
-            const uint64_t bd = umma_desc_kmajor_sw128(kbase + c * MLA_CHUNK_BYTES);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) umma_bf16(d, ad + 2 * k, bd + 2 * k, idesc_qk, 1);
-          }
-          umma_commit(&s_full[st]);
+          for (int c = vb; c < vb + 4; ++c) qk_chunk(d, kbase, c, accum);
+          umma_commit(&s_full[j & 1]);
           return true;
         };
         if (ok) ok = issue_qk(0);
         if (ok && n > 1) ok = issue_qk(1);
         for (int i = 0; i < n && ok; ++i) {
-          const int st = i & 1;
-          if (!mbar_wait(&p_full[st], (i >> 1) & 1, abort_flag, p.status, MS_P_FULL, i)) { ok = false; break; }
+          const int st = i % MLA_STAGES;
+          if (!mbar_wait(&p_full[i & 1], (i >> 1) & 1, abort_flag, p.status, MS_P_FULL, i)) { ok = false; break; }
           tc_fence_after();
           const uint32_t vbase = smem_u32(skv + st * MLA_STAGE_BYTES) + vb * MLA_CHUNK_BYTES;
 #pragma unroll
           for (int k = 0; k < MLA_TILE / 16; ++k) {
             // 16 tokens per MMA: two 8-token groups of 1024 B; dims advance by whole 4 KB chunks
             const uint64_t bd = umma_desc_mnmajor_sw128(vbase + k * 2048, MLA_CHUNK_BYTES, 1024);
-            umma_bf16_ts(tmem_base + TM_O, tmem_base + TM_P + st * (MLA_TILE / 2) + k * 8, bd, idesc_pv,
+            umma_bf16_ts(tmem_base + TM_O, tmem_base + TM_P + (i & 1) * (MLA_TILE / 2) + k * 8, bd, idesc_pv,
                          (i > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&kb_empty[st]);
@@ -217,6 +230,25 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
       float m = -INFINITY, l = 0.f;
       bool ok = true;
+      // this head's q values for latent dims 256..511 and the rope dims go to TMEM as packed bf16 pairs
+      {
+        const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + ((size_t)bq * p.H + row) * 576 + MLA_QS * 64);
+        const bool row_ok = row < p.H;
+#pragma unroll 1
+        for (int c = 0; c < MLA_QT; ++c) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 x = row_ok ? __ldg(qsrc + c * 8 + j) : make_uint4(0, 0, 0, 0);
+            v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+          }
+          tmem_st_x32(lane_addr + TM_Q + c * 32, v);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(qt_full);
+      }
       for (int i = 0; i < n; ++i) {
         const int st = i & 1;
         if (!mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, MS_S_FULL, i)) { ok = false; break; }
@@ -386,7 +418,7 @@ extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, l
   if (make_tmap_2d(&tq, q, 2, (uint64_t)Bq * H, 576, 576, 128, 64, true)) return -10;
   if (make_tmap_2d(&tkv, cache, 2, (uint64_t)num_slots, 576, cache_ld, MLA_TILE, 64, true)) return -11;
   MlaDecodeParams p;
-  p.H = H; p.block_size = block_size; p.block_table = block_table; p.bt_ld = bt_ld; p.seq_lens = seq_lens;
+  p.q = (const __nv_bfloat16*)q; p.H = H; p.block_size = block_size; p.block_table = block_table; p.bt_ld = bt_ld; p.seq_lens = seq_lens;
   p.q_to_seq = q_to_seq; p.scale_log2 = scale * 1.4426950408889634f; p.num_splits = num_splits;
   p.out = (__nv_bfloat16*)out; p.o_part = o_part; p.lse_part = lse_part; p.status = (OmniStatus*)status;
   static bool configured = false;

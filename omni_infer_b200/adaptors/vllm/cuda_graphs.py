@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from ...layers.common import AttnMetadata
+from ...ops import _native as nat
 
 
 class DecodeGraphs:
@@ -52,15 +53,18 @@ class DecodeGraphs:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
+        before = nat.launch_count()
         with torch.cuda.graph(g, pool=self.pool):
             hidden = r.model(ids, md, r.kv_caches)
             logits = r.model.compute_logits(hidden)
+        captured = nat.launch_count() - before
+        nat.add_launches(-captured)          # capture itself runs nothing
         if self.pool is None:
             self.pool = g.pool()
-        self.graphs[padded] = (g, ids, md, hidden, logits)
+        self.graphs[padded] = (g, ids, md, hidden, logits, captured)
 
     def replay(self, padded: int, ids: torch.Tensor, md: AttnMetadata):
-        g, s_ids, s_md, hidden, logits = self.graphs[padded]
+        g, s_ids, s_md, hidden, logits, captured = self.graphs[padded]
         s_ids.copy_(ids)
         s_md.positions.copy_(md.positions)
         s_md.slot_mapping.copy_(md.slot_mapping)
@@ -72,4 +76,5 @@ class DecodeGraphs:
         else:
             s_md.num_valid.fill_(padded * self.r.tpr)
         g.replay()
+        nat.add_launches(captured)
         return hidden, logits

@@ -187,34 +187,73 @@ class ModelRunner:
         return self._to_dev(ids, torch.int64), md
 
     def _prepare_decode(self, so: SchedulerOutput, padded: int):
-        tpr = self.tpr
+        """Decode inputs for ``padded`` rows (live requests first).  Everything is assembled with numpy in
+        one pinned staging buffer and moved with a single host->device copy."""
+        import numpy as np
+
+        tpr, bs, W = self.tpr, self.cfg.block_size, self._bt_width
         B = len(so.scheduled)
-        ids, pos, slots, qlens, seq_lens, bt_rows = [], [], [], [], [], []
-        for s in so.scheduled:
+        n = padded * tpr
+        # int64 section: ids | positions | slots ; int32 section: q_seq_lens | seq_lens | q_to_seq | num_valid | block table
+        n64 = 3 * n
+        n32 = n + padded + n + 2 + padded * W
+        total_bytes = n64 * 8 + n32 * 4
+        key = (padded, tpr)
+        stage = getattr(self, "_stage", None)
+        if stage is None or stage[0] != key:
+            host = torch.empty(total_bytes, dtype=torch.uint8)
+            if self.device.type == "cuda":
+                host = host.pin_memory()
+            self._stage = stage = (key, host, host.numpy())
+        _, host, raw = stage
+        a64 = raw[: n64 * 8].view(np.int64)
+        a32 = raw[n64 * 8:].view(np.int32)
+        ids, pos, slots = a64[:n].reshape(padded, tpr), a64[n:2 * n].reshape(padded, tpr), a64[2 * n:].reshape(padded, tpr)
+        o = 0
+        qlens = a32[o:o + n].reshape(padded, tpr); o += n
+        seq_lens = a32[o:o + padded]; o += padded
+        q_to_seq = a32[o:o + n]; o += n
+        num_valid = a32[o:o + 2]; o += 2
+        bt = a32[o:o + padded * W].reshape(padded, W)
+        ids[:] = 0
+        bt[:] = 0
+        st = np.zeros(padded, dtype=np.int64)
+        for i, s in enumerate(so.scheduled):
             r = s.request
-            st = r.num_computed_tokens
-            drafts = list(s.spec_token_ids) + [0] * (tpr - 1 - len(s.spec_token_ids))
-            ids += [r.all_token_ids[st]] + drafts[: tpr - 1]
-            pos += list(range(st, st + tpr))
-            slots += self._slots(r.block_ids, st, tpr)
-            qlens += [st + j + 1 for j in range(tpr)]
-            seq_lens.append(st + tpr)
-            bt_rows.append(r.block_ids + [0] * (self._bt_width - len(r.block_ids)))
-        for _ in range(padded - B):     # padding rows: no cache write, zero-length attention
-            ids += [0] * tpr
-            pos += [0] * tpr
-            slots += [-1] * tpr
-            qlens += [0] * tpr
-            seq_lens.append(0)
-            bt_rows.append([0] * self._bt_width)
-        q_to_seq = [b for b in range(padded) for _ in range(tpr)]
+            c = r.num_computed_tokens
+            st[i] = c
+            npt = len(r.prompt_token_ids)
+            ids[i, 0] = r.output_token_ids[c - npt] if c >= npt else r.prompt_token_ids[c]
+            if s.spec_token_ids:
+                k = min(len(s.spec_token_ids), tpr - 1)
+                ids[i, 1:1 + k] = s.spec_token_ids[:k]
+            nb = len(r.block_ids)
+            bt[i, :nb] = r.block_ids
+        j = np.arange(tpr, dtype=np.int64)[None, :]
+        pos[:] = st[:, None] + j
+        live = np.arange(padded) < B
+        blk = np.take_along_axis(bt.astype(np.int64), np.minimum(pos // bs, W - 1), axis=1)
+        slots[:] = np.where(live[:, None], blk * bs + pos % bs, -1)
+        pos[~live] = 0
+        qlens[:] = np.where(live[:, None], pos + 1, 0)
+        seq_lens[:] = np.where(live, st + tpr, 0)
+        q_to_seq[:] = np.repeat(np.arange(padded, dtype=np.int32), tpr)
+        num_valid[0] = B * tpr
+        max_seq = int(seq_lens.max()) if B else 0
+        dev = host.to(self.device, non_blocking=True) if self.device.type == "cuda" else host.clone()
+        d64 = dev[: n64 * 8].view(torch.int64)
+        d32 = dev[n64 * 8:].view(torch.int32)
+        o = 0
+        d_q = d32[o:o + n]; o += n
+        d_seq = d32[o:o + padded]; o += padded
+        d_q2s = d32[o:o + n]; o += n
+        d_nv = d32[o:o + 1]; o += 2
+        d_bt = d32[o:o + padded * W].view(padded, W)
         md = AttnMetadata(
-            is_prefill=False, positions=self._to_dev(pos, torch.int64), slot_mapping=self._to_dev(slots, torch.int64),
-            block_table=self._to_dev(bt_rows, torch.int32), seq_lens=self._to_dev(seq_lens, torch.int32),
-            tokens_per_req=tpr, q_seq_lens=self._to_dev(qlens, torch.int32), q_to_seq=self._to_dev(q_to_seq, torch.int32),
-            max_seq_len=max(seq_lens) if seq_lens else 0,
-            num_valid=self._to_dev([B * tpr], torch.int32) if padded != B else None)
-        return self._to_dev(ids, torch.int64), md
+            is_prefill=False, positions=d64[n:2 * n], slot_mapping=d64[2 * n:3 * n], block_table=d_bt, seq_lens=d_seq,
+            tokens_per_req=tpr, q_seq_lens=d_q, q_to_seq=d_q2s, max_seq_len=max_seq,
+            num_valid=d_nv if padded != B else None)
+        return d64[:n], md
 
     # ------------------------------------------------------------------ sampling
     def _sample(self, logits: torch.Tensor, reqs: list, rows_per_req: int) -> torch.Tensor:

@@ -31,6 +31,33 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
+# kernels launched by one call of each entry point (entry points not listed launch one)
+_KERNELS_PER_CALL = {"omni_moe_align": 2}
+
+
+class _CountingLib:
+    """Proxy over the CDLL that counts kernel launches issued through it (benchmarks report the count).
+    Launches replayed from CUDA graphs are added by the graph runner through :func:`add_launches`."""
+
+    def __init__(self, cdll):
+        self._cdll = cdll
+        self.launches = 0
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._cdll, name)
+            n = _KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*args, _raw=raw, _n=n):
+                self.launches += _n
+                return _raw(*args)
+
+            self._cache[name] = fn
+        return fn
+
+
 def lib():
     """Load the kernel library once.  Raises if it has not been built."""
     global _lib
@@ -39,8 +66,17 @@ def lib():
             raise RuntimeError(
                 f"{_LIB_PATH} is missing: run `python -m omni_infer_b200.build` "
                 "(CUDA tensors never fall back to PyTorch ops)")
-        _lib = ctypes.CDLL(str(_LIB_PATH), mode=ctypes.RTLD_GLOBAL)
+        _lib = _CountingLib(ctypes.CDLL(str(_LIB_PATH), mode=ctypes.RTLD_GLOBAL))
     return _lib
+
+
+def launch_count() -> int:
+    return _lib.launches if _lib is not None else 0
+
+
+def add_launches(n: int) -> None:
+    if _lib is not None:
+        _lib.launches += n
 
 
 def ptr(t):

@@ -2,7 +2,9 @@
 import pytest
 import torch
 
-from omni_infer_b200.ops import gemm as G
+import importlib
+
+G = importlib.import_module("omni_infer_b200.ops.gemm")
 
 pytestmark = pytest.mark.gpu
 
