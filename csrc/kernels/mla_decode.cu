@@ -14,9 +14,11 @@
 //   S = Q K^T     A = Q  (smem, K-major, 9 chunks of 64 dims)   B = KV tile (smem, K-major)      -> TMEM
 //   P = softmax   written back to TMEM as packed bf16 (A operand of the second MMA)
 //   O += P V      A = P  (TMEM)                                  B = KV tile (same smem, MN-major) -> TMEM
-// Four of the nine 64-dim q chunks sit in shared memory, the other five in TMEM (as A operands), which
-// leaves room for four KV stages.  KV tiles are 32 tokens; the chunks that only the score MMA reads (the other CTA's
-// value dims and the rope dims) are released as soon as S is issued, the value chunks after P V.
+// KV tiles are 128 tokens (tcgen05.mma reaches its peak rate from N = 128; smaller N is issue-bound at about
+// 46 cycles per instruction).  Five of the nine 64-dim q chunks sit in shared memory, the other four in TMEM
+// (as A operands), which leaves room for one whole KV tile.  Each 64-dim chunk of the tile has its own
+// full/empty barrier pair: the chunks that only the score MMA reads (the other CTA's value dims and the rope
+// dims) are refilled as soon as S is issued, the value chunks after P V.
 // The running max is only raised when it grows by more than 2^8 (lazy rescale), so the O accumulator is
 // rarely read back.
 //
@@ -43,20 +45,19 @@ struct MlaDecodeParams {
   OmniStatus* status;
 };
 
-constexpr int MLA_TILE = 32;
-constexpr int MLA_CHUNK_BYTES = MLA_TILE * 128;       // 32 tokens x 64 dims bf16
-constexpr int MLA_STAGE_BYTES = 9 * MLA_CHUNK_BYTES;  // 36 KB
+constexpr int MLA_TILE = 128;                         // kv tokens per tile (tcgen05.mma runs at peak from N = 128)
+constexpr int MLA_CHUNK_BYTES = MLA_TILE * 128;       // 128 tokens x 64 dims bf16 = 16 KB
+constexpr int MLA_KV_BYTES = 9 * MLA_CHUNK_BYTES;     // 144 KB: one tile, released chunk by chunk
 constexpr int MLA_Q_CHUNK = 128 * 128;                // 128 heads x 64 dims bf16
-constexpr int MLA_Q_BYTES = 9 * MLA_Q_CHUNK;          // 144 KB
-constexpr int MLA_QS = 4;                             // q chunks 0..3 live in shared memory,
-constexpr int MLA_QT = 5;                             // chunks 4..8 (latent dims 256..511 + rope) in TMEM
-constexpr int MLA_STAGES = 4;
-constexpr int MLA_SMEM = MLA_QS * MLA_Q_CHUNK + MLA_STAGES * MLA_STAGE_BYTES + 1024 /*barriers*/ + 1024 /*align*/;
-constexpr int MLA_THREADS = 192;
-// TMEM columns: O accumulator | two S tiles | two packed-bf16 P tiles | five packed-bf16 q chunks
-constexpr int TM_O = 0, TM_S = 256, TM_P = 320, TM_Q = 352, TM_COLS = 512;
+constexpr int MLA_QS = 5;                             // q chunks 0..4 live in shared memory,
+// chunks 5..8 (latent dims 320..511 + rope) are kept in TMEM, two written by each softmax group
+constexpr int MLA_SMEM = MLA_QS * MLA_Q_CHUNK + MLA_KV_BYTES + 1536 /*barriers + softmax exchange*/ + 1024 /*align*/;
+static_assert(MLA_SMEM <= 232448, "exceeds the 227 KB shared-memory limit of one CTA");
+constexpr int MLA_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two groups of four, 64 score columns each)
+// TMEM columns: O accumulator | S tile (P, packed bf16, overwrites its first half) | four packed-bf16 q chunks
+constexpr int TM_O = 0, TM_S = 256, TM_Q = 384, TM_COLS = 512;
 
-enum { MS_Q = 1, MS_KA_EMPTY, MS_KB_EMPTY, MS_KA_FULL, MS_KB_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT };
+enum { MS_Q = 1, MS_KV_EMPTY, MS_KV_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT };
 
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -66,14 +67,13 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
+
+#ifdef MLA_TRACE
+__device__ long long g_mla_trace[16];
+#define TRACE_WAIT(slot, expr) ({ long long _t0 = clock64(); bool _r = (expr); trace[slot] += clock64() - _t0; _r; })
+#else
+#define TRACE_WAIT(slot, expr) (expr)
+#endif
 
 __global__ void __launch_bounds__(MLA_THREADS, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
@@ -82,20 +82,25 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sq = smem;
   uint8_t* skv = smem + MLA_QS * MLA_Q_CHUNK;
-  uint64_t* bars = (uint64_t*)(skv + MLA_STAGES * MLA_STAGE_BYTES);
+  uint64_t* bars = (uint64_t*)(skv + MLA_KV_BYTES);
   uint64_t* q_full = bars;                          // 1
-  uint64_t* ka_full = bars + 1;                     // STAGES
-  uint64_t* ka_empty = ka_full + MLA_STAGES;
-  uint64_t* kb_full = ka_empty + MLA_STAGES;
-  uint64_t* kb_empty = kb_full + MLA_STAGES;
-  uint64_t* s_full = kb_empty + MLA_STAGES;         // 2
-  uint64_t* p_full = s_full + 2;                    // 2
-  uint64_t* o_done = p_full + 2;                    // 1
+  uint64_t* kv_full = bars + 1;                     // 9, one per 64-dim chunk
+  uint64_t* kv_empty = kv_full + 9;                 // 9
+  uint64_t* s_full = kv_empty + 9;                  // 1
+  uint64_t* p_full = s_full + 1;                    // 1
+  uint64_t* o_done = p_full + 1;                    // 1
   uint64_t* o_final = o_done + 1;                   // 1: all P V of this CTA retired
   uint64_t* qt_full = o_final + 1;                  // 1: q chunks written to TMEM
   uint32_t* tmem_slot = (uint32_t*)(qt_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* sm_counter = (int*)(tmem_slot + 2);          // softmax group rendezvous (only grows)
+  float* sm_max = (float*)(bars + 64);              // [2 groups][128 rows] row maxima of the current tile
+  float* sm_sum = sm_max;                           // reused for the row sums after the last tile
 
+#ifdef MLA_TRACE
+  long long trace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long t_start = clock64();
+#endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = blockIdx.x;   // which 256 output dims
   const int split = blockIdx.y;
@@ -110,20 +115,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < MLA_STAGES; ++s) {
-      mbar_init(&ka_full[s], 1);
-      mbar_init(&ka_empty[s], 1);
-      mbar_init(&kb_full[s], 1);
-      mbar_init(&kb_empty[s], 1);
+    for (int c = 0; c < 9; ++c) {
+      mbar_init(&kv_full[c], 1);
+      mbar_init(&kv_empty[c], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 4);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 8);
     mbar_init(o_done, 1);
     mbar_init(o_final, 1);
     mbar_init(qt_full, 4);
     *abort_flag = 0;
+    *sm_counter = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -135,8 +137,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // chunks 0..7 = latent dims 64c..64c+63, chunk 8 = rope dims.  Group B = this CTA's value chunks.
-  const int vb = half * 4;  // first value chunk of this CTA
+  // chunks 0..7 = latent dims 64c..64c+63, chunk 8 = rope dims.  This CTA's value chunks are vb..vb+3; they
+  // are consumed last by the score MMA and stay resident until P V, every other chunk is released as soon
+  // as the score MMA has read it.  order[] = processing order of the chunks.
+  const int vb = half * 4;
+  int order[9];
+  {
+    int o = 0;
+    for (int c = 0; c < 9; ++c) if (c < vb || c >= vb + 4) order[o++] = c;
+    for (int c = vb; c < vb + 4; ++c) order[o++] = c;
+  }
+  const int box_rows = min(p.block_size, MLA_TILE);   // tokens per TMA box (one cache page, at most a tile)
 
   if (n > 0) {
     if (warp == 0) {
@@ -147,21 +158,22 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         for (int c = 0; c < MLA_QS; ++c) tma_load_2d(sq + c * MLA_Q_CHUNK, &tmap_q, q_full, c * 64, bq * p.H);
         const int seq = p.q_to_seq ? p.q_to_seq[bq] : bq;
         const int* bt = p.block_table + (size_t)seq * p.bt_ld;
-        for (int i = 0; i < n; ++i) {
-          const int st = i % MLA_STAGES;
-          const uint32_t ph = (i / MLA_STAGES) & 1;
+        bool ok = true;
+        for (int i = 0; i < n && ok; ++i) {
+          const uint32_t ph = i & 1;
           const int tok0 = (tile_begin + i) * MLA_TILE;
-          const int page = bt[tok0 / p.block_size];
-          const int row = page * p.block_size + tok0 % p.block_size;
-          uint8_t* base = skv + st * MLA_STAGE_BYTES;
-          if (!mbar_wait(&ka_empty[st], ph ^ 1, abort_flag, p.status, MS_KA_EMPTY, i)) break;
-          mbar_expect_tx(&ka_full[st], 5 * MLA_CHUNK_BYTES);
-          for (int c = 0; c < 9; ++c)
-            if (c < vb || c >= vb + 4) tma_load_2d(base + c * MLA_CHUNK_BYTES, &tmap_kv, &ka_full[st], c * 64, row);
-          if (!mbar_wait(&kb_empty[st], ph ^ 1, abort_flag, p.status, MS_KB_EMPTY, i)) break;
-          mbar_expect_tx(&kb_full[st], 4 * MLA_CHUNK_BYTES);
-          for (int c = vb; c < vb + 4; ++c)
-            tma_load_2d(base + c * MLA_CHUNK_BYTES, &tmap_kv, &kb_full[st], c * 64, row);
+          for (int oc = 0; oc < 9; ++oc) {
+            const int c = order[oc];
+            if (!TRACE_WAIT(0, mbar_wait(&kv_empty[c], ph ^ 1, abort_flag, p.status, MS_KV_EMPTY, c))) { ok = false; break; }
+            mbar_expect_tx(&kv_full[c], MLA_CHUNK_BYTES);
+            for (int r0 = 0; r0 < MLA_TILE; r0 += box_rows) {
+              const int tok = tok0 + r0;
+              // pages past the end of the sequence repeat the last valid page (their scores are masked)
+              const int pg = min(tok, kv_len - 1) / p.block_size;
+              const int row = bt[pg] * p.block_size + tok % p.block_size;
+              tma_load_2d(skv + c * MLA_CHUNK_BYTES + r0 * 128, &tmap_kv, &kv_full[c], c * 64, row);
+            }
+          }
         }
       }
     } else if (warp == 1) {
@@ -171,71 +183,75 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         bool ok = mbar_wait(q_full, 0, abort_flag, p.status, MS_Q, 0);
         if (ok) ok = mbar_wait(qt_full, 0, abort_flag, p.status, MS_QT, 0);
         tc_fence_after();
-        // q chunk c times kv chunk c of the staged tile; q comes from shared memory or from TMEM
-        auto qk_chunk = [&](uint32_t d, uint32_t kbase, int c, uint32_t& accum) {
-          const uint64_t bd = umma_desc_kmajor_sw128(kbase + c * MLA_CHUNK_BYTES);
-          if (c < MLA_QS) {
-            const uint64_t ad = umma_desc_kmajor_sw128(smem_u32(sq) + c * MLA_Q_CHUNK);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { umma_bf16(d, ad + 2 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
-          } else {
-            const uint32_t at = tmem_base + TM_Q + (c - MLA_QS) * 32;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { umma_bf16_ts(d, at + 8 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
-          }
-        };
-        auto issue_qk = [&](int j) -> bool {
-          const int st = j % MLA_STAGES;
-          const uint32_t ph = (j / MLA_STAGES) & 1;
-          const uint32_t kbase = smem_u32(skv + st * MLA_STAGE_BYTES);
-          const uint32_t d = tmem_base + TM_S + (j & 1) * MLA_TILE;
-          uint32_t accum = 0;
-          if (!mbar_wait(&ka_full[st], ph, abort_flag, p.status, MS_KA_FULL, j)) return false;
-          tc_fence_after();
-          for (int c = 0; c < 9; ++c) {
-            if (c >= vb && c < vb + 4) continue;
-            qk_chunk(d, kbase, c, accum);
-          }
-          umma_commit(&ka_empty[st]);
-          if (!mbar_wait(&kb_full[st], ph, abort_flag, p.status, MS_KB_FULL, j)) return false;
-          tc_fence_after();
-          for (int c = vb; c < vb + 4; ++c) qk_chunk(d, kbase, c, accum);
-          umma_commit(&s_full[j & 1]);
-          return true;
-        };
-        if (ok) ok = issue_qk(0);
-        if (ok && n > 1) ok = issue_qk(1);
+        const uint32_t kbase = smem_u32(skv);
+        const uint32_t d_s = tmem_base + TM_S;
         for (int i = 0; i < n && ok; ++i) {
-          const int st = i % MLA_STAGES;
-          if (!mbar_wait(&p_full[i & 1], (i >> 1) & 1, abort_flag, p.status, MS_P_FULL, i)) { ok = false; break; }
+          const uint32_t ph = i & 1;
+          uint32_t accum = 0;
+          // ---- S = Q K^T, chunk by chunk (q chunk from shared memory or from TMEM)
+          for (int oc = 0; oc < 9 && ok; ++oc) {
+            const int c = order[oc];
+            if (!TRACE_WAIT(oc < 5 ? 1 : 2, mbar_wait(&kv_full[c], ph, abort_flag, p.status, MS_KV_FULL, c))) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t bd = umma_desc_kmajor_sw128(kbase + c * MLA_CHUNK_BYTES);
+            if (c < MLA_QS) {
+              const uint64_t ad = umma_desc_kmajor_sw128(smem_u32(sq) + c * MLA_Q_CHUNK);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) { umma_bf16(d_s, ad + 2 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
+            } else {
+              const uint32_t at = tmem_base + TM_Q + (c - MLA_QS) * 32;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) { umma_bf16_ts(d_s, at + 8 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
+            }
+            if (oc < 5) umma_commit(&kv_empty[c]);   // not a value chunk of this CTA: free for the next tile
+          }
+          if (!ok) break;
+          umma_commit(s_full);
+          // ---- O += P V
+          if (!TRACE_WAIT(3, mbar_wait(p_full, ph, abort_flag, p.status, MS_P_FULL, i))) { ok = false; break; }
           tc_fence_after();
-          const uint32_t vbase = smem_u32(skv + st * MLA_STAGE_BYTES) + vb * MLA_CHUNK_BYTES;
+          const uint32_t vbase = kbase + vb * MLA_CHUNK_BYTES;
 #pragma unroll
           for (int k = 0; k < MLA_TILE / 16; ++k) {
-            // 16 tokens per MMA: two 8-token groups of 1024 B; dims advance by whole 4 KB chunks
+            // 16 tokens per MMA: two 8-token groups of 1024 B; dims advance by whole 16 KB chunks
             const uint64_t bd = umma_desc_mnmajor_sw128(vbase + k * 2048, MLA_CHUNK_BYTES, 1024);
-            umma_bf16_ts(tmem_base + TM_O, tmem_base + TM_P + (i & 1) * (MLA_TILE / 2) + k * 8, bd, idesc_pv,
-                         (i > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_ts(tmem_base + TM_O, tmem_base + TM_S + k * 8, bd, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&kb_empty[st]);
+          for (int c = vb; c < vb + 4; ++c) umma_commit(&kv_empty[c]);
           umma_commit(o_done);
           if (i == n - 1) umma_commit(o_final);
-          if (i + 2 < n) ok = issue_qk(i + 2);
         }
       }
     } else {
       // ------------------------------------------------------------ softmax / correction / epilogue
+      // Eight warps: lane quadrant qd = warp & 3 selects 32 heads, group grp selects 64 of the 128 score
+      // columns (and 128 of the 256 output columns).  The two warps that share a quadrant exchange their
+      // row maxima through shared memory once per tile; row sums are only combined at the very end.
       const int qd = warp & 3;
+      const int grp = (warp - 2) >> 2;
       const int row = qd * 32 + lane;  // head
       const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
       float m = -INFINITY, l = 0.f;
       bool ok = true;
-      // this head's q values for latent dims 256..511 and the rope dims go to TMEM as packed bf16 pairs
+      int sync_no = 0;
+      // rendezvous of all eight softmax warps; watches the abort flag so that nobody can be stranded
+      auto group_sync = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) { __threadfence_block(); atomicAdd(sm_counter, 1); }
+        ++sync_no;
+        uint32_t spins = 0;
+        while (*(volatile int*)sm_counter < 8 * sync_no) {
+          if (((++spins) & 0xff) == 0 && *abort_flag) return false;
+        }
+        __syncwarp();
+        return true;
+      };
+      // this head's q values for the chunks kept in TMEM, as packed bf16 pairs (group g writes two chunks)
       {
         const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + ((size_t)bq * p.H + row) * 576 + MLA_QS * 64);
         const bool row_ok = row < p.H;
 #pragma unroll 1
-        for (int c = 0; c < MLA_QT; ++c) {
+        for (int c = grp * 2; c < grp * 2 + 2; ++c) {
           uint32_t v[32];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -250,31 +266,44 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (lane == 0) mbar_arrive(qt_full);
       }
       for (int i = 0; i < n; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, MS_S_FULL, i)) { ok = false; break; }
+        if (!TRACE_WAIT(4, mbar_wait(s_full, i & 1, abort_flag, p.status, MS_S_FULL, i))) { ok = false; break; }
         tc_fence_after();
-        uint32_t sv[32];
-        tmem_ld_x32(lane_addr + TM_S + st * MLA_TILE, sv);
-        tmem_ld_wait();
-        const int valid = kv_len - (tile_begin + i) * MLA_TILE;  // >= 1
-        float s[32];
-        float mx = -INFINITY;
+        const int valid = kv_len - (tile_begin + i) * MLA_TILE - grp * 64;  // valid columns of this group's half
+        float s[64];
+        {
+          uint32_t sv0[32], sv1[32];
+          tmem_ld_x32(lane_addr + TM_S + grp * 64, sv0);
+          tmem_ld_x32(lane_addr + TM_S + grp * 64 + 32, sv1);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          s[j] = (j < valid) ? __uint_as_float(sv[j]) * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, s[j]);
+          for (int j = 0; j < 32; ++j) {
+            s[j] = (j < valid) ? __uint_as_float(sv0[j]) * p.scale_log2 : -INFINITY;
+            s[32 + j] = (32 + j < valid) ? __uint_as_float(sv1[j]) * p.scale_log2 : -INFINITY;
+          }
         }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 64; j += 4) {
+          mx4[0] = fmaxf(mx4[0], s[j]); mx4[1] = fmaxf(mx4[1], s[j + 1]);
+          mx4[2] = fmaxf(mx4[2], s[j + 2]); mx4[3] = fmaxf(mx4[3], s[j + 3]);
+        }
+        const float mx_local = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        float* slab = sm_max;   // safe to reuse every tile: all reads happen before the second rendezvous
+        slab[grp * 128 + row] = mx_local;
+        if (!group_sync()) { ok = false; break; }
+        const float mx = fmaxf(slab[row], slab[128 + row]);
         const float m_new = fmaxf(m, mx);
         const bool grow = (m_new - m) > 8.0f;  // also true on the first tile (m = -inf)
         if (i == 0) {
           m = m_new;
         } else if (__any_sync(0xffffffffu, grow)) {
+          // the score MMA of this tile was issued after P V of the previous one, so O is already final
           if (!mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, MS_O_DONE, i)) { ok = false; break; }
           tc_fence_after();
           const float f = grow ? exp2f(m - m_new) : 1.0f;
           if (grow) { l *= f; m = m_new; }
 #pragma unroll 1
-          for (int c = 0; c < 256; c += 32) {
+          for (int c = grp * 128; c < grp * 128 + 128; c += 32) {
             uint32_t ov[32];
             tmem_ld_x32(lane_addr + TM_O + c, ov);
             tmem_ld_wait();
@@ -284,33 +313,44 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           }
           tmem_st_wait();
         }
-        uint32_t pk[16];
-        float rs = 0.f;
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[32];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = exp2f(s[2 * j] - m), p1 = exp2f(s[2 * j + 1] - m);
-          rs += p0 + p1;
+        for (int j = 0; j < 32; ++j) {
+          float p0, p1;
+          const float a0 = s[2 * j] - m, a1 = s[2 * j + 1] - m;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(a0));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(a1));
+          rs4[j & 3] += p0 + p1;
           __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
           pk[j] = *reinterpret_cast<uint32_t*>(&h2);
         }
-        l += rs;
-        tmem_st_x16(lane_addr + TM_P + st * (MLA_TILE / 2), pk);
+        l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        // P (packed bf16) overwrites the first half of S: every warp must have read its S columns first
+        if (!group_sync()) { ok = false; break; }
+        tmem_st_x32(lane_addr + TM_S + grp * 32, pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[st]);
+        if (lane == 0) mbar_arrive(p_full);
       }
       // o_done flips once per tile and is only sampled when a rescale is needed, so its parity cannot
       // tell "last tile retired" from "two tiles behind"; the single-use o_final barrier can.
       if (ok) ok = mbar_wait(o_final, 0, abort_flag, p.status, MS_O_DONE, n);
       if (ok) {
+        sm_sum[grp * 128 + row] = l;
+        ok = group_sync();
+      }
+      if (ok) {
         tc_fence_after();
-        const float inv_l = 1.0f / l;
+        const float inv_l = 1.0f / (sm_sum[row] + sm_sum[128 + row]);
+        const float l_tot = sm_sum[row] + sm_sum[128 + row];
         const bool row_ok = row < p.H;
+        const int c_lo = grp * 128;
         if (p.num_splits == 1) {
           __nv_bfloat16* orow = p.out + ((size_t)bq * p.H + row) * 512 + half * 256;
 #pragma unroll 1
-          for (int c = 0; c < 256; c += 32) {
+          for (int c = c_lo; c < c_lo + 128; c += 32) {
             uint32_t ov[32];
             tmem_ld_x32(lane_addr + TM_O + c, ov);
             tmem_ld_wait();
@@ -327,7 +367,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         } else {
           float* orow = p.o_part + (((size_t)bq * p.num_splits + split) * p.H + row) * 512 + half * 256;
 #pragma unroll 1
-          for (int c = 0; c < 256; c += 32) {
+          for (int c = c_lo; c < c_lo + 128; c += 32) {
             uint32_t ov[32];
             tmem_ld_x32(lane_addr + TM_O + c, ov);
             tmem_ld_wait();
@@ -340,12 +380,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
               }
             }
           }
-          if (half == 0 && row_ok)
-            p.lse_part[((size_t)bq * p.num_splits + split) * p.H + row] = m + log2f(l);
+          if (half == 0 && grp == 0 && row_ok)
+            p.lse_part[((size_t)bq * p.num_splits + split) * p.H + row] = m + log2f(l_tot);
         }
       }
     }
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && warp < 6) {
     // empty KV range for this split (or an empty / padding row): neutral partial result
     const int row = (warp & 3) * 32 + lane;
     if (row < p.H) {
@@ -360,6 +400,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
   }
 
+#ifdef MLA_TRACE
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && warp <= 2) {
+    const long long tot = clock64() - t_start;
+    if (warp == 0) { g_mla_trace[0] = trace[0]; g_mla_trace[8] = tot; g_mla_trace[9] = n; }
+    if (warp == 1) { g_mla_trace[1] = trace[1]; g_mla_trace[2] = trace[2]; g_mla_trace[3] = trace[3]; g_mla_trace[10] = tot; }
+    if (warp == 2) { g_mla_trace[4] = trace[4]; g_mla_trace[11] = tot; }
+  }
+#endif
   if (*abort_flag) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -404,6 +452,12 @@ __global__ void mla_combine_kernel(const float* __restrict__ o_part, const float
 
 using namespace omni;
 
+#ifdef MLA_TRACE
+extern "C" int omni_mla_trace_read(long long* out16) {
+  return (int)cudaMemcpyFromSymbol(out16, g_mla_trace, sizeof(long long) * 16);
+}
+#endif
+
 // Scratch needed for num_splits > 1: o_part = Bq*splits*H*512 floats, lse_part = Bq*splits*H floats.
 extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, long long num_slots,
                                const int* block_table, int bt_ld, const int* seq_lens, const int* q_to_seq, int Bq,
@@ -411,12 +465,13 @@ extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, l
                                float* lse_part, void* status, cudaStream_t stream) {
   if (Bq <= 0) return 0;
   if (H < 1 || H > 128) return -1;
-  if (block_size % MLA_TILE != 0) return -2;
+  if (block_size != 32 && block_size != 64 && block_size % 128 != 0) return -2;
   if (num_splits < 1) return -3;
   if (num_splits > 1 && (o_part == nullptr || lse_part == nullptr)) return -4;
   CUtensorMap tq, tkv;
   if (make_tmap_2d(&tq, q, 2, (uint64_t)Bq * H, 576, 576, 128, 64, true)) return -10;
-  if (make_tmap_2d(&tkv, cache, 2, (uint64_t)num_slots, 576, cache_ld, MLA_TILE, 64, true)) return -11;
+  const int box_rows = block_size < MLA_TILE ? block_size : MLA_TILE;
+  if (make_tmap_2d(&tkv, cache, 2, (uint64_t)num_slots, 576, cache_ld, box_rows, 64, true)) return -11;
   MlaDecodeParams p;
   p.q = (const __nv_bfloat16*)q; p.H = H; p.block_size = block_size; p.block_table = block_table; p.bt_ld = bt_ld; p.seq_lens = seq_lens;
   p.q_to_seq = q_to_seq; p.scale_log2 = scale * 1.4426950408889634f; p.num_splits = num_splits;
