@@ -142,7 +142,8 @@ def main():
     blocks = batch * ((per_req_tokens + bs - 1) // bs + 1) + 2
     ecfg = EngineConfig(model=mc.name, block_size=bs, num_kv_blocks=blocks, max_num_seqs=batch,
                         max_num_batched_tokens=max(16384, in_len), max_model_len=per_req_tokens + bs,
-                        num_speculative_tokens=mtp, decode_gear_list=[batch], enforce_eager=args.eager, seed=1234 + rank)
+                        num_speculative_tokens=mtp, decode_gear_list=[batch], enforce_eager=args.eager, seed=1234 + rank,
+                        ep_backend=args.ep_backend)
     t_load = time.time()
     eng = EngineCore(ecfg, model_cfg=mc)
     eng.worker.runner.cfg.control_accept_rate = args.accept_rate

@@ -43,6 +43,8 @@ class RunnerConfig:
     seed: int = 0
     kv_cache_dtype: str = "auto"
     control_accept_rate: float = -1.0          # test knob of the MTP verifier (reference: model_extra_config)
+    ep_backend: str = "fused"                  # fused (NVLink peer-memory kernels) | nccl (all-to-all baseline)
+    ep_wait_ms: float = 2000.0                 # bound of every cross-rank wait inside the fused kernels
 
 
 class ModelRunner:
@@ -85,7 +87,40 @@ class ModelRunner:
                 d.load_weights(wl, planner=self.planner)
         if self.planner is not None:
             self.planner.init_dram_weights(self.model)
+        self.setup_expert_parallel()
         logger.info("model %s loaded in %.1fs", cfg.name or cfg.architecture, time.time() - t0)
+
+    def setup_expert_parallel(self) -> None:
+        """With more than one rank the routed experts are sharded over all ranks.  Decode-sized batches go
+        through the fused NVLink dispatch/combine kernels (e4m3 rows), anything larger - or bf16 experts -
+        through the all-to-all baseline.  All ranks must take the same path in a step, so the choice is
+        agreed on the host group before every forward (:meth:`_agree_ep_path`)."""
+        self.ep_ctx = None
+        ps = get_parallel_state()
+        cfg = self.model_cfg
+        if ps.world_size == 1 or not cfg.is_moe:
+            return
+        moe_layers = [m for m in self.model.modules() if m.__class__.__name__ == "MoELayer"]
+        for d in self.drafters:
+            moe_layers += [m for m in d.modules() if m.__class__.__name__ == "MoELayer"]
+        self._moe_layers = moe_layers
+        if (self.cfg.ep_backend == "fused" and self.device.type == "cuda" and cfg.quantization == "fp8_block"):
+            from ...parallel.ep_fused import EpContext
+            self.ep_ctx = EpContext(cfg.hidden_size, cfg.num_experts_per_tok, self.cfg.max_num_seqs * self.tpr,
+                                    wait_ms=self.cfg.ep_wait_ms)
+            self.ep_max_tokens = self.ep_ctx.max_tokens
+
+    def _agree_ep_path(self, num_tokens: int) -> None:
+        """Every rank contributes its token count; the fused path is taken only if all of them fit."""
+        if getattr(self, "ep_ctx", None) is None:
+            return
+        import torch.distributed as dist
+        ps = get_parallel_state()
+        t = torch.tensor([num_tokens], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ps.group("cpu").group)
+        fused = int(t.item()) <= self.ep_max_tokens
+        for m in self._moe_layers:
+            m.ep_ctx = self.ep_ctx if fused else None
 
     def kv_bytes_per_block(self) -> int:
         cfg = self.model_cfg
@@ -299,6 +334,7 @@ class ModelRunner:
 
     def _run_prefill(self, so, reqs) -> ModelRunnerOutput:
         ids, md = self._prepare_prefill(so)
+        self._agree_ep_path(int(ids.shape[0]))
         hidden = self.model(ids, md, self.kv_caches)
         last_h = hidden[md.sample_indices]
         logits = self.model.compute_logits(last_h)
@@ -338,6 +374,7 @@ class ModelRunner:
         tpr, B = self.tpr, len(reqs)
         padded = self._get_closest_gear(B) if (self.graphs is not None) else B
         ids, md = self._prepare_decode(so, padded)
+        self._agree_ep_path(padded * tpr)
         steps_out: list = []
         spec_final = None
         for step in range(so.num_step):
@@ -400,6 +437,7 @@ class ModelRunner:
         so = SchedulerOutput([], False)
         ids, md = self._prepare_decode(so, padded)
         md.num_valid = self._to_dev([0], torch.int32)
+        self._agree_ep_path(padded * tpr)
         self._forward_decode(ids, md, padded)
 
     @torch.inference_mode()

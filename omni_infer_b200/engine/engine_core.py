@@ -42,6 +42,7 @@ class EngineConfig:
     enable_chunked_prefill: bool = os.environ.get("FORCE_ENABLE_CHUNK_PREFILL", "0") == "1"
     decode_gear_list: list = field(default_factory=list)
     enforce_eager: bool = False
+    ep_backend: str = "fused"
     seed: int = 0
     kv_transfer_config: Optional[dict] = None    # {"kv_role": "kv_producer"|"kv_consumer", ...}
     enable_omni_attn: bool = False
@@ -59,7 +60,7 @@ class EngineCore:
                           gpu_memory_utilization=cfg.gpu_memory_utilization, max_num_seqs=cfg.max_num_seqs,
                           max_model_len=cfg.max_model_len, max_num_batched_tokens=cfg.max_num_batched_tokens,
                           num_speculative_tokens=cfg.num_speculative_tokens, decode_gear_list=cfg.decode_gear_list,
-                          enforce_eager=cfg.enforce_eager, seed=cfg.seed)
+                          enforce_eager=cfg.enforce_eager, seed=cfg.seed, ep_backend=cfg.ep_backend)
         sched_conn = worker_conn = None
         if kv_connector_pair is not None:
             sched_conn, worker_conn = kv_connector_pair
@@ -86,6 +87,8 @@ class EngineCore:
                              enable_chunked_prefill=cfg.enable_chunked_prefill)
         self.scheduler = Scheduler(sc, self.kv, connector=sched_conn)
         self._ids = itertools.count()
+        from ..parallel import get_parallel_state
+        self._world = get_parallel_state().world_size
         self._pool = ThreadPoolExecutor(max_workers=1) if cfg.async_schedule else None
         self._inflight = None
         self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "generated_tokens": 0}
@@ -115,6 +118,10 @@ class EngineCore:
         if self.cfg.async_schedule:
             return self.step_async()
         so = self.scheduler.schedule()
+        if so.empty and self._world > 1:
+            # data-parallel ranks step together: an idle rank runs a padded dummy batch so that the
+            # expert-parallel exchanges of the busy ranks find their peer
+            self.worker.execute_dummy_batch()
         out = self.worker.execute_model(so)
         res = self.scheduler.update_from_output(so, out)
         self._account(so, res)

@@ -114,7 +114,7 @@ class MoELayer(nn.Module):
             t_hint = max(16, (T * k + self.slots_per_rank - 1) // self.slots_per_rank)
             y = self.experts(perm.x, perm.x_scale, perm.seg_start, perm.seg_len, perm.row_w, t_hint)
             return ops.moe_combine(y, perm.row_of, T, k, shared=shared)
-        if self.ep_ctx is not None:
+        if self.ep_ctx is not None and self.quant == "fp8_block":
             return self.ep_ctx.moe_forward(self, x, ids, w, shared)
         from ..parallel.ep_nccl import moe_forward_nccl
         return moe_forward_nccl(self, x, ids, w, shared)

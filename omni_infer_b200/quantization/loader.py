@@ -227,43 +227,57 @@ def load_quant_description(model_dir: str) -> dict:
 
 @torch.no_grad()
 def init_random_weights(model, seed: int = 0, std: float = 0.02) -> None:
-    """Random N(0, std) initialisation of every parameter (norm weights = 1, biases = 0); quantised
-    parameters are generated in bf16 chunk by chunk and block-quantised on the parameter's device."""
+    """Random N(0, std) initialisation (norm weights = 1, biases = 0).  Every tensor gets its own generator
+    seeded from (seed, parameter name) and every routed expert from (seed, layer, logical expert id), so the
+    weights do not depend on how many ranks the experts are sharded over: a 2-rank model is the same model as
+    the 1-rank one.  Quantised tensors are drawn in fp32 and block-quantised on their device."""
+    import zlib
+
     params = dict(model.named_parameters())
-    devs = {p.device for p in params.values()}
-    gens = {d: torch.Generator(device=d).manual_seed(seed) for d in devs}
+
+    def gen(dev, *key):
+        g = torch.Generator(device=dev)
+        g.manual_seed((seed * 1000003 + zlib.crc32("/".join(str(k) for k in key).encode())) % (2 ** 63 - 1))
+        return g
+
+    def fill(p, sp, g):
+        if p.dtype == FP8:
+            w = torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * std
+            q, s = quant_weight_fp8_block_ref(w)
+            p.copy_(q)
+            sp.copy_(s)
+        elif p.numel() > (1 << 28):
+            flat = p.view(-1)
+            step = 1 << 26
+            for i in range(0, flat.numel(), step):
+                n = min(step, flat.numel() - i)
+                flat[i:i + n].copy_(torch.randn(n, generator=g, device=p.device, dtype=torch.float32) * std)
+        else:
+            p.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * std)
+
+    expert_params = {}
+    for mname, mod in model.named_modules():
+        if mod.__class__.__name__ == "MoELayer":
+            for pn in ("w13", "w2"):
+                expert_params[f"{mname}.{pn}" if mname else pn] = mod
     for name, p in params.items():
-        g = gens[p.device]
         if name.endswith(("_scale", "weight_scale")):
             continue
+        if name in expert_params:
+            mod = expert_params[name]
+            sp = params.get(name + "_scale")
+            for slot in range(p.shape[0]):
+                logical = mod.e_lo + slot if mod.planner is None else mod.planner.logical_of_slot(mod.moe_index, slot)
+                g = gen(p.device, name, "expert", logical)
+                fill(p[slot], sp[slot] if sp is not None else None, g)
+            continue
+        g = gen(p.device, name)
         if "norm" in name and p.dim() == 1:
             p.fill_(1.0)
         elif name.endswith("bias") and p.dim() == 1 and "e_score" not in name:
             p.zero_()
         elif name.endswith("e_score_correction_bias"):
             p.copy_(torch.randn(p.shape, generator=g, device=p.device) * 0.01)
-        elif p.dtype == FP8:
-            sname = name + "_scale"
-            sp = params[sname]
-            lead = p.shape[:-2]
-            if len(lead) == 0:
-                w = torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * std
-                q, s = quant_weight_fp8_block_ref(w)
-                p.copy_(q)
-                sp.copy_(s)
-            else:
-                for i in range(p.shape[0]):
-                    w = torch.randn(p.shape[1:], generator=g, device=p.device, dtype=torch.float32) * std
-                    q, s = quant_weight_fp8_block_ref(w)
-                    p[i].copy_(q)
-                    sp[i].copy_(s)
         else:
-            if p.numel() > (1 << 28):
-                flat = p.view(-1)
-                step = 1 << 26
-                for i in range(0, flat.numel(), step):
-                    n = min(step, flat.numel() - i)
-                    flat[i:i + n].copy_(torch.randn(n, generator=g, device=p.device, dtype=torch.float32) * std)
-            else:
-                p.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * std)
+            fill(p, params.get(name + "_scale"), g)
     model.process_weights_after_loading()
