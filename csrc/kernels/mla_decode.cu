@@ -123,7 +123,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     mbar_init(p_full, 8);
     mbar_init(o_done, 1);
     mbar_init(o_final, 1);
-    mbar_init(qt_full, 4);
+    mbar_init(qt_full, 8);
     *abort_flag = 0;
     *sm_counter = 0;
     mbar_fence_init();

@@ -174,6 +174,9 @@ class ModelRunner:
         """Capture one CUDA graph per decode bucket, largest first so smaller ones reuse its memory pool."""
         if self.device.type != "cuda" or not self.cfg.use_cuda_graph or self.cfg.enforce_eager:
             return
+        if get_parallel_state().world_size > 1 and self.model_cfg.is_moe and getattr(self, "ep_ctx", None) is None:
+            logger.info("expert parallelism over NCCL all-to-all needs host-side split sizes: decode stays eager")
+            return
         from .cuda_graphs import DecodeGraphs
         self.graphs = DecodeGraphs(self)
         t0 = time.time()

@@ -41,14 +41,22 @@ if dist.is_initialized():
 
 
 def _run(world, env_extra, port):
+    import tempfile
+
     env = dict(os.environ, OMNI_ROOT=ROOT, NCCL_NVLS_ENABLE="0", **env_extra)
+    with tempfile.NamedTemporaryFile("w", suffix="_ep_worker.py", delete=False) as f:
+        f.write(WORKER)
+        script = f.name
     if world == 1:
-        cmd = [sys.executable, "-c", WORKER]
+        cmd = [sys.executable, script]
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-               "--master-addr", "127.0.0.1", "--master-port", str(port), "--no-python", sys.executable, "-c", WORKER]
+               "--master-addr", "127.0.0.1", "--master-port", str(port), script]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    os.unlink(script)
+    if res.returncode != 0:
+        errs = [l for l in res.stderr.splitlines() if not l.startswith(("W1", "[W", "***")) and "OMP_NUM" not in l]
+        raise AssertionError("\n".join(res.stdout.splitlines()[-10:] + errs[-40:]))
     line = [l for l in res.stdout.splitlines() if l.startswith("RESULT ")][-1]
     import json
     return json.loads(line[len("RESULT "):])
