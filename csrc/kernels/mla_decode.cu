@@ -24,6 +24,7 @@
 //
 // Stands where the reference calls npu_fused_infer_attention_score on the absorbed path
 // (omni/models/common/layers/attention/deepseek_mla.py:533-560, 625-650).
+#include "../include/omni_noalloc.h"
 #include "../include/omni_ptx.cuh"
 #include "../include/tma_host.h"
 
@@ -491,4 +492,51 @@ extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, l
     e = cudaGetLastError();
   }
   return (int)e;
+}
+
+// -------------------------------------------------------------------------------------------------------
+// Allocation-free variant (see omni_noalloc.h): the split-KV scratch is a fixed array inside the library.
+// In host code the array's name is only a stand-in for the symbol, not a device address; the address each
+// GPU gave it is fetched once per device with cudaGetSymbolAddress and passed to the kernels.
+// -------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_mla_noalloc_scratch[OMNI_MLA_NOALLOC_SCRATCH_BYTES];
+
+static unsigned char* noalloc_scratch_for_current_device(int* rc) {
+  static unsigned char* per_device[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) { *rc = e != cudaSuccess ? (int)e : -101; return nullptr; }
+  if (per_device[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_mla_noalloc_scratch);   // set-up: once per device, with that device current
+    if (e != cudaSuccess || p == nullptr) { *rc = e != cudaSuccess ? (int)e : -102; return nullptr; }
+    per_device[dev] = (unsigned char*)p;
+  }
+  *rc = 0;
+  return per_device[dev];
+}
+
+extern "C" int omni_mla_decode_noalloc(const void* q, const void* cache, int cache_ld, long long num_slots,
+                                       const int* block_table, int bt_ld, const int* seq_lens, const int* q_to_seq,
+                                       int Bq, int H, int block_size, float scale, int num_splits, void* out,
+                                       void* status, cudaStream_t stream) {
+  if (Bq <= 0) return 0;
+  if (num_splits < 1 || H < 1) return -3;
+  const unsigned long long parts = (unsigned long long)Bq * (unsigned long long)num_splits * (unsigned long long)H;
+  if (parts * 512ull * 4ull > (unsigned long long)OMNI_MLA_NOALLOC_OPART_BYTES ||
+      parts > (unsigned long long)OMNI_MLA_NOALLOC_LSE_FLOATS) {
+    fprintf(stderr,
+            "omni_mla_decode_noalloc: Bq*num_splits*H = %llu exceeds the built-in scratch (limit %u); "
+            "use omni_mla_decode with caller-provided scratch\n",
+            parts, (unsigned)(OMNI_MLA_NOALLOC_OPART_BYTES / (512u * 4u)));
+    return OMNI_NOALLOC_TOO_LARGE;
+  }
+  int rc = 0;
+  unsigned char* scratch = noalloc_scratch_for_current_device(&rc);
+  if (scratch == nullptr) return rc;
+  float* o_part = reinterpret_cast<float*>(scratch);
+  float* lse_part = reinterpret_cast<float*>(scratch + OMNI_MLA_NOALLOC_OPART_BYTES);
+  // num_splits == 1 writes `out` directly and leaves the scratch untouched; the pointers are passed either way
+  return omni_mla_decode(q, cache, cache_ld, num_slots, block_table, bt_ld, seq_lens, q_to_seq, Bq, H, block_size,
+                         scale, num_splits, out, o_part, lse_part, status, stream);
 }
