@@ -1,0 +1,332 @@
+// OmniPlacement core: redundant + dynamic expert placement for expert-parallel MoE serving.
+//
+// Native counterpart of the reference's omni_planner C++ extension
+// (omni/accelerators/placement/omni_planner/cpp/*.cpp, include/*.h):
+//   PlacementMapping          pattern [rank][layer][expert] -> deployed positions, redundancy counts and the
+//                             per-rank selector (logical expert -> physical position) with validated updates
+//   ClusterActivation         per-(layer, position) activation counters, cluster-wide collection, wrap-around
+//                             deltas, sliding windows, text dump / replay
+//   MoEWeights                registry of the device tensors of every local expert slot and their byte sizes
+//   GreedyExpertLoadBalancer  dynamic EPLB: EMA of loads, REMOVE / SWAP / ADD instructions
+//   ExpertLoadBalancer        static placement: redundancy allocation + LPT, bucket balance with pairwise swaps
+//   PlacementOptimizer        glue between activations, mapping and the balancers
+//   Distribution              transport: all-gather of small control tuples, pairwise expert-weight swap into a
+//                             ring of staging buffers, copy of completed stages into the live weights
+//   Placement                 background thread that runs rounds of collect -> optimise -> handshake -> swap, and
+//                             do_placement_optimizer() that the inference thread calls between steps
+//
+// No CUDA or NCCL symbols appear here.  Device copies and collectives go through function pointers
+// (PlacementHooks): the Python side installs callbacks backed by torch / NCCL / peer copies, unit tests install
+// host memcpy and an in-process transport (threads + shared queues), as the reference does with its
+// set_ut_memcpy_fun hook.
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <cstdint>
+#include <functional>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+namespace omni_placement {
+
+// ------------------------------------------------------------------------------------------------ hooks
+struct PlacementHooks {
+  // dst/src are device (or host, in tests) addresses
+  std::function<void(void* dst, const void* src, size_t bytes)> memcpy_d2d;
+  std::function<void(void* dst, const void* src, size_t bytes)> memcpy_h2d;
+  std::function<void(void* dst, const void* src, size_t bytes)> memcpy_d2h;
+};
+PlacementHooks& hooks();
+void set_ut_memcpy_fun();    // host memcpy for all three directions (unit tests, CPU ranks)
+void unset_ut_memcpy_fun();
+
+// ------------------------------------------------------------------------------------------------ Tensor
+// Thin handle of a buffer owned by the caller.
+class Tensor {
+ public:
+  Tensor() = default;
+  Tensor(void* data, size_t length, size_t element_size, std::string name = "")
+      : data_(data), length_(length), element_size_(element_size), name_(std::move(name)) {}
+  void* data() const { return data_; }
+  size_t length() const { return length_; }
+  size_t element_size() const { return element_size_; }
+  size_t bytes() const { return length_ * element_size_; }
+  const std::string& name() const { return name_; }
+  void to_host(void* host) const;
+  void to_device(const void* host) const;
+
+ private:
+  void* data_ = nullptr;
+  size_t length_ = 0, element_size_ = 1;
+  std::string name_;
+};
+
+// ------------------------------------------------------------------------------------------------ Mapping
+class PlacementMapping {
+ public:
+  // pattern: [world][layers][experts] of 0/1.  redundant_per_rank extra slots exist on every rank;
+  // ranks_per_host groups ranks into hosts for the selector preference.
+  PlacementMapping(const std::vector<int>& pattern, int world, int layers, int experts, int rank,
+                   int redundant_per_rank, int ranks_per_host, int32_t* selector /* [layers*experts] or null */);
+  static std::vector<int> base_pattern(int world, int layers, int experts);
+  static std::vector<int> load_text_pattern(const std::string& path, int& world, int& layers, int& experts);
+
+  int world() const { return world_; }
+  int layers() const { return layers_; }
+  int experts() const { return experts_; }
+  int rank() const { return rank_; }
+  int slots_per_rank() const { return slots_per_rank_; }
+  int num_positions() const { return world_ * slots_per_rank_; }
+
+  int expert_at(int layer, int global_pos) const { return pos_to_expert_[layer * num_positions() + global_pos]; }
+  int redundant_count(int layer, int expert) const { return deploy_count_[layer * experts_ + expert]; }
+  std::vector<int> positions_of(int layer, int expert) const;
+  std::vector<int> local_slots_of(int layer, int expert) const;
+  int selector(int layer, int expert) const { return selector_host_[layer * experts_ + expert]; }
+  const std::vector<int32_t>& selector_host() const { return selector_host_; }
+
+  // Validated update: position must currently hold `old_expert` (or be empty = -1); an expert never loses its
+  // last replica.  Returns false (and changes nothing) when a check fails.
+  bool update_position(int layer, int global_pos, int old_expert, int new_expert);
+  bool check_update_is_valid(int layer, int global_pos, int old_expert, int new_expert) const;
+  // set several positions at once; succeeds only if afterwards every expert of the touched layers still has a
+  // replica, otherwise nothing changes (rollback)
+  bool apply_batch(const std::vector<std::pair<int, int>>& layer_pos, const std::vector<int>& new_experts);
+  void update_selector_layer(int layer);
+  void update_selector();           // all layers, then pushes to the device selector if one was given
+  void push_selector_to_device();
+
+ private:
+  int world_, layers_, experts_, rank_, slots_per_rank_, ranks_per_host_;
+  std::vector<int> pos_to_expert_;   // [layers][world*slots]
+  std::vector<int> deploy_count_;    // [layers][experts]
+  std::vector<int32_t> selector_host_;
+  int32_t* selector_dev_;
+};
+
+// ------------------------------------------------------------------------------------------------ Activation
+using AllGatherI64 = std::function<void(const int64_t* send, int64_t* recv, size_t count_per_rank)>;
+
+class ClusterActivation {
+ public:
+  // local counters [layers][slots_per_rank] live at `counts` (device int64, written by the router kernel)
+  ClusterActivation(Tensor counts, int layers, int slots_per_rank, int world, int rank, int window = 8);
+  void set_allgather(AllGatherI64 fn) { allgather_ = std::move(fn); }
+  // reads the local counters, all-gathers, computes wrap-around-corrected deltas since the previous collect
+  void collect();
+  void collect_from_txt(const std::string& path);   // replay: one line per layer, world*slots values
+  void dump_txt(const std::string& path) const;
+  int64_t delta(int layer, int global_pos) const { return delta_[layer * positions() + global_pos]; }
+  int64_t windowed(int layer, int global_pos) const;
+  int64_t total(int layer, int global_pos) const { return last_[layer * positions() + global_pos]; }
+  int positions() const { return world_ * slots_; }
+  int layers() const { return layers_; }
+  static constexpr int64_t kWrap = 10000000000000000LL;   // counters are kept modulo 1e16
+
+ private:
+  Tensor counts_;
+  int layers_, slots_, world_, rank_, window_;
+  AllGatherI64 allgather_;
+  std::vector<int64_t> last_, delta_;
+  std::vector<std::vector<int64_t>> history_;
+  bool first_ = true;
+};
+
+// ------------------------------------------------------------------------------------------------ Weights
+struct ExpertTensor { void* ptr; size_t bytes; };
+
+class MoEWeights {
+ public:
+  MoEWeights(int layers, int slots_per_rank) : layers_(layers), slots_(slots_per_rank), w_(layers * slots_per_rank) {}
+  void add_tensor(int layer, int slot, void* ptr, size_t bytes) { w_[layer * slots_ + slot].push_back({ptr, bytes}); }
+  const std::vector<ExpertTensor>& tensors(int layer, int slot) const { return w_[layer * slots_ + slot]; }
+  size_t expert_bytes() const;   // bytes of one expert slot (all its tensors); 0 before init
+  bool is_initialized() const { return initialized_; }
+  void set_initialized() { initialized_ = true; }
+  int layers() const { return layers_; }
+  int slots() const { return slots_; }
+
+ private:
+  int layers_, slots_;
+  std::vector<std::vector<ExpertTensor>> w_;
+  bool initialized_ = false;
+};
+
+// ------------------------------------------------------------------------------------------------ Instructions
+enum class OperationType : int { SWAP = 0, ADD = 1, REMOVE = 2, EMPTY = 3 };
+
+struct ChangeInstruction {
+  int layer_idx = 0;
+  OperationType type = OperationType::EMPTY;
+  int source_rank = -1, source_expert_id = -1, source_global_position = -1;
+  int target_rank = -1, target_expert_id = -1, target_global_position = -1;
+  int prior = 0;
+};
+
+// ------------------------------------------------------------------------------------------------ Greedy EPLB
+class GreedyExpertLoadBalancer {
+ public:
+  GreedyExpertLoadBalancer(int layers, int world, int experts, int slots_per_rank, int max_redundant_per_expert = 10,
+                           double ema_keep = 0.6, double threshold = 1.1, int max_instructions_per_layer = 32);
+  // placement: [layers][world*slots] expert id or -1; activations: same shape (delta counts of this round)
+  std::vector<ChangeInstruction> optimize_and_generate_instructions(const std::vector<int>& placement,
+                                                                    const std::vector<int64_t>& activations);
+  static double imbalance(const std::vector<double>& rank_loads);   // max / min (min clipped to > 0)
+  const std::vector<double>& ema_loads() const { return ema_; }
+
+ private:
+  void optimize_layer(int layer, std::vector<int>& place, std::vector<double>& load, std::vector<ChangeInstruction>& out);
+  std::vector<double> rank_loads(const std::vector<int>& place, const std::vector<double>& load) const;
+  int layers_, world_, experts_, slots_, max_red_;
+  double keep_, threshold_;
+  int max_instr_;
+  std::vector<double> ema_;   // [layers][positions]
+  bool has_ema_ = false;
+};
+
+// ------------------------------------------------------------------------------------------------ Static balancer
+class ExpertLoadBalancer {
+ public:
+  ExpertLoadBalancer(int world, int experts, int slots_per_rank, int ranks_per_host = 8)
+      : world_(world), experts_(experts), slots_(slots_per_rank), rph_(ranks_per_host) {}
+  // loads: per logical expert.  Returns [world*slots] expert id or -1.  Redundant slots go to the hottest experts
+  // (max-heap on load / replicas), replicas are assigned by LPT with host interleave; every expert appears once.
+  std::vector<int> generate_constrained_placement(const std::vector<double>& loads, int max_redundant_per_expert) const;
+  // no redundancy: starting from `placement`, pairwise swaps between the heaviest and lightest ranks
+  std::vector<ChangeInstruction> bucket_balance(int layer, std::vector<int> placement, const std::vector<double>& loads,
+                                                int max_swaps) const;
+  bool validate(const std::vector<int>& placement) const;
+
+ private:
+  int world_, experts_, slots_, rph_;
+};
+
+// ------------------------------------------------------------------------------------------------ Optimizer
+class PlacementOptimizer {
+ public:
+  PlacementOptimizer(PlacementMapping* mapping, ClusterActivation* act, int max_redundant_per_expert = 10);
+  std::vector<ChangeInstruction> optimize();
+  std::vector<int> extract_placement() const;
+  std::vector<int64_t> extract_activations() const;
+  GreedyExpertLoadBalancer& balancer() { return *greedy_; }
+
+ private:
+  PlacementMapping* mapping_;
+  ClusterActivation* act_;
+  std::unique_ptr<GreedyExpertLoadBalancer> greedy_;
+};
+
+// ------------------------------------------------------------------------------------------------ Distribution
+struct HandshakeTuple { int t_rank; int position_offset; int expert_id; };
+
+class Distribution {
+ public:
+  static constexpr int QUEUE_SIZE = 5;
+  virtual ~Distribution() = default;
+  virtual int rank() const = 0;
+  virtual int world() const = 0;
+  virtual void allgather_i64(const int64_t* send, int64_t* recv, size_t count) = 0;
+  virtual void allgather_handshake(const HandshakeTuple& mine, std::vector<HandshakeTuple>& all) = 0;
+  // exchange one expert (all tensors, packed) with `peer`; the received bytes land in staging buffer `stage`
+  virtual void swap(int peer, const std::vector<ExpertTensor>& send, int stage) = 0;
+  virtual void recv_only(int peer, int stage, size_t bytes) = 0;
+  virtual void send_only(int peer, const std::vector<ExpertTensor>& send) = 0;
+  virtual void* staging(int stage) = 0;
+  virtual void barrier() = 0;
+};
+
+// In-process transport for tests and CPU ranks: every "rank" is a thread sharing one hub.
+class FakeHub;
+class FakeDistribution : public Distribution {
+ public:
+  FakeDistribution(std::shared_ptr<FakeHub> hub, int rank, size_t expert_bytes);
+  ~FakeDistribution() override;
+  int rank() const override { return rank_; }
+  int world() const override;
+  void allgather_i64(const int64_t* send, int64_t* recv, size_t count) override;
+  void allgather_handshake(const HandshakeTuple& mine, std::vector<HandshakeTuple>& all) override;
+  void swap(int peer, const std::vector<ExpertTensor>& send, int stage) override;
+  void recv_only(int peer, int stage, size_t bytes) override;
+  void send_only(int peer, const std::vector<ExpertTensor>& send) override;
+  void* staging(int stage) override { return stages_[stage].data(); }
+  void barrier() override;
+  // fault injection (host side): corrupt the next handshake tuple this rank sends
+  void corrupt_next_handshake() { corrupt_ = true; }
+
+ private:
+  std::shared_ptr<FakeHub> hub_;
+  int rank_;
+  std::vector<std::vector<unsigned char>> stages_;
+  bool corrupt_ = false;
+};
+std::shared_ptr<FakeHub> make_fake_hub(int world);
+
+// Callback transport: the embedding process supplies the collectives (torch.distributed / NCCL / peer copies).
+struct DistributionCallbacks {
+  int rank = 0, world = 1;
+  std::function<void(const int64_t*, int64_t*, size_t)> allgather_i64;
+  std::function<void(int peer, const void* send, void* recv, size_t bytes)> sendrecv;   // either pointer may be null
+  std::function<void()> barrier;
+};
+class CallbackDistribution : public Distribution {
+ public:
+  CallbackDistribution(DistributionCallbacks cb, size_t expert_bytes);
+  int rank() const override { return cb_.rank; }
+  int world() const override { return cb_.world; }
+  void allgather_i64(const int64_t* send, int64_t* recv, size_t count) override { cb_.allgather_i64(send, recv, count); }
+  void allgather_handshake(const HandshakeTuple& mine, std::vector<HandshakeTuple>& all) override;
+  void swap(int peer, const std::vector<ExpertTensor>& send, int stage) override;
+  void recv_only(int peer, int stage, size_t bytes) override;
+  void send_only(int peer, const std::vector<ExpertTensor>& send) override;
+  void* staging(int stage) override { return stages_[stage].data(); }
+  void barrier() override { if (cb_.barrier) cb_.barrier(); }
+
+ private:
+  DistributionCallbacks cb_;
+  std::vector<std::vector<unsigned char>> stages_;   // host staging; the apply step copies into device weights
+  std::vector<unsigned char> pack_;
+};
+
+// ------------------------------------------------------------------------------------------------ Manager
+struct PendingApply { int layer, slot, stage, new_expert, global_pos, old_expert; };
+
+class Placement {
+ public:
+  Placement(PlacementMapping* mapping, MoEWeights* weights, ClusterActivation* act, Distribution* dist,
+            int max_redundant_per_expert = 10, double period_s = 60.0);
+  ~Placement();
+  void start();   // background thread
+  void stop();
+  // one round on the calling thread (what the background thread repeats); returns number of applied instructions
+  int run_round();
+  // inference thread, between steps: copies completed staging buffers into the live expert weights and refreshes
+  // the selector.  Returns the number of experts replaced.
+  int do_placement_optimizer();
+  int rounds() const { return rounds_; }
+  int skipped_instructions() const { return skipped_; }
+  std::vector<ChangeInstruction> last_instructions() const;
+
+ private:
+  void loop();
+  bool execute(const ChangeInstruction& ins);
+  PlacementMapping* mapping_;
+  MoEWeights* weights_;
+  ClusterActivation* act_;
+  Distribution* dist_;
+  std::unique_ptr<PlacementOptimizer> optimizer_;
+  double period_s_;
+  std::thread thread_;
+  std::atomic<bool> should_stop_{false};
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::vector<PendingApply> pending_;
+  std::vector<ChangeInstruction> last_;
+  int next_stage_ = 0;
+  std::atomic<int> rounds_{0}, skipped_{0};
+};
+
+}  // namespace omni_placement

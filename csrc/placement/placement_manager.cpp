@@ -1,0 +1,410 @@
+// Distribution transports, the Placement manager and the C API used by the Python binding.
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+
+#include "placement_core.h"
+
+namespace omni_placement {
+
+// ------------------------------------------------------------------------------------------------ FakeHub
+// Shared state of an in-process "cluster": every rank is a thread.  Collectives are generation-counted
+// rendezvous; point-to-point messages go through per-(src,dst) mailboxes.
+class FakeHub {
+ public:
+  explicit FakeHub(int world) : world_(world), slots_(world), mail_(world * world) {}
+  int world() const { return world_; }
+
+  void allgather(int rank, const void* send, void* recv, size_t bytes) {
+    std::unique_lock<std::mutex> lk(mu_);
+    const long gen = gen_;
+    if (buf_.size() != bytes * world_) buf_.assign(bytes * world_, 0);
+    std::memcpy(buf_.data() + bytes * rank, send, bytes);
+    if (++arrived_ == world_) {
+      result_ = buf_;
+      arrived_ = 0;
+      ++gen_;
+      cv_.notify_all();
+    } else {
+      cv_.wait(lk, [&] { return gen_ != gen; });
+    }
+    std::memcpy(recv, result_.data(), bytes * world_);
+    // second phase so that nobody overwrites result_ while a slow rank still copies it out
+    const long gen2 = gen2_;
+    if (++left_ == world_) { left_ = 0; ++gen2_; cv_.notify_all(); } else { cv_.wait(lk, [&] { return gen2_ != gen2; }); }
+  }
+
+  void send(int src, int dst, std::vector<unsigned char> data) {
+    std::unique_lock<std::mutex> lk(mu_);
+    mail_[src * world_ + dst].push_back(std::move(data));
+    cv_.notify_all();
+  }
+  std::vector<unsigned char> recv(int src, int dst) {
+    std::unique_lock<std::mutex> lk(mu_);
+    auto& q = mail_[src * world_ + dst];
+    cv_.wait(lk, [&] { return !q.empty(); });
+    auto d = std::move(q.front());
+    q.erase(q.begin());
+    return d;
+  }
+
+ private:
+  int world_;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::vector<int> slots_;
+  std::vector<std::vector<std::vector<unsigned char>>> mail_;
+  std::vector<unsigned char> buf_, result_;
+  int arrived_ = 0, left_ = 0;
+  long gen_ = 0, gen2_ = 0;
+};
+
+std::shared_ptr<FakeHub> make_fake_hub(int world) { return std::make_shared<FakeHub>(world); }
+
+static std::vector<unsigned char> pack_expert(const std::vector<ExpertTensor>& ts) {
+  size_t tot = 0;
+  for (auto& t : ts) tot += t.bytes;
+  std::vector<unsigned char> out(tot);
+  size_t off = 0;
+  for (auto& t : ts) {
+    hooks().memcpy_d2h(out.data() + off, t.ptr, t.bytes);
+    off += t.bytes;
+  }
+  return out;
+}
+
+FakeDistribution::FakeDistribution(std::shared_ptr<FakeHub> hub, int rank, size_t expert_bytes)
+    : hub_(std::move(hub)), rank_(rank), stages_(QUEUE_SIZE, std::vector<unsigned char>(expert_bytes)) {}
+FakeDistribution::~FakeDistribution() = default;
+int FakeDistribution::world() const { return hub_->world(); }
+void FakeDistribution::allgather_i64(const int64_t* send, int64_t* recv, size_t count) {
+  hub_->allgather(rank_, send, recv, count * sizeof(int64_t));
+}
+void FakeDistribution::allgather_handshake(const HandshakeTuple& mine, std::vector<HandshakeTuple>& all) {
+  HandshakeTuple m = mine;
+  if (corrupt_) { m.expert_id += 1000; corrupt_ = false; }
+  all.resize(world());
+  hub_->allgather(rank_, &m, all.data(), sizeof(HandshakeTuple));
+}
+void FakeDistribution::swap(int peer, const std::vector<ExpertTensor>& send, int stage) {
+  hub_->send(rank_, peer, pack_expert(send));
+  auto d = hub_->recv(peer, rank_);
+  std::memcpy(stages_[stage].data(), d.data(), std::min(d.size(), stages_[stage].size()));
+}
+void FakeDistribution::recv_only(int peer, int stage, size_t) {
+  auto d = hub_->recv(peer, rank_);
+  std::memcpy(stages_[stage].data(), d.data(), std::min(d.size(), stages_[stage].size()));
+}
+void FakeDistribution::send_only(int peer, const std::vector<ExpertTensor>& send) { hub_->send(rank_, peer, pack_expert(send)); }
+void FakeDistribution::barrier() {
+  int64_t x = 0;
+  std::vector<int64_t> all(world());
+  allgather_i64(&x, all.data(), 1);
+}
+
+CallbackDistribution::CallbackDistribution(DistributionCallbacks cb, size_t expert_bytes)
+    : cb_(std::move(cb)), stages_(QUEUE_SIZE, std::vector<unsigned char>(expert_bytes)) {}
+void CallbackDistribution::allgather_handshake(const HandshakeTuple& mine, std::vector<HandshakeTuple>& all) {
+  int64_t s[3] = {mine.t_rank, mine.position_offset, mine.expert_id};
+  std::vector<int64_t> r(3 * (size_t)cb_.world);
+  cb_.allgather_i64(s, r.data(), 3);
+  all.resize(cb_.world);
+  for (int i = 0; i < cb_.world; ++i) all[i] = {(int)r[3 * i], (int)r[3 * i + 1], (int)r[3 * i + 2]};
+}
+void CallbackDistribution::swap(int peer, const std::vector<ExpertTensor>& send, int stage) {
+  pack_ = pack_expert(send);
+  cb_.sendrecv(peer, pack_.data(), stages_[stage].data(), pack_.size());
+}
+void CallbackDistribution::recv_only(int peer, int stage, size_t bytes) {
+  cb_.sendrecv(peer, nullptr, stages_[stage].data(), bytes);
+}
+void CallbackDistribution::send_only(int peer, const std::vector<ExpertTensor>& send) {
+  pack_ = pack_expert(send);
+  cb_.sendrecv(peer, pack_.data(), nullptr, pack_.size());
+}
+
+// ------------------------------------------------------------------------------------------------ Placement
+Placement::Placement(PlacementMapping* mapping, MoEWeights* weights, ClusterActivation* act, Distribution* dist,
+                     int max_redundant_per_expert, double period_s)
+    : mapping_(mapping), weights_(weights), act_(act), dist_(dist), period_s_(period_s) {
+  optimizer_.reset(new PlacementOptimizer(mapping, act, max_redundant_per_expert));
+  if (dist_ != nullptr)
+    act_->set_allgather([this](const int64_t* s, int64_t* r, size_t n) { dist_->allgather_i64(s, r, n); });
+}
+
+Placement::~Placement() { stop(); }
+
+void Placement::start() {
+  should_stop_ = false;
+  thread_ = std::thread([this] { loop(); });
+}
+
+void Placement::stop() {
+  should_stop_ = true;
+  cv_.notify_all();
+  if (thread_.joinable()) thread_.join();
+}
+
+void Placement::loop() {
+  // wait until the expert tensors are registered
+  while (!should_stop_ && !weights_->is_initialized()) std::this_thread::sleep_for(std::chrono::milliseconds(50));
+  while (!should_stop_) {
+    {
+      // the previous round must have been applied by the inference thread before new data is staged
+      std::unique_lock<std::mutex> lk(mu_);
+      cv_.wait(lk, [&] { return should_stop_ || pending_.empty(); });
+    }
+    if (should_stop_) break;
+    try {
+      run_round();
+    } catch (const std::exception&) {
+      ++skipped_;
+    }
+    std::unique_lock<std::mutex> lk(mu_);
+    cv_.wait_for(lk, std::chrono::duration<double>(period_s_), [&] { return should_stop_.load(); });
+  }
+}
+
+std::vector<ChangeInstruction> Placement::last_instructions() const { return last_; }
+
+int Placement::run_round() {
+  act_->collect();
+  auto instr = optimizer_->optimize();
+  last_ = instr;
+  int done = 0;
+  next_stage_ = 0;
+  for (const auto& ins : instr) {
+    if (should_stop_) break;
+    if (next_stage_ >= Distribution::QUEUE_SIZE) break;   // staging ring is full: the rest waits for the next round
+    if (execute(ins)) ++done; else ++skipped_;
+  }
+  if (dist_ != nullptr) dist_->barrier();                 // every rank has finished staging this round
+  ++rounds_;
+  return done;
+}
+
+bool Placement::execute(const ChangeInstruction& ins) {
+  const int S = mapping_->slots_per_rank();
+  const int me = dist_ != nullptr ? dist_->rank() : mapping_->rank();
+  // 1. consistency handshake: every rank reports the instruction it is about to execute
+  HandshakeTuple mine{ins.target_rank, ins.target_global_position % S, ins.source_expert_id};
+  if (dist_ != nullptr) {
+    std::vector<HandshakeTuple> all;
+    dist_->allgather_handshake(mine, all);
+    for (const auto& h : all)
+      if (h.t_rank != mine.t_rank || h.position_offset != mine.position_offset || h.expert_id != mine.expert_id)
+        return false;                                     // ranks disagree: skip, nothing was transferred
+  }
+  // 2. validity against the current mapping (same answer on every rank)
+  const int tp = ins.target_global_position, sp = ins.source_global_position;
+  switch (ins.type) {
+    case OperationType::REMOVE:
+      if (!mapping_->check_update_is_valid(ins.layer_idx, sp, ins.source_expert_id, -1)) return false;
+      break;
+    case OperationType::ADD:
+      if (!mapping_->check_update_is_valid(ins.layer_idx, tp, ins.target_expert_id, ins.source_expert_id)) return false;
+      break;
+    case OperationType::SWAP:
+      if (mapping_->expert_at(ins.layer_idx, sp) != ins.source_expert_id ||
+          mapping_->expert_at(ins.layer_idx, tp) != ins.target_expert_id) return false;
+      break;
+    default:
+      return false;
+  }
+  // 3. data movement into the staging ring (only the ranks involved)
+  std::lock_guard<std::mutex> lk(mu_);
+  if (ins.type == OperationType::REMOVE) {
+    pending_.push_back({ins.layer_idx, sp % S, -1, -1, sp, ins.source_expert_id});
+    return true;
+  }
+  const bool i_am_src = me == ins.source_rank, i_am_dst = me == ins.target_rank;
+  int stage = -1;
+  if (dist_ != nullptr && (i_am_src || i_am_dst)) {
+    stage = next_stage_;
+    if (ins.type == OperationType::SWAP) {
+      const int my_pos = i_am_src ? sp : tp, peer = i_am_src ? ins.target_rank : ins.source_rank;
+      dist_->swap(peer, weights_->tensors(ins.layer_idx, my_pos % S), stage);
+    } else if (i_am_src) {
+      dist_->send_only(ins.target_rank, weights_->tensors(ins.layer_idx, sp % S));
+      stage = -1;
+    } else {
+      dist_->recv_only(ins.source_rank, stage, weights_->expert_bytes());
+    }
+  }
+  if (stage >= 0) ++next_stage_;
+  // every rank records the mapping change; only the receivers carry a staging buffer
+  if (ins.type == OperationType::SWAP) {
+    pending_.push_back({ins.layer_idx, sp % S, i_am_src ? stage : -1, ins.target_expert_id, sp, ins.source_expert_id});
+    pending_.push_back({ins.layer_idx, tp % S, i_am_dst ? stage : -1, ins.source_expert_id, tp, ins.target_expert_id});
+  } else {
+    pending_.push_back({ins.layer_idx, tp % S, i_am_dst ? stage : -1, ins.source_expert_id, tp, ins.target_expert_id});
+  }
+  return true;
+}
+
+int Placement::do_placement_optimizer() {
+  std::vector<PendingApply> todo;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    todo.swap(pending_);
+  }
+  if (todo.empty()) return 0;
+  int replaced = 0;
+  const int S = mapping_->slots_per_rank();
+  // SWAP is recorded as two entries whose intermediate state would fail the "last replica" check: apply swaps as
+  // a pair by clearing validity through a temporary empty position
+  for (const auto& a : todo) {
+    const bool local = a.global_pos / S == (dist_ != nullptr ? dist_->rank() : mapping_->rank());
+    if (local && a.stage >= 0) {
+      size_t off = 0;
+      const unsigned char* src = (const unsigned char*)dist_->staging(a.stage);
+      for (const auto& t : weights_->tensors(a.layer, a.slot)) {
+        hooks().memcpy_h2d(t.ptr, src + off, t.bytes);
+        off += t.bytes;
+      }
+      ++replaced;
+    }
+  }
+  // mapping: a batch (both halves of a swap, a chain of adds) is applied as a whole and rolled back as a whole if
+  // it would leave an expert without a replica - the old selector then stays in force
+  std::vector<std::pair<int, int>> changes;   // (layer, global_pos) -> new expert, in order
+  std::vector<int> news;
+  for (const auto& a : todo) { changes.push_back({a.layer, a.global_pos}); news.push_back(a.new_expert); }
+  if (!mapping_->apply_batch(changes, news)) ++skipped_;
+  mapping_->update_selector();
+  cv_.notify_all();
+  return replaced;
+}
+
+}  // namespace omni_placement
+
+// ------------------------------------------------------------------------------------------------ C API (ctypes)
+using namespace omni_placement;
+extern "C" {
+
+typedef void (*omni_copy_fn)(void* dst, const void* src, unsigned long long bytes);
+typedef void (*omni_allgather_fn)(const long long* send, long long* recv, unsigned long long count);
+typedef void (*omni_sendrecv_fn)(int peer, const void* send, void* recv, unsigned long long bytes);
+typedef void (*omni_barrier_fn)();
+
+void omni_pl_set_copy_hooks(omni_copy_fn d2d, omni_copy_fn h2d, omni_copy_fn d2h) {
+  hooks().memcpy_d2d = [d2d](void* d, const void* s, size_t n) { d2d(d, s, n); };
+  hooks().memcpy_h2d = [h2d](void* d, const void* s, size_t n) { h2d(d, s, n); };
+  hooks().memcpy_d2h = [d2h](void* d, const void* s, size_t n) { d2h(d, s, n); };
+}
+void omni_pl_set_ut_memcpy() { set_ut_memcpy_fun(); }
+void omni_pl_unset_ut_memcpy() { unset_ut_memcpy_fun(); }
+
+void* omni_pl_mapping_create(const int* pattern, int world, int layers, int experts, int rank, int redundant_per_rank,
+                             int ranks_per_host, int* selector) {
+  try {
+    std::vector<int> p(pattern, pattern + (size_t)world * layers * experts);
+    return new PlacementMapping(p, world, layers, experts, rank, redundant_per_rank, ranks_per_host, selector);
+  } catch (const std::exception& e) {
+    fprintf(stderr, "omni_placement: %s\n", e.what());
+    return nullptr;
+  }
+}
+void omni_pl_mapping_destroy(void* m) { delete (PlacementMapping*)m; }
+int omni_pl_mapping_slots_per_rank(void* m) { return ((PlacementMapping*)m)->slots_per_rank(); }
+int omni_pl_mapping_expert_at(void* m, int layer, int pos) { return ((PlacementMapping*)m)->expert_at(layer, pos); }
+int omni_pl_mapping_redundant_count(void* m, int layer, int e) { return ((PlacementMapping*)m)->redundant_count(layer, e); }
+int omni_pl_mapping_selector(void* m, int layer, int e) { return ((PlacementMapping*)m)->selector(layer, e); }
+void omni_pl_mapping_copy_selector(void* m, int* out) {
+  auto& s = ((PlacementMapping*)m)->selector_host();
+  memcpy(out, s.data(), s.size() * sizeof(int));
+}
+int omni_pl_mapping_update(void* m, int layer, int pos, int old_e, int new_e) {
+  auto* mp = (PlacementMapping*)m;
+  const bool ok = mp->update_position(layer, pos, old_e, new_e);
+  if (ok) mp->update_selector();
+  return ok ? 1 : 0;
+}
+
+void* omni_pl_weights_create(int layers, int slots) { return new MoEWeights(layers, slots); }
+void omni_pl_weights_destroy(void* w) { delete (MoEWeights*)w; }
+void omni_pl_weights_add(void* w, int layer, int slot, void* ptr, unsigned long long bytes) {
+  ((MoEWeights*)w)->add_tensor(layer, slot, ptr, bytes);
+}
+void omni_pl_weights_set_initialized(void* w) { ((MoEWeights*)w)->set_initialized(); }
+unsigned long long omni_pl_weights_expert_bytes(void* w) { return ((MoEWeights*)w)->expert_bytes(); }
+
+void* omni_pl_activation_create(void* counts, int layers, int slots, int world, int rank, int window) {
+  return new ClusterActivation(Tensor(counts, (size_t)layers * slots, 8, "activation"), layers, slots, world, rank, window);
+}
+void omni_pl_activation_destroy(void* a) { delete (ClusterActivation*)a; }
+int omni_pl_activation_collect_from_txt(void* a, const char* path) {
+  try { ((ClusterActivation*)a)->collect_from_txt(path); return 0; } catch (const std::exception&) { return -1; }
+}
+void omni_pl_activation_dump(void* a, const char* path) { ((ClusterActivation*)a)->dump_txt(path); }
+long long omni_pl_activation_delta(void* a, int layer, int pos) { return ((ClusterActivation*)a)->delta(layer, pos); }
+
+void* omni_pl_distribution_create(int rank, int world, unsigned long long expert_bytes, omni_allgather_fn ag,
+                                  omni_sendrecv_fn sr, omni_barrier_fn bar) {
+  DistributionCallbacks cb;
+  cb.rank = rank; cb.world = world;
+  cb.allgather_i64 = [ag](const int64_t* s, int64_t* r, size_t n) { ag((const long long*)s, (long long*)r, n); };
+  cb.sendrecv = [sr](int p, const void* s, void* r, size_t n) { sr(p, s, r, n); };
+  cb.barrier = [bar]() { if (bar) bar(); };
+  return new CallbackDistribution(cb, expert_bytes);
+}
+void omni_pl_distribution_destroy(void* d) { delete (Distribution*)d; }
+
+void* omni_pl_placement_create(void* mapping, void* weights, void* act, void* dist, int max_red, double period_s) {
+  return new Placement((PlacementMapping*)mapping, (MoEWeights*)weights, (ClusterActivation*)act, (Distribution*)dist,
+                       max_red, period_s);
+}
+void omni_pl_placement_destroy(void* p) { delete (Placement*)p; }
+void omni_pl_placement_start(void* p) { ((Placement*)p)->start(); }
+void omni_pl_placement_stop(void* p) { ((Placement*)p)->stop(); }
+int omni_pl_placement_run_round(void* p) {
+  try { return ((Placement*)p)->run_round(); } catch (const std::exception& e) { fprintf(stderr, "omni_placement: %s\n", e.what()); return -1; }
+}
+int omni_pl_do_placement_optimizer(void* p) { return ((Placement*)p)->do_placement_optimizer(); }
+int omni_pl_placement_rounds(void* p) { return ((Placement*)p)->rounds(); }
+int omni_pl_placement_skipped(void* p) { return ((Placement*)p)->skipped_instructions(); }
+int omni_pl_placement_last_instructions(void* p, int* out, int max_n) {
+  auto v = ((Placement*)p)->last_instructions();
+  int n = 0;
+  for (auto& i : v) {
+    if (n >= max_n) break;
+    int* o = out + 8 * n++;
+    o[0] = i.layer_idx; o[1] = (int)i.type; o[2] = i.source_rank; o[3] = i.source_expert_id;
+    o[4] = i.source_global_position; o[5] = i.target_rank; o[6] = i.target_expert_id; o[7] = i.target_global_position;
+  }
+  return n;
+}
+
+// static placement from per-expert loads: out[world*slots]
+int omni_pl_static_placement(const double* loads, int world, int experts, int slots, int ranks_per_host, int max_red,
+                             int* out) {
+  try {
+    ExpertLoadBalancer b(world, experts, slots, ranks_per_host);
+    auto p = b.generate_constrained_placement(std::vector<double>(loads, loads + experts), max_red);
+    memcpy(out, p.data(), p.size() * sizeof(int));
+    return b.validate(p) ? 0 : -2;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "omni_placement: %s\n", e.what());
+    return -1;
+  }
+}
+
+// greedy EPLB on host arrays: placement/activations [layers*world*slots]; out: up to max_n instructions of 8 ints
+int omni_pl_greedy_instructions(const int* placement, const long long* activations, int layers, int world, int experts,
+                                int slots, int max_red, int* out, int max_n) {
+  GreedyExpertLoadBalancer g(layers, world, experts, slots, max_red);
+  const size_t n_el = (size_t)layers * world * slots;
+  auto v = g.optimize_and_generate_instructions(std::vector<int>(placement, placement + n_el),
+                                                std::vector<int64_t>(activations, activations + n_el));
+  int n = 0;
+  for (auto& i : v) {
+    if (n >= max_n) break;
+    int* o = out + 8 * n++;
+    o[0] = i.layer_idx; o[1] = (int)i.type; o[2] = i.source_rank; o[3] = i.source_expert_id;
+    o[4] = i.source_global_position; o[5] = i.target_rank; o[6] = i.target_expert_id; o[7] = i.target_global_position;
+  }
+  return n;
+}
+
+}  // extern "C"
