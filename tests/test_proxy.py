@@ -1,0 +1,178 @@
+"""Global proxy: C++ unit tests of the balancer formulas / JSON surgery, and the two-phase prefill -> decode flow
+against mock prefill and decode HTTP servers on localhost (including SSE relay, header injection, failure
+pass-through, and ejection of a dead peer)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import threading
+import time
+import urllib.request
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SRC = os.path.join(ROOT, "csrc", "proxy")
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_cpp_lb_and_json_units(tmp_path):
+    exe = str(tmp_path / "test_lb")
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-Wall", "-pthread", "-fsanitize=address,undefined", "-I", SRC, "-o", exe,
+           os.path.join(SRC, "lb.cpp"), os.path.join(SRC, "test_lb.cpp")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0 and "sanitize" in res.stderr:
+        res = subprocess.run([c for c in cmd if not c.startswith("-fsanitize")], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0 and "ALL PASSED" in run.stdout, run.stdout + run.stderr
+
+
+class _Recorder:
+    def __init__(self):
+        self.requests = []
+
+
+def _make_server(kind, rec, fail=False):
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            rec.requests.append((kind, dict(self.headers), body))
+            if kind == "prefill":
+                if fail:
+                    out = json.dumps({"error": "boom"}).encode()
+                    self.send_response(500)
+                else:
+                    out = json.dumps({"id": "p", "choices": [{"text": "x"}],
+                                      "kv_transfer_params": {"remote_block_ids": [3, 4], "remote_host_ip": "tcp://127.0.0.1:1"}}).encode()
+                    self.send_response(200)
+                self.send_header("Content-Type", "application/json")
+                self.send_header("Content-Length", str(len(out)))
+                self.end_headers()
+                self.wfile.write(out)
+            else:
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.end_headers()
+                for i in range(3):
+                    chunk = {"choices": [{"text": f"t{i}"}], "usage": {"total_tokens": 10 + i}, "output_num_token": i + 1,
+                             "prompt_num_token": 7}
+                    self.wfile.write(f"data: {json.dumps(chunk)}\n\n".encode())
+                    self.wfile.flush()
+                    time.sleep(0.02)
+                self.wfile.write(b"data: [DONE]\n\n")
+
+    srv = ThreadingHTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return srv
+
+
+@pytest.fixture
+def proxy_binary():
+    from omni_infer_b200.accelerators.sched.global_proxy import proxy_binary as pb
+    return str(pb())
+
+
+def _start_proxy(binary, port, prefill_ports, decode_ports, extra=()):
+    cmd = [binary, "--listen", f"127.0.0.1:{port}", "--decode-servers", ",".join(f"127.0.0.1:{p}" for p in decode_ports),
+           "--log-level", "0", "--fail-timeout", "30", *extra]
+    if prefill_ports:
+        cmd += ["--prefill-servers", ",".join(f"127.0.0.1:{p}" for p in prefill_ports)]
+    proc = subprocess.Popen(cmd)
+    for _ in range(100):
+        try:
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=0.5).read()
+            return proc
+        except Exception:
+            time.sleep(0.05)
+    proc.kill()
+    raise RuntimeError("proxy did not come up")
+
+
+def _post(port, body, headers=None):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json", **(headers or {})})
+    try:
+        with urllib.request.urlopen(req, timeout=10) as r:
+            return r.status, r.read().decode()
+    except urllib.error.HTTPError as e:
+        return e.code, e.read().decode()
+
+
+def test_two_phase_flow_and_stream_relay(proxy_binary):
+    rec = _Recorder()
+    p_srv, d_srv = _make_server("prefill", rec), _make_server("decode", rec)
+    port = _free_port()
+    proc = _start_proxy(proxy_binary, port, [p_srv.server_port], [d_srv.server_port])
+    try:
+        status, text = _post(port, {"model": "m", "prompt": "hello", "max_tokens": 32, "stream": True,
+                                    "stream_options": {"include_usage": True}})
+        assert status == 200 and text.count("data:") == 4 and "[DONE]" in text
+        (k1, h1, b1), (k2, h2, b2) = rec.requests
+        assert k1 == "prefill" and b1["max_tokens"] == 1 and b1["stream"] is False and "stream_options" not in b1
+        assert k2 == "decode" and b2["max_tokens"] == 32 and b2["stream"] is True
+        assert b2["kv_transfer_params"]["remote_block_ids"] == [3, 4]
+        assert h1.get("X-Request-Id") and h1["X-Request-Id"] == h2["X-Request-Id"]
+        _post(port, {"prompt": "x", "max_tokens": 2}, {"X-Request-Id": "abc"})
+        assert rec.requests[-1][1]["X-Request-Id"] == "abc"
+        metrics = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=2).read().decode()
+        assert 'omni_proxy_served_total{pool="decode",peer="0"} 2' in metrics
+        assert 'omni_proxy_active_requests{pool="decode",peer="0"} 0' in metrics
+    finally:
+        proc.terminate()
+        proc.wait(timeout=5)
+        p_srv.shutdown()
+        d_srv.shutdown()
+
+
+def test_prefill_failure_passthrough_and_peer_ejection(proxy_binary):
+    rec = _Recorder()
+    bad_p, d_srv = _make_server("prefill", rec, fail=True), _make_server("decode", rec)
+    port = _free_port()
+    proc = _start_proxy(proxy_binary, port, [bad_p.server_port], [d_srv.server_port])
+    try:
+        status, text = _post(port, {"prompt": "x", "max_tokens": 4})
+        assert status == 500 and "boom" in text
+        assert all(k != "decode" for k, _, _ in rec.requests)        # decode never saw the failed request
+    finally:
+        proc.terminate()
+        proc.wait(timeout=5)
+        bad_p.shutdown()
+    # one dead decode peer (closed port) and one live: requests succeed and the dead one is ejected
+    rec2 = _Recorder()
+    p_srv, d_ok = _make_server("prefill", rec2), _make_server("decode", rec2)
+    dead = _free_port()
+    port = _free_port()
+    proc = _start_proxy(proxy_binary, port, [p_srv.server_port], [dead, d_ok.server_port], extra=("--decode-lb", "round_robin"))
+    try:
+        for _ in range(4):
+            status, _ = _post(port, {"prompt": "x", "max_tokens": 4})
+            assert status == 200
+        metrics = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=2).read().decode()
+        assert 'omni_proxy_peer_up{pool="decode",peer="0"} 0' in metrics
+        assert 'omni_proxy_served_total{pool="decode",peer="1"} 4' in metrics
+    finally:
+        proc.terminate()
+        proc.wait(timeout=5)
+        for s in (p_srv, d_ok, d_srv):
+            s.shutdown()
+
+
+def test_launcher_dry_run(capsys):
+    from omni_infer_b200.accelerators.sched import global_proxy as gp
+    assert gp.main(["--decode-servers-list", "127.0.0.1:9", "--prefill-servers-list", "127.0.0.1:8,127.0.0.1:7",
+                    "--decode-lb-sdk", "weighted_least_active", "--dry-run"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["resolved"]["prefill"] == 2 and out["resolved"]["decode_lb"] == "weighted_least_active"
