@@ -1,0 +1,342 @@
+"""Prefill/decode disaggregation connector (reference: LLMDataDistConnector,
+omni/accelerators/pd/llmdatadist_connector_v1.py:87-728, and its transfer manager llmdatadist_manager.py:132-482).
+
+Roles
+  * ``kv_producer`` (prefill instance): a request that finishes its single prefill token hands
+    ``kv_transfer_params = {remote_block_ids, remote_engine_id, remote_host, spec_token_ids, prompt_token_ids,
+    prefilled_token}`` back to the client (the proxy splices it into the decode request) and keeps its blocks until
+    the decode side has them.
+  * ``kv_consumer`` (decode instance): the scheduler reserves local blocks for the whole prompt
+    (``get_num_new_matched_tokens`` -> asynchronous load), the worker side asks the producer to push the blocks
+    into its paged cache, and the request leaves WAITING_FOR_REMOTE_KVS when the push is acknowledged.
+
+Transfer: the producer copies blocks into the consumer's cache (NVLink peer memory on GPUs, csrc/kernels/kv_push.cu;
+index copy on CPU).  Control messages travel over a pluggable transport: an in-process hub (tests, CPU mock, both
+engines in one process) or TCP (``multiprocessing.connection``) between processes, where the consumer registers
+the CUDA IPC handles of its cache tensors on first contact.
+
+Robustness: a push request is retried ``retries`` times ``retry_wait_s`` apart and abandoned after
+``sync_timeout_s`` (reference: 3 x 2 s, 20 s); an abandoned request is reported in ``failed_recving`` and the
+scheduler falls back to prefilling it locally.  Duplicate acknowledgements and acknowledgements for unknown
+requests are ignored."""
+from __future__ import annotations
+
+import logging
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .kv_push import PeerCacheView, flatten_cache, push_blocks_cuda, push_blocks_torch
+
+logger = logging.getLogger("omni_infer_b200.pd")
+
+
+@dataclass
+class ReqMeta:
+    request_id: str
+    local_block_ids: list
+    remote_block_ids: list
+    remote_host: str
+    remote_engine_id: str = ""
+
+
+@dataclass
+class ConnectorMetadata:
+    requests: list = field(default_factory=list)
+
+
+# ------------------------------------------------------------------------------------------------ transports
+class InProcessHub:
+    """Endpoint registry for engines that live in one process.  Fault injection for tests: ``drop_next`` swallows
+    that many push requests, ``duplicate_acks`` delivers every acknowledgement twice."""
+    endpoints: dict = {}
+    drop_next: int = 0
+    duplicate_acks: bool = False
+    lock = threading.Lock()
+
+    @classmethod
+    def reset(cls):
+        cls.endpoints, cls.drop_next, cls.duplicate_acks = {}, 0, False
+
+    @classmethod
+    def register(cls, endpoint: str, worker) -> None:
+        cls.endpoints[endpoint] = worker
+
+    @classmethod
+    def send_push_request(cls, endpoint: str, msg: dict) -> bool:
+        with cls.lock:
+            if cls.drop_next > 0:
+                cls.drop_next -= 1
+                return True            # the message is lost on the way: the sender cannot tell
+        w = cls.endpoints.get(endpoint)
+        if w is None:
+            return False
+        threading.Thread(target=w.handle_push_request, args=(msg,), daemon=True).start()
+        return True
+
+    @classmethod
+    def send_ack(cls, endpoint: str, msg: dict) -> None:
+        w = cls.endpoints.get(endpoint)
+        if w is not None:
+            w.handle_ack(msg)
+            if cls.duplicate_acks:
+                w.handle_ack(msg)
+
+
+class TcpTransport:
+    """Control channel between processes.  Every worker connector listens on its endpoint; messages are pickled
+    dicts: {'op': 'push', ...} consumer -> producer, {'op': 'ack', ...} producer -> consumer."""
+
+    def __init__(self, endpoint: str, worker):
+        from multiprocessing.connection import Listener
+        host, port = endpoint.replace("tcp://", "").rsplit(":", 1)
+        self.listener = Listener((host, int(port)), authkey=b"omni-pd")
+        self.worker = worker
+        self._stop = False
+        threading.Thread(target=self._serve, daemon=True).start()
+
+    def _serve(self):
+        while not self._stop:
+            try:
+                conn = self.listener.accept()
+            except OSError:
+                return
+            threading.Thread(target=self._handle, args=(conn,), daemon=True).start()
+
+    def _handle(self, conn):
+        try:
+            msg = conn.recv()
+            if msg.get("op") == "push":
+                self.worker.handle_push_request(msg)
+            elif msg.get("op") == "ack":
+                self.worker.handle_ack(msg)
+        except (EOFError, OSError):
+            pass
+        finally:
+            conn.close()
+
+    @staticmethod
+    def send(endpoint: str, msg: dict, timeout_s: float = 5.0) -> bool:
+        from multiprocessing.connection import Client
+        host, port = endpoint.replace("tcp://", "").rsplit(":", 1)
+        try:
+            c = Client((host, int(port)), authkey=b"omni-pd")
+            c.send(msg)
+            c.close()
+            return True
+        except (OSError, EOFError):
+            return False
+
+    def close(self):
+        self._stop = True
+        self.listener.close()
+
+
+# ------------------------------------------------------------------------------------------------ scheduler side
+class SchedulerConnector:
+    def __init__(self, kv_role: str, engine_id: str, endpoint: str, block_size: int, num_speculative_tokens: int = 0,
+                 worker=None):
+        self.kv_role, self.engine_id, self.endpoint, self.block_size = kv_role, engine_id, endpoint, block_size
+        self.num_spec = num_speculative_tokens
+        self.worker = worker                  # same-process worker connector (fast path delivery)
+        self._pending: list = []
+
+    @property
+    def is_producer(self) -> bool:
+        return self.kv_role in ("kv_producer", "kv_both")
+
+    @property
+    def is_consumer(self) -> bool:
+        return self.kv_role in ("kv_consumer", "kv_both")
+
+    # -- consumer
+    def get_num_new_matched_tokens(self, req, num_computed_tokens: int):
+        """External tokens = the prompt rounded up to whole blocks, loaded asynchronously."""
+        p = req.kv_transfer_params or {}
+        if not (self.is_consumer and p.get("do_remote_prefill") and p.get("remote_block_ids")):
+            return 0, False
+        n = len(req.prompt_token_ids)
+        return (n + self.block_size - 1) // self.block_size * self.block_size - num_computed_tokens, True
+
+    def update_state_after_alloc(self, req, num_external_tokens: int) -> None:
+        p = req.kv_transfer_params or {}
+        n_blocks = (len(req.prompt_token_ids) + self.block_size - 1) // self.block_size
+        self._pending.append(ReqMeta(req.request_id, list(req.block_ids[:n_blocks]), list(p["remote_block_ids"][:n_blocks]),
+                                     p["remote_host"], p.get("remote_engine_id", "")))
+        p["do_remote_prefill"] = False        # handled: a fallback re-schedule prefills locally
+
+    def build_connector_meta(self) -> ConnectorMetadata:
+        meta = ConnectorMetadata(self._pending)
+        self._pending = []
+        return meta
+
+    def kick(self, meta: ConnectorMetadata) -> None:
+        """Fast path: hand the metadata to the worker connector right away instead of with the next step."""
+        if self.worker is not None and meta.requests:
+            self.worker.bind_connector_metadata(meta)
+            self.worker.start_load_kv()
+
+    # -- producer
+    def request_finished(self, req, block_ids: list):
+        """Returns (delay_free, kv_transfer_params).  Only requests capped at their prefill token hand over KV."""
+        from ...engine.request import RequestStatus
+        p = req.kv_transfer_params or {}
+        if not (self.is_producer and p.get("do_remote_decode") and req.status == RequestStatus.FINISHED_LENGTH_CAPPED):
+            return False, None
+        n_blocks = (len(req.prompt_token_ids) + self.block_size - 1) // self.block_size
+        params = {"do_remote_prefill": True, "do_remote_decode": False, "remote_block_ids": list(block_ids[:n_blocks]),
+                  "remote_engine_id": self.engine_id, "remote_cluster_id": self.engine_id, "remote_host": self.endpoint,
+                  "remote_host_ip": self.endpoint, "spec_token_ids": list(req.spec_token_ids) or [0] * self.num_spec,
+                  "prompt_token_ids": list(req.prompt_token_ids),
+                  "prefilled_token": req.output_token_ids[0] if req.output_token_ids else None}
+        if self.worker is not None:
+            self.worker.expect_pull(req.request_id)
+        return True, params
+
+
+# ------------------------------------------------------------------------------------------------ worker side
+class WorkerConnector:
+    def __init__(self, kv_role: str, engine_id: str, endpoint: str, transport: str = "inproc", sync_timeout_s: float = 20.0,
+                 retries: int = 3, retry_wait_s: float = 2.0):
+        self.kv_role, self.engine_id, self.endpoint, self.transport = kv_role, engine_id, endpoint, transport
+        self.sync_timeout_s, self.retries, self.retry_wait_s = sync_timeout_s, retries, retry_wait_s
+        self.kv_tensors: list = []
+        self._meta: Optional[ConnectorMetadata] = None
+        self._lock = threading.Lock()
+        self._done_recv: set = set()
+        self._failed_recv: set = set()
+        self._done_send: set = set()
+        self._inflight: dict = {}          # request id -> ReqMeta (consumer)
+        self._expected: set = set()        # producer: requests whose blocks wait to be pushed
+        self._peer_views: dict = {}        # producer: consumer endpoint -> cache view
+        self._tcp = None
+        if transport == "inproc":
+            InProcessHub.register(endpoint, self)
+        else:
+            self._tcp = TcpTransport(endpoint, self)
+
+    # -- set-up
+    def register_kv_caches(self, kv_caches) -> None:
+        self.kv_tensors = flatten_cache(kv_caches)
+
+    def cache_descriptor(self) -> dict:
+        """What a producer needs to write into this cache from another process (CUDA IPC handles)."""
+        t0 = self.kv_tensors[0]
+        desc = {"block_bytes": t0[0].numel() * t0.element_size(), "num_blocks": t0.shape[0], "n_tensors": len(self.kv_tensors)}
+        if t0.is_cuda:
+            from ...parallel.symmetric_heap import export_ipc_handles
+            desc["ipc"] = export_ipc_handles(self.kv_tensors)
+        return desc
+
+    # -- step hooks used by the model runner
+    def bind_connector_metadata(self, meta) -> None:
+        self._meta = meta
+
+    def start_load_kv(self) -> None:
+        meta, self._meta = self._meta, None
+        if meta is None:
+            return
+        for r in meta.requests:
+            with self._lock:
+                self._inflight[r.request_id] = r
+            threading.Thread(target=self._request_push, args=(r,), daemon=True).start()
+
+    def wait_for_save(self) -> None:
+        """Producer side: blocks are written by the forward pass itself; nothing to flush."""
+
+    def get_finished(self, finished_req_ids=None):
+        with self._lock:
+            s, r = self._done_send, self._done_recv
+            self._done_send, self._done_recv = set(), set()
+        return s, r
+
+    def take_failed(self) -> set:
+        with self._lock:
+            f, self._failed_recv = self._failed_recv, set()
+        return f
+
+    def expect_pull(self, request_id: str) -> None:
+        with self._lock:
+            self._expected.add(request_id)
+
+    # -- consumer: ask the producer to push, wait for the acknowledgement
+    def _send(self, endpoint: str, msg: dict) -> bool:
+        if self.transport == "inproc":
+            if msg["op"] == "push":
+                return InProcessHub.send_push_request(endpoint, msg)
+            InProcessHub.send_ack(endpoint, msg)
+            return True
+        return TcpTransport.send(endpoint, msg)
+
+    def _request_push(self, r: ReqMeta) -> None:
+        msg = {"op": "push", "request_id": r.request_id, "src_blocks": r.remote_block_ids, "dst_blocks": r.local_block_ids,
+               "reply_to": self.endpoint, "consumer": self.engine_id}
+        if self.transport != "inproc":
+            msg["cache"] = self.cache_descriptor()
+        deadline = time.monotonic() + self.sync_timeout_s
+        for attempt in range(self.retries + 1):
+            self._send(r.remote_host, msg)
+            wait_until = min(deadline, time.monotonic() + self.retry_wait_s)
+            while time.monotonic() < wait_until:
+                with self._lock:
+                    if r.request_id not in self._inflight:
+                        return                       # acknowledged
+                time.sleep(0.002)
+            if time.monotonic() >= deadline:
+                break
+            logger.warning("kv push for %s not acknowledged, retry %d", r.request_id, attempt + 1)
+        with self._lock:
+            if self._inflight.pop(r.request_id, None) is not None:
+                self._failed_recv.add(r.request_id)
+        logger.error("kv push for %s abandoned after %.1fs", r.request_id, self.sync_timeout_s)
+
+    def handle_ack(self, msg: dict) -> None:
+        with self._lock:
+            if self._inflight.pop(msg["request_id"], None) is not None:     # duplicates and strangers are ignored
+                self._done_recv.add(msg["request_id"])
+
+    # -- producer: copy the blocks into the consumer's cache, then acknowledge
+    def _peer_cache(self, msg: dict):
+        if self.transport == "inproc":
+            return InProcessHub.endpoints[msg["reply_to"]].kv_tensors
+        key = msg["reply_to"]
+        if key not in self._peer_views:
+            d = msg["cache"]
+            from ...parallel.symmetric_heap import open_ipc_handles
+            self._peer_views[key] = PeerCacheView(open_ipc_handles(d["ipc"]), d["block_bytes"], d["num_blocks"])
+        return self._peer_views[key]
+
+    def handle_push_request(self, msg: dict) -> None:
+        rid = msg["request_id"]
+        with self._lock:
+            known = rid in self._expected
+        if not known:
+            logger.warning("push request for unknown or already served request %s", rid)
+            # a retry of a request that was served: acknowledge again so the consumer can stop waiting
+            self._send(msg["reply_to"], {"op": "ack", "request_id": rid})
+            return
+        peer = self._peer_cache(msg)
+        if isinstance(peer, PeerCacheView):
+            push_blocks_cuda(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
+        else:
+            push_blocks_torch(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
+            if self.kv_tensors and self.kv_tensors[0].is_cuda:
+                torch.cuda.synchronize()
+        with self._lock:
+            self._expected.discard(rid)
+            self._done_send.add(rid)
+        self._send(msg["reply_to"], {"op": "ack", "request_id": rid})
+
+    def close(self) -> None:
+        if self._tcp is not None:
+            self._tcp.close()
+
+
+def dump_thread_to_file(path: str) -> None:
+    """Stack of every thread (connector threads included) for post-mortems."""
+    import faulthandler
+    with open(path, "w") as f:
+        faulthandler.dump_traceback(file=f, all_threads=True)

@@ -142,11 +142,20 @@ class ModelRunner:
         dt = self.model.model.dtype if hasattr(self.model, "model") else torch.bfloat16
         self.num_blocks = num_blocks
 
+        ipc = (self.kv_connector is not None and getattr(self.kv_connector, "transport", "inproc") != "inproc"
+               and self.device.type == "cuda")
+
+        def zeros(*shape):
+            if ipc:     # another process will open this memory through CUDA IPC
+                from ...parallel.symmetric_heap import alloc_ipc_tensor
+                return alloc_ipc_tensor(shape, dt)
+            return torch.zeros(*shape, dtype=dt, device=self.device)
+
         def one():
             if cfg.use_mla:
-                return torch.zeros(num_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim, dtype=dt, device=self.device)
-            return (torch.zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim, dtype=dt, device=self.device),
-                    torch.zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim, dtype=dt, device=self.device))
+                return zeros(num_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim)
+            return (zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim),
+                    zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim))
 
         self.kv_caches = [one() for _ in range(self.model.num_kv_layers)]
         self.drafter_kv = [[one()] for _ in self.drafters]
@@ -317,9 +326,11 @@ class ModelRunner:
             self.kv_connector.bind_connector_metadata(so.kv_connector_metadata)
             self.kv_connector.start_load_kv()
         if so.empty:
+            failed = set()
             if self.kv_connector is not None:
                 fin_send, fin_recv = self.kv_connector.get_finished(so.finished_req_ids)
-            return ModelRunnerOutput([], [[]], None, fin_send, fin_recv)
+                failed = self.kv_connector.take_failed()
+            return ModelRunnerOutput([], [[]], None, fin_send, fin_recv, failed)
         if self.planner is not None:
             self.planner.place_experts()
         reqs = [s.request for s in so.scheduled]
@@ -331,6 +342,7 @@ class ModelRunner:
             self.kv_connector.wait_for_save()
             fin_send, fin_recv = self.kv_connector.get_finished(so.finished_req_ids)
             out.finished_sending, out.finished_recving = fin_send, fin_recv
+            out.failed_recving = self.kv_connector.take_failed()
         out.step_time_s = time.perf_counter() - t0
         self.step_times.append(out.step_time_s)
         return out

@@ -121,6 +121,7 @@ class ModelRunnerOutput:
     spec_token_ids: Optional[list] = None      # next drafts per request
     finished_sending: set = field(default_factory=set)
     finished_recving: set = field(default_factory=set)
+    failed_recving: set = field(default_factory=set)     # remote KV never arrived: prefill locally instead
     step_time_s: float = 0.0
 
 

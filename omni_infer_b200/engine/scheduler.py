@@ -253,6 +253,15 @@ class Scheduler:
         results: list = []
         if out.finished_recving:
             self.finished_recving |= set(out.finished_recving)
+        for rid in getattr(out, "failed_recving", None) or ():
+            # the remote KV never arrived: give the blocks back and prefill the prompt on this instance
+            req = self.requests.get(rid)
+            if req is not None and req.status == RequestStatus.WAITING_FOR_REMOTE_KVS:
+                self.kv.free(req)
+                req.status = RequestStatus.WAITING
+                req.num_computed_tokens = 0
+                req.record("KV transfer failed: local prefill")
+                self.stats["kv_fallbacks"] = self.stats.get("kv_fallbacks", 0) + 1
         for rid in out.finished_sending or ():
             req = self.pending_free.pop(rid, None)
             if req is not None:

@@ -68,3 +68,36 @@ class SymmetricBuffer:
         if self.local_ptr:
             L.omni_symm_free(ctypes.c_void_p(self.local_ptr))
             self.local_ptr = 0
+
+
+def alloc_ipc_tensor(shape, dtype, device=None) -> torch.Tensor:
+    """A zero-filled tensor backed by its own ``cudaMalloc`` allocation, so that its base address can be exported
+    with CUDA IPC (tensors from the caching allocator are sub-allocations and cannot)."""
+    n = 1
+    for d in shape:
+        n *= d
+    nbytes = n * torch.empty(0, dtype=dtype).element_size()
+    p = ctypes.c_void_p()
+    nat.check_rc(nat.lib().omni_symm_alloc(ctypes.byref(p), ctypes.c_longlong(max(nbytes, 256))), "omni_symm_alloc")
+    t = torch.as_tensor(_CudaArray(p.value, nbytes), device="cuda").view(dtype).view(*shape)
+    t._omni_ipc_base = p.value
+    return t
+
+
+def export_ipc_handles(tensors) -> list:
+    out = []
+    for t in tensors:
+        h = (ctypes.c_ubyte * 64)()
+        nat.check_rc(nat.lib().omni_symm_get_handle(ctypes.c_void_p(t.data_ptr()), h), "omni_symm_get_handle")
+        out.append(bytes(h))
+    return out
+
+
+def open_ipc_handles(handles) -> list:
+    ptrs = []
+    for hb in handles:
+        h = (ctypes.c_ubyte * 64)(*hb)
+        q = ctypes.c_void_p()
+        nat.check_rc(nat.lib().omni_symm_open_handle(h, ctypes.byref(q)), "omni_symm_open_handle")
+        ptrs.append(q.value)
+    return ptrs
