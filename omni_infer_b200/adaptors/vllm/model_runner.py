@@ -63,6 +63,7 @@ class ModelRunner:
         self.tpr = 1 + cfg.num_speculative_tokens
         self._bt_width = (cfg.max_model_len + cfg.block_size - 1) // cfg.block_size + 1
         self.step_times: list = []
+        self.omni = None
 
     # ------------------------------------------------------------------ model / cache set-up
     def load_model(self, weights=None, seed: Optional[int] = 0) -> None:
@@ -162,6 +163,22 @@ class ModelRunner:
         if self.kv_connector is not None:
             self.kv_connector.register_kv_caches(self.kv_caches + [k[0] for k in self.drafter_kv])
 
+    def enable_omni_attn(self, state, num_window_blocks: int) -> None:
+        """Compressed layers get a cache of per-request windows; decode runs eagerly from here on."""
+        cfg, bs = self.model_cfg, self.cfg.block_size
+        self.omni = state
+        dt = self.model.model.dtype
+        for i in range(self.model.num_kv_layers):
+            if not state.is_compressed(i):
+                continue
+            if cfg.use_mla:
+                self.kv_caches[i] = torch.zeros(num_window_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim, dtype=dt,
+                                                device=self.device)
+            else:
+                self.kv_caches[i] = tuple(torch.zeros(num_window_blocks, bs, cfg.num_key_value_heads, cfg.head_dim,
+                                                      dtype=dt, device=self.device) for _ in range(2))
+        self.graphs = None
+
     # ------------------------------------------------------------------ gears / graphs
     def gear_list(self) -> list:
         if self.cfg.decode_gear_list:
@@ -231,6 +248,13 @@ class ModelRunner:
             context_lens=ctx, max_q=max(qlens), max_k=max(seq_lens),
             kv_gather_slots=self._to_dev(gather, torch.int64) if need_gather else None,
             sample_indices=self._to_dev(sample_idx, torch.int64))
+        if self.omni is not None:
+            oslots = []
+            for s in so.scheduled:
+                r = s.request
+                oslots += self.omni.prefill_slots(r.omni_block_ids, r.num_computed_tokens, s.num_scheduled_tokens,
+                                                  r.num_prompt_tokens)
+            md.omni = {"pattern": self.omni.pattern, "slot_mapping": self._to_dev(oslots, torch.int64)}
         return self._to_dev(ids, torch.int64), md
 
     def _prepare_decode(self, so: SchedulerOutput, padded: int):
@@ -300,6 +324,13 @@ class ModelRunner:
             is_prefill=False, positions=d64[n:2 * n], slot_mapping=d64[2 * n:3 * n], block_table=d_bt, seq_lens=d_seq,
             tokens_per_req=tpr, q_seq_lens=d_q, q_to_seq=d_q2s, max_seq_len=max_seq,
             num_valid=d_nv if padded != B else None)
+        if self.omni is not None:
+            nb = self.omni.spec.blocks_per_request
+            wt = [list(s.request.omni_block_ids) for s in so.scheduled] + [[0] * nb] * (padded - B)
+            pl = [s.request.num_prompt_tokens for s in so.scheduled] + [0] * (padded - B)
+            om = self.omni.decode_metadata(d_seq, self._to_dev(pl, torch.int32), self._to_dev(wt, torch.int32))
+            om["pattern"] = self.omni.pattern
+            md.omni = om
         return d64[:n], md
 
     # ------------------------------------------------------------------ sampling

@@ -13,6 +13,7 @@ class GQAAttention(nn.Module):
     def __init__(self, cfg, layer_idx: int, *, dtype, device=None, cos_sin=None):
         super().__init__()
         self.cfg = cfg
+        self.layer_idx = layer_idx
         self.Hq, self.Hkv, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         quant = cfg.quantization if cfg.quantization == "fp8_block" else "none"
         self.qkv_proj = Linear(cfg.hidden_size, (self.Hq + 2 * self.Hkv) * self.D, dtype=dtype, quant=quant,
@@ -27,6 +28,7 @@ class GQAAttention(nn.Module):
         pass
 
     def forward(self, x, md: AttnMetadata, kv_cache, xq=None):
+        md = _omni_view(md, self.layer_idx)
         T = x.shape[0]
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         k_cache, v_cache = kv_cache
@@ -47,3 +49,17 @@ class GQAAttention(nn.Module):
             o = ops.attention.gqa_decode(q.contiguous(), k_cache, v_cache, md.block_table, md.q_seq_lens, self.scale,
                                          md.max_seq_len)
         return self.o_proj(o.reshape(T, Hq * D))
+
+
+def _omni_view(md: AttnMetadata, layer_idx: int) -> AttnMetadata:
+    """Metadata as a compressed Omni-Attention layer sees it: its own slot mapping and, for decode, the per-request
+    window table and attended lengths.  Full layers (and runs without Omni-Attention) get ``md`` unchanged."""
+    om = md.omni
+    if om is None or layer_idx >= len(om["pattern"]) or not om["pattern"][layer_idx]:
+        return md
+    import copy
+    v = copy.copy(md)
+    v.slot_mapping = om["slot_mapping"]
+    if not md.is_prefill:
+        v.block_table, v.q_seq_lens, v.max_seq_len, v.q_to_seq = om["block_table"], om["q_seq_lens"], om["max_seq_len"], None
+    return v

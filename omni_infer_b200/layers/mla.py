@@ -71,6 +71,7 @@ class MLAAttention(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, x, md: AttnMetadata, kv_cache, xq=None):
+        md = _omni_view(md, self.layer_idx)
         if md.is_prefill:
             return self._forward_prefill(x, xq, md, kv_cache)
         return self._forward_decode(x, xq, md, kv_cache)
@@ -100,3 +101,17 @@ class MLAAttention(nn.Module):
                                max_seq_len=md.max_seq_len, kv_lora=self.kvl)
         o = ops.bmm_heads(o_lat, self.w_uv)
         return self.o_proj(o.reshape(T, H * self.vd))
+
+
+def _omni_view(md: AttnMetadata, layer_idx: int) -> AttnMetadata:
+    """Metadata as a compressed Omni-Attention layer sees it: its own slot mapping and, for decode, the per-request
+    window table and attended lengths.  Full layers (and runs without Omni-Attention) get ``md`` unchanged."""
+    om = md.omni
+    if om is None or layer_idx >= len(om["pattern"]) or not om["pattern"][layer_idx]:
+        return md
+    import copy
+    v = copy.copy(md)
+    v.slot_mapping = om["slot_mapping"]
+    if not md.is_prefill:
+        v.block_table, v.q_seq_lens, v.max_seq_len, v.q_to_seq = om["block_table"], om["q_seq_lens"], om["max_seq_len"], None
+    return v
