@@ -1,0 +1,260 @@
+"""OpenAI-compatible HTTP front end over one engine (one API server + one engine core per data-parallel rank, as
+the reference arranges with its scale-out patch).
+
+  POST /v1/completions, /v1/chat/completions   streaming (SSE) or not
+  GET  /health, /metrics                        liveness and Prometheus text
+  POST /start_profile, /stop_profile            torch profiler on the worker
+
+Behaviour carried over from the reference's engine patches:
+  * every stream chunk carries ``prompt_num_token`` / ``output_num_token`` and ``usage.total_tokens`` so the proxy's
+    body filters can track decode load (num_token_for_proxy.patch)
+  * a request with ``kv_transfer_params.do_remote_decode`` (sent by the proxy with max_tokens = 1) answers with the
+    ``kv_transfer_params`` for the decode instance, including ``prompt_token_ids`` and the ``prefilled_token`` so the
+    decode side neither tokenises again nor recomputes the first token (tokenizer_proc_pool.patch,
+    patch_support_prefilled_token_skip_tokenize.patch)
+  * long prompts are tokenised in the process pool (engine/tokenizer_pool.py)
+  * keep-alive timeout 120 s."""
+from __future__ import annotations
+
+import json
+import logging
+import queue
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import Optional
+
+from .engine_core import EngineConfig, EngineCore
+from .request import SamplingParams
+from .tokenizer_pool import TokenizerPool
+
+logger = logging.getLogger("omni_infer_b200.api")
+
+
+class AsyncEngine:
+    """Engine loop on its own thread; per-request output queues."""
+
+    def __init__(self, engine: EngineCore):
+        self.engine = engine
+        self.queues: dict = {}
+        self.lock = threading.Lock()
+        self.inbox: queue.Queue = queue.Queue()
+        self._stop = False
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+        self.stats = {"requests": 0, "tokens": 0, "started": time.time()}
+
+    def submit(self, prompt_ids, sampling, request_id, kv_transfer_params=None) -> queue.Queue:
+        q: queue.Queue = queue.Queue()
+        with self.lock:
+            self.queues[request_id] = q
+        self.inbox.put((prompt_ids, sampling, request_id, kv_transfer_params))
+        self.stats["requests"] += 1
+        return q
+
+    def abort(self, request_id):
+        self.inbox.put(("abort", request_id))
+
+    def _loop(self):
+        eng = self.engine
+        while not self._stop:
+            try:
+                while True:
+                    item = self.inbox.get_nowait() if eng.has_unfinished else self.inbox.get(timeout=0.05)
+                    if item[0] == "abort":
+                        eng.abort(item[1])
+                    else:
+                        eng.add_request(item[0], item[1], item[2], item[3])
+            except queue.Empty:
+                pass
+            if not eng.has_unfinished:
+                continue
+            try:
+                outs = eng.step()
+            except Exception as e:  # noqa: BLE001  (a failed step must not kill the serving thread)
+                logger.exception("engine step failed: %s", e)
+                with self.lock:
+                    for q in self.queues.values():
+                        q.put(None)
+                    self.queues.clear()
+                continue
+            for o in outs:
+                self.stats["tokens"] += len(o.new_token_ids)
+                with self.lock:
+                    q = self.queues.get(o.request_id)
+                    if o.finished:
+                        self.queues.pop(o.request_id, None)
+                if q is not None:
+                    q.put(o)
+
+    def stop(self):
+        self._stop = True
+
+
+def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
+    class Handler(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+        timeout = 120           # keep-alive
+
+        def log_message(self, *a):
+            pass
+
+        def _json(self, code, obj):
+            body = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_GET(self):
+            if self.path == "/health":
+                return self._json(200, {"status": "ok"})
+            if self.path == "/metrics":
+                s, e = aeng.stats, aeng.engine
+                text = (f"omni_requests_total {s['requests']}\nomni_generated_tokens_total {s['tokens']}\n"
+                        f"omni_running_requests {e.scheduler.num_running}\nomni_waiting_requests {e.scheduler.num_waiting}\n"
+                        f"omni_kv_cache_usage {e.kv.usage:.4f}\nomni_preemptions_total {e.scheduler.stats['preemptions']}\n").encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(text)))
+                self.end_headers()
+                self.wfile.write(text)
+                return
+            self._json(404, {"error": "not found"})
+
+        def do_POST(self):
+            n = int(self.headers.get("Content-Length", "0"))
+            try:
+                body = json.loads(self.rfile.read(n) or b"{}")
+            except json.JSONDecodeError:
+                return self._json(400, {"error": "invalid JSON"})
+            if self.path in ("/start_profile", "/stop_profile"):
+                aeng.engine.worker.profile(self.path == "/start_profile")
+                return self._json(200, {"status": "ok"})
+            chat = self.path == "/v1/chat/completions"
+            if not chat and self.path != "/v1/completions":
+                return self._json(404, {"error": "not found"})
+            kvp = body.get("kv_transfer_params")
+            # decode instance: reuse the prompt ids produced by the prefill instance
+            if kvp and kvp.get("prompt_token_ids"):
+                ids = list(kvp["prompt_token_ids"])
+            elif chat:
+                ids = tok.encode(tok.tokenizer.apply_chat_template(body.get("messages", []), add_generation_prompt=True)
+                                 if hasattr(tok.tokenizer, "apply_chat_template") else str(body.get("messages")))
+            else:
+                p = body.get("prompt", "")
+                ids = list(p) if isinstance(p, list) and p and isinstance(p[0], int) else tok.encode(p if isinstance(p, str) else str(p))
+            sp = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
+                                temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
+                                top_p=float(body.get("top_p", 1.0) or 1.0), ignore_eos=bool(body.get("ignore_eos", False)))
+            rid = self.headers.get("X-Request-Id") or ("cmpl-" + uuid.uuid4().hex)
+            q = aeng.submit(ids, sp, rid, kvp)
+            stream = bool(body.get("stream", False))
+            created = int(time.time())
+            n_prompt, out_ids, final = len(ids), [], None
+
+            def chunk_obj(text, finish):
+                usage = {"prompt_tokens": n_prompt, "completion_tokens": len(out_ids), "total_tokens": n_prompt + len(out_ids)}
+                choice = ({"index": 0, "delta": {"content": text}, "finish_reason": finish} if chat
+                          else {"index": 0, "text": text, "finish_reason": finish})
+                return {"id": rid, "object": "chat.completion.chunk" if chat else "text_completion", "created": created,
+                        "model": model_name, "choices": [choice], "usage": usage, "prompt_num_token": n_prompt,
+                        "output_num_token": len(out_ids)}
+
+            if stream:
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Connection", "close")
+                self.end_headers()
+            try:
+                while True:
+                    o = q.get(timeout=600)
+                    if o is None:
+                        raise RuntimeError("engine failure")
+                    out_ids += o.new_token_ids
+                    if stream and (o.new_token_ids or o.finished):
+                        self.wfile.write(("data: " + json.dumps(chunk_obj(tok.decode(o.new_token_ids), o.finish_reason if o.finished else None)) + "\n\n").encode())
+                        self.wfile.flush()
+                    if o.finished:
+                        final = o
+                        break
+            except (BrokenPipeError, ConnectionResetError):
+                aeng.abort(rid)
+                return
+            except (queue.Empty, RuntimeError) as e:
+                aeng.abort(rid)
+                if not stream:
+                    return self._json(500, {"error": str(e) or "timeout"})
+                return
+            if stream:
+                self.wfile.write(b"data: [DONE]\n\n")
+                self.wfile.flush()
+                self.close_connection = True
+                return
+            text = tok.decode(out_ids)
+            resp = chunk_obj(text, final.finish_reason)
+            resp["object"] = "chat.completion" if chat else "text_completion"
+            if chat:
+                resp["choices"][0] = {"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": final.finish_reason}
+            if final.kv_transfer_params:
+                resp["kv_transfer_params"] = final.kv_transfer_params
+            self._json(200, resp)
+
+    return Handler
+
+
+def serve(engine_cfg: EngineConfig, host: str = "0.0.0.0", port: int = 8000, tokenizer: Optional[str] = None,
+          model_cfg=None, block: bool = True):
+    engine = EngineCore(engine_cfg, model_cfg=model_cfg)
+    aeng = AsyncEngine(engine)
+    tok = TokenizerPool(tokenizer, vocab_size=engine.model_cfg.vocab_size)
+    srv = ThreadingHTTPServer((host, port), make_handler(aeng, tok, engine.model_cfg.name or engine_cfg.model))
+    srv.daemon_threads = True
+    if block:
+        try:
+            srv.serve_forever()
+        finally:
+            aeng.stop()
+            tok.shutdown()
+        return None
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return srv, aeng
+
+
+def main(argv=None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(description="OpenAI-compatible API server over one engine")
+    ap.add_argument("--model", default="tiny-deepseek-v3")
+    ap.add_argument("--host", default="0.0.0.0")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--tokenizer", default=None)
+    ap.add_argument("--device", default=None)
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-model-len", type=int, default=4096)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--block-size", type=int, default=128)
+    ap.add_argument("--num-kv-blocks", type=int, default=0)
+    ap.add_argument("--num-speculative-tokens", type=int, default=0)
+    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--data-parallel-rank", type=int, default=0)
+    ap.add_argument("--kv-transfer-config", default=None, help="JSON")
+    ap.add_argument("--additional-config", default=None, help="JSON")
+    ap.add_argument("--enforce-eager", action="store_true")
+    a = ap.parse_args(argv)
+    cfg = EngineConfig(model=a.model, device=a.device, max_num_seqs=a.max_num_seqs, max_model_len=a.max_model_len,
+                       max_num_batched_tokens=a.max_num_batched_tokens, block_size=a.block_size, num_kv_blocks=a.num_kv_blocks,
+                       num_speculative_tokens=a.num_speculative_tokens, tp_size=a.tensor_parallel_size,
+                       enforce_eager=a.enforce_eager,
+                       kv_transfer_config=json.loads(a.kv_transfer_config) if a.kv_transfer_config else None)
+    if a.additional_config:
+        from ..adaptors.vllm.platform import ConfigUpdater
+        ConfigUpdater.update_engine_config(cfg, json.loads(a.additional_config))
+    serve(cfg, a.host, a.port, a.tokenizer)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,110 @@
+"""Serving stack on CPU: API server (stream / non-stream, token counters, prefill hand-off fields), tokenizer pool,
+deployment-file transform, launcher liveness handling, CLI dry run."""
+import json
+import sys
+import time
+import urllib.request
+
+import pytest
+import yaml
+
+from omni_infer_b200.cli import main as cli_main
+from omni_infer_b200.cli.config_transform import transform_deployment_config
+from omni_infer_b200.cli.launch import Launcher, dp_rank_env
+from omni_infer_b200.engine.api_server import serve
+from omni_infer_b200.engine.engine_core import EngineConfig
+from omni_infer_b200.engine.tokenizer_pool import TokenizerPool
+
+
+def _post(port, path, body, stream=False):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=30) as r:
+        return r.read().decode()
+
+
+def test_api_server_completions_and_stream():
+    from omni_infer_b200.accelerators.pd import InProcessHub
+    InProcessHub.reset()
+    cfg = EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu",
+                       kv_transfer_config={"kv_role": "kv_producer", "engine_id": "api-p", "endpoint": "inproc://api-p"})
+    srv, aeng = serve(cfg, "127.0.0.1", 0, block=False)
+    port = srv.server_port
+    try:
+        r = json.loads(_post(port, "/v1/completions", {"prompt": "hello world", "max_tokens": 5}))
+        assert r["usage"]["completion_tokens"] == 5 and r["prompt_num_token"] == 11 and r["output_num_token"] == 5
+        text = _post(port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "stream": True})
+        chunks = [json.loads(l[6:]) for l in text.splitlines() if l.startswith("data: {")]
+        assert chunks[-1]["output_num_token"] == 4 and chunks[-1]["usage"]["total_tokens"] == chunks[-1]["prompt_num_token"] + 4
+        assert "[DONE]" in text and chunks[-1]["choices"][0]["finish_reason"] == "length"
+        # prefill leg of a PD request: one token, hand-off parameters in the response
+        r = json.loads(_post(port, "/v1/completions", {"prompt": [1, 2, 3, 4, 5], "max_tokens": 1,
+                                                       "kv_transfer_params": {"do_remote_decode": True}}))
+        kv = r["kv_transfer_params"]
+        assert kv["prompt_token_ids"] == [1, 2, 3, 4, 5] and kv["remote_block_ids"] and kv["prefilled_token"] is not None
+        m = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        assert "omni_requests_total 3" in m
+    finally:
+        srv.shutdown()
+        aeng.stop()
+        InProcessHub.reset()
+
+
+def test_tokenizer_pool_offloads_long_prompts():
+    pool = TokenizerPool(None, vocab_size=300, workers=1, threshold=10, enabled=True)
+    try:
+        assert pool.encode("short") == [ord(c) for c in "short"]
+        long = "x" * 50
+        assert pool.encode(long) == [ord("x")] * 50
+        assert TokenizerPool._parse_cores("0-2,5") == {0, 1, 2, 5}
+    finally:
+        pool.shutdown()
+
+
+DEPLOY = {
+    "deployment": {
+        "prefill": {"group1": [{"ip": "127.0.0.1", "devices": "0,1", "api_port": 9000}, {"ip": "127.0.0.1", "devices": "2,3", "api_port": 9001}]},
+        "decode": {"group1": [{"ip": "127.0.0.1", "ascend_rt_visible_devices": "4,5,6,7", "api_port": 9100}]},
+        "proxy": {"ip": "127.0.0.1", "listen_port": 8080, "prefill_lb_sdk": "prefill_score_balance", "decode_lb_sdk": "weighted_least_active"},
+    },
+    "services": {"model_path": "deepseek-v3", "prefill": {"max_model_len": 32000}, "decode": {"max_model_len": 16384, "num_speculative_tokens": 1,
+                 "additional_config": {"multi_step": 2}}},
+}
+
+
+def test_deployment_transform_and_cli_dry_run(tmp_path, capsys):
+    procs = transform_deployment_config(DEPLOY)
+    assert [p.role for p in procs] == ["prefill", "prefill", "decode", "proxy"]
+    assert procs[0].env["CUDA_VISIBLE_DEVICES"] == "0,1" and procs[2].env["CUDA_VISIBLE_DEVICES"] == "4,5,6,7"
+    assert "--enforce-eager" in procs[0].argv and "--num-speculative-tokens" in procs[2].argv
+    px = procs[3].argv
+    assert px[px.index("--prefill-servers-list") + 1] == "127.0.0.1:9000,127.0.0.1:9001"
+    assert px[px.index("--decode-lb-sdk") + 1] == "weighted_least_active"
+    kv = json.loads(procs[2].argv[procs[2].argv.index("--kv-transfer-config") + 1])
+    assert kv["kv_role"] == "kv_consumer" and kv["transport"] == "tcp"
+    f = tmp_path / "deploy.yml"
+    f.write_text(yaml.safe_dump(DEPLOY))
+    assert cli_main.main(["serve", str(f), "--dry-run"]) == 0
+    assert len(json.loads(capsys.readouterr().out)) == 4
+    assert cli_main.main(["status", "--config", str(f)]) == 1          # nothing is listening
+    env = dp_rank_env(3, 8)
+    assert env["VLLM_DP_RANK"] == "3" and env["WORLD_SIZE"] == "8"
+
+
+def test_launcher_detects_dead_child(tmp_path):
+    from omni_infer_b200.cli.config_transform import ProcessSpec
+    procs = [ProcessSpec("sleeper", "decode", ["-c", "import time; time.sleep(30)"]),
+             ProcessSpec("crasher", "prefill", ["-c", "import sys; sys.exit(3)"])]
+    la = Launcher(procs, str(tmp_path))
+    la.start()
+    try:
+        dead = []
+        for _ in range(100):
+            dead += la.poll()
+            if dead:
+                break
+            time.sleep(0.05)
+        assert dead == ["crasher"] and "sleeper" in la.children
+    finally:
+        la.stop()
+    assert not la.children
