@@ -47,20 +47,26 @@ class GroupCoordinator:
         if self.world_size == 1:
             return x if not async_op else (x, None)
         x = x.contiguous()
-        out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+        out = torch.empty((self.world_size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         work = dist.all_gather_into_tensor(out, x, group=self.group, async_op=async_op)
         if async_op:
             return out, work
         if dim == 0:
-            return out.reshape(self.world_size * x.shape[0], *x.shape[1:])
-        return torch.cat(list(out.unbind(0)), dim=dim)
+            return out
+        return torch.cat(list(out.view(self.world_size, *x.shape).unbind(0)), dim=dim)
 
     def reduce_scatter(self, x: torch.Tensor, async_op: bool = False):
         """Sum over the group, scatter along dim 0 (rows must be divisible by the group size)."""
         if self.world_size == 1:
             return x if not async_op else (x, None)
         x = x.contiguous()
-        out = torch.empty((x.shape[0] // self.world_size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        n = x.shape[0] // self.world_size
+        if not x.is_cuda:       # gloo has no reduce-scatter: all-reduce and keep this rank's rows
+            y = x.clone()
+            dist.all_reduce(y, group=self.group)
+            out = y[self.rank_in_group * n:(self.rank_in_group + 1) * n].contiguous()
+            return (out, None) if async_op else out
+        out = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         work = dist.reduce_scatter_tensor(out, x, group=self.group, async_op=async_op)
         return (out, work) if async_op else out
 

@@ -1,0 +1,155 @@
+"""Multi-process logic on CPU ranks (gloo, world size 2): process groups and collectives, expert parallelism over the
+all-to-all path against a single-rank run, a dynamic placement round with a real expert swap between ranks, and
+host-side failure detection (a peer that never joins a collective ends it with an error, not a hang)."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _spawn(fn, world, *args):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = {}
+    for _ in range(world):
+        r, val = q.get(timeout=180)
+        out[r] = val
+    for p in procs:
+        p.join(timeout=60)
+    for r, v in out.items():
+        if isinstance(v, str) and v.startswith("ERROR"):
+            raise AssertionError(f"rank {r}: {v}")
+    return out
+
+
+def _entry(fn, rank, world, port, q, args):
+    sys.path.insert(0, ROOT)
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NO_GPU_MOCK="1")
+    try:
+        q.put((rank, fn(rank, world, *args)))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "ERROR " + traceback.format_exc()[-1500:]))
+
+
+# ---------------------------------------------------------------------------------------------- collectives
+def _collectives(rank, world):
+    from omni_infer_b200.parallel import destroy_distributed, init_distributed
+    ps = init_distributed(backend="gloo", tp_size=2, dense_mlp_tp_size=2)
+    g = ps.group("tp")
+    x = torch.full((4, 3), float(rank + 1))
+    assert torch.equal(g.all_reduce(x.clone()), torch.full((4, 3), 3.0))
+    ag = g.all_gather(x)
+    assert ag.shape == (8, 3) and ag[0, 0] == 1 and ag[4, 0] == 2
+    rs = g.reduce_scatter(torch.arange(8.).view(4, 2))
+    assert torch.equal(rs, (2 * torch.arange(8.).view(4, 2))[rank * 2:(rank + 1) * 2])
+    a2a = g.all_to_all(torch.arange(4.) + 10 * rank)
+    assert a2a.tolist() == ([0, 1, 10, 11] if rank == 0 else [2, 3, 12, 13])
+    sw = g.swap(torch.tensor([float(rank)]))
+    assert sw.item() == 1 - rank
+    assert ps.dp_size == 1 and ps.tp_rank == rank and ps.ep_size == 2
+    destroy_distributed()
+    return "ok"
+
+
+def test_groups_and_collectives():
+    assert set(_spawn(_collectives, 2).values()) == {"ok"}
+
+
+# ---------------------------------------------------------------------------------------------- EP over all-to-all
+def _ep_engine(rank, world):
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", seed=3))
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (20,), generator=g).tolist() for _ in range(3)]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in prompts]
+    outs = eng.run_until_done()
+    if dist.is_initialized():
+        dist.barrier()
+    return [outs[i] for i in ids]
+
+
+def test_expert_parallel_matches_single_rank():
+    single = _spawn(_ep_engine, 1)[0]
+    two = _spawn(_ep_engine, 2)
+    assert two[0] == single and two[1] == single
+
+
+# ---------------------------------------------------------------------------------------------- placement across ranks
+def _placement_round(rank, world):
+    from omni_infer_b200.accelerators.placement import OmniPlanner
+    from omni_infer_b200.layers.moe import MoELayer
+    from omni_infer_b200.models.config import tiny_deepseek_v3
+    from omni_infer_b200.parallel import destroy_distributed, init_distributed
+    init_distributed(backend="gloo")
+    cfg = tiny_deepseek_v3()
+    pl = OmniPlanner(num_moe_layers=1, num_experts=8, max_redundant_per_rank=1, enable_dynamic=False, _new=True)
+    layer = MoELayer(cfg, 1, dtype=torch.float32, planner=pl)
+    model = torch.nn.ModuleList([layer])
+    with torch.no_grad():
+        for s in range(layer.slots_per_rank):           # slot contents identify the expert they hold
+            e = pl.logical_of_slot(0, s)
+            layer.w13[s].fill_(float(e))
+            layer.w2[s].fill_(float(e))
+    pl.init_dram_weights(model)
+    # expert 0 (on rank 0) is very hot
+    pl.sent_counts[0, 0] = 5000 if rank == 0 else 4000
+    pl.sent_counts[0, 1] = 10
+    pl.sent_counts[0, 5] = 10
+    n = pl.run_round()
+    applied = pl.apply_pending()
+    ins = pl.last_instructions()
+    sel = pl.selector(0).tolist()
+    spare = float(layer.w13[4, 0, 0])                    # the redundant slot of this rank
+    place = pl.mapping.placement()[0].tolist()
+    OmniPlanner.cleanup()
+    destroy_distributed()
+    return {"n": n, "applied": applied, "ins": ins, "sel": sel, "spare": spare, "place": place}
+
+
+def test_dynamic_placement_round_moves_a_hot_expert():
+    out = _spawn(_placement_round, 2)
+    r0, r1 = out[0], out[1]
+    assert r0["place"] == r1["place"]                    # both ranks agree on the new placement
+    assert r0["n"] >= 1 and any(i["type"] == 1 and i["source_expert"] == 0 for i in r0["ins"])   # ADD of expert 0
+    assert r1["place"][9] == 0                           # replica landed in rank 1's redundant slot (position 5+4)
+    assert r1["spare"] == 0.0 and r1["applied"] >= 1     # with expert 0's weights
+    assert r1["sel"][0] == 9 and r0["sel"][0] == 0       # every rank routes expert 0 to its own replica
+
+
+# ---------------------------------------------------------------------------------------------- failure detection
+def _absent_peer(rank, world):
+    import datetime
+    if rank == 1:
+        return "absent"                                   # this rank never joins
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=3))
+        dist.barrier()
+        return "no error"
+    except Exception as e:  # noqa: BLE001
+        return "detected: " + type(e).__name__
+
+
+def test_missing_rank_is_reported_not_hung():
+    out = _spawn(_absent_peer, 2)
+    assert out[1] == "absent" and out[0].startswith("detected")
