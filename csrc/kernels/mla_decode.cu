@@ -14,11 +14,12 @@
 //   S = Q K^T     A = Q  (smem, K-major, 9 chunks of 64 dims)   B = KV tile (smem, K-major)      -> TMEM
 //   P = softmax   written back to TMEM as packed bf16 (A operand of the second MMA)
 //   O += P V      A = P  (TMEM)                                  B = KV tile (same smem, MN-major) -> TMEM
-// KV tiles are 128 tokens (tcgen05.mma reaches its peak rate from N = 128; smaller N is issue-bound at about
-// 46 cycles per instruction).  Five of the nine 64-dim q chunks sit in shared memory, the other four in TMEM
-// (as A operands), which leaves room for one whole KV tile.  Each 64-dim chunk of the tile has its own
-// full/empty barrier pair: the chunks that only the score MMA reads (the other CTA's value dims and the rope
-// dims) are refilled as soon as S is issued, the value chunks after P V.
+// KV tiles are 64 tokens, two of them in flight: the score MMA of tile i+1 runs on the tensor pipe while the
+// softmax warps work on tile i (two S buffers in TMEM), and P V of tile i follows as soon as P is written.
+// Five of the nine 64-dim q chunks sit in shared memory, the other four in TMEM (as A operands), which
+// leaves 144 KB for KV staging.  Each 64-dim chunk of a tile has its own full/empty barrier pair: the chunks
+// that only the score MMA reads (the other CTA's value dims and the rope dims) go through a small ring and
+// are refilled as soon as S is issued, the value chunks sit in one of three stages until P V has run.
 // The running max is only raised when it grows by more than 2^8 (lazy rescale), so the O accumulator is
 // rarely read back.
 //
@@ -46,19 +47,27 @@ struct MlaDecodeParams {
   OmniStatus* status;
 };
 
-constexpr int MLA_TILE = 128;                         // kv tokens per tile (tcgen05.mma runs at peak from N = 128)
-constexpr int MLA_CHUNK_BYTES = MLA_TILE * 128;       // 128 tokens x 64 dims bf16 = 16 KB
-constexpr int MLA_KV_BYTES = 9 * MLA_CHUNK_BYTES;     // 144 KB: one tile, released chunk by chunk
+constexpr int MLA_TILE = 64;                          // kv tokens per tile
+constexpr int MLA_CHUNK_BYTES = MLA_TILE * 128;       // 64 tokens x 64 dims bf16 = 8 KB
+// KV staging, 144 KB: this CTA's four value chunks of a tile are needed until its P V has run, the other five
+// chunks only until the score MMA has read them.  The value chunks cycle through three 32 KB stages, the
+// score-only chunks through a ring of six 8 KB slots, so every load is issued about one tile ahead of its use.
+constexpr int MLA_VSTAGES = 3;
+constexpr int MLA_VSTAGE_BYTES = 4 * MLA_CHUNK_BYTES;
+constexpr int MLA_NSLOTS = 6;
+constexpr int MLA_KV_BYTES = MLA_VSTAGES * MLA_VSTAGE_BYTES + MLA_NSLOTS * MLA_CHUNK_BYTES;
 constexpr int MLA_Q_CHUNK = 128 * 128;                // 128 heads x 64 dims bf16
-constexpr int MLA_QS = 5;                             // q chunks 0..4 live in shared memory,
-// chunks 5..8 (latent dims 320..511 + rope) are kept in TMEM, two written by each softmax group
-constexpr int MLA_SMEM = MLA_QS * MLA_Q_CHUNK + MLA_KV_BYTES + 1536 /*barriers + softmax exchange*/ + 1024 /*align*/;
+constexpr int MLA_QS = 5;   // q chunks in shared memory: this CTA's four value-dim chunks and the rope chunk;
+// the other half's four latent chunks are kept in TMEM (packed bf16), two written by each softmax group
+constexpr int MLA_SMEM =
+    MLA_QS * MLA_Q_CHUNK + MLA_KV_BYTES + 1536 /*barriers + softmax exchange*/ + 1024 /*align*/;
 static_assert(MLA_SMEM <= 232448, "exceeds the 227 KB shared-memory limit of one CTA");
-constexpr int MLA_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two groups of four, 64 score columns each)
-// TMEM columns: O accumulator | S tile (P, packed bf16, overwrites its first half) | four packed-bf16 q chunks
+constexpr int MLA_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two groups of four, 32 score columns each)
+// TMEM columns: O accumulator | two S tiles (P, packed bf16, overwrites half of each group's own S columns) |
+// four packed-bf16 q chunks
 constexpr int TM_O = 0, TM_S = 256, TM_Q = 384, TM_COLS = 512;
 
-enum { MS_Q = 1, MS_KV_EMPTY, MS_KV_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT };
+enum { MS_Q = 1, MS_KV_EMPTY, MS_KV_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT, MS_TMEM };
 
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -76,6 +85,158 @@ __device__ long long g_mla_trace[16];
 #define TRACE_WAIT(slot, expr) (expr)
 #endif
 
+// ---------------------------------------------------------------------------------------------------------
+// Producer and MMA roles.  Both walk the same sequence of KV chunks with a few running counters (no division,
+// no tables), and their loops are kept small: a tcgen05.mma issues in about 50 cycles from a short loop whose
+// descriptors are a uniform base plus a small offset, but far slower from long unrolled code.
+//
+// KV chunk c = latent dims 64c..64c+63 (c < 8) or the rope dims (c = 8).  CTA half h owns the value chunks
+// 4h..4h+3 and accumulates those 256 output dims.  Per tile, in this order:
+//   1. the four latent chunks of the other half (score MMA only; their q chunks sit in TMEM),
+//   2. the rope chunk (score MMA only; q chunk in shared memory slot 4),
+//   3. this half's four value chunks (q chunks in shared memory slots 0..3), which stay in their stage until
+//      P V of the tile has run.
+// Chunks of kinds 1 and 2 go through a ring of MLA_NSLOTS 8 KB slots, kind 3 through MLA_VSTAGES stages.
+// ---------------------------------------------------------------------------------------------------------
+struct MlaPipe {
+  uint32_t sq_addr, kv_addr;
+  uint64_t *kv_full, *kv_empty, *s_full, *p_full, *o_done, *o_final;
+  volatile int* abort_flag;
+  OmniStatus* status;
+};
+struct MlaRing {   // position in the score-only ring / the value stages
+  uint32_t slot = 0, par = 0, vstage = 0, vpar = 0;
+  __device__ __forceinline__ void next_slot() { if (++slot == MLA_NSLOTS) { slot = 0; par ^= 1u; } }
+  __device__ __forceinline__ void next_stage() { if (++vstage == MLA_VSTAGES) { vstage = 0; vpar ^= 1u; } }
+};
+
+template <int HALF>
+__device__ __forceinline__ void mla_producer(const MlaPipe& px, const CUtensorMap* tmap_kv, const int* bt, int block_size,
+                                             int box_rows, int kv_len, int tile_begin, int n) {
+  MlaRing rg;
+#pragma unroll 1
+  for (int i = 0; i < n; ++i) {
+    const int tok0 = (tile_begin + i) * MLA_TILE;
+    // cache rows of this tile's TMA boxes (pages past the end of the sequence repeat the last valid page;
+    // their scores are masked)
+    int rows[MLA_TILE / 32];
+#pragma unroll
+    for (int r = 0; r < MLA_TILE / 32; ++r) {
+      const int tok = tok0 + r * 32;
+      const int pg = min(tok, kv_len - 1) / block_size;
+      rows[r] = bt[pg] * block_size + tok % block_size;
+    }
+#pragma unroll 1
+    for (int oc = 0; oc < 5; ++oc) {
+      const int c = oc < 4 ? (1 - HALF) * 4 + oc : 8;
+      uint64_t* full = &px.kv_full[MLA_VSTAGES + rg.slot];
+      if (!mbar_wait(&px.kv_empty[MLA_VSTAGES + rg.slot], rg.par ^ 1u, px.abort_flag, px.status, MS_KV_EMPTY, c)) return;
+      mbar_expect_tx(full, MLA_CHUNK_BYTES);
+      const uint32_t dst = px.kv_addr + MLA_VSTAGES * MLA_VSTAGE_BYTES + rg.slot * MLA_CHUNK_BYTES;
+      if (box_rows == MLA_TILE) tma_load_2d_addr(dst, tmap_kv, full, c * 64, rows[0]);
+      else {
+#pragma unroll
+        for (int r = 0; r < MLA_TILE / 32; ++r) tma_load_2d_addr(dst + r * 32 * 128, tmap_kv, full, c * 64, rows[r]);
+      }
+      rg.next_slot();
+    }
+    {
+      uint64_t* full = &px.kv_full[rg.vstage];
+      if (!mbar_wait(&px.kv_empty[rg.vstage], rg.vpar ^ 1u, px.abort_flag, px.status, MS_KV_EMPTY, 100 + (int)rg.vstage)) return;
+      mbar_expect_tx(full, MLA_VSTAGE_BYTES);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const uint32_t dst = px.kv_addr + rg.vstage * MLA_VSTAGE_BYTES + v * MLA_CHUNK_BYTES;
+        if (box_rows == MLA_TILE) tma_load_2d_addr(dst, tmap_kv, full, (HALF * 4 + v) * 64, rows[0]);
+        else {
+#pragma unroll
+          for (int r = 0; r < MLA_TILE / 32; ++r)
+            tma_load_2d_addr(dst + r * 32 * 128, tmap_kv, full, (HALF * 4 + v) * 64, rows[r]);
+        }
+      }
+      rg.next_stage();
+    }
+  }
+}
+
+// S = Q K^T of the next tile in the score stream, into S buffer `buf`.  Run by the whole MMA warp; one
+// elected lane issues.
+__device__ __forceinline__ bool mla_issue_scores(const MlaPipe& px, MlaRing& rg, const uint32_t buf) {
+  constexpr uint32_t idesc_qk = umma_idesc(128, MLA_TILE, 1, 1, 0, 0);
+  const uint32_t d_s = TM_S + buf * 64;
+  const uint64_t qdesc0 = umma_desc_kmajor_sw128(px.sq_addr);
+  const uint64_t ring0 = umma_desc_kmajor_sw128(px.kv_addr + MLA_VSTAGES * MLA_VSTAGE_BYTES);
+  const uint64_t vdesc0 = umma_desc_kmajor_sw128(px.kv_addr);
+#pragma unroll 1
+  for (int oc = 0; oc < 5; ++oc) {
+    if (!mbar_wait(&px.kv_full[MLA_VSTAGES + rg.slot], rg.par, px.abort_flag, px.status, MS_KV_FULL, oc)) return false;
+    tc_fence_after();
+    const uint64_t bd = ring0 + (uint64_t)(rg.slot * (MLA_CHUNK_BYTES >> 4));
+    if (elect_one()) {
+      if (oc < 4) {
+        const uint32_t at = TM_Q + oc * 32;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_bf16_ts(d_s, at + 8 * k, bd + 2 * k, idesc_qk, (oc > 0 || k > 0) ? 1u : 0u);
+      } else {
+        const uint64_t ad = qdesc0 + (uint64_t)((4 * MLA_Q_CHUNK) >> 4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_bf16(d_s, ad + 2 * k, bd + 2 * k, idesc_qk, 1u);
+      }
+      umma_commit(&px.kv_empty[MLA_VSTAGES + rg.slot]);   // the slot can be refilled
+    }
+    __syncwarp();
+    rg.next_slot();
+  }
+  if (!mbar_wait(&px.kv_full[rg.vstage], rg.vpar, px.abort_flag, px.status, MS_KV_FULL, 100 + (int)rg.vstage)) return false;
+  tc_fence_after();
+  if (elect_one()) {
+    const uint64_t vd = vdesc0 + (uint64_t)(rg.vstage * (MLA_VSTAGE_BYTES >> 4));
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        umma_bf16(d_s, qdesc0 + (uint64_t)(v * (MLA_Q_CHUNK >> 4) + 2 * k), vd + (uint64_t)(v * (MLA_CHUNK_BYTES >> 4) + 2 * k),
+                  idesc_qk, 1u);
+    }
+    umma_commit(&px.s_full[buf]);
+  }
+  __syncwarp();
+  rg.next_stage();
+  return true;
+}
+
+__device__ __forceinline__ void mla_mma(const MlaPipe& px, int n) {
+  constexpr uint32_t idesc_pv = umma_idesc(128, 256, 1, 1, 0, 1);
+  MlaRing rg;                 // score stream (runs one tile ahead of the P V stream)
+  uint32_t pv_stage = 0;
+  if (!mla_issue_scores(px, rg, 0u)) return;
+  const uint64_t vdesc0 = umma_desc_mnmajor_sw128(px.kv_addr, MLA_CHUNK_BYTES, 1024);
+#pragma unroll 1
+  for (int i = 0; i < n; ++i) {
+    const uint32_t buf = (uint32_t)i & 1u;
+    // the next tile's scores run on the tensor pipe while the softmax warps work on this one
+    if (i + 1 < n && !mla_issue_scores(px, rg, buf ^ 1u)) return;
+    // ---- O += P V
+    if (!mbar_wait(&px.p_full[buf], ((uint32_t)i >> 1) & 1u, px.abort_flag, px.status, MS_P_FULL, i)) return;
+    tc_fence_after();
+    if (elect_one()) {
+      // 16 tokens per MMA: two 8-token groups of 1024 B; dims advance by whole 8 KB chunks.  P of tokens
+      // 0..31 sits in columns 0..15 of the S buffer, P of tokens 32..63 in columns 32..47.
+      const uint64_t vd = vdesc0 + (uint64_t)(pv_stage * (MLA_VSTAGE_BYTES >> 4));
+      const uint32_t pbase = TM_S + buf * 64;
+      umma_bf16_ts(TM_O, pbase, vd, idesc_pv, i > 0 ? 1u : 0u);
+#pragma unroll
+      for (int k = 1; k < MLA_TILE / 16; ++k)
+        umma_bf16_ts(TM_O, pbase + (k >> 1) * 32 + (k & 1) * 8, vd + (uint64_t)(k * 128), idesc_pv, 1u);
+      umma_commit(&px.kv_empty[pv_stage]);
+      umma_commit(px.o_done);
+      if (i == n - 1) umma_commit(px.o_final);
+    }
+    __syncwarp();
+    if (++pv_stage == MLA_VSTAGES) pv_stage = 0;
+  }
+}
+
 __global__ void __launch_bounds__(MLA_THREADS, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                   const MlaDecodeParams p) {
@@ -85,18 +246,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint8_t* skv = smem + MLA_QS * MLA_Q_CHUNK;
   uint64_t* bars = (uint64_t*)(skv + MLA_KV_BYTES);
   uint64_t* q_full = bars;                          // 1
-  uint64_t* kv_full = bars + 1;                     // 9, one per 64-dim chunk
-  uint64_t* kv_empty = kv_full + 9;                 // 9
-  uint64_t* s_full = kv_empty + 9;                  // 1
-  uint64_t* p_full = s_full + 1;                    // 1
-  uint64_t* o_done = p_full + 1;                    // 1
+  uint64_t* kv_full = bars + 1;                     // [3 value stages] then [6 score-only slots]
+  uint64_t* kv_empty = kv_full + 9;                 // same layout
+  uint64_t* s_full = kv_empty + 9;                  // 2, one per S buffer
+  uint64_t* p_full = s_full + 2;                    // 2
+  uint64_t* o_done = p_full + 2;                    // 1
   uint64_t* o_final = o_done + 1;                   // 1: all P V of this CTA retired
   uint64_t* qt_full = o_final + 1;                  // 1: q chunks written to TMEM
   uint32_t* tmem_slot = (uint32_t*)(qt_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* sm_counter = (int*)(tmem_slot + 2);          // softmax group rendezvous (only grows)
-  float* sm_max = (float*)(bars + 64);              // [2 groups][128 rows] row maxima of the current tile
-  float* sm_sum = sm_max;                           // reused for the row sums after the last tile
+  __nv_bfloat16* sm_max = (__nv_bfloat16*)(bars + 64);  // [2 tile parities][2 groups][128 rows] row maxima, 1 KB
+  float* sm_sum = (float*)(bars + 64);                  // [2 groups][128 rows], same 1 KB after the last tile
 
 #ifdef MLA_TRACE
   long long trace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -120,8 +281,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       mbar_init(&kv_full[c], 1);
       mbar_init(&kv_empty[c], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 8);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], 8);
+    }
     mbar_init(o_done, 1);
     mbar_init(o_final, 1);
     mbar_init(qt_full, 8);
@@ -136,96 +299,42 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  // chunks 0..7 = latent dims 64c..64c+63, chunk 8 = rope dims.  This CTA's value chunks are vb..vb+3; they
-  // are consumed last by the score MMA and stay resident until P V, every other chunk is released as soon
-  // as the score MMA has read it.  order[] = processing order of the chunks.
-  const int vb = half * 4;
-  int order[9];
-  {
-    int o = 0;
-    for (int c = 0; c < 9; ++c) if (c < vb || c >= vb + 4) order[o++] = c;
-    for (int c = vb; c < vb + 4; ++c) order[o++] = c;
+  // the whole TMEM (512 columns) is allocated, so the base can only be column 0 of lane 0; keeping it a
+  // literal keeps every TMEM address of the MMA role a compile-time constant
+  constexpr uint32_t tmem_base = 0;
+  if (*tmem_slot != 0u) {
+    if (threadIdx.x == 0) { *abort_flag = 1; report_status(p.status, OMNI_ERR_MBAR_TIMEOUT, MS_TMEM, (int)*tmem_slot); }
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(*tmem_slot, TM_COLS);
+    return;
   }
+
   const int box_rows = min(p.block_size, MLA_TILE);   // tokens per TMA box (one cache page, at most a tile)
 
   if (n > 0) {
     if (warp == 0) {
       if (lane == 0) {
+        const MlaPipe px{smem_u32(sq), smem_u32(skv), kv_full, kv_empty, s_full, p_full, o_done, o_final, abort_flag, p.status};
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_kv);
+        // q chunks in shared memory: this half's four value-dim chunks (slots 0..3) and the rope chunk (slot 4)
         mbar_expect_tx(q_full, MLA_QS * MLA_Q_CHUNK);
-        for (int c = 0; c < MLA_QS; ++c) tma_load_2d(sq + c * MLA_Q_CHUNK, &tmap_q, q_full, c * 64, bq * p.H);
+        for (int c = 0; c < 4; ++c) tma_load_2d(sq + c * MLA_Q_CHUNK, &tmap_q, q_full, (half * 4 + c) * 64, bq * p.H);
+        tma_load_2d(sq + 4 * MLA_Q_CHUNK, &tmap_q, q_full, 512, bq * p.H);
         const int seq = p.q_to_seq ? p.q_to_seq[bq] : bq;
         const int* bt = p.block_table + (size_t)seq * p.bt_ld;
-        bool ok = true;
-        for (int i = 0; i < n && ok; ++i) {
-          const uint32_t ph = i & 1;
-          const int tok0 = (tile_begin + i) * MLA_TILE;
-          for (int oc = 0; oc < 9; ++oc) {
-            const int c = order[oc];
-            if (!TRACE_WAIT(0, mbar_wait(&kv_empty[c], ph ^ 1, abort_flag, p.status, MS_KV_EMPTY, c))) { ok = false; break; }
-            mbar_expect_tx(&kv_full[c], MLA_CHUNK_BYTES);
-            for (int r0 = 0; r0 < MLA_TILE; r0 += box_rows) {
-              const int tok = tok0 + r0;
-              // pages past the end of the sequence repeat the last valid page (their scores are masked)
-              const int pg = min(tok, kv_len - 1) / p.block_size;
-              const int row = bt[pg] * p.block_size + tok % p.block_size;
-              tma_load_2d(skv + c * MLA_CHUNK_BYTES + r0 * 128, &tmap_kv, &kv_full[c], c * 64, row);
-            }
-          }
-        }
+        if (half == 0) mla_producer<0>(px, &tmap_kv, bt, p.block_size, box_rows, kv_len, tile_begin, n);
+        else mla_producer<1>(px, &tmap_kv, bt, p.block_size, box_rows, kv_len, tile_begin, n);
       }
     } else if (warp == 1) {
-      if (lane == 0) {
-        constexpr uint32_t idesc_qk = umma_idesc(128, MLA_TILE, 1, 1, 0, 0);
-        constexpr uint32_t idesc_pv = umma_idesc(128, 256, 1, 1, 0, 1);
-        bool ok = mbar_wait(q_full, 0, abort_flag, p.status, MS_Q, 0);
-        if (ok) ok = mbar_wait(qt_full, 0, abort_flag, p.status, MS_QT, 0);
-        tc_fence_after();
-        const uint32_t kbase = smem_u32(skv);
-        const uint32_t d_s = tmem_base + TM_S;
-        for (int i = 0; i < n && ok; ++i) {
-          const uint32_t ph = i & 1;
-          uint32_t accum = 0;
-          // ---- S = Q K^T, chunk by chunk (q chunk from shared memory or from TMEM)
-          for (int oc = 0; oc < 9 && ok; ++oc) {
-            const int c = order[oc];
-            if (!TRACE_WAIT(oc < 5 ? 1 : 2, mbar_wait(&kv_full[c], ph, abort_flag, p.status, MS_KV_FULL, c))) { ok = false; break; }
-            tc_fence_after();
-            const uint64_t bd = umma_desc_kmajor_sw128(kbase + c * MLA_CHUNK_BYTES);
-            if (c < MLA_QS) {
-              const uint64_t ad = umma_desc_kmajor_sw128(smem_u32(sq) + c * MLA_Q_CHUNK);
-#pragma unroll
-              for (int k = 0; k < 4; ++k) { umma_bf16(d_s, ad + 2 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
-            } else {
-              const uint32_t at = tmem_base + TM_Q + (c - MLA_QS) * 32;
-#pragma unroll
-              for (int k = 0; k < 4; ++k) { umma_bf16_ts(d_s, at + 8 * k, bd + 2 * k, idesc_qk, accum); accum = 1; }
-            }
-            if (oc < 5) umma_commit(&kv_empty[c]);   // not a value chunk of this CTA: free for the next tile
-          }
-          if (!ok) break;
-          umma_commit(s_full);
-          // ---- O += P V
-          if (!TRACE_WAIT(3, mbar_wait(p_full, ph, abort_flag, p.status, MS_P_FULL, i))) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t vbase = kbase + vb * MLA_CHUNK_BYTES;
-#pragma unroll
-          for (int k = 0; k < MLA_TILE / 16; ++k) {
-            // 16 tokens per MMA: two 8-token groups of 1024 B; dims advance by whole 16 KB chunks
-            const uint64_t bd = umma_desc_mnmajor_sw128(vbase + k * 2048, MLA_CHUNK_BYTES, 1024);
-            umma_bf16_ts(tmem_base + TM_O, tmem_base + TM_S + k * 8, bd, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-          }
-          for (int c = vb; c < vb + 4; ++c) umma_commit(&kv_empty[c]);
-          umma_commit(o_done);
-          if (i == n - 1) umma_commit(o_final);
-        }
-      }
+      const MlaPipe px{smem_u32(sq), smem_u32(skv), kv_full, kv_empty, s_full, p_full, o_done, o_final, abort_flag, p.status};
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, MS_Q, 0);
+      if (ok) ok = mbar_wait(qt_full, 0, abort_flag, p.status, MS_QT, 0);
+      tc_fence_after();
+      if (ok) mla_mma(px, n);
     } else {
       // ------------------------------------------------------------ softmax / correction / epilogue
-      // Eight warps: lane quadrant qd = warp & 3 selects 32 heads, group grp selects 64 of the 128 score
+      // Eight warps: lane quadrant qd = warp & 3 selects 32 heads, group grp selects 32 of the 64 score
       // columns (and 128 of the 256 output columns).  The two warps that share a quadrant exchange their
       // row maxima through shared memory once per tile; row sums are only combined at the very end.
       const int qd = warp & 3;
@@ -247,9 +356,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         __syncwarp();
         return true;
       };
-      // this head's q values for the chunks kept in TMEM, as packed bf16 pairs (group g writes two chunks)
+      // this head's q values for the chunks kept in TMEM (the other half's 256 latent dims), as packed bf16
+      // pairs; group g writes two of the four chunks
       {
-        const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + ((size_t)bq * p.H + row) * 576 + MLA_QS * 64);
+        const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + ((size_t)bq * p.H + row) * 576 + (1 - half) * 256);
         const bool row_ok = row < p.H;
 #pragma unroll 1
         for (int c = grp * 2; c < grp * 2 + 2; ++c) {
@@ -267,38 +377,46 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (lane == 0) mbar_arrive(qt_full);
       }
       for (int i = 0; i < n; ++i) {
-        if (!TRACE_WAIT(4, mbar_wait(s_full, i & 1, abort_flag, p.status, MS_S_FULL, i))) { ok = false; break; }
+        const int st = i & 1;
+        if (!TRACE_WAIT(4, mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, MS_S_FULL, i))) { ok = false; break; }
         tc_fence_after();
-        const int valid = kv_len - (tile_begin + i) * MLA_TILE - grp * 64;  // valid columns of this group's half
-        float s[64];
+#ifdef MLA_TRACE
+        const long long t_sm0 = clock64();
+#endif
+        const int valid = kv_len - (tile_begin + i) * MLA_TILE - grp * 32;  // valid columns of this group's half
+        const uint32_t s_addr = lane_addr + TM_S + st * 64 + grp * 32;
+        float s[32];
         {
-          uint32_t sv0[32], sv1[32];
-          tmem_ld_x32(lane_addr + TM_S + grp * 64, sv0);
-          tmem_ld_x32(lane_addr + TM_S + grp * 64 + 32, sv1);
+          uint32_t sv[32];
+          tmem_ld_x32(s_addr, sv);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            s[j] = (j < valid) ? __uint_as_float(sv0[j]) * p.scale_log2 : -INFINITY;
-            s[32 + j] = (32 + j < valid) ? __uint_as_float(sv1[j]) * p.scale_log2 : -INFINITY;
-          }
+          for (int j = 0; j < 32; ++j) s[j] = (j < valid) ? __uint_as_float(sv[j]) * p.scale_log2 : -INFINITY;
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < 64; j += 4) {
+        for (int j = 0; j < 32; j += 4) {
           mx4[0] = fmaxf(mx4[0], s[j]); mx4[1] = fmaxf(mx4[1], s[j + 1]);
           mx4[2] = fmaxf(mx4[2], s[j + 2]); mx4[3] = fmaxf(mx4[3], s[j + 3]);
         }
         const float mx_local = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        float* slab = sm_max;   // safe to reuse every tile: all reads happen before the second rendezvous
-        slab[grp * 128 + row] = mx_local;
-        if (!group_sync()) { ok = false; break; }
-        const float mx = fmaxf(slab[row], slab[128 + row]);
+        // the slab alternates with the tile parity: a warp may already write tile i+1's maxima while its
+        // partner still reads tile i's (one rendezvous per tile separates the writes of tiles i and i+2).
+        // Both warps of a row read both (bf16-rounded) entries, so they agree on the reference exactly; the
+        // reference only has to be near the true maximum, not equal to it.
+        __nv_bfloat16* slab = sm_max + st * 256;
+        slab[grp * 128 + row] = __float2bfloat16_rn(mx_local);
+        if (!TRACE_WAIT(5, group_sync())) { ok = false; break; }
+        const float mx = fmaxf(__bfloat162float(slab[row]), __bfloat162float(slab[128 + row]));
         const float m_new = fmaxf(m, mx);
         const bool grow = (m_new - m) > 8.0f;  // also true on the first tile (m = -inf)
         if (i == 0) {
           m = m_new;
         } else if (__any_sync(0xffffffffu, grow)) {
-          // the score MMA of this tile was issued after P V of the previous one, so O is already final
+#ifdef MLA_TRACE
+          trace[7] += 1;
+#endif
+          // P V of the previous tile must have retired before O is touched; P V of this tile waits for P
           if (!mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, MS_O_DONE, i)) { ok = false; break; }
           tc_fence_after();
           const float f = grow ? exp2f(m - m_new) : 1.0f;
@@ -315,9 +433,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           tmem_st_wait();
         }
         float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[32];
+        uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 16; ++j) {
           float p0, p1;
           const float a0 = s[2 * j] - m, a1 = s[2 * j + 1] - m;
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(a0));
@@ -327,17 +445,20 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           pk[j] = *reinterpret_cast<uint32_t*>(&h2);
         }
         l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-        // P (packed bf16) overwrites the first half of S: every warp must have read its S columns first
-        if (!group_sync()) { ok = false; break; }
-        tmem_st_x32(lane_addr + TM_S + grp * 32, pk);
+        // P (packed bf16) overwrites the first half of this group's own S columns, which only its warps read
+        tmem_st_x16(s_addr, pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full);
+        if (lane == 0) mbar_arrive(&p_full[st]);
+#ifdef MLA_TRACE
+        trace[6] += clock64() - t_sm0;
+#endif
       }
       // o_done flips once per tile and is only sampled when a rescale is needed, so its parity cannot
       // tell "last tile retired" from "two tiles behind"; the single-use o_final barrier can.
       if (ok) ok = mbar_wait(o_final, 0, abort_flag, p.status, MS_O_DONE, n);
+      if (ok) ok = group_sync();   // every warp is past its last read of the maxima slabs
       if (ok) {
         sm_sum[grp * 128 + row] = l;
         ok = group_sync();
@@ -406,7 +527,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     const long long tot = clock64() - t_start;
     if (warp == 0) { g_mla_trace[0] = trace[0]; g_mla_trace[8] = tot; g_mla_trace[9] = n; }
     if (warp == 1) { g_mla_trace[1] = trace[1]; g_mla_trace[2] = trace[2]; g_mla_trace[3] = trace[3]; g_mla_trace[10] = tot; }
-    if (warp == 2) { g_mla_trace[4] = trace[4]; g_mla_trace[11] = tot; }
+    if (warp == 2) { g_mla_trace[4] = trace[4]; g_mla_trace[5] = trace[5]; g_mla_trace[6] = trace[6]; g_mla_trace[7] = trace[7]; g_mla_trace[11] = tot; }
   }
 #endif
   if (*abort_flag) {
@@ -466,7 +587,7 @@ extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, l
                                float* lse_part, void* status, cudaStream_t stream) {
   if (Bq <= 0) return 0;
   if (H < 1 || H > 128) return -1;
-  if (block_size != 32 && block_size != 64 && block_size % 128 != 0) return -2;
+  if (block_size != 32 && block_size % 64 != 0) return -2;
   if (num_splits < 1) return -3;
   if (num_splits > 1 && (o_part == nullptr || lse_part == nullptr)) return -4;
   CUtensorMap tq, tkv;
