@@ -86,34 +86,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #define OMNI_WAIT_LIMIT_NS 2000000000ull
 #endif
 
-// Bounded wait.  Returns true when the phase completed, false when the CTA is aborting
-// (either this wait ran out, or another role raised `*abort_flag`).
-// The slow path is kept out of line: waits are inlined dozens of times and the code of a warp-specialised
-// kernel should stay small enough for the instruction cache.
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, OmniStatus* st,
-                                            int site, int detail) {
+// Bounded wait.  Returns true when the phase completed, false when the CTA is aborting (either this wait ran
+// out, or another role raised `*abort_flag`).  Waits are inlined dozens of times in warp-specialised kernels
+// whose code should stay small, so the path that runs out only records where it gave up in the abort word;
+// the kernel's teardown turns that into the status record (report_abort).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          OmniStatus* /*st*/, int site, int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    ++spins;
-    if ((spins & 0x3f) == 0) {
+  while (!mbar_try_wait(bar, parity)) {
+    if (((++spins) & 0x3f) == 0) {
       if (*abort_flag) return false;
-      uint64_t now = globaltimer_ns();
+      const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > OMNI_WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        report_status(st, OMNI_ERR_MBAR_TIMEOUT, site, detail);
+        *abort_flag = 0x40000000 | ((site & 0xff) << 16) | (detail & 0xffff);
         return false;
       }
     }
   }
+  return true;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          OmniStatus* st, int site, int detail) {
-  if (mbar_try_wait(bar, parity)) return true;
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag, st, site, detail);
+// Called by one thread in the teardown of a kernel whose abort word is set.
+__device__ __forceinline__ void report_abort(volatile int* abort_flag, OmniStatus* st) {
+  const int v = *abort_flag;
+  if (v & 0x40000000) report_status(st, OMNI_ERR_MBAR_TIMEOUT, (v >> 16) & 0xff, v & 0xffff);
 }
 
 // Wait on a global-memory flag written by another GPU / CTA (acquire at system scope).

@@ -265,6 +265,7 @@ fmha_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
 
   if (*abort_flag) {
+    if (threadIdx.x == 0) report_abort(abort_flag, p.status);
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }

@@ -55,6 +55,8 @@ struct GemmParams {
   const float* row_scale;  // optional [rows]
   int x_group_col;       // head-batched mode: group g reads X columns [g*x_group_col, +K) ...
   int out_group_col;     // ... and writes out columns [g*out_group_col, +n_out)
+  int k_splits;          // > 1: the K range is cut into k_splits parts that different CTAs accumulate into a
+  int kb_per_split;      //      zero-initialised fp32 output with atomic adds (EPI 0 only); K blocks per part
   OmniStatus* status;
 };
 
@@ -76,7 +78,7 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
 };
 
-enum { SITE_PROD_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_TMEM_EMPTY = 3, SITE_EPI_TMEM_FULL = 4 };
+enum { SITE_PROD_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_TMEM_EMPTY = 3, SITE_EPI_TMEM_FULL = 4, SITE_TMEM_BASE = 5 };
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -95,6 +97,15 @@ __device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {
       : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
 }
 
+#ifdef GEMM_TRACE
+__device__ long long g_gemm_trace[16];
+#define GT_BEGIN long long _gt0 = clock64()
+#define GT_END(slot) gtrace[slot] += clock64() - _gt0
+#else
+#define GT_BEGIN
+#define GT_END(slot)
+#endif
+
 template <int KIND, int BN, int NACC, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -104,10 +115,11 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   constexpr int BK_ELEMS = (KIND == 0) ? 64 : 128;       // one 128-byte swizzle span
   constexpr int ACC_COLS = NACC * BN;                    // TMEM columns of one accumulator buffer
   constexpr int CW = BN / 2;                             // token columns owned by one epilogue group
-  constexpr int TMEM_COLS_RAW = 2 * ACC_COLS;
-  constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128
-                            : TMEM_COLS_RAW <= 256 ? 256 : 512;
-  static_assert(TMEM_COLS_RAW <= 512, "accumulators exceed TMEM");
+  // One CTA per SM, so it takes the whole TMEM: the allocation then starts at column 0 and every TMEM address
+  // is a compile-time constant.  (tcgen05.mma issues several times slower when its operands have to be moved
+  // over from ordinary registers, as a base address loaded from shared memory would be.)
+  constexpr int TMEM_COLS = 512;
+  static_assert(2 * ACC_COLS <= 512, "accumulators exceed TMEM");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "invalid token tile");
 
   extern __shared__ uint8_t smem_raw[];
@@ -125,6 +137,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   float* sc_ring = amax_x + 256;                         // [STAGES][BN], 16-byte aligned (bulk copies, float4 reads)
   static_assert((1024 + L::PREFIX_BYTES + 1024) % 16 == 0, "scale ring must be 16-byte aligned");
 
+#ifdef GEMM_TRACE
+  long long gtrace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long gt_start = clock64();
+#endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK_ELEMS - 1) / BK_ELEMS;
@@ -133,7 +149,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], (KIND == 1) ? 9 : 1);     // MMA commit (+ 8 epilogue warps that read the scale ring)
+      // bf16: released by the MMA commit.  fp8: released by the 8 epilogue warps once they have read the stage's
+      // scale-ring slot, which they only do after the stage's MMAs have retired (they waited for tfull).
+      mbar_init(&empty_bar[s], (KIND == 1) ? 8 : 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
@@ -164,7 +182,13 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   tc_fence_after();
 
-  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t tmem_base = 0;
+  if (*tmem_slot != 0u) {   // cannot happen while the whole TMEM is requested; never compute on a wrong base
+    if (threadIdx.x == 0) { *abort_flag = 1; report_status(p.status, OMNI_ERR_MBAR_TIMEOUT, SITE_TMEM_BASE, (int)*tmem_slot); }
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(*tmem_slot, TMEM_COLS);
+    return;
+  }
   const int total_tiles = tile_prefix[p.G];
 
   // tile index -> (group, m_tile, n_tile, first row, rows valid)
@@ -190,18 +214,20 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (lane == 0) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
-      int it = 0;
+      uint32_t s = 0, sph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int vt = blockIdx.x; vt < total_tiles * p.k_splits && ok; vt += gridDim.x) {
+        const int tile = vt / p.k_splits;
+        const int kb0 = (vt - tile * p.k_splits) * p.kb_per_split;
+        const int kb1 = min(num_kb, kb0 + p.kb_per_split);
         int g, mt, row0, rows;
         decode_tile(tile, g, mt, row0, rows);
         const int wrow = g * p.w_rows_per_group + mt * 128;
         // activation scales of this tile's rows: [kb][row0 .. row0+BN), clipped to the allocation
         const int sc_n = (KIND == 1) ? max(0, min(BN, p.x_scale_ld - row0)) : 0;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, SITE_PROD_EMPTY, s)) { ok = false; break; }
+#pragma unroll 1
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[s], sph ^ 1u, abort_flag, p.status, SITE_PROD_EMPTY, (int)s)) { ok = false; break; }
           uint8_t* st = smem + s * L::STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], L::STAGE_BYTES + sc_n * 4);
           tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * BK_ELEMS, wrow, pol_w);
@@ -210,17 +236,24 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           tma_load_2d_hint(st + NACC * L::A_BYTES, &tmap_x, &full_bar[s], kb * BK_ELEMS + g * p.x_group_col, row0, pol_x);
           if (KIND == 1 && sc_n > 0)
             bulk_load_1d(sc_ring + s * BN, p.x_scale + (size_t)kb * p.x_scale_ld + row0, sc_n * 4, &full_bar[s]);
+          if (++s == STAGES) { s = 0; sph ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the (small) loop and waits on the barriers; one elected lane issues.  That keeps the
+    // warp convergent, which measurably shortens the issue path of tcgen05.mma.
+    {
       constexpr uint32_t idesc = (KIND == 0) ? umma_idesc(128, BN, 1, 1) : umma_idesc(128, BN, 0, 0);
-      int it = 0;       // smem stage counter
-      int acc_it = 0;   // accumulator buffer counter
+      uint32_t s = 0, sph = 0;   // smem stage and its phase
+      int acc_it = 0;            // accumulator buffer counter
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const uint32_t smem_base = smem_u32(smem);
+      for (int vt = blockIdx.x; vt < total_tiles * p.k_splits && ok; vt += gridDim.x) {
+        const int tile = vt / p.k_splits;
+        const int kb0 = (vt - tile * p.k_splits) * p.kb_per_split;
+        const int kb1 = min(num_kb, kb0 + p.kb_per_split);
         if (KIND == 0) {
           const int buf = acc_it & 1;
           if (!mbar_wait(&tempty_bar[buf], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.status, SITE_MMA_TMEM_EMPTY, buf)) {
@@ -228,41 +261,49 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
           tc_fence_after();
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          int buf = acc_it & 1;
+#pragma unroll 1
+        for (int kb = kb0; kb < kb1; ++kb) {
+          const int buf = acc_it & 1;
           if (KIND == 1) {
+            GT_BEGIN;
             if (!mbar_wait(&tempty_bar[buf], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.status, SITE_MMA_TMEM_EMPTY, buf)) {
               ok = false; break;
             }
+            GT_END(0);
           }
-          const int s = it % STAGES;
-          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag, p.status, SITE_MMA_FULL, s)) { ok = false; break; }
+          {
+            GT_BEGIN;
+            if (!mbar_wait(&full_bar[s], sph, abort_flag, p.status, SITE_MMA_FULL, (int)s)) { ok = false; break; }
+            GT_END(1);
+          }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-          const uint64_t adesc = umma_desc_kmajor_sw128(sa);
-          const uint64_t bdesc = umma_desc_kmajor_sw128(sa + NACC * L::A_BYTES);
-          const uint32_t d0 = tmem_base + buf * ACC_COLS;
+          if (elect_one()) {
+            const uint32_t sa = smem_base + s * L::STAGE_BYTES;
+            const uint64_t adesc = umma_desc_kmajor_sw128(sa);
+            const uint64_t adesc2 = umma_desc_kmajor_sw128(sa + L::A_BYTES);
+            const uint64_t bdesc = umma_desc_kmajor_sw128(sa + NACC * L::A_BYTES);
+            const uint32_t d0 = tmem_base + buf * ACC_COLS;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t accum = (KIND == 0) ? ((kb | k) != 0) : (k != 0);
-            if (KIND == 0) {
-              umma_bf16(d0, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
-              if (NACC == 2)
-                umma_bf16(d0 + BN, umma_desc_kmajor_sw128(sa + L::A_BYTES) + 2 * k, bdesc + 2 * k, idesc, accum);
-            } else {
-              umma_fp8(d0, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
-              if (NACC == 2)
-                umma_fp8(d0 + BN, umma_desc_kmajor_sw128(sa + L::A_BYTES) + 2 * k, bdesc + 2 * k, idesc, accum);
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t accum = (KIND == 0) ? (kb != kb0 || k != 0) : (k != 0);
+              if (KIND == 0) {
+                umma_bf16(d0, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+                if (NACC == 2) umma_bf16(d0 + BN, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
+              } else {
+                umma_fp8(d0, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+                if (NACC == 2) umma_fp8(d0 + BN, adesc2 + 2 * k, bdesc + 2 * k, idesc, accum);
+              }
             }
+            if (KIND == 0) umma_commit(&empty_bar[s]);  // operands consumed once these MMAs retire
+            else umma_commit(&tfull_bar[buf]);
           }
-          umma_commit(&empty_bar[s]);  // operands consumed once these MMAs retire
-          if (KIND == 1) {
-            umma_commit(&tfull_bar[buf]);
-            ++acc_it;
-          }
+          __syncwarp();
+          if (KIND == 1) ++acc_it;
+          if (++s == STAGES) { s = 0; sph ^= 1u; }
         }
         if (KIND == 0 && ok) {
-          umma_commit(&tfull_bar[acc_it & 1]);
+          if (elect_one()) umma_commit(&tfull_bar[acc_it & 1]);
+          __syncwarp();
           ++acc_it;
         }
       }
@@ -275,10 +316,13 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int c_lo = grp * CW;              // first token column of this group
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     int acc_it = 0;
-    int it = 0;
+    uint32_t s = 0;                         // smem stage whose scale-ring slot belongs to the current K block
     int epi_sync = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    for (int vt = blockIdx.x; vt < total_tiles * p.k_splits && ok; vt += gridDim.x) {
+        const int tile = vt / p.k_splits;
+        const int kb0 = (vt - tile * p.k_splits) * p.kb_per_split;
+        const int kb1 = min(num_kb, kb0 + p.kb_per_split);
       int g, mt, row0, rows;
       decode_tile(tile, g, mt, row0, rows);
       const int n_in = mt * 128 + r;
@@ -292,13 +336,20 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const int sb_per_group = p.w_rows_per_group / 128;
         const float* wsc0 = p.w_scale + ((size_t)g * sb_per_group + mt) * num_kb;
         const float* wsc1 = p.w_scale + ((size_t)g * sb_per_group + mt + p.n_out / 128) * num_kb;
-        for (int kb = 0; kb < num_kb; ++kb, ++acc_it, ++it) {
+#pragma unroll 1
+        for (int kb = kb0; kb < kb1; ++kb, ++acc_it) {
           const int buf = acc_it & 1;
-          const int s = it % STAGES;
-          if (!mbar_wait(&tfull_bar[buf], (acc_it >> 1) & 1, abort_flag, p.status, SITE_EPI_TMEM_FULL, buf)) {
-            ok = false; break;
+          {
+            GT_BEGIN;
+            if (!mbar_wait(&tfull_bar[buf], (acc_it >> 1) & 1, abort_flag, p.status, SITE_EPI_TMEM_FULL, buf)) {
+              ok = false; break;
+            }
+            GT_END(2);
           }
           tc_fence_after();
+#ifdef GEMM_TRACE
+          const long long gt_busy0 = clock64();
+#endif
           // pull this group's columns of the fresh partial product out of TMEM in one round trip
           uint32_t t[NACC][CW];
 #pragma unroll
@@ -317,23 +368,66 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tempty_bar[buf]);   // the MMA may overwrite this buffer now
+          // acc += t * (x_scale * w_scale), sixteen columns at a time.  The scale reads of the next chunk are
+          // issued before the arithmetic of this one and the products are formed in a batch, so that neither the
+          // shared-memory latency nor the multiply -> fma dependency sits between consecutive instructions.
           const float4* sc4 = reinterpret_cast<const float4*>(sc_ring + s * BN + c_lo);
           const float2 w0 = make_float2(sw0, sw0), w1 = make_float2(sw1, sw1);
+          constexpr int NCH = CW / 16;
+          float4 sxc[4];
 #pragma unroll
-          for (int j4 = 0; j4 < CW / 4; ++j4) {
-            const float4 sx = sc4[j4];
-            const float2 sxa = make_float2(sx.x, sx.y), sxb = make_float2(sx.z, sx.w);
+#ifdef GEMM_X_NOLDS
+          for (int q4 = 0; q4 < 4; ++q4) sxc[q4] = make_float4(sw0, sw1, sw0, sw1);
+#else
+          for (int q4 = 0; q4 < 4; ++q4) sxc[q4] = sc4[q4];
+#endif
 #pragma unroll
-            for (int a = 0; a < NACC; ++a) {
-              const float2 wa = (a == 0) ? w0 : w1;
-              fma2(acc[a * CW / 2 + 2 * j4], make_float2(__uint_as_float(t[a][4 * j4]), __uint_as_float(t[a][4 * j4 + 1])),
-                   mul2(sxa, wa));
-              fma2(acc[a * CW / 2 + 2 * j4 + 1],
-                   make_float2(__uint_as_float(t[a][4 * j4 + 2]), __uint_as_float(t[a][4 * j4 + 3])), mul2(sxb, wa));
+          for (int c = 0; c < NCH; ++c) {
+            float4 nxt[4];
+            if (c + 1 < NCH) {
+#pragma unroll
+#ifdef GEMM_X_NOLDS
+              for (int q4 = 0; q4 < 4; ++q4) nxt[q4] = sxc[q4];
+#else
+              for (int q4 = 0; q4 < 4; ++q4) nxt[q4] = sc4[(c + 1) * 4 + q4];
+#endif
+            }
+            float2 pr[NACC][8];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+              for (int a = 0; a < NACC; ++a) {
+                const float2 wa = (a == 0) ? w0 : w1;
+#ifdef GEMM_X_NOMUL
+                pr[a][2 * q4] = make_float2(sxc[q4].x, sxc[q4].y);
+                pr[a][2 * q4 + 1] = make_float2(sxc[q4].z, sxc[q4].w);
+                (void)wa;
+#else
+                pr[a][2 * q4] = mul2(make_float2(sxc[q4].x, sxc[q4].y), wa);
+                pr[a][2 * q4 + 1] = mul2(make_float2(sxc[q4].z, sxc[q4].w), wa);
+#endif
+              }
+            }
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+#pragma unroll
+              for (int a = 0; a < NACC; ++a) {
+                const int col = c * 16 + 2 * h;
+                fma2(acc[a * CW / 2 + col / 2], make_float2(__uint_as_float(t[a][col]), __uint_as_float(t[a][col + 1])), pr[a][h]);
+              }
+            }
+            if (c + 1 < NCH) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) sxc[q4] = nxt[q4];
             }
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty_bar[s]);      // scale ring slot read
+#ifdef GEMM_TRACE
+          gtrace[3] += clock64() - gt_busy0;
+          gtrace[5] += 1;
+#endif
+          if (++s == STAGES) s = 0;
         }
         if (!ok) break;
       } else {
@@ -371,7 +465,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 const size_t row = (size_t)(row0 + c_lo + c0 + j);
                 float y = vals[j];
                 if (p.row_scale) y *= __ldg(p.row_scale + row);
-                if (p.out_f32) ((float*)p.out)[row * p.out_ld + n] = y;
+                if (p.k_splits > 1) atomicAdd((float*)p.out + row * p.out_ld + n, y);
+                else if (p.out_f32) ((float*)p.out)[row * p.out_ld + n] = y;
                 else ((__nv_bfloat16*)p.out)[row * p.out_ld + n] = __float2bfloat16(y);
               }
             }
@@ -453,8 +548,16 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     }
   }
 
+#ifdef GEMM_TRACE
+  if (blockIdx.x == 0 && lane == 0 && warp >= 1 && warp <= 2) {
+    const long long tot = clock64() - gt_start;
+    if (warp == 1) { g_gemm_trace[0] = gtrace[0]; g_gemm_trace[1] = gtrace[1]; g_gemm_trace[8] = tot; }
+    if (warp == 2) { g_gemm_trace[2] = gtrace[2]; g_gemm_trace[3] = gtrace[3]; g_gemm_trace[5] = gtrace[5]; g_gemm_trace[9] = tot; }
+  }
+#endif
   // ------------------------------------------------------------------ teardown
   if (*abort_flag) {
+    if (threadIdx.x == 0) report_abort(abort_flag, p.status);
     // give copies that are still in flight time to land before the CTA's memory is released
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -488,6 +591,12 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
 
 using namespace omni;
 
+#ifdef GEMM_TRACE
+extern "C" int omni_gemm_trace_read(long long* out16) {
+  return (int)cudaMemcpyFromSymbol(out16, g_gemm_trace, sizeof(long long) * 16);
+}
+#endif
+
 // kind: 0 bf16, 1 fp8 block-scaled.  epi: 0 store, 1 swiglu->bf16, 2 swiglu->fp8+scales.
 // bn: token tile (16, 32, 64, 128, 256); 0 picks from `t_hint` (expected rows per group).
 // x_rows: number of addressable rows of X (and of `out`); rows beyond it read as zero.
@@ -512,7 +621,29 @@ extern "C" int omni_gemm(int kind, int epi, const void* w, const void* x, void* 
     if (bn > cap) bn = cap;
   }
   if (bn == 16) bn = 32;   // smallest instantiated token tile
+  // Few output tiles and a long K (the router): cut K so that the whole GPU works on it.  Needs an fp32
+  // output that this call may zero first (dense rows, no per-row multiplier).
+  int k_splits = 1;
+  const int num_kb_h = (K + ((kind == 0) ? 64 : 128) - 1) / ((kind == 0) ? 64 : 128);
+  if (epi == 0 && out_f32 && G == 1 && seg_len == nullptr && row_scale == nullptr && out_group_col == 0 && out_ld == n_out) {
+    if (bn > 128) bn = 128;
+    const int tiles = ((n_out + 127) / 128) * ((T + bn - 1) / bn);
+    const int sms = sm_count();
+    if (tiles * 2 <= sms && num_kb_h >= 8) {
+      k_splits = sms / tiles;
+      if (k_splits > num_kb_h / 4) k_splits = num_kb_h / 4;
+      if (k_splits > 32) k_splits = 32;
+      if (k_splits < 1) k_splits = 1;
+    }
+  }
   GemmParams p;
+  p.kb_per_split = (num_kb_h + k_splits - 1) / k_splits;
+  k_splits = (num_kb_h + p.kb_per_split - 1) / p.kb_per_split;   // no empty parts
+  p.k_splits = k_splits;
+  if (k_splits > 1) {
+    cudaError_t e = cudaMemsetAsync(out, 0, (size_t)T * out_ld * sizeof(float), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
   p.G = G; p.n_out = n_out; p.K = K; p.T = T; p.seg_start = seg_start; p.seg_len = seg_len;
   p.w_rows_per_group = n_out * nacc; p.w_scale = w_scale; p.x_scale = x_scale; p.x_scale_ld = x_scale_ld;
   p.out = out; p.out_ld = out_ld; p.out_f32 = out_f32; p.out_scale = out_scale; p.out_scale_ld = out_scale_ld;

@@ -531,6 +531,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   }
 #endif
   if (*abort_flag) {
+    if (threadIdx.x == 0) report_abort(abort_flag, p.status);
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
