@@ -15,7 +15,9 @@
 //               accumulator lanes, scaling, activation, stores
 //
 // Variants (template parameters):
-//   KIND  0 = bf16 operands (accumulate the whole K range in TMEM)
+//   KIND  0 = bf16 operands (accumulate the whole K range in TMEM).  This is the kernel's main use: the fp8
+//             GEMMs of the models run on the token-major kernel in gemm_tokmajor_sm100.cu, which promotes
+//             with one multiplier per thread; the fp8 kind here is kept as the alternative orientation.
 //         1 = e4m3 operands with DeepSeek-style block scales: W scale per 128x128 block, X scale
 //             per (row, 128-wide K block).  Every 128-wide K block is multiplied into a fresh
 //             TMEM buffer (two buffers ping-pong) and promoted into fp32 registers with
@@ -376,21 +378,13 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           constexpr int NCH = CW / 16;
           float4 sxc[4];
 #pragma unroll
-#ifdef GEMM_X_NOLDS
-          for (int q4 = 0; q4 < 4; ++q4) sxc[q4] = make_float4(sw0, sw1, sw0, sw1);
-#else
           for (int q4 = 0; q4 < 4; ++q4) sxc[q4] = sc4[q4];
-#endif
 #pragma unroll
           for (int c = 0; c < NCH; ++c) {
             float4 nxt[4];
             if (c + 1 < NCH) {
 #pragma unroll
-#ifdef GEMM_X_NOLDS
-              for (int q4 = 0; q4 < 4; ++q4) nxt[q4] = sxc[q4];
-#else
               for (int q4 = 0; q4 < 4; ++q4) nxt[q4] = sc4[(c + 1) * 4 + q4];
-#endif
             }
             float2 pr[NACC][8];
 #pragma unroll
@@ -398,14 +392,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
               for (int a = 0; a < NACC; ++a) {
                 const float2 wa = (a == 0) ? w0 : w1;
-#ifdef GEMM_X_NOMUL
-                pr[a][2 * q4] = make_float2(sxc[q4].x, sxc[q4].y);
-                pr[a][2 * q4 + 1] = make_float2(sxc[q4].z, sxc[q4].w);
-                (void)wa;
-#else
                 pr[a][2 * q4] = mul2(make_float2(sxc[q4].x, sxc[q4].y), wa);
                 pr[a][2 * q4 + 1] = mul2(make_float2(sxc[q4].z, sxc[q4].w), wa);
-#endif
               }
             }
 #pragma unroll

@@ -92,6 +92,12 @@ def gemm_ref(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, 
     return y.to(out_dtype)
 
 
+def _fp8_impl():
+    """Which fp8 kernel ``gemm`` uses: "tokmajor" (default) or "swapab" (weights on the UMMA M dimension)."""
+    import os
+    return os.environ.get("OMNI_FP8_GEMM", "tokmajor")
+
+
 def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi="store",
          row_scale=None, out_dtype=None, out=None, out_scale=None, bn=0, t_hint=0):
     """``out[t] = epi(x[t] @ w[g(t)].T)``.
@@ -128,6 +134,18 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
         if out is None:
             out = torch.empty(T, n_out, dtype=out_dtype if e == 0 else torch.bfloat16, device=x.device)
         out_f32 = 1 if out.dtype == torch.float32 else 0
+    if kind == 1 and _fp8_impl() == "tokmajor" and n_out % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+        # tokens on the UMMA M dimension: one scale multiplier per thread and K block, vector stores
+        rc = L.omni_gemm_tm(
+            nat.c_int(e), nat.ptr(w), nat.ptr(x), nat.ptr(out), nat.c_int(G), nat.c_int(n_out), nat.c_int(K),
+            nat.c_int(T), nat.c_int(T), nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(w_scale), nat.ptr(x_scale),
+            nat.c_int(x_scale.shape[1]), nat.c_int(out.stride(0)), nat.c_int(out_f32), nat.ptr(out_scale),
+            nat.c_int(out_scale.shape[1] if out_scale is not None else 0), nat.ptr(row_scale),
+            nat.c_int(x.stride(0)), nat.ptr(nat.status_buffer(x.device)), nat.stream())
+        nat.check_rc(rc, "omni_gemm_tm")
+        if e == 2:
+            return out, out_scale
+        return out
     rc = L.omni_gemm(
         nat.c_int(kind), nat.c_int(e), nat.ptr(w), nat.ptr(x), nat.ptr(out), nat.c_int(G), nat.c_int(n_out),
         nat.c_int(K), nat.c_int(T), nat.c_int(T), nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(w_scale),
