@@ -57,7 +57,7 @@ def report(name, us, bytes_, flops, extra=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["mla_decode", "gemm", "grouped", "fmha"])
+    ap.add_argument("what", choices=["mla_decode", "gemm", "grouped", "fmha", "bmm"])
     ap.add_argument("--bq", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=128)
@@ -118,6 +118,15 @@ def main():
             wbytes = E * nw * a.k * 2
         us = timeit(fn, a.iters)
         report(f"grouped_{a.kind}_{a.epi}", us, wbytes, 2.0 * E * tpe * nw * a.k, {"E": E, "tokens_per_expert": tpe, "N": a.n, "K": a.k})
+    elif a.what == "bmm":
+        # per-head GEMM of the absorbed MLA projections: q_nope [T, H, 192 (128 used)] @ W_UK[h] -> [T, H, 576 (512 used)]
+        H = a.heads
+        q = (torch.randn(a.t, H, 192, device=dev) * 0.5).bfloat16()
+        w = (torch.randn(H, a.n, a.k, device=dev) * 0.05).bfloat16()
+        out = torch.empty(a.t, H, 576, dtype=torch.bfloat16, device=dev)
+        us = timeit(lambda: ops.bmm_heads(q[:, :, :a.k], w, out=out), a.iters)
+        report("bmm_heads_bf16", us, (a.t * H * a.k + H * a.n * a.k + a.t * H * a.n) * 2, 2.0 * a.t * H * a.n * a.k,
+               {"T": a.t, "H": H, "N": a.n, "K": a.k})
     elif a.what == "fmha":
         H, L = 16, a.ctx
         q = (torch.randn(L, H, 192, device=dev) * 0.5).bfloat16()

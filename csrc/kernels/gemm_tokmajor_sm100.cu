@@ -28,6 +28,21 @@
 // matching up rows, and the tile produces 128 output features: EPI 1 -> bf16, EPI 2 -> e4m3 with one scale
 // per token and 128 output features (exactly one tile).
 //
+// KIND 0 = bf16 operands: the whole K range accumulates in TMEM and the epilogue runs once per tile.
+// KIND 1 = e4m3 operands with block scales, promoted per K block as described above.
+//
+// Fused collectives (tensor-parallel attention), both over peer memory mapped into this process:
+//   * reduce-scatter epilogue: this rank's GEMM result is a partial sum; token row t belongs to rank
+//     t / rows_per_rank, and the epilogue writes each row straight into that rank's receive slab
+//     [source rank][local row][n_out] with 16-byte peer stores, tile by tile while later tiles still compute.
+//     The last CTA publishes one flag per destination (release at system scope); tp_fused.cu sums the slabs.
+//   * all-gather prologue: X is a gather buffer that every rank fills with its own row block; the producer
+//     waits (bounded) for the flag of the source rank of a tile's rows before it issues the tile's first TMA
+//     load, and takes this rank's own rows first, so the GEMM starts before the remote rows have arrived.
+// Stands where the reference runs o_proj then reduce_scatter, and all_gather then the q_a / MLP input
+// projections (omni/models/common/layers/attention/deepseek_mla.py:437-470,
+// omni/models/common/layers/linear.py:139-199).
+//
 // Stands where the reference calls npu_quant_matmul / npu_grouped_matmul / npu_dequant_swiglu_quant
 // (omni/models/common/layers/moe/fused_moe/fused_moe.py:541-575,
 //  omni/quantization/compressed_tensors/compressed_tensors_moe.py:221-253).
@@ -53,6 +68,19 @@ struct TmGemmParams {
   float* out_scale;      // EPI 2: [n_out/128, out_scale_ld]
   int out_scale_ld;
   const float* row_scale;  // optional [rows]
+  int x_group_col;       // head-batched mode: group g reads X columns [g*x_group_col, +K) ...
+  int out_group_col;     // ... and writes out columns [g*out_group_col, +n_out)
+  // reduce-scatter epilogue (rs_world > 1): out is ignored, rows go to rs_out[row / rs_rows_per_rank]
+  int rs_world, rs_rank, rs_rows_per_rank;
+  void* rs_out[8];       // per destination rank: slab base [world][rows_per_rank][out_ld] (bf16)
+  int* rs_flag[8];       // per destination rank: flag word of this source rank
+  int* rs_done;          // local: CTAs finished (reset by the last one)
+  int* rs_epoch;         // local: round counter, advanced by the last CTA and published to the destinations
+  // all-gather prologue (ag_world > 1): rows [s*ag_rows_per_rank, +ag_rows_per_rank) of X arrive from rank s
+  int ag_world, ag_rank, ag_rows_per_rank;
+  const int* ag_flag;    // local: [world] round of the last block received from each rank
+  const int* ag_epoch;   // local: current round (advanced by the push kernel that precedes this launch)
+  unsigned long long ag_wait_ns;
   OmniStatus* status;
 };
 
@@ -80,7 +108,8 @@ struct TmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
 };
 
-enum { TMS_PROD_EMPTY = 21, TMS_MMA_FULL = 22, TMS_MMA_TMEM_EMPTY = 23, TMS_EPI_TMEM_FULL = 24, TMS_TMEM_BASE = 25 };
+enum { TMS_PROD_EMPTY = 21, TMS_MMA_FULL = 22, TMS_MMA_TMEM_EMPTY = 23, TMS_EPI_TMEM_FULL = 24, TMS_TMEM_BASE = 25,
+       TMS_AG_FLAG = 26 };
 
 __device__ __forceinline__ void tm_bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -101,13 +130,14 @@ __device__ long long g_tm_trace[16];
 #define TT_END(slot)
 #endif
 
-template <int EPI>
+template <int KIND, int EPI>
 __global__ void __launch_bounds__(TM_THREADS, 1)
 gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                      const TmGemmParams p) {
   using L = TmSmem;
   constexpr int STAGES = L::STAGES;
   constexpr bool GLU = EPI != 0;
+  constexpr int BK_ELEMS = (KIND == 0) ? 64 : 128;   // one 128-byte swizzle span
   constexpr int NB = 2;                          // weight-row blocks per tile
   constexpr int ACC_COLS = NB * TM_BN;           // TMEM columns of one accumulator buffer
   constexpr int NBUF = 512 / ACC_COLS;
@@ -134,15 +164,15 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
 #endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_kb = (p.K + 127) / 128;
+  const int num_kb = (p.K + BK_ELEMS - 1) / BK_ELEMS;
   const int n_tiles = GLU ? p.n_out / TM_BN : (p.n_out + 2 * TM_BN - 1) / (2 * TM_BN);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      // released by the eight epilogue warps once they have read the stage's scale slot, which they only do
-      // after the stage's MMAs have retired (they waited for tfull)
-      mbar_init(&empty_bar[s], 8);
+      // fp8: released by the eight epilogue warps once they have read the stage's scale slot, which they only
+      // do after the stage's MMAs have retired (they waited for tfull).  bf16: released by the MMA commit.
+      mbar_init(&empty_bar[s], KIND == 1 ? 8 : 1);
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(&tfull_bar[b], 1);
@@ -193,7 +223,14 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     const int len = p.seg_len ? p.seg_len[g] : p.T;
     const int m_tiles = (len + 127) / 128;
     nt = local / m_tiles;
-    const int mt = local - nt * m_tiles;
+    int mt = local - nt * m_tiles;
+    if (p.ag_world > 1 && p.ag_rows_per_rank >= 128) {          // own rows first: they need no wait
+      mt += p.ag_rank * (p.ag_rows_per_rank / 128);
+      if (mt >= m_tiles) mt -= m_tiles;
+    } else if (p.rs_world > 1 && p.rs_rows_per_rank >= 128) {   // own rows last: remote rows have further to go
+      mt += (p.rs_rank + 1) * (p.rs_rows_per_rank / 128);
+      if (mt >= m_tiles) mt -= m_tiles;
+    }
     const int start = p.seg_start ? p.seg_start[g] : 0;
     row0 = start + mt * 128;
     rows = min(128, len - mt * 128);
@@ -207,6 +244,8 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
         const uint64_t pol_w = l2_policy_evict_first();
         const uint64_t pol_x = l2_policy_evict_last();
         uint32_t s = 0, sph = 0;
+        uint32_t ag_seen = 0;
+        const int ag_round = (p.ag_world > 1) ? *p.ag_epoch : 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
           int g, nt, row0, rows;
@@ -214,15 +253,31 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
           const int wrow = g * p.w_rows_per_group + (GLU ? nt * TM_BN : nt * 2 * TM_BN);
           const int wrow1 = GLU ? wrow + p.n_out : wrow + TM_BN;
           // activation scales of this tile's rows: [kb][row0 .. row0+128), clipped to the allocation
-          const int sc_n = max(0, min(128, p.x_scale_ld - row0));
+          const int sc_n = (KIND == 1) ? max(0, min(128, p.x_scale_ld - row0)) : 0;
+          if (p.ag_world > 1) {
+            // rows of this tile come from ranks s_lo..s_hi; wait until their blocks have landed here
+            const int s_lo = row0 / p.ag_rows_per_rank;
+            const int s_hi = min(p.ag_world - 1, (row0 + 127) / p.ag_rows_per_rank);
+            for (int sr = s_lo; sr <= s_hi && ok; ++sr) {
+              if (sr == p.ag_rank || ((ag_seen >> sr) & 1u)) continue;
+              if (!flag_wait_ge(p.ag_flag + sr, ag_round, p.ag_wait_ns, p.status, TMS_AG_FLAG, sr)) {
+                *abort_flag = 1;
+                ok = false;
+              }
+              ag_seen |= 1u << sr;
+            }
+            if (!ok) break;
+            // the rows were written by peers through the generic proxy; the TMA engine reads through the async one
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
 #pragma unroll 1
           for (int kb = 0; kb < num_kb; ++kb) {
             if (!mbar_wait(&empty_bar[s], sph ^ 1u, abort_flag, p.status, TMS_PROD_EMPTY, (int)s)) { ok = false; break; }
             uint8_t* st = smem + s * L::STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], L::STAGE_BYTES + sc_n * 4);
-            tma_load_2d_hint(st, &tmap_x, &full_bar[s], kb * 128, row0, pol_x);
-            tma_load_2d_hint(st + L::A_BYTES, &tmap_w, &full_bar[s], kb * 128, wrow, pol_w);
-            tma_load_2d_hint(st + L::A_BYTES + L::B_BYTES, &tmap_w, &full_bar[s], kb * 128, wrow1, pol_w);
+            tma_load_2d_hint(st, &tmap_x, &full_bar[s], kb * BK_ELEMS + g * p.x_group_col, row0, pol_x);
+            tma_load_2d_hint(st + L::A_BYTES, &tmap_w, &full_bar[s], kb * BK_ELEMS, wrow, pol_w);
+            tma_load_2d_hint(st + L::A_BYTES + L::B_BYTES, &tmap_w, &full_bar[s], kb * BK_ELEMS, wrow1, pol_w);
             if (sc_n > 0)
               tm_bulk_load_1d(sc_ring + s * 128, p.x_scale + (size_t)kb * p.x_scale_ld + row0, sc_n * 4, &full_bar[s]);
             if (++s == STAGES) { s = 0; sph ^= 1u; }
@@ -232,15 +287,19 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     } else if (warp == 1) {
       // ---------------------------------------------------------------- MMA issuer (whole warp, one elected lane issues)
       // the two 16 KB weight blocks of a stage are adjacent, which is exactly the K-major layout of 256 rows
-      constexpr uint32_t idesc = umma_idesc(128, 2 * TM_BN, 0, 0);
+      constexpr uint32_t idesc = (KIND == 0) ? umma_idesc(128, 2 * TM_BN, 1, 1) : umma_idesc(128, 2 * TM_BN, 0, 0);
       uint32_t s = 0, sph = 0;
       uint32_t buf = 0, bph = 0;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (KIND == 0) {   // one accumulator buffer per tile
+          if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, abort_flag, p.status, TMS_MMA_TMEM_EMPTY, (int)buf)) { ok = false; break; }
+          tc_fence_after();
+        }
 #pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
-          {
+          if (KIND == 1) {
             TT_BEGIN;
             if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, abort_flag, p.status, TMS_MMA_TMEM_EMPTY, (int)buf)) { ok = false; break; }
             TT_END(0);
@@ -257,13 +316,22 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
             const uint64_t bdesc = umma_desc_kmajor_sw128(sa + L::A_BYTES);
             const uint32_t d0 = tmem_base + buf * ACC_COLS;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma_fp8(d0, adesc + 2 * k, bdesc + 2 * k, idesc, k != 0);
-            umma_commit(&tfull_bar[buf]);
+            for (int k = 0; k < 4; ++k) {
+              if (KIND == 0) umma_bf16(d0, adesc + 2 * k, bdesc + 2 * k, idesc, (kb != 0 || k != 0) ? 1u : 0u);
+              else umma_fp8(d0, adesc + 2 * k, bdesc + 2 * k, idesc, k != 0);
+            }
+            if (KIND == 0) {
+              umma_commit(&empty_bar[s]);                       // operands consumed once these MMAs retire
+              if (kb == num_kb - 1) umma_commit(&tfull_bar[buf]);
+            } else {
+              umma_commit(&tfull_bar[buf]);
+            }
           }
           __syncwarp();
-          if (++buf == NBUF) { buf = 0; bph ^= 1u; }
+          if (KIND == 1) { if (++buf == NBUF) { buf = 0; bph ^= 1u; } }
           if (++s == STAGES) { s = 0; sph ^= 1u; }
         }
+        if (KIND == 0) { if (++buf == NBUF) { buf = 0; bph ^= 1u; } }
       }
     }
   } else {
@@ -297,8 +365,8 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       const int blk0 = GLU ? nt : 2 * nt;
       const int blk1 = GLU ? nt + p.n_out / 128 : 2 * nt + 1;
       const bool blk1_ok = blk1 < sb_per_group;           // store variant: the last tile may have one block only
-      const float* wsc0 = p.w_scale + ((size_t)g * sb_per_group + blk0) * num_kb;
-      const float* wsc1 = p.w_scale + ((size_t)g * sb_per_group + (blk1_ok ? blk1 : blk0)) * num_kb;
+      const float* wsc0 = (KIND == 1) ? p.w_scale + ((size_t)g * sb_per_group + blk0) * num_kb : nullptr;
+      const float* wsc1 = (KIND == 1) ? p.w_scale + ((size_t)g * sb_per_group + (blk1_ok ? blk1 : blk0)) * num_kb : nullptr;
 
       float2 acc[NB][TM_CW / 2];
 #pragma unroll
@@ -306,8 +374,28 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
 #pragma unroll
         for (int j = 0; j < TM_CW / 2; ++j) acc[a][j] = make_float2(0.f, 0.f);
 
+      if (KIND == 0) {
+        // the MMA warp accumulated the whole K range in TMEM: fetch the finished tile
+        if (!mbar_wait(&tfull_bar[buf], bph, abort_flag, p.status, TMS_EPI_TMEM_FULL, (int)buf)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int a = 0; a < NB; ++a) {
+#pragma unroll
+          for (int c0 = 0; c0 < TM_CW; c0 += 16) {
+            uint32_t v[16];
+            tmem_ld_x16(lane_addr + buf * ACC_COLS + a * TM_BN + c_lo + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[a][c0 / 2 + j] = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        if (++buf == NBUF) { buf = 0; bph ^= 1u; }
+      }
 #pragma unroll 1
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = 0; KIND == 1 && kb < num_kb; ++kb) {
         // consecutive weight scales share a cache line, so these loads hit L1 except once every 32 K blocks
         const float sw0 = __ldg(wsc0 + kb);
         const float sw1 = blk1_ok ? __ldg(wsc1 + kb) : 0.f;
@@ -361,36 +449,46 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       if (EPI == 0) {
         const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
         if (row_ok) {
+          // where this token row goes: the local output, or (reduce-scatter) the receive slab of the rank that
+          // owns the row, at [this rank][row inside the owner's block]
+          uint8_t* obase = (uint8_t*)p.out;
+          size_t orow = row;
+          if (p.rs_world > 1) {
+            const int dst = (int)(row / (size_t)p.rs_rows_per_rank);
+            obase = (uint8_t*)p.rs_out[dst];
+            orow = (size_t)p.rs_rank * p.rs_rows_per_rank + (row - (size_t)dst * p.rs_rows_per_rank);
+          }
 #pragma unroll
           for (int a = 0; a < NB; ++a) {
-            const int n0 = (2 * nt + a) * TM_BN + c_lo;   // block a = output features [ (2 nt + a) * 128, +128 )
-            if (n0 >= p.n_out) continue;
+            const int nl = (2 * nt + a) * TM_BN + c_lo;   // block a = output features [ (2 nt + a) * 128, +128 )
+            if (nl >= p.n_out) continue;
+            const size_t ocol = (size_t)nl + (size_t)g * p.out_group_col;
             if (p.out_f32) {
-              float* o = (float*)p.out + row * p.out_ld + n0;
+              float* o = (float*)obase + orow * p.out_ld + ocol;
 #pragma unroll
               for (int j = 0; j < TM_CW / 2; j += 2) {
-                if (n0 + 2 * j + 3 < p.n_out) {
+                if (nl + 2 * j + 3 < p.n_out) {
                   *reinterpret_cast<float4*>(o + 2 * j) =
                       make_float4(acc[a][j].x * rs, acc[a][j].y * rs, acc[a][j + 1].x * rs, acc[a][j + 1].y * rs);
                 } else {
                   const float v4[4] = {acc[a][j].x * rs, acc[a][j].y * rs, acc[a][j + 1].x * rs, acc[a][j + 1].y * rs};
                   for (int e = 0; e < 4; ++e)
-                    if (n0 + 2 * j + e < p.n_out) o[2 * j + e] = v4[e];
+                    if (nl + 2 * j + e < p.n_out) o[2 * j + e] = v4[e];
                 }
               }
             } else {
-              __nv_bfloat16* o = (__nv_bfloat16*)p.out + row * p.out_ld + n0;
+              __nv_bfloat16* o = (__nv_bfloat16*)obase + orow * p.out_ld + ocol;
 #pragma unroll
               for (int j = 0; j < TM_CW / 2; j += 4) {
                 __nv_bfloat162 h[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[a][j + e].x * rs, acc[a][j + e].y * rs);
-                if (n0 + 2 * j + 7 < p.n_out) {
+                if (nl + 2 * j + 7 < p.n_out) {
                   *reinterpret_cast<uint4*>(o + 2 * j) = *reinterpret_cast<uint4*>(h);
                 } else {
                   const __nv_bfloat16* hv = reinterpret_cast<const __nv_bfloat16*>(h);
                   for (int e = 0; e < 8; ++e)
-                    if (n0 + 2 * j + e < p.n_out) o[2 * j + e] = hv[e];
+                    if (nl + 2 * j + e < p.n_out) o[2 * j + e] = hv[e];
                 }
               }
             }
@@ -453,6 +551,23 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     if (warp == 4) { g_tm_trace[2] = gtrace[2]; g_tm_trace[3] = gtrace[3]; g_tm_trace[5] = gtrace[5]; g_tm_trace[9] = tot; }
   }
 #endif
+  // ------------------------------------------------------------------ reduce-scatter: tell the destinations
+  if (p.rs_world > 1) {
+    if (warp >= 4) __threadfence_system();   // this thread's peer stores are performed before the flag below
+    __syncthreads();
+    if (threadIdx.x == 0 && !*abort_flag) {
+      __threadfence();
+      const int done = atomicAdd(p.rs_done, 1);
+      if (done == (int)gridDim.x - 1) {      // every CTA of this rank has written its rows
+        *p.rs_done = 0;                       // ready for the next launch
+        const int round = *p.rs_epoch + 1;    // kept in device memory so that a replayed CUDA graph advances it too
+        *p.rs_epoch = round;
+        __threadfence_system();
+        for (int d = 0; d < p.rs_world; ++d) st_release_sys(p.rs_flag[d], round);
+      }
+    }
+  }
+
   // ------------------------------------------------------------------ teardown
   if (*abort_flag) {
     if (threadIdx.x == 0) report_abort(abort_flag, p.status);
@@ -468,10 +583,10 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   }
 }
 
-template <int EPI>
+template <int KIND, int EPI>
 static int launch_tm(const CUtensorMap& tx, const CUtensorMap& tw, const TmGemmParams& p, int grid, cudaStream_t st) {
   using L = TmSmem;
-  auto kfn = gemm_tokmajor_kernel<EPI>;
+  auto kfn = gemm_tokmajor_kernel<KIND, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -492,34 +607,90 @@ extern "C" int omni_gemm_trace_read(long long* out16) {
 }
 #endif
 
-// Block-scaled e4m3 GEMM, tokens on the UMMA M dimension.  Arguments as omni_gemm (kind is always e4m3).
+// Collective side of a call (all zero / null for a plain GEMM).
+struct OmniTmCollective {
+  int rs_world, rs_rank, rs_rows_per_rank, pad0;
+  void* rs_out[8];
+  int* rs_flag[8];
+  int* rs_done;
+  int* rs_epoch;
+  int ag_world, ag_rank, ag_rows_per_rank, pad1;
+  const int* ag_flag;
+  const int* ag_epoch;
+  unsigned long long ag_wait_ns;
+};
+
+// Token-major GEMM.  kind: 0 bf16, 1 e4m3 block-scaled.  Arguments as omni_gemm; `coll` may be null.
 // Requirements beyond omni_gemm's: n_out a multiple of 8 (16-byte output vectors), for the SwiGLU variants a
-// multiple of 128; segment starts a multiple of 4 rows (bulk copies of activation scales); out_ld a multiple
-// of 8 elements.  Returns 0 on success, a negative value for bad arguments, a positive CUDA error otherwise.
+// multiple of 128; segment starts a multiple of 4 rows for e4m3 (bulk copies of activation scales); out_ld a
+// multiple of 8 elements.  Returns 0 on success, a negative value for bad arguments, a positive CUDA error
+// otherwise.
+extern "C" int omni_gemm_tm2(int kind, int epi, const void* w, const void* x, void* out, int G, int n_out, int K, int x_rows,
+                             int T, const int* seg_start, const int* seg_len, const float* w_scale, const float* x_scale,
+                             int x_scale_ld, int out_ld, int out_f32, float* out_scale, int out_scale_ld,
+                             const float* row_scale, int x_group_col, int out_group_col, int x_ld,
+                             const OmniTmCollective* coll, void* status, cudaStream_t stream) {
+  if (G < 1 || G > TM_MAX_GROUPS || n_out < 1 || K < 1) return -1;
+  if (kind != 0 && kind != 1) return -1;
+  const int nb = (epi == 0) ? 1 : 2;
+  const int esz = (kind == 0) ? 2 : 1;
+  if ((K * esz) % 16 != 0) return -2;
+  if (nb == 2 && (n_out % 128) != 0) return -3;
+  if (kind == 1 && (w_scale == nullptr || x_scale == nullptr)) return -4;
+  if (kind == 1 && ((x_scale_ld % 4) != 0 || ((uintptr_t)x_scale % 16) != 0)) return -7;
+  if (epi == 2 && (out_scale == nullptr || kind != 1)) return -5;
+  if ((n_out % 8) != 0 || (out_ld % 8) != 0 || (out_group_col % 8) != 0) return -8;
+  if (epi < 0 || epi > 2) return -9;
+  TmGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.G = G; p.n_out = n_out; p.K = K; p.T = T; p.seg_start = seg_start; p.seg_len = seg_len;
+  p.w_rows_per_group = n_out * nb; p.w_scale = w_scale; p.x_scale = x_scale; p.x_scale_ld = x_scale_ld;
+  p.out = out; p.out_ld = out_ld; p.out_f32 = out_f32; p.out_scale = out_scale; p.out_scale_ld = out_scale_ld;
+  p.row_scale = row_scale; p.x_group_col = x_group_col; p.out_group_col = out_group_col; p.status = (OmniStatus*)status;
+  p.rs_world = 1; p.ag_world = 1;
+  if (coll != nullptr) {
+    if (coll->rs_world > 1) {
+      if (coll->rs_world > 8 || epi != 0 || out_f32 || G != 1 || seg_len != nullptr || coll->rs_rows_per_rank < 1) return -12;
+      p.rs_world = coll->rs_world; p.rs_rank = coll->rs_rank; p.rs_rows_per_rank = coll->rs_rows_per_rank;
+      p.rs_epoch = coll->rs_epoch; p.rs_done = coll->rs_done;
+      if (p.rs_epoch == nullptr) return -12;
+      for (int d = 0; d < coll->rs_world; ++d) {
+        if (coll->rs_out[d] == nullptr || coll->rs_flag[d] == nullptr || ((uintptr_t)coll->rs_out[d] % 16) != 0) return -12;
+        p.rs_out[d] = coll->rs_out[d]; p.rs_flag[d] = coll->rs_flag[d];
+      }
+      if (p.rs_done == nullptr || (long long)coll->rs_world * coll->rs_rows_per_rank < T) return -12;
+    }
+    if (coll->ag_world > 1) {
+      if (coll->ag_world > 8 || G != 1 || seg_len != nullptr || coll->ag_flag == nullptr || coll->ag_rows_per_rank < 1) return -13;
+      p.ag_world = coll->ag_world; p.ag_rank = coll->ag_rank; p.ag_rows_per_rank = coll->ag_rows_per_rank;
+      p.ag_epoch = coll->ag_epoch; p.ag_flag = coll->ag_flag; p.ag_wait_ns = coll->ag_wait_ns;
+      if (p.ag_epoch == nullptr) return -13;
+    }
+  }
+  if (p.rs_world == 1 && ((uintptr_t)out % 16) != 0) return -8;
+  if (x_ld <= 0) x_ld = K;
+  const uint64_t x_cols = x_group_col > 0 ? (uint64_t)x_ld : (uint64_t)K;
+  const int bk = (kind == 0) ? 64 : 128;
+  if (x_group_col > 0 && (K % bk) != 0) return -6;   // a K tail would read the next group's columns
+  CUtensorMap tx, tw;
+  if (make_tmap_2d(&tx, x, esz, (uint64_t)x_rows, x_cols, x_ld, 128, bk, true)) return -11;
+  if (make_tmap_2d(&tw, w, esz, (uint64_t)G * p.w_rows_per_group, K, K, TM_BN, bk, true)) return -10;
+  const int grid = sm_count();
+  if (kind == 0) {
+    if (epi == 0) return launch_tm<0, 0>(tx, tw, p, grid, stream);
+    if (epi == 1) return launch_tm<0, 1>(tx, tw, p, grid, stream);
+    return -9;
+  }
+  if (epi == 0) return launch_tm<1, 0>(tx, tw, p, grid, stream);
+  if (epi == 1) return launch_tm<1, 1>(tx, tw, p, grid, stream);
+  return launch_tm<1, 2>(tx, tw, p, grid, stream);
+}
+
+// e4m3 only, no collective (kept for callers of the first version of the interface)
 extern "C" int omni_gemm_tm(int epi, const void* w, const void* x, void* out, int G, int n_out, int K, int x_rows, int T,
                             const int* seg_start, const int* seg_len, const float* w_scale, const float* x_scale,
                             int x_scale_ld, int out_ld, int out_f32, float* out_scale, int out_scale_ld,
                             const float* row_scale, int x_ld, void* status, cudaStream_t stream) {
-  if (G < 1 || G > TM_MAX_GROUPS || n_out < 1 || K < 1) return -1;
-  const int nb = (epi == 0) ? 1 : 2;
-  if ((K % 16) != 0) return -2;
-  if (nb == 2 && (n_out % 128) != 0) return -3;
-  if (w_scale == nullptr || x_scale == nullptr) return -4;
-  if ((x_scale_ld % 4) != 0 || ((uintptr_t)x_scale % 16) != 0) return -7;
-  if (epi == 2 && out_scale == nullptr) return -5;
-  if ((n_out % 8) != 0 || (out_ld % 8) != 0 || ((uintptr_t)out % 16) != 0) return -8;
-  if (epi < 0 || epi > 2) return -9;
-  TmGemmParams p;
-  p.G = G; p.n_out = n_out; p.K = K; p.T = T; p.seg_start = seg_start; p.seg_len = seg_len;
-  p.w_rows_per_group = n_out * nb; p.w_scale = w_scale; p.x_scale = x_scale; p.x_scale_ld = x_scale_ld;
-  p.out = out; p.out_ld = out_ld; p.out_f32 = out_f32; p.out_scale = out_scale; p.out_scale_ld = out_scale_ld;
-  p.row_scale = row_scale; p.status = (OmniStatus*)status;
-  if (x_ld <= 0) x_ld = K;
-  CUtensorMap tx, tw;
-  if (make_tmap_2d(&tx, x, 1, (uint64_t)x_rows, K, x_ld, 128, 128, true)) return -11;
-  if (make_tmap_2d(&tw, w, 1, (uint64_t)G * p.w_rows_per_group, K, K, TM_BN, 128, true)) return -10;
-  const int grid = sm_count();
-  if (epi == 0) return launch_tm<0>(tx, tw, p, grid, stream);
-  if (epi == 1) return launch_tm<1>(tx, tw, p, grid, stream);
-  return launch_tm<2>(tx, tw, p, grid, stream);
+  return omni_gemm_tm2(1, epi, w, x, out, G, n_out, K, x_rows, T, seg_start, seg_len, w_scale, x_scale, x_scale_ld, out_ld,
+                       out_f32, out_scale, out_scale_ld, row_scale, 0, 0, x_ld, nullptr, status, stream);
 }

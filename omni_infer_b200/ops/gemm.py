@@ -92,6 +92,30 @@ def gemm_ref(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, 
     return y.to(out_dtype)
 
 
+class TmCollective(nat.ctypes.Structure):
+    """Collective side of a token-major GEMM call (mirrors OmniTmCollective in gemm_tokmajor_sm100.cu)."""
+    _fields_ = [("rs_world", nat.ctypes.c_int), ("rs_rank", nat.ctypes.c_int), ("rs_rows_per_rank", nat.ctypes.c_int),
+                ("pad0", nat.ctypes.c_int), ("rs_out", nat.ctypes.c_void_p * 8), ("rs_flag", nat.ctypes.c_void_p * 8),
+                ("rs_done", nat.ctypes.c_void_p), ("rs_epoch", nat.ctypes.c_void_p),
+                ("ag_world", nat.ctypes.c_int), ("ag_rank", nat.ctypes.c_int), ("ag_rows_per_rank", nat.ctypes.c_int),
+                ("pad1", nat.ctypes.c_int), ("ag_flag", nat.ctypes.c_void_p), ("ag_epoch", nat.ctypes.c_void_p),
+                ("ag_wait_ns", nat.ctypes.c_ulonglong)]
+
+
+def _tm2(kind, e, w, x, out, G, n_out, K, T, seg_start, seg_len, w_scale, x_scale, out_f32, out_scale, row_scale,
+         x_group_col=0, out_group_col=0, out_ld=None, x_ld=None, coll=None):
+    rc = nat.lib().omni_gemm_tm2(
+        nat.c_int(kind), nat.c_int(e), nat.ptr(w), nat.ptr(x), nat.ptr(out), nat.c_int(G), nat.c_int(n_out), nat.c_int(K),
+        nat.c_int(T), nat.c_int(T), nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(w_scale), nat.ptr(x_scale),
+        nat.c_int(x_scale.shape[1] if x_scale is not None else 0),
+        nat.c_int(out_ld if out_ld is not None else out.stride(0)), nat.c_int(out_f32), nat.ptr(out_scale),
+        nat.c_int(out_scale.shape[1] if out_scale is not None else 0), nat.ptr(row_scale),
+        nat.c_int(x_group_col), nat.c_int(out_group_col), nat.c_int(x_ld if x_ld is not None else x.stride(0)),
+        nat.ctypes.byref(coll) if coll is not None else None,
+        nat.ptr(nat.status_buffer(x.device)), nat.stream())
+    nat.check_rc(rc, "omni_gemm_tm2")
+
+
 def _fp8_impl():
     """Which fp8 kernel ``gemm`` uses: "tokmajor" (default) or "swapab" (weights on the UMMA M dimension)."""
     import os
@@ -134,15 +158,15 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
         if out is None:
             out = torch.empty(T, n_out, dtype=out_dtype if e == 0 else torch.bfloat16, device=x.device)
         out_f32 = 1 if out.dtype == torch.float32 else 0
-    if kind == 1 and _fp8_impl() == "tokmajor" and n_out % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
-        # tokens on the UMMA M dimension: one scale multiplier per thread and K block, vector stores
-        rc = L.omni_gemm_tm(
-            nat.c_int(e), nat.ptr(w), nat.ptr(x), nat.ptr(out), nat.c_int(G), nat.c_int(n_out), nat.c_int(K),
-            nat.c_int(T), nat.c_int(T), nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(w_scale), nat.ptr(x_scale),
-            nat.c_int(x_scale.shape[1]), nat.c_int(out.stride(0)), nat.c_int(out_f32), nat.ptr(out_scale),
-            nat.c_int(out_scale.shape[1] if out_scale is not None else 0), nat.ptr(row_scale),
-            nat.c_int(x.stride(0)), nat.ptr(nat.status_buffer(x.device)), nat.stream())
-        nat.check_rc(rc, "omni_gemm_tm")
+    tm_ok = n_out % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and _fp8_impl() == "tokmajor"
+    # fp8: always token-major (one scale multiplier per thread and K block).  bf16: token-major from 64 rows per
+    # group on (vector stores, N = 256 tiles); below that, and for the split-K fp32 router GEMM, tokens stay on N.
+    rows_hint = t_hint if (seg_len is not None and t_hint > 0) else T
+    if tm_ok and e != 2 and kind == 0 and rows_hint >= 64 and not out_f32 and bn == 0:
+        _tm2(0, e, w, x, out, G, n_out, K, T, seg_start, seg_len, None, None, 0, None, row_scale)
+        return out
+    if tm_ok and kind == 1:
+        _tm2(1, e, w, x, out, G, n_out, K, T, seg_start, seg_len, w_scale, x_scale, out_f32, out_scale, row_scale)
         if e == 2:
             return out, out_scale
         return out
@@ -185,6 +209,11 @@ def bmm_heads(x, w, out=None, out_col_offset=0):
         out = torch.empty(T, H, N, dtype=x.dtype, device=x.device)
     assert out.stride(2) == 1 and out.stride(0) == H * out.stride(1)
     base_out = out[:, :, out_col_offset:] if out_col_offset else out
+    if (T >= 64 and N % 8 == 0 and out.stride(0) % 8 == 0 and out.stride(1) % 8 == 0 and base_out.data_ptr() % 16 == 0
+            and _fp8_impl() == "tokmajor"):
+        _tm2(0, 0, w, x, base_out, H, N, K, T, None, None, None, None, 0, None, None,
+             x_group_col=x.stride(1), out_group_col=out.stride(1), out_ld=out.stride(0), x_ld=x.stride(0))
+        return out
     rc = nat.lib().omni_gemm(
         nat.c_int(0), nat.c_int(0), nat.ptr(w), nat.ptr(x), nat.ptr(base_out), nat.c_int(H), nat.c_int(N), nat.c_int(K),
         nat.c_int(T), nat.c_int(T), nat.ptr(None), nat.ptr(None), nat.ptr(None), nat.ptr(None), nat.c_int(0),
