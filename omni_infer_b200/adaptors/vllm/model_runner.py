@@ -45,6 +45,8 @@ class RunnerConfig:
     control_accept_rate: float = -1.0          # test knob of the MTP verifier (reference: model_extra_config)
     ep_backend: str = "fused"                  # fused (NVLink peer-memory kernels) | nccl (all-to-all baseline)
     ep_wait_ms: float = 2000.0                 # bound of every cross-rank wait inside the fused kernels
+    attn_tp: bool = False                      # attention heads sharded over all ranks, token-sharded hidden states
+    tp_backend: str = "fused"                  # fused | nccl
 
 
 class ModelRunner:
@@ -69,6 +71,7 @@ class ModelRunner:
     def load_model(self, weights=None, seed: Optional[int] = 0) -> None:
         cfg = self.model_cfg
         t0 = time.time()
+        self.setup_tensor_parallel()
         self.model = build_model(cfg, device=self.device, planner=self.planner,
                                  seed=seed if weights is None else None)
         from ...models.deepseek_mtp import DeepseekV3MTP
@@ -90,6 +93,25 @@ class ModelRunner:
             self.planner.init_dram_weights(self.model)
         self.setup_expert_parallel()
         logger.info("model %s loaded in %.1fs", cfg.name or cfg.architecture, time.time() - t0)
+
+    def setup_tensor_parallel(self) -> None:
+        """Tensor-parallel attention: every rank runs the same batch, heads are sharded, and the row all-gather /
+        reduce-scatter around the attention block run inside the GEMMs (parallel/tp_fused.py)."""
+        ps = get_parallel_state()
+        cfg = self.model_cfg
+        if not self.cfg.attn_tp or ps.world_size == 1:
+            return
+        assert getattr(cfg, "is_mla", True) and cfg.architecture.startswith("Deepseek"), \
+            "tensor-parallel attention is wired for the MLA models"
+        cfg.attn_tp_size, cfg.attn_tp_rank = ps.world_size, ps.rank
+        from ...parallel.tp_fused import TpFusedContext, TpNcclBaseline
+        grp = ps.group("world").group
+        if self.cfg.tp_backend == "fused" and self.device.type == "cuda":
+            max_tok = max(self.cfg.max_num_batched_tokens, self.cfg.max_num_seqs * self.tpr) + 4 * ps.world_size
+            ps.tp_fused = TpFusedContext(grp, max_tokens=max_tok, max_k_bytes=cfg.hidden_size * 2, max_n=cfg.hidden_size,
+                                         wait_ms=self.cfg.ep_wait_ms)
+        else:
+            ps.tp_fused = TpNcclBaseline(grp)
 
     def setup_expert_parallel(self) -> None:
         """With more than one rank the routed experts are sharded over all ranks.  Decode-sized batches go

@@ -43,6 +43,8 @@ class EngineConfig:
     decode_gear_list: list = field(default_factory=list)
     enforce_eager: bool = False
     ep_backend: str = "fused"
+    attn_tp: bool = False            # tensor-parallel attention over all ranks (default: data-parallel attention)
+    tp_backend: str = "fused"        # fused (GEMMs with the collectives inside) | nccl (library collectives)
     seed: int = 0
     kv_transfer_config: Optional[dict] = None    # {"kv_role": "kv_producer"|"kv_consumer", ...}
     enable_omni_attn: bool = False
@@ -60,7 +62,8 @@ class EngineCore:
                           gpu_memory_utilization=cfg.gpu_memory_utilization, max_num_seqs=cfg.max_num_seqs,
                           max_model_len=cfg.max_model_len, max_num_batched_tokens=cfg.max_num_batched_tokens,
                           num_speculative_tokens=cfg.num_speculative_tokens, decode_gear_list=cfg.decode_gear_list,
-                          enforce_eager=cfg.enforce_eager, seed=cfg.seed, ep_backend=cfg.ep_backend)
+                          enforce_eager=cfg.enforce_eager, seed=cfg.seed, ep_backend=cfg.ep_backend,
+                          attn_tp=cfg.attn_tp, tp_backend=cfg.tp_backend)
         sched_conn = worker_conn = None
         if kv_connector_pair is not None:
             sched_conn, worker_conn = kv_connector_pair

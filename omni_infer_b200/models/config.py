@@ -11,6 +11,10 @@ from typing import Any, Optional
 @dataclass
 class ModelConfig:
     architecture: str = "DeepseekV3ForCausalLM"
+    # tensor-parallel attention: heads sharded over attn_tp_size ranks, hidden states sharded by token rows between
+    # layers (set by the model runner; 1 = every rank runs whole attention layers on its own requests)
+    attn_tp_size: int = 1
+    attn_tp_rank: int = 0
     vocab_size: int = 1024
     hidden_size: int = 256
     num_hidden_layers: int = 2

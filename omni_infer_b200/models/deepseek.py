@@ -35,6 +35,22 @@ class DeepseekDecoderLayer(nn.Module):
             self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, quant=q, device=device)
         self.is_moe = is_moe
 
+    def forward_tp(self, h, residual, md: AttnMetadata, kv_cache, tp, num_valid):
+        """Same layer on this rank's token rows, attention sharded by heads (see MLAAttention.forward_tp)."""
+        if residual is None:
+            residual = h.clone()
+            n = self.input_layernorm(h, quant=self.quant)
+        else:
+            n = self.input_layernorm(h, residual=residual, quant=self.quant)
+        x, xq = (n[0], (n[1], n[2])) if self.quant else (n, None)
+        residual, x = self.self_attn.forward_tp(x, xq, md, kv_cache, residual, self.post_attention_layernorm, tp)
+        xq = ops.quant_fp8_block(x) if self.quant else None
+        if self.is_moe:
+            out = self.mlp(x, xq=xq, num_valid=num_valid)
+        else:
+            out = self.mlp(x, xq=xq)
+        return out, residual
+
     def forward(self, h, residual, md: AttnMetadata, kv_cache):
         if residual is None:
             residual = h.clone()
@@ -50,6 +66,34 @@ class DeepseekDecoderLayer(nn.Module):
         else:
             out = self.mlp(x, xq=xq)
         return out, residual
+
+
+def shard_rows_for_tp(cfg, input_ids, md, embed_weight, inputs_embeds=None):
+    """This rank's block of the token rows, padded so that every rank has the same number (a multiple of four:
+    activation-scale rows are copied 16 bytes at a time).  Returns (tp context, rows [rpr, hidden], number of
+    valid rows among them as a device tensor, real row count)."""
+    from ..parallel.parallel_state import get_parallel_state
+    tp = get_parallel_state().tp_fused
+    assert tp is not None, "tensor-parallel attention needs the runner to set up the TP context first"
+    W, r = tp.world, tp.rank
+    T = input_ids.shape[0] if inputs_embeds is None else inputs_embeds.shape[0]
+    step = W * 4
+    Tp = (T + step - 1) // step * step
+    rpr = Tp // W
+    lo, hi = r * rpr, min(T, (r + 1) * rpr)
+    if inputs_embeds is None:
+        ids = input_ids[lo:hi] if hi > lo else input_ids[:0]
+        h = ops.embedding(ids, embed_weight)
+    else:
+        h = inputs_embeds[lo:hi] if hi > lo else inputs_embeds[:0]
+    if h.shape[0] < rpr:
+        h = torch.cat([h, h.new_zeros(rpr - h.shape[0], h.shape[1])], 0)
+    dev = h.device
+    if md.num_valid is not None:
+        nv = (md.num_valid[:1].to(torch.int32) - lo).clamp(0, rpr)
+    else:
+        nv = torch.tensor([max(0, hi - lo)], dtype=torch.int32, device=dev) if Tp != T else None
+    return tp, h.contiguous(), nv, T
 
 
 class DeepseekModel(nn.Module):
@@ -69,11 +113,25 @@ class DeepseekModel(nn.Module):
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
 
     def forward(self, input_ids, md: AttnMetadata, kv_caches, inputs_embeds=None):
+        if self.cfg.attn_tp_size > 1:
+            return self._forward_tp(input_ids, md, kv_caches, inputs_embeds)
         h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
         residual = None
         for i, layer in enumerate(self.layers):
             h, residual = layer(h, residual, md, kv_caches[i])
         return self.norm(h, residual=residual)
+
+    def _forward_tp(self, input_ids, md: AttnMetadata, kv_caches, inputs_embeds=None):
+        """Tensor-parallel attention: every rank sees the same batch, works on its block of the (padded) token rows
+        between the attention blocks, and gathers the final hidden states so that sampling is identical everywhere."""
+        from ..parallel.parallel_state import get_parallel_state
+        tp, h, num_valid, T = shard_rows_for_tp(self.cfg, input_ids, md, self.embed_tokens.weight, inputs_embeds)
+        residual = None
+        for i, layer in enumerate(self.layers):
+            h, residual = layer.forward_tp(h, residual, md, kv_caches[i], tp, num_valid)
+        out = self.norm(h, residual=residual)
+        full = get_parallel_state().group("world").all_gather(out, dim=0)
+        return full[:T]
 
 
 class DeepseekV3ForCausalLM(nn.Module):

@@ -42,6 +42,14 @@ class DeepseekV3MTP(nn.Module):
         emb = ops.embedding(input_ids, self._main.model.embed_tokens.weight)
         x = torch.cat([self.enorm(emb), self.hnorm(previous_hidden_states)], dim=-1)
         h = self.eh_proj(x)
+        if self.cfg.attn_tp_size > 1:
+            # tensor-parallel attention: the drafter layer works on this rank's block of the rows like the main stack
+            from ..parallel.parallel_state import get_parallel_state
+            from .deepseek import shard_rows_for_tp
+            tp, hs, nv, T = shard_rows_for_tp(self.cfg, input_ids, md, None, inputs_embeds=h)
+            hs, residual = self.decoder.forward_tp(hs, None, md, kv_caches[0], tp, nv)
+            out = self.shared_head_norm(hs, residual=residual)
+            return get_parallel_state().group("world").all_gather(out, dim=0)[:T]
         h, residual = self.decoder(h, None, md, kv_caches[0])
         return self.shared_head_norm(h, residual=residual)
 

@@ -107,6 +107,7 @@ class ParallelState:
     tp_size: int = 1
     backend: str = "none"
     groups: dict = field(default_factory=dict)
+    tp_fused: object = None     # TpFusedContext / TpNcclBaseline when attention runs tensor parallel
 
     @property
     def dp_size(self) -> int:

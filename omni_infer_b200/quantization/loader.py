@@ -46,6 +46,17 @@ class WeightLoader:
     def _store(self, pname: str, sname: Optional[str], w, scale, offset, rows=None, index=None):
         p = self.params[pname]
         tgt = p.data if index is None else p.data[index]
+        slice_fn = getattr(p, "tp_slice_fn", None)
+        if slice_fn is not None and rows is None and index is None:
+            # tensor-parallel shard of a whole checkpoint tensor (merged projections are not sharded by this route)
+            if p.dtype == FP8 and not (w.dtype == FP8 and scale is not None):
+                w, scale = quant_weight_fp8_block_ref(_to_float(w, scale, offset).to(tgt.device))
+                offset = None
+            if p.dtype == FP8:
+                scale = self.params[sname].tp_slice_fn(scale)
+            elif scale is not None:
+                w, scale, offset = _to_float(w, scale, offset), None, None
+            w = slice_fn(w)
         r0, r1 = rows if rows is not None else (0, tgt.shape[0])
         if p.dtype == FP8:
             sp = self.params[sname]
@@ -241,6 +252,18 @@ def init_random_weights(model, seed: int = 0, std: float = 0.02) -> None:
         return g
 
     def fill(p, sp, g):
+        full = getattr(p, "tp_full_shape", None)
+        if full is not None:
+            # tensor-parallel shard: draw the whole tensor (so that the sharded model is the unsharded one), keep this
+            # rank's slice; e4m3 tensors are quantised whole and their scale blocks sliced alongside
+            w = torch.randn(full, generator=g, device=p.device, dtype=torch.float32) * std
+            if p.dtype == FP8:
+                q, s_ = quant_weight_fp8_block_ref(w)
+                p.copy_(p.tp_slice_fn(q))
+                sp.copy_(sp.tp_slice_fn(s_))
+            else:
+                p.copy_(p.tp_slice_fn(w))
+            return
         if p.dtype == FP8:
             w = torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32) * std
             q, s = quant_weight_fp8_block_ref(w)

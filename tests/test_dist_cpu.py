@@ -95,6 +95,29 @@ def test_expert_parallel_matches_single_rank():
     assert two[0] == single and two[1] == single
 
 
+# ---------------------------------------------------------------------------------------------- TP attention
+def _tp_engine(rank, world):
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", seed=3,
+                                  attn_tp=True, tp_backend="nccl"))
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (17 + i,), generator=g).tolist() for i in range(3)]   # 56 rows: not a multiple of 8
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in prompts]
+    outs = eng.run_until_done()
+    if dist.is_initialized():
+        dist.barrier()
+    return [outs[i] for i in ids]
+
+
+def test_tensor_parallel_attention_matches_single_rank():
+    """Heads sharded over two ranks, hidden states sharded by token rows between layers (library collectives on CPU):
+    same tokens as the unsharded model."""
+    single = _spawn(_tp_engine, 1)[0]
+    two = _spawn(_tp_engine, 2)
+    assert two[0] == single and two[1] == single
+
+
 # ---------------------------------------------------------------------------------------------- placement across ranks
 def _placement_round(rank, world):
     from omni_infer_b200.accelerators.placement import OmniPlanner

@@ -22,7 +22,9 @@ from omni_infer_b200.ops import _native as nat
 backend = os.environ.get("EP_BACKEND", "fused")
 mc = get_config("small-deepseek", quantization="fp8_block", num_nextn_predict_layers=1)
 eng = EngineCore(EngineConfig(block_size=128, num_kv_blocks=24, max_model_len=512, max_num_seqs=4,
-                              num_speculative_tokens=int(os.environ.get("MTP", "0")), ep_backend=backend, seed=7), model_cfg=mc)
+                              num_speculative_tokens=int(os.environ.get("MTP", "0")), ep_backend=backend, seed=7,
+                              attn_tp=os.environ.get("ATTN_TP", "0") == "1", tp_backend=os.environ.get("TP_BACKEND", "fused")),
+                 model_cfg=mc)
 rank = int(os.environ.get("RANK", "0"))
 g = torch.Generator().manual_seed(5)
 prompts = [torch.randint(0, 4096, (40,), generator=g).tolist() for _ in range(4)]
@@ -147,3 +149,18 @@ def test_tp2_fused_gemm_collectives_match_nccl():
     for k, v in res.items():
         tol = 0.0 if k.startswith("ag_x") else 2e-2
         assert v <= tol, (k, v, res)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_attention_with_ep2_moe_matches_single_rank():
+    """Attention heads sharded over two ranks with the collectives inside the GEMMs, experts sharded over the same two
+    ranks: same tokens as one GPU, with and without an MTP drafter, and as with NCCL collectives."""
+    single = _run(1, {}, 0)
+    fused = _run(2, {"ATTN_TP": "1", "TP_BACKEND": "fused"}, 29614)
+    nccl = _run(2, {"ATTN_TP": "1", "TP_BACKEND": "nccl"}, 29615)
+    assert _agreement(fused, single) > 0.6
+    assert _agreement(nccl, single) > 0.6
+    assert _agreement(fused, nccl) > 0.6
+    mtp1 = _run(1, {"MTP": "1"}, 0)
+    mtp2 = _run(2, {"MTP": "1", "ATTN_TP": "1"}, 29616)
+    assert _agreement(mtp2, mtp1) > 0.6
