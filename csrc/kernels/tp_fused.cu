@@ -4,6 +4,10 @@
 //                   included) with 16-byte peer stores, then publish "block of rank r, round e has landed" on every
 //                   rank.  The GEMM that follows on each rank waits per source block, so it starts on its own rows
 //                   while the others are still in flight.
+//   omni_ag_collect plain all-gather, consumer side: wait (bounded) for every rank's block of the current round, then
+//                   copy the gathered rows out of the receive buffer.  The receive buffer has two halves used in
+//                   turn (chosen by the round counter in device memory), so a rank that is already pushing the next
+//                   round cannot overwrite rows a slower rank is still copying.
 //   omni_rs_reduce  reduce-scatter, consumer side: the GEMM epilogues of all ranks have written their partial rows
 //                   into this rank's slab [source rank][row][n]; wait (bounded) for every source's flag, add the
 //                   slabs in fp32, optionally add the residual stream and apply RMSNorm in the same pass.
@@ -26,6 +30,7 @@ struct AgPushParams {
   int rows, row_bytes;     // row_bytes a multiple of 16
   long long dst_row_pitch; // bytes between rows of the gather buffers
   long long dst_offset;    // byte offset of this rank's block inside every gather buffer
+  long long parity_stride; // != 0: the gather buffers have two halves this far apart, rounds alternate between them
   int world, rank, signal;
   uint8_t* gather[8];      // per rank: base of its gather buffer
   int* flag[8];            // per rank: flag word of this source rank
@@ -36,9 +41,11 @@ struct AgPushParams {
 __global__ void ag_push_kernel(const AgPushParams p) {
   const int vec_per_row = p.row_bytes / 16;
   const long long total = (long long)p.rows * vec_per_row;
+  const long long half = p.parity_stride ? (long long)((*p.epoch + 1) & 1) * p.parity_stride : 0;   // round being produced
+  __syncthreads();   // every thread has read the round counter before the last CTA advances it
   for (int d0 = 0; d0 < p.world; ++d0) {
     const int d = (p.rank + 1 + d0) % p.world;   // remote ranks first, the local copy last
-    uint8_t* dst = p.gather[d] + p.dst_offset;
+    uint8_t* dst = p.gather[d] + p.dst_offset + half;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
       const int r = (int)(i / vec_per_row), c = (int)(i - (long long)r * vec_per_row);
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.src + (long long)r * p.row_bytes) + c);
@@ -145,21 +152,65 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(const RsReduceParams p) 
   }
 }
 
+struct AgCollectParams {
+  const uint8_t* gather;   // local receive buffer (two halves)
+  long long parity_stride;
+  uint8_t* dst;
+  long long bytes;         // multiple of 16
+  int world;
+  const int* flag;         // [world]
+  const int* epoch;        // local round counter (already advanced by this rank's push)
+  unsigned long long wait_ns;
+  OmniStatus* status;
+};
+
+__global__ void __launch_bounds__(256) ag_collect_kernel(const AgCollectParams p) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  const int round = *p.epoch;
+  if (threadIdx.x < p.world) {
+    if (!flag_wait_ge(p.flag + threadIdx.x, round, p.wait_ns, p.status, TPS_RS_FLAG + 1, threadIdx.x)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const uint8_t* src = p.gather + (long long)(round & 1) * p.parity_stride;
+  const long long nv = p.bytes / 16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x)
+    reinterpret_cast<uint4*>(p.dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+}
+
 }  // namespace omni
 
 using namespace omni;
+
+extern "C" int omni_ag_collect(const void* gather, long long parity_stride, void* dst, long long bytes, int world,
+                               const int* flag, const int* epoch, unsigned long long wait_ns, void* status,
+                               cudaStream_t stream) {
+  if (world < 1 || world > 8 || (bytes % 16) != 0 || (parity_stride % 16) != 0 || epoch == nullptr || flag == nullptr) return -1;
+  AgCollectParams p;
+  p.gather = (const uint8_t*)gather; p.parity_stride = parity_stride; p.dst = (uint8_t*)dst; p.bytes = bytes; p.world = world;
+  p.flag = flag; p.epoch = epoch; p.wait_ns = wait_ns; p.status = (OmniStatus*)status;
+  long long nv = bytes / 16;
+  int grid = (int)((nv + 255) / 256);
+  if (grid < 1) grid = 1;
+  if (grid > 148) grid = 148;
+  ag_collect_kernel<<<grid, 256, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
 
 // Copies [rows, row_bytes] from `src` to byte offset `dst_offset` (row pitch `dst_row_pitch`) of every rank's
 // gather buffer.  With signal != 0 the last CTA then advances this rank's round counter and writes it to this
 // rank's flag word on every rank.
 extern "C" int omni_ag_push(const void* src, int rows, int row_bytes, long long dst_row_pitch, long long dst_offset,
-                            int world, int rank, int signal, void* const* gather, int* const* flag, int* epoch, int* done,
-                            cudaStream_t stream) {
+                            long long parity_stride, int world, int rank, int signal, void* const* gather,
+                            int* const* flag, int* epoch, int* done, cudaStream_t stream) {
+  if (parity_stride != 0 && (!signal || (parity_stride % 16) != 0)) return -4;
   if (world < 1 || world > 8 || rows < 0 || (row_bytes % 16) != 0 || (dst_row_pitch % 16) != 0 || (dst_offset % 16) != 0) return -1;
   if (signal && (epoch == nullptr || done == nullptr)) return -2;
   AgPushParams p;
   p.src = (const uint8_t*)src; p.rows = rows; p.row_bytes = row_bytes; p.dst_row_pitch = dst_row_pitch;
-  p.world = world; p.rank = rank; p.signal = signal; p.dst_offset = dst_offset; p.epoch = epoch; p.done = done;
+  p.world = world; p.rank = rank; p.signal = signal; p.dst_offset = dst_offset; p.parity_stride = parity_stride; p.epoch = epoch; p.done = done;
   for (int d = 0; d < world; ++d) {
     if (gather[d] == nullptr || (signal && flag[d] == nullptr) || ((uintptr_t)gather[d] % 16) != 0) return -3;
     p.gather[d] = (uint8_t*)gather[d];

@@ -225,6 +225,10 @@ class ModelRunner:
         if get_parallel_state().world_size > 1 and self.model_cfg.is_moe and getattr(self, "ep_ctx", None) is None:
             logger.info("expert parallelism over NCCL all-to-all needs host-side split sizes: decode stays eager")
             return
+        tpc = get_parallel_state().tp_fused
+        if tpc is not None and tpc.__class__.__name__ == "TpNcclBaseline":
+            logger.info("tensor-parallel attention over library collectives: decode stays eager")
+            return
         from .cuda_graphs import DecodeGraphs
         self.graphs = DecodeGraphs(self)
         t0 = time.time()

@@ -130,8 +130,7 @@ class DeepseekModel(nn.Module):
         for i, layer in enumerate(self.layers):
             h, residual = layer.forward_tp(h, residual, md, kv_caches[i], tp, num_valid)
         out = self.norm(h, residual=residual)
-        full = get_parallel_state().group("world").all_gather(out, dim=0)
-        return full[:T]
+        return tp.all_gather_rows(out.contiguous(), out.shape[0] * tp.world)[:T]
 
 
 class DeepseekV3ForCausalLM(nn.Module):

@@ -49,7 +49,7 @@ class DeepseekV3MTP(nn.Module):
             tp, hs, nv, T = shard_rows_for_tp(self.cfg, input_ids, md, None, inputs_embeds=h)
             hs, residual = self.decoder.forward_tp(hs, None, md, kv_caches[0], tp, nv)
             out = self.shared_head_norm(hs, residual=residual)
-            return get_parallel_state().group("world").all_gather(out, dim=0)[:T]
+            return tp.all_gather_rows(out.contiguous(), out.shape[0] * tp.world)[:T]
         h, residual = self.decoder(h, None, md, kv_caches[0])
         return self.shared_head_norm(h, residual=residual)
 

@@ -54,7 +54,9 @@ class TpFusedContext:
         self.off_slab = off; off = _align(off + self.world * self.max_rpr * self.max_n * 2)
         self.off_ag_flag = off; off = _align(off + 64)
         self.off_rs_flag = off; off = _align(off + 64)
-        self.off_ctrl = off; off = _align(off + 64)     # [0] ag round, [1] ag done, [2] rs round, [3] rs done
+        self.off_fin = off; self.fin_half = _align(self.max_tokens * self.max_k_bytes); off = _align(off + 2 * self.fin_half)
+        self.off_fin_flag = off; off = _align(off + 64)
+        self.off_ctrl = off; off = _align(off + 64)     # [0] ag round, [1] ag done, [2] rs round, [3] rs done, [4] final round, [5] final done
         self.buf = SymmetricBuffer(off, group)
         self.buf.local_tensor(0, off).zero_()
         torch.cuda.synchronize()
@@ -64,6 +66,8 @@ class TpFusedContext:
         self._ag_done = lp + self.off_ctrl + 4
         self._rs_round = lp + self.off_ctrl + 8
         self._rs_done = lp + self.off_ctrl + 12
+        self._fin_round = lp + self.off_ctrl + 16
+        self._fin_done = lp + self.off_ctrl + 20
 
     # ------------------------------------------------------------------ helpers
     def rows_per_rank(self, total_rows: int) -> int:
@@ -100,13 +104,13 @@ class TpFusedContext:
                                        + [None] * (8 - self.world))
             xs_c = x_scale_shard.contiguous()
             rc = L.omni_ag_push(nat.ptr(xs_c), nat.c_int(kb), nat.c_int(rpr * 4), ctypes.c_longlong(total_rows * 4),
-                                ctypes.c_longlong(self.rank * rpr * 4), nat.c_int(self.world), nat.c_int(self.rank),
-                                nat.c_int(0), sc, flags, None, None, nat.stream())
+                                ctypes.c_longlong(self.rank * rpr * 4), ctypes.c_longlong(0), nat.c_int(self.world),
+                                nat.c_int(self.rank), nat.c_int(0), sc, flags, None, None, nat.stream())
             nat.check_rc(rc, "omni_ag_push(scales)")
             nat.add_launches(1)
         rc = L.omni_ag_push(nat.ptr(x_shard), nat.c_int(rpr), nat.c_int(row_bytes), ctypes.c_longlong(row_bytes),
-                            ctypes.c_longlong(self.rank * rpr * row_bytes), nat.c_int(self.world), nat.c_int(self.rank),
-                            nat.c_int(1), gather, flags, ctypes.c_void_p(self._ag_round), ctypes.c_void_p(self._ag_done),
+                            ctypes.c_longlong(self.rank * rpr * row_bytes), ctypes.c_longlong(0), nat.c_int(self.world),
+                            nat.c_int(self.rank), nat.c_int(1), gather, flags, ctypes.c_void_p(self._ag_round), ctypes.c_void_p(self._ag_done),
                             nat.stream())
         nat.check_rc(rc, "omni_ag_push")
         nat.add_launches(1)
@@ -132,6 +136,32 @@ class TpFusedContext:
         if e == 2:
             return (out, out_scale), x_full, xs_full
         return out, x_full, xs_full
+
+    # ------------------------------------------------------------------ plain all-gather of rows
+    def all_gather_rows(self, x_shard: torch.Tensor, total_rows: int) -> torch.Tensor:
+        """[rpr, K] on every rank -> [total_rows, K] on every rank, through peer stores and flags (no library call, so it
+        can sit inside a captured CUDA graph).  Used for the final hidden states, which every rank samples from."""
+        rpr = self.rows_per_rank(total_rows)
+        assert x_shard.shape[0] == rpr and x_shard.is_contiguous()
+        row_bytes = x_shard.shape[1] * x_shard.element_size()
+        assert row_bytes % 16 == 0 and row_bytes <= self.max_k_bytes and total_rows <= self.max_tokens
+        L = nat.lib()
+        gather = (ctypes.c_void_p * 8)(*[self._peer(r, self.off_fin) for r in range(self.world)] + [None] * (8 - self.world))
+        flags = (ctypes.c_void_p * 8)(*[self._peer(r, self.off_fin_flag + 4 * self.rank) for r in range(self.world)]
+                                      + [None] * (8 - self.world))
+        rc = L.omni_ag_push(nat.ptr(x_shard), nat.c_int(rpr), nat.c_int(row_bytes), ctypes.c_longlong(row_bytes),
+                            ctypes.c_longlong(self.rank * rpr * row_bytes), ctypes.c_longlong(self.fin_half),
+                            nat.c_int(self.world), nat.c_int(self.rank), nat.c_int(1), gather, flags,
+                            ctypes.c_void_p(self._fin_round), ctypes.c_void_p(self._fin_done), nat.stream())
+        nat.check_rc(rc, "omni_ag_push(final)")
+        out = torch.empty(total_rows, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        rc = L.omni_ag_collect(ctypes.c_void_p(self.buf.local_ptr + self.off_fin), ctypes.c_longlong(self.fin_half), nat.ptr(out),
+                               ctypes.c_longlong(total_rows * row_bytes), nat.c_int(self.world),
+                               ctypes.c_void_p(self.buf.local_ptr + self.off_fin_flag), ctypes.c_void_p(self._fin_round),
+                               ctypes.c_ulonglong(self.wait_ns), nat.ptr(nat.status_buffer(x_shard.device)), nat.stream())
+        nat.check_rc(rc, "omni_ag_collect")
+        nat.add_launches(2)
+        return out
 
     # ------------------------------------------------------------------ GEMM + reduce-scatter
     def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, *, w_scale=None, x_scale=None, residual=None,
@@ -198,6 +228,11 @@ class TpNcclBaseline:
             xs_full = None
         out = ops.gemm(x_full, w, w_scale=w_scale, x_scale=xs_full, epi=epi, out_dtype=out_dtype)
         return out, x_full, xs_full
+
+    def all_gather_rows(self, x_shard, total_rows):
+        out = torch.empty(total_rows, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        dist.all_gather_into_tensor(out, x_shard.contiguous(), group=self.group)
+        return out
 
     def gemm_reduce_scatter(self, x, w, *, w_scale=None, x_scale=None, residual=None, norm_weight=None, eps=1e-6):
         T = x.shape[0]

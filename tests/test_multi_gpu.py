@@ -110,7 +110,7 @@ def _run(world, env_extra, port, worker=None):
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                "--master-addr", "127.0.0.1", "--master-port", str(port), script]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     os.unlink(script)
     if res.returncode != 0:
         errs = [l for l in res.stderr.splitlines() if not l.startswith(("W1", "[W", "***")) and "OMP_NUM" not in l]
