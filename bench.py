@@ -38,6 +38,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not a benchmark)")
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--ep-backend", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--attn-tp", action="store_true",
+                    help="tensor-parallel attention over all ranks (one shared batch) instead of data-parallel attention")
+    ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--synthetic-kv", action="store_true", help="fill the KV cache without running prefill")
     return ap.parse_args()
 
@@ -142,15 +145,16 @@ def main():
     blocks = batch * ((per_req_tokens + bs - 1) // bs + 1) + 2
     ecfg = EngineConfig(model=mc.name, block_size=bs, num_kv_blocks=blocks, max_num_seqs=batch,
                         max_num_batched_tokens=max(16384, in_len), max_model_len=per_req_tokens + bs,
-                        num_speculative_tokens=mtp, decode_gear_list=[batch], enforce_eager=args.eager, seed=1234 + rank,
-                        ep_backend=args.ep_backend)
+                        num_speculative_tokens=mtp, decode_gear_list=[batch], enforce_eager=args.eager,
+                        seed=1234 + (0 if args.attn_tp else rank), ep_backend=args.ep_backend, attn_tp=args.attn_tp,
+                        tp_backend=args.tp_backend)
     t_load = time.time()
     eng = EngineCore(ecfg, model_cfg=mc)
     eng.worker.runner.cfg.control_accept_rate = args.accept_rate
     load_s = time.time() - t_load
 
     dev = torch.device("cuda", local_rank)
-    g = torch.Generator().manual_seed(100 + rank)
+    g = torch.Generator().manual_seed(100 + (0 if args.attn_tp else rank))   # TP attention: every rank serves the same batch
     # the step's inputs start in pinned host memory, as a serving front end would hand them over
     prompts = torch.randint(0, mc.vocab_size, (batch, in_len), generator=g).pin_memory()
     sp = SamplingParams(max_tokens=10 ** 6, ignore_eos=True)
@@ -220,6 +224,8 @@ def main():
         sm = t.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         dev_ms, wall_ms, tokens_total = float(mx[0]), float(mx[1]), float(sm[2])
+        if args.attn_tp:
+            tokens_total /= world      # one shared batch, counted once
     else:
         dev_ms, wall_ms, tokens_total = float(t[0]), float(t[1]), float(t[2])
     if rank == 0:
@@ -230,11 +236,12 @@ def main():
             "value": round(value, 1), "unit": "tok/s (all GPUs)", "per_gpu_tok_s": round(value / world, 1),
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 3),
             "tpot_p50_ms": round(statistics.median(step_dev), 3), "ttft_p50_ms": round(statistics.median(ttft), 2),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 weights (128x128 block scales), bf16 activations/KV" if mc.quantization == "fp8_block" else "bf16",
+            "higher_is_better": True, "scaling": "strong" if args.attn_tp else "weak", "vs_baseline": None, "dtype": "fp8_e4m3 weights (128x128 block scales), bf16 activations/KV" if mc.quantization == "fp8_block" else "bf16",
             "data": "synthetic (uniform random token ids, random-init weights)",
-            "config": {"model": name, "global_batch": batch * world, "seq_len": in_len, "output_steps": total_steps,
-                       "parallelism": f"ep{world}+dp{world}-attn", "mtp_draft_layers": mtp,
-                       "mtp_accepted_tokens_per_step": round(tokens_total / (args.steps * batch * world), 3),
+            "config": {"model": name, "global_batch": batch * (1 if args.attn_tp else world), "seq_len": in_len, "output_steps": total_steps,
+                       "parallelism": (f"tp{world}-attn({args.tp_backend})+ep{world}" if args.attn_tp and world > 1
+                                       else f"ep{world}+dp{world}-attn"), "mtp_draft_layers": mtp,
+                       "mtp_accepted_tokens_per_step": round(tokens_total / (args.steps * batch * (1 if args.attn_tp else world)), 3),
                        "accept_rate_forced": args.accept_rate, "layers": mc.num_hidden_layers,
                        "routed_experts": mc.n_routed_experts, "cuda_graph": not args.eager,
                        "l2_policy": "inputs larger than L2 (>= 90 GB of weights and KV streamed per step)",

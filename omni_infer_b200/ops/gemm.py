@@ -148,6 +148,13 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     e = _EPI[epi]
     n_out = n_w if e == 0 else n_w // 2
+    if e == 1 and n_out % 128 != 0:
+        # the fused SwiGLU epilogue pairs 128-row gate and up blocks; odd widths (e.g. 10944) take the plain GEMM
+        # and a separate activation kernel
+        from .basic import silu_mul
+        both = gemm(x, w, w_scale=w_scale, x_scale=x_scale, seg_start=seg_start, seg_len=seg_len, epi="store",
+                    row_scale=row_scale, out_dtype=torch.bfloat16, bn=bn, t_hint=t_hint)
+        return silu_mul(both)
     if e == 2:
         if out is None:
             out = torch.empty(T, n_out, dtype=FP8, device=x.device)
