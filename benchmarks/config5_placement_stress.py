@@ -1,0 +1,110 @@
+#!/usr/bin/env python
+"""Load-balance stress for OmniPlacement: a fixed per-layer router bias makes expert popularity Zipf-like (s = 1.2 over a
+random expert permutation, seed 0).  Runs the same decode workload with and without redundant expert slots and periodic
+re-placement, and reports the max/mean expert-position load, the max/mean rank load and the decode throughput.
+
+    python benchmarks/config5_placement_stress.py --config small --steps 64                      # one GPU or CPU
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        benchmarks/config5_placement_stress.py --config deepseek-v3 --redundant 4 --replace-every 1000 --steps 2048
+
+The reference's counterpart is its placement optimiser fed by recorded activations
+(omni/accelerators/placement/omni_placement/omni_planner.py, cpp/placement_manager.cpp)."""
+import argparse
+import json
+import math
+import os
+import sys
+import time
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore  # noqa: E402
+from omni_infer_b200.engine.request import SamplingParams  # noqa: E402
+from omni_infer_b200.models.config import get_config  # noqa: E402
+
+
+def zipf_bias(num_experts: int, layer: int, s: float = 1.2, strength: float = 6.0, seed: int = 0) -> torch.Tensor:
+    """log-popularity bias: expert of Zipf rank r gets strength * log(p_r / p_max), p_r ~ r^-s, ranks permuted per layer."""
+    g = torch.Generator().manual_seed(seed * 1000 + layer)
+    perm = torch.randperm(num_experts, generator=g)
+    p = torch.arange(1, num_experts + 1, dtype=torch.float32) ** (-s)
+    b = torch.empty(num_experts)
+    b[perm] = strength * torch.log(p / p.max()) / math.log(num_experts)
+    return b
+
+
+def run(args, redundant: int, dynamic: bool):
+    from omni_infer_b200.accelerators.placement import OmniPlanner
+    from omni_infer_b200.parallel.parallel_state import get_parallel_state
+    mc = get_config("deepseek-v3", quantization="fp8_block") if args.config == "deepseek-v3" else \
+        get_config("small-deepseek", quantization="fp8_block" if torch.cuda.is_available() else "none")
+    if args.layers:
+        mc.num_hidden_layers = args.layers
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.config == "deepseek-v3" and world < 8:
+        mc.n_routed_experts = 32 * world          # per-rank slice of the full model (as bench.py does)
+        mc.n_group, mc.topk_group = 1, 1
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    pc = {"max_redundant_per_rank": redundant, "enable_dynamic": False, "apply_interval": 10 ** 9} if (redundant or dynamic) else None
+    bs = 128 if device == "cuda" else 16
+    per_req = args.input_len + args.steps + 16
+    ecfg = EngineConfig(model=mc.name, block_size=bs, num_kv_blocks=args.batch * (per_req // bs + 2) + 2, max_num_seqs=args.batch,
+                        max_model_len=per_req + bs, device=device, seed=3, placement_config=pc,
+                        enforce_eager=device == "cpu", decode_gear_list=[args.batch])
+    eng = EngineCore(ecfg, model_cfg=mc)
+    rank = get_parallel_state().rank
+    planner = eng.worker.runner.planner
+    moes = [m for m in eng.worker.runner.model.modules() if m.__class__.__name__ == "MoELayer"]
+    for m in moes:
+        m.routing_bias_override = zipf_bias(mc.n_routed_experts, m.moe_index).to(device)
+    g = torch.Generator().manual_seed(7 + rank)
+    sp = SamplingParams(max_tokens=10 ** 6, ignore_eos=True)
+    for _ in range(args.batch):
+        eng.add_request(torch.randint(0, mc.vocab_size, (args.input_len,), generator=g).tolist(), sp)
+    while eng.scheduler.num_waiting:
+        eng.step()
+    if planner is not None:
+        planner.sent_counts.zero_()
+    moves = 0
+    if device == "cuda":
+        torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tok0 = eng.metrics["generated_tokens"]
+    for i in range(args.steps):
+        eng.step()
+        if dynamic and planner is not None and (i + 1) % args.replace_every == 0:
+            planner.run_round()                   # synchronous round: collect, optimise, stage
+            moves += planner.apply_pending()      # between steps: copy staged experts, refresh the selector
+    if device == "cuda":
+        torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    stats = planner.load_stats() if planner is not None else _stats_without_planner(moes)
+    res = {"redundant_slots_per_rank": redundant, "dynamic": dynamic, "moves_applied": int(moves),
+           "tok_s_per_gpu": round((eng.metrics["generated_tokens"] - tok0) / dt, 1), **{k: round(v, 3) for k, v in stats.items()}}
+    if planner is not None:
+        OmniPlanner.cleanup()
+    return res
+
+
+def _stats_without_planner(moes):
+    return {"max_over_mean_rank_load": float("nan"), "max_over_mean_position_load": float("nan")}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="small", choices=["small", "deepseek-v3"])
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--input-len", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--redundant", type=int, default=2, help="redundant expert slots per rank in the second run")
+    ap.add_argument("--replace-every", type=int, default=16)
+    a = ap.parse_args()
+    out = {"baseline": run(a, 0, True), "with_placement": run(a, a.redundant, True)}
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

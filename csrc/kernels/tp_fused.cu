@@ -69,6 +69,7 @@ __global__ void ag_push_kernel(const AgPushParams p) {
 
 struct RsReduceParams {
   const __nv_bfloat16* slab;   // [world][rows_per_rank][ld]
+  long long parity_stride;     // elements; != 0: two halves used in turn, the current one is (round & 1)
   int world, rows, n, ld;
   long long src_pitch;         // elements between source slabs
   const int* flag;             // [world]
@@ -97,11 +98,12 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(const RsReduceParams p) 
   const int row = blockIdx.x;
   if (row >= p.rows) return;
   const int nv = p.n / 8;
+  const __nv_bfloat16* slab = p.slab + (p.parity_stride ? (long long)(*p.epoch & 1) * p.parity_stride : 0);
   float ssq = 0.f;
   for (int v = threadIdx.x; v < nv; v += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < p.world; ++s) {
-      const uint4 u = *reinterpret_cast<const uint4*>(p.slab + (long long)s * p.src_pitch + (long long)row * p.ld + v * 8);
+      const uint4 u = *reinterpret_cast<const uint4*>(slab + (long long)s * p.src_pitch + (long long)row * p.ld + v * 8);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -224,13 +226,27 @@ extern "C" int omni_ag_push(const void* src, int rows, int row_bytes, long long 
   return (int)cudaGetLastError();
 }
 
+// parity_bytes != 0: the slab has two halves that far apart, used in turn; the current one is (round & 1).
+extern "C" int omni_rs_reduce2(const void* slab, long long parity_bytes, int world, int rows, int n, int ld, long long src_pitch,
+                               const int* flag, const int* epoch, unsigned long long wait_ns, const void* residual_in,
+                               void* sum_out, const void* norm_weight, void* norm_out, float eps, void* status,
+                               cudaStream_t stream);
+
 extern "C" int omni_rs_reduce(const void* slab, int world, int rows, int n, int ld, long long src_pitch, const int* flag,
                               const int* epoch, unsigned long long wait_ns, const void* residual_in, void* sum_out,
                               const void* norm_weight, void* norm_out, float eps, void* status, cudaStream_t stream) {
-  if (world < 1 || world > 8 || rows < 0 || (n % 8) != 0 || (ld % 8) != 0 || (src_pitch % 8) != 0) return -1;
+  return omni_rs_reduce2(slab, 0, world, rows, n, ld, src_pitch, flag, epoch, wait_ns, residual_in, sum_out, norm_weight,
+                         norm_out, eps, status, stream);
+}
+
+extern "C" int omni_rs_reduce2(const void* slab, long long parity_bytes, int world, int rows, int n, int ld, long long src_pitch,
+                               const int* flag, const int* epoch, unsigned long long wait_ns, const void* residual_in,
+                               void* sum_out, const void* norm_weight, void* norm_out, float eps, void* status,
+                               cudaStream_t stream) {
+  if (world < 1 || world > 8 || rows < 0 || (n % 8) != 0 || (ld % 8) != 0 || (src_pitch % 8) != 0 || (parity_bytes % 16) != 0) return -1;
   if (norm_weight != nullptr && norm_out == nullptr) return -2;
   RsReduceParams p;
-  p.slab = (const __nv_bfloat16*)slab; p.world = world; p.rows = rows; p.n = n; p.ld = ld; p.src_pitch = src_pitch;
+  p.slab = (const __nv_bfloat16*)slab; p.parity_stride = parity_bytes / 2; p.world = world; p.rows = rows; p.n = n; p.ld = ld; p.src_pitch = src_pitch;
   p.flag = flag; p.epoch = epoch; p.wait_ns = wait_ns; p.residual_in = (const __nv_bfloat16*)residual_in;
   p.sum_out = (__nv_bfloat16*)sum_out; p.norm_weight = (const __nv_bfloat16*)norm_weight;
   p.norm_out = (__nv_bfloat16*)norm_out; p.eps = eps; p.status = (OmniStatus*)status;

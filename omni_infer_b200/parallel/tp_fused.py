@@ -56,7 +56,10 @@ class TpFusedContext:
         self.off_rs_flag = off; off = _align(off + 64)
         self.off_fin = off; self.fin_half = _align(self.max_tokens * self.max_k_bytes); off = _align(off + 2 * self.fin_half)
         self.off_fin_flag = off; off = _align(off + 64)
-        self.off_ctrl = off; off = _align(off + 64)     # [0] ag round, [1] ag done, [2] rs round, [3] rs done, [4] final round, [5] final done
+        self.ar_rows = min(self.max_tokens, 1024)         # all-reduce is for decode-sized messages
+        self.off_ar = off; self.ar_half = _align(self.world * self.ar_rows * self.max_n * 2); off = _align(off + 2 * self.ar_half)
+        self.off_ar_flag = off; off = _align(off + 64)
+        self.off_ctrl = off; off = _align(off + 64)     # [0] ag round, [1] ag done, [2] rs round, [3] rs done, [4] final round, [5] final done, [6] ar round, [7] ar done
         self.buf = SymmetricBuffer(off, group)
         self.buf.local_tensor(0, off).zero_()
         torch.cuda.synchronize()
@@ -68,6 +71,8 @@ class TpFusedContext:
         self._rs_done = lp + self.off_ctrl + 12
         self._fin_round = lp + self.off_ctrl + 16
         self._fin_done = lp + self.off_ctrl + 20
+        self._ar_round = lp + self.off_ctrl + 24
+        self._ar_done = lp + self.off_ctrl + 28
 
     # ------------------------------------------------------------------ helpers
     def rows_per_rank(self, total_rows: int) -> int:
@@ -163,6 +168,33 @@ class TpFusedContext:
         nat.add_launches(2)
         return out
 
+    # ------------------------------------------------------------------ one-shot all-reduce
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum of ``x`` [rows, n] (bf16) over the ranks, for decode-sized messages: every rank stores its rows into
+        its slot on every rank (two halves used in turn, chosen by the round counter in device memory), then each
+        rank adds the slots in fp32.  One NVLink crossing, no library call."""
+        rows, n = x.shape
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and n % 8 == 0 and n <= self.max_n and rows <= self.ar_rows
+        L = nat.lib()
+        slot_bytes = self.ar_rows * self.max_n * 2
+        gather = (ctypes.c_void_p * 8)(*[self._peer(r, self.off_ar) for r in range(self.world)] + [None] * (8 - self.world))
+        flags = (ctypes.c_void_p * 8)(*[self._peer(r, self.off_ar_flag + 4 * self.rank) for r in range(self.world)]
+                                      + [None] * (8 - self.world))
+        rc = L.omni_ag_push(nat.ptr(x), nat.c_int(rows), nat.c_int(n * 2), ctypes.c_longlong(n * 2),
+                            ctypes.c_longlong(self.rank * slot_bytes), ctypes.c_longlong(self.ar_half), nat.c_int(self.world),
+                            nat.c_int(self.rank), nat.c_int(1), gather, flags, ctypes.c_void_p(self._ar_round),
+                            ctypes.c_void_p(self._ar_done), nat.stream())
+        nat.check_rc(rc, "omni_ag_push(all_reduce)")
+        out = torch.empty_like(x)
+        rc = L.omni_rs_reduce2(ctypes.c_void_p(self.buf.local_ptr + self.off_ar), ctypes.c_longlong(self.ar_half),
+                               nat.c_int(self.world), nat.c_int(rows), nat.c_int(n), nat.c_int(n),
+                               ctypes.c_longlong(slot_bytes // 2), ctypes.c_void_p(self.buf.local_ptr + self.off_ar_flag),
+                               ctypes.c_void_p(self._ar_round), ctypes.c_ulonglong(self.wait_ns), None, nat.ptr(out), None, None,
+                               nat.c_float(0.0), nat.ptr(nat.status_buffer(x.device)), nat.stream())
+        nat.check_rc(rc, "omni_rs_reduce2")
+        nat.add_launches(2)
+        return out
+
     # ------------------------------------------------------------------ GEMM + reduce-scatter
     def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, *, w_scale=None, x_scale=None, residual=None,
                             norm_weight=None, eps: float = 1e-6):
@@ -233,6 +265,11 @@ class TpNcclBaseline:
         out = torch.empty(total_rows, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
         dist.all_gather_into_tensor(out, x_shard.contiguous(), group=self.group)
         return out
+
+    def all_reduce(self, x):
+        y = x.float()
+        dist.all_reduce(y, group=self.group)
+        return y.to(x.dtype)
 
     def gemm_reduce_scatter(self, x, w, *, w_scale=None, x_scale=None, residual=None, norm_weight=None, eps=1e-6):
         T = x.shape[0]

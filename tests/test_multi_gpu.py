@@ -88,6 +88,10 @@ for it in range(3):                          # several rounds: the round counter
     o8_f = ctx.gemm_reduce_scatter(aq, wo8, w_scale=wos8, x_scale=as_)
     o8_b = base.gemm_reduce_scatter(aq, wo8, w_scale=wos8, x_scale=as_)
     res[f"rs_fp8_{it}"] = rel(o8_f, o8_b)
+    # ---- one-shot all-reduce and plain all-gather of rows against NCCL
+    z = (torch.randn(64, H, device="cuda", generator=g) * 0.5).bfloat16()
+    res[f"ar_{it}"] = rel(ctx.all_reduce(z), base.all_reduce(z))
+    res[f"agrows_{it}"] = rel(ctx.all_gather_rows(x_sh, T), base.all_gather_rows(x_sh, T))
 torch.cuda.synchronize()
 nat.check_status()
 dist.barrier()
@@ -147,7 +151,7 @@ def test_tp2_fused_gemm_collectives_match_nccl():
     against NCCL collectives around the same GEMMs."""
     res = _run(2, {}, 29613, worker=TP_WORKER)
     for k, v in res.items():
-        tol = 0.0 if k.startswith("ag_x") else 2e-2
+        tol = 0.0 if k.startswith(("ag_x", "agrows")) else 2e-2
         assert v <= tol, (k, v, res)
 
 
