@@ -10,7 +10,8 @@
 // heads x 512 dims would fill all of TMEM, so two CTAs (blockIdx.x = 0/1) each own 256 output dims;
 // both compute the full score tile.  blockIdx.y splits the KV range (flash-decoding), blockIdx.z = q row.
 //
-// Per CTA: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = softmax / correction / epilogue.
+// Per CTA: warp 0 = TMA producer, warps 1 and 10 = MMA issuers (even / odd tiles), warps 2..9 = softmax /
+// correction / epilogue.
 //   S = Q K^T     A = Q  (smem, K-major, 9 chunks of 64 dims)   B = KV tile (smem, K-major)      -> TMEM
 //   P = softmax   written back to TMEM as packed bf16 (A operand of the second MMA)
 //   O += P V      A = P  (TMEM)                                  B = KV tile (same smem, MN-major) -> TMEM
@@ -62,7 +63,8 @@ constexpr int MLA_QS = 5;   // q chunks in shared memory: this CTA's four value-
 constexpr int MLA_SMEM =
     MLA_QS * MLA_Q_CHUNK + MLA_KV_BYTES + 1536 /*barriers + softmax exchange*/ + 1024 /*align*/;
 static_assert(MLA_SMEM <= 232448, "exceeds the 227 KB shared-memory limit of one CTA");
-constexpr int MLA_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two groups of four, 32 score columns each)
+// warp 0 TMA, warps 1 and 10 MMA issue (even and odd tiles), warps 2..9 softmax (two groups of four, 32 score columns each)
+constexpr int MLA_THREADS = 352;
 // TMEM columns: O accumulator | two S tiles (P, packed bf16, overwrites half of each group's own S columns) |
 // four packed-bf16 q chunks
 constexpr int TM_O = 0, TM_S = 256, TM_Q = 384, TM_COLS = 512;
@@ -108,6 +110,11 @@ struct MlaRing {   // position in the score-only ring / the value stages
   uint32_t slot = 0, par = 0, vstage = 0, vpar = 0;
   __device__ __forceinline__ void next_slot() { if (++slot == MLA_NSLOTS) { slot = 0; par ^= 1u; } }
   __device__ __forceinline__ void next_stage() { if (++vstage == MLA_VSTAGES) { vstage = 0; vpar ^= 1u; } }
+  __device__ __forceinline__ void skip_tile() {   // a tile that another issuer walks through
+    slot += 5;
+    if (slot >= MLA_NSLOTS) { slot -= MLA_NSLOTS; par ^= 1u; }
+    next_stage();
+  }
 };
 
 template <int HALF>
@@ -205,17 +212,23 @@ __device__ __forceinline__ bool mla_issue_scores(const MlaPipe& px, MlaRing& rg,
   return true;
 }
 
-__device__ __forceinline__ void mla_mma(const MlaPipe& px, int n) {
+// MMA issue for the tiles i = which, which + 2, ...  Issuing a score tile costs one lane about 1700 cycles (36
+// instructions of about 48), as much as the tensor pipe needs to execute a whole tile, so two warps share the work:
+// while one waits for the softmax of its tile and issues P V, the other issues the scores of the next tile.
+// Tile i uses S buffer i & 1, so each issuer always works on the same buffer.
+__device__ __forceinline__ void mla_mma(const MlaPipe& px, int n, const int which) {
   constexpr uint32_t idesc_pv = umma_idesc(128, 256, 1, 1, 0, 1);
-  MlaRing rg;                 // score stream (runs one tile ahead of the P V stream)
-  uint32_t pv_stage = 0;
-  if (!mla_issue_scores(px, rg, 0u)) return;
+  MlaRing rg;
+  if (which) rg.skip_tile();
+  uint32_t pv_stage = (uint32_t)which;       // i % MLA_VSTAGES
+  const uint32_t buf = (uint32_t)which;
   const uint64_t vdesc0 = umma_desc_mnmajor_sw128(px.kv_addr, MLA_CHUNK_BYTES, 1024);
 #pragma unroll 1
-  for (int i = 0; i < n; ++i) {
-    const uint32_t buf = (uint32_t)i & 1u;
-    // the next tile's scores run on the tensor pipe while the softmax warps work on this one
-    if (i + 1 < n && !mla_issue_scores(px, rg, buf ^ 1u)) return;
+  for (int i = which; i < n; i += 2) {
+    if (!mla_issue_scores(px, rg, buf)) return;
+    rg.skip_tile();
+    // the first P V zero-initialises the accumulator: the other issuer's first P V must enter the pipe after it
+    if (i == 1 && !mbar_wait(px.o_done, 0u, px.abort_flag, px.status, MS_O_DONE, 0)) return;
     // ---- O += P V
     if (!mbar_wait(&px.p_full[buf], ((uint32_t)i >> 1) & 1u, px.abort_flag, px.status, MS_P_FULL, i)) return;
     tc_fence_after();
@@ -230,10 +243,11 @@ __device__ __forceinline__ void mla_mma(const MlaPipe& px, int n) {
         umma_bf16_ts(TM_O, pbase + (k >> 1) * 32 + (k & 1) * 8, vd + (uint64_t)(k * 128), idesc_pv, 1u);
       umma_commit(&px.kv_empty[pv_stage]);
       umma_commit(px.o_done);
-      if (i == n - 1) umma_commit(px.o_final);
+      if (i + 2 >= n) umma_commit(px.o_final);   // this issuer's last tile
     }
     __syncwarp();
-    if (++pv_stage == MLA_VSTAGES) pv_stage = 0;
+    pv_stage += 2;
+    if (pv_stage >= MLA_VSTAGES) pv_stage -= MLA_VSTAGES;
   }
 }
 
@@ -251,7 +265,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint64_t* s_full = kv_empty + 9;                  // 2, one per S buffer
   uint64_t* p_full = s_full + 2;                    // 2
   uint64_t* o_done = p_full + 2;                    // 1
-  uint64_t* o_final = o_done + 1;                   // 1: all P V of this CTA retired
+  uint64_t* o_final = o_done + 1;                   // 1: all P V of this CTA retired (one arrival per issuer)
   uint64_t* qt_full = o_final + 1;                  // 1: q chunks written to TMEM
   uint32_t* tmem_slot = (uint32_t*)(qt_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -286,7 +300,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       mbar_init(&p_full[b], 8);
     }
     mbar_init(o_done, 1);
-    mbar_init(o_final, 1);
+    mbar_init(o_final, n >= 2 ? 2 : 1);   // the last P V of each issuer that has tiles
     mbar_init(qt_full, 8);
     *abort_flag = 0;
     *sm_counter = 0;
@@ -326,12 +340,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (half == 0) mla_producer<0>(px, &tmap_kv, bt, p.block_size, box_rows, kv_len, tile_begin, n);
         else mla_producer<1>(px, &tmap_kv, bt, p.block_size, box_rows, kv_len, tile_begin, n);
       }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 10) {
       const MlaPipe px{smem_u32(sq), smem_u32(skv), kv_full, kv_empty, s_full, p_full, o_done, o_final, abort_flag, p.status};
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, MS_Q, 0);
       if (ok) ok = mbar_wait(qt_full, 0, abort_flag, p.status, MS_QT, 0);
       tc_fence_after();
-      if (ok) mla_mma(px, n);
+      if (ok) mla_mma(px, n, warp == 1 ? 0 : 1);
     } else {
       // ------------------------------------------------------------ softmax / correction / epilogue
       // Eight warps: lane quadrant qd = warp & 3 selects 32 heads, group grp selects 32 of the 64 score
