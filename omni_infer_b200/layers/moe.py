@@ -20,6 +20,20 @@ from ..parallel import get_parallel_state
 from .common import Linear, SwiGLUMLP
 
 
+import os as _os
+
+MULTI_STREAM = _os.environ.get("OMNI_MOE_MULTI_STREAM", "1") == "1"
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device):
+    key = (device.type, device.index)
+    st = _SIDE_STREAMS.get(key)
+    if st is None:
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return st
+
+
 class MoEGate(nn.Module):
     def __init__(self, cfg, dtype, device=None):
         super().__init__()
@@ -104,15 +118,46 @@ class MoELayer(nn.Module):
         act = ops.gemm(xs, self.w13, seg_start=seg_start, seg_len=seg_len, epi="swiglu", t_hint=t_hint)
         return ops.gemm(act, self.w2, seg_start=seg_start, seg_len=seg_len, row_scale=row_w, t_hint=t_hint)
 
+    def _shared_on_side_stream(self, x, xq):
+        """The shared experts only depend on the layer input, so they run on a second stream beside the router,
+        the permutation and the dispatch (small kernels that leave most SMs idle); the routed path joins before it
+        adds their output.  Under CUDA-graph capture this becomes a parallel branch of the graph
+        (the reference overlaps the same work with its multi-stream option, omni/models/deepseek/deepseek_moe.py)."""
+        main = torch.cuda.current_stream()
+        side = _side_stream(x.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            shared = self.shared_experts(x, xq=xq)
+            done = torch.cuda.Event()
+            done.record(side)
+        shared.record_stream(main)
+        self._shared_done = done
+        return shared
+
+    def join_shared(self):
+        """Make the current stream wait for the shared-expert branch (no-op when it ran inline)."""
+        ev = getattr(self, "_shared_done", None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            self._shared_done = None
+
     def forward(self, x, xq=None, num_valid=None):
         T = x.shape[0]
         k = self.cfg.num_experts_per_tok
+        shared = None
+        if self.shared_experts is not None:
+            if x.is_cuda and MULTI_STREAM:
+                shared = self._shared_on_side_stream(x, xq)
+            else:
+                shared = self.shared_experts(x, xq=xq)
         ids, w = self.route(x, num_valid)
-        shared = self.shared_experts(x, xq=xq) if self.shared_experts is not None else None
         if self.ep_size == 1:
             perm = ops.moe_permute(x, ids, w, self.e_lo, self.slots_per_rank, quant=self.quant == "fp8_block")
             t_hint = max(16, (T * k + self.slots_per_rank - 1) // self.slots_per_rank)
             y = self.experts(perm.x, perm.x_scale, perm.seg_start, perm.seg_len, perm.row_w, t_hint)
+            self.join_shared()
             return ops.moe_combine(y, perm.row_of, T, k, shared=shared)
         if self.ep_ctx is not None and self.quant == "fp8_block":
             return self.ep_ctx.moe_forward(self, x, ids, w, shared)

@@ -159,7 +159,7 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
         if out is None:
             out = torch.empty(T, n_out, dtype=FP8, device=x.device)
         if out_scale is None:
-            out_scale = torch.zeros(n_out // 128, max(4, (T + 3) // 4 * 4), dtype=torch.float32, device=x.device)
+            out_scale = torch.empty(n_out // 128, max(4, (T + 3) // 4 * 4), dtype=torch.float32, device=x.device)
         out_f32 = 0
     else:
         if out is None:

@@ -128,13 +128,16 @@ def moe_permute(x, ids, w, e_lo, e_local, quant=False, align=16, capacity=None):
                           nat.ptr(total), nat.ptr(nat.status_buffer(dev)), nat.stream())
     nat.check_rc(rc, "omni_moe_align")
     row_of = torch.empty(n, dtype=torch.int32, device=dev)
-    row_w = torch.zeros(capacity, dtype=torch.float32, device=dev)
+    # Rows between a segment's length and its aligned end are never written and never read back: the GEMMs compute a
+    # token row only from that row's own inputs and store valid rows only, so the buffers need no zero fill (32 MB per
+    # layer at decode sizes).
+    row_w = torch.empty(capacity, dtype=torch.float32, device=dev)
     if quant:
-        xq = torch.zeros(capacity, H, dtype=FP8, device=dev)
-        xs = torch.zeros(H // 128, capacity, dtype=torch.float32, device=dev)
+        xq = torch.empty(capacity, H, dtype=FP8, device=dev)
+        xs = torch.empty(H // 128, capacity, dtype=torch.float32, device=dev)
         xp = None
     else:
-        xp = torch.zeros(capacity, H, dtype=x.dtype, device=dev)
+        xp = torch.empty(capacity, H, dtype=x.dtype, device=dev)
         xq = xs = None
     rc = L.omni_moe_scatter(nat.ptr(x), nat.c_int(H), nat.ptr(ids), nat.ptr(w), nat.ptr(pos), nat.c_int(n),
                             nat.c_int(k), nat.c_int(e_lo), nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(xp),

@@ -85,9 +85,9 @@ class EpContext:
         nat.check_rc(L.omni_moe_align(nat.ptr(r_ids), nat.c_int(n), nat.c_int(0), nat.c_int(S), nat.c_int(16),
                                       nat.c_int(capacity), nat.ptr(counts), nat.ptr(pos), nat.ptr(seg_start),
                                       nat.ptr(seg_len), nat.ptr(total), st, nat.stream()), "omni_moe_align")
-        xq = torch.zeros(capacity, self.H, dtype=FP8, device=dev)
-        xs = torch.zeros(self.H // 128, capacity, dtype=torch.float32, device=dev)
-        row_w = torch.zeros(capacity, dtype=torch.float32, device=dev)
+        xq = torch.empty(capacity, self.H, dtype=FP8, device=dev)     # padding rows are never read back (see ops.moe_permute)
+        xs = torch.empty(self.H // 128, capacity, dtype=torch.float32, device=dev)
+        row_w = torch.empty(capacity, dtype=torch.float32, device=dev)
         row_rank = torch.empty(capacity, dtype=torch.int32, device=dev)
         row_slot = torch.empty(capacity, dtype=torch.int32, device=dev)
         nat.check_rc(L.omni_ep_scatter_q(lay, peers, nat.ptr(r_ids), nat.ptr(pos), nat.ptr(r_w), nat.ptr(r_slot),
@@ -104,6 +104,7 @@ class EpContext:
                                             nat.c_int(S), nat.ptr(row_rank), nat.ptr(row_slot), nat.c_int(capacity),
                                             lay, peers, nat.stream()), "omni_ep_combine_send")
         out = torch.empty(T, self.H, dtype=x.dtype, device=dev)
+        layer.join_shared()
         nat.check_rc(L.omni_ep_combine_reduce(lay, peers, nat.ptr(ids), nat.c_int(T), nat.c_int(k), nat.ptr(shared),
                                               nat.ptr(out), ctypes.c_ulonglong(self.wait_ns), st, nat.stream()),
                      "omni_ep_combine_reduce")

@@ -51,5 +51,6 @@ def moe_forward_nccl(layer, x, ids, w, shared):
     out = torch.zeros(T, H, dtype=torch.float32, device=dev)
     out.index_add_(0, tok, ret.float())
     if shared is not None:
+        layer.join_shared()
         out += shared.float()
     return out.to(x.dtype)
