@@ -237,15 +237,48 @@ __global__ void moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, int H, c
   }
 }
 
+// same for rows that are already quantised (the e4m3 output of the preceding RMSNorm): a token routed to k local
+// experts is copied k times instead of being quantised k times.  xs_in is K-block major [H/128, xs_in_ld].
+__global__ void moe_scatter_q8_kernel(const uint8_t* __restrict__ xq_in, const float* __restrict__ xs_in, int xs_in_ld, int H,
+                                      const int* __restrict__ ids, const float* __restrict__ w, const int* __restrict__ pos,
+                                      int n, int top_k, int e_lo, const int* __restrict__ seg_start,
+                                      const int* __restrict__ seg_len, uint8_t* xq, float* xs, int xs_ld, int* row_of,
+                                      float* row_w, int* src_of) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= n) return;
+  const int ps = pos[i];
+  const int e = ids[i] - e_lo;
+  if (ps < 0 || ps >= seg_len[e]) {
+    if (lane == 0) row_of[i] = -1;
+    return;
+  }
+  const int row = seg_start[e] + ps;
+  const int t = i / top_k;
+  if (lane == 0) {
+    row_of[i] = row;
+    row_w[row] = w[i];
+    if (src_of) src_of[row] = i;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(xq_in + (size_t)t * H);
+  uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)row * H);
+  for (int c = lane; c < (H >> 4); c += 32) dst[c] = __ldg(src + c);
+  for (int b = lane; b < (H >> 7); b += 32) xs[(size_t)b * xs_ld + row] = __ldg(xs_in + (size_t)b * xs_in_ld + t);
+}
+
 // one CTA per token: fixed summation order over k (deterministic)
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int H, const int* __restrict__ row_of,
                                    const float* __restrict__ w, int top_k, const __nv_bfloat16* __restrict__ shared,
                                    __nv_bfloat16* out) {
+  // gridDim.y column parts per token: a decode batch has only a few hundred tokens, one CTA each would leave SMs idle
   const int t = blockIdx.x;
-  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+  const int part = (H / 8 + gridDim.y - 1) / gridDim.y * 8;
+  const int c_lo = blockIdx.y * part, c_hi = min(H, c_lo + part);
+  for (int c = c_lo + threadIdx.x * 8; c < c_hi; c += blockDim.x * 8) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 4
     for (int k = 0; k < top_k; ++k) {
       const int row = row_of[t * top_k + k];
       if (row < 0) continue;
@@ -313,13 +346,29 @@ extern "C" int omni_moe_scatter(const void* x, int H, const int* ids, const floa
   return (int)cudaGetLastError();
 }
 
+extern "C" int omni_moe_scatter_q8(const void* xq_in, const float* xs_in, int xs_in_ld, int H, const int* ids, const float* w,
+                                   const int* pos, int n, int top_k, int e_lo, const int* seg_start, const int* seg_len,
+                                   void* xq, float* xs, int xs_ld, int* row_of, float* row_w, int* src_of,
+                                   cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H % 128 != 0 || xq_in == nullptr || xs_in == nullptr || xq == nullptr || xs == nullptr) return -1;
+  const long long threads = (long long)n * 32;
+  moe_scatter_q8_kernel<<<(int)((threads + 255) / 256), 256, 0, stream>>>(
+      (const uint8_t*)xq_in, xs_in, xs_in_ld, H, ids, w, pos, n, top_k, e_lo, seg_start, seg_len, (uint8_t*)xq, xs, xs_ld,
+      row_of, row_w, src_of);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int omni_moe_combine(const void* y, int H, const int* row_of, const float* w, int T, int top_k,
                                 const void* shared, void* out, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H % 8 != 0) return -1;
-  int threads = H / 8;
+  int parts = 1;
+  while (T * parts < 1184 && parts < 8 && H / (parts * 2) >= 512) parts *= 2;   // aim at 8 CTAs per SM
+  int threads = (H / parts + 7) / 8;
+  threads = (threads + 31) / 32 * 32;
   if (threads > 256) threads = 256;
-  moe_combine_kernel<<<T, threads, 0, stream>>>((const __nv_bfloat16*)y, H, row_of, w, top_k,
+  moe_combine_kernel<<<dim3(T, parts), threads, 0, stream>>>((const __nv_bfloat16*)y, H, row_of, w, top_k,
                                                 (const __nv_bfloat16*)shared, (__nv_bfloat16*)out);
   return (int)cudaGetLastError();
 }

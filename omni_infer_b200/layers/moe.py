@@ -154,7 +154,7 @@ class MoELayer(nn.Module):
                 shared = self.shared_experts(x, xq=xq)
         ids, w = self.route(x, num_valid)
         if self.ep_size == 1:
-            perm = ops.moe_permute(x, ids, w, self.e_lo, self.slots_per_rank, quant=self.quant == "fp8_block")
+            perm = ops.moe_permute(x, ids, w, self.e_lo, self.slots_per_rank, quant=self.quant == "fp8_block", xq_in=xq)
             t_hint = max(16, (T * k + self.slots_per_rank - 1) // self.slots_per_rank)
             y = self.experts(perm.x, perm.x_scale, perm.seg_start, perm.seg_len, perm.row_w, t_hint)
             self.join_shared()

@@ -107,8 +107,10 @@ def moe_permute_ref(x, ids, w, e_lo, e_local, quant=False, align=16, capacity=No
                           torch.tensor([int(padded.sum())], dtype=torch.int32))
 
 
-def moe_permute(x, ids, w, e_lo, e_local, quant=False, align=16, capacity=None):
-    """Sort token rows by local expert.  ``capacity`` bounds the permuted buffer (default: worst case)."""
+def moe_permute(x, ids, w, e_lo, e_local, quant=False, align=16, capacity=None, xq_in=None):
+    """Sort token rows by local expert.  ``capacity`` bounds the permuted buffer (default: worst case).  With ``quant`` the
+    rows come out as e4m3 + scales; ``xq_in`` = (e4m3 rows, K-block-major scales) of ``x`` lets them be copied instead of
+    quantised once per routed expert."""
     if not x.is_cuda:
         return moe_permute_ref(x, ids, w, e_lo, e_local, quant, align, capacity)
     T, k = ids.shape
@@ -139,6 +141,13 @@ def moe_permute(x, ids, w, e_lo, e_local, quant=False, align=16, capacity=None):
     else:
         xp = torch.empty(capacity, H, dtype=x.dtype, device=dev)
         xq = xs = None
+    if quant and xq_in is not None:
+        rc = L.omni_moe_scatter_q8(nat.ptr(xq_in[0]), nat.ptr(xq_in[1]), nat.c_int(xq_in[1].shape[1]), nat.c_int(H),
+                                   nat.ptr(ids), nat.ptr(w), nat.ptr(pos), nat.c_int(n), nat.c_int(k), nat.c_int(e_lo),
+                                   nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(xq), nat.ptr(xs), nat.c_int(capacity),
+                                   nat.ptr(row_of), nat.ptr(row_w), nat.ptr(None), nat.stream())
+        nat.check_rc(rc, "omni_moe_scatter_q8")
+        return MoePermutation(xq, xs, seg_start, seg_len, row_of, row_w, total)
     rc = L.omni_moe_scatter(nat.ptr(x), nat.c_int(H), nat.ptr(ids), nat.ptr(w), nat.ptr(pos), nat.c_int(n),
                             nat.c_int(k), nat.c_int(e_lo), nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(xp),
                             nat.ptr(xq), nat.ptr(xs), nat.c_int(capacity), nat.ptr(row_of), nat.ptr(row_w),

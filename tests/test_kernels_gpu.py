@@ -167,6 +167,20 @@ def test_moe_permute_combine(quant):
                 assert abs(float(perm.row_w[r]) - float(w[t, j])) < 1e-6
             else:
                 assert r == -1
+    if quant:   # rows that arrive already quantised are copied, not re-quantised: identical bytes and scales
+        xq_in = ops.quant_fp8_block(x)
+        perm2 = M.moe_permute(x, ids, w, e_lo, e_local, quant=True, xq_in=xq_in)
+        assert perm2.seg_len.tolist() == lens and perm2.seg_start.tolist() == starts
+        ro2 = perm2.row_of.view(T, k)
+        for t_ in range(T):
+            for j in range(k):
+                r = int(ro2[t_, j])
+                if 0 <= int(ids[t_, j]) - e_lo < e_local:
+                    assert torch.equal(perm2.x.view(torch.uint8)[r], xq_in[0].view(torch.uint8)[t_])
+                    assert torch.equal(perm2.x_scale[:, r], xq_in[1][:, t_])
+                    assert abs(float(perm2.row_w[r]) - float(w[t_, j])) < 1e-6
+                else:
+                    assert r == -1
     y = torch.randn(perm.x.shape[0], H, device=DEV).bfloat16()
     shared = torch.randn(T, H, device=DEV).bfloat16()
     out = M.moe_combine(y, perm.row_of, T, k, w=w, shared=shared)
