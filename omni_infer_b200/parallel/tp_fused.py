@@ -34,7 +34,15 @@ def _align(x: int, a: int = 256) -> int:
 
 
 class TpFusedContext:
-    """Symmetric buffers + round counters for the fused tensor-parallel GEMMs of one process group."""
+    """Symmetric buffers + round counters for the fused tensor-parallel GEMMs of one process group.
+
+    Every rank must issue the same sequence of calls.  The gather buffer and the reduce-scatter slab are single
+    buffers: ``allgather_gemm`` and ``gemm_reduce_scatter`` calls must alternate (as they do in a layer: all-gather
+    before the attention block, reduce-scatter after it), because a reduce-scatter only completes on a rank when every
+    rank has finished the GEMM that read the previous gather, and the next push can only overtake a rank that has
+    finished its slab reduce.  ``all_gather_rows`` and ``all_reduce`` use their own buffers with two halves selected by
+    a round counter in device memory, so they may be called at any point of the sequence.  All counters and flags
+    live in device memory and advance inside the kernels: the calls can be captured in a CUDA graph and replayed."""
 
     def __init__(self, group, max_tokens: int, max_k_bytes: int, max_n: int, wait_ms: float = 2000.0):
         self.group = group
