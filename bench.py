@@ -243,7 +243,7 @@ def main():
                                        else f"ep{world}+dp{world}-attn"), "mtp_draft_layers": mtp,
                        "mtp_accepted_tokens_per_step": round(tokens_total / (args.steps * batch * (1 if args.attn_tp else world)), 3),
                        "accept_rate_forced": args.accept_rate, "layers": mc.num_hidden_layers,
-                       "routed_experts": mc.n_routed_experts, "cuda_graph": not args.eager,
+                       "routed_experts": mc.n_routed_experts, "cuda_graph": eng.worker.runner.graphs is not None,
                        "l2_policy": "inputs larger than L2 (>= 90 GB of weights and KV streamed per step)",
                        "ep_backend": args.ep_backend if world > 1 else "local", "load_s": round(load_s, 1)},
             "clocks": clocks,
