@@ -282,7 +282,7 @@ class TpNcclBaseline:
     def gemm_reduce_scatter(self, x, w, *, w_scale=None, x_scale=None, residual=None, norm_weight=None, eps=1e-6):
         T = x.shape[0]
         rpr = self.rows_per_rank(T)
-        part = ops.gemm(x, w, w_scale=w_scale, x_scale=x_scale, out_dtype=torch.bfloat16)
+        part = ops.gemm(x, w, w_scale=w_scale, x_scale=x_scale, out_dtype=torch.float32)   # partial sums stay fp32
         if dist.get_backend(self.group) == "gloo":
             full = part.float()
             dist.all_reduce(full, group=self.group)
