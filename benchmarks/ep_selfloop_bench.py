@@ -73,7 +73,7 @@ def main():
         evs = []
         for r in range(W):
             evs.append(timed("dispatch_send", lambda r=r: nat.check_rc(L.omni_ep_dispatch_send(
-                nat.ptr(xs_[r]), nat.ptr(ids_[r]), nat.ptr(ws_[r]), nat.c_int(T), nat.c_int(k), nat.c_int(S),
+                nat.ptr(xs_[r]), None, None, nat.c_int(0), nat.ptr(ids_[r]), nat.ptr(ws_[r]), nat.c_int(T), nat.c_int(k), nat.c_int(S),
                 ctypes.byref(lays[r]), peers, st, nat.stream()), "send")))
         state = []
         for r in range(W):

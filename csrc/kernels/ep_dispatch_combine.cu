@@ -3,8 +3,9 @@
 // Every rank owns one "symmetric" buffer allocated with cudaMalloc and opened by all peers through CUDA IPC;
 // `peer[r]` is rank r's buffer as seen from this rank, the layout (EpLayout) is identical on all ranks.
 //
-//   dispatch  omni_ep_dispatch_send   one warp per (token, k): quantises the token row to e4m3 with 1x128 scales
-//                                     and stores row + scales + {local expert, source slot, weight} straight into
+//   dispatch  omni_ep_dispatch_send   one warp per (token, k): quantises the token row to e4m3 with 1x128 scales (or
+//                                     copies the e4m3 form the caller already has, or the bf16 row for models with
+//                                     unquantised experts) and stores row + scales + {local expert, source slot, weight} straight into
 //                                     the destination rank's receive region over NVLink; the last block publishes
 //                                     per-destination counts and release-stores one flag per destination
 //             omni_ep_dispatch_recv   bounded wait on the flags of all sources, then compacts the received
@@ -34,6 +35,7 @@ struct EpLayout {
   int cap;              // receive rows reserved per source rank
   int H;                // hidden size (multiple of 128)
   int max_slots;        // T_max * top_k rows of the combine buffer
+  int payload;          // dispatched rows: 1 (or 0) = e4m3 with 1x128 scales, 2 = bf16 without scales
   // byte offsets inside the symmetric buffer
   long long off_recv_x, off_recv_s, off_recv_meta, off_recv_cnt, off_recv_flag, off_comb, off_comb_flag, off_ctrl;
 };
@@ -46,7 +48,8 @@ struct EpPeers { unsigned char* p[16]; };
 __device__ __forceinline__ void st_v4_u32(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 
 __global__ void __launch_bounds__(256)
-ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
+ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ xq_in,
+                        const float* __restrict__ xs_in, int xs_in_ld, const int* __restrict__ ids,
                         const float* __restrict__ w, int n_pairs, int top_k, int slots_per_rank, EpLayout L,
                         EpPeers peers, OmniStatus* status) {
   unsigned char* self = peers.p[L.rank];
@@ -67,9 +70,23 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ x, const int* __restri
     }
     unsigned char* dst = peers.p[d];
     const size_t rrow = (size_t)L.rank * L.cap + slot;
+    const int t = i / top_k;
+    if (L.payload == 2) {
+      // bf16 rows travel as they are (models whose experts are not quantised)
+      const uint4* s4 = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+      uint4* d4 = reinterpret_cast<uint4*>(dst + L.off_recv_x + rrow * (size_t)H * 2);
+      for (int c = lane; c < (H >> 3); c += 32) d4[c] = __ldg(s4 + c);
+    } else if (xq_in != nullptr) {
+      // the caller already has the e4m3 form of the rows (output of the preceding RMSNorm): copy, do not re-quantise
+      const uint4* s4 = reinterpret_cast<const uint4*>(xq_in + (size_t)t * H);
+      uint4* d4 = reinterpret_cast<uint4*>(dst + L.off_recv_x + rrow * H);
+      for (int c = lane; c < (H >> 4); c += 32) d4[c] = __ldg(s4 + c);
+      float* xs = reinterpret_cast<float*>(dst + L.off_recv_s) + rrow * nb;
+      for (int b = lane; b < nb; b += 32) xs[b] = __ldg(xs_in + (size_t)b * xs_in_ld + t);
+    } else {
     uint8_t* xq = dst + L.off_recv_x + rrow * H;
     float* xs = reinterpret_cast<float*>(dst + L.off_recv_s) + rrow * nb;
-    const __nv_bfloat16* src = x + (size_t)(i / top_k) * H;
+    const __nv_bfloat16* src = x + (size_t)t * H;
     for (int b = 0; b < nb; ++b) {
       const int c = b * 128 + lane * 4;
       uint2 raw = *reinterpret_cast<const uint2*>(src + c);
@@ -89,6 +106,7 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ x, const int* __restri
       for (int j = 0; j < 4; ++j) o[j] = f32_to_e4m3(v[j] * inv);
       *reinterpret_cast<uint32_t*>(xq + c) = *reinterpret_cast<uint32_t*>(o);   // 128 B per warp store
       if (lane == 0) xs[b] = sc;
+    }
     }
     if (lane == 0) {
       EpMeta mt;
@@ -167,11 +185,14 @@ __global__ void ep_scatter_q_kernel(EpLayout L, EpPeers peers, const int* __rest
   const int row = seg_start[e] + ps;
   unsigned char* self = peers.p[L.rank];
   const int H = L.H, nb = H >> 7;
-  const uint4* src = reinterpret_cast<const uint4*>(self + L.off_recv_x + (size_t)i * H);
-  uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)row * H);
-  for (int c = lane; c < (H >> 4); c += 32) dst[c] = src[c];
-  const float* ss = reinterpret_cast<const float*>(self + L.off_recv_s) + (size_t)i * nb;
-  for (int b = lane; b < nb; b += 32) xs[(size_t)b * xs_ld + row] = ss[b];
+  const size_t rb = (size_t)H * (L.payload == 2 ? 2 : 1);   // bytes per row
+  const uint4* src = reinterpret_cast<const uint4*>(self + L.off_recv_x + (size_t)i * rb);
+  uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)row * rb);
+  for (int c = lane; c < (int)(rb >> 4); c += 32) dst[c] = src[c];
+  if (L.payload != 2) {
+    const float* ss = reinterpret_cast<const float*>(self + L.off_recv_s) + (size_t)i * nb;
+    for (int b = lane; b < nb; b += 32) xs[(size_t)b * xs_ld + row] = ss[b];
+  }
   if (lane == 0) {
     row_w[row] = w[i];
     row_src_rank[row] = i / L.cap;
@@ -242,11 +263,15 @@ __global__ void ep_combine_reduce_kernel(EpLayout L, EpPeers peers, const int* _
   if (t >= n_tokens) return;   // an idle rank still waits above so that epochs stay in step
   const int H = L.H;
   const __nv_bfloat16* comb = reinterpret_cast<const __nv_bfloat16*>(self + L.off_comb);
-  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+  // gridDim.y column parts per token: a decode batch has only a few hundred tokens, one CTA each leaves SMs idle
+  const int part = (H / 8 + gridDim.y - 1) / gridDim.y * 8;
+  const int c_lo = blockIdx.y * part, c_hi = min(H, c_lo + part);
+  for (int c = c_lo + threadIdx.x * 8; c < c_hi; c += blockDim.x * 8) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     if (ok_all) {
+#pragma unroll 4
       for (int k = 0; k < top_k; ++k) {
         if (ids[t * top_k + k] < 0) continue;
         uint4 raw = *reinterpret_cast<const uint4*>(comb + (size_t)(t * top_k + k) * H + c);
@@ -299,16 +324,21 @@ static EpPeers make_peers(void* const* peer_ptrs, int world) {
   return p;
 }
 
-extern "C" int omni_ep_dispatch_send(const void* x, const int* ids, const float* w, int T, int top_k,
-                                     int slots_per_rank, const EpLayout* L, void* const* peer_ptrs, void* status,
-                                     cudaStream_t stream) {
+// x: bf16 rows [T, H].  xq_in / xs_in (optional, e4m3 payload only): the same rows already quantised, scales K-block
+// major [H/128, xs_in_ld]; then x may be null.
+extern "C" int omni_ep_dispatch_send(const void* x, const void* xq_in, const float* xs_in, int xs_in_ld, const int* ids,
+                                     const float* w, int T, int top_k, int slots_per_rank, const EpLayout* L,
+                                     void* const* peer_ptrs, void* status, cudaStream_t stream) {
   if (L->world > 16 || (L->H % 128) != 0) return -1;
+  if (x == nullptr && (xq_in == nullptr || L->payload == 2)) return -2;
+  if (xq_in != nullptr && xs_in == nullptr) return -2;
   const int n = T * top_k;
   int blocks = (n + 7) / 8;
   if (blocks < 1) blocks = 1;
   if (blocks > 592) blocks = 592;
-  ep_dispatch_send_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ids, w, n, top_k, slots_per_rank, *L,
-                                                      make_peers(peer_ptrs, L->world), (OmniStatus*)status);
+  ep_dispatch_send_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (const uint8_t*)xq_in, xs_in, xs_in_ld, ids, w, n,
+                                                      top_k, slots_per_rank, *L, make_peers(peer_ptrs, L->world),
+                                                      (OmniStatus*)status);
   return (int)cudaGetLastError();
 }
 
@@ -346,10 +376,13 @@ extern "C" int omni_ep_combine_send(const void* y, const int* total_rows, const 
 extern "C" int omni_ep_combine_reduce(const EpLayout* L, void* const* peer_ptrs, const int* ids, int T, int top_k,
                                       const void* shared, void* out, unsigned long long wait_ns, void* status,
                                       cudaStream_t stream) {
-  int threads = L->H / 8;
+  int parts = 1;
+  while (T * parts < 1184 && parts < 8 && L->H / (parts * 2) >= 512) parts *= 2;   // aim at 8 CTAs per SM
+  int threads = (L->H / parts + 7) / 8;
+  threads = (threads + 31) / 32 * 32;
   if (threads > 256) threads = 256;
   if (threads < 32) threads = 32;
-  ep_combine_reduce_kernel<<<T > 0 ? T : 1, threads, 0, stream>>>(*L, make_peers(peer_ptrs, L->world), ids, T, top_k,
+  ep_combine_reduce_kernel<<<dim3(T > 0 ? T : 1, parts), threads, 0, stream>>>(*L, make_peers(peer_ptrs, L->world), ids, T, top_k,
                                                       (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, wait_ns,
                                                       (OmniStatus*)status);
   return (int)cudaGetLastError();

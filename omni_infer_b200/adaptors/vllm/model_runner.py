@@ -115,8 +115,8 @@ class ModelRunner:
 
     def setup_expert_parallel(self) -> None:
         """With more than one rank the routed experts are sharded over all ranks.  Decode-sized batches go
-        through the fused NVLink dispatch/combine kernels (e4m3 rows), anything larger - or bf16 experts -
-        through the all-to-all baseline.  All ranks must take the same path in a step, so the choice is
+        through the fused NVLink dispatch/combine kernels (e4m3 rows for e4m3 experts, bf16 rows otherwise),
+        anything larger through the all-to-all baseline.  All ranks must take the same path in a step, so the choice is
         agreed on the host group before every forward (:meth:`_agree_ep_path`)."""
         self.ep_ctx = None
         ps = get_parallel_state()
@@ -127,10 +127,12 @@ class ModelRunner:
         for d in self.drafters:
             moe_layers += [m for m in d.modules() if m.__class__.__name__ == "MoELayer"]
         self._moe_layers = moe_layers
-        if (self.cfg.ep_backend == "fused" and self.device.type == "cuda" and cfg.quantization == "fp8_block"):
+        if (self.cfg.ep_backend == "fused" and self.device.type == "cuda" and cfg.dtype == "bfloat16"
+                and cfg.hidden_size % 128 == 0):
             from ...parallel.ep_fused import EpContext
+            # e4m3 experts: rows are dispatched quantised (1x128 scales); unquantised experts: bf16 rows as they are
             self.ep_ctx = EpContext(cfg.hidden_size, cfg.num_experts_per_tok, self.cfg.max_num_seqs * self.tpr,
-                                    wait_ms=self.cfg.ep_wait_ms)
+                                    wait_ms=self.cfg.ep_wait_ms, payload="fp8" if cfg.quantization == "fp8_block" else "bf16")
             self.ep_max_tokens = self.ep_ctx.max_tokens
 
     def _agree_ep_path(self, num_tokens: int) -> None:

@@ -159,7 +159,7 @@ class MoELayer(nn.Module):
             y = self.experts(perm.x, perm.x_scale, perm.seg_start, perm.seg_len, perm.row_w, t_hint)
             self.join_shared()
             return ops.moe_combine(y, perm.row_of, T, k, shared=shared)
-        if self.ep_ctx is not None and self.quant == "fp8_block":
-            return self.ep_ctx.moe_forward(self, x, ids, w, shared)
+        if self.ep_ctx is not None and x.is_cuda and x.dtype == torch.bfloat16:
+            return self.ep_ctx.moe_forward(self, x, ids, w, shared, xq=xq)
         from ..parallel.ep_nccl import moe_forward_nccl
         return moe_forward_nccl(self, x, ids, w, shared)

@@ -19,7 +19,7 @@ from .symmetric_heap import SymmetricBuffer
 
 class EpLayout(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("cap", ctypes.c_int), ("H", ctypes.c_int),
-                ("max_slots", ctypes.c_int), ("off_recv_x", ctypes.c_longlong), ("off_recv_s", ctypes.c_longlong),
+                ("max_slots", ctypes.c_int), ("payload", ctypes.c_int), ("off_recv_x", ctypes.c_longlong), ("off_recv_s", ctypes.c_longlong),
                 ("off_recv_meta", ctypes.c_longlong), ("off_recv_cnt", ctypes.c_longlong),
                 ("off_recv_flag", ctypes.c_longlong), ("off_comb", ctypes.c_longlong),
                 ("off_comb_flag", ctypes.c_longlong), ("off_ctrl", ctypes.c_longlong)]
@@ -30,7 +30,7 @@ def _align(x, a=256):
 
 
 class EpContext:
-    def __init__(self, hidden: int, top_k: int, max_tokens: int, wait_ms: float = 2000.0, group=None):
+    def __init__(self, hidden: int, top_k: int, max_tokens: int, wait_ms: float = 2000.0, group=None, payload: str = "fp8"):
         ps = get_parallel_state()
         self.world, self.rank = ps.world_size, ps.rank
         self.H, self.top_k, self.max_tokens = hidden, top_k, max_tokens
@@ -39,8 +39,10 @@ class EpContext:
         self.wait_ns = int(wait_ms * 1e6)
         W, cap, H = self.world, self.cap, hidden
         off = 0
-        lay = EpLayout(world=W, rank=self.rank, cap=cap, H=H, max_slots=self.max_slots)
-        lay.off_recv_x = off; off = _align(off + W * cap * H)
+        self.payload = payload                          # "fp8": e4m3 rows + 1x128 scales; "bf16": rows as they are
+        pb = 2 if payload == "bf16" else 1
+        lay = EpLayout(world=W, rank=self.rank, cap=cap, H=H, max_slots=self.max_slots, payload=pb)
+        lay.off_recv_x = off; off = _align(off + W * cap * H * pb)
         lay.off_recv_s = off; off = _align(off + W * cap * (H // 128) * 4)
         lay.off_recv_meta = off; off = _align(off + W * cap * 16)
         lay.off_recv_cnt = off; off = _align(off + 64 * 4)
@@ -56,8 +58,9 @@ class EpContext:
         self.buf.close()
 
     # ------------------------------------------------------------------ one MoE layer
-    def moe_forward(self, layer, x, ids, w, shared):
-        """x [T,H] bf16, ids/w [T,k] physical expert ids and routing weights -> [T,H]."""
+    def moe_forward(self, layer, x, ids, w, shared, xq=None):
+        """x [T,H] bf16, ids/w [T,k] physical expert ids and routing weights -> [T,H].  ``xq`` = (e4m3 rows, K-block-major
+        scales) of x, when the caller has them, is sent instead of quantising every (token, expert) pair again."""
         L = nat.lib()
         lay, peers = ctypes.byref(self.layout), self.buf.ptr_array
         T = x.shape[0]
@@ -65,8 +68,12 @@ class EpContext:
         dev = x.device
         assert T <= self.max_tokens, "batch exceeds the fused EP buffers; the runner must pick the NCCL path"
         st = nat.ptr(nat.status_buffer(dev))
-        nat.check_rc(L.omni_ep_dispatch_send(nat.ptr(x), nat.ptr(ids), nat.ptr(w), nat.c_int(T), nat.c_int(k),
-                                             nat.c_int(layer.slots_per_rank), lay, peers, st, nat.stream()),
+        fp8 = self.payload == "fp8"
+        assert fp8 == (layer.quant == "fp8_block"), "payload of the EP buffers does not match the expert weights"
+        pre = xq if (fp8 and xq is not None and T > 0) else None
+        nat.check_rc(L.omni_ep_dispatch_send(nat.ptr(x), nat.ptr(pre[0]) if pre else None, nat.ptr(pre[1]) if pre else None,
+                                             nat.c_int(pre[1].shape[1] if pre else 0), nat.ptr(ids), nat.ptr(w), nat.c_int(T),
+                                             nat.c_int(k), nat.c_int(layer.slots_per_rank), lay, peers, st, nat.stream()),
                      "omni_ep_dispatch_send")
         n = self.world * self.cap
         r_ids = torch.empty(n, dtype=torch.int32, device=dev)
@@ -85,8 +92,9 @@ class EpContext:
         nat.check_rc(L.omni_moe_align(nat.ptr(r_ids), nat.c_int(n), nat.c_int(0), nat.c_int(S), nat.c_int(16),
                                       nat.c_int(capacity), nat.ptr(counts), nat.ptr(pos), nat.ptr(seg_start),
                                       nat.ptr(seg_len), nat.ptr(total), st, nat.stream()), "omni_moe_align")
-        xq = torch.empty(capacity, self.H, dtype=FP8, device=dev)     # padding rows are never read back (see ops.moe_permute)
-        xs = torch.empty(self.H // 128, capacity, dtype=torch.float32, device=dev)
+        # padding rows are never read back (see ops.moe_permute)
+        xq = torch.empty(capacity, self.H, dtype=FP8 if fp8 else x.dtype, device=dev)
+        xs = torch.empty(self.H // 128, capacity, dtype=torch.float32, device=dev) if fp8 else None
         row_w = torch.empty(capacity, dtype=torch.float32, device=dev)
         row_rank = torch.empty(capacity, dtype=torch.int32, device=dev)
         row_slot = torch.empty(capacity, dtype=torch.int32, device=dev)
@@ -95,11 +103,7 @@ class EpContext:
                                          nat.c_int(capacity), nat.ptr(row_w), nat.ptr(row_rank), nat.ptr(row_slot),
                                          nat.stream()), "omni_ep_scatter_q")
         t_hint = max(32, (self.max_tokens * k + S - 1) // S if T == 0 else (T * k * 1 + S - 1) // S)
-        if layer.quant == "fp8_block":
-            y = layer.experts(xq, xs, seg_start, seg_len, row_w, t_hint)
-        else:
-            xb = ops.dequant_act_ref(xq, xs).to(x.dtype) if False else None   # bf16 experts take bf16 rows
-            raise NotImplementedError("the fused EP path carries e4m3 rows; bf16 expert weights use the NCCL path")
+        y = layer.experts(xq, xs, seg_start, seg_len, row_w, t_hint)
         nat.check_rc(L.omni_ep_combine_send(nat.ptr(y), nat.ptr(total), nat.ptr(seg_start), nat.ptr(seg_len),
                                             nat.c_int(S), nat.ptr(row_rank), nat.ptr(row_slot), nat.c_int(capacity),
                                             lay, peers, nat.stream()), "omni_ep_combine_send")

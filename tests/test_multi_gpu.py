@@ -20,7 +20,7 @@ from omni_infer_b200.engine.request import SamplingParams
 from omni_infer_b200.models.config import get_config
 from omni_infer_b200.ops import _native as nat
 backend = os.environ.get("EP_BACKEND", "fused")
-mc = get_config("small-deepseek", quantization="fp8_block", num_nextn_predict_layers=1)
+mc = get_config("small-deepseek", quantization=os.environ.get("QUANT", "fp8_block"), num_nextn_predict_layers=1)
 eng = EngineCore(EngineConfig(block_size=128, num_kv_blocks=24, max_model_len=512, max_num_seqs=4,
                               num_speculative_tokens=int(os.environ.get("MTP", "0")), ep_backend=backend, seed=7,
                               attn_tp=os.environ.get("ATTN_TP", "0") == "1", tp_backend=os.environ.get("TP_BACKEND", "fused")),
@@ -168,3 +168,13 @@ def test_tp2_attention_with_ep2_moe_matches_single_rank():
     mtp1 = _run(1, {"MTP": "1"}, 0)
     mtp2 = _run(2, {"MTP": "1", "ATTN_TP": "1"}, 29616)
     assert _agreement(mtp2, mtp1) > 0.6
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ep2_fused_bf16_experts_match_single_rank():
+    """Unquantised (bf16) experts: the fused dispatch carries bf16 rows; same tokens as one GPU and as the NCCL path."""
+    single = _run(1, {"QUANT": "none"}, 0)
+    fused = _run(2, {"QUANT": "none", "EP_BACKEND": "fused"}, 29618)
+    nccl = _run(2, {"QUANT": "none", "EP_BACKEND": "nccl"}, 29619)
+    assert _agreement(fused, single) > 0.6
+    assert _agreement(fused, nccl) > 0.6
