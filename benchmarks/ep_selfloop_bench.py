@@ -33,17 +33,20 @@ def main():
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--experts-per-rank", type=int, default=32)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--prequant", action="store_true", help="hand already quantised rows to the dispatch (copy instead of quantise)")
+    ap.add_argument("--payload", default="fp8", choices=["fp8", "bf16"], help="what the dispatched rows carry")
     a = ap.parse_args()
     W, T, H, k, S = a.world, a.tokens, a.hidden, a.topk, a.experts_per_rank
     dev = torch.device("cuda")
     L = nat.lib()
     cap = T * k
+    pb = 2 if a.payload == "bf16" else 1
     lays = []
     off = 0
     for r in range(W):
-        lay = EpLayout(world=W, rank=r, cap=cap, H=H, max_slots=T * k)
+        lay = EpLayout(world=W, rank=r, cap=cap, H=H, max_slots=T * k, payload=pb)
         off = 0
-        for name, size in (("off_recv_x", W * cap * H), ("off_recv_s", W * cap * (H // 128) * 4), ("off_recv_meta", W * cap * 16),
+        for name, size in (("off_recv_x", W * cap * H * pb), ("off_recv_s", W * cap * (H // 128) * 4), ("off_recv_meta", W * cap * 16),
                            ("off_recv_cnt", 256), ("off_recv_flag", 256), ("off_comb", T * k * H * 2), ("off_comb_flag", 256),
                            ("off_ctrl", 256)):
             setattr(lay, name, off)
@@ -56,6 +59,7 @@ def main():
     xs_ = [(torch.randn(T, H, device=dev, generator=g) * 0.5).bfloat16() for _ in range(W)]
     ids_ = [torch.stack([torch.randperm(W * S, device=dev, generator=g)[:k] for _ in range(T)]).int().contiguous() for _ in range(W)]
     ws_ = [torch.rand(T, k, device=dev, generator=g).float().contiguous() for _ in range(W)]
+    pre = [ops.quant_fp8_block(x) for x in xs_] if (a.prequant and pb == 1) else None
     st = nat.ptr(nat.status_buffer(dev))
     n = W * cap
     capacity = (n + S * 15 + 15) // 16 * 16
@@ -73,7 +77,8 @@ def main():
         evs = []
         for r in range(W):
             evs.append(timed("dispatch_send", lambda r=r: nat.check_rc(L.omni_ep_dispatch_send(
-                nat.ptr(xs_[r]), None, None, nat.c_int(0), nat.ptr(ids_[r]), nat.ptr(ws_[r]), nat.c_int(T), nat.c_int(k), nat.c_int(S),
+                nat.ptr(xs_[r]), nat.ptr(pre[r][0]) if pre else None, nat.ptr(pre[r][1]) if pre else None,
+                nat.c_int(pre[r][1].shape[1] if pre else 0), nat.ptr(ids_[r]), nat.ptr(ws_[r]), nat.c_int(T), nat.c_int(k), nat.c_int(S),
                 ctypes.byref(lays[r]), peers, st, nat.stream()), "send")))
         state = []
         for r in range(W):
@@ -88,7 +93,8 @@ def main():
             evs.append(timed("align", lambda: nat.check_rc(L.omni_moe_align(
                 nat.ptr(r_ids), nat.c_int(n), nat.c_int(0), nat.c_int(S), nat.c_int(16), nat.c_int(capacity), nat.ptr(counts),
                 nat.ptr(pos), nat.ptr(seg_start), nat.ptr(seg_len), nat.ptr(total), st, nat.stream()), "align")))
-            xq = torch.empty(capacity, H, dtype=FP8, device=dev); xsc = torch.empty(H // 128, capacity, dtype=torch.float32, device=dev)
+            xq = torch.empty(capacity, H, dtype=FP8 if pb == 1 else torch.bfloat16, device=dev)
+            xsc = torch.empty(H // 128, capacity, dtype=torch.float32, device=dev)
             row_w = torch.empty(capacity, dtype=torch.float32, device=dev)
             row_rank = torch.empty(capacity, dtype=torch.int32, device=dev); row_slot = torch.empty(capacity, dtype=torch.int32, device=dev)
             evs.append(timed("scatter_q", lambda: nat.check_rc(L.omni_ep_scatter_q(
@@ -96,7 +102,8 @@ def main():
                 nat.ptr(seg_len), nat.ptr(xq), nat.ptr(xsc), nat.c_int(capacity), nat.ptr(row_w), nat.ptr(row_rank),
                 nat.ptr(row_slot), nat.stream()), "scatter")))
             # identity experts: y = w * dequant(x); rows between segments are never sent back
-            y = (ops.dequant_act_ref(xq, xsc) * row_w.unsqueeze(1)).to(torch.bfloat16)
+            xf = ops.dequant_act_ref(xq, xsc) if pb == 1 else xq.float()
+            y = (xf * row_w.unsqueeze(1)).to(torch.bfloat16)
             state.append((y, total, seg_start, seg_len, row_rank, row_slot))
         for r in range(W):
             y, total, seg_start, seg_len, row_rank, row_slot = state[r]
@@ -116,12 +123,15 @@ def main():
             for name, e0, e1 in evs:
                 times[name].append(e0.elapsed_time(e1) * 1e3)
     # check rank 0's result
-    xq0, xs0 = ops.quant_fp8_block(xs_[0])
-    ref = ops.dequant_act_ref(xq0, xs0) * ws_[0].sum(1, keepdim=True)
+    if pb == 1:
+        xq0, xs0 = ops.quant_fp8_block(xs_[0])
+        ref = ops.dequant_act_ref(xq0, xs0) * ws_[0].sum(1, keepdim=True)
+    else:
+        ref = xs_[0].float() * ws_[0].sum(1, keepdim=True)
     err = float((outs[0].float() - ref).abs().max() / ref.abs().max())
     med = {m: round(sorted(v)[len(v) // 2], 1) for m, v in times.items()}
-    row_bytes = H + (H // 128) * 4 + 16
-    print(json.dumps({"emulated_world": W, "tokens_per_rank": T, "hidden": H, "top_k": k, "us_per_launch_median": med,
+    row_bytes = (H + (H // 128) * 4 if pb == 1 else 2 * H) + 16
+    print(json.dumps({"emulated_world": W, "tokens_per_rank": T, "hidden": H, "top_k": k, "payload": a.payload, "prequantised_input": bool(pre), "us_per_launch_median": med,
                       "dispatch_payload_MB_per_rank": round(T * k * row_bytes / 1e6, 1),
                       "combine_payload_MB_per_rank": round(T * k * H * 2 / 1e6, 1), "rel_err_vs_reference": round(err, 4)}))
     assert err < 2e-2, err
