@@ -137,7 +137,7 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __re
   }
 }
 
-// One block.  Waits for every source, then writes ids_out[src*cap + j] = local expert (or -1), w_out, slot_out.
+// Waits for every source, then writes ids_out[src*cap + j] = local expert (or -1), w_out, slot_out.
 __global__ void __launch_bounds__(1024)
 ep_dispatch_recv_kernel(EpLayout L, EpPeers peers, int* ids_out, float* w_out, int* src_slot_out, int* counts_out,
                         unsigned long long wait_ns, OmniStatus* status) {
@@ -151,11 +151,13 @@ ep_dispatch_recv_kernel(EpLayout L, EpPeers peers, int* ids_out, float* w_out, i
   if ((int)threadIdx.x < L.world) {
     const bool ok = flag_wait_ge(&flag[threadIdx.x], epoch, wait_ns, status, 201, threadIdx.x);
     n_from[threadIdx.x] = ok ? ld_relaxed_sys(&cnt[threadIdx.x]) : 0;
-    if (counts_out) counts_out[threadIdx.x] = n_from[threadIdx.x];
+    if (counts_out && blockIdx.x == 0) counts_out[threadIdx.x] = n_from[threadIdx.x];
   }
   __syncthreads();
+  // every block waits for the flags itself (they are already set for all but the first to arrive), then takes its
+  // share of the world * cap metadata slots
   const EpMeta* meta = reinterpret_cast<const EpMeta*>(self + L.off_recv_meta);
-  for (int i = threadIdx.x; i < L.world * L.cap; i += blockDim.x) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < L.world * L.cap; i += gridDim.x * blockDim.x) {
     const int s = i / L.cap, j = i - s * L.cap;
     if (j < n_from[s]) {
       const EpMeta m = meta[i];
@@ -225,6 +227,7 @@ ep_combine_send_kernel(const __nv_bfloat16* __restrict__ y, const int* __restric
     if (s < 0 || s >= L.world || slot < 0 || slot >= L.max_slots) continue;
     const uint4* src = reinterpret_cast<const uint4*>(y + (size_t)row * H);
     uint4* dst = reinterpret_cast<uint4*>(peers.p[s] + L.off_comb + (size_t)slot * H * 2);
+#pragma unroll 4
     for (int c = lane; c < (H >> 3); c += 32) dst[c] = src[c];
   }
   __threadfence_system();
@@ -345,7 +348,10 @@ extern "C" int omni_ep_dispatch_send(const void* x, const void* xq_in, const flo
 extern "C" int omni_ep_dispatch_recv(const EpLayout* L, void* const* peer_ptrs, int* ids_out, float* w_out,
                                      int* src_slot_out, int* counts_out, unsigned long long wait_ns, void* status,
                                      cudaStream_t stream) {
-  ep_dispatch_recv_kernel<<<1, 1024, 0, stream>>>(*L, make_peers(peer_ptrs, L->world), ids_out, w_out, src_slot_out,
+  int blocks = (L->world * L->cap + 4095) / 4096;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 32) blocks = 32;
+  ep_dispatch_recv_kernel<<<blocks, 1024, 0, stream>>>(*L, make_peers(peer_ptrs, L->world), ids_out, w_out, src_slot_out,
                                                   counts_out, wait_ns, (OmniStatus*)status);
   return (int)cudaGetLastError();
 }
