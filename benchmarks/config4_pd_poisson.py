@@ -61,8 +61,23 @@ def main():
             kv_transfer_config={"kv_role": role, "engine_id": name, "endpoint": f"inproc://{name}", "sync_timeout_s": 20.0,
                                 "retries": 3, "retry_wait_s": 0.5}), model_cfg=copy.deepcopy(mc))
 
-    P = engine("kv_producer", "prefill0", 8, 16 * (a.input_len // bs + 2) + 2)
-    D = engine("kv_consumer", "decode0", a.max_decode_batch, live * (per_req // bs + 2) + 2)
+    p_blocks = 16 * (a.input_len // bs + 2) + 2
+    P = engine("kv_producer", "prefill0", 8, p_blocks)
+    d_blocks = live * (per_req // bs + 2) + 2
+    d_seqs = a.max_decode_batch
+    if device == "cuda":
+        # both engines hold the weights; keep the decode cache inside what is left of the device (never size a run so that
+        # it can exhaust memory)
+        wbytes = sum(q.numel() * q.element_size() for q in P.worker.runner.model.parameters())
+        per_block = P.worker.runner.kv_bytes_per_block()
+        total = torch.cuda.get_device_properties(0).total_memory
+        room = int(total * 0.88) - 2 * wbytes - p_blocks * per_block
+        fit = max(0, room // per_block)
+        if fit < d_blocks:
+            d_seqs = max(1, int((fit - 2) // (per_req // bs + 2)) - 8)
+            d_blocks = (d_seqs + 8) * (per_req // bs + 2) + 2
+            print(f"decode batch reduced to {d_seqs} sequences to fit the device", file=sys.stderr)
+    D = engine("kv_consumer", "decode0", d_seqs, d_blocks)
     g = torch.Generator().manual_seed(0)
     gaps = torch.empty(n_req).exponential_(a.rate, generator=g).tolist()
     arrivals, t = [], 0.0
