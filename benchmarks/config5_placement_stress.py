@@ -46,7 +46,8 @@ def run(args, redundant: int, dynamic: bool):
         mc.n_routed_experts = 32 * world          # per-rank slice of the full model (as bench.py does)
         mc.n_group, mc.topk_group = 1, 1
     device = "cuda" if torch.cuda.is_available() else "cpu"
-    pc = {"max_redundant_per_rank": redundant, "enable_dynamic": False, "apply_interval": 10 ** 9} if (redundant or dynamic) else None
+    # the baseline run also gets a planner (identity placement, never re-placed) so that both runs count loads the same way
+    pc = {"max_redundant_per_rank": redundant, "enable_dynamic": False, "apply_interval": 10 ** 9}
     bs = 128 if device == "cuda" else 16
     per_req = args.input_len + args.steps + 16
     ecfg = EngineConfig(model=mc.name, block_size=bs, num_kv_blocks=args.batch * (per_req // bs + 2) + 2, max_num_seqs=args.batch,
@@ -101,7 +102,7 @@ def main():
     ap.add_argument("--redundant", type=int, default=2, help="redundant expert slots per rank in the second run")
     ap.add_argument("--replace-every", type=int, default=16)
     a = ap.parse_args()
-    out = {"baseline": run(a, 0, True), "with_placement": run(a, a.redundant, True)}
+    out = {"baseline": run(a, 0, False), "with_placement": run(a, a.redundant, True)}
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(out))
 

@@ -70,12 +70,14 @@ class EngineCore:
         elif cfg.kv_transfer_config:
             from ..accelerators.pd import create_connectors
             sched_conn, worker_conn = create_connectors(cfg.kv_transfer_config, block_size=cfg.block_size)
-        if planner is None and cfg.placement_config:
-            from ..accelerators.placement import OmniPlanner
-            planner = OmniPlanner.from_config(cfg.placement_config, self.model_cfg)
         self.worker = B200Worker(self.model_cfg, rc, tp_size=cfg.tp_size, device=cfg.device, planner=planner,
                                  kv_connector=worker_conn)
         self.worker.init_device()
+        if planner is None and cfg.placement_config:
+            # the planner sizes its slot tables from the world size, so it is built after the process group exists
+            from ..accelerators.placement import OmniPlanner
+            planner = OmniPlanner.from_config(cfg.placement_config, self.model_cfg)
+            self.worker.planner = self.worker.runner.planner = planner
         self.worker.load_model(weights, seed=cfg.seed)
         n_blocks = self.worker.determine_available_memory()
         self.worker.initialize_cache(n_blocks)
