@@ -27,3 +27,16 @@ def test_placement_stress_workload_reports_load_ratios():
     for arm in ("baseline", "with_placement"):
         assert out[arm]["tok_s_per_gpu"] > 0
     assert out["with_placement"]["max_over_mean_position_load"] >= 1.0
+
+
+def test_placement_stress_two_ranks_moves_experts_and_evens_rank_load():
+    """Two gloo ranks: the planner must size its tables from the real world size, and a dynamic round must lower the
+    rank-load imbalance of the Zipf-biased router."""
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                          "127.0.0.1", "--master-port", "29655", "benchmarks/config5_placement_stress.py", "--config", "small",
+                          "--steps", "32", "--batch", "4", "--input-len", "16", "--redundant", "2", "--replace-every", "8"],
+                         capture_output=True, text=True, timeout=600, env=ENV, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["baseline"]["moves_applied"] == 0 and out["with_placement"]["moves_applied"] > 0
+    assert out["with_placement"]["max_over_mean_rank_load"] < out["baseline"]["max_over_mean_rank_load"]
