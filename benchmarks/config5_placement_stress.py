@@ -67,22 +67,37 @@ def run(args, redundant: int, dynamic: bool):
         eng.step()
     if planner is not None:
         planner.sent_counts.zero_()
-    moves = 0
+    moves, rounds, round_s, snap = 0, 0, 0.0, None
     if device == "cuda":
         torch.cuda.synchronize()
     t0 = time.perf_counter()
     tok0 = eng.metrics["generated_tokens"]
     for i in range(args.steps):
         eng.step()
+        if planner is not None and (i + 1) % args.replace_every == 0 and i + 1 < args.steps:
+            snap = planner.sent_counts.clone()    # the last window starts at the last round boundary, in both arms
         if dynamic and planner is not None and (i + 1) % args.replace_every == 0:
+            if device == "cuda":
+                torch.cuda.synchronize()
+            tr = time.perf_counter()
             planner.run_round()                   # synchronous round: collect, optimise, stage
             moves += planner.apply_pending()      # between steps: copy staged experts, refresh the selector
+            if device == "cuda":
+                torch.cuda.synchronize()
+            round_s += time.perf_counter() - tr
+            rounds += 1
     if device == "cuda":
         torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     stats = planner.load_stats() if planner is not None else _stats_without_planner(moes)
     res = {"redundant_slots_per_rank": redundant, "dynamic": dynamic, "moves_applied": int(moves),
-           "tok_s_per_gpu": round((eng.metrics["generated_tokens"] - tok0) / dt, 1), **{k: round(v, 3) for k, v in stats.items()}}
+           "tok_s_per_gpu": round((eng.metrics["generated_tokens"] - tok0) / dt, 1),
+           # a round runs synchronously here; in serving it runs on the planner's thread once a minute
+           "tok_s_per_gpu_outside_rounds": round((eng.metrics["generated_tokens"] - tok0) / max(dt - round_s, 1e-9), 1),
+           "rounds": rounds, "ms_per_round": round(round_s / rounds * 1e3, 1) if rounds else None,
+           **{k: round(v, 3) for k, v in stats.items()}}
+    if planner is not None and snap is not None:
+        res["last_window"] = {k: round(v, 3) for k, v in planner.load_stats(since=snap).items()}
     if planner is not None:
         OmniPlanner.cleanup()
     return res

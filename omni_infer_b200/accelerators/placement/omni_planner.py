@@ -252,9 +252,10 @@ class OmniPlanner(metaclass=_Singleton):
         names = ("layer", "type", "source_rank", "source_expert", "source_pos", "target_rank", "target_expert", "target_pos")
         return [dict(zip(names, buf[8 * i:8 * i + 8])) for i in range(n)]
 
-    def load_stats(self) -> dict:
-        """max / mean tokens per rank and per expert position over the accumulated counters (placement gauges)."""
-        c = self.sent_counts.float()
+    def load_stats(self, since: Optional[torch.Tensor] = None) -> dict:
+        """max / mean tokens per rank and per expert position over the accumulated counters (placement gauges);
+        ``since`` = an earlier copy of ``sent_counts`` restricts the gauges to what was counted after it."""
+        c = (self.sent_counts if since is None else self.sent_counts - since).float()
         if self.world > 1 and dist.is_initialized():
             c = c.clone()
             dist.all_reduce(c, group=get_parallel_state().group("world").group)
