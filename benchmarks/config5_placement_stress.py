@@ -11,7 +11,6 @@ The reference's counterpart is its placement optimiser fed by recorded activatio
 (omni/accelerators/placement/omni_placement/omni_planner.py, cpp/placement_manager.cpp)."""
 import argparse
 import json
-import math
 import os
 import sys
 import time
@@ -22,16 +21,6 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore  # noqa: E402
 from omni_infer_b200.engine.request import SamplingParams  # noqa: E402
 from omni_infer_b200.models.config import get_config  # noqa: E402
-
-
-def zipf_bias(num_experts: int, layer: int, s: float = 1.2, strength: float = 6.0, seed: int = 0) -> torch.Tensor:
-    """log-popularity bias: expert of Zipf rank r gets strength * log(p_r / p_max), p_r ~ r^-s, ranks permuted per layer."""
-    g = torch.Generator().manual_seed(seed * 1000 + layer)
-    perm = torch.randperm(num_experts, generator=g)
-    p = torch.arange(1, num_experts + 1, dtype=torch.float32) ** (-s)
-    b = torch.empty(num_experts)
-    b[perm] = strength * torch.log(p / p.max()) / math.log(num_experts)
-    return b
 
 
 def run(args, redundant: int, dynamic: bool):
@@ -46,6 +35,7 @@ def run(args, redundant: int, dynamic: bool):
         mc.n_routed_experts = 32 * world          # per-rank slice of the full model (as bench.py does)
         mc.n_group, mc.topk_group = 1, 1
     device = "cuda" if torch.cuda.is_available() else "cpu"
+    mc.router_skew = {"s": 1.2, "strength": 6.0, "seed": 0}     # part of the model, so captured decode graphs include it
     # the baseline run also gets a planner (identity placement, never re-placed) so that both runs count loads the same way
     pc = {"max_redundant_per_rank": redundant, "enable_dynamic": False, "apply_interval": 10 ** 9}
     bs = 128 if device == "cuda" else 16
@@ -56,9 +46,6 @@ def run(args, redundant: int, dynamic: bool):
     eng = EngineCore(ecfg, model_cfg=mc)
     rank = get_parallel_state().rank
     planner = eng.worker.runner.planner
-    moes = [m for m in eng.worker.runner.model.modules() if m.__class__.__name__ == "MoELayer"]
-    for m in moes:
-        m.routing_bias_override = zipf_bias(mc.n_routed_experts, m.moe_index).to(device)
     g = torch.Generator().manual_seed(7 + rank)
     sp = SamplingParams(max_tokens=10 ** 6, ignore_eos=True)
     for _ in range(args.batch):
@@ -89,7 +76,10 @@ def run(args, redundant: int, dynamic: bool):
     if device == "cuda":
         torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    stats = planner.load_stats() if planner is not None else _stats_without_planner(moes)
+    if device == "cuda":
+        from omni_infer_b200.ops import _native as nat
+        nat.check_status()
+    stats = planner.load_stats()
     res = {"redundant_slots_per_rank": redundant, "dynamic": dynamic, "moves_applied": int(moves),
            "tok_s_per_gpu": round((eng.metrics["generated_tokens"] - tok0) / dt, 1),
            # a round runs synchronously here; in serving it runs on the planner's thread once a minute
@@ -101,10 +91,6 @@ def run(args, redundant: int, dynamic: bool):
     if planner is not None:
         OmniPlanner.cleanup()
     return res
-
-
-def _stats_without_planner(moes):
-    return {"max_over_mean_rank_load": float("nan"), "max_over_mean_position_load": float("nan")}
 
 
 def main():

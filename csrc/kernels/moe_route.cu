@@ -26,7 +26,10 @@ struct RouterParams {
   int renorm;
   float scale;
   const int* selector;    // [E] logical -> physical, or null
-  unsigned long long* counts;  // [n_physical] activation histogram, or null
+  unsigned long long* counts;  // [n_counts] activation histogram over physical positions, or null
+  int n_counts;
+  OmniStatus* st;         // a row without any selectable expert (all scores NaN) or a selector entry outside the
+                          // histogram is reported here and the pair is dropped (id -1, weight 0)
   int forced_balance;     // ids = round robin (benchmark aid), weights uniform
   const int* num_valid;   // optional device scalar: rows >= *num_valid are padding
   int* out_ids;           // [T, top_k]
@@ -50,7 +53,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const RouterParams p) 
       if (p.selector) id = p.selector[id];
       p.out_ids[(size_t)t * p.top_k + j] = padded ? -1 : id;
       p.out_w[(size_t)t * p.top_k + j] = padded ? 0.f : p.scale / (float)p.top_k;
-      if (p.counts && !padded) atomicAdd(&p.counts[id], 1ull);
+      if (p.counts && !padded && id >= 0 && id < p.n_counts) atomicAdd(&p.counts[id], 1ull);
     }
     return;
   }
@@ -143,7 +146,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const RouterParams p) 
     w = __shfl_sync(0xffffffffu, w, idx & 31);
     wsum += w;
     if (lane == r) { my_w = w; my_id = idx; }
-    if (lane == (idx & 31)) sel[idx] = -INFINITY;
+    if (idx < p.E && lane == (idx & 31)) sel[idx] = -INFINITY;
     __syncwarp();
   }
   if (lane < p.top_k) {
@@ -151,10 +154,24 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const RouterParams p) 
     if (p.renorm) w = w / (wsum + 1e-20f);
     w *= p.scale;
     int id = my_id;
-    if (p.selector) id = p.selector[id];
+    if (id < 0 || id >= p.E) {                 // nothing compared greater than -inf: the scores of this row are NaN
+      report_status(p.st, OMNI_ERR_BOUNDS, 1, t);
+      id = -1;
+      w = 0.f;
+    } else if (p.selector) {
+      id = p.selector[id];
+    }
+    if (p.counts && id >= 0) {
+      if (id < p.n_counts) {
+        atomicAdd(&p.counts[id], 1ull);
+      } else {
+        report_status(p.st, OMNI_ERR_BOUNDS, 2, id);
+        id = -1;
+        w = 0.f;
+      }
+    }
     p.out_ids[(size_t)t * p.top_k + lane] = id;
     p.out_w[(size_t)t * p.top_k + lane] = w;
-    if (p.counts) atomicAdd(&p.counts[id], 1ull);
   }
 }
 
@@ -307,8 +324,9 @@ using namespace omni;
 
 extern "C" int omni_router_topk(const float* logits, const float* bias, int T, int E, int mode, int n_group,
                                 int topk_group, int group_mode, int top_k, int renorm, float scale,
-                                const int* selector, void* counts, int forced_balance, const int* num_valid,
-                                int* out_ids, float* out_w, cudaStream_t stream) {
+                                const int* selector, void* counts, int n_counts, int forced_balance,
+                                const int* num_valid, int* out_ids, float* out_w, void* status,
+                                cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E > 32 * ROUTER_MAX_PER_LANE || top_k > 32 || top_k > E) return -1;
   if (n_group > 32 || (n_group > 1 && E % n_group != 0)) return -2;
@@ -316,6 +334,7 @@ extern "C" int omni_router_topk(const float* logits, const float* bias, int T, i
   p.logits = logits; p.bias = bias; p.T = T; p.E = E; p.mode = mode; p.n_group = n_group;
   p.topk_group = topk_group; p.group_mode = group_mode; p.top_k = top_k; p.renorm = renorm; p.scale = scale;
   p.selector = selector; p.counts = (unsigned long long*)counts; p.forced_balance = forced_balance;
+  p.n_counts = n_counts; p.st = (OmniStatus*)status;
   p.num_valid = num_valid; p.out_ids = out_ids; p.out_w = out_w;
   const int warps = 4;
   router_topk_kernel<<<(T + warps - 1) / warps, warps * 32, warps * E * sizeof(float), stream>>>(p);

@@ -49,6 +49,18 @@ class MoEGate(nn.Module):
         return ops.gemm(x, self.weight, out_dtype=torch.float32)
 
 
+def zipf_router_bias(num_experts: int, layer: int, s: float = 1.2, strength: float = 6.0, seed: int = 0) -> torch.Tensor:
+    """Log-popularity bias: the expert of Zipf rank r gets strength * log(p_r / p_max) / log(E), p_r ~ r^-s, with the
+    ranks permuted per layer."""
+    import math
+    g = torch.Generator().manual_seed(seed * 1000 + layer)
+    perm = torch.randperm(num_experts, generator=g)
+    p = torch.arange(1, num_experts + 1, dtype=torch.float32) ** (-s)
+    b = torch.empty(num_experts)
+    b[perm] = strength * torch.log(p / p.max()) / math.log(num_experts)
+    return b
+
+
 class MoELayer(nn.Module):
     def __init__(self, cfg, layer_idx: int, *, dtype, device=None, planner=None, ep_backend: str = "auto"):
         super().__init__()
@@ -84,7 +96,13 @@ class MoELayer(nn.Module):
         self.ep_backend = ep_backend
         self.ep_ctx = None          # set by the model runner when the fused NVLink path is enabled
         self.forced_balance = False
-        self.routing_bias_override = None   # benchmark aid: fixed per-layer logit bias (load-skew stress)
+        # benchmark aid: fixed per-layer logit bias (load-skew stress); set at construction so that captured decode graphs
+        # contain the addition
+        self.routing_bias_override = None
+        if getattr(cfg, "router_skew", None):
+            self.routing_bias_override = zipf_router_bias(cfg.n_routed_experts, self.moe_index, **cfg.router_skew)
+            if device is not None:
+                self.routing_bias_override = self.routing_bias_override.to(device)
 
     # ------------------------------------------------------------------ routing
     def route(self, x, num_valid=None):

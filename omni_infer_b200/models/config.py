@@ -15,6 +15,9 @@ class ModelConfig:
     # layers (set by the model runner; 1 = every rank runs whole attention layers on its own requests)
     attn_tp_size: int = 1
     attn_tp_rank: int = 0
+    # benchmark aid: {"s": 1.2, "strength": 6.0, "seed": 0} adds a fixed Zipf-shaped bias to every router's logits so that
+    # expert popularity is skewed (load-balance stress); None = the router as trained
+    router_skew: Optional[dict] = None
     vocab_size: int = 1024
     hidden_size: int = 256
     num_hidden_layers: int = 2

@@ -112,8 +112,9 @@ def check_status(device=None, reset: bool = True) -> None:
     if vals[0] != 0:
         if reset:
             buf.zero_()
-        raise KernelProtocolError(
-            f"kernel wait gave up: code={vals[0]} site={vals[1]} block={vals[2]} detail={vals[3]}")
+        what = {1: "mbarrier wait gave up", 2: "flag wait gave up", 3: "index out of bounds (access skipped)",
+                4: "capacity exceeded"}.get(vals[0], "kernel error")
+        raise KernelProtocolError(f"{what}: code={vals[0]} site={vals[1]} block={vals[2]} detail={vals[3]}")
 
 
 def check_rc(rc: int, what: str) -> None:

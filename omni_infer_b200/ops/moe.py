@@ -62,7 +62,8 @@ def router_topk(logits, top_k, *, mode="softmax", bias=None, n_group=1, topk_gro
         nat.ptr(logits), nat.ptr(bias), nat.c_int(T), nat.c_int(E), nat.c_int(0 if mode == "softmax" else 1),
         nat.c_int(n_group), nat.c_int(topk_group), nat.c_int(1 if group_mode == "top2sum" else 0), nat.c_int(top_k),
         nat.c_int(1 if renorm else 0), nat.c_float(scale), nat.ptr(selector), nat.ptr(counts),
-        nat.c_int(1 if forced_balance else 0), nat.ptr(num_valid), nat.ptr(ids), nat.ptr(w), nat.stream())
+        nat.c_int(counts.numel() if counts is not None else 0), nat.c_int(1 if forced_balance else 0), nat.ptr(num_valid),
+        nat.ptr(ids), nat.ptr(w), nat.ptr(nat.status_buffer(logits.device)), nat.stream())
     nat.check_rc(rc, "omni_router_topk")
     return ids, w
 
