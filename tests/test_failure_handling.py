@@ -72,3 +72,31 @@ def test_kv_push_copies_blocks_and_rejects_bad_ids():
     st = nat.status_buffer().tolist()
     assert st[0] == 3 and st[1] == 300                            # bounds error recorded, access skipped
     nat.status_buffer().zero_()
+
+
+def test_router_drops_and_reports_a_row_of_nan_scores():
+    """A row whose router scores are all NaN has no selectable expert: its pairs come back as id -1 with weight 0, the
+    status word names the row, other rows are routed as usual, and nothing is indexed with the invalid id (neither the
+    selector table nor the activation histogram)."""
+    from omni_infer_b200 import ops
+    from omni_infer_b200.ops import _native as nat
+
+    dev = torch.device("cuda")
+    T, E, k = 6, 64, 8
+    g = torch.Generator(device="cuda").manual_seed(0)
+    logits = torch.randn(T, E, device=dev, generator=g)
+    logits[3] = float("nan")
+    selector = torch.arange(E, dtype=torch.int32, device=dev).flip(0).contiguous()
+    counts = torch.zeros(E, dtype=torch.int64, device=dev)
+    nat.status_buffer(dev).zero_()
+    ids, w = ops.router_topk(logits, k, selector=selector, counts=counts, mode="sigmoid", renorm=True, scale=1.0)
+    torch.cuda.synchronize()
+    with pytest.raises(nat.KernelProtocolError) as ei:
+        nat.check_status()
+    assert "code=3" in str(ei.value) and "detail=3" in str(ei.value)
+    assert ids[3].tolist() == [-1] * k and w[3].abs().sum().item() == 0.0
+    ok = [0, 1, 2, 4, 5]
+    ref_ids, _ = ops.router_topk_ref(logits[ok], k, mode="sigmoid", renorm=True, scale=1.0)
+    assert torch.equal(ids[ok].sort(-1).values.long(), (E - 1 - ref_ids.long()).sort(-1).values)
+    assert counts.sum().item() == len(ok) * k
+    nat.check_status()                                            # cleared; the context is still usable
