@@ -41,7 +41,11 @@ def parse():
     ap.add_argument("--attn-tp", action="store_true",
                     help="tensor-parallel attention over all ranks (one shared batch) instead of data-parallel attention")
     ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--synthetic-kv", action="store_true", help="fill the KV cache without running prefill")
+    ap.add_argument("--decode-ctx", type=int, default=-1,
+                    help="context length at the middle of the timed steps; -1 = the config's mean decode context "
+                         "(input + output / 2), 0 = time right after the prefill")
+    ap.add_argument("--no-breakdown", action="store_true", help="skip the untimed per-module timing step")
+    ap.add_argument("--no-nccl-arm", action="store_true", help="skip the untimed NCCL all-to-all comparison steps (N > 1)")
     return ap.parse_args()
 
 
@@ -93,6 +97,106 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def fast_forward(eng, n_tokens: int, vocab: int, seed: int) -> None:
+    """Advance every running request by ``n_tokens`` without running the model: synthetic output ids, KV slots
+    allocated by the block manager and filled with random values in every layer's cache.  The timed decode steps
+    then run at the context length the workload has on average, not at the length right after the prefill."""
+    import torch
+
+    if n_tokens <= 0:
+        return
+    runner = eng.worker.runner
+    bs = runner.cfg.block_size
+    g = torch.Generator().manual_seed(seed)
+    slots = []
+    for req in eng.scheduler.running:
+        c = req.num_computed_tokens
+        if eng.kv.allocate_slots(req, n_tokens + len(req.spec_token_ids) + 1) is None:
+            raise RuntimeError("KV cache too small for the requested decode context")
+        slots += runner._slots(req.block_ids, c, n_tokens)
+        req.output_token_ids.extend(torch.randint(0, vocab, (n_tokens,), generator=g).tolist())
+        req.num_computed_tokens = c + n_tokens
+    idx = torch.tensor(slots, dtype=torch.int64, device=runner.device)
+    caches = list(runner.kv_caches) + [k[0] for k in runner.drafter_kv]
+    width = None
+    for c in caches:
+        for t in (c if isinstance(c, tuple) else (c,)):
+            flat = t.view(-1, t.shape[-1] if t.dim() == 3 else t.shape[-2] * t.shape[-1])
+            if width != flat.shape[1]:
+                width = flat.shape[1]
+                rnd = (torch.randn(idx.numel(), width, device=runner.device) * 0.5).to(t.dtype)
+            flat[idx] = rnd
+    torch.cuda.synchronize()
+
+
+def module_breakdown(eng, mc):
+    """One extra, untimed decode step run eagerly with CUDA events around the top-level module classes.  Returns
+    milliseconds per class and the HBM bytes each class has to stream (its parameters once, plus the KV cache for
+    attention), so that the line carries achieved / measured-copy-bandwidth fractions."""
+    import torch
+
+    runner = eng.worker.runner
+    classes = {"MLAAttention": "attention", "GQAAttention": "attention", "MoELayer": "experts", "SwiGLUMLP": "dense_mlp"}
+    spans, depth, hooks, nbytes = [], [0], [], {}
+
+    def pre(mod, _inp):
+        if depth[0] == 0:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            mod._bd_start = ev
+        depth[0] += 1
+
+    def post(mod, _inp, _out):
+        depth[0] -= 1
+        if depth[0] == 0:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            spans.append((classes[mod.__class__.__name__], mod._bd_start, ev))
+
+    models = [runner.model] + list(runner.drafters)
+    for m in models:
+        for mod in m.modules():
+            kind = classes.get(mod.__class__.__name__)
+            if kind is None:
+                continue
+            hooks.append(mod.register_forward_pre_hook(pre))
+            hooks.append(mod.register_forward_hook(post))
+    seen = set()
+    for m in models:
+        for mod in m.modules():
+            kind = classes.get(mod.__class__.__name__)
+            if kind is None:
+                continue
+            for prm in mod.parameters():
+                if id(prm) not in seen:
+                    seen.add(id(prm))
+                    nbytes[kind] = nbytes.get(kind, 0) + prm.numel() * prm.element_size()
+    graphs, runner.graphs = runner.graphs, None
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    try:
+        eng.step()                     # eager warm-up of this path
+        torch.cuda.synchronize()
+        spans.clear()
+        a.record()
+        eng.step()
+        b.record()
+        torch.cuda.synchronize()
+    finally:
+        runner.graphs = graphs
+        for h in hooks:
+            h.remove()
+    ms = {}
+    for kind, e0, e1 in spans:
+        ms[kind] = ms.get(kind, 0.0) + e0.elapsed_time(e1)
+    total = a.elapsed_time(b)
+    ms["other"] = max(0.0, total - sum(ms.values()))
+    ctx = sum(r.num_computed_tokens for r in eng.scheduler.running)
+    n_kv = len(runner.kv_caches) + len(runner.drafter_kv)
+    nbytes["attention"] = nbytes.get("attention", 0) + ctx * mc.kv_bytes_per_token(2) * n_kv
+    return {"eager_step_ms": round(total, 2), "ms": {k: round(v, 2) for k, v in ms.items()},
+            "hbm_bytes": {k: int(v) for k, v in nbytes.items()}}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -140,8 +244,11 @@ def main():
         mtp = 0
     tpr = 1 + mtp
     bs = 128
+    out_len = {"deepseek-v3": 1024, "deepseek-v2-lite": 256, "qwen3-30b-a3b": 512}.get(args.config, 0)
+    decode_ctx = args.decode_ctx if args.decode_ctx >= 0 else (in_len + out_len // 2 if not (args.batch or args.input_len) else 0)
     total_steps = args.warmup + args.steps
-    per_req_tokens = in_len + tpr * (total_steps + 4) + 8
+    extra_steps = 8 + (0 if args.no_breakdown else 2) + (0 if args.no_nccl_arm or world == 1 else 8)
+    per_req_tokens = max(in_len, decode_ctx) + tpr * (total_steps + extra_steps + 4) + 8
     blocks = batch * ((per_req_tokens + bs - 1) // bs + 1) + 2
     ecfg = EngineConfig(model=mc.name, block_size=bs, num_kv_blocks=blocks, max_num_seqs=batch,
                         max_num_batched_tokens=max(16384, in_len), max_model_len=per_req_tokens + bs,
@@ -179,6 +286,10 @@ def main():
     torch.cuda.synchronize()
     nat.check_status()
 
+    # ---- move to the context length the timed steps are meant to run at (their middle sits at decode_ctx)
+    skip = decode_ctx - in_len - 1 - args.warmup - args.steps // 2 if decode_ctx else 0
+    fast_forward(eng, skip, mc.vocab_size, 7 + rank)
+
     # ---- decode: W warm-up steps, K timed steps
     for _ in range(args.warmup):
         eng.step()
@@ -211,6 +322,30 @@ def main():
     tokens = eng.metrics["generated_tokens"] - tokens0
     launches = nat.launch_count() - launches0
     nat.check_status()
+    ctx_mid = statistics.mean(r.num_computed_tokens for r in eng.scheduler.running) - args.steps / 2
+
+    # ---- untimed extras: per-module breakdown of one eager step; the same steps over the NCCL all-to-all baseline
+    breakdown = None if args.no_breakdown else module_breakdown(eng, mc)
+    nccl_ms = None
+    runner = eng.worker.runner
+    if world > 1 and not args.no_nccl_arm and not args.attn_tp and getattr(runner, "ep_ctx", None) is not None:
+        runner.force_ep_baseline = True        # every rank sets it, so the agreement stays consistent
+        for _ in range(2):
+            eng.step()
+        torch.cuda.synchronize()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(4):
+            eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        nccl_ms = e0.elapsed_time(e1) / 4
+        runner.force_ep_baseline = False
+        tt = torch.tensor([nccl_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        nccl_ms = float(tt[0])
+    nat.check_status()
     # bytes moved per step by the runner: ids, positions, slots (int64), q_seq_lens, seq_lens, q_to_seq, block table (int32)
     n_rows = batch * tpr
     bt_w = eng.worker.runner._bt_width
@@ -239,6 +374,7 @@ def main():
             "higher_is_better": True, "scaling": "strong" if args.attn_tp else "weak", "vs_baseline": None, "dtype": "fp8_e4m3 weights (128x128 block scales), bf16 activations/KV" if mc.quantization == "fp8_block" else "bf16",
             "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": name, "global_batch": batch * (1 if args.attn_tp else world), "seq_len": in_len, "output_steps": total_steps,
+                       "ctx_at_timing": round(ctx_mid, 1),
                        "parallelism": (f"tp{world}-attn({args.tp_backend})+ep{world}" if args.attn_tp and world > 1
                                        else f"ep{world}+dp{world}-attn"), "mtp_draft_layers": mtp,
                        "mtp_accepted_tokens_per_step": round(tokens_total / (args.steps * batch * (1 if args.attn_tp else world)), 3),
@@ -252,6 +388,24 @@ def main():
             "gpu_launches": int(launches),
             "impl": "ours",
         }
+        peaks = {"hbm_gbs": 6533.2}
+        try:
+            peaks.update(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))))
+        except Exception:  # noqa: BLE001
+            pass
+        if breakdown is not None:
+            fr = {}
+            for k, b in breakdown["hbm_bytes"].items():
+                t_ms = breakdown["ms"].get(k)
+                if t_ms:
+                    fr[k] = round(b / (t_ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)
+            breakdown["frac_of_measured_hbm_copy"] = fr
+            total_b = sum(breakdown["hbm_bytes"].values())
+            breakdown["step_frac_of_measured_hbm_copy"] = round(total_b / (dev_ms / args.steps * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)
+            line["breakdown"] = breakdown
+        if nccl_ms is not None:
+            line["nccl_all_to_all_arm"] = {"ms_per_step": round(nccl_ms, 3), "steps": 4, "mode": "eager, same engine and batch",
+                                           "fused_speedup": round(nccl_ms / (dev_ms / args.steps), 3)}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

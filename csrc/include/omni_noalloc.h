@@ -19,10 +19,13 @@
  *   - Limits: Bq * num_splits * H * 512 * 4 bytes of partial outputs must fit OMNI_MLA_NOALLOC_OPART_BYTES
  *     (16 MiB, i.e. Bq * num_splits * H <= 8192) and Bq * num_splits * H log-sum-exp values must fit
  *     OMNI_MLA_NOALLOC_LSE_FLOATS.  Larger problems are refused with OMNI_NOALLOC_TOO_LARGE (-100) and a
- *     message on stderr; nothing is launched.
+ *     message on stderr; nothing is launched.  The limit applies to num_splits > 1 only: a call with one
+ *     split writes `out` directly, uses no scratch and may be of any size.
  *   - The call makes no cudaMalloc / cudaFree and uses no allocating library routine.
  *   - The first call on each device looks up the device address of the array (cudaGetSymbolAddress, return
- *     code checked) and remembers it.  Make that first call before starting any stream capture.
+ *     code checked) and remembers it.  Make that first call before starting any stream capture, and do not
+ *     let two threads make their first call on the same device at the same moment (the look-up is not
+ *     locked; later calls are free to come from any thread).
  *   - All calls share the one array and it keeps whatever the previous call left in it.  The kernels write
  *     every partial result they later read, so nothing has to be cleared between calls; but two calls whose
  *     kernels overlap on the GPU (different streams, or the same stream from two threads without ordering)

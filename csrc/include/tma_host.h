@@ -74,6 +74,20 @@ inline int make_tmap_3d(CUtensorMap* m, const void* base, int elem_bytes, uint64
   return 0;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device.  The attribute belongs to the device's
+// context, so a process that launches on a second GPU has to set it there too; `done` is the caller's
+// per-kernel table of devices already configured (a function-local `static bool done[64]`).
+inline int ensure_dyn_smem(const void* kernel, int bytes, bool (&done)[64]) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < 64 && done[dev]) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < 64) done[dev] = true;
+  return 0;
+}
+
 inline int sm_count() {
   static int n = 0;
   if (n == 0) {

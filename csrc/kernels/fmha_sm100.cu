@@ -452,12 +452,8 @@ extern "C" int omni_fmha_varlen(const void* q, long long q_rows, int q_ld, int q
   p.k_head_stride = k_head_stride; p.v_head_stride = v_head_stride; p.v_col0 = v_col0; p.k2_col0 = k2_col0;
   p.nk1 = d_k1 / 64; p.nk2 = d_k2 / 64; p.scale_log2 = scale * 1.4426950408889634f; p.causal = causal;
   p.out = (__nv_bfloat16*)out; p.status = (OmniStatus*)status;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(fmha_varlen_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FM_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static bool configured[64] = {false};
+  if (int e = ensure_dyn_smem((const void*)fmha_varlen_kernel, FM_SMEM, configured)) return e;
   dim3 grid((max_q + FM_BQ - 1) / FM_BQ, B, Hq);
   fmha_varlen_kernel<<<grid, FM_THREADS, FM_SMEM, stream>>>(tq, tk, tk2, tv, p);
   return (int)cudaGetLastError();

@@ -99,14 +99,8 @@ __device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {
       : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
 }
 
-#ifdef GEMM_TRACE
-__device__ long long g_gemm_trace[16];
-#define GT_BEGIN long long _gt0 = clock64()
-#define GT_END(slot) gtrace[slot] += clock64() - _gt0
-#else
 #define GT_BEGIN
 #define GT_END(slot)
-#endif
 
 template <int KIND, int BN, int NACC, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -139,10 +133,6 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   float* sc_ring = amax_x + 256;                         // [STAGES][BN], 16-byte aligned (bulk copies, float4 reads)
   static_assert((1024 + L::PREFIX_BYTES + 1024) % 16 == 0, "scale ring must be 16-byte aligned");
 
-#ifdef GEMM_TRACE
-  long long gtrace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  const long long gt_start = clock64();
-#endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK_ELEMS - 1) / BK_ELEMS;
@@ -349,9 +339,6 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             GT_END(2);
           }
           tc_fence_after();
-#ifdef GEMM_TRACE
-          const long long gt_busy0 = clock64();
-#endif
           // pull this group's columns of the fresh partial product out of TMEM in one round trip
           uint32_t t[NACC][CW];
 #pragma unroll
@@ -411,10 +398,6 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty_bar[s]);      // scale ring slot read
-#ifdef GEMM_TRACE
-          gtrace[3] += clock64() - gt_busy0;
-          gtrace[5] += 1;
-#endif
           if (++s == STAGES) s = 0;
         }
         if (!ok) break;
@@ -536,13 +519,6 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     }
   }
 
-#ifdef GEMM_TRACE
-  if (blockIdx.x == 0 && lane == 0 && warp >= 1 && warp <= 2) {
-    const long long tot = clock64() - gt_start;
-    if (warp == 1) { g_gemm_trace[0] = gtrace[0]; g_gemm_trace[1] = gtrace[1]; g_gemm_trace[8] = tot; }
-    if (warp == 2) { g_gemm_trace[2] = gtrace[2]; g_gemm_trace[3] = gtrace[3]; g_gemm_trace[5] = gtrace[5]; g_gemm_trace[9] = tot; }
-  }
-#endif
   // ------------------------------------------------------------------ teardown
   if (*abort_flag) {
     if (threadIdx.x == 0) report_abort(abort_flag, p.status);
@@ -565,12 +541,8 @@ template <int KIND, int BN, int NACC, int EPI>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid, cudaStream_t st) {
   using L = GemmSmem<BN, NACC>;
   auto kfn = gemm_swapab_kernel<KIND, BN, NACC, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static bool configured[64] = {false};
+  if (int e = ensure_dyn_smem((const void*)kfn, L::TOTAL, configured)) return e;
   kfn<<<grid, GEMM_THREADS, L::TOTAL, st>>>(tw, tx, p);
   return (int)cudaGetLastError();
 }
@@ -579,11 +551,6 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
 
 using namespace omni;
 
-#ifdef GEMM_TRACE
-extern "C" int omni_gemm_trace_read(long long* out16) {
-  return (int)cudaMemcpyFromSymbol(out16, g_gemm_trace, sizeof(long long) * 16);
-}
-#endif
 
 // kind: 0 bf16, 1 fp8 block-scaled.  epi: 0 store, 1 swiglu->bf16, 2 swiglu->fp8+scales.
 // bn: token tile (16, 32, 64, 128, 256); 0 picks from `t_hint` (expected rows per group).

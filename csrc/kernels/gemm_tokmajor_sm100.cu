@@ -121,14 +121,6 @@ __device__ __forceinline__ void tm_fma2(float2& acc, float2 a, float2 b) {
       : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
 }
 
-#ifdef GEMM_TRACE
-__device__ long long g_tm_trace[16];
-#define TT_BEGIN long long _gt0 = clock64()
-#define TT_END(slot) gtrace[slot] += clock64() - _gt0
-#else
-#define TT_BEGIN
-#define TT_END(slot)
-#endif
 
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(TM_THREADS, 1)
@@ -158,10 +150,6 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   float* sc_ring = amax_x + 256;                         // [STAGES][128], 16-byte aligned (bulk copies)
   static_assert((1024 + L::PREFIX_BYTES + 1024) % 16 == 0, "scale ring must be 16-byte aligned");
 
-#ifdef GEMM_TRACE
-  long long gtrace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  const long long gt_start = clock64();
-#endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK_ELEMS - 1) / BK_ELEMS;
@@ -300,14 +288,10 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
 #pragma unroll 1
         for (int kb = 0; kb < num_kb; ++kb) {
           if (KIND == 1) {
-            TT_BEGIN;
             if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, abort_flag, p.status, TMS_MMA_TMEM_EMPTY, (int)buf)) { ok = false; break; }
-            TT_END(0);
           }
           {
-            TT_BEGIN;
             if (!mbar_wait(&full_bar[s], sph, abort_flag, p.status, TMS_MMA_FULL, (int)s)) { ok = false; break; }
-            TT_END(1);
           }
           tc_fence_after();
           if (elect_one()) {
@@ -400,14 +384,9 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
         const float sw0 = __ldg(wsc0 + kb);
         const float sw1 = blk1_ok ? __ldg(wsc1 + kb) : 0.f;
         {
-          TT_BEGIN;
           if (!mbar_wait(&tfull_bar[buf], bph, abort_flag, p.status, TMS_EPI_TMEM_FULL, (int)buf)) { ok = false; break; }
-          TT_END(2);
         }
         tc_fence_after();
-#ifdef GEMM_TRACE
-        const long long gt_busy0 = clock64();
-#endif
         const float sx = sc_ring[s * 128 + r];
 #pragma unroll
         for (int a = 0; a < NB; ++a) {
@@ -434,10 +413,6 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
           for (int j = 0; j < TM_CW / 2; ++j)
             tm_fma2(acc[a][j], make_float2(__uint_as_float(t[2 * j]), __uint_as_float(t[2 * j + 1])), m2);
         }
-#ifdef GEMM_TRACE
-        gtrace[3] += clock64() - gt_busy0;
-        gtrace[5] += 1;
-#endif
         if (++buf == NBUF) { buf = 0; bph ^= 1u; }
         if (++s == STAGES) s = 0;
       }
@@ -544,13 +519,6 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     }
   }
 
-#ifdef GEMM_TRACE
-  if (blockIdx.x == 0 && lane == 0 && (warp == 1 || warp == 4)) {
-    const long long tot = clock64() - gt_start;
-    if (warp == 1) { g_tm_trace[0] = gtrace[0]; g_tm_trace[1] = gtrace[1]; g_tm_trace[8] = tot; }
-    if (warp == 4) { g_tm_trace[2] = gtrace[2]; g_tm_trace[3] = gtrace[3]; g_tm_trace[5] = gtrace[5]; g_tm_trace[9] = tot; }
-  }
-#endif
   // ------------------------------------------------------------------ reduce-scatter: tell the destinations
   if (p.rs_world > 1) {
     if (warp >= 4) __threadfence_system();   // this thread's peer stores are performed before the flag below
@@ -587,12 +555,8 @@ template <int KIND, int EPI>
 static int launch_tm(const CUtensorMap& tx, const CUtensorMap& tw, const TmGemmParams& p, int grid, cudaStream_t st) {
   using L = TmSmem;
   auto kfn = gemm_tokmajor_kernel<KIND, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static bool configured[64] = {false};
+  if (int e = ensure_dyn_smem((const void*)kfn, L::TOTAL, configured)) return e;
   kfn<<<grid, TM_THREADS, L::TOTAL, st>>>(tx, tw, p);
   return (int)cudaGetLastError();
 }
@@ -601,11 +565,6 @@ static int launch_tm(const CUtensorMap& tx, const CUtensorMap& tw, const TmGemmP
 
 using namespace omni;
 
-#ifdef GEMM_TRACE
-extern "C" int omni_gemm_trace_read(long long* out16) {
-  return (int)cudaMemcpyFromSymbol(out16, g_tm_trace, sizeof(long long) * 16);
-}
-#endif
 
 // Collective side of a call (all zero / null for a plain GEMM).
 struct OmniTmCollective {
@@ -684,13 +643,4 @@ extern "C" int omni_gemm_tm2(int kind, int epi, const void* w, const void* x, vo
   if (epi == 0) return launch_tm<1, 0>(tx, tw, p, grid, stream);
   if (epi == 1) return launch_tm<1, 1>(tx, tw, p, grid, stream);
   return launch_tm<1, 2>(tx, tw, p, grid, stream);
-}
-
-// e4m3 only, no collective (kept for callers of the first version of the interface)
-extern "C" int omni_gemm_tm(int epi, const void* w, const void* x, void* out, int G, int n_out, int K, int x_rows, int T,
-                            const int* seg_start, const int* seg_len, const float* w_scale, const float* x_scale,
-                            int x_scale_ld, int out_ld, int out_f32, float* out_scale, int out_scale_ld,
-                            const float* row_scale, int x_ld, void* status, cudaStream_t stream) {
-  return omni_gemm_tm2(1, epi, w, x, out, G, n_out, K, x_rows, T, seg_start, seg_len, w_scale, x_scale, x_scale_ld, out_ld,
-                       out_f32, out_scale, out_scale_ld, row_scale, 0, 0, x_ld, nullptr, status, stream);
 }

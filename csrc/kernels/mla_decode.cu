@@ -80,12 +80,6 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       : "memory");
 }
 
-#ifdef MLA_TRACE
-__device__ long long g_mla_trace[16];
-#define TRACE_WAIT(slot, expr) ({ long long _t0 = clock64(); bool _r = (expr); trace[slot] += clock64() - _t0; _r; })
-#else
-#define TRACE_WAIT(slot, expr) (expr)
-#endif
 
 // ---------------------------------------------------------------------------------------------------------
 // Producer and MMA roles.  Both walk the same sequence of KV chunks with a few running counters (no division,
@@ -273,10 +267,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   __nv_bfloat16* sm_max = (__nv_bfloat16*)(bars + 64);  // [2 tile parities][2 groups][128 rows] row maxima, 1 KB
   float* sm_sum = (float*)(bars + 64);                  // [2 groups][128 rows], same 1 KB after the last tile
 
-#ifdef MLA_TRACE
-  long long trace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  const long long t_start = clock64();
-#endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = blockIdx.x;   // which 256 output dims
   const int split = blockIdx.y;
@@ -392,11 +382,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       for (int i = 0; i < n; ++i) {
         const int st = i & 1;
-        if (!TRACE_WAIT(4, mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, MS_S_FULL, i))) { ok = false; break; }
+        if (!mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, MS_S_FULL, i)) { ok = false; break; }
         tc_fence_after();
-#ifdef MLA_TRACE
-        const long long t_sm0 = clock64();
-#endif
         const int valid = kv_len - (tile_begin + i) * MLA_TILE - grp * 32;  // valid columns of this group's half
         const uint32_t s_addr = lane_addr + TM_S + st * 64 + grp * 32;
         float s[32];
@@ -420,16 +407,13 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         // reference only has to be near the true maximum, not equal to it.
         __nv_bfloat16* slab = sm_max + st * 256;
         slab[grp * 128 + row] = __float2bfloat16_rn(mx_local);
-        if (!TRACE_WAIT(5, group_sync())) { ok = false; break; }
+        if (!group_sync()) { ok = false; break; }
         const float mx = fmaxf(__bfloat162float(slab[row]), __bfloat162float(slab[128 + row]));
         const float m_new = fmaxf(m, mx);
         const bool grow = (m_new - m) > 8.0f;  // also true on the first tile (m = -inf)
         if (i == 0) {
           m = m_new;
         } else if (__any_sync(0xffffffffu, grow)) {
-#ifdef MLA_TRACE
-          trace[7] += 1;
-#endif
           // P V of the previous tile must have retired before O is touched; P V of this tile waits for P
           if (!mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, MS_O_DONE, i)) { ok = false; break; }
           tc_fence_after();
@@ -465,9 +449,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[st]);
-#ifdef MLA_TRACE
-        trace[6] += clock64() - t_sm0;
-#endif
       }
       // o_done flips once per tile and is only sampled when a rescale is needed, so its parity cannot
       // tell "last tile retired" from "two tiles behind"; the single-use o_final barrier can.
@@ -536,14 +517,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
   }
 
-#ifdef MLA_TRACE
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && warp <= 2) {
-    const long long tot = clock64() - t_start;
-    if (warp == 0) { g_mla_trace[0] = trace[0]; g_mla_trace[8] = tot; g_mla_trace[9] = n; }
-    if (warp == 1) { g_mla_trace[1] = trace[1]; g_mla_trace[2] = trace[2]; g_mla_trace[3] = trace[3]; g_mla_trace[10] = tot; }
-    if (warp == 2) { g_mla_trace[4] = trace[4]; g_mla_trace[5] = trace[5]; g_mla_trace[6] = trace[6]; g_mla_trace[7] = trace[7]; g_mla_trace[11] = tot; }
-  }
-#endif
   if (*abort_flag) {
     if (threadIdx.x == 0) report_abort(abort_flag, p.status);
     const uint64_t t0 = globaltimer_ns();
@@ -589,11 +562,6 @@ __global__ void mla_combine_kernel(const float* __restrict__ o_part, const float
 
 using namespace omni;
 
-#ifdef MLA_TRACE
-extern "C" int omni_mla_trace_read(long long* out16) {
-  return (int)cudaMemcpyFromSymbol(out16, g_mla_trace, sizeof(long long) * 16);
-}
-#endif
 
 // Scratch needed for num_splits > 1: o_part = Bq*splits*H*512 floats, lse_part = Bq*splits*H floats.
 extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, long long num_slots,
@@ -613,12 +581,8 @@ extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, l
   p.q = (const __nv_bfloat16*)q; p.H = H; p.block_size = block_size; p.block_table = block_table; p.bt_ld = bt_ld; p.seq_lens = seq_lens;
   p.q_to_seq = q_to_seq; p.scale_log2 = scale * 1.4426950408889634f; p.num_splits = num_splits;
   p.out = (__nv_bfloat16*)out; p.o_part = o_part; p.lse_part = lse_part; p.status = (OmniStatus*)status;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MLA_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static bool configured[64] = {false};
+  if (int e = ensure_dyn_smem((const void*)mla_decode_kernel, MLA_SMEM, configured)) return e;
   dim3 grid(2, num_splits, Bq);
   mla_decode_kernel<<<grid, MLA_THREADS, MLA_SMEM, stream>>>(tq, tkv, p);
   cudaError_t e = cudaGetLastError();
@@ -659,8 +623,9 @@ extern "C" int omni_mla_decode_noalloc(const void* q, const void* cache, int cac
   if (Bq <= 0) return 0;
   if (num_splits < 1 || H < 1) return -3;
   const unsigned long long parts = (unsigned long long)Bq * (unsigned long long)num_splits * (unsigned long long)H;
-  if (parts * 512ull * 4ull > (unsigned long long)OMNI_MLA_NOALLOC_OPART_BYTES ||
-      parts > (unsigned long long)OMNI_MLA_NOALLOC_LSE_FLOATS) {
+  // one split writes `out` directly and never touches the scratch, so the limit only binds split-KV calls
+  if (num_splits > 1 && (parts * 512ull * 4ull > (unsigned long long)OMNI_MLA_NOALLOC_OPART_BYTES ||
+                         parts > (unsigned long long)OMNI_MLA_NOALLOC_LSE_FLOATS)) {
     fprintf(stderr,
             "omni_mla_decode_noalloc: Bq*num_splits*H = %llu exceeds the built-in scratch (limit %u); "
             "use omni_mla_decode with caller-provided scratch\n",

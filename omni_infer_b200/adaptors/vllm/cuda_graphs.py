@@ -43,7 +43,7 @@ class DecodeGraphs:
     def capture(self, padded: int) -> None:
         r = self.r
         ids, md = self._static_inputs(padded)
-        r._agree_ep_path(padded * r.tpr)
+        r._agree_ep_path(padded * r.tpr, 1, False)
         # warm-up on a side stream (first-use set-up such as shared-memory attributes must not be captured)
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())

@@ -135,17 +135,55 @@ class ModelRunner:
                                     wait_ms=self.cfg.ep_wait_ms, payload="fp8" if cfg.quantization == "fp8_block" else "bf16")
             self.ep_max_tokens = self.ep_ctx.max_tokens
 
-    def _agree_ep_path(self, num_tokens: int) -> None:
-        """Every rank contributes its token count; the fused path is taken only if all of them fit."""
-        if getattr(self, "ep_ctx", None) is None:
-            return
-        import torch.distributed as dist
+    def _agree_start(self, num_tokens: int, rounds: int, has_work: bool):
+        """Start the per-step agreement of the data-parallel ranks (host group, asynchronous so that it overlaps
+        the input preparation).  Every rank contributes its token rows, the model rounds its batch needs (a prefill
+        is one round, a decode ``num_step``) and whether it has live requests.  The reference keeps its DP ranks in
+        step the same way, with a MAX all-reduce of the token count on the CPU group
+        (omni/adaptors/vllm/worker/npu_model_runner.py:989-995)."""
         ps = get_parallel_state()
-        t = torch.tensor([num_tokens], dtype=torch.int64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ps.group("cpu").group)
-        fused = int(t.item()) <= self.ep_max_tokens
+        if ps.world_size == 1 or not getattr(self, "_moe_layers", None):
+            return None
+        import torch.distributed as dist
+        t = torch.tensor([num_tokens, rounds, 1 if has_work else 0], dtype=torch.int64)
+        work = dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ps.group("cpu").group, async_op=True)
+        return t, work
+
+    def _agree_finish(self, handle, rounds: int = 1) -> int:
+        """Finish the agreement: choose the expert-parallel path every rank takes in this step (the fused peer-memory
+        kernels only if every rank's rows fit their buffers and nothing forces the baseline) and return the number of
+        model rounds all ranks run.  ``peers_busy`` tells the engine loop whether any rank still has requests."""
+        if handle is None:
+            self.peers_busy = False
+            self._ep_fused_now = getattr(self, "ep_ctx", None) is not None
+            return rounds
+        t, work = handle
+        work.wait()
+        max_tokens, max_rounds, any_work = int(t[0]), int(t[1]), bool(int(t[2]))
+        self.peers_busy = any_work
+        ctx = getattr(self, "ep_ctx", None)
+        fused = ctx is not None and max_tokens <= self.ep_max_tokens and not getattr(self, "force_ep_baseline", False)
+        self._ep_fused_now = fused
         for m in self._moe_layers:
-            m.ep_ctx = self.ep_ctx if fused else None
+            m.ep_ctx = ctx if fused else None
+        return max(rounds, max_rounds)
+
+    def _agree_ep_path(self, num_tokens: int, rounds: int = 1, has_work: bool = True) -> int:
+        return self._agree_finish(self._agree_start(num_tokens, rounds, has_work), rounds)
+
+    def _dummy_rounds(self, n: int) -> None:
+        """Extra rounds with no live row, so that this rank makes as many expert-parallel exchanges as the rank with
+        the most rounds: one main-model forward and one forward per drafter each."""
+        if n <= 0:
+            return
+        padded = self._get_closest_gear(1) if self.graphs is not None else 1
+        ids, md = self._prepare_decode(SchedulerOutput([], False), padded)
+        md.num_valid = self._to_dev([0], torch.int32)
+        for _ in range(n):
+            hidden, _ = self._forward_decode(ids, md, padded)
+            h = hidden
+            for di, d in enumerate(self.drafters):
+                h = d(ids, md, self.drafter_kv[di], h)
 
     def kv_bytes_per_block(self) -> int:
         cfg = self.model_cfg
@@ -407,8 +445,9 @@ class ModelRunner:
         return out
 
     def _run_prefill(self, so, reqs) -> ModelRunnerOutput:
+        handle = self._agree_start(sum(x.num_scheduled_tokens for x in so.scheduled), 1, True)
         ids, md = self._prepare_prefill(so)
-        self._agree_ep_path(int(ids.shape[0]))
+        rounds = self._agree_finish(handle, 1)
         hidden = self.model(ids, md, self.kv_caches)
         last_h = hidden[md.sample_indices]
         logits = self.model.compute_logits(last_h)
@@ -433,12 +472,16 @@ class ModelRunner:
             spec_t = torch.stack(spec_cols, dim=1).tolist()
             pad = self.cfg.num_speculative_tokens - len(self.drafters)
             spec = [row + [0] * pad for row in spec_t]
+        self._dummy_rounds(rounds - 1)
         tl = toks.tolist()
         return ModelRunnerOutput([r.request_id for r in reqs], [[[t] for t in tl]], spec)
 
     def _forward_decode(self, ids, md, padded):
         """hidden, logits and greedy tokens for one decode step (CUDA graph replay when available)."""
-        if self.graphs is not None and self.graphs.has(padded):
+        # a captured graph contains the fused exchange; when the ranks agreed on the baseline for this step (a peer
+        # prefills more rows than the fused buffers hold) the step runs eagerly on the agreed path instead
+        graph_ok = getattr(self, "_ep_fused_now", True) or getattr(self, "ep_ctx", None) is None
+        if self.graphs is not None and self.graphs.has(padded) and graph_ok:
             return self.graphs.replay(padded, ids, md)
         hidden = self.model(ids, md, self.kv_caches)
         logits = self.model.compute_logits(hidden)
@@ -447,8 +490,9 @@ class ModelRunner:
     def _run_decode(self, so, reqs) -> ModelRunnerOutput:
         tpr, B = self.tpr, len(reqs)
         padded = self._get_closest_gear(B) if (self.graphs is not None) else B
+        handle = self._agree_start(padded * tpr, so.num_step, True)
         ids, md = self._prepare_decode(so, padded)
-        self._agree_ep_path(padded * tpr)
+        rounds = self._agree_finish(handle, so.num_step)
         steps_out: list = []
         spec_final = None
         for step in range(so.num_step):
@@ -492,6 +536,7 @@ class ModelRunner:
                 md.max_seq_len += tpr
                 last_tok = fwd.gather(1, acc.long().unsqueeze(1))
                 ids = torch.cat([last_tok, draft_t], dim=1).reshape(-1)
+        self._dummy_rounds(rounds - so.num_step)
         # ---- one host sync for the whole round
         if tpr == 1:
             stacked = torch.stack(steps_out, dim=0).tolist()           # [steps][B]
@@ -504,15 +549,12 @@ class ModelRunner:
     # ------------------------------------------------------------------ warm-up / dummy batches
     @torch.inference_mode()
     def execute_dummy_batch(self, num_tokens: int = 1) -> None:
-        """Idle data-parallel ranks still run one padded decode step so that collectives match
-        (omni/adaptors/vllm/worker/npu_worker.py:285)."""
-        tpr = self.tpr
+        """An idle data-parallel rank still takes part in the step: it joins the agreement and runs as many rounds
+        (main model + drafters, no live row) as the busiest rank, so that every expert-parallel exchange finds its
+        peer (omni/adaptors/vllm/worker/npu_worker.py:285)."""
         padded = self._get_closest_gear(1) if self.graphs is not None else 1
-        so = SchedulerOutput([], False)
-        ids, md = self._prepare_decode(so, padded)
-        md.num_valid = self._to_dev([0], torch.int32)
-        self._agree_ep_path(padded * tpr)
-        self._forward_decode(ids, md, padded)
+        rounds = self._agree_ep_path(padded * self.tpr, 1, False)
+        self._dummy_rounds(rounds)
 
     @torch.inference_mode()
     def profile_run(self) -> None:

@@ -61,7 +61,7 @@ class AsyncEngine:
         while not self._stop:
             try:
                 while True:
-                    item = self.inbox.get_nowait() if eng.has_unfinished else self.inbox.get(timeout=0.05)
+                    item = self.inbox.get_nowait() if (eng.has_unfinished or eng._world > 1) else self.inbox.get(timeout=0.05)
                     if item[0] == "abort":
                         eng.abort(item[1])
                     else:
@@ -69,7 +69,12 @@ class AsyncEngine:
             except queue.Empty:
                 pass
             if not eng.has_unfinished:
-                continue
+                if eng._world == 1:
+                    continue
+                # several data-parallel ranks share the expert-parallel exchanges: an idle rank keeps stepping (dummy
+                # batches) so that busy peers never wait for it; when the whole group was idle it paces itself
+                if not eng.peers_busy:
+                    time.sleep(0.002)
             try:
                 outs = eng.step()
             except Exception as e:  # noqa: BLE001  (a failed step must not kill the serving thread)

@@ -157,13 +157,23 @@ class EngineCore:
         self.metrics["prefill_steps" if so.is_prefill else "decode_steps"] += 0 if so.empty else 1
         self.metrics["generated_tokens"] += sum(len(r.new_token_ids) for r in res)
 
+    @property
+    def peers_busy(self) -> bool:
+        """With several data-parallel ranks: did any rank report live requests in the last step's agreement?"""
+        return self._world > 1 and bool(getattr(self.worker.runner, "peers_busy", False))
+
     def run_until_done(self, max_steps: int = 1_000_000) -> dict:
+        """Step until this rank has nothing left; with several data-parallel ranks, until no rank has (an idle rank
+        keeps stepping with dummy batches so that its peers' expert-parallel exchanges complete).  Every rank sees the
+        same agreement, so all of them leave the loop after the same step."""
         outs: dict = {}
         for _ in range(max_steps):
-            if not self.has_unfinished:
+            if not self.has_unfinished and self._world == 1:
                 break
             for r in self.step():
                 outs.setdefault(r.request_id, []).extend(r.new_token_ids)
+            if self._world > 1 and not self.has_unfinished and not self.peers_busy:
+                break
         return outs
 
 

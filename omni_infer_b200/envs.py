@@ -19,6 +19,7 @@ env_variables: dict[str, Callable[[], Any]] = {
     "MODEL_EXTRA_CFG_PATH": _S("MODEL_EXTRA_CFG_PATH", ""),
     "OMNI_GRAPH_CACHE_HOME": _S("OMNI_GRAPH_CACHE_HOME", os.path.expanduser("~/.cache/omni_infer_b200")),
     "NO_GPU_MOCK": _B("NO_GPU_MOCK"),
+    "OMNI_INIT_ON_HOST": _B("OMNI_INIT_ON_HOST"),               # random-init weights drawn on the CPU (tiny models)
     "FORCE_ENABLE_CHUNK_PREFILL": _B("FORCE_ENABLE_CHUNK_PREFILL"),
     # PD disaggregation
     "ROLE": _S("ROLE", "mixed"),

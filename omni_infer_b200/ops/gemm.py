@@ -116,12 +116,6 @@ def _tm2(kind, e, w, x, out, G, n_out, K, T, seg_start, seg_len, w_scale, x_scal
     nat.check_rc(rc, "omni_gemm_tm2")
 
 
-def _fp8_impl():
-    """Which fp8 kernel ``gemm`` uses: "tokmajor" (default) or "swapab" (weights on the UMMA M dimension)."""
-    import os
-    return os.environ.get("OMNI_FP8_GEMM", "tokmajor")
-
-
 def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi="store",
          row_scale=None, out_dtype=None, out=None, out_scale=None, bn=0, t_hint=0):
     """``out[t] = epi(x[t] @ w[g(t)].T)``.
@@ -165,7 +159,7 @@ def gemm(x, w, *, w_scale=None, x_scale=None, seg_start=None, seg_len=None, epi=
         if out is None:
             out = torch.empty(T, n_out, dtype=out_dtype if e == 0 else torch.bfloat16, device=x.device)
         out_f32 = 1 if out.dtype == torch.float32 else 0
-    tm_ok = n_out % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and _fp8_impl() == "tokmajor"
+    tm_ok = n_out % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
     # fp8: always token-major (one scale multiplier per thread and K block).  bf16: token-major from 64 rows per
     # group on (vector stores, N = 256 tiles); below that, and for the split-K fp32 router GEMM, tokens stay on N.
     rows_hint = t_hint if (seg_len is not None and t_hint > 0) else T
@@ -216,8 +210,7 @@ def bmm_heads(x, w, out=None, out_col_offset=0):
         out = torch.empty(T, H, N, dtype=x.dtype, device=x.device)
     assert out.stride(2) == 1 and out.stride(0) == H * out.stride(1)
     base_out = out[:, :, out_col_offset:] if out_col_offset else out
-    if (T >= 64 and N % 8 == 0 and out.stride(0) % 8 == 0 and out.stride(1) % 8 == 0 and base_out.data_ptr() % 16 == 0
-            and _fp8_impl() == "tokmajor"):
+    if (T >= 64 and N % 8 == 0 and out.stride(0) % 8 == 0 and out.stride(1) % 8 == 0 and base_out.data_ptr() % 16 == 0):
         _tm2(0, 0, w, x, base_out, H, N, K, T, None, None, None, None, 0, None, None,
              x_group_col=x.stride(1), out_group_col=out.stride(1), out_ld=out.stride(0), x_ld=x.stride(0))
         return out

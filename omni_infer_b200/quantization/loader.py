@@ -242,16 +242,35 @@ def init_random_weights(model, seed: int = 0, std: float = 0.02) -> None:
     seeded from (seed, parameter name) and every routed expert from (seed, layer, logical expert id), so the
     weights do not depend on how many ranks the experts are sharded over: a 2-rank model is the same model as
     the 1-rank one.  Quantised tensors are drawn in fp32 and block-quantised on their device."""
+    import os
     import zlib
 
     params = dict(model.named_parameters())
+    # OMNI_INIT_ON_HOST=1 draws and quantises on the CPU and copies the result over: a handful of memcpys per
+    # tensor instead of a dozen small kernels (for tiny models whose first launches should be the model's own)
+    host_init = os.environ.get("OMNI_INIT_ON_HOST", "0") == "1"
 
     def gen(dev, *key):
+        if host_init:
+            dev = "cpu"
         g = torch.Generator(device=dev)
         g.manual_seed((seed * 1000003 + zlib.crc32("/".join(str(k) for k in key).encode())) % (2 ** 63 - 1))
         return g
 
     def fill(p, sp, g):
+        if host_init:
+            full = getattr(p, "tp_full_shape", None)
+            w = torch.randn(tuple(full) if full is not None else tuple(p.shape), generator=g, dtype=torch.float32) * std
+            s_ = None
+            if p.dtype == FP8:
+                w, s_ = quant_weight_fp8_block_ref(w)
+            if full is not None:
+                w = p.tp_slice_fn(w)
+                s_ = sp.tp_slice_fn(s_) if s_ is not None else None
+            p.copy_(w.to(p.dtype))
+            if s_ is not None:
+                sp.copy_(s_)
+            return
         full = getattr(p, "tp_full_shape", None)
         if full is not None:
             # tensor-parallel shard: draw the whole tensor (so that the sharded model is the unsharded one), keep this
@@ -300,7 +319,7 @@ def init_random_weights(model, seed: int = 0, std: float = 0.02) -> None:
         elif name.endswith("bias") and p.dim() == 1 and "e_score" not in name:
             p.zero_()
         elif name.endswith("e_score_correction_bias"):
-            p.copy_(torch.randn(p.shape, generator=g, device=p.device) * 0.01)
+            p.copy_(torch.randn(p.shape, generator=g, device=g.device) * 0.01)
         else:
             fill(p, params.get(name + "_scale"), g)
     model.process_weights_after_loading()

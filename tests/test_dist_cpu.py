@@ -95,6 +95,42 @@ def test_expert_parallel_matches_single_rank():
     assert two[0] == single and two[1] == single
 
 
+def _ep_uneven(rank, world, mode):
+    """Data-parallel ranks with different work: rank 0 serves three long requests, rank 1 one short request
+    (mode "uneven") or none at all (mode "idle").  With multi-step decode and an MTP drafter the ranks need
+    different numbers of model rounds per step; the agreement pads the quieter rank with dummy rounds."""
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    kw = dict(block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=3)
+    if mode != "plain":
+        kw.update(num_step=2, num_speculative_tokens=1, model_overrides={"num_nextn_predict_layers": 1})
+    eng = EngineCore(EngineConfig(**kw))
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (20 + 3 * i,), generator=g).tolist() for i in range(3)]
+    if world == 1 or rank == 0:
+        ids = [eng.add_request(p, SamplingParams(max_tokens=9)) for p in prompts]
+    elif mode == "idle":
+        ids = []
+    else:
+        ids = [eng.add_request(prompts[1], SamplingParams(max_tokens=3))]
+    outs = eng.run_until_done(max_steps=200)
+    if dist.is_initialized():
+        dist.barrier()
+    return [outs[i] for i in ids]
+
+
+@pytest.mark.parametrize("mode", ["uneven", "idle"])
+def test_uneven_data_parallel_ranks_stay_in_step(mode):
+    """Neither rank waits for an exchange its peer never joins, and the busy rank's tokens equal a single-rank run."""
+    single = _spawn(_ep_uneven, 1, mode)[0]
+    two = _spawn(_ep_uneven, 2, mode)
+    assert two[0] == single
+    if mode == "uneven":
+        assert two[1] == [single[1][:3]]
+    else:
+        assert two[1] == []
+
+
 # ---------------------------------------------------------------------------------------------- TP attention
 def _tp_engine(rank, world):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore

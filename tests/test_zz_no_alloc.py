@@ -44,9 +44,17 @@ def test_noalloc_matches_regular_entry_point_twice():
         sl = torch.tensor(lens, dtype=torch.int32, device=dev)
         want = A.mla_decode(q, cache, bt, sl, scale, num_splits=splits)      # regular path, caller scratch
         got = torch.empty(Bq, H, 512, dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        reserved_before = torch.cuda.memory_reserved()
         rc = _call_noalloc(lib, q, cache.view(-1, 576), bt, sl, H, bs, scale, splits, got, status)
         assert rc == 0, f"call {call}: rc={rc}"
         torch.cuda.synchronize()
+        # the property in the name: neither the driver nor torch's pool handed out memory for the call
+        # (the very first call may still load the module lazily, so only the second one is held to it)
+        if call > 0:
+            assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.cuda.memory_reserved() == reserved_before
         assert status.tolist()[0] == 0
         torch.testing.assert_close(got.float(), want.float(), rtol=3e-2, atol=2e-2)
         ref = A.mla_decode_ref(q, cache, bt, sl, scale)
@@ -66,3 +74,26 @@ def test_noalloc_rejects_oversized_problem():
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     rc = _call_noalloc(lib, q, cache.view(-1, 576), bt, sl, 128, 128, 0.1, 8, out, status)
     assert rc == -100
+
+
+def test_noalloc_single_split_has_no_size_limit():
+    """One split never touches the built-in scratch, so a batch far above the split-KV limit is accepted."""
+    from omni_infer_b200.ops import _native as nat
+    from omni_infer_b200.ops import attention as A
+
+    lib = ctypes.CDLL(str(nat.lib_path()))
+    torch.manual_seed(1)
+    dev = "cuda"
+    Bq, H, bs, scale = 96, 128, 128, 1.0 / math.sqrt(192)      # 96 * 128 = 12288 parts > 8192
+    cache = (torch.randn(Bq + 1, bs, 576, device=dev) * 0.5).bfloat16()
+    bt = (torch.arange(Bq, device=dev, dtype=torch.int32) + 1).view(Bq, 1).contiguous()
+    q = (torch.randn(Bq, H, 576, device=dev) * 0.5).bfloat16()
+    sl = torch.full((Bq,), 100, dtype=torch.int32, device=dev)
+    out = torch.empty(Bq, H, 512, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    rc = _call_noalloc(lib, q, cache.view(-1, 576), bt, sl, H, bs, scale, 1, out, status)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    ref = A.mla_decode_ref(q, cache, bt, sl, scale)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=3e-2, atol=2e-2)
