@@ -3,6 +3,7 @@
 //                         vocab-parallel heads
 //   omni_sample_topk_topp temperature / top-k / top-p sampling, one CTA per row (exact, sort-free:
 //                         threshold search on the probability mass)
+//   omni_apply_penalties  repetition / frequency / presence penalties from each row's token history
 //   omni_mtp_verify       MTP draft verification and next drafter inputs
 //   omni_step_advance     multi-step decode: positions+1, seq_lens+1, next slot from the block table
 //   omni_embedding        (vocab-parallel) embedding gather
@@ -266,6 +267,47 @@ __global__ void omni_attn_slots_kernel(const int* __restrict__ seq_lens, const i
   if (eff_lens) eff_lens[b] = min(L, cap);
 }
 
+
+// Sampling penalties, one CTA per row (omni/models/common/layers/sampler.py:143-200).  hist[row, :] holds the
+// row's prompt tokens followed by its output tokens, -1 padded; the first prompt_len[row] entries are prompt.
+//   repetition: logits of tokens seen in prompt or output are divided (if > 0) or multiplied (if <= 0) by rep
+//   frequency:  logits -= freq * (occurrences among the output tokens)
+//   presence:   logits -= pres * (token occurs among the output tokens)
+// counts[row, :] (int32 per vocabulary entry) is scratch owned by the row's CTA: cleared, filled with atomics
+// (bit 30 = "seen in the prompt", low bits = output occurrences), then read back.  Rows whose three
+// parameters are neutral return at once.
+template <typename T>
+__global__ void __launch_bounds__(1024) penalties_kernel(T* __restrict__ logits, int V, int ld, const int* __restrict__ hist,
+                                                        int hist_ld, const int* __restrict__ prompt_len,
+                                                        const float* __restrict__ rep, const float* __restrict__ freq,
+                                                        const float* __restrict__ pres, int* __restrict__ counts) {
+  const int row = blockIdx.x;
+  const float r = rep[row], f = freq[row], pz = pres[row];
+  if (r == 1.0f && f == 0.0f && pz == 0.0f) return;
+  int* cnt = counts + (size_t)row * V;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  const int* h = hist + (size_t)row * hist_ld;
+  const int np = prompt_len[row];
+  for (int i = threadIdx.x; i < hist_ld; i += blockDim.x) {
+    const int t = h[i];
+    if (t < 0 || t >= V) continue;
+    if (i < np) atomicOr(&cnt[t], 1 << 30);
+    else atomicAdd(&cnt[t], 1);
+  }
+  __syncthreads();
+  T* lr = logits + (size_t)row * ld;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const int c = cnt[i];
+    if (c == 0) continue;
+    float v = to_f<T>(lr[i]);
+    if (r != 1.0f) v = v > 0.f ? v / r : v * r;
+    const int n_out = c & ((1 << 30) - 1);
+    if (n_out > 0) v -= f * (float)n_out + pz;
+    lr[i] = (T)v;
+  }
+}
+
 }  // namespace omni
 
 using namespace omni;
@@ -331,5 +373,19 @@ extern "C" int omni_omni_attn_slots(const int* seq_lens, const int* prompt_lens,
   if (B <= 0) return 0;
   omni_attn_slots_kernel<<<(B + 127) / 128, 128, 0, stream>>>(seq_lens, prompt_lens, block_table, bt_ld, block_size,
                                                               sink, recent, B, slots, eff_lens);
+  return (int)cudaGetLastError();
+}
+
+// In place on logits [B, V] (fp32 or bf16).  counts: int32 scratch [B, V].
+extern "C" int omni_apply_penalties(void* logits, int is_bf16, int B, int V, int ld, const int* hist, int hist_ld,
+                                    const int* prompt_len, const float* rep, const float* freq, const float* pres,
+                                    int* counts, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (hist == nullptr || counts == nullptr) return -1;
+  if (is_bf16)
+    penalties_kernel<__nv_bfloat16><<<B, 1024, 0, stream>>>((__nv_bfloat16*)logits, V, ld, hist, hist_ld, prompt_len, rep,
+                                                            freq, pres, counts);
+  else
+    penalties_kernel<float><<<B, 1024, 0, stream>>>((float*)logits, V, ld, hist, hist_ld, prompt_len, rep, freq, pres, counts);
   return (int)cudaGetLastError();
 }

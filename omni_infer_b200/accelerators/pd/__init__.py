@@ -9,9 +9,34 @@ CONNECTOR_NAME = "B200PeerPushConnectorV1"       # the reference registers "Asce
 _ids = itertools.count()
 
 
+COMPAT_NAMES = ("AscendHcclConnectorV1",)       # accepted so that existing kv-transfer configs keep working
+_REGISTERED: dict = {}
+
+
 def register() -> dict:
-    """Entry point kept from the reference's ``vllm.general_plugins`` hook ``kv_connectors``."""
-    return {CONNECTOR_NAME: "omni_infer_b200.accelerators.pd.connector"}
+    """Entry point ``vllm.general_plugins`` / ``kv_connectors`` (reference: omni/accelerators/pd/__init__.py):
+    registers the connector under its name (and the reference's name as an alias) in this package's table and,
+    when the host engine imports, with that engine's connector factory."""
+    mod, cls = "omni_infer_b200.accelerators.pd.connector", "WorkerConnector"
+    for name in (CONNECTOR_NAME, *COMPAT_NAMES):
+        _REGISTERED[name] = (mod, cls)
+    try:
+        from vllm.distributed.kv_transfer.kv_connector.factory import KVConnectorFactory
+        for name in (CONNECTOR_NAME, *COMPAT_NAMES):
+            if name not in getattr(KVConnectorFactory, "_registry", {}):
+                KVConnectorFactory.register_connector(name, mod, cls)
+    except Exception:  # noqa: BLE001  (no host engine: the in-repo engine uses create_connectors directly)
+        pass
+    return {name: mod for name in _REGISTERED}
+
+
+def get_connector_class(name: str):
+    """Resolve a connector name from a kv-transfer config to its class."""
+    import importlib
+    if not _REGISTERED:
+        register()
+    mod, cls = _REGISTERED[name]
+    return getattr(importlib.import_module(mod), cls)
 
 
 def create_connectors(kv_transfer_config: dict, block_size: int = 128, num_speculative_tokens: int = 0):
@@ -23,7 +48,7 @@ def create_connectors(kv_transfer_config: dict, block_size: int = 128, num_specu
     endpoint = c.get("endpoint", f"inproc://{eid}")
     transport = c.get("transport", "inproc" if endpoint.startswith("inproc") else "tcp")
     worker = WorkerConnector(role, eid, endpoint, transport, float(c.get("sync_timeout_s", 20.0)), int(c.get("retries", 3)),
-                             float(c.get("retry_wait_s", 2.0)))
+                             float(c.get("retry_wait_s", 2.0)), authkey=c.get("authkey"))
     sched = SchedulerConnector(role, eid, endpoint, block_size, num_speculative_tokens,
                                worker=worker if c.get("async_pull_kv", True) else None)
     return sched, worker

@@ -17,8 +17,10 @@ the CUDA IPC handles of its cache tensors on first contact.
 
 Robustness: a push request is retried ``retries`` times ``retry_wait_s`` apart and abandoned after
 ``sync_timeout_s`` (reference: 3 x 2 s, 20 s); an abandoned request is reported in ``failed_recving`` and the
-scheduler falls back to prefilling it locally.  Duplicate acknowledgements and acknowledgements for unknown
-requests are ignored."""
+scheduler falls back to prefilling it locally.  Every push carries an attempt id: only the acknowledgement of the
+attempt being waited for counts, a producer that does not know the request answers ``nack`` (local prefill at once,
+never a decode on blocks nobody wrote), and a consumer that gives up sends ``cancel`` and frees the blocks only after
+the producer confirmed that nothing of that attempt is being written any more."""
 from __future__ import annotations
 
 import logging
@@ -81,19 +83,71 @@ class InProcessHub:
     def send_ack(cls, endpoint: str, msg: dict) -> None:
         w = cls.endpoints.get(endpoint)
         if w is not None:
-            w.handle_ack(msg)
-            if cls.duplicate_acks:
-                w.handle_ack(msg)
+            w.dispatch(msg)
+            if cls.duplicate_acks and msg.get("op") == "ack":
+                w.dispatch(msg)
+
+    @classmethod
+    def send_cancel(cls, endpoint: str, msg: dict) -> bool:
+        w = cls.endpoints.get(endpoint)
+        if w is None:
+            return False
+        threading.Thread(target=w.dispatch, args=(msg,), daemon=True).start()
+        return True
+
+
+def _authkey(key=None) -> bytes:
+    """Shared secret of the control channel: the ``authkey`` of the kv-transfer config, else ``OMNI_KV_AUTHKEY``.
+    Without one the channel only accepts loopback endpoints."""
+    import os
+    k = key or os.environ.get("OMNI_KV_AUTHKEY", "")
+    return k.encode() if isinstance(k, str) else bytes(k)
+
+
+def _encode(msg: dict) -> bytes:
+    """Wire format: one JSON document per connection (bytes values, the CUDA IPC handles, as base64)."""
+    import base64
+    import json
+
+    def conv(o):
+        if isinstance(o, (bytes, bytearray)):
+            return {"__b64__": base64.b64encode(bytes(o)).decode()}
+        if isinstance(o, dict):
+            return {k: conv(v) for k, v in o.items()}
+        if isinstance(o, (list, tuple)):
+            return [conv(v) for v in o]
+        return o
+    return json.dumps(conv(msg)).encode()
+
+
+def _decode(raw: bytes) -> dict:
+    import base64
+    import json
+
+    def conv(o):
+        if isinstance(o, dict):
+            if set(o) == {"__b64__"}:
+                return base64.b64decode(o["__b64__"])
+            return {k: conv(v) for k, v in o.items()}
+        if isinstance(o, list):
+            return [conv(v) for v in o]
+        return o
+    return conv(json.loads(raw.decode()))
 
 
 class TcpTransport:
-    """Control channel between processes.  Every worker connector listens on its endpoint; messages are pickled
-    dicts: {'op': 'push', ...} consumer -> producer, {'op': 'ack', ...} producer -> consumer."""
+    """Control channel between processes.  Every worker connector listens on its endpoint.  A message is one JSON
+    document sent as a byte frame (nothing is unpickled); the connection handshake uses the configured key.
+    Messages: push / cancel consumer -> producer, ack / nack / cancel_ack producer -> consumer."""
 
-    def __init__(self, endpoint: str, worker):
+    def __init__(self, endpoint: str, worker, authkey=None):
         from multiprocessing.connection import Listener
         host, port = endpoint.replace("tcp://", "").rsplit(":", 1)
-        self.listener = Listener((host, int(port)), authkey=b"omni-pd")
+        self.key = _authkey(authkey)
+        if not self.key and host not in ("127.0.0.1", "localhost", "::1"):
+            raise ValueError("a kv-transfer endpoint that is not loopback needs an authkey (config 'authkey' or OMNI_KV_AUTHKEY)")
+        self.key = self.key or b"omni-pd-loopback"
+        self.listener = Listener((host, int(port)), authkey=self.key)
         self.worker = worker
         self._stop = False
         threading.Thread(target=self._serve, daemon=True).start()
@@ -104,30 +158,28 @@ class TcpTransport:
                 conn = self.listener.accept()
             except OSError:
                 return
+            except Exception:  # noqa: BLE001  (failed handshake of a stranger)
+                continue
             threading.Thread(target=self._handle, args=(conn,), daemon=True).start()
 
     def _handle(self, conn):
         try:
-            msg = conn.recv()
-            if msg.get("op") == "push":
-                self.worker.handle_push_request(msg)
-            elif msg.get("op") == "ack":
-                self.worker.handle_ack(msg)
-        except (EOFError, OSError):
+            msg = _decode(conn.recv_bytes(1 << 22))
+            self.worker.dispatch(msg)
+        except (EOFError, OSError, ValueError, KeyError):
             pass
         finally:
             conn.close()
 
-    @staticmethod
-    def send(endpoint: str, msg: dict, timeout_s: float = 5.0) -> bool:
+    def send(self, endpoint: str, msg: dict) -> bool:
         from multiprocessing.connection import Client
         host, port = endpoint.replace("tcp://", "").rsplit(":", 1)
         try:
-            c = Client((host, int(port)), authkey=b"omni-pd")
-            c.send(msg)
+            c = Client((host, int(port)), authkey=self.key)
+            c.send_bytes(_encode(msg))
             c.close()
             return True
-        except (OSError, EOFError):
+        except Exception:  # noqa: BLE001
             return False
 
     def close(self):
@@ -199,8 +251,10 @@ class SchedulerConnector:
 
 # ------------------------------------------------------------------------------------------------ worker side
 class WorkerConnector:
+    SERVED_LIMIT = 4096          # producer: how many served request ids are remembered for re-acknowledgement
+
     def __init__(self, kv_role: str, engine_id: str, endpoint: str, transport: str = "inproc", sync_timeout_s: float = 20.0,
-                 retries: int = 3, retry_wait_s: float = 2.0):
+                 retries: int = 3, retry_wait_s: float = 2.0, authkey=None):
         self.kv_role, self.engine_id, self.endpoint, self.transport = kv_role, engine_id, endpoint, transport
         self.sync_timeout_s, self.retries, self.retry_wait_s = sync_timeout_s, retries, retry_wait_s
         self.kv_tensors: list = []
@@ -209,14 +263,19 @@ class WorkerConnector:
         self._done_recv: set = set()
         self._failed_recv: set = set()
         self._done_send: set = set()
-        self._inflight: dict = {}          # request id -> ReqMeta (consumer)
+        self._inflight: dict = {}          # consumer: request id -> (ReqMeta, attempt id)
+        self._cancel_acked: set = set()    # consumer: (request id, attempt) whose cancel the producer confirmed
+        self._attempts = 0
         self._expected: set = set()        # producer: requests whose blocks wait to be pushed
+        self._served: dict = {}            # producer: request id -> attempt id of the push that was served (bounded)
+        self._cancelled: set = set()       # producer: (request id, attempt) the consumer gave up on
+        self._copying: set = set()         # producer: request ids whose copy is running right now
         self._peer_views: dict = {}        # producer: consumer endpoint -> cache view
         self._tcp = None
         if transport == "inproc":
             InProcessHub.register(endpoint, self)
         else:
-            self._tcp = TcpTransport(endpoint, self)
+            self._tcp = TcpTransport(endpoint, self, authkey)
 
     # -- set-up
     def register_kv_caches(self, kv_caches) -> None:
@@ -241,8 +300,10 @@ class WorkerConnector:
             return
         for r in meta.requests:
             with self._lock:
-                self._inflight[r.request_id] = r
-            threading.Thread(target=self._request_push, args=(r,), daemon=True).start()
+                self._attempts += 1
+                attempt = f"{self.engine_id}:{self._attempts}"
+                self._inflight[r.request_id] = (r, attempt)
+            threading.Thread(target=self._request_push, args=(r, attempt), daemon=True).start()
 
     def wait_for_save(self) -> None:
         """Producer side: blocks are written by the forward pass itself; nothing to flush."""
@@ -262,41 +323,91 @@ class WorkerConnector:
         with self._lock:
             self._expected.add(request_id)
 
-    # -- consumer: ask the producer to push, wait for the acknowledgement
+    # -- message plumbing
+    def dispatch(self, msg: dict) -> None:
+        op = msg.get("op")
+        if op == "push":
+            self.handle_push_request(msg)
+        elif op == "ack":
+            self.handle_ack(msg)
+        elif op == "nack":
+            self.handle_nack(msg)
+        elif op == "cancel":
+            self.handle_cancel(msg)
+        elif op == "cancel_ack":
+            with self._lock:
+                self._cancel_acked.add((msg["request_id"], msg.get("attempt")))
+
     def _send(self, endpoint: str, msg: dict) -> bool:
         if self.transport == "inproc":
             if msg["op"] == "push":
                 return InProcessHub.send_push_request(endpoint, msg)
+            if msg["op"] == "cancel":
+                return InProcessHub.send_cancel(endpoint, msg)
             InProcessHub.send_ack(endpoint, msg)
             return True
-        return TcpTransport.send(endpoint, msg)
+        return self._tcp.send(endpoint, msg)
 
-    def _request_push(self, r: ReqMeta) -> None:
-        msg = {"op": "push", "request_id": r.request_id, "src_blocks": r.remote_block_ids, "dst_blocks": r.local_block_ids,
-               "reply_to": self.endpoint, "consumer": self.engine_id}
+    # -- consumer: ask the producer to push, wait for the acknowledgement
+    def _still_waiting(self, rid: str, attempt: str) -> bool:
+        with self._lock:
+            cur = self._inflight.get(rid)
+            return cur is not None and cur[1] == attempt
+
+    def _request_push(self, r: ReqMeta, attempt: str) -> None:
+        msg = {"op": "push", "request_id": r.request_id, "attempt": attempt, "src_blocks": r.remote_block_ids,
+               "dst_blocks": r.local_block_ids, "reply_to": self.endpoint, "consumer": self.engine_id}
         if self.transport != "inproc":
             msg["cache"] = self.cache_descriptor()
         deadline = time.monotonic() + self.sync_timeout_s
-        for attempt in range(self.retries + 1):
+        for n in range(self.retries + 1):
             self._send(r.remote_host, msg)
-            wait_until = min(deadline, time.monotonic() + self.retry_wait_s)
+            # the last send waits out the whole synchronisation timeout, earlier ones one retry interval
+            wait_until = deadline if n == self.retries else min(deadline, time.monotonic() + self.retry_wait_s)
             while time.monotonic() < wait_until:
-                with self._lock:
-                    if r.request_id not in self._inflight:
-                        return                       # acknowledged
+                if not self._still_waiting(r.request_id, attempt):
+                    return                       # acknowledged, or refused by the producer
                 time.sleep(0.002)
             if time.monotonic() >= deadline:
                 break
-            logger.warning("kv push for %s not acknowledged, retry %d", r.request_id, attempt + 1)
+            logger.warning("kv push for %s not acknowledged, retry %d", r.request_id, n + 1)
+        # Give up.  A push that is still on its way must not land in blocks that were handed to another request:
+        # tell the producer, and release the blocks only when it has confirmed (it waits for a running copy) or
+        # stays silent for another retry interval (then it is gone and cannot write either).
+        self._send(r.remote_host, {"op": "cancel", "request_id": r.request_id, "attempt": attempt, "reply_to": self.endpoint})
+        t_end = time.monotonic() + max(self.retry_wait_s, 0.05)
+        while time.monotonic() < t_end:
+            with self._lock:
+                if (r.request_id, attempt) in self._cancel_acked:
+                    self._cancel_acked.discard((r.request_id, attempt))
+                    break
+            if not self._still_waiting(r.request_id, attempt):
+                return                           # the acknowledgement overtook the cancel: the blocks are good
+            time.sleep(0.002)
         with self._lock:
-            if self._inflight.pop(r.request_id, None) is not None:
+            cur = self._inflight.get(r.request_id)
+            if cur is not None and cur[1] == attempt:
+                del self._inflight[r.request_id]
                 self._failed_recv.add(r.request_id)
         logger.error("kv push for %s abandoned after %.1fs", r.request_id, self.sync_timeout_s)
 
     def handle_ack(self, msg: dict) -> None:
+        """Only the acknowledgement of the attempt that is being waited for counts: duplicates, strangers and late
+        acknowledgements of an abandoned attempt are ignored."""
         with self._lock:
-            if self._inflight.pop(msg["request_id"], None) is not None:     # duplicates and strangers are ignored
+            cur = self._inflight.get(msg["request_id"])
+            if cur is not None and msg.get("attempt", cur[1]) == cur[1]:
+                del self._inflight[msg["request_id"]]
                 self._done_recv.add(msg["request_id"])
+
+    def handle_nack(self, msg: dict) -> None:
+        """The producer does not know the request (it restarted, or freed the blocks): nothing was written, so the
+        request goes to the local-prefill fallback at once instead of decoding on an empty cache."""
+        with self._lock:
+            cur = self._inflight.get(msg["request_id"])
+            if cur is not None and msg.get("attempt", cur[1]) == cur[1]:
+                del self._inflight[msg["request_id"]]
+                self._failed_recv.add(msg["request_id"])
 
     # -- producer: copy the blocks into the consumer's cache, then acknowledge
     def _peer_cache(self, msg: dict):
@@ -310,25 +421,58 @@ class WorkerConnector:
         return self._peer_views[key]
 
     def handle_push_request(self, msg: dict) -> None:
-        rid = msg["request_id"]
+        rid, attempt = msg["request_id"], msg.get("attempt")
         with self._lock:
+            if (rid, attempt) in self._cancelled:
+                return                           # the consumer already gave this attempt up
+            if rid in self._copying:
+                return                           # a retry while the first copy is still running: one ack will follow
+            served = self._served.get(rid, False)
             known = rid in self._expected
+            if known:
+                self._copying.add(rid)
         if not known:
-            logger.warning("push request for unknown or already served request %s", rid)
-            # a retry of a request that was served: acknowledge again so the consumer can stop waiting
-            self._send(msg["reply_to"], {"op": "ack", "request_id": rid})
+            if served is not False and served == attempt:
+                # a retry of the attempt that was served (its acknowledgement was lost): acknowledge again
+                self._send(msg["reply_to"], {"op": "ack", "request_id": rid, "attempt": attempt})
+            else:
+                logger.warning("push request for unknown request %s refused", rid)
+                self._send(msg["reply_to"], {"op": "nack", "request_id": rid, "attempt": attempt})
             return
-        peer = self._peer_cache(msg)
-        if isinstance(peer, PeerCacheView):
-            push_blocks_cuda(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
-        else:
-            push_blocks_torch(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
-            if self.kv_tensors and self.kv_tensors[0].is_cuda:
-                torch.cuda.synchronize()
+        try:
+            peer = self._peer_cache(msg)
+            if isinstance(peer, PeerCacheView):
+                push_blocks_cuda(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
+            else:
+                push_blocks_torch(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
+                if self.kv_tensors and self.kv_tensors[0].is_cuda:
+                    torch.cuda.synchronize()
+        finally:
+            with self._lock:
+                self._copying.discard(rid)
         with self._lock:
             self._expected.discard(rid)
             self._done_send.add(rid)
-        self._send(msg["reply_to"], {"op": "ack", "request_id": rid})
+            self._served[rid] = attempt
+            while len(self._served) > self.SERVED_LIMIT:
+                self._served.pop(next(iter(self._served)))
+        self._send(msg["reply_to"], {"op": "ack", "request_id": rid, "attempt": attempt})
+
+    def handle_cancel(self, msg: dict) -> None:
+        rid, attempt = msg["request_id"], msg.get("attempt")
+        with self._lock:
+            self._cancelled.add((rid, attempt))
+            if len(self._cancelled) > self.SERVED_LIMIT:
+                self._cancelled.pop()
+        # a copy of this request that is running right now finishes first: after the confirmation nothing of this
+        # attempt is written any more
+        t_end = time.monotonic() + 5.0
+        while time.monotonic() < t_end:
+            with self._lock:
+                if rid not in self._copying:
+                    break
+            time.sleep(0.001)
+        self._send(msg["reply_to"], {"op": "cancel_ack", "request_id": rid, "attempt": attempt})
 
     def close(self) -> None:
         if self._tcp is not None:

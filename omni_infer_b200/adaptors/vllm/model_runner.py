@@ -400,8 +400,30 @@ class ModelRunner:
         return d64[:n], md
 
     # ------------------------------------------------------------------ sampling
+    def _penalise(self, logits: torch.Tensor, reqs: list, rows_per_req: int) -> torch.Tensor:
+        """Repetition / frequency / presence penalties of the requests that ask for them; every row of a request
+        (its verified token and its draft positions) sees the request's token history."""
+        if not any(r.sampling.has_penalties for r in reqs):
+            return logits
+        n = logits.shape[0]
+        width = max(r.num_tokens for r in reqs)
+        hist = torch.full((n, width), -1, dtype=torch.int32)
+        npr = torch.zeros(n, dtype=torch.int32)
+        rep, freq, pres = torch.ones(n), torch.zeros(n), torch.zeros(n)
+        for i, r in enumerate(reqs):
+            if not r.sampling.has_penalties:
+                continue
+            sl = slice(i * rows_per_req, (i + 1) * rows_per_req)
+            toks = torch.tensor(r.all_token_ids, dtype=torch.int32)
+            hist[sl, : toks.numel()] = toks
+            npr[sl] = r.num_prompt_tokens
+            rep[sl], freq[sl], pres[sl] = r.sampling.repetition_penalty, r.sampling.frequency_penalty, r.sampling.presence_penalty
+        dev = self.device
+        return ops.apply_penalties(logits, hist.to(dev), npr.to(dev), rep.to(dev), freq.to(dev), pres.to(dev))
+
     def _sample(self, logits: torch.Tensor, reqs: list, rows_per_req: int) -> torch.Tensor:
         """logits [len(reqs) * rows_per_req (+ padding), V] -> token ids (padding rows included)."""
+        logits = self._penalise(logits, reqs, rows_per_req)
         if all(r.sampling.greedy for r in reqs):
             return ops.argmax(logits)
         n = logits.shape[0]
@@ -497,7 +519,7 @@ class ModelRunner:
         spec_final = None
         for step in range(so.num_step):
             hidden, logits = self._forward_decode(ids, md, padded)
-            toks = self._sample(logits, reqs, tpr) if not all(r.sampling.greedy for r in reqs) else ops.argmax(logits)
+            toks = self._sample(logits, reqs, tpr)
             if tpr == 1:
                 steps_out.append(toks[:B])
                 if step + 1 < so.num_step:

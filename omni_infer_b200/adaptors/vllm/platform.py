@@ -60,8 +60,21 @@ class ConfigUpdater:
         return engine_cfg
 
 
-class B200Platform:
-    _enum = "OOT"
+def _host_platform_base():
+    """The host engine's ``Platform`` base class and its out-of-tree enum value when that engine imports; a plain
+    ``object`` otherwise, so that the in-repo engine does not depend on it."""
+    try:
+        from vllm.platforms.interface import Platform, PlatformEnum
+        return Platform, PlatformEnum.OOT
+    except Exception:  # noqa: BLE001  (absent, or built for another torch)
+        return object, "OOT"
+
+
+_Base, _OOT = _host_platform_base()
+
+
+class B200Platform(_Base):
+    _enum = _OOT
     device_name = "cuda"
     device_type = "cuda"
     dispatch_key = "CUDA"
@@ -79,11 +92,60 @@ class B200Platform:
 
     @classmethod
     def check_and_update_config(cls, engine_cfg, additional_config=None) -> None:
+        """Called by the host engine with its ``VllmConfig`` (worker class, block size 128, additional-config
+        switches; reference: platform.py:179-259, 375-390) or by the in-repo engine with an ``EngineConfig``."""
+        if hasattr(engine_cfg, "parallel_config"):
+            pc = engine_cfg.parallel_config
+            if getattr(pc, "worker_cls", "auto") in ("auto", None):
+                pc.worker_cls = WORKER_CLS
+            cc = getattr(engine_cfg, "cache_config", None)
+            if cc is not None and not getattr(cc, "block_size", None):
+                cc.block_size = 128
+            add = getattr(engine_cfg, "additional_config", None) or {}
+            sc = getattr(engine_cfg, "scheduler_config", None)
+            if sc is not None and isinstance(add, dict) and add.get("enable_hybrid_graph_mode"):
+                sc.scheduler_cls = "omni_infer_b200.engine.scheduler.Scheduler"
+            return
         ConfigUpdater.update_engine_config(engine_cfg, additional_config)
 
     @classmethod
-    def get_attn_backend_cls(cls, use_mla: bool) -> str:
+    def get_attn_backend_cls(cls, use_mla=False, *args, **kwargs) -> str:
+        # the host engine passes (selected_backend, attn_selector_config, ...); MLA models are told apart by use_mla
+        if not isinstance(use_mla, bool):
+            sel = args[0] if args else kwargs.get("attn_selector_config")
+            use_mla = bool(getattr(sel, "use_mla", kwargs.get("use_mla", False)))
         return ("omni_infer_b200.layers.mla.MLAAttention" if use_mla else "omni_infer_b200.layers.gqa.GQAAttention")
+
+    @classmethod
+    def get_device_capability(cls, device_id: int = 0):
+        if not torch.cuda.is_available():
+            return None
+        major, minor = torch.cuda.get_device_capability(device_id)
+        try:
+            from vllm.platforms.interface import DeviceCapability
+            return DeviceCapability(major=major, minor=minor)
+        except Exception:  # noqa: BLE001
+            return (major, minor)
+
+    @classmethod
+    def get_device_total_memory(cls, device_id: int = 0) -> int:
+        return torch.cuda.get_device_properties(device_id).total_memory if torch.cuda.is_available() else 0
+
+    @classmethod
+    def set_device(cls, device) -> None:
+        if torch.cuda.is_available():
+            torch.cuda.set_device(device)
+
+    @classmethod
+    def get_current_memory_usage(cls, device=None) -> float:
+        if not torch.cuda.is_available():
+            return 0.0
+        torch.cuda.reset_peak_memory_stats(device)
+        return float(torch.cuda.max_memory_allocated(device))
+
+    @classmethod
+    def inference_mode(cls):
+        return torch.inference_mode(mode=True)
 
     @classmethod
     def get_device_communicator_cls(cls) -> str:

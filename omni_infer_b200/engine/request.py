@@ -24,6 +24,10 @@ class SamplingParams:
     def greedy(self) -> bool:
         return self.temperature < 1e-5
 
+    @property
+    def has_penalties(self) -> bool:
+        return self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+
 
 class RequestStatus(enum.IntEnum):
     WAITING = 0

@@ -9,4 +9,4 @@ from .basic import (embedding, mla_kv_rope_cache, quant_fp8_block, rmsnorm, rope
 from .gemm import (FP8, bmm_heads, dequant_act_ref, dequant_weight_ref, gemm, gemm_ref, quant_fp8_block_ref,  # noqa: F401
                    quant_weight_fp8_block_ref)
 from .moe import MoePermutation, moe_combine, moe_permute, router_topk, router_topk_ref  # noqa: F401
-from .sampling import argmax, mtp_verify, omni_attn_slots, sample_topk_topp, step_advance  # noqa: F401
+from .sampling import apply_penalties, apply_penalties_ref, argmax, mtp_verify, omni_attn_slots, sample_topk_topp, step_advance  # noqa: F401

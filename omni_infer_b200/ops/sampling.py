@@ -25,6 +25,53 @@ def argmax(logits, vocab_offset=0, want_max=False):
     return (ids, mx) if want_max else ids
 
 
+def apply_penalties_ref(logits, hist, prompt_len, rep, freq, pres):
+    """fp32 reference of :func:`apply_penalties` (returns a new tensor)."""
+    B, V = logits.shape
+    out = logits.float().clone()
+    for b in range(B):
+        r, f, p = float(rep[b]), float(freq[b]), float(pres[b])
+        if r == 1.0 and f == 0.0 and p == 0.0:
+            continue
+        h = hist[b]
+        h = h[h >= 0].long()
+        npr = int(prompt_len[b])
+        seen = torch.zeros(V, dtype=torch.bool, device=logits.device)
+        seen[h] = True
+        cnt = torch.zeros(V, dtype=torch.float32, device=logits.device)
+        cnt.scatter_add_(0, h[npr:], torch.ones(h[npr:].numel(), device=logits.device))
+        row = out[b]
+        row = torch.where(seen, torch.where(row > 0, row / r, row * r), row)
+        row = row - f * cnt - p * (cnt > 0).float()
+        out[b] = row
+    return out.to(logits.dtype)
+
+
+_pen_scratch = {}
+
+
+def apply_penalties(logits, hist, prompt_len, rep, freq, pres):
+    """Repetition / frequency / presence penalties (omni/models/common/layers/sampler.py:143-200), in place on CUDA.
+
+    ``hist`` [B, L] int32: each row's prompt tokens followed by its output tokens, -1 padded; ``prompt_len`` [B]
+    int32; ``rep`` / ``freq`` / ``pres`` [B] fp32 (1, 0, 0 = no penalty).  Returns the penalised logits."""
+    if not logits.is_cuda:
+        return apply_penalties_ref(logits, hist, prompt_len, rep, freq, pres)
+    B, V = logits.shape
+    assert logits.stride(1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
+    key = logits.device.index
+    sc = _pen_scratch.get(key)
+    if sc is None or sc.numel() < B * V:
+        sc = _pen_scratch[key] = torch.empty(B * V, dtype=torch.int32, device=logits.device)
+    hist = hist.contiguous()
+    rc = nat.lib().omni_apply_penalties(
+        nat.ptr(logits), nat.c_int(1 if logits.dtype == torch.bfloat16 else 0), nat.c_int(B), nat.c_int(V),
+        nat.c_int(logits.stride(0)), nat.ptr(hist), nat.c_int(hist.shape[1]), nat.ptr(prompt_len), nat.ptr(rep),
+        nat.ptr(freq), nat.ptr(pres), nat.ptr(sc), nat.stream())
+    nat.check_rc(rc, "omni_apply_penalties")
+    return logits
+
+
 def sample_topk_topp_ref(logits, temperature, top_k, top_p, uniform):
     """Reference with the same semantics as the kernel: keep {p >= tau}, tau = max(k-th largest p,
     largest threshold whose kept mass >= top_p); inverse CDF in index order."""

@@ -67,3 +67,26 @@ def test_mtp_greedy_equivalence():
     mtp2 = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu",
                model_overrides=over, num_speculative_tokens=1, num_step=3)
     assert mtp2.generate(prompts, SamplingParams(max_tokens=14)) == want
+
+
+def test_sampling_penalties_change_greedy_output():
+    """A strong repetition penalty forbids tokens of the prompt and earlier outputs; presence / frequency penalties act on
+    output tokens only.  Reference semantics: omni/models/common/layers/sampler.py:143-200."""
+    import torch
+
+    from omni_infer_b200.engine.engine_core import LLM
+    from omni_infer_b200.engine.request import SamplingParams
+    from omni_infer_b200.ops.sampling import apply_penalties_ref
+
+    llm = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu", seed=0)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, 1024, (24,), generator=g).tolist()
+    plain = llm.generate([prompt], SamplingParams(max_tokens=12))[0]
+    pen = llm.generate([prompt], SamplingParams(max_tokens=12, repetition_penalty=1e6))[0]
+    assert len(set(pen)) == len(pen) and not (set(pen) & set(prompt))
+    assert plain != pen or len(set(plain)) == len(plain)
+    # reference arithmetic on a hand-made row
+    logits = torch.tensor([[2.0, -1.0, 0.5, 3.0]])
+    hist = torch.tensor([[0, 1, 3, 3, -1]], dtype=torch.int32)
+    out = apply_penalties_ref(logits, hist, torch.tensor([2]), torch.tensor([2.0]), torch.tensor([0.5]), torch.tensor([0.25]))
+    assert torch.allclose(out, torch.tensor([[1.0, -2.0, 0.5, 3.0 / 2 - 0.5 * 2 - 0.25]]))

@@ -256,6 +256,59 @@ def test_mla_decode(H, lens, bs, splits):
     _close(out, ref, 3e-2, 2e-2)
 
 
+@pytest.mark.parametrize("q_per_seq,seq_lens,splits", [(2, [300, 65, 1024], 1), (4, [64, 700], 1), (3, [129, 5, 2047], 2),
+                                                       (1, [63, 64, 65, 127, 128, 191, 192, 193], 1)])
+def test_mla_decode_query_rows_of_one_sequence(q_per_seq, seq_lens, splits):
+    """Several q rows per request (a verified token plus MTP drafts): row j of a request sees its length minus the
+    rows after it, all rows share one block-table row through q_to_seq; lengths around the 64-token tile edges so that
+    both CTAs of a pair get odd and even tile counts."""
+    torch.manual_seed(21)
+    H, bs = 128, 128
+    B_ = len(seq_lens)
+    max_blocks = (max(seq_lens) + bs - 1) // bs + 1
+    nblocks = B_ * max_blocks + 2
+    cache = (torch.randn(nblocks, bs, 576, device=DEV) * 0.5).bfloat16()
+    bt = (torch.randperm(nblocks - 1, device=DEV)[: B_ * max_blocks].int() + 1).view(B_, max_blocks).contiguous()
+    rows, q2s = [], []
+    for i, L in enumerate(seq_lens):
+        for j in range(q_per_seq):
+            rows.append(max(0, L - (q_per_seq - 1 - j)))
+            q2s.append(i)
+    Bq = len(rows)
+    q = (torch.randn(Bq, H, 576, device=DEV) * 0.5).bfloat16()
+    sl = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    q2 = torch.tensor(q2s, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(192)
+    out = A.mla_decode(q, cache, bt, sl, scale, q_to_seq=q2, num_splits=splits, max_seq_len=max(seq_lens))
+    ref = A.mla_decode_ref(q, cache, bt, sl, scale, q_to_seq=q2)
+    _close(out, ref, 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("pattern", ["late_peak", "early_peak", "alternating"])
+def test_mla_decode_wide_score_range(pattern):
+    """Scores whose maximum moves by far more than the lazy-rescale threshold between tiles: the late tiles dominate,
+    the first tile dominates, or odd and even tiles (computed by different CTAs of a pair) sit at different levels."""
+    torch.manual_seed(22)
+    H, bs, L = 128, 128, 640
+    cache = (torch.randn(8, bs, 576, device=DEV) * 0.3).bfloat16()
+    bt = (torch.arange(6, device=DEV, dtype=torch.int32) + 1).view(1, 6)
+    q = (torch.randn(1, H, 576, device=DEV) * 0.5).bfloat16()
+    flat = cache.view(-1, 576)
+    tile = torch.arange(L, device=DEV) // 64
+    boost = {"late_peak": (tile >= 8).float() * 6.0, "early_peak": (tile == 0).float() * 6.0,
+             "alternating": (tile % 2).float() * 5.0}[pattern]
+    # make the keys of the boosted tiles align with q's mean direction, so that their scores are far larger
+    direction = q[0].float().mean(0)
+    direction = direction / direction.norm()
+    slots = (bt[0, torch.arange(L, device=DEV) // bs].long() * bs + torch.arange(L, device=DEV) % bs)
+    flat[slots] = (flat[slots].float() + boost[:, None] * direction[None, :] * 30.0).bfloat16()
+    sl = torch.tensor([L], dtype=torch.int32, device=DEV)
+    scale = 1.0
+    out = A.mla_decode(q, cache, bt, sl, scale, num_splits=1, max_seq_len=L)
+    ref = A.mla_decode_ref(q, cache, bt, sl, scale)
+    _close(out, ref, 3e-2, 2e-2)
+
+
 @pytest.mark.parametrize("qlens,ctx", [([5, 130, 64], [0, 0, 0]), ([256], [0]), ([17, 100], [40, 0]), ([1, 1], [300, 5])])
 def test_fmha_mla_prefill(qlens, ctx):
     """Non-absorbed MLA prefill: q 192 wide, k = kv_b slice | shared roped k_pe, v = kv_b slice."""
@@ -304,3 +357,23 @@ def test_gqa_paged_decode(lens, splits):
     out = gqa_paged_decode(q, kc, vc, bt, sl, scale, max(lens), num_splits=splits)
     ref = A.gqa_decode_ref(q, kc, vc, bt, sl, scale)
     _close(out, ref, 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_apply_penalties(dtype):
+    """Repetition / frequency / presence penalties against the fp32 reference; one row is neutral and must be untouched."""
+    from omni_infer_b200.ops import sampling as S
+    torch.manual_seed(31)
+    Bn, V, L = 5, 5000, 300
+    logits = (torch.randn(Bn, V, device=DEV) * 3).to(dtype)
+    hist = torch.randint(0, V, (Bn, L), device=DEV, dtype=torch.int32)
+    hist[:, 250:] = -1
+    hist[1, 100:120] = 7                      # a token repeated in the output
+    npr = torch.tensor([40, 60, 0, 250, 100], dtype=torch.int32, device=DEV)
+    rep = torch.tensor([1.3, 1.0, 1.0, 2.0, 1.1], device=DEV)
+    freq = torch.tensor([0.0, 0.5, 0.0, 0.0, 0.2], device=DEV)
+    pres = torch.tensor([0.0, 0.0, 0.0, 0.7, 0.3], device=DEV)
+    ref = S.apply_penalties_ref(logits.clone(), hist, npr, rep, freq, pres)
+    got = S.apply_penalties(logits.clone(), hist, npr, rep, freq, pres)
+    _close(got, ref, 1e-2, 1e-2)
+    assert torch.equal(got[2], logits[2])

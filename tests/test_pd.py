@@ -92,3 +92,66 @@ def test_transfer_that_never_completes_falls_back_to_local_prefill():
     outs = _run_pd(P, D, prompts, 5)
     assert D.scheduler.stats.get("kv_fallbacks", 0) == 2
     assert [outs[f"r{i}"] for i in range(2)] == want
+
+
+def test_unknown_request_is_refused_and_prefilled_locally():
+    """A producer that lost its state (restart) answers nack: the consumer must not decode on blocks nobody wrote."""
+    prompts = _prompts(2)
+    want = _mixed_reference(prompts, 5)
+    P, D = _engine("kv_producer", "p3"), _engine("kv_consumer", "d3")
+    real = P.worker.runner.kv_connector
+    orig = real.expect_pull
+    real.expect_pull = lambda rid: None          # the producer "forgets" every hand-over
+    outs = _run_pd(P, D, prompts, 5)
+    real.expect_pull = orig
+    assert D.scheduler.stats.get("kv_fallbacks", 0) == 2
+    assert [outs[f"r{i}"] for i in range(2)] == want
+
+
+def test_late_and_foreign_acks_do_not_complete_a_request():
+    from omni_infer_b200.accelerators.pd.connector import ReqMeta, WorkerConnector
+    c = WorkerConnector("kv_consumer", "cx", "inproc://cx", sync_timeout_s=0.3, retries=0, retry_wait_s=0.05)
+    with c._lock:
+        c._inflight["a"] = (ReqMeta("a", [1], [2], "inproc://nobody"), "cx:7")
+    c.handle_ack({"op": "ack", "request_id": "a", "attempt": "cx:6"})      # an older attempt
+    c.handle_ack({"op": "ack", "request_id": "zzz", "attempt": "cx:7"})    # a stranger
+    assert c.get_finished()[1] == set() and "a" in c._inflight
+    c.handle_ack({"op": "ack", "request_id": "a", "attempt": "cx:7"})
+    assert c.get_finished()[1] == {"a"}
+
+
+def test_cancel_waits_for_a_running_copy_and_blocks_later_pushes():
+    import threading
+
+    from omni_infer_b200.accelerators.pd.connector import WorkerConnector
+    prod = WorkerConnector("kv_producer", "px", "inproc://px")
+    cons = WorkerConnector("kv_consumer", "cy", "inproc://cy")
+    prod.kv_tensors = [torch.zeros(4, 8)]
+    cons.kv_tensors = [torch.zeros(4, 8)]
+    prod.expect_pull("q")
+    with prod._lock:
+        prod._copying.add("q")                   # a copy of the request is "running"
+    done = []
+    th = threading.Thread(target=lambda: (prod.handle_cancel({"op": "cancel", "request_id": "q", "attempt": "cy:1",
+                                                              "reply_to": "inproc://cy"}), done.append(1)))
+    th.start()
+    time.sleep(0.05)
+    assert not done and ("q", "cy:1") not in cons._cancel_acked          # confirmation is held back
+    with prod._lock:
+        prod._copying.discard("q")
+    th.join(2)
+    assert done and ("q", "cy:1") in cons._cancel_acked
+    # the cancelled attempt is never copied, even if its push request arrives afterwards
+    prod.kv_tensors[0].fill_(3.0)
+    prod.handle_push_request({"op": "push", "request_id": "q", "attempt": "cy:1", "src_blocks": [0], "dst_blocks": [1],
+                              "reply_to": "inproc://cy"})
+    assert float(cons.kv_tensors[0].sum()) == 0.0
+
+
+def test_wire_format_is_json_and_needs_a_key_off_loopback():
+    from omni_infer_b200.accelerators.pd.connector import TcpTransport, _decode, _encode
+    msg = {"op": "push", "request_id": "r", "cache": {"ipc": [bytes(range(64))], "num_blocks": 3}}
+    raw = _encode(msg)
+    assert raw.startswith(b"{") and _decode(raw) == msg
+    with pytest.raises(ValueError):
+        TcpTransport("tcp://10.1.2.3:1", None)

@@ -1,0 +1,80 @@
+"""The plugin surface: pyproject.toml declares the host engine's entry-point groups (``vllm.platform_plugins``,
+``vllm.general_plugins``) and the ``omni_cli`` script (reference: pyproject.toml:17-27).  The tests install nothing:
+they write the distribution's metadata directory from pyproject.toml into a temporary path entry, which is exactly
+what the host engine's plugin loader (``importlib.metadata.entry_points(group=...)``) reads."""
+import importlib
+import importlib.metadata as md
+import os
+import sys
+import tomllib
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture()
+def dist_info(tmp_path, monkeypatch):
+    proj = tomllib.load(open(os.path.join(ROOT, "pyproject.toml"), "rb"))["project"]
+    d = tmp_path / f"{proj['name']}-{proj['version']}.dist-info"
+    d.mkdir()
+    (d / "METADATA").write_text(f"Metadata-Version: 2.1\nName: {proj['name']}\nVersion: {proj['version']}\n")
+    lines = ["[console_scripts]"] + [f"{k} = {v}" for k, v in proj["scripts"].items()]
+    for group, eps in proj["entry-points"].items():
+        lines += ["", f"[{group}]"] + [f"{k} = {v}" for k, v in eps.items()]
+    (d / "entry_points.txt").write_text("\n".join(lines) + "\n")
+    monkeypatch.syspath_prepend(str(tmp_path))
+    monkeypatch.setenv("NO_GPU_MOCK", "1")
+    importlib.invalidate_caches()
+    return proj
+
+
+def test_platform_plugin_is_discovered_and_resolves(dist_info):
+    eps = [e for e in md.entry_points(group="vllm.platform_plugins") if e.name == "b200"]
+    assert len(eps) == 1
+    qualname = eps[0].load()()
+    assert qualname == "omni_infer_b200.adaptors.vllm.platform.B200Platform"
+    mod, cls = qualname.rsplit(".", 1)
+    platform = getattr(importlib.import_module(mod), cls)
+    assert platform.get_worker_cls() == "omni_infer_b200.adaptors.vllm.worker.B200Worker"
+    assert platform.get_attn_backend_cls(True).endswith("MLAAttention")
+    try:
+        from vllm.platforms.interface import Platform, PlatformEnum
+    except Exception:  # noqa: BLE001
+        pytest.skip("no host engine installed: the class stands alone")
+    assert issubclass(platform, Platform) and platform._enum == PlatformEnum.OOT
+    assert platform().is_out_of_tree()
+
+
+def test_host_engine_loader_sees_the_plugins(dist_info):
+    try:
+        from vllm.plugins import load_plugins_by_group
+    except Exception:  # noqa: BLE001
+        pytest.skip("no host engine installed")
+    found = load_plugins_by_group("vllm.platform_plugins")
+    assert "b200" in found and found["b200"]() .endswith("B200Platform")
+    general = load_plugins_by_group("vllm.general_plugins")
+    assert {"b200_optimized_models", "kv_connectors"} <= set(general)
+    models = general["b200_optimized_models"]()
+    assert {"DeepseekV3ForCausalLM", "DeepseekV2ForCausalLM", "Qwen2ForCausalLM", "DeepSeekMTPModel"} <= set(models)
+    conns = general["kv_connectors"]()
+    assert "B200PeerPushConnectorV1" in conns and "AscendHcclConnectorV1" in conns
+    from omni_infer_b200.accelerators.pd import get_connector_class
+    assert get_connector_class("AscendHcclConnectorV1").__name__ == "WorkerConnector"
+
+
+def test_check_and_update_config_on_a_host_engine_config(dist_info):
+    from types import SimpleNamespace
+
+    from omni_infer_b200.adaptors.vllm.platform import B200Platform
+    vc = SimpleNamespace(parallel_config=SimpleNamespace(worker_cls="auto"), cache_config=SimpleNamespace(block_size=None),
+                         scheduler_config=SimpleNamespace(scheduler_cls=None),
+                         additional_config={"enable_hybrid_graph_mode": True})
+    B200Platform.check_and_update_config(vc)
+    assert vc.parallel_config.worker_cls.endswith("B200Worker") and vc.cache_config.block_size == 128
+    assert vc.scheduler_config.scheduler_cls.endswith("engine.scheduler.Scheduler")
+
+
+def test_cli_script_entry(dist_info):
+    eps = {e.name: e for e in md.entry_points(group="console_scripts")}
+    assert eps["omni_cli"].load().__module__ == "omni_infer_b200.cli.main"
