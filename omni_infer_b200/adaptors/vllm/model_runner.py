@@ -153,14 +153,17 @@ class ModelRunner:
         """Finish the agreement: choose the expert-parallel path every rank takes in this step (the fused peer-memory
         kernels only if every rank's rows fit their buffers and nothing forces the baseline) and return the number of
         model rounds all ranks run.  ``peers_busy`` tells the engine loop whether any rank still has requests."""
+        ps = get_parallel_state()
         if handle is None:
             self.peers_busy = False
             self._ep_fused_now = getattr(self, "ep_ctx", None) is not None
+            ps.step_max_tokens = 0
             return rounds
         t, work = handle
         work.wait()
         max_tokens, max_rounds, any_work = int(t[0]), int(t[1]), bool(int(t[2]))
         self.peers_busy = any_work
+        ps.step_max_tokens = max_tokens        # layers sharded over a sub-group pad their rows to this
         ctx = getattr(self, "ep_ctx", None)
         fused = ctx is not None and max_tokens <= self.ep_max_tokens and not getattr(self, "force_ep_baseline", False)
         self._ep_fused_now = fused
@@ -503,6 +506,11 @@ class ModelRunner:
         # a captured graph contains the fused exchange; when the ranks agreed on the baseline for this step (a peer
         # prefills more rows than the fused buffers hold) the step runs eagerly on the agreed path instead
         graph_ok = getattr(self, "_ep_fused_now", True) or getattr(self, "ep_ctx", None) is None
+        cfg = self.model_cfg
+        if getattr(cfg, "dense_mlp_tp_size", 1) > 1 or getattr(cfg, "o_proj_tp_size", 1) > 1:
+            # sub-group collectives inside a graph have the captured row count: replay only when every rank runs it
+            m = get_parallel_state().step_max_tokens
+            graph_ok = graph_ok and (m == 0 or m == padded * self.tpr)
         if self.graphs is not None and self.graphs.has(padded) and graph_ok:
             return self.graphs.replay(padded, ids, md)
         hidden = self.model(ids, md, self.kv_caches)

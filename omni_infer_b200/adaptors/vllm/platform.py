@@ -57,6 +57,12 @@ class ConfigUpdater:
             engine_cfg.placement_config = {"config_path": oc.omni_placement_config_path}
         engine_cfg.ep_backend = "fused" if oc.moe_dispatch_combine else "nccl"
         engine_cfg.tp_size = max(1, engine_cfg.tp_size)
+        pc = extra.parall_config
+        engine_cfg.dense_mlp_tp_size = max(1, int(pc.dense_mlp_tp_size))
+        engine_cfg.o_proj_tp_size = max(1, int(pc.o_proj_tp_size))
+        if pc.redundancy_shared_expert_num:
+            logger.warning("redundancy_shared_expert_num=%d: dedicated shared-expert ranks are not built; the shared expert "
+                           "runs on every rank (or sharded over dense_mlp_tp_size)", pc.redundancy_shared_expert_num)
         return engine_cfg
 
 

@@ -42,6 +42,9 @@ class B200Worker:
             torch.cuda.set_device(self.device)
         else:
             self.device = torch.device("cpu")
+        if ps.world_size > 1 and not self.runner_cfg.attn_tp:
+            self.model_cfg.dense_mlp_tp_size = max(1, min(self.dense_mlp_tp_size, ps.world_size))
+            self.model_cfg.o_proj_tp_size = max(1, min(self.o_proj_tp_size, ps.world_size))
         self.runner = ModelRunner(self.model_cfg, self.runner_cfg, self.device, planner=self.planner,
                                   kv_connector=self.kv_connector)
 

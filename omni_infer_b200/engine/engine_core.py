@@ -29,6 +29,8 @@ class EngineConfig:
     model_overrides: dict = field(default_factory=dict)
     device: Optional[str] = None
     tp_size: int = 1
+    dense_mlp_tp_size: int = 1       # dense MLP layers + shared expert sharded over sub-groups of this size
+    o_proj_tp_size: int = 1          # o_proj sharded over sub-groups of this size (attention data parallel)
     block_size: int = 128
     num_kv_blocks: int = 0
     gpu_memory_utilization: float = 0.9
@@ -71,7 +73,8 @@ class EngineCore:
             from ..accelerators.pd import create_connectors
             sched_conn, worker_conn = create_connectors(cfg.kv_transfer_config, block_size=cfg.block_size)
         self.worker = B200Worker(self.model_cfg, rc, tp_size=cfg.tp_size, device=cfg.device, planner=planner,
-                                 kv_connector=worker_conn)
+                                 kv_connector=worker_conn, dense_mlp_tp_size=cfg.dense_mlp_tp_size,
+                                 o_proj_tp_size=cfg.o_proj_tp_size)
         self.worker.init_device()
         if planner is None and cfg.placement_config:
             # the planner sizes its slot tables from the world size, so it is built after the process group exists

@@ -43,7 +43,14 @@ class MLAAttention(nn.Module):
         self.kv_a_layernorm = RMSNorm(self.kvl, cfg.rms_norm_eps, dtype, device)
         # kept unquantised: the absorbed decode path multiplies activations by slices of it
         self.kv_b_proj = Linear(self.kvl, H * (self.nope + self.vd), dtype=dtype, quant="none", device=device)
-        self.o_proj = Linear(H * self.vd, hs, dtype=dtype, quant=quant, device=device)
+        if getattr(cfg, "o_proj_tp_size", 1) > 1 and self.tp_world == 1:
+            # attention stays data parallel, o_proj is sharded over the o_proj_tp sub-group
+            from ..parallel import get_parallel_state
+            from .linear import DP2TPRowParallelLinear
+            self.o_proj = DP2TPRowParallelLinear(H * self.vd, hs, get_parallel_state().group("o_proj_tp"), dtype=dtype,
+                                                 quant=quant, device=device)
+        else:
+            self.o_proj = Linear(H * self.vd, hs, dtype=dtype, quant=quant, device=device)
         self.cos_sin = cos_sin
         if self.tp_world > 1:
             self._mark_tp_shards()

@@ -91,8 +91,14 @@ class MoELayer(nn.Module):
                                          requires_grad=False)
         else:
             self.w13_scale = self.w2_scale = None
-        self.shared_experts = (SwiGLUMLP(H, I * cfg.n_shared_experts, dtype=dtype, quant=quant, device=device)
-                               if cfg.n_shared_experts > 0 else None)
+        self.shared_experts = None
+        if cfg.n_shared_experts > 0:
+            if getattr(cfg, "dense_mlp_tp_size", 1) > 1 and getattr(cfg, "attn_tp_size", 1) == 1:
+                # sharded over the mlp_tp sub-group like the dense layers (omni/models/deepseek/deepseek_v3.py:86-136)
+                from .linear import ParallelSwiGLUMLP
+                self.shared_experts = ParallelSwiGLUMLP(H, I * cfg.n_shared_experts, dtype=dtype, quant=quant, device=device)
+            else:
+                self.shared_experts = SwiGLUMLP(H, I * cfg.n_shared_experts, dtype=dtype, quant=quant, device=device)
         self.ep_backend = ep_backend
         self.ep_ctx = None          # set by the model runner when the fused NVLink path is enabled
         self.forced_balance = False

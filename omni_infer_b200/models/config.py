@@ -15,6 +15,10 @@ class ModelConfig:
     # layers (set by the model runner; 1 = every rank runs whole attention layers on its own requests)
     attn_tp_size: int = 1
     attn_tp_rank: int = 0
+    # sub-group sharding while attention is data parallel: the dense MLP layers and the shared expert over the
+    # ``mlp_tp`` group, o_proj over the ``o_proj_tp`` group (set by the worker from the engine configuration)
+    dense_mlp_tp_size: int = 1
+    o_proj_tp_size: int = 1
     # benchmark aid: {"s": 1.2, "strength": 6.0, "seed": 0} adds a fixed Zipf-shaped bias to every router's logits so that
     # expert popularity is skewed (load-balance stress); None = the router as trained
     router_skew: Optional[dict] = None

@@ -32,7 +32,11 @@ class DeepseekDecoderLayer(nn.Module):
             self.mlp = MoELayer(cfg, layer_idx, dtype=dtype, device=device, planner=planner)
         else:
             q = cfg.quantization if self.quant else "none"
-            self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, quant=q, device=device)
+            if cfg.dense_mlp_tp_size > 1 and cfg.attn_tp_size == 1:
+                from ..layers.linear import ParallelSwiGLUMLP
+                self.mlp = ParallelSwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, quant=q, device=device)
+            else:
+                self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype=dtype, quant=q, device=device)
         self.is_moe = is_moe
 
     def forward_tp(self, h, residual, md: AttnMetadata, kv_cache, tp, num_valid):

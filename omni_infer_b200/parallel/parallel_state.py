@@ -108,6 +108,7 @@ class ParallelState:
     backend: str = "none"
     groups: dict = field(default_factory=dict)
     tp_fused: object = None     # TpFusedContext / TpNcclBaseline when attention runs tensor parallel
+    step_max_tokens: int = 0    # largest token-row count of any rank in the current step (0 = not agreed)
 
     @property
     def dp_size(self) -> int:

@@ -131,6 +131,30 @@ def test_uneven_data_parallel_ranks_stay_in_step(mode):
         assert two[1] == []
 
 
+def _subgroup_engine(rank, world, mlp_tp, o_tp):
+    """Data-parallel attention with the dense MLP / shared expert sharded over ``mlp_tp`` ranks and o_proj over
+    ``o_tp`` ranks (all-gather -> MLP -> reduce-scatter; all-to-all -> o_proj -> reduce-scatter), uneven batches."""
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=3,
+                                  dense_mlp_tp_size=mlp_tp, o_proj_tp_size=o_tp))
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (20 + 3 * i,), generator=g).tolist() for i in range(3)]
+    mine = prompts if (world == 1 or rank == 0) else prompts[1:2]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in mine]
+    outs = eng.run_until_done(max_steps=200)
+    if dist.is_initialized():
+        dist.barrier()
+    return [outs[i] for i in ids]
+
+
+@pytest.mark.parametrize("mlp_tp,o_tp", [(2, 1), (1, 2), (2, 2)])
+def test_dense_mlp_and_o_proj_subgroups_match_single_rank(mlp_tp, o_tp):
+    single = _spawn(_subgroup_engine, 1, 1, 1)[0]
+    two = _spawn(_subgroup_engine, 2, mlp_tp, o_tp)
+    assert two[0] == single and two[1] == [single[1]]
+
+
 # ---------------------------------------------------------------------------------------------- TP attention
 def _tp_engine(rank, world):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
