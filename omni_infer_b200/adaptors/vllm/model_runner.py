@@ -76,6 +76,8 @@ class ModelRunner:
                                  seed=seed if weights is None else None)
         from ...models.deepseek_mtp import DeepseekV3MTP
         n_draft = min(self.cfg.num_speculative_tokens, max(cfg.num_nextn_predict_layers, 0), 3)
+        if self.cfg.num_speculative_tokens and get_parallel_state().pp_size > 1:
+            raise ValueError("MTP drafting is not combined with pipeline parallelism")
         if self.cfg.num_speculative_tokens and n_draft == 0:
             raise ValueError("speculative decoding needs num_nextn_predict_layers > 0 in the model config")
         for i in range(n_draft):
@@ -128,7 +130,7 @@ class ModelRunner:
             moe_layers += [m for m in d.modules() if m.__class__.__name__ == "MoELayer"]
         self._moe_layers = moe_layers
         if (self.cfg.ep_backend == "fused" and self.device.type == "cuda" and cfg.dtype == "bfloat16"
-                and cfg.hidden_size % 128 == 0):
+                and cfg.hidden_size % 128 == 0 and ps.pp_size == 1):
             from ...parallel.ep_fused import EpContext
             # e4m3 experts: rows are dispatched quantised (1x128 scales); unquantised experts: bf16 rows as they are
             self.ep_ctx = EpContext(cfg.hidden_size, cfg.num_experts_per_tok, self.cfg.max_num_seqs * self.tpr,
@@ -264,6 +266,9 @@ class ModelRunner:
     def capture_model(self) -> None:
         """Capture one CUDA graph per decode bucket, largest first so smaller ones reuse its memory pool."""
         if self.device.type != "cuda" or not self.cfg.use_cuda_graph or self.cfg.enforce_eager:
+            return
+        if get_parallel_state().pp_size > 1:
+            logger.info("pipeline parallelism: stages hand over hidden states with point-to-point sends; decode stays eager")
             return
         if get_parallel_state().world_size > 1 and self.model_cfg.is_moe and getattr(self, "ep_ctx", None) is None:
             logger.info("expert parallelism over NCCL all-to-all needs host-side split sizes: decode stays eager")
@@ -474,9 +479,15 @@ class ModelRunner:
         ids, md = self._prepare_prefill(so)
         rounds = self._agree_finish(handle, 1)
         hidden = self.model(ids, md, self.kv_caches)
-        last_h = hidden[md.sample_indices]
-        logits = self.model.compute_logits(last_h)
-        toks = self._sample(logits, reqs, 1)
+        pp = self._pipeline()
+        if pp is None or pp.is_last:
+            last_h = hidden[md.sample_indices]
+            logits = self.model.compute_logits(last_h)
+            toks = self._sample(logits, reqs, 1)
+        else:
+            toks = None
+        if pp is not None:
+            toks = pp.broadcast_tokens(toks, len(reqs), self.device)
         spec = None
         if self.drafters:
             # drafter prefill: tokens shifted left, the sampled token closes each request's row
@@ -514,8 +525,14 @@ class ModelRunner:
         if self.graphs is not None and self.graphs.has(padded) and graph_ok:
             return self.graphs.replay(padded, ids, md)
         hidden = self.model(ids, md, self.kv_caches)
-        logits = self.model.compute_logits(hidden)
+        pp = self._pipeline()
+        logits = self.model.compute_logits(hidden) if (pp is None or pp.is_last) else None
         return hidden, logits
+
+    def _pipeline(self):
+        """This rank's pipeline stage, or None without pipeline parallelism."""
+        inner = getattr(self.model, "model", None)
+        return getattr(inner, "pp", None)
 
     def _run_decode(self, so, reqs) -> ModelRunnerOutput:
         tpr, B = self.tpr, len(reqs)
@@ -527,7 +544,10 @@ class ModelRunner:
         spec_final = None
         for step in range(so.num_step):
             hidden, logits = self._forward_decode(ids, md, padded)
-            toks = self._sample(logits, reqs, tpr)
+            pp = self._pipeline()
+            toks = self._sample(logits, reqs, tpr) if logits is not None else None
+            if pp is not None:
+                toks = pp.broadcast_tokens(toks, padded * tpr, self.device)
             if tpr == 1:
                 steps_out.append(toks[:B])
                 if step + 1 < so.num_step:

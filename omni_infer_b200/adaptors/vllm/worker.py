@@ -20,9 +20,10 @@ logger = logging.getLogger("omni_infer_b200.worker")
 
 class B200Worker:
     def __init__(self, model_cfg: ModelConfig, runner_cfg: RunnerConfig, *, tp_size: int = 1, device: Optional[str] = None,
-                 planner=None, kv_connector=None, dense_mlp_tp_size: int = 1, o_proj_tp_size: int = 1):
+                 planner=None, kv_connector=None, dense_mlp_tp_size: int = 1, o_proj_tp_size: int = 1, pp_size: int = 1):
         self.model_cfg, self.runner_cfg = model_cfg, runner_cfg
         self.tp_size, self.dense_mlp_tp_size, self.o_proj_tp_size = tp_size, dense_mlp_tp_size, o_proj_tp_size
+        self.pp_size = pp_size
         self.requested_device = device
         self.planner, self.kv_connector = planner, kv_connector
         self.runner: Optional[ModelRunner] = None
@@ -34,7 +35,8 @@ class B200Worker:
         no_gpu = os.environ.get("NO_GPU_MOCK", os.environ.get("NO_NPU_MOCK", "0")) == "1"
         use_cuda = torch.cuda.is_available() and not no_gpu and self.requested_device != "cpu"
         ps = init_distributed(backend="nccl" if use_cuda else "gloo", tp_size=self.tp_size,
-                              dense_mlp_tp_size=self.dense_mlp_tp_size, o_proj_tp_size=self.o_proj_tp_size) \
+                              dense_mlp_tp_size=self.dense_mlp_tp_size, o_proj_tp_size=self.o_proj_tp_size,
+                              pp_size=self.pp_size) \
             if int(os.environ.get("WORLD_SIZE", "1")) > 1 else get_parallel_state()
         if use_cuda:
             # with one engine per data-parallel rank, LOCAL_RANK already accounts for the DP offset

@@ -29,6 +29,7 @@ class EngineConfig:
     model_overrides: dict = field(default_factory=dict)
     device: Optional[str] = None
     tp_size: int = 1
+    pp_size: int = 1                 # pipeline stages; every stage of a pipeline is given the same requests
     dense_mlp_tp_size: int = 1       # dense MLP layers + shared expert sharded over sub-groups of this size
     o_proj_tp_size: int = 1          # o_proj sharded over sub-groups of this size (attention data parallel)
     block_size: int = 128
@@ -74,7 +75,7 @@ class EngineCore:
             sched_conn, worker_conn = create_connectors(cfg.kv_transfer_config, block_size=cfg.block_size)
         self.worker = B200Worker(self.model_cfg, rc, tp_size=cfg.tp_size, device=cfg.device, planner=planner,
                                  kv_connector=worker_conn, dense_mlp_tp_size=cfg.dense_mlp_tp_size,
-                                 o_proj_tp_size=cfg.o_proj_tp_size)
+                                 o_proj_tp_size=cfg.o_proj_tp_size, pp_size=cfg.pp_size)
         self.worker.init_device()
         if planner is None and cfg.placement_config:
             # the planner sizes its slot tables from the world size, so it is built after the process group exists

@@ -215,8 +215,22 @@ def qwen2_small(**kw) -> ModelConfig:
     return c
 
 
+def tiny_qwen3_moe(**kw) -> ModelConfig:
+    """CPU-sized GQA MoE in the shape of Qwen3-MoE: 2 layers, 4 q / 2 kv heads of 32 dims with q/k norm, 8 experts
+    top-2 with renormalised softmax routing, no shared expert."""
+    c = ModelConfig(architecture="Qwen3MoeForCausalLM", name="tiny-qwen3-moe", vocab_size=1024, hidden_size=128,
+                    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32, use_mla=False,
+                    intermediate_size=256, moe_intermediate_size=64, n_routed_experts=8, n_shared_experts=0,
+                    num_experts_per_tok=2, first_k_dense_replace=0, scoring_func="softmax", topk_method="greedy",
+                    norm_topk_prob=True, rope_theta=1e6, qk_norm=True, dtype="float32", max_position_embeddings=512)
+    for k, v in kw.items():
+        setattr(c, k, v)
+    return c
+
+
 PRESETS = {
     "tiny-deepseek-v3": tiny_deepseek_v3,
+    "tiny-qwen3-moe": tiny_qwen3_moe,
     "small-deepseek": small_deepseek_gpu,
     "deepseek-v2-lite": deepseek_v2_lite,
     "deepseek-v3": deepseek_v3,

@@ -49,15 +49,28 @@ class QwenModel(nn.Module):
                                               cfg.rope_scaling, device=device or "cpu")
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
         self.embed_tokens.weight.requires_grad_(False)
-        self.layers = nn.ModuleList([QwenDecoderLayer(cfg, i, dtype=dtype, device=device, cos_sin=self.cos_sin,
-                                                      planner=planner) for i in range(cfg.num_hidden_layers)])
+        from ..parallel.parallel_state import get_parallel_state
+        from ..parallel.pipeline import PipelineStage, PPMissingLayer, layer_range
+        ps = get_parallel_state()
+        n = cfg.num_hidden_layers
+        self.pp = PipelineStage() if ps.pp_size > 1 else None
+        self.layer_lo, self.layer_hi = layer_range(n, ps.pp_rank, ps.pp_size) if self.pp else (0, n)
+        self.layers = nn.ModuleList([QwenDecoderLayer(cfg, i, dtype=dtype, device=device, cos_sin=self.cos_sin, planner=planner)
+                                     if self.layer_lo <= i < self.layer_hi else PPMissingLayer() for i in range(n)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
 
     def forward(self, input_ids, md, kv_caches, inputs_embeds=None):
-        h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
-        residual = None
-        for i, layer in enumerate(self.layers):
-            h, residual = layer(h, residual, md, kv_caches[i])
+        pp = self.pp
+        if pp is None or pp.is_first:
+            h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
+            residual = None
+        else:
+            h, residual = pp.recv_intermediate(input_ids.shape[0], self.cfg.hidden_size, self.dtype, input_ids.device)
+        for i in range(self.layer_lo, self.layer_hi):
+            h, residual = self.layers[i](h, residual, md, kv_caches[i - self.layer_lo])
+        if pp is not None and not pp.is_last:
+            pp.send_intermediate(h, residual)
+            return h
         return self.norm(h, residual=residual)
 
 
@@ -73,7 +86,7 @@ class Qwen2ForCausalLM(nn.Module):
 
     @property
     def num_kv_layers(self):
-        return len(self.model.layers)
+        return self.model.layer_hi - self.model.layer_lo
 
     def forward(self, input_ids, md, kv_caches, inputs_embeds=None):
         return self.model(input_ids, md, kv_caches, inputs_embeds)

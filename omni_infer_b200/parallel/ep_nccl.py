@@ -14,8 +14,8 @@ from .parallel_state import get_parallel_state
 
 def moe_forward_nccl(layer, x, ids, w, shared):
     ps = get_parallel_state()
-    g = ps.group("world")
-    W = ps.world_size
+    g = ps.group("ep")
+    W = ps.ep_size
     T, k = ids.shape
     H = x.shape[1]
     S = layer.slots_per_rank

@@ -8,6 +8,9 @@ One process per GPU.  World ranks are laid out ``[dp][tp]`` (TP fastest).  Group
 * ``mlp_tp``     sub-group for the dense MLP layers / shared expert (``dense_mlp_tp_size``)
 * ``o_proj_tp``  sub-group that shards o_proj while attention itself is data parallel
 * ``cpu``        gloo group over the world for host-side agreement (padding, KV block counts)
+* ``pp`` / ``ep`` with pipeline parallelism the layout is ``[pp][inner]``: ``pp`` links the ranks that hold the same
+                 inner position in every stage, ``ep`` is the stage's own ranks (the experts of a stage's layers are
+                 sharded over them); without pipeline parallelism ``ep`` is the whole instance
 
 The reference additionally builds local/cross/round/far/near-cross groups for its multi-node
 hierarchical pipelines (omni/adaptors/vllm/distributed/parallel_state.py:349-635); one NVSwitch
@@ -105,6 +108,7 @@ class ParallelState:
     world_size: int = 1
     local_rank: int = 0
     tp_size: int = 1
+    pp_size: int = 1
     backend: str = "none"
     groups: dict = field(default_factory=dict)
     tp_fused: object = None     # TpFusedContext / TpNcclBaseline when attention runs tensor parallel
@@ -123,18 +127,22 @@ class ParallelState:
         return self.rank // self.tp_size
 
     @property
+    def pp_rank(self) -> int:
+        return self.rank // (self.world_size // self.pp_size)
+
+    @property
     def ep_size(self) -> int:
-        return self.world_size
+        return self.world_size // self.pp_size
 
     @property
     def ep_rank(self) -> int:
-        return self.rank
+        return self.rank % self.ep_size
 
     def group(self, name: str) -> GroupCoordinator:
         return self.groups[name]
 
 
-_STATE = ParallelState(groups={k: GroupCoordinator(k, [0], 0) for k in ("world", "tp", "dp", "mlp_tp", "o_proj_tp", "cpu")})
+_STATE = ParallelState(groups={k: GroupCoordinator(k, [0], 0) for k in ("world", "tp", "dp", "mlp_tp", "o_proj_tp", "cpu", "pp", "ep")})
 
 
 def get_parallel_state() -> ParallelState:
@@ -152,7 +160,7 @@ def _build(name, all_rank_lists, rank, backend=None) -> GroupCoordinator:
 
 
 def init_distributed(backend: Optional[str] = None, tp_size: int = 1, dense_mlp_tp_size: int = 1,
-                     o_proj_tp_size: int = 1, timeout_s: float = 600.0) -> ParallelState:
+                     o_proj_tp_size: int = 1, timeout_s: float = 600.0, pp_size: int = 1) -> ParallelState:
     """Join the job described by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT and build
     every group.  ``backend`` defaults to nccl with CUDA, gloo otherwise."""
     import datetime
@@ -176,9 +184,10 @@ def init_distributed(backend: Optional[str] = None, tp_size: int = 1, dense_mlp_
     elif torch.cuda.is_available():
         torch.cuda.set_device(local_rank)
     assert world % tp_size == 0
-    st = ParallelState(rank=rank, world_size=world, local_rank=local_rank, tp_size=tp_size, backend=backend)
+    assert world % pp_size == 0
+    st = ParallelState(rank=rank, world_size=world, local_rank=local_rank, tp_size=tp_size, pp_size=pp_size, backend=backend)
     if world == 1:
-        st.groups = {k: GroupCoordinator(k, [0], 0) for k in ("world", "tp", "dp", "mlp_tp", "o_proj_tp", "cpu")}
+        st.groups = {k: GroupCoordinator(k, [0], 0) for k in ("world", "tp", "dp", "mlp_tp", "o_proj_tp", "cpu", "pp", "ep")}
         _STATE = st
         return st
     allr = list(range(world))
@@ -190,6 +199,9 @@ def init_distributed(backend: Optional[str] = None, tp_size: int = 1, dense_mlp_
     o = max(1, min(o_proj_tp_size, world))
     st.groups["o_proj_tp"] = _build("o_proj_tp", [allr[i:i + o] for i in range(0, world, o)], rank)
     st.groups["cpu"] = _build("cpu", [allr], rank, backend="gloo")
+    inner = world // pp_size
+    st.groups["pp"] = _build("pp", [allr[i::inner] for i in range(inner)], rank)
+    st.groups["ep"] = _build("ep", [allr[s * inner:(s + 1) * inner] for s in range(pp_size)], rank)
     _STATE = st
     return st
 
@@ -199,7 +211,7 @@ def destroy_distributed() -> None:
     if dist.is_initialized():
         dist.destroy_process_group()
     _STATE = ParallelState(groups={k: GroupCoordinator(k, [0], 0)
-                                   for k in ("world", "tp", "dp", "mlp_tp", "o_proj_tp", "cpu")})
+                                   for k in ("world", "tp", "dp", "mlp_tp", "o_proj_tp", "cpu", "pp", "ep")})
 
 
 # -- free-function aliases with the reference's names (omni/adaptors/vllm/distributed/communication_op.py)

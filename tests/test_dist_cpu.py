@@ -155,6 +155,44 @@ def test_dense_mlp_and_o_proj_subgroups_match_single_rank(mlp_tp, o_tp):
     assert two[0] == single and two[1] == [single[1]]
 
 
+def _pp_engine(rank, world, model):
+    """Two pipeline stages: each builds half of the layers, hidden states travel by point-to-point sends, the last
+    stage samples and broadcasts the tokens; both stages are given the same requests."""
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    eng = EngineCore(EngineConfig(model=model, block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=3,
+                                  pp_size=world))
+    if world > 1:
+        m = eng.worker.runner.model.model
+        assert (m.layer_lo, m.layer_hi) == ((0, 1) if rank == 0 else (1, 2)) or m.layer_hi - m.layer_lo >= 1
+        assert eng.worker.runner.model.num_kv_layers == m.layer_hi - m.layer_lo
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (18 + 5 * i,), generator=g).tolist() for i in range(3)]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in prompts]
+    outs = eng.run_until_done(max_steps=200)
+    if dist.is_initialized():
+        dist.barrier()
+    return [outs[i] for i in ids]
+
+
+@pytest.mark.parametrize("model", ["tiny-deepseek-v3", "tiny-qwen3-moe"])
+def test_pipeline_parallel_matches_single_rank(model):
+    single = _spawn(_pp_engine, 1, model)[0]
+    two = _spawn(_pp_engine, 2, model)
+    assert two[0] == single and two[1] == single
+
+
+def test_pipeline_layer_ranges():
+    from omni_infer_b200.parallel.pipeline import layer_range
+    for n, pp in ((61, 4), (27, 2), (48, 8), (2, 2), (5, 3)):
+        spans = [layer_range(n, r, pp) for r in range(pp)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        sizes = [b - a for a, b in spans]
+        assert max(sizes) - min(sizes) <= 1
+    assert [layer_range(61, r, 4) for r in range(4)] == [(0, 15), (15, 31), (31, 46), (46, 61)]
+
+
 # ---------------------------------------------------------------------------------------------- TP attention
 def _tp_engine(rank, world):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
