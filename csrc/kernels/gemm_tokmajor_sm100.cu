@@ -453,17 +453,31 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
               }
             } else {
               __nv_bfloat16* o = (__nv_bfloat16*)obase + orow * p.out_ld + ocol;
+              // 32-byte stores where the row allows it: a lane then writes whole 32-byte sectors (the lanes of a
+              // warp write 32 different rows, so 16-byte stores would leave every sector half written per instruction)
+              const bool wide = (((uintptr_t)o & 31) == 0) && (nl + TM_CW <= p.n_out);
 #pragma unroll
-              for (int j = 0; j < TM_CW / 2; j += 4) {
-                __nv_bfloat162 h[4];
+              for (int j = 0; j < TM_CW / 2; j += 8) {
+                __nv_bfloat162 h[8];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[a][j + e].x * rs, acc[a][j + e].y * rs);
-                if (nl + 2 * j + 7 < p.n_out) {
-                  *reinterpret_cast<uint4*>(o + 2 * j) = *reinterpret_cast<uint4*>(h);
+                for (int e = 0; e < 8; ++e) h[e] = __floats2bfloat162_rn(acc[a][j + e].x * rs, acc[a][j + e].y * rs);
+                if (wide) {
+                  const uint32_t* hw = reinterpret_cast<const uint32_t*>(h);
+                  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                               ::"l"(o + 2 * j), "r"(hw[0]), "r"(hw[1]), "r"(hw[2]), "r"(hw[3]), "r"(hw[4]), "r"(hw[5]),
+                                 "r"(hw[6]), "r"(hw[7])
+                               : "memory");
                 } else {
-                  const __nv_bfloat16* hv = reinterpret_cast<const __nv_bfloat16*>(h);
-                  for (int e = 0; e < 8; ++e)
-                    if (nl + 2 * j + e < p.n_out) o[2 * j + e] = hv[e];
+#pragma unroll
+                  for (int q4 = 0; q4 < 2; ++q4) {
+                    if (nl + 2 * j + 8 * q4 + 7 < p.n_out) {
+                      *reinterpret_cast<uint4*>(o + 2 * j + 8 * q4) = *reinterpret_cast<uint4*>(h + 4 * q4);
+                    } else {
+                      const __nv_bfloat16* hv = reinterpret_cast<const __nv_bfloat16*>(h + 4 * q4);
+                      for (int e = 0; e < 8; ++e)
+                        if (nl + 2 * j + 8 * q4 + e < p.n_out) o[2 * j + 8 * q4 + e] = hv[e];
+                    }
+                  }
                 }
               }
             }
@@ -482,12 +496,22 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
         if (EPI == 1) {
           if (row_ok) {
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + row * p.out_ld + n0;
+            const bool wide = ((uintptr_t)o & 31) == 0;
 #pragma unroll
-            for (int j = 0; j < TM_CW / 2; j += 4) {
-              __nv_bfloat162 h[4];
+            for (int j = 0; j < TM_CW / 2; j += 8) {
+              __nv_bfloat162 h[8];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[0][j + e].x, acc[0][j + e].y);
-              *reinterpret_cast<uint4*>(o + 2 * j) = *reinterpret_cast<uint4*>(h);
+              for (int e = 0; e < 8; ++e) h[e] = __floats2bfloat162_rn(acc[0][j + e].x, acc[0][j + e].y);
+              const uint32_t* hw = reinterpret_cast<const uint32_t*>(h);
+              if (wide) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                             ::"l"(o + 2 * j), "r"(hw[0]), "r"(hw[1]), "r"(hw[2]), "r"(hw[3]), "r"(hw[4]), "r"(hw[5]),
+                               "r"(hw[6]), "r"(hw[7])
+                             : "memory");
+              } else {
+                *reinterpret_cast<uint4*>(o + 2 * j) = *reinterpret_cast<const uint4*>(h);
+                *reinterpret_cast<uint4*>(o + 2 * j + 8) = *reinterpret_cast<const uint4*>(h + 4);
+              }
             }
           }
         } else {
@@ -502,15 +526,25 @@ gemm_tokmajor_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
           const float inv = 1.0f / scl;
           if (row_ok) {
             uint8_t* o = (uint8_t*)p.out + row * p.out_ld + n0;
+            const bool wide = ((uintptr_t)o & 31) == 0;
 #pragma unroll
-            for (int j = 0; j < TM_CW / 2; j += 8) {
-              uint8_t b[16];
+            for (int j = 0; j < TM_CW / 2; j += 16) {
+              __align__(16) uint8_t b[32];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
+              for (int e = 0; e < 16; ++e) {
                 b[2 * e] = f32_to_e4m3(acc[0][j + e].x * inv);
                 b[2 * e + 1] = f32_to_e4m3(acc[0][j + e].y * inv);
               }
-              *reinterpret_cast<uint4*>(o + 2 * j) = *reinterpret_cast<uint4*>(b);
+              const uint32_t* bw = reinterpret_cast<const uint32_t*>(b);
+              if (wide) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                             ::"l"(o + 2 * j), "r"(bw[0]), "r"(bw[1]), "r"(bw[2]), "r"(bw[3]), "r"(bw[4]), "r"(bw[5]),
+                               "r"(bw[6]), "r"(bw[7])
+                             : "memory");
+              } else {
+                *reinterpret_cast<uint4*>(o + 2 * j) = *reinterpret_cast<const uint4*>(b);
+                *reinterpret_cast<uint4*>(o + 2 * j + 16) = *reinterpret_cast<const uint4*>(b + 16);
+              }
             }
             if (grp == 0) p.out_scale[(size_t)nt * p.out_scale_ld + row] = scl;
           }

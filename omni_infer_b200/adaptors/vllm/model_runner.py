@@ -144,7 +144,8 @@ class ModelRunner:
         step the same way, with a MAX all-reduce of the token count on the CPU group
         (omni/adaptors/vllm/worker/npu_model_runner.py:989-995)."""
         ps = get_parallel_state()
-        if ps.world_size == 1 or not getattr(self, "_moe_layers", None):
+        # every rank must take the same decision here, whatever layers it happens to hold (pipeline stages)
+        if ps.world_size == 1 or not self.model_cfg.is_moe:
             return None
         import torch.distributed as dist
         t = torch.tensor([num_tokens, rounds, 1 if has_work else 0], dtype=torch.int64)
@@ -169,7 +170,7 @@ class ModelRunner:
         ctx = getattr(self, "ep_ctx", None)
         fused = ctx is not None and max_tokens <= self.ep_max_tokens and not getattr(self, "force_ep_baseline", False)
         self._ep_fused_now = fused
-        for m in self._moe_layers:
+        for m in getattr(self, "_moe_layers", ()):
             m.ep_ctx = ctx if fused else None
         return max(rounds, max_rounds)
 
