@@ -236,6 +236,7 @@ class Distribution {
   virtual void recv_only(int peer, int stage, size_t bytes) = 0;
   virtual void send_only(int peer, const std::vector<ExpertTensor>& send) = 0;
   virtual void* staging(int stage) = 0;
+  virtual bool staging_on_device() const { return false; }   // staging buffers are device memory (device-fabric transport)
   virtual void barrier() = 0;
 };
 
@@ -275,6 +276,12 @@ struct DistributionCallbacks {
 class CallbackDistribution : public Distribution {
  public:
   CallbackDistribution(DistributionCallbacks cb, size_t expert_bytes);
+  // Device-fabric form: the embedding process owns a device send buffer (one packed expert, visible to the peers)
+  // and QUEUE_SIZE device staging buffers.  An expert is packed with device-to-device copies, the callback moves
+  // it over the fabric (peer copy or NCCL) straight into the receiver's staging buffer, and the apply step copies
+  // from staging into the live weights on the device.  No byte goes through host memory.
+  CallbackDistribution(DistributionCallbacks cb, size_t expert_bytes, void* device_send_buf, void* const* device_stages);
+  bool staging_on_device() const override { return device_send_ != nullptr; }
   int rank() const override { return cb_.rank; }
   int world() const override { return cb_.world; }
   void allgather_i64(const int64_t* send, int64_t* recv, size_t count) override { cb_.allgather_i64(send, recv, count); }
@@ -282,13 +289,16 @@ class CallbackDistribution : public Distribution {
   void swap(int peer, const std::vector<ExpertTensor>& send, int stage) override;
   void recv_only(int peer, int stage, size_t bytes) override;
   void send_only(int peer, const std::vector<ExpertTensor>& send) override;
-  void* staging(int stage) override { return stages_[stage].data(); }
+  void* staging(int stage) override { return device_send_ ? device_stages_[stage] : (void*)stages_[stage].data(); }
   void barrier() override { if (cb_.barrier) cb_.barrier(); }
 
  private:
+  size_t pack_device(const std::vector<ExpertTensor>& ts);
   DistributionCallbacks cb_;
   std::vector<std::vector<unsigned char>> stages_;   // host staging; the apply step copies into device weights
   std::vector<unsigned char> pack_;
+  void* device_send_ = nullptr;
+  std::vector<void*> device_stages_;
 };
 
 // ------------------------------------------------------------------------------------------------ Manager

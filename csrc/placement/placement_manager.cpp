@@ -112,14 +112,37 @@ void CallbackDistribution::allgather_handshake(const HandshakeTuple& mine, std::
   all.resize(cb_.world);
   for (int i = 0; i < cb_.world; ++i) all[i] = {(int)r[3 * i], (int)r[3 * i + 1], (int)r[3 * i + 2]};
 }
+CallbackDistribution::CallbackDistribution(DistributionCallbacks cb, size_t expert_bytes, void* device_send_buf,
+                                           void* const* device_stages)
+    : cb_(std::move(cb)), device_send_(device_send_buf), device_stages_(device_stages, device_stages + QUEUE_SIZE) {
+  (void)expert_bytes;
+}
+size_t CallbackDistribution::pack_device(const std::vector<ExpertTensor>& ts) {
+  size_t off = 0;
+  for (auto& t : ts) {
+    hooks().memcpy_d2d((unsigned char*)device_send_ + off, t.ptr, t.bytes);
+    off += t.bytes;
+  }
+  return off;
+}
 void CallbackDistribution::swap(int peer, const std::vector<ExpertTensor>& send, int stage) {
+  if (device_send_) {
+    const size_t n = pack_device(send);
+    cb_.sendrecv(peer, device_send_, device_stages_[stage], n);
+    return;
+  }
   pack_ = pack_expert(send);
   cb_.sendrecv(peer, pack_.data(), stages_[stage].data(), pack_.size());
 }
 void CallbackDistribution::recv_only(int peer, int stage, size_t bytes) {
-  cb_.sendrecv(peer, nullptr, stages_[stage].data(), bytes);
+  cb_.sendrecv(peer, nullptr, staging(stage), bytes);
 }
 void CallbackDistribution::send_only(int peer, const std::vector<ExpertTensor>& send) {
+  if (device_send_) {
+    const size_t n = pack_device(send);
+    cb_.sendrecv(peer, device_send_, nullptr, n);
+    return;
+  }
   pack_ = pack_expert(send);
   cb_.sendrecv(peer, pack_.data(), nullptr, pack_.size());
 }
@@ -259,8 +282,10 @@ int Placement::do_placement_optimizer() {
     if (local && a.stage >= 0) {
       size_t off = 0;
       const unsigned char* src = (const unsigned char*)dist_->staging(a.stage);
+      const bool dev = dist_->staging_on_device();
       for (const auto& t : weights_->tensors(a.layer, a.slot)) {
-        hooks().memcpy_h2d(t.ptr, src + off, t.bytes);
+        if (dev) hooks().memcpy_d2d(t.ptr, src + off, t.bytes);
+        else hooks().memcpy_h2d(t.ptr, src + off, t.bytes);
         off += t.bytes;
       }
       ++replaced;
@@ -348,6 +373,16 @@ void* omni_pl_distribution_create(int rank, int world, unsigned long long expert
   cb.sendrecv = [sr](int p, const void* s, void* r, size_t n) { sr(p, s, r, n); };
   cb.barrier = [bar]() { if (bar) bar(); };
   return new CallbackDistribution(cb, expert_bytes);
+}
+void* omni_pl_distribution_create_device(int rank, int world, unsigned long long expert_bytes, omni_allgather_fn ag,
+                                         omni_sendrecv_fn sr, omni_barrier_fn bar, void* device_send_buf,
+                                         void* const* device_stages) {
+  DistributionCallbacks cb;
+  cb.rank = rank; cb.world = world;
+  cb.allgather_i64 = [ag](const int64_t* s, int64_t* r, size_t n) { ag((const long long*)s, (long long*)r, n); };
+  cb.sendrecv = [sr](int p, const void* s, void* r, size_t n) { sr(p, s, r, n); };
+  cb.barrier = [bar]() { if (bar) bar(); };
+  return new CallbackDistribution(cb, expert_bytes, device_send_buf, device_stages);
 }
 void omni_pl_distribution_destroy(void* d) { delete (Distribution*)d; }
 

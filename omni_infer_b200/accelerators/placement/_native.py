@@ -41,6 +41,7 @@ def lib():
             ("omni_pl_activation_dump", None, [vp, ctypes.c_char_p]),
             ("omni_pl_activation_delta", ctypes.c_longlong, [vp, ci, ci]),
             ("omni_pl_distribution_create", vp, [ci, ci, ull, ALLGATHER_FN, SENDRECV_FN, BARRIER_FN]),
+            ("omni_pl_distribution_create_device", vp, [ci, ci, ull, ALLGATHER_FN, SENDRECV_FN, BARRIER_FN, vp, vp]),
             ("omni_pl_distribution_destroy", None, [vp]),
             ("omni_pl_placement_create", vp, [vp, vp, vp, vp, ci, cd]),
             ("omni_pl_placement_destroy", None, [vp]),

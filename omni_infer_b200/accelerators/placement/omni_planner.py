@@ -101,15 +101,23 @@ class OmniPlanner(metaclass=_Singleton):
             L.omni_pl_set_ut_memcpy()
             return
         rt = ctypes.CDLL("libcudart.so.12")
-        rt.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+        rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+        rt.cudaStreamSynchronize.argtypes = [ctypes.c_void_p]
         dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._rt, self._dev_index = rt, dev_index
+        # copies of the placement machinery run on their own low-priority, non-blocking stream: they never order
+        # themselves against the inference streams, and a copy only blocks the thread that asked for it
+        lo, _hi = torch.cuda.Stream.priority_range() if hasattr(torch.cuda.Stream, "priority_range") else (0, -1)
+        self._copy_stream = torch.cuda.Stream(device=self.device, priority=lo)
+        stream_ptr = ctypes.c_void_p(self._copy_stream.cuda_stream)
 
         def mk(kind):
             def f(dst, src, n):
                 rt.cudaSetDevice(dev_index)       # the background thread has no current device yet
-                rc = rt.cudaMemcpy(dst, src, n, kind)
+                rc = rt.cudaMemcpyAsync(dst, src, n, kind, stream_ptr)
+                rc = rc or rt.cudaStreamSynchronize(stream_ptr)
                 if rc != 0:
-                    logger.error("cudaMemcpy(kind=%d) failed with %d", kind, rc)
+                    logger.error("cudaMemcpyAsync(kind=%d) failed with %d", kind, rc)
             return nat.COPY_FN(f)
 
         hooks = (mk(3), mk(1), mk(2))      # d2d, h2d, d2h
@@ -201,9 +209,63 @@ class OmniPlanner(metaclass=_Singleton):
             if world > 1:
                 dist.barrier(group=g)
 
+        if self.device.type == "cuda" and world > 1 and os.environ.get("OMNI_PLACEMENT_HOST_STAGING", "0") != "1":
+            return self._make_device_distribution(eb, allgather, barrier)
         cbs = (nat.ALLGATHER_FN(allgather), nat.SENDRECV_FN(sendrecv), nat.BARRIER_FN(barrier))
         self._keep += list(cbs)
         return L.omni_pl_distribution_create(rank, world, eb, *cbs)
+
+    def _make_device_distribution(self, expert_bytes: int, allgather, barrier):
+        """Expert weights travel over the device fabric (reference: rank-ordered device Send/Recv into a ring of five
+        staging buffers, omni/accelerators/placement/omni_planner/cpp/distribution.cpp:173-218, moe_weights.cpp:32-101).
+
+        Every rank owns one send buffer (a packed expert, exported with CUDA IPC and mapped by all peers) and five
+        staging buffers.  To move an expert the source packs it into its send buffer with device copies and tells the
+        destination over the host group that it is ready; the destination pulls it across NVLink into a staging
+        buffer with an asynchronous peer copy on the placement stream (copy engines, no SM kernel, nothing ordered
+        against the inference streams) and acknowledges, so that the send buffer can be reused.  The inference
+        thread later copies staging -> live weights on the device between two steps."""
+        from ...parallel.symmetric_heap import alloc_ipc_tensor, export_ipc_handles, open_ipc_handles
+        L = nat.lib()
+        world, rank, g = self.world, self.rank, self._pl_group
+        nbytes = (int(expert_bytes) + 255) // 256 * 256
+        self._send_buf = alloc_ipc_tensor((nbytes,), torch.uint8)
+        self._stages = [torch.empty(nbytes, dtype=torch.uint8, device=self.device) for _ in range(5)]
+        handles = [None] * world
+        dist.all_gather_object(handles, export_ipc_handles([self._send_buf])[0], group=g)
+        self._peer_send = [open_ipc_handles([h])[0] if r != rank else self._send_buf.data_ptr() for r, h in enumerate(handles)]
+        rt, stream_ptr = self._rt, ctypes.c_void_p(self._copy_stream.cuda_stream)
+        tok = torch.zeros(1, dtype=torch.int64)
+
+        def exchange(peer, sending, receiving):
+            """One small host message each way that applies: 'my buffer is ready' / 'I am done with yours'."""
+            ops = []
+            if sending:
+                ops.append(dist.P2POp(dist.isend, tok.clone(), peer, g))
+            if receiving:
+                ops.append(dist.P2POp(dist.irecv, torch.empty_like(tok), peer, g))
+            if rank > peer:
+                ops.reverse()
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+        def sendrecv(peer, send, recv, n):
+            rt.cudaSetDevice(self._dev_index)
+            has_send, has_recv = bool(send), bool(recv)
+            exchange(peer, has_send, has_recv)             # data packed on the sender(s)
+            if has_recv:
+                rc = rt.cudaMemcpyAsync(recv, ctypes.c_void_p(self._peer_send[peer]), n, 3, stream_ptr)
+                rc = rc or rt.cudaStreamSynchronize(stream_ptr)
+                if rc != 0:
+                    logger.error("peer copy of an expert from rank %d failed with %d", peer, rc)
+            exchange(peer, has_recv, has_send)             # readers are done: send buffers may be reused
+
+        cbs = (nat.ALLGATHER_FN(allgather), nat.SENDRECV_FN(sendrecv), nat.BARRIER_FN(barrier))
+        self._keep += list(cbs)
+        stage_ptrs = (ctypes.c_void_p * 5)(*[ctypes.c_void_p(t.data_ptr()) for t in self._stages])
+        self._keep.append(stage_ptrs)
+        return L.omni_pl_distribution_create_device(rank, world, expert_bytes, *cbs, ctypes.c_void_p(self._send_buf.data_ptr()),
+                                                    stage_ptrs)
 
     def _ensure_placement(self):
         if self._placement is None:

@@ -182,3 +182,130 @@ def test_ep2_fused_bf16_experts_match_single_rank():
     nccl = _run(2, {"QUANT": "none", "EP_BACKEND": "nccl"}, 29619)
     assert _agreement(fused, single) > 0.6
     assert _agreement(fused, nccl) > 0.6
+
+
+PLACEMENT_WORKER = r'''
+import os, sys, json, time, torch
+sys.path.insert(0, os.environ["OMNI_ROOT"])
+import torch.distributed as dist
+from omni_infer_b200.accelerators.placement import OmniPlanner
+from omni_infer_b200.layers.moe import MoELayer
+from omni_infer_b200.models.config import get_config
+from omni_infer_b200.parallel import destroy_distributed, init_distributed
+ps = init_distributed(backend="nccl")
+rank = ps.rank
+dev = torch.device("cuda", ps.local_rank)
+cfg = get_config("small-deepseek", quantization="fp8_block")
+pl = OmniPlanner(num_moe_layers=1, num_experts=cfg.n_routed_experts, max_redundant_per_rank=1, enable_dynamic=False,
+                 device=str(dev), _new=True)
+layer = MoELayer(cfg, 1, dtype=torch.bfloat16, device=dev, planner=pl)
+model = torch.nn.ModuleList([layer])
+S = layer.slots_per_rank
+with torch.no_grad():
+    for s in range(S):                               # slot contents identify the expert they hold
+        e = pl.logical_of_slot(0, s)
+        layer.w13.data[s] = torch.full_like(layer.w13.data[s].float(), float(e % 7 + 1)).to(layer.w13.dtype)
+        layer.w2.data[s] = torch.full_like(layer.w2.data[s].float(), float(e % 7 + 1)).to(layer.w2.dtype)
+        layer.w13_scale.data[s].fill_(float(e))
+        layer.w2_scale.data[s].fill_(float(e) + 0.5)
+pl.init_dram_weights(model)
+pl.sent_counts[0, 0] = 5000 if rank == 0 else 4000   # expert 0 (on rank 0) is very hot
+pl.sent_counts[0, 1] = 10
+pl.sent_counts[0, S + 1] = 10
+torch.cuda.synchronize()
+t0 = time.perf_counter()
+n = pl.run_round()
+t_round = time.perf_counter() - t0
+t0 = time.perf_counter()
+applied = pl.apply_pending()
+torch.cuda.synchronize()
+t_apply = time.perf_counter() - t0
+spare = S - 1
+out = {"n": n, "applied": applied, "sel": pl.selector(0).tolist()[:2], "place": pl.mapping.placement()[0].tolist(),
+       "spare_w13": float(layer.w13.data[spare].float().flatten()[0]), "spare_scale": float(layer.w13_scale.data[spare].flatten()[0]),
+       "spare_w2s": float(layer.w2_scale.data[spare].flatten()[-1]), "device_staging": hasattr(pl, "_send_buf"),
+       "round_ms": t_round * 1e3, "apply_ms": t_apply * 1e3}
+allo = [None, None]
+dist.all_gather_object(allo, out, group=ps.group("cpu").group)
+if rank == 0:
+    print("RESULT " + json.dumps(allo))
+OmniPlanner.cleanup()
+destroy_distributed()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_swap_travels_over_the_device_fabric():
+    """A hot expert gets a replica in the other rank's redundant slot; weights and scales arrive through the peer-copy
+    transport (device staging ring, no host staging) and the selector routes each rank to its own replica."""
+    r0, r1 = _run(2, {}, 29621, worker=PLACEMENT_WORKER)
+    assert r0["device_staging"] and r1["device_staging"]
+    assert r0["place"] == r1["place"] and r0["n"] >= 1 and r1["applied"] >= 1
+    S = len(r0["place"]) // 2
+    assert r1["place"][2 * S - 1] == 0                    # replica of expert 0 in rank 1's spare slot
+    assert r1["spare_w13"] == 1.0 and r1["spare_scale"] == 0.0 and r1["spare_w2s"] == 0.5    # expert 0's tensors
+    assert r0["sel"][0] == 0 and r1["sel"][0] == 2 * S - 1
+
+
+KVPUSH_WORKER = r'''
+import os, sys, json, torch
+sys.path.insert(0, os.environ["OMNI_ROOT"])
+import torch.distributed as dist
+from omni_infer_b200.accelerators.pd.kv_push import PeerCacheView, push_blocks_cuda
+from omni_infer_b200.parallel.symmetric_heap import alloc_ipc_tensor, export_ipc_handles, open_ipc_handles
+from omni_infer_b200.ops import _native as nat
+rank = int(os.environ["RANK"]); lr = int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(lr)
+dist.init_process_group("gloo")
+L, NB, BS, W = int(os.environ.get("KV_LAYERS", "8")), 40, 128, 576
+blocks = list(range(3, 35))
+dst_blocks = [b + 2 for b in blocks]
+res = {}
+if rank == 1:      # decode instance: owns the destination cache, exports it
+    caches = [alloc_ipc_tensor((NB, BS, W), torch.bfloat16) for _ in range(L)]
+    dist.broadcast_object_list([export_ipc_handles(caches)], src=1)
+    dist.barrier()                                      # producer has pushed
+    torch.cuda.synchronize()
+    ok = True
+    for l, c in enumerate(caches):
+        want = torch.zeros_like(c)
+        for sb, db in zip(blocks, dst_blocks):
+            want[db] = float(l * 100 + sb)
+        ok = ok and bool(torch.equal(c, want))
+    res = {"bytes_equal": ok}
+else:              # prefill instance: maps the peer cache and pushes blocks into it
+    box = [None]
+    dist.broadcast_object_list(box, src=1)
+    view = PeerCacheView(open_ipc_handles(box[0]), BS * W * 2, NB)
+    src = [torch.zeros(NB, BS, W, dtype=torch.bfloat16, device="cuda") for _ in range(L)]
+    for l, c in enumerate(src):
+        for sb in blocks:
+            c[sb] = float(l * 100 + sb)
+    push_blocks_cuda(src, view, blocks, dst_blocks)     # warm-up + the copy that is checked
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for _ in range(5):
+        push_blocks_cuda(src, view, blocks, dst_blocks)
+    ev[1].record()
+    torch.cuda.synchronize()
+    nat.check_status()
+    nbytes = L * len(blocks) * BS * W * 2
+    ms = ev[0].elapsed_time(ev[1]) / 5
+    res = {"push_ms": ms, "gb_s": nbytes / ms / 1e6, "bytes": nbytes}
+    dist.barrier()
+allo = [None, None]
+dist.all_gather_object(allo, res)
+if rank == 0:
+    print("RESULT " + json.dumps(allo))
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_kv_push_between_two_processes_on_two_gpus():
+    """Blocks of a prefill process on GPU 0 land in the paged cache that a decode process owns on GPU 1 (opened
+    through CUDA IPC, written by the push kernel over NVLink): every byte compares equal, untouched blocks stay zero."""
+    prod, cons = _run(2, {}, 29622, worker=KVPUSH_WORKER)
+    assert cons["bytes_equal"]
+    assert prod["gb_s"] > 50.0, prod

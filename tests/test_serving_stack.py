@@ -108,3 +108,55 @@ def test_launcher_detects_dead_child(tmp_path):
     finally:
         la.stop()
     assert not la.children
+
+
+def test_pd_run_and_qwen_one_click_plans(tmp_path):
+    """The launchers keep the reference's option names: per-DP-rank servers with the DP environment, KV roles by
+    instance role, hardware-specific options accepted and ignored, and the one-click Qwen layouts."""
+    import json as _json
+
+    from omni_infer_b200.cli import pd_run, run_model_qwen
+    a = pd_run.parse(["--role", "decode", "--num-servers", "2", "--num-dp", "4", "--server-offset", "2", "--base-api-port", "19001",
+                      "--master-ip", "127.0.0.1", "--master-port", "8503", "--rank-table-path", "x.json", "--hccl-buffsize", "200",
+                      "--enable-mtp", "--num-speculative-tokens", "1", "--cuda-visible-devices", "4,5", "--extra-args=--enforce-eager"])
+    plan = pd_run.build_plan(a)
+    assert [p.env["VLLM_DP_RANK"] for p in plan] == ["2", "3"] and plan[0].env["VLLM_DP_SIZE"] == "4"
+    assert plan[0].env["CUDA_VISIBLE_DEVICES"] == "4" and plan[1].env["CUDA_VISIBLE_DEVICES"] == "5"
+    kv = _json.loads(plan[1].argv[plan[1].argv.index("--kv-transfer-config") + 1])
+    assert kv["kv_role"] == "kv_consumer" and kv["engine_id"].endswith("-3")
+    assert "--num-speculative-tokens" in plan[0].argv and plan[0].argv[-1] == "--enforce-eager"
+    q = run_model_qwen.build_plan(run_model_qwen.parse(["--model-path", "qwen3-30b-a3b", "--deploy-mode", "pd_separate",
+                                                        "--server-list", "0,1,2,3", "--service-port", "6660,6760"]))
+    assert [p.role for p in q] == ["prefill", "prefill", "decode", "decode", "proxy"]
+    assert "--prefill-servers-list" in q[-1].argv and q[2].api_port == 6760
+    m = run_model_qwen.build_plan(run_model_qwen.parse(["--model-path", "qwen2-small", "--server-list", "0,1", "--graph-true", "true"]))
+    assert [p.role for p in m] == ["mixed", "mixed", "proxy"] and "--enforce-eager" not in m[0].argv
+
+
+def test_proxy_launcher_rolls_back_to_the_configuration_that_started(tmp_path):
+    import json as _json
+    import subprocess as sp
+    import sys as _sys
+    import time as _time
+
+    base = [_sys.executable, "-m", "omni_infer_b200.accelerators.sched.global_proxy", "--pid-file", str(tmp_path / "pid"),
+            "--state-dir", str(tmp_path / "state"), "--listen-host", "127.0.0.1", "--log-file", str(tmp_path / "proxy.log")]
+    good = base + ["--listen-port", "18471", "--decode-servers-list", "127.0.0.1:18999"]
+    dry = sp.run(good + ["--dry-run"], capture_output=True, text=True)
+    info = _json.loads(dry.stdout)
+    assert info["nofile"] == 65535 and any("somaxconn" in c for c in info["os_tuning"])
+    try:
+        assert sp.run(good, capture_output=True, text=True).returncode == 0
+        st = _json.loads(sp.run(base + ["--decode-servers-list", "x:1", "--status"], capture_output=True, text=True).stdout)
+        assert st["running"]
+        sp.run(base + ["--decode-servers-list", "x:1", "--stop"], capture_output=True)
+        _time.sleep(0.2)
+        # a configuration that cannot start (port 1 needs privileges / is invalid): the launcher restarts the good one
+        bad = base + ["--listen-port", "1", "--decode-servers-list", "127.0.0.1:18999"]
+        r = sp.run(bad, capture_output=True, text=True)
+        if r.returncode != 0:
+            assert "rolled back" in r.stderr
+            st = _json.loads(sp.run(base + ["--decode-servers-list", "x:1", "--status"], capture_output=True, text=True).stdout)
+            assert st["running"] and "18471" in " ".join(st["config"]["command"])
+    finally:
+        sp.run(base + ["--decode-servers-list", "x:1", "--stop"], capture_output=True)
