@@ -321,7 +321,12 @@ def main():
     step_dev = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     tokens = eng.metrics["generated_tokens"] - tokens0
     launches = nat.launch_count() - launches0
-    nat.check_status()
+    try:
+        nat.check_status()
+    except nat.KernelProtocolError:
+        print(f"[rank {rank}] a bounded wait ran out; device ms per timed step: {[round(x, 2) for x in step_dev]}",
+              file=sys.stderr, flush=True)
+        raise
     ctx_mid = statistics.mean(r.num_computed_tokens for r in eng.scheduler.running) - args.steps / 2
 
     # ---- untimed extras: per-module breakdown of one eager step; the same steps over the NCCL all-to-all baseline

@@ -90,17 +90,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // out, or another role raised `*abort_flag`).  Waits are inlined dozens of times in warp-specialised kernels
 // whose code should stay small, so the path that runs out only records where it gave up in the abort word;
 // the kernel's teardown turns that into the status record (report_abort).
+// A wait's deadline, robust against a single bad timer reading: the limit has to run out twice in a row, each time
+// over half the limit, and a reading that cannot be right (the timer going backwards, or jumping by several
+// limits at once) restarts the measurement instead of ending the wait.
+struct WaitClock {
+  uint64_t t0 = 0;
+  uint32_t expired = 0;
+  // true when the wait has lasted longer than `limit_ns`
+  __device__ __forceinline__ bool over(uint64_t limit_ns) {
+    const uint64_t now = globaltimer_ns();
+    if (t0 == 0) { t0 = now; return false; }
+    const int64_t d = (int64_t)(now - t0);
+    if (d < 0 || (uint64_t)d > 4 * limit_ns) { t0 = now; expired = 0; return false; }
+    if ((uint64_t)d <= limit_ns / 2) return false;
+    t0 = now;
+    return ++expired >= 2;
+  }
+};
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           OmniStatus* /*st*/, int site, int detail) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
+  WaitClock clk;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (((++spins) & 0x3f) == 0) {
       if (*abort_flag) return false;
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > OMNI_WAIT_LIMIT_NS) {
+      if (clk.over(OMNI_WAIT_LIMIT_NS)) {
         *abort_flag = 0x40000000 | ((site & 0xff) << 16) | (detail & 0xffff);
         return false;
       }
@@ -137,12 +153,12 @@ __device__ __forceinline__ int atom_add_release_sys(int* p, int v) {
 __device__ __forceinline__ bool flag_wait_ge(const int* p, int expected, uint64_t limit_ns, OmniStatus* st,
                                              int site, int detail) {
   if (ld_acquire_sys(p) >= expected) return true;
-  uint64_t t0 = globaltimer_ns();
+  WaitClock clk;
   uint32_t spins = 0;
   while (true) {
     if (ld_acquire_sys(p) >= expected) return true;
     if (((++spins) & 0x1f) == 0) {
-      if (globaltimer_ns() - t0 > limit_ns) {
+      if (clk.over(limit_ns)) {
         report_status(st, OMNI_ERR_FLAG_TIMEOUT, site, detail);
         return false;
       }

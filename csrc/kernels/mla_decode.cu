@@ -69,7 +69,7 @@ constexpr int MLA_THREADS = 352;
 // four packed-bf16 q chunks
 constexpr int TM_O = 0, TM_S = 256, TM_Q = 384, TM_COLS = 512;
 
-enum { MS_Q = 1, MS_KV_EMPTY, MS_KV_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT, MS_TMEM };
+enum { MS_Q = 31, MS_KV_EMPTY, MS_KV_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT, MS_TMEM };
 
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {

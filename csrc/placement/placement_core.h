@@ -189,6 +189,23 @@ class GreedyExpertLoadBalancer {
 };
 
 // ------------------------------------------------------------------------------------------------ Static balancer
+// Plans placement changes for one snapshot of activation counts (no history, unlike the greedy balancer above): the
+// target is derived from the loads, the result is a list of instructions bounded by a communication limit.
+struct StaticBalanceOptions {
+  int max_redundant_per_expert = 10;   // replicas of one expert: at most 1 + this
+  int diff_limit = -1;                 // instructions per layer (communication limit); < 0: 2 * world
+  double accept_margin = 0.1;          // a layer's plan is kept only if it lowers max/mean by more than this
+};
+
+struct LayerPlan {
+  int layer = 0;
+  std::vector<int> placement;          // placement after the kept instructions
+  std::vector<ChangeInstruction> instructions;
+  double ratio_before = 1.0, ratio_after = 1.0;   // max rank load / mean rank load, replicas share an expert's load evenly
+  int considered = 0;                  // instructions generated before the limit and the acceptance test cut them
+  bool accepted = false;
+};
+
 class ExpertLoadBalancer {
  public:
   ExpertLoadBalancer(int world, int experts, int slots_per_rank, int ranks_per_host = 8)
@@ -200,6 +217,36 @@ class ExpertLoadBalancer {
   std::vector<ChangeInstruction> bucket_balance(int layer, std::vector<int> placement, const std::vector<double>& loads,
                                                 int max_swaps) const;
   bool validate(const std::vector<int>& placement) const;
+
+  // ---- analysis of one layer ([world*slots] expert id or -1; activations are per position)
+  int positions() const { return world_ * slots_; }
+  std::vector<double> expert_loads(const std::vector<int>& placement, const std::vector<int64_t>& activations) const;
+  std::vector<int> replica_counts(const std::vector<int>& placement) const;
+  std::vector<double> simulated_rank_loads(const std::vector<int>& placement, const std::vector<double>& loads) const;
+  double simulated_ratio(const std::vector<int>& placement, const std::vector<double>& loads) const;
+  double measured_ratio(const std::vector<int>& placement, const std::vector<int64_t>& activations) const;
+  int find_position(const std::vector<int>& placement, int rank, int expert) const;   // -1 if absent
+  int find_empty(const std::vector<int>& placement, int rank) const;                  // -1 if full
+  bool validate_counts(const std::vector<int>& placement, int min_per_rank, int max_per_rank) const;
+  // how many per-rank set differences separate two placements (experts to drop + experts to fetch)
+  int diff_count(const std::vector<int>& from, const std::vector<int>& to) const;
+
+  // ---- planning
+  // One layer: REMOVE of surplus replicas, ADD of replicas of the hottest experts onto the coldest ranks, then SWAPs
+  // between the heaviest and the lightest rank; every prefix of the list leaves a valid placement.  The list is cut at
+  // the communication limit and at its best prefix, and dropped entirely if the gain is within the margin.
+  LayerPlan plan_layer(int layer, const std::vector<int>& placement, const std::vector<int64_t>& activations,
+                       const StaticBalanceOptions& opt) const;
+  // All layers: placement / activations are [layers][world*slots].  Returns the kept instructions with priorities.
+  std::vector<ChangeInstruction> optimize_and_generate_instructions(int layers, const std::vector<int>& placement,
+                                                                    const std::vector<int64_t>& activations,
+                                                                    const StaticBalanceOptions& opt,
+                                                                    std::vector<LayerPlan>* plans = nullptr) const;
+  // prior = 1 + the highest prior of an earlier instruction of the same layer that touches the same expert or the same
+  // position: instructions of equal prior are independent and may run in one exchange wave.  Sorts by (layer, prior).
+  static void assign_priorities(std::vector<ChangeInstruction>& instructions);
+  // applies one instruction to a layer's placement; false (placement untouched) if it does not fit
+  bool apply(std::vector<int>& placement, const ChangeInstruction& ins) const;
 
  private:
   int world_, experts_, slots_, rph_;

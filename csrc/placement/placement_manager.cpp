@@ -442,4 +442,34 @@ int omni_pl_greedy_instructions(const int* placement, const long long* activatio
   return n;
 }
 
+// static planner on host arrays: placement/activations [layers*world*slots].  out: up to max_n instructions of 9 ints
+// (the 8 fields of the greedy call, then the wave priority); ratios: [layers][2] simulated max/mean before and after.
+int omni_pl_static_instructions(const int* placement, const long long* activations, int layers, int world, int experts,
+                                int slots, int ranks_per_host, int max_red, int diff_limit, double accept_margin, int* out,
+                                int max_n, double* ratios) {
+  try {
+    ExpertLoadBalancer b(world, experts, slots, ranks_per_host);
+    StaticBalanceOptions opt;
+    opt.max_redundant_per_expert = max_red; opt.diff_limit = diff_limit; opt.accept_margin = accept_margin;
+    const size_t n_el = (size_t)layers * world * slots;
+    std::vector<LayerPlan> plans;
+    auto v = b.optimize_and_generate_instructions(layers, std::vector<int>(placement, placement + n_el),
+                                                  std::vector<int64_t>(activations, activations + n_el), opt, &plans);
+    if (ratios)
+      for (int l = 0; l < layers; ++l) { ratios[2 * l] = plans[l].ratio_before; ratios[2 * l + 1] = plans[l].ratio_after; }
+    int n = 0;
+    for (auto& i : v) {
+      if (n >= max_n) break;
+      int* o = out + 9 * n++;
+      o[0] = i.layer_idx; o[1] = (int)i.type; o[2] = i.source_rank; o[3] = i.source_expert_id;
+      o[4] = i.source_global_position; o[5] = i.target_rank; o[6] = i.target_expert_id; o[7] = i.target_global_position;
+      o[8] = i.prior;
+    }
+    return n;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "omni_placement: %s\n", e.what());
+    return -1;
+  }
+}
+
 }  // extern "C"

@@ -20,7 +20,19 @@ void LoadBalancer::lock() const {
 }
 void LoadBalancer::unlock() const { s_->lock.store(0, std::memory_order_release); }
 
-bool LoadBalancer::is_up(int i, double now) const { return s_->peers[i].down_until <= now; }
+bool LoadBalancer::is_up(int i, double now) const {
+  lock();
+  const bool up = up_locked(i, now);
+  unlock();
+  return up;
+}
+
+PeerState LoadBalancer::peer(int i) const {
+  lock();
+  PeerState copy = s_->peers[i];
+  unlock();
+  return copy;
+}
 
 void LoadBalancer::mark_failed(int peer, double now) {
   lock();
@@ -32,7 +44,7 @@ void LoadBalancer::mark_failed(int peer, double now) {
 int LoadBalancer::pick(int64_t len, double now, Ticket& t) {
   const int n = s_->n_peers;
   std::vector<int> up;
-  for (int i = 0; i < n; ++i) if (is_up(i, now)) up.push_back(i);
+  for (int i = 0; i < n; ++i) if (up_locked(i, now)) up.push_back(i);
   if (up.empty()) for (int i = 0; i < n; ++i) up.push_back(i);   // everything is down: try anyway
   auto argmin = [&](auto score) {
     int best = up[0];

@@ -80,13 +80,14 @@ class LoadBalancer {
   void prefill_started(int64_t len);
   void prefill_finished(int64_t len);
   void mark_failed(int peer, double now_s);
-  bool is_up(int peer, double now_s) const;
-  const PeerState& peer(int i) const { return s_->peers[i]; }
+  bool is_up(int peer, double now_s) const;       // takes the lock: callable from the metrics thread
+  PeerState peer(int i) const;                    // a snapshot taken under the lock
   int n_peers() const { return s_->n_peers; }
   const LbParams& params() const { return p_; }
 
  private:
   int pick(int64_t len, double now_s, Ticket& t);
+  bool up_locked(int i, double now_s) const { return s_->peers[i].down_until <= now_s; }
   void lock() const;
   void unlock() const;
   LbShared* s_;

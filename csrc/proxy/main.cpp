@@ -324,7 +324,7 @@ static std::string metrics_text() {
   auto dump = [&](const char* pool, LoadBalancer* lb) {
     if (!lb) return;
     for (int i = 0; i < lb->n_peers(); ++i) {
-      const PeerState& p = lb->peer(i);
+      const PeerState p = lb->peer(i);
       o << "omni_proxy_active_requests{pool=\"" << pool << "\",peer=\"" << i << "\"} " << p.active_requests << "\n";
       o << "omni_proxy_request_length{pool=\"" << pool << "\",peer=\"" << i << "\"} " << p.total_request_length << "\n";
       o << "omni_proxy_decode_tokens{pool=\"" << pool << "\",peer=\"" << i << "\"} " << p.total_decode_num << "\n";

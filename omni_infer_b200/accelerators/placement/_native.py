@@ -54,6 +54,7 @@ def lib():
             ("omni_pl_placement_last_instructions", ci, [vp, vp, ci]),
             ("omni_pl_static_placement", ci, [vp, ci, ci, ci, ci, ci, vp]),
             ("omni_pl_greedy_instructions", ci, [vp, vp, ci, ci, ci, ci, ci, vp, ci]),
+            ("omni_pl_static_instructions", ci, [vp, vp, ci, ci, ci, ci, ci, ci, ci, cd, vp, ci, vp]),
             ("omni_pl_set_copy_hooks", None, [COPY_FN, COPY_FN, COPY_FN]),
             ("omni_pl_set_ut_memcpy", None, []),
             ("omni_pl_unset_ut_memcpy", None, []),

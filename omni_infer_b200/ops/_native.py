@@ -105,6 +105,15 @@ class KernelProtocolError(RuntimeError):
     """A kernel gave up on a bounded wait (code, site, block, detail)."""
 
 
+def _site_kernel(site: int) -> str:
+    """Which kernel family a wait-site id belongs to (each family numbers its sites in its own decade)."""
+    for lo, hi, name in ((1, 9, "weight-major GEMM"), (11, 19, "prefill attention"), (21, 29, "token-major GEMM"),
+                         (31, 39, "MLA decode"), (41, 49, "TP collectives"), (200, 299, "EP dispatch/combine")):
+        if lo <= site <= hi:
+            return name
+    return "an unnamed kernel"
+
+
 def check_status(device=None, reset: bool = True) -> None:
     """Synchronise and raise :class:`KernelProtocolError` if any kernel reported a failed wait."""
     buf = status_buffer(device)
@@ -114,7 +123,8 @@ def check_status(device=None, reset: bool = True) -> None:
             buf.zero_()
         what = {1: "mbarrier wait gave up", 2: "flag wait gave up", 3: "index out of bounds (access skipped)",
                 4: "capacity exceeded"}.get(vals[0], "kernel error")
-        raise KernelProtocolError(f"{what}: code={vals[0]} site={vals[1]} block={vals[2]} detail={vals[3]}")
+        raise KernelProtocolError(f"{what} in {_site_kernel(vals[1])}: code={vals[0]} site={vals[1]} block={vals[2]} "
+                                  f"detail={vals[3]}")
 
 
 def check_rc(rc: int, what: str) -> None:

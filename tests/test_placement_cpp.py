@@ -10,15 +10,35 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = os.path.join(ROOT, "csrc", "placement")
 
 
-def test_cpp_unit_tests_pass_under_sanitizers(tmp_path):
-    exe = str(tmp_path / "test_placement")
-    srcs = [os.path.join(SRC, f) for f in ("placement_mapping.cpp", "placement_balancer.cpp", "placement_manager.cpp",
-                                           "test_placement.cpp")]
-    cmd = ["g++", "-O1", "-g", "-std=c++17", "-Wall", "-pthread", "-fsanitize=address,undefined", "-I", SRC, "-o", exe] + srcs
+CORE = ("placement_mapping.cpp", "placement_balancer.cpp", "placement_static.cpp", "placement_manager.cpp")
+
+
+def _build_and_run(tmp_path, name, test_source, sanitizer):
+    exe = str(tmp_path / name)
+    srcs = [os.path.join(SRC, f) for f in (*CORE, test_source)]
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-Wall", "-pthread", f"-fsanitize={sanitizer}", "-I", SRC, "-o", exe] + srcs
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0 and "sanitize" in res.stderr:
+        if sanitizer == "thread":
+            pytest.skip("-fsanitize=thread is not available with this compiler")
         cmd = [c for c in cmd if not c.startswith("-fsanitize")]
         res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-3000:]
-    run = subprocess.run([exe], capture_output=True, text=True, timeout=120)
-    assert run.returncode == 0 and "ALL PASSED" in run.stdout, run.stdout + run.stderr
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and "ALL PASSED" in run.stdout, run.stdout + run.stderr[-3000:]
+    return run
+
+
+def test_cpp_unit_tests_pass_under_sanitizers(tmp_path):
+    _build_and_run(tmp_path, "test_placement", "test_placement.cpp", "address,undefined")
+
+
+def test_cpp_static_planner_tests_pass_under_sanitizers(tmp_path):
+    """Snapshot planner of the static balancer: helpers, instruction semantics, limits, priorities, 300 random cases."""
+    _build_and_run(tmp_path, "test_placement_static", "test_placement_static.cpp", "address,undefined")
+
+
+def test_cpp_manager_threads_are_race_free_under_thread_sanitizer(tmp_path):
+    """The two-rank round of the manager test runs its ranks as threads over the in-process transport."""
+    run = _build_and_run(tmp_path, "test_placement_tsan", "test_placement.cpp", "thread")
+    assert "ThreadSanitizer" not in run.stderr, run.stderr[-3000:]

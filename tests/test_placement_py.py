@@ -81,3 +81,129 @@ def test_pattern_tool(tmp_path):
     assert after["max_over_mean_rank_load"] < before["max_over_mean_rank_load"]
     # the generated pattern loads into the mapping
     ExpertMapping(pat, world, 1, layers, experts, redundant_per_rank=2).close()
+
+
+def _write_dumps(folder, counts, parts=2):
+    folder.mkdir(exist_ok=True)
+    for i in range(parts):
+        np.savetxt(folder / f"activation_rank0_{i}.txt", counts / parts, fmt="%d")
+
+
+def test_pattern_tool_steps_from_logs_to_analysis(tmp_path, capsys):
+    """logs -> CSV (mode and step filters, tiles, malformed lines), CSV -> patterns in both modes with a special-layer
+    count, check + view, analysis table: each step reads the file the previous one wrote."""
+    layers, world, per = 3, 4, 2
+    log = tmp_path / "act.log"
+    lines = []
+    rng = np.random.default_rng(0)
+    truth = np.zeros((layers, world * per))
+    for step in range(10):
+        for r in range(world):
+            for l in range(layers):
+                v = rng.integers(0, 300, per)
+                if l == 1 and r == 0:
+                    v[0] += 5000                      # layer 1: expert 0 is hot
+                mode = "decode" if step % 2 else "prefill"
+                lines.append(f"INFO xyz [dump activation] {mode} step {step} in rank {r} for layer {l} get {per} experts data: "
+                             + "\t".join(map(str, v)))
+                if mode == "decode" and 3 <= step <= 8:
+                    truth[l, r * per:(r + 1) * per] += np.ceil(v / 128)
+    lines.append("[dump activation] decode step 4 in rank 9 for layer 0 get 2 experts data: 1\t2")      # rank out of range
+    lines.append("[dump activation] decode step 4 in rank 0 for layer 0 get 3 experts data: 1\t2\t3")   # wrong width
+    lines.append("unrelated line")
+    log.write_text("\n".join(lines) + "\n")
+    csv_path = tmp_path / "counts.csv"
+    assert pattern_tool.main(["logs-to-csv", "--inputs", str(log), "--input-mode", "log", "--layers", str(layers),
+                              "--world-of-data", str(world), "--positions", str(world * per), "--collecting-mode", "decode",
+                              "--step-range", "3:8", "--tile", "128", "--out", str(csv_path)]) == 0
+    import json
+    info = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert info["skipped_lines"] == 2 and info["layers"] == layers and info["columns"] == world * per
+    got = pattern_tool.read_csv(str(csv_path))
+    assert np.array_equal(got, truth)
+    with pytest.raises(ValueError):
+        pattern_tool.parse_step_range("9:3")
+
+    outdir = tmp_path / "patterns"
+    assert pattern_tool.main(["generate", "--csv", str(csv_path), "--outdir", str(outdir), "--world", str(world),
+                              "--mode", "all", "--redundant-per-rank", "1", "--special-layers", "-1", "1"]) == 0
+    names = sorted(p.name for p in outdir.iterdir())
+    assert names == ["pattern_rearrange_1layers_4ranks.npy", "pattern_rearrange_alllayers_4ranks.npy",
+                     "pattern_redundant_1layers_4ranks.npy", "pattern_redundant_alllayers_4ranks.npy"]
+    base = base_pattern(world, layers, world * per)
+    one = np.load(outdir / "pattern_redundant_1layers_4ranks.npy")
+    assert one.shape == (world, layers, world * per)
+    assert np.array_equal(one[:, 0], base[:, 0]) and np.array_equal(one[:, 2], base[:, 2])     # only the worst layer changed
+    assert one[:, 1, 0].sum() >= 2                                                            # its hot expert is replicated
+    re = np.load(outdir / "pattern_rearrange_alllayers_4ranks.npy")
+    assert (re.sum(axis=0) == 1).all() and (re.sum(axis=2) == per).all()                      # a permutation per layer
+
+    view = tmp_path / "view.txt"
+    assert pattern_tool.main(["check", "--pattern", str(outdir / "pattern_redundant_1layers_4ranks.npy"),
+                              "--redundant-per-rank", "1", "--view", str(view)]) == 0
+    text = view.read_text()
+    assert "layer 1:" in text and "0*" in text and "rank 3:" in text
+    broken = one.copy()
+    broken[:, 0, 3] = 0
+    np.save(tmp_path / "broken.npy", broken)
+    with pytest.raises(AssertionError):
+        pattern_tool.main(["check", "--pattern", str(tmp_path / "broken.npy")])
+
+    table = tmp_path / "analysis.csv"
+    capsys.readouterr()
+    assert pattern_tool.main(["analyse", "--csv", str(csv_path), "--patterns", *[str(outdir / n) for n in names],
+                              "--out", str(table)]) == 0
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["mean_max_over_mean"]
+    assert summary["pattern_redundant_alllayers_4ranks"] < summary["base"]
+    assert summary["pattern_rearrange_alllayers_4ranks"] <= summary["base"] + 1e-9
+    import csv
+    rows = list(csv.DictReader(open(table)))
+    assert len(rows) == 5 * layers and {"deployment", "layer", "rank_0", "best", "max", "max_over_mean",
+                                        "max_load_reduction"} <= set(rows[0])
+    hot = [r for r in rows if r["deployment"] == "pattern_redundant_alllayers_4ranks" and r["layer"] == "1"][0]
+    assert float(hot["max_load_reduction"]) > 0.3
+
+
+def test_pattern_tool_pipeline_and_incremental_plan(tmp_path, capsys):
+    import json
+    layers, world, per, red = 2, 4, 2, 1
+    slots = per + red
+    counts = np.full((layers, world * per), 40.0)
+    counts[0, 0] = 900
+    dumps = tmp_path / "decode"
+    _write_dumps(dumps, counts)
+    work = tmp_path / "work"
+    assert pattern_tool.main(["pipeline", "--inputs", str(dumps), "--world", str(world), "--redundant-per-rank", str(red),
+                              "--workdir", str(work)]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["mean_max_over_mean"]["pattern_redundant_alllayers_4ranks"] < out["mean_max_over_mean"]["base"]
+    for f in ("topk_id_count.csv", "load_analysis.csv", "pattern_redundant_alllayers_4ranks.npy",
+              "pattern_redundant_alllayers_4ranks.view.txt"):
+        assert (work / f).exists(), f
+
+    # incremental plan from the base layout with per-position dumps taken under it
+    cur = base_pattern(world, layers, world * per)
+    np.save(tmp_path / "cur.npy", cur)
+    placement = pattern_tool.pattern_to_placement(cur, slots)
+    pos_counts = np.zeros_like(placement, dtype=np.float64)
+    for l in range(layers):
+        for p, e in enumerate(placement[l]):
+            if e >= 0:
+                pos_counts[l, p] = counts[l, e]
+    pdumps = tmp_path / "pos"
+    _write_dumps(pdumps, pos_counts, parts=1)
+    plan_path = tmp_path / "plan.json"
+    assert pattern_tool.main(["plan", "--current-pattern", str(tmp_path / "cur.npy"), "--dumps", str(pdumps), "--slots", str(slots),
+                              "--diff-limit", "2", "--out", str(plan_path)]) == 0
+    plan = json.loads(plan_path.read_text())
+    ins = plan["instructions"]
+    assert 1 <= len(ins) <= 2 and all(i["layer"] == 0 for i in ins)          # layer 1 is flat: nothing planned
+    assert ins[0]["op"] == "add" and ins[0]["source_expert"] == 0 and ins[0]["wave"] == 1
+    assert plan["ratio_after"][0] < plan["ratio_before"][0] - 0.1 and plan["ratio_after"][1] == plan["ratio_before"][1]
+    # the library call agrees and rejects a bad placement
+    ins2, ratios = pattern_tool.plan_instructions(placement, pos_counts, world, world * per, diff_limit=2)
+    assert ins2 == ins and ratios.shape == (layers, 2)
+    bad = placement.copy()
+    bad[0, 0] = 1
+    with pytest.raises(RuntimeError):
+        pattern_tool.plan_instructions(bad, pos_counts, world, world * per)

@@ -37,6 +37,31 @@ def test_cpp_lb_and_json_units(tmp_path):
     assert run.returncode == 0 and "ALL PASSED" in run.stdout, run.stdout + run.stderr
 
 
+def _build(tmp_path, name, sources, sanitizer):
+    exe = str(tmp_path / name)
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-Wall", "-pthread", f"-fsanitize={sanitizer}", "-I", SRC, "-o", exe,
+           *[os.path.join(SRC, f) for f in sources]]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0 and "sanitize" in res.stderr:
+        pytest.skip(f"-fsanitize={sanitizer} is not available with this compiler")
+    assert res.returncode == 0, res.stderr[-3000:]
+    return exe
+
+
+def test_cpp_lb_state_is_race_free_under_thread_sanitizer(tmp_path):
+    """Worker threads, the stream filters, peer ejection and a metrics reader on one balancer state, every policy."""
+    exe = _build(tmp_path, "test_lb_threads_tsan", ("lb.cpp", "test_lb_threads.cpp"), "thread")
+    run = subprocess.run([exe, "--no-fork"], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and "ALL PASSED" in run.stdout, run.stdout + run.stderr[-3000:]
+    assert "ThreadSanitizer" not in run.stderr, run.stderr[-3000:]
+
+
+def test_cpp_lb_state_shared_between_forked_workers(tmp_path):
+    exe = _build(tmp_path, "test_lb_threads_asan", ("lb.cpp", "test_lb_threads.cpp"), "address,undefined")
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and "ALL PASSED" in run.stdout, run.stdout + run.stderr[-3000:]
+
+
 class _Recorder:
     def __init__(self):
         self.requests = []
@@ -168,6 +193,47 @@ def test_prefill_failure_passthrough_and_peer_ejection(proxy_binary):
         proc.wait(timeout=5)
         for s in (p_srv, d_ok, d_srv):
             s.shutdown()
+
+
+def test_proxy_under_thread_sanitizer_serves_concurrent_requests(tmp_path):
+    """The whole proxy (event loop, upstream threads, metrics) built with ThreadSanitizer, one worker process,
+    16 concurrent clients; the run must end without a data-race report."""
+    exe = _build(tmp_path, "omni_proxy_tsan", ("lb.cpp", "main.cpp"), "thread")
+    rec = _Recorder()
+    p_srv, d_srv = _make_server("prefill", rec), _make_server("decode", rec)
+    port = _free_port()
+    log = open(tmp_path / "tsan.log", "w")
+    cmd = [exe, "--listen", f"127.0.0.1:{port}", "--decode-servers", f"127.0.0.1:{d_srv.server_port}",
+           "--prefill-servers", f"127.0.0.1:{p_srv.server_port}", "--log-level", "0", "--workers", "1"]
+    proc = subprocess.Popen(cmd, stderr=log)
+    try:
+        for _ in range(200):
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=0.5).read()
+                break
+            except Exception:
+                time.sleep(0.05)
+        results = []
+
+        def client(i):
+            for k in range(4):
+                results.append(_post(port, {"prompt": f"p{i}", "max_tokens": 4, "stream": k % 2 == 0})[0])
+                urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read()
+
+        ts = [threading.Thread(target=client, args=(i,)) for i in range(16)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        assert results.count(200) == 64, results
+    finally:
+        proc.terminate()
+        proc.wait(timeout=20)
+        log.close()
+        p_srv.shutdown()
+        d_srv.shutdown()
+    report = (tmp_path / "tsan.log").read_text()
+    assert "ThreadSanitizer" not in report, report[-4000:]
 
 
 def test_launcher_dry_run(capsys):
