@@ -66,6 +66,11 @@ ep_dispatch_send_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __re
     slot = __shfl_sync(0xffffffffu, slot, 0);
     if (slot >= L.cap) {                       // never write past the region: drop and report
       if (lane == 0) report_status(status, OMNI_ERR_CAPACITY, 200, d);
+      // nobody will answer for this pair, and its row of the combine buffer still holds an older round's output for
+      // some other token: clear it, so that the reduction adds zero (the previous round's reduction has finished:
+      // it ran earlier on this stream)
+      uint4* z4 = reinterpret_cast<uint4*>(self + L.off_comb + (size_t)i * H * 2);
+      for (int c = lane; c < (H >> 3); c += 32) z4[c] = make_uint4(0u, 0u, 0u, 0u);
       continue;
     }
     unsigned char* dst = peers.p[d];

@@ -177,6 +177,14 @@ class GreedyExpertLoadBalancer {
                                                                     const std::vector<int64_t>& activations);
   static double imbalance(const std::vector<double>& rank_loads);   // max / min (min clipped to > 0)
   const std::vector<double>& ema_loads() const { return ema_; }
+  bool has_ema() const { return has_ema_; }
+  // restores the moving average saved by an earlier run (same [layers][positions] shape); false if the size differs
+  bool set_ema(const std::vector<double>& ema) {
+    if (ema.size() != ema_.size()) return false;
+    ema_ = ema;
+    has_ema_ = true;
+    return true;
+  }
 
  private:
   void optimize_layer(int layer, std::vector<int>& place, std::vector<double>& load, std::vector<ChangeInstruction>& out);
@@ -366,6 +374,10 @@ class Placement {
   int rounds() const { return rounds_; }
   int skipped_instructions() const { return skipped_; }
   std::vector<ChangeInstruction> last_instructions() const;
+  // the balancer's moving average of position loads: saved at shutdown and restored at start so that a restart does
+  // not begin from a cold history.  Both take the manager's lock (the background thread updates the average).
+  std::vector<double> ema_snapshot();
+  bool restore_ema(const std::vector<double>& ema);
 
  private:
   void loop();
@@ -379,6 +391,7 @@ class Placement {
   std::thread thread_;
   std::atomic<bool> should_stop_{false};
   std::mutex mu_;
+  std::mutex ema_mu_;   // the optimizer's history: a round updates it, snapshot / restore read and write it
   std::condition_variable cv_;
   std::vector<PendingApply> pending_;
   std::vector<ChangeInstruction> last_;

@@ -191,9 +191,23 @@ void Placement::loop() {
 
 std::vector<ChangeInstruction> Placement::last_instructions() const { return last_; }
 
+std::vector<double> Placement::ema_snapshot() {
+  std::lock_guard<std::mutex> lk(ema_mu_);
+  return optimizer_->balancer().has_ema() ? optimizer_->balancer().ema_loads() : std::vector<double>();
+}
+
+bool Placement::restore_ema(const std::vector<double>& ema) {
+  std::lock_guard<std::mutex> lk(ema_mu_);
+  return optimizer_->balancer().set_ema(ema);
+}
+
 int Placement::run_round() {
   act_->collect();
-  auto instr = optimizer_->optimize();
+  std::vector<ChangeInstruction> instr;
+  {
+    std::lock_guard<std::mutex> lk(ema_mu_);
+    instr = optimizer_->optimize();
+  }
   last_ = instr;
   int done = 0;
   next_stage_ = 0;
@@ -409,6 +423,18 @@ int omni_pl_placement_last_instructions(void* p, int* out, int max_n) {
     o[4] = i.source_global_position; o[5] = i.target_rank; o[6] = i.target_expert_id; o[7] = i.target_global_position;
   }
   return n;
+}
+
+// moving average of the balancer: returns the number of doubles written (0 when no round has run yet), -1 if `max_n`
+// is too small
+int omni_pl_placement_get_ema(void* p, double* out, int max_n) {
+  auto v = ((Placement*)p)->ema_snapshot();
+  if ((int)v.size() > max_n) return -1;
+  memcpy(out, v.data(), v.size() * sizeof(double));
+  return (int)v.size();
+}
+int omni_pl_placement_set_ema(void* p, const double* in, int n) {
+  return ((Placement*)p)->restore_ema(std::vector<double>(in, in + n)) ? 0 : -1;
 }
 
 // static placement from per-expert loads: out[world*slots]

@@ -56,6 +56,7 @@ struct Config {
   int workers = 1, threads = 64, retries = 2;
   double timeout_s = 600.0, connect_timeout_s = 3.0;
   int log_level = 1;
+  bool timeline = false;   // one "<<<Action" line per request stage on stderr, in the engine's format
 };
 
 static Config g_cfg;
@@ -64,6 +65,16 @@ static LbShared* g_shm_decode = nullptr;
 static LoadBalancer* g_lb_prefill = nullptr;
 static LoadBalancer* g_lb_decode = nullptr;
 static volatile sig_atomic_t g_stop = 0;
+
+// Per-request timeline in the format of the engine's logger, so that one tool can merge the proxy's and the engines'
+// lines by request id (wall clock: the processes share no monotonic origin).
+static void timeline(const char* action, const std::string& rid) {
+  if (!g_cfg.timeline) return;
+  const double t = std::chrono::duration<double>(std::chrono::system_clock::now().time_since_epoch()).count();
+  char line[512];
+  const int n = snprintf(line, sizeof(line), "<<<Action: %s; Timestamp:%.6f; RequestID:%s; Role:proxy\n", action, t, rid.c_str());
+  if (n > 0) (void)!write(STDERR_FILENO, line, (size_t)std::min<int>(n, (int)sizeof(line) - 1));   // one write: lines of concurrent requests do not interleave
+}
 
 static double now_s() {
   return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
@@ -265,9 +276,11 @@ static bool run_prefill(const HttpMessage& req, const std::string& body, HttpMes
     std::string wire = r.serialize_head() + body;
     std::string rest;
     HttpMessage resp;
+    timeline("Proxy sends to prefill", req.header("X-Request-Id"));
     const bool got = send_all(up, wire.data(), wire.size(), g_cfg.timeout_s) && read_head(up, resp, rest, g_cfg.timeout_s) &&
                      read_body_all(up, resp, rest, g_cfg.timeout_s);
     close(up);
+    if (got) timeline("Proxy got prefill response", req.header("X-Request-Id"));
     g_lb_prefill->free_peer(t, !got, now_s());
     if (got) { out = resp; ok = true; }
   }
@@ -291,6 +304,7 @@ static bool run_decode(int client, const HttpMessage& req, const std::string& bo
     r.set_header("Connection", "close");
     r.remove_header("Transfer-Encoding");
     std::string wire = r.serialize_head() + body;
+    timeline("Proxy sends to decode", req.header("X-Request-Id"));
     bool sent = send_all(up, wire.data(), wire.size(), g_cfg.timeout_s);
     bool any = false, client_ok = true;
     char buf[16384];
@@ -299,6 +313,7 @@ static bool run_decode(int client, const HttpMessage& req, const std::string& bo
       if (!wait_fd(up, POLLIN, g_cfg.timeout_s)) break;
       ssize_t n = recv(up, buf, sizeof(buf), 0);
       if (n <= 0) break;
+      if (!any) timeline("Proxy relays first decode bytes", req.header("X-Request-Id"));
       any = true;
       if (!send_all(client, buf, (size_t)n, g_cfg.timeout_s)) { client_ok = false; break; }
       std::string view = tail + std::string(buf, (size_t)n);
@@ -346,6 +361,8 @@ static void handle_connection(int client) {
   if (req.method == "GET" && req.path == "/health") { send_simple(client, 200, "OK", "{\"status\":\"ok\"}"); close(client); return; }
   if (req.method == "GET" && req.path == "/metrics") { send_simple(client, 200, "OK", metrics_text(), "text/plain; version=0.0.4"); close(client); return; }
   if (req.header("X-Request-Id").empty()) req.set_header("X-Request-Id", make_request_id());
+  const std::string rid = req.header("X-Request-Id");
+  timeline("Proxy got request", rid);
   std::string body = req.body;
   const bool generation = req.method == "POST" && (req.path == "/v1/completions" || req.path == "/v1/chat/completions");
   if (generation && !g_cfg.prefill.empty()) {
@@ -370,6 +387,7 @@ static void handle_connection(int client) {
     }
   }
   run_decode(client, req, body);
+  timeline("Proxy finished request", rid);
   shutdown(client, SHUT_RDWR);
   close(client);
 }
@@ -480,6 +498,7 @@ int main(int argc, char** argv) {
     else if (a == "--retries") g_cfg.retries = atoi(val().c_str());
     else if (a == "--timeout") g_cfg.timeout_s = atof(val().c_str());
     else if (a == "--log-level") g_cfg.log_level = atoi(val().c_str());
+    else if (a == "--timeline") g_cfg.timeline = true;
     else if (a == "--dump-config") dump = true;
     else if (a == "--help") { printf("omni_proxy --listen host:port --prefill-servers h:p,... --decode-servers h:p,... [--prefill-lb P] [--decode-lb P]\n  policies: pd_score_balance prefill_score_balance weighted_least_active length_balance greedy_timeout auto_balance_controller least_total_load round_robin\n"); return 0; }
     else { fprintf(stderr, "unknown option %s\n", a.c_str()); return 2; }

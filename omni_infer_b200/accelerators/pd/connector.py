@@ -233,10 +233,12 @@ class SchedulerConnector:
 
     # -- producer
     def request_finished(self, req, block_ids: list):
-        """Returns (delay_free, kv_transfer_params).  Only requests capped at their prefill token hand over KV."""
+        """Returns (delay_free, kv_transfer_params).  On a producer every request that ends at its token cap hands its
+        KV over (the proxy's prefill leg is a plain request with max_tokens = 1 and no flag of its own, as in the
+        reference's connector, llmdatadist_connector_v1.py:209-228); ``do_remote_decode: false`` opts a request out."""
         from ...engine.request import RequestStatus
         p = req.kv_transfer_params or {}
-        if not (self.is_producer and p.get("do_remote_decode") and req.status == RequestStatus.FINISHED_LENGTH_CAPPED):
+        if not (self.is_producer and p.get("do_remote_decode", True) and req.status == RequestStatus.FINISHED_LENGTH_CAPPED):
             return False, None
         n_blocks = (len(req.prompt_token_ids) + self.block_size - 1) // self.block_size
         params = {"do_remote_prefill": True, "do_remote_decode": False, "remote_block_ids": list(block_ids[:n_blocks]),

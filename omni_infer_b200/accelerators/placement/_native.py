@@ -52,6 +52,8 @@ def lib():
             ("omni_pl_placement_rounds", ci, [vp]),
             ("omni_pl_placement_skipped", ci, [vp]),
             ("omni_pl_placement_last_instructions", ci, [vp, vp, ci]),
+            ("omni_pl_placement_get_ema", ci, [vp, vp, ci]),
+            ("omni_pl_placement_set_ema", ci, [vp, vp, ci]),
             ("omni_pl_static_placement", ci, [vp, ci, ci, ci, ci, ci, vp]),
             ("omni_pl_greedy_instructions", ci, [vp, vp, ci, ci, ci, ci, ci, vp, ci]),
             ("omni_pl_static_instructions", ci, [vp, vp, ci, ci, ci, ci, ci, ci, ci, cd, vp, ci, vp]),

@@ -84,7 +84,7 @@ class OmniPlanner(metaclass=_Singleton):
             cfg = dict(yaml.safe_load(open(cfg["config_path"])) or {}, **{k: v for k, v in cfg.items() if k != "config_path"})
         layers = model_cfg.num_hidden_layers - model_cfg.first_k_dense_replace
         layers = min(layers, int(cfg.get("max_moe_layer_num", layers)))
-        pattern = None
+        pattern = cfg.get("pattern")          # an array handed over directly (restored state)
         if cfg.get("pattern_path"):
             pattern = np.load(cfg["pattern_path"])
         dev = "cuda" if torch.cuda.is_available() and os.environ.get("NO_GPU_MOCK", "0") != "1" else "cpu"
@@ -273,7 +273,52 @@ class OmniPlanner(metaclass=_Singleton):
             self._dist = self._make_distribution()
             self._placement = L.omni_pl_placement_create(self.mapping.handle, self._weights, self._act, self._dist,
                                                          self.max_redundant_per_expert, self.period_s)
+            self._restore_ema()
         return self._placement
+
+    # ------------------------------------------------------------------ state kept across restarts
+    pending_ema = None         # (saved positions [layers, P], saved averages [layers, P]) or a bare average array
+
+    def export_state(self) -> dict:
+        """What a restart needs to continue where this run stands: the placement as a 0/1 pattern (the start-up
+        format), the same placement position by position, and the balancer's moving average of position loads."""
+        from .expert_mapping import pattern_from_placement
+        placement = self.mapping.placement()
+        out = {"placement_pattern": pattern_from_placement(placement, self.world, self.slots_per_rank, self.experts),
+               "placement_positions": placement}
+        if self._placement is not None:
+            buf = np.zeros(self.layers * self.num_positions, dtype=np.float64)
+            n = nat.lib().omni_pl_placement_get_ema(self._placement, buf.ctypes.data, buf.size)
+            if n == buf.size:
+                out["placement_ema"] = buf.reshape(self.layers, self.num_positions)
+        return out
+
+    def _restore_ema(self) -> None:
+        """Hands a saved moving average to the new balancer.  A placement restored from its pattern fills each rank's
+        slots in expert order, which need not be the order they had when the average was saved, so the values are
+        carried over by (layer, rank, expert), not by position."""
+        pend = self.pending_ema
+        self.pending_ema = None
+        if pend is None:
+            return
+        saved_pos, ema = pend if isinstance(pend, tuple) else (None, pend)
+        ema = np.asarray(ema, dtype=np.float64)
+        if ema.shape != (self.layers, self.num_positions):
+            logger.info("saved load history has shape %s, this deployment needs %s: ignored", ema.shape,
+                        (self.layers, self.num_positions))
+            return
+        now = self.mapping.placement()
+        if saved_pos is not None and np.asarray(saved_pos).shape == now.shape and not np.array_equal(saved_pos, now):
+            S, remapped = self.slots_per_rank, np.zeros_like(ema)
+            for l in range(self.layers):
+                for r in range(self.world):
+                    old = {int(e): ema[l, r * S + k] for k, e in enumerate(saved_pos[l, r * S:(r + 1) * S]) if e >= 0}
+                    for k, e in enumerate(now[l, r * S:(r + 1) * S]):
+                        remapped[l, r * S + k] = old.get(int(e), 0.0)
+            ema = remapped
+        ema = np.ascontiguousarray(ema)
+        if nat.lib().omni_pl_placement_set_ema(self._placement, ema.ctypes.data, ema.size) != 0:
+            logger.warning("the balancer refused the saved load history")
 
     def start_dynamic_optimize_expert_load_balance(self) -> None:
         nat.lib().omni_pl_placement_start(self._ensure_placement())

@@ -39,6 +39,8 @@ def build_command(a) -> list:
            "--batch-size", str(a.batch_size), "--decode-req-limit", str(a.decode_req_limit)]
     if a.prefill_servers_list:
         cmd += ["--prefill-servers", a.prefill_servers_list]
+    if a.timeline:
+        cmd.append("--timeline")
     return cmd
 
 
@@ -57,6 +59,7 @@ def parse(argv=None):
     ap.add_argument("--decode-req-limit", type=int, default=0)
     ap.add_argument("--fail-timeout", type=float, default=10.0)
     ap.add_argument("--log-level", type=int, default=1)
+    ap.add_argument("--timeline", action="store_true", help="per-request stage lines in the log (utils/timeline.py reads them)")
     ap.add_argument("--pid-file", default="/tmp/omni_proxy.pid")
     ap.add_argument("--log-file", default="/tmp/omni_proxy.log")
     ap.add_argument("--stop", action="store_true")

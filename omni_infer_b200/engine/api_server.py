@@ -28,6 +28,7 @@ from typing import Optional
 from .engine_core import EngineConfig, EngineCore
 from .request import SamplingParams
 from .tokenizer_pool import TokenizerPool
+from ..utils import timeline
 
 logger = logging.getLogger("omni_infer_b200.api")
 
@@ -95,6 +96,10 @@ class AsyncEngine:
 
     def stop(self):
         self._stop = True
+        try:
+            self.engine.save_state()
+        except Exception:                      # shutting down: a state file that cannot be written must not hang it
+            logging.getLogger("omni_infer_b200.api_server").exception("could not write the state directory")
 
 
 def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
@@ -155,6 +160,7 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                                 temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
                                 top_p=float(body.get("top_p", 1.0) or 1.0), ignore_eos=bool(body.get("ignore_eos", False)))
             rid = self.headers.get("X-Request-Id") or ("cmpl-" + uuid.uuid4().hex)
+            timeline.emit("Get request in api server", rid, role=aeng.engine.role)
             q = aeng.submit(ids, sp, rid, kvp)
             stream = bool(body.get("stream", False))
             created = int(time.time())
@@ -179,6 +185,8 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                     o = q.get(timeout=600)
                     if o is None:
                         raise RuntimeError("engine failure")
+                    if not out_ids and o.new_token_ids:
+                        timeline.emit("First token out of api server", rid, role=aeng.engine.role)
                     out_ids += o.new_token_ids
                     if stream and (o.new_token_ids or o.finished):
                         self.wfile.write(("data: " + json.dumps(chunk_obj(tok.decode(o.new_token_ids), o.finish_reason if o.finished else None)) + "\n\n").encode())
@@ -194,6 +202,7 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                 if not stream:
                     return self._json(500, {"error": str(e) or "timeout"})
                 return
+            timeline.emit("Finish response in api server", rid, role=aeng.engine.role)
             if stream:
                 self.wfile.write(b"data: [DONE]\n\n")
                 self.wfile.flush()

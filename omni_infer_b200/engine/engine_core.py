@@ -54,6 +54,8 @@ class EngineConfig:
     omni_attn_config: Optional[dict] = None
     placement_config: Optional[dict] = None
     eos_token_id: Optional[int] = None
+    # per-rank state kept across restarts (KV block count, captured graph buckets, placement pattern and load history)
+    state_dir: Optional[str] = os.environ.get("OMNI_STATE_DIR") or None
 
 
 class EngineCore:
@@ -77,15 +79,35 @@ class EngineCore:
                                  kv_connector=worker_conn, dense_mlp_tp_size=cfg.dense_mlp_tp_size,
                                  o_proj_tp_size=cfg.o_proj_tp_size, pp_size=cfg.pp_size)
         self.worker.init_device()
+        self.state = None
+        if cfg.state_dir:
+            from ..parallel import get_parallel_state as _ps
+            from .state_dir import StateDir, fingerprint
+            self.state = StateDir(cfg.state_dir, _ps().rank, fingerprint(self.model_cfg, cfg, _ps().world_size))
         if planner is None and cfg.placement_config:
             # the planner sizes its slot tables from the world size, so it is built after the process group exists
             from ..accelerators.placement import OmniPlanner
-            planner = OmniPlanner.from_config(cfg.placement_config, self.model_cfg)
+            pc = dict(cfg.placement_config)
+            saved = self.state.get_array("placement_pattern") if self.state is not None else None
+            if saved is not None and not pc.get("pattern_path"):
+                pc["pattern"] = saved          # the placement the previous run had arrived at
+            planner = OmniPlanner.from_config(pc, self.model_cfg)
             self.worker.planner = self.worker.runner.planner = planner
+        self.planner = planner
         self.worker.load_model(weights, seed=cfg.seed)
+        if self.state is not None and not rc.num_kv_blocks and self.state.get("num_kv_blocks"):
+            rc.num_kv_blocks = int(self.state.get("num_kv_blocks"))      # skips the profile run; ranks still agree on the minimum
         n_blocks = self.worker.determine_available_memory()
         self.worker.initialize_cache(n_blocks)
         self.worker.compile_or_warm_up_model()
+        if self.state is not None:
+            graphs = getattr(self.worker.runner, "graphs", None)
+            self.state.save(num_kv_blocks=int(n_blocks),
+                            graph_buckets=sorted(getattr(graphs, "graphs", {}).keys()) if graphs is not None else [])
+            ema = self.state.get_array("placement_ema")
+            if planner is not None and ema is not None:
+                # handed to the balancer when the dynamic machinery is built
+                planner.pending_ema = (self.state.get_array("placement_positions"), ema)
         self.kv = KVCacheManager(n_blocks, cfg.block_size, cfg.enable_prefix_caching)
         if cfg.enable_omni_attn:
             from ..accelerators.cache import apply_omni_attn_patch
@@ -103,11 +125,23 @@ class EngineCore:
         self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "generated_tokens": 0}
 
     # ------------------------------------------------------------------ intake
+    def save_state(self) -> None:
+        """Writes what a restart can reuse (called at shutdown, and by whoever wants a checkpoint in between)."""
+        if self.state is None:
+            return
+        if self.planner is not None:
+            self.state.save(**self.planner.export_state())
+
+    @property
+    def role(self) -> str:
+        kv_role = (self.cfg.kv_transfer_config or {}).get("kv_role", "")
+        return {"kv_producer": "prefill", "kv_consumer": "decode"}.get(kv_role, "mixed")
+
     def add_request(self, prompt_token_ids, sampling: Optional[SamplingParams] = None, request_id: Optional[str] = None,
                     kv_transfer_params: Optional[dict] = None, priority: int = 0) -> str:
         rid = request_id or f"req-{next(self._ids)}"
         req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), priority=priority,
-                      eos_token_id=self.cfg.eos_token_id, kv_transfer_params=kv_transfer_params)
+                      eos_token_id=self.cfg.eos_token_id, kv_transfer_params=kv_transfer_params, role=self.role)
         if not self.scheduler.try_pull_kv_fast_path(req):
             self.scheduler.add_request(req)
         else:

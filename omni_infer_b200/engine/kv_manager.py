@@ -83,7 +83,8 @@ class KVCacheManager:
                        lookahead: int = 0) -> Optional[list]:
         """Make sure ``req`` owns blocks for ``num_computed_tokens + num_new_tokens + lookahead`` tokens.
         Returns the newly added block ids, or None when memory is short (nothing is changed then)."""
-        if computed_blocks and not req.block_ids:
+        took_prefix = bool(computed_blocks) and not req.block_ids
+        if took_prefix:
             for b in computed_blocks:
                 self.ref[b] += 1
                 self.evictable.pop(b, None)
@@ -92,6 +93,8 @@ class KVCacheManager:
         if need <= 0:
             return []
         if need > self.num_free_blocks:
+            if took_prefix:
+                self.free(req)      # give the cached-prefix references back: a failed call leaves no trace
             return None
         new = []
         for _ in range(need):

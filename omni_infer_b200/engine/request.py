@@ -69,6 +69,7 @@ class Request:
     finish_time: Optional[float] = None
     num_preemptions: int = 0
     events: list = field(default_factory=list)           # (timestamp, action) timeline
+    role: str = ""                                       # prefill / decode / mixed: names the engine in timeline lines
 
     @property
     def all_token_ids(self) -> list:
@@ -91,7 +92,11 @@ class Request:
         return self.status.finished
 
     def record(self, action: str) -> None:
-        self.events.append((time.time(), action))
+        now = time.time()
+        self.events.append((now, action))
+        from ..utils import timeline
+        if timeline.enabled():
+            timeline.emit(action, self.request_id, role=self.role or None, ts=now)
 
 
 @dataclass

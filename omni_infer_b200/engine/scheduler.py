@@ -171,7 +171,8 @@ class Scheduler:
                 req.num_cached_tokens = n_cached
             if self.kv.allocate_slots(req, num_new, computed_blocks) is None:
                 if req.num_cached_tokens and not req.block_ids:
-                    req.num_computed_tokens = 0
+                    req.num_computed_tokens = 0     # the prefix references were handed back: start over next time
+                    req.num_cached_tokens = 0
                 break
             self.waiting.popleft()
             req.status = RequestStatus.RUNNING
@@ -313,6 +314,7 @@ class Scheduler:
             sink.append(int(t))
             if req.first_token_time is None:
                 req.first_token_time = _t.monotonic()
+                req.record("First token sampled")
             n_out = len(req.output_token_ids)
             if not sp.ignore_eos and req.eos_token_id is not None and t == req.eos_token_id:
                 self._finish(req, RequestStatus.FINISHED_STOPPED)

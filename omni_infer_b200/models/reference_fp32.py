@@ -116,3 +116,44 @@ class ReferenceDeepseek:
             out.append(t)
             toks.append(t)
         return out
+
+
+class ReferenceQwen(ReferenceDeepseek):
+    """The same naive recomputation for the GQA models (Qwen2: dense, biased qkv; Qwen3-MoE: per-head q/k RMSNorm,
+    routed experts without a shared one).  Only the attention differs: explicit per-head K/V repeated over the query
+    groups, rotate-half RoPE."""
+
+    def __init__(self, cfg: ModelConfig, state_dict: dict, prefix: str = ""):
+        self.cfg, self.sd, self.prefix = cfg, state_dict, prefix
+        self.cos_sin = ops.rope_cos_sin_table(cfg.head_dim, min(cfg.max_position_embeddings, 8192), cfg.rope_theta,
+                                              cfg.rope_scaling)
+
+    def _attn(self, x, p):
+        cfg, sd = self.cfg, self.sd
+        L, Hq, Hkv, D = x.shape[0], cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        qkv = x @ _w(sd, p + "qkv_proj.weight").t()
+        if p + "qkv_proj.bias" in sd:
+            qkv = qkv + sd[p + "qkv_proj.bias"].float().cpu()
+        qkv = qkv.view(L, Hq + 2 * Hkv, D)
+        q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:]
+        if cfg.qk_norm:
+            q = _rms(q, _w(sd, p + "q_norm.weight"), cfg.rms_norm_eps)
+            k = _rms(k, _w(sd, p + "k_norm.weight"), cfg.rms_norm_eps)
+        cs = self.cos_sin[:L]
+        cos, sin = cs[:, None, : D // 2], cs[:, None, D // 2:]
+
+        def rot(t):
+            a, b = t[..., : D // 2], t[..., D // 2:]
+            return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+
+        q, k = rot(q), rot(k)
+        rep = Hq // Hkv
+        k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+        s = torch.einsum("ihd,jhd->hij", q, k) * D ** -0.5
+        s = s.masked_fill(torch.triu(torch.ones(L, L, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("hij,jhd->ihd", torch.softmax(s, -1), v).reshape(L, Hq * D)
+        return o @ _w(sd, p + "o_proj.weight").t()
+
+
+def reference_for(cfg: ModelConfig, state_dict: dict):
+    return ReferenceDeepseek(cfg, state_dict) if cfg.use_mla else ReferenceQwen(cfg, state_dict)

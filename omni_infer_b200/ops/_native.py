@@ -97,7 +97,9 @@ def status_buffer(device=None) -> torch.Tensor:
         dev = torch.device("cuda", torch.cuda.current_device())
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     if key not in _status:
-        _status[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
+        # a plain tensor even when the first caller runs under inference mode: callers reset it in place later
+        with torch.inference_mode(False):
+            _status[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _status[key]
 
 

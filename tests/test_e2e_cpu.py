@@ -1,6 +1,7 @@
 """End-to-end on CPU: the engine (scheduler + paged latent cache + absorbed decode + fused-layout ops)
 must reproduce the naive fp32 oracle token for token (tiny DeepSeek-V3-style MLA+MoE, 4 prompts of 32
 tokens, 16 greedy tokens)."""
+import pytest
 import torch
 
 from omni_infer_b200.engine.engine_core import LLM, EngineConfig, EngineCore
@@ -90,3 +91,19 @@ def test_sampling_penalties_change_greedy_output():
     hist = torch.tensor([[0, 1, 3, 3, -1]], dtype=torch.int32)
     out = apply_penalties_ref(logits, hist, torch.tensor([2]), torch.tensor([2.0]), torch.tensor([0.5]), torch.tensor([0.25]))
     assert torch.allclose(out, torch.tensor([[1.0, -2.0, 0.5, 3.0 / 2 - 0.5 * 2 - 0.25]]))
+
+
+@pytest.mark.parametrize("name,over", [("tiny-qwen3-moe", {}),
+                                       ("qwen2-small", {"dtype": "float32", "hidden_size": 256, "intermediate_size": 512,
+                                                        "head_dim": 32, "vocab_size": 1024})])
+def test_qwen_models_match_their_fp32_oracle(name, over):
+    """GQA models (dense with biased qkv; MoE with q/k norm and renormalised softmax routing) through the engine
+    give exactly the oracle's greedy tokens on CPU."""
+    from omni_infer_b200.models.reference_fp32 import reference_for
+    llm = LLM(name, block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", model_overrides=over)
+    ref = reference_for(llm.engine.model_cfg, dict(llm.engine.worker.runner.model.state_dict()))
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (21,), generator=g).tolist() for _ in range(2)]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=6))
+    for p, o in zip(prompts, outs):
+        assert o == ref.greedy(p, 6)

@@ -137,3 +137,109 @@ def test_topology_tool(tmp_path):
     assert len(T.merge(a, b).instances) == 2
     with pytest.raises(ValueError):
         T.merge(a, a)
+
+
+def test_kv_manager_failed_allocation_hands_prefix_references_back():
+    """A request that hits the prefix cache but then finds no room for the rest of its prompt must leave the block
+    manager as it found it: cached blocks evictable again, no reference held, no block id on the request."""
+    from omni_infer_b200.engine.kv_manager import KVCacheManager
+    from omni_infer_b200.engine.request import Request
+
+    kv = KVCacheManager(num_blocks=6, block_size=4, enable_prefix_caching=True)      # block 0 is the null block
+    first = Request("a", list(range(10)))
+    assert kv.allocate_slots(first, 10) is not None and len(first.block_ids) == 3
+    first.num_computed_tokens = 10
+    kv.cache_full_blocks(first)
+    cached = first.block_ids[:2]
+    kv.free(first)
+    assert kv.num_free_blocks == 5 and all(kv.ref[b] == 0 for b in cached)
+
+    # the same 8-token prefix, then a tail that needs 6 more blocks than there are
+    second = Request("b", list(range(8)) + list(range(100, 120)))
+    blocks, n_cached = kv.get_computed_blocks(second)
+    assert blocks == cached and n_cached == 8
+    second.num_computed_tokens = n_cached
+    free_before = kv.num_free_blocks
+    assert kv.allocate_slots(second, second.num_tokens - n_cached, blocks) is None
+    assert second.block_ids == [] and kv.num_free_blocks == free_before
+    assert all(kv.ref[b] == 0 for b in cached) and all(b in kv.evictable for b in cached)
+
+    # and a request that fits still finds the cached prefix and takes it
+    third = Request("c", list(range(8)) + [200, 201])
+    blocks3, n3 = kv.get_computed_blocks(third)
+    assert blocks3 == cached
+    third.num_computed_tokens = n3
+    assert kv.allocate_slots(third, third.num_tokens - n3, blocks3) is not None
+    assert third.block_ids[:2] == cached and all(kv.ref[b] == 1 for b in cached)
+
+
+def test_state_dir_round_trip_and_fingerprint(tmp_path):
+    import numpy as np
+    from omni_infer_b200.engine.state_dir import StateDir
+
+    fp = {"model": "m", "world": 2, "block_size": 128}
+    st = StateDir(str(tmp_path), rank=1, fp=fp)
+    assert st.load() == {} and st.get("num_kv_blocks") is None and st.get_array("placement_ema") is None
+    st.save(num_kv_blocks=321, graph_buckets=[1, 2, 4])
+    st.save(placement_ema=np.arange(6, dtype=np.float64).reshape(2, 3))          # merges with what is there
+    again = StateDir(str(tmp_path), rank=1, fp=dict(fp))
+    assert again.get("num_kv_blocks") == 321 and again.get("graph_buckets") == [1, 2, 4]
+    assert np.array_equal(again.get_array("placement_ema"), np.arange(6.0).reshape(2, 3))
+    assert StateDir(str(tmp_path), rank=0, fp=fp).load() == {}                      # per rank
+    assert StateDir(str(tmp_path), rank=1, fp={**fp, "block_size": 64}).load() == {}   # another configuration: ignored
+    (tmp_path / "state_rank1.json").write_text("{ not json")
+    assert StateDir(str(tmp_path), rank=1, fp=fp).load() == {}                      # unreadable: start cold
+    assert not [f for f in os.listdir(tmp_path) if f.startswith(".tmp_")]          # no temporary file left behind
+
+
+def test_engine_restart_reuses_block_count_placement_and_load_history(tmp_path):
+    """First run: serves requests, runs a placement round (which builds the balancer's load history) and saves its
+    state.  Second run with the same configuration starts from the saved block count, placement and history.  A run
+    with another configuration starts cold."""
+    import numpy as np
+    from omni_infer_b200.accelerators.placement import OmniPlanner
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+
+    def make(**kw):
+        OmniPlanner.cleanup()
+        cfg = dict(block_size=16, num_kv_blocks=0, max_model_len=128, device="cpu", state_dir=str(tmp_path),
+                   placement_config={"max_redundant_per_rank": 2, "device": "cpu"})
+        cfg.update(kw)
+        return EngineCore(EngineConfig(**cfg))
+
+    first = make(num_kv_blocks=40)
+    assert first.state.get("num_kv_blocks") == 40 and first.state.get("graph_buckets") == []
+    pl = first.planner
+    g = torch.Generator().manual_seed(0)
+    first.add_request(torch.randint(0, 1024, (20,), generator=g).tolist(), SamplingParams(max_tokens=4))
+    first.run_until_done()
+    assert pl.run_round() >= 0
+    first.save_state()
+    saved_pos, saved_ema = first.state.get_array("placement_positions"), first.state.get_array("placement_ema")
+    assert saved_pos.shape == saved_ema.shape == (pl.layers, pl.num_positions) and saved_ema.sum() > 0
+    assert first.state.get_array("placement_pattern").shape == (pl.world, pl.layers, pl.experts)
+
+    second = make()                                  # no block count given: taken from the state directory
+    assert second.kv.num_blocks == 40
+    assert np.array_equal(second.planner.mapping.placement(), saved_pos)
+    second.planner.run_round()                       # builds the balancer, which takes the saved history first
+    assert second.planner.pending_ema is None
+    blended = second.planner.export_state()["placement_ema"]
+    # nothing was routed in the second run, so its first round blends the restored history with zeros (keep = 0.6)
+    assert np.allclose(blended, 0.6 * saved_ema)
+
+    # the history follows the experts when a rank's slots come back in another order
+    pl2 = second.planner
+    perm = saved_pos.copy()
+    perm[:, [0, 1]] = perm[:, [1, 0]]
+    marked = np.zeros_like(saved_ema)
+    marked[:, 0], marked[:, 1] = 7.0, 9.0            # saved under the permuted order: slot 0 held expert 1
+    pl2.pending_ema = (perm, marked)
+    pl2._restore_ema()
+    now = pl2.export_state()["placement_ema"]
+    assert np.all(now[:, 0] == 9.0) and np.all(now[:, 1] == 7.0)
+
+    cold = make(block_size=32, num_kv_blocks=24)     # another block size: the saved state does not apply
+    assert cold.kv.num_blocks == 24 and cold.state.get_array("placement_ema") is None
+    OmniPlanner.cleanup()

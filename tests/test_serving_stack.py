@@ -160,3 +160,67 @@ def test_proxy_launcher_rolls_back_to_the_configuration_that_started(tmp_path):
             assert st["running"] and "18471" in " ".join(st["config"]["command"])
     finally:
         sp.run(base + ["--decode-servers-list", "x:1", "--stop"], capture_output=True)
+
+
+def test_request_timeline_joins_proxy_prefill_and_decode(tmp_path):
+    """One request through the C++ proxy, a prefill engine and a decode engine: the three logs join on the request id
+    into one ordered timeline, and the tool reports the stage intervals."""
+    import subprocess
+    from omni_infer_b200.accelerators.pd import InProcessHub
+    from omni_infer_b200.build import PROXY_BIN, build_proxy
+    from omni_infer_b200.utils import timeline
+
+    InProcessHub.reset()
+    eng_log, proxy_log = tmp_path / "engines.log", tmp_path / "proxy.log"
+    assert timeline.configure(str(eng_log))
+    build_proxy()
+    kv = lambda role, name: {"kv_role": role, "engine_id": name, "endpoint": f"inproc://{name}"}
+    base = dict(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu")
+    p_srv, p_eng = serve(EngineConfig(kv_transfer_config=kv("kv_producer", "tl-p"), **base), "127.0.0.1", 0, block=False)
+    d_srv, d_eng = serve(EngineConfig(kv_transfer_config=kv("kv_consumer", "tl-d"), **base), "127.0.0.1", 0, block=False)
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    with open(proxy_log, "w") as plog:
+        proxy = subprocess.Popen([str(PROXY_BIN), "--listen", f"127.0.0.1:{port}", "--prefill-servers", f"127.0.0.1:{p_srv.server_port}",
+                                  "--decode-servers", f"127.0.0.1:{d_srv.server_port}", "--log-level", "0", "--timeline"], stderr=plog)
+        try:
+            for _ in range(100):
+                try:
+                    urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=0.5).read()
+                    break
+                except Exception:
+                    time.sleep(0.05)
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions",
+                                         data=json.dumps({"prompt": list(range(1, 40)), "max_tokens": 4}).encode(),
+                                         headers={"Content-Type": "application/json", "X-Request-Id": "tl-req-1"})
+            out = json.loads(urllib.request.urlopen(req, timeout=60).read())
+            assert out["usage"]["completion_tokens"] == 4
+        finally:
+            proxy.terminate()
+            proxy.wait(timeout=10)
+            for srv, eng in ((p_srv, p_eng), (d_srv, d_eng)):
+                srv.shutdown()
+                eng.stop()
+            timeline.configure("")
+            InProcessHub.reset()
+    tl = timeline.parse([str(proxy_log), str(eng_log)])
+    ev = tl["tl-req-1"]
+    roles = [r for _, r, _ in ev]
+    actions = [a for _, _, a in ev]
+    assert {"proxy", "prefill", "decode"} <= set(roles)
+    assert actions[0] == "Proxy got request" and actions[-1] == "Proxy finished request"
+    pairs = list(zip(roles, actions))
+    order = [("proxy", "Proxy sends to prefill"), ("prefill", "Get request in api server"), ("prefill", "Prefill scheduled"),
+             ("prefill", "First token sampled"), ("proxy", "Proxy got prefill response"), ("proxy", "Proxy sends to decode"),
+             ("decode", "Get request in api server"), ("decode", "First token out of api server"),
+             ("decode", "Finish response in api server"), ("proxy", "Proxy relays first decode bytes")]   # not streamed
+    pos = [pairs.index(x) for x in order]
+    assert pos == sorted(pos), pairs
+    assert any(r == "decode" and "pull kv" in a for r, a in pairs), pairs
+    s = timeline.summary(tl)
+    assert s["requests"] == 1 and s["end_to_end_ms"]["p50"] > 0
+    assert "proxy:Proxy sends to prefill -> prefill:Get request in api server" in s["stages"]
+    text = timeline.render(tl)
+    assert "request tl-req-1" in text and "p50" in text
+    assert timeline.main([str(proxy_log), str(eng_log), "--json", str(tmp_path / "s.json")]) == 0
+    assert json.load(open(tmp_path / "s.json"))["requests"] == 1
