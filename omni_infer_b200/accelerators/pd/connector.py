@@ -166,8 +166,8 @@ class TcpTransport:
         try:
             msg = _decode(conn.recv_bytes(1 << 22))
             self.worker.dispatch(msg)
-        except (EOFError, OSError, ValueError, KeyError):
-            pass
+        except (EOFError, OSError, ValueError, KeyError) as e:
+            logger.warning("kv control message dropped: %s: %s", type(e).__name__, e)
         finally:
             conn.close()
 
@@ -417,7 +417,10 @@ class WorkerConnector:
             return InProcessHub.endpoints[msg["reply_to"]].kv_tensors
         key = msg["reply_to"]
         if key not in self._peer_views:
-            d = msg["cache"]
+            d = msg.get("cache") or {}
+            if "ipc" not in d:
+                # host tensors of another process cannot be mapped: refuse, so that the consumer prefills locally at once
+                raise LookupError("the consumer's cache is not shareable between processes (no device IPC handles)")
             from ...parallel.symmetric_heap import open_ipc_handles
             self._peer_views[key] = PeerCacheView(open_ipc_handles(d["ipc"]), d["block_bytes"], d["num_blocks"])
         return self._peer_views[key]
@@ -442,7 +445,12 @@ class WorkerConnector:
                 self._send(msg["reply_to"], {"op": "nack", "request_id": rid, "attempt": attempt})
             return
         try:
-            peer = self._peer_cache(msg)
+            try:
+                peer = self._peer_cache(msg)
+            except LookupError as e:
+                logger.warning("push request for %s refused: %s", rid, e)
+                self._send(msg["reply_to"], {"op": "nack", "request_id": rid, "attempt": attempt})
+                return
             if isinstance(peer, PeerCacheView):
                 push_blocks_cuda(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
             else:

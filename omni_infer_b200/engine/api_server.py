@@ -257,11 +257,16 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-transfer-config", default=None, help="JSON")
     ap.add_argument("--additional-config", default=None, help="JSON")
     ap.add_argument("--enforce-eager", action="store_true")
+    ap.add_argument("--model-overrides", default=None, help="JSON of model-config fields to override (e.g. fewer layers)")
+    ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    ap.add_argument("--enable-chunked-prefill", action="store_true")
     a = ap.parse_args(argv)
     cfg = EngineConfig(model=a.model, device=a.device, max_num_seqs=a.max_num_seqs, max_model_len=a.max_model_len,
                        max_num_batched_tokens=a.max_num_batched_tokens, block_size=a.block_size, num_kv_blocks=a.num_kv_blocks,
                        num_speculative_tokens=a.num_speculative_tokens, tp_size=a.tensor_parallel_size,
-                       enforce_eager=a.enforce_eager,
+                       enforce_eager=a.enforce_eager, gpu_memory_utilization=a.gpu_memory_utilization,
+                       enable_chunked_prefill=a.enable_chunked_prefill,
+                       model_overrides=json.loads(a.model_overrides) if a.model_overrides else {},
                        kv_transfer_config=json.loads(a.kv_transfer_config) if a.kv_transfer_config else None)
     if a.additional_config:
         from ..adaptors.vllm.platform import ConfigUpdater
