@@ -37,7 +37,11 @@ def run(args, redundant: int, dynamic: bool):
     device = "cuda" if torch.cuda.is_available() else "cpu"
     mc.router_skew = {"s": 1.2, "strength": 6.0, "seed": 0}     # part of the model, so captured decode graphs include it
     # the baseline run also gets a planner (identity placement, never re-placed) so that both runs count loads the same way
-    pc = {"max_redundant_per_rank": redundant, "enable_dynamic": False, "apply_interval": 10 ** 9}
+    background = dynamic and args.background
+    # background: rounds run on the planner's own thread every --period seconds while decode goes on; the runner applies
+    # a finished round between two steps (every 16 steps it looks for one).  Otherwise rounds run synchronously below.
+    pc = {"max_redundant_per_rank": redundant, "enable_dynamic": background, "period_s": args.period,
+          "apply_interval": 16 if background else 10 ** 9}
     bs = 128 if device == "cuda" else 16
     per_req = args.input_len + args.steps + 16
     ecfg = EngineConfig(model=mc.name, block_size=bs, num_kv_blocks=args.batch * (per_req // bs + 2) + 2, max_num_seqs=args.batch,
@@ -63,7 +67,7 @@ def run(args, redundant: int, dynamic: bool):
         eng.step()
         if planner is not None and (i + 1) % args.replace_every == 0 and i + 1 < args.steps:
             snap = planner.sent_counts.clone()    # the last window starts at the last round boundary, in both arms
-        if dynamic and planner is not None and (i + 1) % args.replace_every == 0:
+        if dynamic and not background and planner is not None and (i + 1) % args.replace_every == 0:
             if device == "cuda":
                 torch.cuda.synchronize()
             tr = time.perf_counter()
@@ -80,7 +84,12 @@ def run(args, redundant: int, dynamic: bool):
         from omni_infer_b200.ops import _native as nat
         nat.check_status()
     stats = planner.load_stats()
-    res = {"redundant_slots_per_rank": redundant, "dynamic": dynamic, "moves_applied": int(moves),
+    if background:
+        from omni_infer_b200.accelerators.placement import _native as pnat
+        moves = planner.applied_total
+        rounds = pnat.lib().omni_pl_placement_rounds(planner._placement) if planner._placement else 0
+    res = {"redundant_slots_per_rank": redundant, "dynamic": dynamic, "background_rounds": bool(background),
+           "moves_applied": int(moves),
            "tok_s_per_gpu": round((eng.metrics["generated_tokens"] - tok0) / dt, 1),
            # a round runs synchronously here; in serving it runs on the planner's thread once a minute
            "tok_s_per_gpu_outside_rounds": round((eng.metrics["generated_tokens"] - tok0) / max(dt - round_s, 1e-9), 1),
@@ -102,6 +111,8 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--redundant", type=int, default=2, help="redundant expert slots per rank in the second run")
     ap.add_argument("--replace-every", type=int, default=16)
+    ap.add_argument("--background", action="store_true", help="placement rounds on the planner's thread while decode runs")
+    ap.add_argument("--period", type=float, default=5.0, help="seconds between background rounds")
     a = ap.parse_args()
     out = {"baseline": run(a, 0, False), "with_placement": run(a, a.redundant, True)}
     if int(os.environ.get("RANK", "0")) == 0:

@@ -153,6 +153,9 @@ __device__ __forceinline__ int atom_add_release_sys(int* p, int v) {
 __device__ __forceinline__ bool flag_wait_ge(const int* p, int expected, uint64_t limit_ns, OmniStatus* st,
                                              int site, int detail) {
   if (ld_acquire_sys(p) >= expected) return true;
+  // a wait that already ran out in this step (the status word is still set: the host has not read it yet) means a
+  // peer is gone or late: every later wait of the step gives up at once instead of spending its own limit
+  if (st != nullptr && *reinterpret_cast<volatile int*>(&st->code) != OMNI_OK) return false;
   WaitClock clk;
   uint32_t spins = 0;
   while (true) {

@@ -38,18 +38,34 @@ class PeerCacheView:
         self.ptrs, self.block_bytes, self.num_blocks = ptrs, block_bytes, num_blocks
 
 
+_push_streams: dict = {}
+
+
+def _push_stream(dev) -> "torch.cuda.Stream":
+    """One high-priority, non-blocking stream per device for KV pushes: a push must not queue behind the prefill that
+    the producer is running on its compute stream (hundreds of milliseconds for a long prompt), nor order itself
+    against it; the blocks it reads were complete before the request's first token left the producer."""
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _push_streams:
+        _lo, hi = torch.cuda.Stream.priority_range() if hasattr(torch.cuda.Stream, "priority_range") else (0, -1)
+        _push_streams[key] = torch.cuda.Stream(device=dev, priority=hi)
+    return _push_streams[key]
+
+
 def push_blocks_cuda(src_tensors, dst_view: PeerCacheView, src_blocks, dst_blocks, stream=None) -> None:
     dev = src_tensors[0].device
     n_t = len(src_tensors)
     assert n_t == len(dst_view.ptrs)
     bb = src_tensors[0][0].numel() * src_tensors[0].element_size()
     assert bb == dst_view.block_bytes, "prefill and decode caches must use the same block geometry"
-    src_ptrs = torch.tensor([t.data_ptr() for t in src_tensors], dtype=torch.int64, device=dev)
-    dst_ptrs = torch.tensor(dst_view.ptrs, dtype=torch.int64, device=dev)
-    sb = torch.tensor(src_blocks, dtype=torch.int64, device=dev)
-    db = torch.tensor(dst_blocks, dtype=torch.int64, device=dev)
-    st = stream if stream is not None else torch.cuda.current_stream()
-    with torch.cuda.stream(st):
+    st = stream if stream is not None else _push_stream(dev)
+    with torch.cuda.device(dev), torch.cuda.stream(st):
+        # one pinned staging tensor for the four index arrays: a single asynchronous copy on the push stream
+        host = torch.tensor([t.data_ptr() for t in src_tensors] + list(dst_view.ptrs) + list(src_blocks) + list(dst_blocks),
+                            dtype=torch.int64).pin_memory()
+        devt = host.to(dev, non_blocking=True)
+        nb = len(src_blocks)
+        src_ptrs, dst_ptrs, sb, db = devt[:n_t], devt[n_t:2 * n_t], devt[2 * n_t:2 * n_t + nb], devt[2 * n_t + nb:]
         rc = nat.lib().omni_kv_push(nat.ptr(src_ptrs), nat.ptr(dst_ptrs), nat.ptr(sb), nat.ptr(db),
                                     ctypes.c_longlong(bb), ctypes.c_longlong(src_tensors[0].shape[0]),
                                     ctypes.c_longlong(dst_view.num_blocks), nat.c_int(n_t), nat.c_int(len(src_blocks)),

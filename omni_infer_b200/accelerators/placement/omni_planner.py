@@ -71,6 +71,7 @@ class OmniPlanner(metaclass=_Singleton):
         self.sent_counts = torch.zeros(num_moe_layers, self.num_positions, dtype=torch.int64, device=self.device)
         self.local_counts = torch.zeros(num_moe_layers, self.slots_per_rank, dtype=torch.int64, device=self.device)
         self._step = 0
+        self.applied_total = 0    # experts replaced since start (all rounds)
         self._weights = self._act = self._dist = self._placement = None
         self._keep = []          # ctypes callbacks must outlive the C++ objects
         self._pl_group = None
@@ -347,6 +348,7 @@ class OmniPlanner(metaclass=_Singleton):
     def apply_pending(self) -> int:
         L = nat.lib()
         n = L.omni_pl_do_placement_optimizer(self._placement)
+        self.applied_total += int(n)
         self.mapping.refresh_selector()
         if self.enable_dump and self.dump_dir:
             os.makedirs(self.dump_dir, exist_ok=True)

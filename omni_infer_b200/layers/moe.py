@@ -82,8 +82,12 @@ class MoELayer(nn.Module):
         self.gate = MoEGate(cfg, dtype, device)
         wdt = FP8 if quant == "fp8_block" else dtype
         S = self.slots_per_rank
-        self.w13 = nn.Parameter(torch.empty(S, 2 * I, H, dtype=wdt, device=device), requires_grad=False)
-        self.w2 = nn.Parameter(torch.empty(S, H, I, dtype=wdt, device=device), requires_grad=False)
+        # zero-filled, not left as allocated: a redundant slot that no expert has been copied into yet must not hold
+        # bit patterns that read as NaN should a stale selector ever point at it
+        self.w13 = nn.Parameter(torch.zeros(S, 2 * I, H, dtype=torch.uint8 if wdt == FP8 else wdt, device=device).view(wdt),
+                                requires_grad=False)
+        self.w2 = nn.Parameter(torch.zeros(S, H, I, dtype=torch.uint8 if wdt == FP8 else wdt, device=device).view(wdt),
+                               requires_grad=False)
         if quant == "fp8_block":
             self.w13_scale = nn.Parameter(torch.ones(S, 2 * I // 128, H // 128, dtype=torch.float32, device=device),
                                           requires_grad=False)

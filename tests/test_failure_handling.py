@@ -47,6 +47,17 @@ def test_flag_wait_runs_out_and_reports_status():
     code, site, _, detail = status.tolist()
     assert code == 2 and site == 201 and detail == 1              # flag timeout, dispatch receive, peer 1
     assert counts.tolist() == [0, 0] and (ids == -1).all()        # nothing was taken from the silent peer
+    # the status word is still set (the host has not read it): the next wait on the silent peer, with a limit of a
+    # whole second, gives up at once instead of spending its own limit, so a lost peer costs one limit per step and
+    # not one per layer
+    t2 = torch.cuda.Event(enable_timing=True); t3 = torch.cuda.Event(enable_timing=True)
+    t2.record()
+    rc = L.omni_ep_dispatch_recv(ctypes.byref(lay), peers, nat.ptr(ids), nat.ptr(w), nat.ptr(slot), nat.ptr(counts),
+                                 ctypes.c_ulonglong(1_000_000_000), nat.ptr(status), nat.stream())
+    t3.record()
+    torch.cuda.synchronize()
+    assert rc == 0 and t2.elapsed_time(t3) < 100.0
+    assert status.tolist()[:2] == [2, 201]                        # the first record is kept
     with pytest.raises(nat.KernelProtocolError):
         nat.check_status()
     # the context is still fine
