@@ -40,7 +40,7 @@ def parse():
     ap.add_argument("--ep-backend", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--attn-tp", action="store_true",
                     help="tensor-parallel attention over all ranks (one shared batch) instead of data-parallel attention")
-    ap.add_argument("--tp-backend", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--tp-backend", default="fused", choices=["fused", "nvls", "nccl"])
     ap.add_argument("--decode-ctx", type=int, default=-1,
                     help="context length at the middle of the timed steps; -1 = the config's mean decode context "
                          "(input + output / 2), 0 = time right after the prefill")

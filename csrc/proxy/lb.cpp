@@ -46,10 +46,21 @@ int LoadBalancer::pick(int64_t len, double now, Ticket& t) {
   std::vector<int> up;
   for (int i = 0; i < n; ++i) if (up_locked(i, now)) up.push_back(i);
   if (up.empty()) for (int i = 0; i < n; ++i) up.push_back(i);   // everything is down: try anyway
+  // ties go to the peer after the one that won the last tie (not always to the first): a lightly loaded pool, where
+  // every peer scores the same most of the time, then spreads its requests instead of sending them all to peer 0
   auto argmin = [&](auto score) {
-    int best = up[0];
+    const int m = (int)up.size();
+    const int start = s_->rr_next % m;
+    int best = up[start];
     double bs = score(best);
-    for (int i : up) { double v = score(i); if (v < bs) { bs = v; best = i; } }
+    bool tie = false;
+    for (int k = 1; k < m; ++k) {
+      const int i = up[(start + k) % m];
+      const double v = score(i);
+      if (v < bs) { bs = v; best = i; tie = false; }
+      else if (v == bs) tie = true;
+    }
+    if (tie) s_->rr_next = (s_->rr_next + 1) % std::max(1, n);
     return best;
   };
   const std::string& pol = p_.policy;

@@ -23,11 +23,14 @@
 #include <poll.h>
 #include <signal.h>
 #include <sys/epoll.h>
+#include <sys/eventfd.h>
 #include <sys/mman.h>
 #include <sys/socket.h>
 #include <sys/wait.h>
 #include <unistd.h>
 
+#include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <condition_variable>
 #include <cstdio>
@@ -39,6 +42,7 @@
 #include <sstream>
 #include <string>
 #include <thread>
+#include <unordered_set>
 #include <vector>
 
 #include "json_min.h"
@@ -288,9 +292,175 @@ static bool run_prefill(const HttpMessage& req, const std::string& body, HttpMes
   return ok;
 }
 
+// ------------------------------------------------------------------------------------------------ stream relay
+// Once a decode instance has started to answer, the rest of the (possibly minutes-long) token stream is moved by one
+// event loop instead of the worker thread that set the request up: thousands of open streams then cost a file
+// descriptor pair each, not a thread each, as in the event-driven proxy of the reference.  The loop forwards bytes
+// upstream -> client, runs the body filters (token counters for the balancers) on what passes, and gives the peer
+// back when the upstream closes.  A client that reads slowly only stalls its own stream: its bytes wait in a pending
+// buffer and its upstream is not read until the buffer has drained.
+struct RelayConn;
+struct RelayTag { RelayConn* c; bool is_client; };
+struct RelayConn {
+  int up = -1, client = -1;
+  Ticket t;
+  std::string rid, tail, pending;
+  bool reading = true;
+  RelayTag up_tag{this, false}, client_tag{this, true};   // what the event loop gets back from epoll
+};
+
+static void scan_counters(RelayConn& c, const char* buf, size_t n) {
+  std::string view = c.tail + std::string(buf, n);
+  long long v, pn, on;
+  if (find_int_after(view, "total_tokens", v)) g_lb_decode->on_decoded_tokens(c.t, v);
+  if (find_int_after(view, "output_num_token", on)) {
+    pn = 0;
+    find_int_after(view, "prompt_num_token", pn);
+    g_lb_decode->on_token_counts(c.t, pn, on);
+  }
+  c.tail = view.size() > 64 ? view.substr(view.size() - 64) : view;
+}
+
+class Relay {
+ public:
+  Relay() {
+    ep_ = epoll_create1(0);
+    wake_ = eventfd(0, EFD_NONBLOCK);
+    struct epoll_event ev = {};
+    ev.events = EPOLLIN;
+    ev.data.ptr = nullptr;       // the wake-up descriptor
+    epoll_ctl(ep_, EPOLL_CTL_ADD, wake_, &ev);
+    th_ = std::thread([this] { loop(); });
+  }
+  ~Relay() { stop(); }
+  void stop() {
+    if (stopped_.exchange(true)) return;
+    uint64_t one = 1;
+    (void)!write(wake_, &one, sizeof(one));
+    if (th_.joinable()) th_.join();
+    for (auto* c : conns_) finish(c, false);
+    conns_.clear();
+    close(ep_);
+    close(wake_);
+  }
+  // takes ownership of both descriptors and of the ticket
+  void add(RelayConn* c) {
+    fcntl(c->up, F_SETFL, fcntl(c->up, F_GETFL, 0) | O_NONBLOCK);
+    fcntl(c->client, F_SETFL, fcntl(c->client, F_GETFL, 0) | O_NONBLOCK);
+    { std::lock_guard<std::mutex> lk(mu_); incoming_.push_back(c); }
+    uint64_t one = 1;
+    (void)!write(wake_, &one, sizeof(one));
+  }
+  size_t open_streams() const { return n_open_.load(); }
+
+ private:
+  using Tag = RelayTag;
+  void arm(RelayConn* c) {
+    struct epoll_event ev = {};
+    ev.events = EPOLLIN;
+    ev.data.ptr = &c->up_tag;
+    epoll_ctl(ep_, EPOLL_CTL_ADD, c->up, &ev);
+    struct epoll_event ec = {};
+    ec.events = 0;
+    ec.data.ptr = &c->client_tag;
+    epoll_ctl(ep_, EPOLL_CTL_ADD, c->client, &ec);
+  }
+  // which events are wanted depends on whether bytes are waiting for the client
+  void want(RelayConn* c) {
+    struct epoll_event ev = {};
+    ev.data.ptr = &c->up_tag;
+    ev.events = (c->pending.empty() && c->reading) ? EPOLLIN : 0;
+    epoll_ctl(ep_, EPOLL_CTL_MOD, c->up, &ev);
+    struct epoll_event ec = {};
+    ec.data.ptr = &c->client_tag;
+    ec.events = c->pending.empty() ? 0 : EPOLLOUT;
+    epoll_ctl(ep_, EPOLL_CTL_MOD, c->client, &ec);
+  }
+  void finish(RelayConn* c, bool failed) {
+    epoll_ctl(ep_, EPOLL_CTL_DEL, c->up, nullptr);
+    epoll_ctl(ep_, EPOLL_CTL_DEL, c->client, nullptr);
+    close(c->up);
+    shutdown(c->client, SHUT_RDWR);
+    close(c->client);
+    g_lb_decode->free_peer(c->t, failed, now_s());
+    timeline("Proxy finished request", c->rid);
+    n_open_--;
+    delete c;
+  }
+  // true while the connection lives
+  bool flush(RelayConn* c) {
+    while (!c->pending.empty()) {
+      ssize_t w = send(c->client, c->pending.data(), c->pending.size(), MSG_NOSIGNAL);
+      if (w > 0) { c->pending.erase(0, (size_t)w); continue; }
+      if (w < 0 && (errno == EAGAIN || errno == EWOULDBLOCK)) return true;
+      if (w < 0 && errno == EINTR) continue;
+      return false;     // the client went away
+    }
+    return true;
+  }
+  void loop() {
+    char buf[32768];
+    std::vector<struct epoll_event> evs(256);
+    while (!stopped_) {
+      int n = epoll_wait(ep_, evs.data(), (int)evs.size(), 500);
+      {
+        std::lock_guard<std::mutex> lk(mu_);
+        for (auto* c : incoming_) { conns_.insert(c); n_open_++; arm(c); }
+        incoming_.clear();
+      }
+      std::vector<RelayConn*> dead;
+      auto is_dead = [&](RelayConn* c) { return std::find(dead.begin(), dead.end(), c) != dead.end(); };
+      for (int i = 0; i < n; ++i) {
+        Tag* tag = (Tag*)evs[i].data.ptr;
+        if (tag == nullptr) { uint64_t v; (void)!read(wake_, &v, sizeof(v)); continue; }
+        RelayConn* c = tag->c;
+        if (is_dead(c)) continue;
+        if (tag->is_client) {
+          if (!flush(c)) { dead.push_back(c); continue; }
+          if (c->pending.empty()) {
+            if (!c->reading) { dead.push_back(c); continue; }   // upstream had closed: these were the last bytes
+            want(c);
+          }
+          continue;
+        }
+        bool closed = false, lost_client = false;
+        while (c->pending.empty()) {
+          ssize_t r = recv(c->up, buf, sizeof(buf), 0);
+          if (r > 0) {
+            scan_counters(*c, buf, (size_t)r);
+            c->pending.assign(buf, (size_t)r);
+            if (!flush(c)) { lost_client = true; break; }
+            continue;
+          }
+          if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK)) break;
+          if (r < 0 && errno == EINTR) continue;
+          closed = true;      // end of the stream (or an upstream error)
+          break;
+        }
+        if (lost_client || (closed && c->pending.empty())) { dead.push_back(c); continue; }
+        if (closed) c->reading = false;
+        want(c);
+      }
+      for (auto* c : dead) {
+        conns_.erase(c);
+        finish(c, false);
+      }
+    }
+  }
+  int ep_ = -1, wake_ = -1;
+  std::thread th_;
+  std::mutex mu_;
+  std::vector<RelayConn*> incoming_;
+  std::unordered_set<RelayConn*> conns_;
+  std::atomic<bool> stopped_{false};
+  std::atomic<size_t> n_open_{0};
+};
+static Relay* g_relay = nullptr;
+
 // relays the decode response to the client as it arrives; returns false when the client went away
-static bool run_decode(int client, const HttpMessage& req, const std::string& body) {
+static bool run_decode(int client, const HttpMessage& req, const std::string& body, bool& handed_over) {
   const int64_t len = (int64_t)req.body.size();
+  handed_over = false;
   for (int attempt = 0; attempt <= g_cfg.retries; ++attempt) {
     Ticket t = g_lb_decode->get_peer(len, now_s());
     int up = connect_to(g_cfg.decode[t.peer], g_cfg.connect_timeout_s);
@@ -306,29 +476,29 @@ static bool run_decode(int client, const HttpMessage& req, const std::string& bo
     std::string wire = r.serialize_head() + body;
     timeline("Proxy sends to decode", req.header("X-Request-Id"));
     bool sent = send_all(up, wire.data(), wire.size(), g_cfg.timeout_s);
-    bool any = false, client_ok = true;
+    // the first bytes are awaited here, so that a peer that accepts the connection and then dies is still retried on
+    // another one; everything after them belongs to the relay loop
     char buf[16384];
-    std::string tail;   // last bytes of the previous chunk, so counters split across reads are still seen
-    while (sent) {
-      if (!wait_fd(up, POLLIN, g_cfg.timeout_s)) break;
-      ssize_t n = recv(up, buf, sizeof(buf), 0);
-      if (n <= 0) break;
-      if (!any) timeline("Proxy relays first decode bytes", req.header("X-Request-Id"));
-      any = true;
-      if (!send_all(client, buf, (size_t)n, g_cfg.timeout_s)) { client_ok = false; break; }
-      std::string view = tail + std::string(buf, (size_t)n);
-      long long v, pn, on;
-      if (find_int_after(view, "total_tokens", v)) g_lb_decode->on_decoded_tokens(t, v);
-      if (find_int_after(view, "output_num_token", on)) {
-        pn = 0;
-        find_int_after(view, "prompt_num_token", pn);
-        g_lb_decode->on_token_counts(t, pn, on);
-      }
-      tail = view.size() > 64 ? view.substr(view.size() - 64) : view;
+    ssize_t n = -1;
+    if (sent && wait_fd(up, POLLIN, g_cfg.timeout_s)) n = recv(up, buf, sizeof(buf), 0);
+    if (n <= 0) {
+      close(up);
+      g_lb_decode->free_peer(t, true, now_s());
+      continue;
     }
-    close(up);
-    g_lb_decode->free_peer(t, !any, now_s());
-    if (any || !client_ok) return client_ok;
+    timeline("Proxy relays first decode bytes", req.header("X-Request-Id"));
+    RelayConn* c = new RelayConn();
+    c->up = up; c->client = client; c->t = t; c->rid = req.header("X-Request-Id");
+    scan_counters(*c, buf, (size_t)n);
+    if (!send_all(client, buf, (size_t)n, g_cfg.timeout_s)) {   // the client is already gone
+      close(up);
+      g_lb_decode->free_peer(c->t, false, now_s());
+      delete c;
+      return false;
+    }
+    g_relay->add(c);
+    handed_over = true;
+    return true;
   }
   send_simple(client, 502, "Bad Gateway", "{\"error\":\"no decode instance reachable\"}");
   return true;
@@ -336,6 +506,7 @@ static bool run_decode(int client, const HttpMessage& req, const std::string& bo
 
 static std::string metrics_text() {
   std::ostringstream o;
+  if (g_relay) o << "omni_proxy_open_streams " << g_relay->open_streams() << "\n";
   auto dump = [&](const char* pool, LoadBalancer* lb) {
     if (!lb) return;
     for (int i = 0; i < lb->n_peers(); ++i) {
@@ -386,7 +557,9 @@ static void handle_connection(int client) {
       if (json_get(presp.body, key, v)) json_set(body, key, v);
     }
   }
-  run_decode(client, req, body);
+  bool handed_over = false;
+  run_decode(client, req, body, handed_over);
+  if (handed_over) return;          // the relay loop owns the descriptors now and closes them at the end of the stream
   timeline("Proxy finished request", rid);
   shutdown(client, SHUT_RDWR);
   close(client);
@@ -429,6 +602,8 @@ class Pool {
 };
 
 static void serve(int lfd) {
+  Relay relay;            // per worker process
+  g_relay = &relay;
   Pool pool(g_cfg.threads);
   int ep = epoll_create1(0);
   struct epoll_event ev = {};
@@ -449,6 +624,8 @@ static void serve(int lfd) {
     }
   }
   pool.stop();
+  relay.stop();
+  g_relay = nullptr;
   close(ep);
 }
 

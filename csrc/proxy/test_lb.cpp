@@ -40,8 +40,16 @@ static int test_policies() {
     LbParams p; p.policy = "pd_score_balance_prefill";
     LoadBalancer lb(fresh(), 3, p);
     Ticket a = lb.get_peer(1000, 0), b = lb.get_peer(10, 0), c = lb.get_peer(10, 0), d = lb.get_peer(10, 0);
-    CHECK(a.peer == 0 && b.peer == 1 && c.peer == 2 && d.peer == 1);
-    CHECK(lb.peer(0).total_time_cost == 1000 && lb.peer(1).total_time_cost == 20);
+    // equal scores go round: a -> 0 (all idle), b -> 1 (1 and 2 tie), c -> 2 (the only idle one), d -> 2 (1 and 2 tie again,
+    // the turn has moved on)
+    CHECK(a.peer == 0 && b.peer == 1 && c.peer == 2 && d.peer == 2);
+    CHECK(lb.peer(0).total_time_cost == 1000 && lb.peer(1).total_time_cost == 10 && lb.peer(2).total_time_cost == 20);
+    {  // an idle pool spreads equal requests over all peers instead of sending them to the first
+      LoadBalancer idle(fresh(), 4, p);
+      int hits[4] = {0, 0, 0, 0};
+      for (int i = 0; i < 40; ++i) { Ticket t = idle.get_peer(100, 0); ++hits[t.peer]; idle.free_peer(t, false, 0); }
+      CHECK(hits[0] == 10 && hits[1] == 10 && hits[2] == 10 && hits[3] == 10);
+    }
     lb.free_peer(a, false, 0);
     CHECK(lb.peer(0).total_time_cost == 0 && lb.peer(0).active_requests == 0 && lb.peer(0).served == 1);
   }

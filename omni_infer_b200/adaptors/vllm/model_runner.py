@@ -46,7 +46,7 @@ class RunnerConfig:
     ep_backend: str = "fused"                  # fused (NVLink peer-memory kernels) | nccl (all-to-all baseline)
     ep_wait_ms: float = 2000.0                 # bound of every cross-rank wait inside the fused kernels
     attn_tp: bool = False                      # attention heads sharded over all ranks, token-sharded hidden states
-    tp_backend: str = "fused"                  # fused | nccl
+    tp_backend: str = "fused"                  # fused | nvls | nccl
 
 
 class ModelRunner:
@@ -108,10 +108,11 @@ class ModelRunner:
         cfg.attn_tp_size, cfg.attn_tp_rank = ps.world_size, ps.rank
         from ...parallel.tp_fused import TpFusedContext, TpNcclBaseline
         grp = ps.group("world").group
-        if self.cfg.tp_backend == "fused" and self.device.type == "cuda":
+        if self.cfg.tp_backend in ("fused", "nvls") and self.device.type == "cuda":
             max_tok = max(self.cfg.max_num_batched_tokens, self.cfg.max_num_seqs * self.tpr) + 4 * ps.world_size
+            # "nvls": the reducing collectives go through the NVSwitch's in-switch reduction (multimem)
             ps.tp_fused = TpFusedContext(grp, max_tokens=max_tok, max_k_bytes=cfg.hidden_size * 2, max_n=cfg.hidden_size,
-                                         wait_ms=self.cfg.ep_wait_ms)
+                                         wait_ms=self.cfg.ep_wait_ms, nvls=self.cfg.tp_backend == "nvls")
         else:
             ps.tp_fused = TpNcclBaseline(grp)
 

@@ -47,7 +47,7 @@ class EngineConfig:
     enforce_eager: bool = False
     ep_backend: str = "fused"
     attn_tp: bool = False            # tensor-parallel attention over all ranks (default: data-parallel attention)
-    tp_backend: str = "fused"        # fused (GEMMs with the collectives inside) | nccl (library collectives)
+    tp_backend: str = "fused"        # fused (GEMMs with the collectives inside) | nvls (same, reductions inside the NVSwitch) | nccl (library collectives)
     seed: int = 0
     kv_transfer_config: Optional[dict] = None    # {"kv_role": "kv_producer"|"kv_consumer", ...}
     enable_omni_attn: bool = False

@@ -44,7 +44,7 @@ class TpFusedContext:
     a round counter in device memory, so they may be called at any point of the sequence.  All counters and flags
     live in device memory and advance inside the kernels: the calls can be captured in a CUDA graph and replayed."""
 
-    def __init__(self, group, max_tokens: int, max_k_bytes: int, max_n: int, wait_ms: float = 2000.0):
+    def __init__(self, group, max_tokens: int, max_k_bytes: int, max_n: int, wait_ms: float = 2000.0, nvls: bool = False):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -81,6 +81,13 @@ class TpFusedContext:
         self._fin_done = lp + self.off_ctrl + 20
         self._ar_round = lp + self.off_ctrl + 24
         self._ar_done = lp + self.off_ctrl + 28
+        # in-switch reduction (multimem) for the two reducing collectives: the row-parallel GEMM then writes its
+        # partial product to local memory and every rank pulls the sums of its rows through the NVSwitch, instead of
+        # every rank storing its partial rows into the owner's slab
+        self.nvls = None
+        if nvls:
+            from .nvls import NvlsWorkspace
+            self.nvls = NvlsWorkspace(group, self.max_tokens * self.max_n * 2, wait_ms)
 
     # ------------------------------------------------------------------ helpers
     def rows_per_rank(self, total_rows: int) -> int:
@@ -182,6 +189,8 @@ class TpFusedContext:
         its slot on every rank (two halves used in turn, chosen by the round counter in device memory), then each
         rank adds the slots in fp32.  One NVLink crossing, no library call."""
         rows, n = x.shape
+        if self.nvls is not None:
+            return self.nvls.all_reduce(x)
         assert x.dtype == torch.bfloat16 and x.is_contiguous() and n % 8 == 0 and n <= self.max_n and rows <= self.ar_rows
         L = nat.lib()
         slot_bytes = self.ar_rows * self.max_n * 2
@@ -215,6 +224,11 @@ class TpFusedContext:
             w = w.unsqueeze(0)
         N, K = w.shape[1], w.shape[2]
         assert N <= self.max_n and N % 8 == 0 and rpr <= self.max_rpr
+        if self.nvls is not None:
+            fp8 = x.dtype == FP8
+            part = self.nvls.view((T, N))
+            _tm2(1 if fp8 else 0, 0, w, x, part, 1, N, K, T, None, None, w_scale, x_scale, 0, None, None, out_ld=N)
+            return self.nvls.reduce_rows(T, N, residual=residual, norm_weight=norm_weight, eps=eps)
         coll = TmCollective()
         coll.rs_world, coll.rs_rank, coll.rs_rows_per_rank = self.world, self.rank, rpr
         for d in range(self.world):

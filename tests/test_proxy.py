@@ -67,7 +67,7 @@ class _Recorder:
         self.requests = []
 
 
-def _make_server(kind, rec, fail=False):
+def _make_server(kind, rec, fail=False, chunks=3, gap=0.02):
     class H(BaseHTTPRequestHandler):
         def log_message(self, *a):
             pass
@@ -91,12 +91,12 @@ def _make_server(kind, rec, fail=False):
                 self.send_response(200)
                 self.send_header("Content-Type", "text/event-stream")
                 self.end_headers()
-                for i in range(3):
+                for i in range(chunks):
                     chunk = {"choices": [{"text": f"t{i}"}], "usage": {"total_tokens": 10 + i}, "output_num_token": i + 1,
                              "prompt_num_token": 7}
                     self.wfile.write(f"data: {json.dumps(chunk)}\n\n".encode())
                     self.wfile.flush()
-                    time.sleep(0.02)
+                    time.sleep(gap)
                 self.wfile.write(b"data: [DONE]\n\n")
 
     srv = ThreadingHTTPServer(("127.0.0.1", 0), H)
@@ -155,6 +155,43 @@ def test_two_phase_flow_and_stream_relay(proxy_binary):
         metrics = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=2).read().decode()
         assert 'omni_proxy_served_total{pool="decode",peer="0"} 2' in metrics
         assert 'omni_proxy_active_requests{pool="decode",peer="0"} 0' in metrics
+    finally:
+        proc.terminate()
+        proc.wait(timeout=5)
+        p_srv.shutdown()
+        d_srv.shutdown()
+
+
+def test_many_long_streams_need_no_thread_each(proxy_binary):
+    """48 token streams of about a second each through a proxy with two worker threads: the streams are carried by the
+    relay loop, so all of them run at the same time (they would take 24 s one pair after the other), every client gets
+    every chunk, the decode counters return to zero and /metrics answers while the streams are open."""
+    rec = _Recorder()
+    p_srv, d_srv = _make_server("prefill", rec), _make_server("decode", rec, chunks=20, gap=0.05)
+    port = _free_port()
+    proc = _start_proxy(proxy_binary, port, [p_srv.server_port], [d_srv.server_port], extra=("--threads", "2"))
+    try:
+        results, seen_open = [], []
+
+        def client(i):
+            results.append(_post(port, {"prompt": f"p{i}", "max_tokens": 20, "stream": True}))
+
+        t0 = time.time()
+        ts = [threading.Thread(target=client, args=(i,)) for i in range(48)]
+        for t in ts:
+            t.start()
+        time.sleep(0.6)
+        m = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        seen_open = [int(l.split()[1]) for l in m.splitlines() if l.startswith("omni_proxy_open_streams")]
+        for t in ts:
+            t.join()
+        took = time.time() - t0
+        assert all(st == 200 and text.count("data: {") == 20 and "[DONE]" in text for st, text in results), results[:2]
+        assert took < 8.0, took
+        assert seen_open and seen_open[0] >= 8, m
+        m = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        assert 'omni_proxy_active_requests{pool="decode",peer="0"} 0' in m and 'omni_proxy_decode_tokens{pool="decode",peer="0"} 0' in m
+        assert 'omni_proxy_served_total{pool="decode",peer="0"} 48' in m and "omni_proxy_open_streams 0" in m
     finally:
         proc.terminate()
         proc.wait(timeout=5)
