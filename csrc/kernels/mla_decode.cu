@@ -69,7 +69,7 @@ constexpr int MLA_THREADS = 352;
 // four packed-bf16 q chunks
 constexpr int TM_O = 0, TM_S = 256, TM_Q = 384, TM_COLS = 512;
 
-enum { MS_Q = 31, MS_KV_EMPTY, MS_KV_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT, MS_TMEM };
+enum { MS_Q = 31, MS_KV_EMPTY, MS_KV_FULL, MS_P_FULL, MS_S_FULL, MS_O_DONE, MS_QT, MS_TMEM, MS_SC_ISSUED };
 
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -80,6 +80,20 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       : "memory");
 }
 
+
+// What every warp was waiting for when a CTA gave up: the first CTA of a process whose wait runs out leaves this
+// record (read and cleared by omni_mla_debug_read), so that a time-out can be told from its report alone.
+//   [0] taken  [1..3] blockIdx x, y, z  [4] tiles of the CTA  [5] kv_len  [6] first tile  [7] num_splits
+//   [8 + w] warp w: (site << 16) | detail of the wait it left, 0 if it was not waiting
+__device__ int g_mla_debug[32];
+constexpr int MLA_DBG_INTS_AFTER_ABORT = 27;   // the per-warp words sit at byte 320 of the barrier block
+
+__device__ __forceinline__ bool mla_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, OmniStatus* st, int site,
+                                         int detail) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, st, site, detail);
+  if (!ok) const_cast<int*>(abort_flag)[MLA_DBG_INTS_AFTER_ABORT + (threadIdx.x >> 5)] = (site << 16) | (detail & 0xffff);
+  return ok;
+}
 
 // ---------------------------------------------------------------------------------------------------------
 // Producer and MMA roles.  Both walk the same sequence of KV chunks with a few running counters (no division,
@@ -96,7 +110,7 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
 // ---------------------------------------------------------------------------------------------------------
 struct MlaPipe {
   uint32_t sq_addr, kv_addr;
-  uint64_t *kv_full, *kv_empty, *s_full, *p_full, *o_done, *o_final;
+  uint64_t *kv_full, *kv_empty, *s_full, *p_full, *o_done, *o_final, *sc_issued;
   volatile int* abort_flag;
   OmniStatus* status;
 };
@@ -131,7 +145,7 @@ __device__ __forceinline__ void mla_producer(const MlaPipe& px, const CUtensorMa
     for (int oc = 0; oc < 5; ++oc) {
       const int c = oc < 4 ? (1 - HALF) * 4 + oc : 8;
       uint64_t* full = &px.kv_full[MLA_VSTAGES + rg.slot];
-      if (!mbar_wait(&px.kv_empty[MLA_VSTAGES + rg.slot], rg.par ^ 1u, px.abort_flag, px.status, MS_KV_EMPTY, c)) return;
+      if (!mla_wait(&px.kv_empty[MLA_VSTAGES + rg.slot], rg.par ^ 1u, px.abort_flag, px.status, MS_KV_EMPTY, (i << 8) | c)) return;
       mbar_expect_tx(full, MLA_CHUNK_BYTES);
       const uint32_t dst = px.kv_addr + MLA_VSTAGES * MLA_VSTAGE_BYTES + rg.slot * MLA_CHUNK_BYTES;
       if (box_rows == MLA_TILE) tma_load_2d_addr(dst, tmap_kv, full, c * 64, rows[0]);
@@ -143,7 +157,7 @@ __device__ __forceinline__ void mla_producer(const MlaPipe& px, const CUtensorMa
     }
     {
       uint64_t* full = &px.kv_full[rg.vstage];
-      if (!mbar_wait(&px.kv_empty[rg.vstage], rg.vpar ^ 1u, px.abort_flag, px.status, MS_KV_EMPTY, 100 + (int)rg.vstage)) return;
+      if (!mla_wait(&px.kv_empty[rg.vstage], rg.vpar ^ 1u, px.abort_flag, px.status, MS_KV_EMPTY, (i << 8) | (100 + (int)rg.vstage))) return;
       mbar_expect_tx(full, MLA_VSTAGE_BYTES);
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
@@ -162,7 +176,7 @@ __device__ __forceinline__ void mla_producer(const MlaPipe& px, const CUtensorMa
 
 // S = Q K^T of the next tile in the score stream, into S buffer `buf`.  Run by the whole MMA warp; one
 // elected lane issues.
-__device__ __forceinline__ bool mla_issue_scores(const MlaPipe& px, MlaRing& rg, const uint32_t buf) {
+__device__ __forceinline__ bool mla_issue_scores(const MlaPipe& px, MlaRing& rg, const uint32_t buf, const int tile) {
   constexpr uint32_t idesc_qk = umma_idesc(128, MLA_TILE, 1, 1, 0, 0);
   const uint32_t d_s = TM_S + buf * 64;
   const uint64_t qdesc0 = umma_desc_kmajor_sw128(px.sq_addr);
@@ -170,7 +184,7 @@ __device__ __forceinline__ bool mla_issue_scores(const MlaPipe& px, MlaRing& rg,
   const uint64_t vdesc0 = umma_desc_kmajor_sw128(px.kv_addr);
 #pragma unroll 1
   for (int oc = 0; oc < 5; ++oc) {
-    if (!mbar_wait(&px.kv_full[MLA_VSTAGES + rg.slot], rg.par, px.abort_flag, px.status, MS_KV_FULL, oc)) return false;
+    if (!mla_wait(&px.kv_full[MLA_VSTAGES + rg.slot], rg.par, px.abort_flag, px.status, MS_KV_FULL, (tile << 8) | oc)) return false;
     tc_fence_after();
     const uint64_t bd = ring0 + (uint64_t)(rg.slot * (MLA_CHUNK_BYTES >> 4));
     if (elect_one()) {
@@ -188,7 +202,7 @@ __device__ __forceinline__ bool mla_issue_scores(const MlaPipe& px, MlaRing& rg,
     __syncwarp();
     rg.next_slot();
   }
-  if (!mbar_wait(&px.kv_full[rg.vstage], rg.vpar, px.abort_flag, px.status, MS_KV_FULL, 100 + (int)rg.vstage)) return false;
+  if (!mla_wait(&px.kv_full[rg.vstage], rg.vpar, px.abort_flag, px.status, MS_KV_FULL, (tile << 8) | (100 + (int)rg.vstage))) return false;
   tc_fence_after();
   if (elect_one()) {
     const uint64_t vd = vdesc0 + (uint64_t)(rg.vstage * (MLA_VSTAGE_BYTES >> 4));
@@ -200,6 +214,7 @@ __device__ __forceinline__ bool mla_issue_scores(const MlaPipe& px, MlaRing& rg,
                   idesc_qk, 1u);
     }
     umma_commit(&px.s_full[buf]);
+    mbar_arrive(&px.sc_issued[buf]);   // every chunk of this tile has landed: the other issuer may look at the ring again
   }
   __syncwarp();
   rg.next_stage();
@@ -219,12 +234,18 @@ __device__ __forceinline__ void mla_mma(const MlaPipe& px, int n, const int whic
   const uint64_t vdesc0 = umma_desc_mnmajor_sw128(px.kv_addr, MLA_CHUNK_BYTES, 1024);
 #pragma unroll 1
   for (int i = which; i < n; i += 2) {
-    if (!mla_issue_scores(px, rg, buf)) return;
+    // A ring slot (and a value stage) is filled for the two issuers in turn, and a parity wait can only tell the
+    // current fill from the one before it.  The fill before "mine" belongs to the previous tile, which the other
+    // issuer consumes; if it has not landed yet when this warp arrives (TMA loads complete in any order), the wait for
+    // mine would see the fill two back as "complete" and pass on stale data, and the releases that follow wedge the
+    // ring.  So this warp first waits until the other one has seen every chunk of the previous tile land.
+    if (i >= 1 && !mla_wait(&px.sc_issued[buf ^ 1u], ((uint32_t)(i - 1) >> 1) & 1u, px.abort_flag, px.status, MS_SC_ISSUED, i)) return;
+    if (!mla_issue_scores(px, rg, buf, i)) return;
     rg.skip_tile();
     // the first P V zero-initialises the accumulator: the other issuer's first P V must enter the pipe after it
-    if (i == 1 && !mbar_wait(px.o_done, 0u, px.abort_flag, px.status, MS_O_DONE, 0)) return;
+    if (i == 1 && !mla_wait(px.o_done, 0u, px.abort_flag, px.status, MS_O_DONE, 0)) return;
     // ---- O += P V
-    if (!mbar_wait(&px.p_full[buf], ((uint32_t)i >> 1) & 1u, px.abort_flag, px.status, MS_P_FULL, i)) return;
+    if (!mla_wait(&px.p_full[buf], ((uint32_t)i >> 1) & 1u, px.abort_flag, px.status, MS_P_FULL, i)) return;
     tc_fence_after();
     if (elect_one()) {
       // 16 tokens per MMA: two 8-token groups of 1024 B; dims advance by whole 8 KB chunks.  P of tokens
@@ -261,6 +282,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint64_t* o_done = p_full + 2;                    // 1
   uint64_t* o_final = o_done + 1;                   // 1: all P V of this CTA retired (one arrival per issuer)
   uint64_t* qt_full = o_final + 1;                  // 1: q chunks written to TMEM
+  uint64_t* sc_issued = bars + 30;                  // 2, one per issuer: the scores of its current tile are all issued
   uint32_t* tmem_slot = (uint32_t*)(qt_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* sm_counter = (int*)(tmem_slot + 2);          // softmax group rendezvous (only grows)
@@ -289,11 +311,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], 8);
     }
+    mbar_init(&sc_issued[0], 1);
+    mbar_init(&sc_issued[1], 1);
     mbar_init(o_done, 1);
     mbar_init(o_final, n >= 2 ? 2 : 1);   // the last P V of each issuer that has tiles
     mbar_init(qt_full, 8);
     *abort_flag = 0;
     *sm_counter = 0;
+    for (int w = 0; w < 12; ++w) const_cast<int*>(abort_flag)[MLA_DBG_INTS_AFTER_ABORT + w] = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -318,7 +343,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   if (n > 0) {
     if (warp == 0) {
       if (lane == 0) {
-        const MlaPipe px{smem_u32(sq), smem_u32(skv), kv_full, kv_empty, s_full, p_full, o_done, o_final, abort_flag, p.status};
+        const MlaPipe px{smem_u32(sq), smem_u32(skv), kv_full, kv_empty, s_full, p_full, o_done, o_final, sc_issued, abort_flag, p.status};
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_kv);
         // q chunks in shared memory: this half's four value-dim chunks (slots 0..3) and the rope chunk (slot 4)
@@ -331,9 +356,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         else mla_producer<1>(px, &tmap_kv, bt, p.block_size, box_rows, kv_len, tile_begin, n);
       }
     } else if (warp == 1 || warp == 10) {
-      const MlaPipe px{smem_u32(sq), smem_u32(skv), kv_full, kv_empty, s_full, p_full, o_done, o_final, abort_flag, p.status};
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, MS_Q, 0);
-      if (ok) ok = mbar_wait(qt_full, 0, abort_flag, p.status, MS_QT, 0);
+      const MlaPipe px{smem_u32(sq), smem_u32(skv), kv_full, kv_empty, s_full, p_full, o_done, o_final, sc_issued, abort_flag, p.status};
+      bool ok = mla_wait(q_full, 0, abort_flag, p.status, MS_Q, 0);
+      if (ok) ok = mla_wait(qt_full, 0, abort_flag, p.status, MS_QT, 0);
       tc_fence_after();
       if (ok) mla_mma(px, n, warp == 1 ? 0 : 1);
     } else {
@@ -355,7 +380,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         ++sync_no;
         uint32_t spins = 0;
         while (*(volatile int*)sm_counter < 8 * sync_no) {
-          if (((++spins) & 0xff) == 0 && *abort_flag) return false;
+          if (((++spins) & 0xff) == 0 && *abort_flag) {
+            const_cast<int*>(abort_flag)[MLA_DBG_INTS_AFTER_ABORT + warp] = (99 << 16) | (sync_no & 0xffff);
+            return false;
+          }
         }
         __syncwarp();
         return true;
@@ -382,7 +410,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       for (int i = 0; i < n; ++i) {
         const int st = i & 1;
-        if (!mbar_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, MS_S_FULL, i)) { ok = false; break; }
+        if (!mla_wait(&s_full[st], (i >> 1) & 1, abort_flag, p.status, MS_S_FULL, i)) { ok = false; break; }
         tc_fence_after();
         const int valid = kv_len - (tile_begin + i) * MLA_TILE - grp * 32;  // valid columns of this group's half
         const uint32_t s_addr = lane_addr + TM_S + st * 64 + grp * 32;
@@ -415,7 +443,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           m = m_new;
         } else if (__any_sync(0xffffffffu, grow)) {
           // P V of the previous tile must have retired before O is touched; P V of this tile waits for P
-          if (!mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, MS_O_DONE, i)) { ok = false; break; }
+          if (!mla_wait(o_done, (i - 1) & 1, abort_flag, p.status, MS_O_DONE, i)) { ok = false; break; }
           tc_fence_after();
           const float f = grow ? exp2f(m - m_new) : 1.0f;
           if (grow) { l *= f; m = m_new; }
@@ -452,7 +480,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       // o_done flips once per tile and is only sampled when a rescale is needed, so its parity cannot
       // tell "last tile retired" from "two tiles behind"; the single-use o_final barrier can.
-      if (ok) ok = mbar_wait(o_final, 0, abort_flag, p.status, MS_O_DONE, n);
+      if (ok) ok = mla_wait(o_final, 0, abort_flag, p.status, MS_O_DONE, n);
       if (ok) ok = group_sync();   // every warp is past its last read of the maxima slabs
       if (ok) {
         sm_sum[grp * 128 + row] = l;
@@ -524,6 +552,20 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag && threadIdx.x == 0 && atomicCAS(&g_mla_debug[0], 0, 1) == 0) {
+    g_mla_debug[1] = blockIdx.x; g_mla_debug[2] = blockIdx.y; g_mla_debug[3] = blockIdx.z;
+    g_mla_debug[4] = n; g_mla_debug[5] = kv_len; g_mla_debug[6] = tile_begin; g_mla_debug[7] = p.num_splits;
+    for (int w = 0; w < 12; ++w) g_mla_debug[8 + w] = const_cast<int*>(abort_flag)[MLA_DBG_INTS_AFTER_ABORT + w];
+    // bit b set = "the phase of parity 0 of barrier b has completed" (i.e. the barrier now runs an odd phase)
+    int full_odd = 0, empty_odd = 0, misc = 0;
+    for (int c = 0; c < 9; ++c) {
+      full_odd |= (int)mbar_try_wait(&kv_full[c], 0) << c;
+      empty_odd |= (int)mbar_try_wait(&kv_empty[c], 0) << c;
+    }
+    misc |= (int)mbar_try_wait(&s_full[0], 0) | ((int)mbar_try_wait(&s_full[1], 0) << 1) | ((int)mbar_try_wait(&p_full[0], 0) << 2) |
+            ((int)mbar_try_wait(&p_full[1], 0) << 3) | ((int)mbar_try_wait(o_done, 0) << 4) | ((int)mbar_try_wait(o_final, 0) << 5);
+    g_mla_debug[20] = full_odd; g_mla_debug[21] = empty_odd; g_mla_debug[22] = misc;
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TM_COLS);
@@ -562,6 +604,14 @@ __global__ void mla_combine_kernel(const float* __restrict__ o_part, const float
 
 using namespace omni;
 
+
+// Copies the record of the first CTA whose wait ran out (32 ints, all zero if none did) and clears it.
+extern "C" int omni_mla_debug_read(int* out32) {
+  cudaError_t e = cudaMemcpyFromSymbol(out32, g_mla_debug, sizeof(int) * 32);
+  if (e != cudaSuccess) return (int)e;
+  static const int zeros[32] = {0};
+  return (int)cudaMemcpyToSymbol(g_mla_debug, zeros, sizeof(zeros));
+}
 
 // Scratch needed for num_splits > 1: o_part = Bq*splits*H*512 floats, lse_part = Bq*splits*H floats.
 extern "C" int omni_mla_decode(const void* q, const void* cache, int cache_ld, long long num_slots,

@@ -101,7 +101,18 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const NvlsParams p)
   // threads of one rank touch addresses world * 16 bytes apart and all ranks together cover the buffer densely
   const long long vecs = p.numel / 8;
   const long long mine = (vecs + p.world - 1 - p.rank) / p.world;     // vectors v with v % world == rank
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < mine; i += (long long)gridDim.x * blockDim.x) {
+  // four reductions in flight per thread before the first broadcast: the round trip through the switch is long and a
+  // thread that waits for each sum before asking for the next leaves the links idle
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < mine; i += 4 * stride) {
+    uint32_t r[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mm_ld_reduce_bf16x8(p.mc + ((i + u * stride) * p.world + p.rank) * 16, r[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mm_st_bf16x8(p.mc + ((i + u * stride) * p.world + p.rank) * 16, r[u]);
+  }
+  for (; i < mine; i += stride) {
     const long long v = i * p.world + p.rank;
     uint32_t r[4];
     mm_ld_reduce_bf16x8(p.mc + v * 16, r);
@@ -202,9 +213,12 @@ extern "C" int omni_nvls_allreduce(void* mc, void* local, void* const* peer_bufs
   if (numel <= 0 || numel % 8 != 0 || numel * 2 > flag_offset) return -3;
   p.numel = numel;
   const long long mine = (numel / 8 + world - 1) / world;
-  int grid = (int)((mine + 511) / 512);
+  // small messages: few CTAs (every CTA polls the entry flags); large ones: enough threads to keep four vectors per
+  // thread in flight on every link, at most one CTA per SM
+  int grid = (int)((mine + 2047) / 2048);
   if (grid < 1) grid = 1;
-  if (grid > (ctas > 0 ? ctas : 32)) grid = ctas > 0 ? ctas : 32;
+  const int cap = ctas > 0 ? ctas : 148;
+  if (grid > cap) grid = cap;
   nvls_allreduce_kernel<<<grid, 512, 0, stream>>>(p);
   return (int)cudaGetLastError();
 }

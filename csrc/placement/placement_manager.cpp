@@ -172,13 +172,25 @@ void Placement::stop() {
 void Placement::loop() {
   // wait until the expert tensors are registered
   while (!should_stop_ && !weights_->is_initialized()) std::this_thread::sleep_for(std::chrono::milliseconds(50));
-  while (!should_stop_) {
+  while (true) {
     {
       // the previous round must have been applied by the inference thread before new data is staged
       std::unique_lock<std::mutex> lk(mu_);
       cv_.wait(lk, [&] { return should_stop_ || pending_.empty(); });
     }
-    if (should_stop_) break;
+    // The threads of all ranks leave together: a round is a sequence of collectives, so a thread that simply
+    // returned when its own rank asked it to stop would leave the others blocked in the next one (and their stop()
+    // blocked in join).  Every round therefore starts by exchanging "do I want to stop"; if anybody does, all do.
+    int64_t mine = should_stop_ ? 1 : 0;
+    std::vector<int64_t> all((size_t)dist_->world(), 0);
+    try {
+      dist_->allgather_i64(&mine, all.data(), 1);
+    } catch (const std::exception&) {
+      break;
+    }
+    bool stop = false;
+    for (int64_t v : all) stop = stop || v != 0;
+    if (stop) break;
     try {
       run_round();
     } catch (const std::exception&) {

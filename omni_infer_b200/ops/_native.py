@@ -125,8 +125,17 @@ def check_status(device=None, reset: bool = True) -> None:
             buf.zero_()
         what = {1: "mbarrier wait gave up", 2: "flag wait gave up", 3: "index out of bounds (access skipped)",
                 4: "capacity exceeded"}.get(vals[0], "kernel error")
+        extra = ""
+        if 31 <= vals[1] <= 39:
+            # the MLA decode kernel leaves what each of its warps was waiting for when the first CTA gave up
+            rec = (ctypes.c_int * 32)()
+            if lib().omni_mla_debug_read(rec) == 0 and rec[0]:
+                waits = {w: (rec[8 + w] >> 16, rec[8 + w] & 0xffff) for w in range(12) if rec[8 + w]}
+                extra = (f"; first CTA to give up: block=({rec[1]},{rec[2]},{rec[3]}) tiles={rec[4]} kv_len={rec[5]} "
+                         f"first_tile={rec[6]} splits={rec[7]} warp waits (site, detail)={waits} "
+                         f"odd-phase masks: kv_full={rec[20]:09b} kv_empty={rec[21]:09b} s/p/o={rec[22]:06b}")
         raise KernelProtocolError(f"{what} in {_site_kernel(vals[1])}: code={vals[0]} site={vals[1]} block={vals[2]} "
-                                  f"detail={vals[3]}")
+                                  f"detail={vals[3]}{extra}")
 
 
 def check_rc(rc: int, what: str) -> None:

@@ -28,9 +28,11 @@ def _align(x: int, a: int = 256) -> int:
 def available(device=None) -> bool:
     """True when the device and the driver offer multicast memory (NVSwitch systems)."""
     try:
+        import torch.distributed._symmetric_memory as symm
         from torch._C._distributed_c10d import _SymmetricMemory
         dev = torch.device(device if device is not None else "cuda")
-        return bool(_SymmetricMemory.has_multicast_support(dev.type, dev.index if dev.index is not None else torch.cuda.current_device()))
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        return bool(_SymmetricMemory.has_multicast_support(symm.DeviceType.CUDA, idx))
     except Exception:  # noqa: BLE001  (no such API in this build: no NVLS)
         return False
 

@@ -141,3 +141,21 @@ def test_in_switch_all_reduce_and_reduce_rows():
     assert r["allreduce_max_err"] <= r["allreduce_ref_max"] * 2.0 ** -8 + 1e-3, r
     assert r["rows_max_err"] < 0.05 and r["norm_max_err"] < 0.06, r
     assert r["graph_replay_ok"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_attention_with_in_switch_reduction_matches_oracle():
+    """The small MLA + MoE model with tensor-parallel attention whose o_proj reduce-scatter (+ residual + RMSNorm) runs
+    through the NVSwitch: every generated token against the fp32 oracle, first tokens equal to the peer-store path's."""
+    import test_multi_gpu as mg
+    from omni_infer_b200.parallel import nvls
+    if not nvls.available():
+        pytest.skip("no multicast support on this device / driver")
+    world = 8 if torch.cuda.device_count() >= 8 else (4 if torch.cuda.device_count() >= 4 else 2)
+    env = {"ATTN_TP": "1", "TP_BACKEND": "nvls"}
+    # this worker must keep NVLS on: _run of the other file switches it off for NCCL, which does not affect the
+    # symmetric-memory rendezvous of the workspace
+    got = mg._run(world, env, 29651)
+    mg._near_oracle(got, what=f"TP{world} attention, in-switch reduce-scatter")
+    peer = mg._run(world, {"ATTN_TP": "1", "TP_BACKEND": "fused"}, 29652)
+    assert [o[0] for o in got] == [o[0] for o in peer]
