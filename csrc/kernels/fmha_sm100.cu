@@ -10,8 +10,7 @@
 // Causal mask is aligned to the end of the key range (query i of a request with Lq queries and Lk keys sees
 // keys <= Lk - Lq + i), which also covers chunked prefill and prefix-cache hits.
 //
-// omni_gqa_paged_decode: one query token per request over a paged K/V cache; split-KV partials plus an
-// LSE merge.  CUDA-core kernel (bandwidth-bound at the 8:1 head ratio of the supported models).
+// The paged decode of the GQA models (one query token per request) is a separate kernel: gqa_decode.cu.
 //
 // Reference call sites: npu_fused_infer_attention_score / npu_fusion_attention
 // (omni/models/common/layers/attention/deepseek_mla.py:386-400, omni/models/common/layers/attention/backend/attention.py:590-666).
@@ -277,153 +276,6 @@ fmha_varlen_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// GQA paged decode.  grid (Hkv, splits, B), 128 threads.  D = 128.  G = Hq / Hkv <= 16.
-// Each warp walks tiles of 32 keys: lane = key for the scores, lane = 4 output dims for P V.
-// ------------------------------------------------------------------------------------------------
-constexpr int GD_MAXG = 16;
-
-__global__ void __launch_bounds__(128)
-gqa_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                  const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int bt_ld,
-                  const int* __restrict__ seq_lens, int block_size, int Hq, int Hkv, float scale_log2, int splits,
-                  float* o_part, float* lse_part, __nv_bfloat16* out) {
-  constexpr int D = 128;
-  const int hk = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
-  const int G = Hq / Hkv;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int L = seq_lens[b];
-  const int tiles = (L + 31) / 32;
-  const int tps = (tiles + splits - 1) / splits;
-  const int t_begin = split * tps, t_end = min(tiles, t_begin + tps);
-
-  __shared__ __align__(16) __nv_bfloat16 sq[GD_MAXG * D];
-  __shared__ float sp[4][GD_MAXG][32];
-  __shared__ float s_m[4][GD_MAXG], s_l[4][GD_MAXG];
-  __shared__ float s_o[4][GD_MAXG][D];
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) sq[i] = q[((size_t)b * Hq + hk * G) * D + i];
-  __syncthreads();
-
-  float m[GD_MAXG], l[GD_MAXG], o[GD_MAXG][4];
-#pragma unroll
-  for (int g = 0; g < GD_MAXG; ++g) { m[g] = -INFINITY; l[g] = 0.f; o[g][0] = o[g][1] = o[g][2] = o[g][3] = 0.f; }
-
-  for (int t = t_begin + warp; t < t_end; t += 4) {
-    const int key = t * 32 + lane;
-    const bool valid = key < L;
-    size_t slot = 0;
-    if (valid) slot = (size_t)block_table[(size_t)b * bt_ld + key / block_size] * block_size + key % block_size;
-    float sc[GD_MAXG];
-#pragma unroll
-    for (int g = 0; g < GD_MAXG; ++g) sc[g] = 0.f;
-    if (valid) {
-      const __nv_bfloat16* kr = k_cache + (slot * Hkv + hk) * D;
-#pragma unroll 4
-      for (int d0 = 0; d0 < D; d0 += 8) {
-        uint4 raw = *reinterpret_cast<const uint4*>(kr + d0);
-        const __nv_bfloat16* kh = reinterpret_cast<const __nv_bfloat16*>(&raw);
-        float kf[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kf[e] = __bfloat162float(kh[e]);
-#pragma unroll
-        for (int g = 0; g < GD_MAXG; ++g) {
-          if (g < G) {
-            uint4 qraw = *reinterpret_cast<const uint4*>(sq + g * D + d0);
-            const __nv_bfloat16* qh = reinterpret_cast<const __nv_bfloat16*>(&qraw);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) sc[g] = fmaf(kf[e], __bfloat162float(qh[e]), sc[g]);
-          }
-        }
-      }
-    }
-    // per-head online softmax over this tile
-#pragma unroll
-    for (int g = 0; g < GD_MAXG; ++g) {
-      if (g < G) {
-        const float s = valid ? sc[g] * scale_log2 : -INFINITY;
-        const float mt = warp_max(s);
-        const float m_new = fmaxf(m[g], mt);
-        const float f = exp2f(m[g] - m_new);
-        const float pj = exp2f(s - m_new);
-        l[g] = l[g] * f + warp_sum(pj);
-        m[g] = m_new;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[g][e] *= f;
-        sp[warp][g][lane] = pj;
-      }
-    }
-    __syncwarp();
-    // P V: lane owns dims [4*lane, 4*lane+4)
-    const int nk = min(32, L - t * 32);
-    for (int j = 0; j < nk; ++j) {
-      const int kj = t * 32 + j;
-      const size_t sj = (size_t)block_table[(size_t)b * bt_ld + kj / block_size] * block_size + kj % block_size;
-      uint2 raw = *reinterpret_cast<const uint2*>(v_cache + (sj * Hkv + hk) * D + lane * 4);
-      const __nv_bfloat16* vh = reinterpret_cast<const __nv_bfloat16*>(&raw);
-      const float v0 = __bfloat162float(vh[0]), v1 = __bfloat162float(vh[1]), v2 = __bfloat162float(vh[2]),
-                  v3 = __bfloat162float(vh[3]);
-#pragma unroll
-      for (int g = 0; g < GD_MAXG; ++g) {
-        if (g < G) {
-          const float pj = sp[warp][g][j];
-          o[g][0] = fmaf(pj, v0, o[g][0]); o[g][1] = fmaf(pj, v1, o[g][1]);
-          o[g][2] = fmaf(pj, v2, o[g][2]); o[g][3] = fmaf(pj, v3, o[g][3]);
-        }
-      }
-    }
-    __syncwarp();
-  }
-  // merge the four warps
-#pragma unroll
-  for (int g = 0; g < GD_MAXG; ++g) {
-    if (g < G) {
-      if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) s_o[warp][g][lane * 4 + e] = o[g][e];
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx - g * D;
-    float mm = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
-    float ll = 0.f, acc = 0.f;
-    if (mm > -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float f = (s_m[w][g] == -INFINITY) ? 0.f : exp2f(s_m[w][g] - mm);
-        ll += s_l[w][g] * f;
-        acc += s_o[w][g][d] * f;
-      }
-    }
-    const int hq = hk * G + g;
-    if (splits == 1) {
-      out[((size_t)b * Hq + hq) * D + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
-    } else {
-      o_part[(((size_t)b * splits + split) * Hq + hq) * D + d] = ll > 0.f ? acc / ll : 0.f;
-      if (d == 0) lse_part[((size_t)b * splits + split) * Hq + hq] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
-    }
-  }
-}
-
-__global__ void gqa_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part, int splits,
-                                   int Hq, __nv_bfloat16* out) {
-  constexpr int D = 128;
-  const int bh = blockIdx.x;
-  const int b = bh / Hq, h = bh - b * Hq;
-  const int d = threadIdx.x;
-  float mx = -INFINITY;
-  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, lse_part[((size_t)b * splits + s) * Hq + h]);
-  float den = 0.f, acc = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float v = lse_part[((size_t)b * splits + s) * Hq + h];
-    if (v == -INFINITY) continue;
-    const float w = exp2f(v - mx);
-    den += w;
-    acc += w * o_part[(((size_t)b * splits + s) * Hq + h) * D + d];
-  }
-  out[(size_t)bh * D + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
-}
-
 }  // namespace omni
 
 using namespace omni;
@@ -457,25 +309,4 @@ extern "C" int omni_fmha_varlen(const void* q, long long q_rows, int q_ld, int q
   dim3 grid((max_q + FM_BQ - 1) / FM_BQ, B, Hq);
   fmha_varlen_kernel<<<grid, FM_THREADS, FM_SMEM, stream>>>(tq, tk, tk2, tv, p);
   return (int)cudaGetLastError();
-}
-
-extern "C" int omni_gqa_paged_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                     int bt_ld, const int* seq_lens, int B, int Hq, int Hkv, int D, int block_size,
-                                     float scale, int splits, float* o_part, float* lse_part, void* out,
-                                     cudaStream_t stream) {
-  if (B <= 0) return 0;
-  if (D != 128 || Hq % Hkv != 0 || Hq / Hkv > GD_MAXG) return -1;
-  if (splits > 1 && (o_part == nullptr || lse_part == nullptr)) return -2;
-  dim3 grid(Hkv, splits, B);
-  gqa_decode_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
-                                              (const __nv_bfloat16*)v_cache, block_table, bt_ld, seq_lens, block_size,
-                                              Hq, Hkv, scale * 1.4426950408889634f, splits, o_part, lse_part,
-                                              (__nv_bfloat16*)out);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  if (splits > 1) {
-    gqa_combine_kernel<<<B * Hq, 128, 0, stream>>>(o_part, lse_part, splits, Hq, (__nv_bfloat16*)out);
-    e = cudaGetLastError();
-  }
-  return (int)e;
 }

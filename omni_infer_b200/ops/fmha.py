@@ -53,9 +53,13 @@ def gqa_paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale, max_seq_
     Hkv, bs = k_cache.shape[2], k_cache.shape[1]
     assert q.is_contiguous() and q.dtype == torch.bfloat16
     if num_splits <= 0:
+        # three CTAs fit an SM (shared memory and registers): aim for that many everywhere, but keep at least two
+        # 32-key tiles per warp of a CTA so that the merge at the end stays small against the streaming part
         num_splits = 1
-        if max_seq_len is not None and B * Hkv < 296:
-            num_splits = max(1, min(296 // max(B * Hkv, 1), (max_seq_len + 255) // 256, 32))
+        ctas = B * Hkv
+        if max_seq_len is not None and ctas < 444:
+            tiles = (max_seq_len + 31) // 32
+            num_splits = max(1, min((444 + ctas - 1) // ctas, tiles // 8, 32))
     out = torch.empty(B, Hq, D, dtype=q.dtype, device=q.device)
     o_part = lse = None
     if num_splits > 1:

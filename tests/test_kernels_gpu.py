@@ -341,10 +341,12 @@ def test_fmha_gqa_prefill(qlens):
     _close(out, ref, 3e-2, 2e-2)
 
 
-@pytest.mark.parametrize("lens,splits", [([1, 33, 500], 1), ([2000, 64], 4), ([0, 77], 0)])
-def test_gqa_paged_decode(lens, splits):
+@pytest.mark.parametrize("lens,splits,Hq,Hkv,bs", [([1, 33, 500], 1, 32, 4, 16), ([2000, 64], 4, 32, 4, 16), ([0, 77], 0, 32, 4, 16),
+                                                   ([31, 32, 65, 4100], 0, 32, 2, 128),      # 16 query heads per KV head
+                                                   ([300, 129], 3, 8, 4, 128), ([1500], 0, 32, 4, 128)])
+def test_gqa_paged_decode(lens, splits, Hq, Hkv, bs):
     torch.manual_seed(11)
-    B_, Hq, Hkv, D, bs = len(lens), 32, 4, 128, 16
+    B_, D = len(lens), 128
     max_blocks = (max(lens) + bs - 1) // bs + 1
     nb = B_ * max_blocks + 1
     kc = (torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5).bfloat16()
