@@ -142,6 +142,7 @@ struct ExpertTensor { void* ptr; size_t bytes; };
 class MoEWeights {
  public:
   MoEWeights(int layers, int slots_per_rank) : layers_(layers), slots_(slots_per_rank), w_(layers * slots_per_rank) {}
+  ~MoEWeights();
   void add_tensor(int layer, int slot, void* ptr, size_t bytes) { w_[layer * slots_ + slot].push_back({ptr, bytes}); }
   const std::vector<ExpertTensor>& tensors(int layer, int slot) const { return w_[layer * slots_ + slot]; }
   size_t expert_bytes() const;   // bytes of one expert slot (all its tensors); 0 before init
@@ -150,10 +151,30 @@ class MoEWeights {
   int layers() const { return layers_; }
   int slots() const { return slots_; }
 
+  // ---- host replica: every logical expert of every layer once in POSIX shared memory, shared by the ranks of a host.
+  // With it an expert is replaced by a host-to-device copy on the rank that wants it; no other rank takes part.
+  // (The other replacement variant moves the expert between ranks through the Distribution.)
+  // Creates the segment (first caller) or attaches to it; every rank of the host calls this with the same arguments.
+  bool init_shared_memory(const std::string& name, int experts, int ranks_on_host);
+  // Copies the experts this rank holds (as the mapping says) into the replica, then counts itself as done.
+  void replicate_to_shared_memory(const PlacementMapping& mapping);
+  bool replica_enabled() const { return shm_ != nullptr; }
+  bool replica_complete() const;                                  // every rank of the host has replicated
+  bool replica_has(int layer, int expert) const;
+  // host -> device copy of `expert` of `layer` into the tensors of local slot `slot`; false if the replica lacks it
+  bool replace_from_shared_memory(int layer, int expert, int slot) const;
+  void close_shared_memory(bool unlink);
+  size_t replica_bytes() const { return shm_bytes_; }
+
  private:
+  unsigned char* replica_ptr(int layer, int expert) const;
   int layers_, slots_;
   std::vector<std::vector<ExpertTensor>> w_;
   bool initialized_ = false;
+  unsigned char* shm_ = nullptr;
+  size_t shm_bytes_ = 0, shm_data_off_ = 0;
+  int shm_experts_ = 0, shm_ranks_ = 0;
+  std::string shm_name_;
 };
 
 // ------------------------------------------------------------------------------------------------ Instructions
@@ -276,7 +297,7 @@ class PlacementOptimizer {
 };
 
 // ------------------------------------------------------------------------------------------------ Distribution
-struct HandshakeTuple { int t_rank; int position_offset; int expert_id; };
+struct HandshakeTuple { int t_rank; int position_offset; int expert_id; int replica_ok = 0; };
 
 class Distribution {
  public:
@@ -309,6 +330,7 @@ class FakeDistribution : public Distribution {
   void recv_only(int peer, int stage, size_t bytes) override;
   void send_only(int peer, const std::vector<ExpertTensor>& send) override;
   void* staging(int stage) override { return stages_[stage].data(); }
+  int transfers() const { return transfers_; }   // swap / send / receive calls made (tests)
   void barrier() override;
   // fault injection (host side): corrupt the next handshake tuple this rank sends
   void corrupt_next_handshake() { corrupt_ = true; }
@@ -318,6 +340,7 @@ class FakeDistribution : public Distribution {
   int rank_;
   std::vector<std::vector<unsigned char>> stages_;
   bool corrupt_ = false;
+  int transfers_ = 0;
 };
 std::shared_ptr<FakeHub> make_fake_hub(int world);
 
@@ -357,7 +380,7 @@ class CallbackDistribution : public Distribution {
 };
 
 // ------------------------------------------------------------------------------------------------ Manager
-struct PendingApply { int layer, slot, stage, new_expert, global_pos, old_expert; };
+struct PendingApply { int layer, slot, stage, new_expert, global_pos, old_expert; bool from_replica = false; };
 
 class Placement {
  public:

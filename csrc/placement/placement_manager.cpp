@@ -88,15 +88,20 @@ void FakeDistribution::allgather_handshake(const HandshakeTuple& mine, std::vect
   hub_->allgather(rank_, &m, all.data(), sizeof(HandshakeTuple));
 }
 void FakeDistribution::swap(int peer, const std::vector<ExpertTensor>& send, int stage) {
+  ++transfers_;
   hub_->send(rank_, peer, pack_expert(send));
   auto d = hub_->recv(peer, rank_);
   std::memcpy(stages_[stage].data(), d.data(), std::min(d.size(), stages_[stage].size()));
 }
 void FakeDistribution::recv_only(int peer, int stage, size_t) {
+  ++transfers_;
   auto d = hub_->recv(peer, rank_);
   std::memcpy(stages_[stage].data(), d.data(), std::min(d.size(), stages_[stage].size()));
 }
-void FakeDistribution::send_only(int peer, const std::vector<ExpertTensor>& send) { hub_->send(rank_, peer, pack_expert(send)); }
+void FakeDistribution::send_only(int peer, const std::vector<ExpertTensor>& send) {
+  ++transfers_;
+  hub_->send(rank_, peer, pack_expert(send));
+}
 void FakeDistribution::barrier() {
   int64_t x = 0;
   std::vector<int64_t> all(world());
@@ -106,11 +111,11 @@ void FakeDistribution::barrier() {
 CallbackDistribution::CallbackDistribution(DistributionCallbacks cb, size_t expert_bytes)
     : cb_(std::move(cb)), stages_(QUEUE_SIZE, std::vector<unsigned char>(expert_bytes)) {}
 void CallbackDistribution::allgather_handshake(const HandshakeTuple& mine, std::vector<HandshakeTuple>& all) {
-  int64_t s[3] = {mine.t_rank, mine.position_offset, mine.expert_id};
-  std::vector<int64_t> r(3 * (size_t)cb_.world);
-  cb_.allgather_i64(s, r.data(), 3);
+  int64_t s[4] = {mine.t_rank, mine.position_offset, mine.expert_id, mine.replica_ok};
+  std::vector<int64_t> r(4 * (size_t)cb_.world);
+  cb_.allgather_i64(s, r.data(), 4);
   all.resize(cb_.world);
-  for (int i = 0; i < cb_.world; ++i) all[i] = {(int)r[3 * i], (int)r[3 * i + 1], (int)r[3 * i + 2]};
+  for (int i = 0; i < cb_.world; ++i) all[i] = {(int)r[4 * i], (int)r[4 * i + 1], (int)r[4 * i + 2], (int)r[4 * i + 3]};
 }
 CallbackDistribution::CallbackDistribution(DistributionCallbacks cb, size_t expert_bytes, void* device_send_buf,
                                            void* const* device_stages)
@@ -237,13 +242,24 @@ bool Placement::execute(const ChangeInstruction& ins) {
   const int S = mapping_->slots_per_rank();
   const int me = dist_ != nullptr ? dist_->rank() : mapping_->rank();
   // 1. consistency handshake: every rank reports the instruction it is about to execute
-  HandshakeTuple mine{ins.target_rank, ins.target_global_position % S, ins.source_expert_id};
+  // the host replica is used for this instruction only if every rank can (same decision everywhere): the receiving
+  // rank must find the expert in its host's replica
+  const bool need_data = ins.type == OperationType::ADD || ins.type == OperationType::SWAP;
+  int replica_ok = 0;
+  if (need_data && weights_->replica_enabled() && weights_->replica_complete()) {
+    replica_ok = 1;
+    if (me == ins.target_rank && !weights_->replica_has(ins.layer_idx, ins.source_expert_id)) replica_ok = 0;
+    if (ins.type == OperationType::SWAP && me == ins.source_rank && !weights_->replica_has(ins.layer_idx, ins.target_expert_id)) replica_ok = 0;
+  }
+  HandshakeTuple mine{ins.target_rank, ins.target_global_position % S, ins.source_expert_id, replica_ok};
   if (dist_ != nullptr) {
     std::vector<HandshakeTuple> all;
     dist_->allgather_handshake(mine, all);
-    for (const auto& h : all)
+    for (const auto& h : all) {
       if (h.t_rank != mine.t_rank || h.position_offset != mine.position_offset || h.expert_id != mine.expert_id)
         return false;                                     // ranks disagree: skip, nothing was transferred
+      if (!h.replica_ok) replica_ok = 0;
+    }
   }
   // 2. validity against the current mapping (same answer on every rank)
   const int tp = ins.target_global_position, sp = ins.source_global_position;
@@ -268,6 +284,17 @@ bool Placement::execute(const ChangeInstruction& ins) {
     return true;
   }
   const bool i_am_src = me == ins.source_rank, i_am_dst = me == ins.target_rank;
+  if (replica_ok) {
+    // replacement from the host replica: nothing travels between ranks and no staging buffer is taken; the rank
+    // that receives an expert copies it host -> device when the change is applied between two steps
+    if (ins.type == OperationType::SWAP) {
+      pending_.push_back({ins.layer_idx, sp % S, -1, ins.target_expert_id, sp, ins.source_expert_id, i_am_src});
+      pending_.push_back({ins.layer_idx, tp % S, -1, ins.source_expert_id, tp, ins.target_expert_id, i_am_dst});
+    } else {
+      pending_.push_back({ins.layer_idx, tp % S, -1, ins.source_expert_id, tp, ins.target_expert_id, i_am_dst});
+    }
+    return true;
+  }
   int stage = -1;
   if (dist_ != nullptr && (i_am_src || i_am_dst)) {
     stage = next_stage_;
@@ -305,7 +332,9 @@ int Placement::do_placement_optimizer() {
   // a pair by clearing validity through a temporary empty position
   for (const auto& a : todo) {
     const bool local = a.global_pos / S == (dist_ != nullptr ? dist_->rank() : mapping_->rank());
-    if (local && a.stage >= 0) {
+    if (local && a.from_replica) {
+      if (weights_->replace_from_shared_memory(a.layer, a.new_expert, a.slot)) ++replaced;
+    } else if (local && a.stage >= 0) {
       size_t off = 0;
       const unsigned char* src = (const unsigned char*)dist_->staging(a.stage);
       const bool dev = dist_->staging_on_device();
@@ -436,6 +465,16 @@ int omni_pl_placement_last_instructions(void* p, int* out, int max_n) {
   }
   return n;
 }
+
+// host replica of the expert weights (second replacement variant): 0 on success
+int omni_pl_weights_init_shm(void* w, const char* name, int experts, int ranks_on_host) {
+  return ((MoEWeights*)w)->init_shared_memory(name, experts, ranks_on_host) ? 0 : -1;
+}
+void omni_pl_weights_replicate(void* w, void* mapping) { ((MoEWeights*)w)->replicate_to_shared_memory(*(PlacementMapping*)mapping); }
+int omni_pl_weights_replica_complete(void* w) { return ((MoEWeights*)w)->replica_complete() ? 1 : 0; }
+int omni_pl_weights_replica_has(void* w, int layer, int expert) { return ((MoEWeights*)w)->replica_has(layer, expert) ? 1 : 0; }
+unsigned long long omni_pl_weights_replica_bytes(void* w) { return ((MoEWeights*)w)->replica_bytes(); }
+void omni_pl_weights_close_shm(void* w, int unlink) { ((MoEWeights*)w)->close_shared_memory(unlink != 0); }
 
 // moving average of the balancer: returns the number of doubles written (0 when no round has run yet), -1 if `max_n`
 // is too small

@@ -5,6 +5,17 @@
 #include <sstream>
 #include <stdexcept>
 
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cerrno>
+#include <chrono>
+#include <cstring>
+#include <thread>
+
 #include "placement_core.h"
 
 namespace omni_placement {
@@ -239,6 +250,119 @@ size_t MoEWeights::expert_bytes() const {
     return b;
   }
   return 0;
+}
+
+// Layout of the segment: header {magic, ranks_done, expert_bytes, layers, experts}, one "present" byte per
+// (layer, expert), then the experts back to back (each the concatenation of its tensors, 256-byte aligned).
+namespace {
+struct ReplicaHeader {
+  std::atomic<uint32_t> magic;
+  std::atomic<uint32_t> ranks_done;
+  uint64_t expert_bytes;
+  uint32_t layers, experts;
+};
+constexpr uint32_t kReplicaMagic = 0x4f4d4e49u;   // set last by the creator: attachers wait for it
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+}  // namespace
+
+MoEWeights::~MoEWeights() { close_shared_memory(false); }
+
+bool MoEWeights::init_shared_memory(const std::string& name, int experts, int ranks_on_host) {
+  const size_t eb = align_up(expert_bytes(), 256);
+  if (eb == 0 || experts <= 0 || ranks_on_host <= 0 || shm_ != nullptr) return false;
+  const size_t flags_off = align_up(sizeof(ReplicaHeader), 64);
+  const size_t data_off = align_up(flags_off + (size_t)layers_ * experts, 4096);
+  const size_t total = data_off + (size_t)layers_ * experts * eb;
+  bool creator = true;
+  int fd = shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+  if (fd < 0 && errno == EEXIST) { creator = false; fd = shm_open(name.c_str(), O_RDWR, 0600); }
+  if (fd < 0) return false;
+  if (creator && ftruncate(fd, (off_t)total) != 0) { close(fd); shm_unlink(name.c_str()); return false; }
+  if (!creator) {   // the creator may not have sized the segment yet
+    struct stat st;
+    for (int i = 0; i < 2000; ++i) {
+      if (fstat(fd, &st) == 0 && (size_t)st.st_size >= total) break;
+      std::this_thread::sleep_for(std::chrono::milliseconds(5));
+    }
+    if (fstat(fd, &st) != 0 || (size_t)st.st_size < total) { close(fd); return false; }
+  }
+  void* p = mmap(nullptr, total, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) return false;
+  auto* h = reinterpret_cast<ReplicaHeader*>(p);
+  if (creator) {
+    h->ranks_done.store(0);
+    h->expert_bytes = eb;
+    h->layers = (uint32_t)layers_;
+    h->experts = (uint32_t)experts;
+    std::memset((unsigned char*)p + flags_off, 0, (size_t)layers_ * experts);
+    h->magic.store(kReplicaMagic, std::memory_order_release);
+  } else {
+    for (int i = 0; i < 2000 && h->magic.load(std::memory_order_acquire) != kReplicaMagic; ++i)
+      std::this_thread::sleep_for(std::chrono::milliseconds(5));
+    if (h->magic.load(std::memory_order_acquire) != kReplicaMagic || h->expert_bytes != eb || h->layers != (uint32_t)layers_ ||
+        h->experts != (uint32_t)experts) {
+      munmap(p, total);
+      return false;      // a segment of another deployment under the same name
+    }
+  }
+  shm_ = (unsigned char*)p;
+  shm_bytes_ = total;
+  shm_data_off_ = data_off;
+  shm_experts_ = experts;
+  shm_ranks_ = ranks_on_host;
+  shm_name_ = name;
+  return true;
+}
+
+unsigned char* MoEWeights::replica_ptr(int layer, int expert) const {
+  const size_t eb = reinterpret_cast<const ReplicaHeader*>(shm_)->expert_bytes;
+  return shm_ + shm_data_off_ + ((size_t)layer * shm_experts_ + expert) * eb;
+}
+
+void MoEWeights::replicate_to_shared_memory(const PlacementMapping& mapping) {
+  if (shm_ == nullptr) return;
+  unsigned char* flags = shm_ + align_up(sizeof(ReplicaHeader), 64);
+  const int base = mapping.rank() * slots_;
+  for (int l = 0; l < layers_; ++l)
+    for (int s = 0; s < slots_; ++s) {
+      const int e = mapping.expert_at(l, base + s);
+      if (e < 0 || e >= shm_experts_) continue;
+      unsigned char* flag = &flags[(size_t)l * shm_experts_ + e];
+      unsigned char expected = 0;
+      // a replica of it on this host already wrote (or writes) it
+      if (!__atomic_compare_exchange_n(flag, &expected, (unsigned char)1, false, __ATOMIC_ACQ_REL, __ATOMIC_ACQUIRE)) continue;
+      unsigned char* dst = replica_ptr(l, e);
+      size_t off = 0;
+      for (const auto& t : tensors(l, s)) { hooks().memcpy_d2h(dst + off, t.ptr, t.bytes); off += t.bytes; }
+      __atomic_store_n(flag, (unsigned char)2, __ATOMIC_RELEASE);    // 2 = content complete
+    }
+  reinterpret_cast<ReplicaHeader*>(shm_)->ranks_done.fetch_add(1, std::memory_order_acq_rel);
+}
+
+bool MoEWeights::replica_complete() const {
+  return shm_ != nullptr && (int)reinterpret_cast<const ReplicaHeader*>(shm_)->ranks_done.load(std::memory_order_acquire) >= shm_ranks_;
+}
+
+bool MoEWeights::replica_has(int layer, int expert) const {
+  if (shm_ == nullptr || layer < 0 || layer >= layers_ || expert < 0 || expert >= shm_experts_) return false;
+  const unsigned char* flags = shm_ + align_up(sizeof(ReplicaHeader), 64);
+  return __atomic_load_n(&flags[(size_t)layer * shm_experts_ + expert], __ATOMIC_ACQUIRE) == 2;
+}
+
+bool MoEWeights::replace_from_shared_memory(int layer, int expert, int slot) const {
+  if (!replica_has(layer, expert) || slot < 0 || slot >= slots_) return false;
+  const unsigned char* src = replica_ptr(layer, expert);
+  size_t off = 0;
+  for (const auto& t : tensors(layer, slot)) { hooks().memcpy_h2d(t.ptr, src + off, t.bytes); off += t.bytes; }
+  return true;
+}
+
+void MoEWeights::close_shared_memory(bool unlink) {
+  if (shm_ != nullptr) munmap(shm_, shm_bytes_);
+  shm_ = nullptr;
+  if (unlink && !shm_name_.empty()) shm_unlink(shm_name_.c_str());
+  if (unlink) shm_name_.clear();
 }
 
 }  // namespace omni_placement

@@ -8,6 +8,9 @@
 #include <numeric>
 #include <thread>
 
+#include <sys/mman.h>
+#include <unistd.h>
+
 #include "placement_core.h"
 
 using namespace omni_placement;
@@ -141,7 +144,8 @@ static int test_balancers() {
 }
 
 // Two "ranks" as threads: full round (collect -> greedy -> handshake -> swap through staging -> apply).
-static int run_cluster(bool corrupt, int& applied0, int& skipped0, std::vector<float>& w_rank1_slot2, int& sel_e0_rank1) {
+static int run_cluster(bool corrupt, int& applied0, int& skipped0, std::vector<float>& w_rank1_slot2, int& sel_e0_rank1,
+                       const char* replica_name = nullptr, int* transfers = nullptr) {
   const int W = 2, L = 1, E = 4, RED = 1;   // 3 slots per rank
   const int S = E / W + RED;
   auto hub = make_fake_hub(W);
@@ -168,6 +172,19 @@ static int run_cluster(bool corrupt, int& applied0, int& skipped0, std::vector<f
     dists.emplace_back(new FakeDistribution(hub, r, ws[r]->expert_bytes()));
     pls.emplace_back(new Placement(maps[r].get(), ws[r].get(), acts[r].get(), dists[r].get(), 10, 3600.0));
   }
+  if (replica_name != nullptr) {
+    // both ranks live on one host: they share one replica segment and fill it side by side
+    std::thread tr([&] {
+      if (!ws[1]->init_shared_memory(replica_name, E, W)) return;
+      ws[1]->replicate_to_shared_memory(*maps[1]);
+    });
+    if (!ws[0]->init_shared_memory(replica_name, E, W)) { tr.join(); return 2; }
+    ws[0]->replicate_to_shared_memory(*maps[0]);
+    tr.join();
+    if (!ws[0]->replica_complete() || !ws[1]->replica_complete()) return 3;
+    for (int e = 0; e < E; ++e)
+      if (!ws[0]->replica_has(0, e) || !ws[1]->replica_has(0, e)) return 4;
+  }
   if (corrupt) dists[1]->corrupt_next_handshake();
   int done[2] = {0, 0};
   std::thread t([&] { done[1] = pls[1]->run_round(); });
@@ -179,6 +196,8 @@ static int run_cluster(bool corrupt, int& applied0, int& skipped0, std::vector<f
   skipped0 = pls[0]->skipped_instructions();
   w_rank1_slot2.assign(storage[1].begin() + 2 * 8, storage[1].begin() + 3 * 8);
   sel_e0_rank1 = maps[1]->selector(0, 0);
+  if (transfers != nullptr) *transfers = dists[0]->transfers() + dists[1]->transfers();
+  if (replica_name != nullptr) { ws[1]->close_shared_memory(false); ws[0]->close_shared_memory(true); }
   // both ranks hold the same view of the placement
   for (int p = 0; p < W * S; ++p)
     if (maps[0]->expert_at(0, p) != maps[1]->expert_at(0, p)) return 1;
@@ -198,6 +217,56 @@ static int test_manager() {
   // a corrupted handshake tuple makes every rank skip the instruction; nothing moves
   CHECK(run_cluster(true, applied, skipped, w, sel) == 0);
   CHECK(skipped >= 1 && w[0] == -1.f && sel == 0);
+  return 0;
+}
+
+static int test_replica() {
+  set_ut_memcpy_fun();
+  const std::string name = "/omni_test_replica_" + std::to_string((long)getpid());
+  shm_unlink(name.c_str());
+  // the same round as test_manager, with the host replica: the expert arrives by a host -> device copy on the rank
+  // that wants it, and nothing goes through the transport
+  int applied, skipped, sel, transfers = -1;
+  std::vector<float> w;
+  CHECK(run_cluster(false, applied, skipped, w, sel, name.c_str(), &transfers) == 0);
+  CHECK(applied >= 1 && skipped == 0 && transfers == 0);
+  CHECK(w[0] == 0.f && w[3] == 3.f && sel == 5);
+  int t2 = -1;
+  CHECK(run_cluster(false, applied, skipped, w, sel, nullptr, &t2) == 0 && t2 >= 2);   // without it: a send and a receive
+  // segment bookkeeping
+  MoEWeights a(2, 2), b(2, 2), c(2, 2);
+  float buf_a[2][2][4], buf_b[2][2][4];
+  for (int l = 0; l < 2; ++l)
+    for (int s = 0; s < 2; ++s) {
+      for (int k = 0; k < 4; ++k) { buf_a[l][s][k] = float(100 * l + 10 * s + k); buf_b[l][s][k] = -1.f; }
+      a.add_tensor(l, s, buf_a[l][s], sizeof(buf_a[l][s]));
+      b.add_tensor(l, s, buf_b[l][s], sizeof(buf_b[l][s]));
+      c.add_tensor(l, s, buf_b[l][s], sizeof(buf_b[l][s]));
+    }
+  CHECK(!a.replica_enabled() && !a.replica_has(0, 0) && !a.replace_from_shared_memory(0, 0, 0));
+  CHECK(a.init_shared_memory(name, 4, 2));
+  CHECK(!a.init_shared_memory(name, 4, 2));                     // already attached
+  CHECK(a.replica_enabled() && !a.replica_complete() && a.replica_bytes() >= 2 * 4 * 256);
+  CHECK(!c.init_shared_memory(name, 8, 2));                     // same name, another shape: refused
+  CHECK(b.init_shared_memory(name, 4, 2));                      // second rank of the host attaches
+  auto pat = PlacementMapping::base_pattern(2, 2, 4);
+  PlacementMapping m0(pat, 2, 2, 4, 0, 0, 8, nullptr), m1(pat, 2, 2, 4, 1, 0, 8, nullptr);
+  a.replicate_to_shared_memory(m0);                             // rank 0 holds experts 0, 1
+  CHECK(a.replica_has(1, 1) && b.replica_has(0, 0) && !b.replica_has(0, 2) && !b.replica_complete());
+  CHECK(!b.replace_from_shared_memory(0, 2, 0));                // not there yet: nothing is copied
+  CHECK(buf_b[0][0][0] == -1.f);
+  CHECK(b.replace_from_shared_memory(1, 1, 0));                 // expert 1 of layer 1 into rank 1's slot 0
+  CHECK(buf_b[1][0][0] == 110.f && buf_b[1][0][3] == 113.f);
+  b.replicate_to_shared_memory(m1);                             // its own (overwritten) slot goes in as expert 2
+  CHECK(a.replica_complete() && b.replica_complete() && a.replica_has(0, 3));
+  CHECK(!a.replica_has(0, 4) && !a.replica_has(2, 0) && !a.replace_from_shared_memory(0, 0, 5));
+  b.close_shared_memory(false);
+  CHECK(!b.replica_enabled());
+  a.close_shared_memory(true);
+  MoEWeights d(2, 2);
+  for (int l = 0; l < 2; ++l) for (int s = 0; s < 2; ++s) d.add_tensor(l, s, buf_b[l][s], sizeof(buf_b[l][s]));
+  CHECK(d.init_shared_memory(name, 4, 1) && !d.replica_has(0, 0));   // unlinked: a fresh, empty segment
+  d.close_shared_memory(true);
   return 0;
 }
 
@@ -232,6 +301,7 @@ int main() {
   rc |= test_balancers();
   rc |= test_weights_tensor();
   rc |= test_manager();
+  rc |= test_replica();
   printf("%s (%d checks)\n", rc ? "FAILED" : "ALL PASSED", g_checks);
   return rc;
 }

@@ -52,6 +52,12 @@ def lib():
             ("omni_pl_placement_rounds", ci, [vp]),
             ("omni_pl_placement_skipped", ci, [vp]),
             ("omni_pl_placement_last_instructions", ci, [vp, vp, ci]),
+            ("omni_pl_weights_init_shm", ci, [vp, ctypes.c_char_p, ci, ci]),
+            ("omni_pl_weights_replicate", None, [vp, vp]),
+            ("omni_pl_weights_replica_complete", ci, [vp]),
+            ("omni_pl_weights_replica_has", ci, [vp, ci, ci]),
+            ("omni_pl_weights_replica_bytes", ull, [vp]),
+            ("omni_pl_weights_close_shm", None, [vp, ci]),
             ("omni_pl_placement_get_ema", ci, [vp, vp, ci]),
             ("omni_pl_placement_set_ema", ci, [vp, vp, ci]),
             ("omni_pl_static_placement", ci, [vp, ci, ci, ci, ci, ci, vp]),

@@ -53,7 +53,7 @@ class OmniPlanner(metaclass=_Singleton):
     def __init__(self, num_moe_layers: int, num_experts: int, device="cpu", pattern: Optional[np.ndarray] = None,
                  max_redundant_per_rank: int = 0, max_redundant_per_expert: int = 10, enable_dynamic: bool = False,
                  period_s: float = 60.0, apply_interval: int = 16, enable_dump: bool = False, dump_dir: str = "",
-                 ranks_per_host: int = 8):
+                 ranks_per_host: int = 8, host_replica: str = ""):
         ps = get_parallel_state()
         self.world, self.rank = ps.ep_size, ps.ep_rank
         self.device = torch.device(device)
@@ -62,6 +62,9 @@ class OmniPlanner(metaclass=_Singleton):
         self.max_redundant_per_expert = max_redundant_per_expert
         self.enable_dynamic, self.period_s, self.apply_interval = enable_dynamic, period_s, apply_interval
         self.enable_dump, self.dump_dir = enable_dump, dump_dir
+        # name of a POSIX shared-memory segment that holds every expert once per host (the reference's second
+        # replacement variant): an expert is then replaced by a host -> device copy on the rank that wants it
+        self.host_replica, self.ranks_per_host = host_replica, ranks_per_host
         self.mapping = ExpertMapping(pattern, self.world, self.rank, num_moe_layers, num_experts, max_redundant_per_rank,
                                      ranks_per_host, device)
         self.slots_per_rank = self.mapping.slots_per_rank
@@ -94,7 +97,8 @@ class OmniPlanner(metaclass=_Singleton):
                    max_redundant_per_expert=int(cfg.get("max_redundant_per_expert", 10)),
                    enable_dynamic=bool(cfg.get("enable_dynamic", False)), period_s=float(cfg.get("period_s", 60.0)),
                    apply_interval=int(cfg.get("apply_interval", 16)), enable_dump=bool(cfg.get("enable_dump", False)),
-                   dump_dir=cfg.get("dump_dir", ""), _new=True)
+                   dump_dir=cfg.get("dump_dir", ""), ranks_per_host=int(cfg.get("ranks_per_host", 8)),
+                   host_replica=str(cfg.get("host_replica", "")), _new=True)
 
     def _install_copy_hooks(self) -> None:
         L = nat.lib()
@@ -171,6 +175,13 @@ class OmniPlanner(metaclass=_Singleton):
                     L.omni_pl_weights_add(self._weights, mod.moe_index, s, ctypes.c_void_p(sl.data_ptr()),
                                           sl.numel() * sl.element_size())
         L.omni_pl_weights_set_initialized(self._weights)
+        if self.host_replica:
+            on_host = min(self.ranks_per_host, self.world)
+            if L.omni_pl_weights_init_shm(self._weights, self.host_replica.encode(), self.experts, on_host) != 0:
+                raise RuntimeError(f"cannot create or attach the expert replica {self.host_replica!r}")
+            L.omni_pl_weights_replicate(self._weights, self.mapping.handle)
+            logger.info("expert replica %s: %.1f MiB of host memory", self.host_replica,
+                        L.omni_pl_weights_replica_bytes(self._weights) / 2 ** 20)
         self._act = L.omni_pl_activation_create(ctypes.c_void_p(self.local_counts.data_ptr()), self.layers,
                                                 self.slots_per_rank, self.world, self.rank, 8)
         if self.enable_dynamic:
@@ -385,6 +396,8 @@ class OmniPlanner(metaclass=_Singleton):
             L.omni_pl_activation_destroy(self._act)
             self._act = None
         if self._weights:
+            if self.host_replica:
+                L.omni_pl_weights_close_shm(self._weights, 1 if self.rank % max(self.ranks_per_host, 1) == 0 else 0)
             L.omni_pl_weights_destroy(self._weights)
             self._weights = None
         self.mapping.close()

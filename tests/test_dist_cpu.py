@@ -217,14 +217,15 @@ def test_tensor_parallel_attention_matches_single_rank():
 
 
 # ---------------------------------------------------------------------------------------------- placement across ranks
-def _placement_round(rank, world):
+def _placement_round(rank, world, host_replica=""):
     from omni_infer_b200.accelerators.placement import OmniPlanner
     from omni_infer_b200.layers.moe import MoELayer
     from omni_infer_b200.models.config import tiny_deepseek_v3
     from omni_infer_b200.parallel import destroy_distributed, init_distributed
     init_distributed(backend="gloo")
     cfg = tiny_deepseek_v3()
-    pl = OmniPlanner(num_moe_layers=1, num_experts=8, max_redundant_per_rank=1, enable_dynamic=False, _new=True)
+    pl = OmniPlanner(num_moe_layers=1, num_experts=8, max_redundant_per_rank=1, enable_dynamic=False, host_replica=host_replica,
+                     _new=True)
     layer = MoELayer(cfg, 1, dtype=torch.float32, planner=pl)
     model = torch.nn.ModuleList([layer])
     with torch.no_grad():
@@ -237,6 +238,9 @@ def _placement_round(rank, world):
     pl.sent_counts[0, 0] = 5000 if rank == 0 else 4000
     pl.sent_counts[0, 1] = 10
     pl.sent_counts[0, 5] = 10
+    if host_replica:
+        import torch.distributed as dist
+        dist.barrier()                                   # every rank of the host has filled its part of the replica
     n = pl.run_round()
     applied = pl.apply_pending()
     ins = pl.last_instructions()
@@ -248,6 +252,10 @@ def _placement_round(rank, world):
     return {"n": n, "applied": applied, "ins": ins, "sel": sel, "spare": spare, "place": place}
 
 
+def _placement_round_replica(rank, world):
+    return _placement_round(rank, world, host_replica=f"/omni_pytest_replica_{os.getppid()}")
+
+
 def test_dynamic_placement_round_moves_a_hot_expert():
     out = _spawn(_placement_round, 2)
     r0, r1 = out[0], out[1]
@@ -256,6 +264,16 @@ def test_dynamic_placement_round_moves_a_hot_expert():
     assert r1["place"][9] == 0                           # replica landed in rank 1's redundant slot (position 5+4)
     assert r1["spare"] == 0.0 and r1["applied"] >= 1     # with expert 0's weights
     assert r1["sel"][0] == 9 and r0["sel"][0] == 0       # every rank routes expert 0 to its own replica
+
+
+def test_placement_round_from_the_host_replica():
+    """Same round with the experts replicated once per host in shared memory: the rank that wants the hot expert copies
+    it from there; the result is the same placement, weights and selectors as with the transfer between ranks."""
+    out = _spawn(_placement_round_replica, 2)
+    r0, r1 = out[0], out[1]
+    assert r0["place"] == r1["place"] and r1["place"][9] == 0
+    assert r1["spare"] == 0.0 and r1["applied"] >= 1
+    assert r1["sel"][0] == 9 and r0["sel"][0] == 0
 
 
 # ---------------------------------------------------------------------------------------------- failure detection
