@@ -3,6 +3,9 @@
 #include <cstring>
 
 #include "json_min.h"
+#include <cmath>
+#include <cstdlib>
+
 #include "lb.h"
 
 using namespace omni_proxy;
@@ -132,8 +135,125 @@ static int test_policies() {
   return 0;
 }
 
+static int test_policy_edges() {
+  {  // accounting never goes below zero, also when a ticket is given back twice or with stale counters
+    LbParams p; p.policy = "pd_score_balance_prefill";
+    LoadBalancer lb(fresh(), 2, p);
+    Ticket a = lb.get_peer(500, 0);
+    lb.free_peer(a, false, 0);
+    lb.free_peer(a, false, 0);
+    CHECK(lb.peer(a.peer).active_requests == 0 && lb.peer(a.peer).total_request_length == 0 && lb.peer(a.peer).total_time_cost == 0);
+    Ticket none;
+    lb.free_peer(none, false, 0);                       // a ticket that never got a peer: ignored
+    lb.on_decoded_tokens(none, 10);
+    lb.on_token_counts(none, 1, 1);
+    CHECK(lb.peer(0).total_decode_num == 0 && lb.peer(1).total_tokens == 0);
+  }
+  {  // stream counters only grow: a chunk that reports less than before changes nothing
+    LbParams p; p.policy = "pd_score_balance_decode";
+    LoadBalancer lb(fresh(), 1, p);
+    Ticket t = lb.get_peer(10, 0);
+    lb.on_decoded_tokens(t, 30);
+    lb.on_decoded_tokens(t, 20);
+    lb.on_decoded_tokens(t, 45);
+    CHECK(lb.peer(0).total_decode_num == 45 && t.decoded == 45);
+    lb.on_token_counts(t, 100, 5);
+    lb.on_token_counts(t, 100, 3);
+    CHECK(lb.peer(0).total_tokens == 105);
+    lb.free_peer(t, false, 0);
+    CHECK(lb.peer(0).total_decode_num == 0 && lb.peer(0).total_tokens == 0 && lb.peer(0).served == 1);
+  }
+  {  // pd_score decode: a peer over its request limit is passed over; when every peer is over it, the least loaded one serves
+    LbParams p; p.policy = "pd_score_balance_decode"; p.decode_req_limit = 1;
+    LoadBalancer lb(fresh(), 2, p);
+    Ticket a = lb.get_peer(10, 0), b = lb.get_peer(10, 0), c = lb.get_peer(10, 0), d = lb.get_peer(10, 0);
+    CHECK(a.peer == 0 && b.peer == 0);                  // up to limit + 1 requests on the first peer with equal load
+    CHECK(c.peer == 1 && d.peer == 1);                  // then it is passed over
+    lb.on_decoded_tokens(c, 1000);                      // peer 1 is now far heavier
+    Ticket e = lb.get_peer(10, 0);                      // both over the limit: the lighter one serves
+    CHECK(e.peer == 0);
+  }
+  {  // the list of requests still in prefill is bounded; finishing an unknown length is harmless
+    LbParams p; p.policy = "pd_score_balance_decode";
+    LbShared* shm = fresh();
+    LoadBalancer lb(shm, 2, p);
+    for (int i = 0; i < MAX_ACTIVE_PREFILL + 10; ++i) lb.prefill_started(100 + i);
+    CHECK(shm->n_active_prefill == MAX_ACTIVE_PREFILL);
+    lb.prefill_finished(99999);
+    CHECK(shm->n_active_prefill == MAX_ACTIVE_PREFILL);
+    lb.prefill_finished(100);
+    CHECK(shm->n_active_prefill == MAX_ACTIVE_PREFILL - 1);
+  }
+  {  // greedy_timeout: a peer is busy until now + cost; time passing frees it
+    LbParams p; p.policy = "greedy_timeout"; p.warmup = 5; p.exponent = 1.0;
+    LoadBalancer lb(fresh(), 2, p);
+    Ticket a = lb.get_peer(1000, 10.0);                 // busy until 10 + 1.005 s
+    CHECK(std::fabs(a.cost - 1.005) < 1e-9 && std::fabs(lb.peer(a.peer).available_time - 11.005) < 1e-9);
+    Ticket b = lb.get_peer(1000, 10.0);
+    CHECK(b.peer != a.peer);
+    Ticket c = lb.get_peer(10, 20.0);                   // both free again by now
+    CHECK(std::fabs(lb.peer(c.peer).available_time - 20.015) < 1e-9);
+  }
+  {  // length_balance: the accumulated score decays with every request a peer takes
+    LbParams p; p.policy = "length_balance"; p.decay_factor = 0.5; p.req_len_weight = 1.0;
+    LoadBalancer lb(fresh(), 1, p);
+    Ticket a = lb.get_peer(2048, 0);
+    CHECK(std::fabs(lb.peer(0).length_score - 2.0) < 1e-12);
+    lb.free_peer(a, false, 0);
+    Ticket b = lb.get_peer(1024, 0);
+    CHECK(std::fabs(lb.peer(0).length_score - (2.0 * 0.5 + 1.0)) < 1e-12);
+    lb.free_peer(b, false, 0);
+  }
+  {  // least_total_load: (length sum + this request) * (ceil(requests / batch) + 1) / 2
+    LbParams p; p.policy = "least_total_load"; p.batch_size = 2;
+    LoadBalancer lb(fresh(), 2, p);
+    Ticket a = lb.get_peer(100, 0), b = lb.get_peer(300, 0);        // peer loads 100 / 300, one request each
+    Ticket c = lb.get_peer(50, 0);                                   // (100+50)*(1+1)/2 = 150 < (300+50)*(1+1)/2
+    CHECK(c.peer == a.peer);
+    Ticket d = lb.get_peer(50, 0);                                   // a's peer: (150+50)*(ceil(3/2)+1)/2 = 300; b's: 350*(1+1)/2 = 350
+    CHECK(d.peer == a.peer);
+    Ticket e = lb.get_peer(50, 0);                                   // a's peer: (200+50)*(2+1)/2 = 375; b's: 350
+    CHECK(e.peer == b.peer);
+  }
+  {  // failures: ejected after max_fails consecutive failures, a success in between resets the count
+    LbParams p; p.policy = "round_robin"; p.max_fails = 2; p.fail_timeout_s = 10;
+    LoadBalancer lb(fresh(), 2, p);
+    Ticket a = lb.get_peer(1, 0);
+    lb.free_peer(a, true, 0);
+    CHECK(lb.is_up(a.peer, 1.0) && lb.peer(a.peer).failures == 1 && lb.peer(a.peer).served == 0);
+    Ticket ok = lb.get_peer(1, 0);
+    while (ok.peer != a.peer) { lb.free_peer(ok, false, 0); ok = lb.get_peer(1, 0); }
+    lb.free_peer(ok, false, 0);
+    CHECK(lb.peer(a.peer).failures == 0);
+    lb.mark_failed(a.peer, 5.0);
+    lb.mark_failed(a.peer, 5.0);
+    CHECK(!lb.is_up(a.peer, 6.0) && lb.is_up(a.peer, 15.1));
+    // everything down: requests are still handed out rather than refused
+    lb.mark_failed(1 - a.peer, 5.0);
+    lb.mark_failed(1 - a.peer, 5.0);
+    Ticket t = lb.get_peer(1, 6.0);
+    CHECK(t.peer == 0 || t.peer == 1);
+  }
+  {  // a second balancer object on the same state (another worker process) sees and continues it
+    LbParams p; p.policy = "weighted_least_active";
+    LbShared* shm = fresh();
+    LoadBalancer one(shm, 3, p), two(shm, 99, p);        // the second size is ignored: the state is already sized
+    CHECK(two.n_peers() == 3);
+    Ticket a = one.get_peer(1, 0), b = two.get_peer(1, 0), c = one.get_peer(1, 0);
+    CHECK(a.peer != b.peer && b.peer != c.peer && a.peer != c.peer);
+    two.free_peer(a, false, 0);
+    CHECK(one.peer(a.peer).active_requests == 0 && one.peer(a.peer).served == 1);
+  }
+  {  // more peers than the state can hold are cut off, not overrun
+    LbParams p;
+    LoadBalancer lb(fresh(), MAX_PEERS + 50, p);
+    CHECK(lb.n_peers() == MAX_PEERS);
+  }
+  return 0;
+}
+
 int main() {
-  int rc = test_json() | test_policies();
+  int rc = test_json() | test_policies() | test_policy_edges();
   printf("%s (%d checks)\n", rc ? "FAILED" : "ALL PASSED", g_checks);
   return rc;
 }
