@@ -73,7 +73,7 @@ def main():
     ap.add_argument("--max-decode-batch", type=int, default=128)
     ap.add_argument("--start-timeout", type=float, default=600.0)
     ap.add_argument("--timeline", action="store_true")
-    ap.add_argument("--logdir", default="gpurun_out/config4")
+    ap.add_argument("--logdir", default="config4_logs")
     a = ap.parse_args()
 
     model = {"tiny": "tiny-deepseek-v3", "small": "small-deepseek", "qwen3-30b-a3b": "qwen3-30b-a3b"}[a.config]
