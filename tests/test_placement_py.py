@@ -207,3 +207,67 @@ def test_pattern_tool_pipeline_and_incremental_plan(tmp_path, capsys):
     bad[0, 0] = 1
     with pytest.raises(RuntimeError):
         pattern_tool.plan_instructions(bad, pos_counts, world, world * per)
+
+
+def test_token_level_optimizers():
+    """The six routing post-processors of the reference's ``optim`` package and their loader."""
+    from omni_infer_b200.accelerators.placement import optim
+
+    # 4 ranks x 3 slots, 8 experts; expert 0 also on rank 2, expert 5 also on rank 0
+    pat = base_pattern(4, 1, 8)
+    pat[2, 0, 0] = 1
+    pat[0, 0, 5] = 1
+    m = ExpertMapping(pat, world=4, rank=0, layers=1, experts=8, redundant_per_rank=1)
+    place = m.placement()[0].tolist()
+    pos0 = [p for p, e in enumerate(place) if e == 0]
+    pos5 = [p for p, e in enumerate(place) if e == 5]
+    assert len(pos0) == 2 and len(pos5) == 2
+    ids = torch.tensor([[0, 5], [0, 3], [5, 0], [0, 7]])
+    w = torch.full((4, 2), 0.5)
+
+    # HEAT: own rank first, then own host, then the rank's offset
+    for rank, want0 in ((0, pos0[0]), (2, pos0[1]), (3, pos0[1]), (1, pos0[0])):     # hosts of two ranks: {0,1}, {2,3}
+        h = optim.HEATExpertsBalancer(m, rank=rank, ranks_per_host=2)
+        _, out, _ = h.optimize(0, None, ids, w)
+        assert out[0, 0].item() == want0, (rank, out.tolist())
+        assert place[out[1, 1].item()] == 3                 # single-replica experts go to their only position
+    far = optim.HEATExpertsBalancer(m, rank=1, ranks_per_host=1)     # no replica on its rank or host: offset 1 % 2
+    assert far.optimize(0, None, ids, w)[1][0, 0].item() == pos0[1]
+    assert optim.HEATExpertsBalancer(m, rank=1, ranks_per_host=1, global_offset=True).optimize(0, None, ids, w)[1][0, 0].item() == pos0[0]
+
+    # Redundant2: replicas alternate with the token index
+    r2 = optim.Redundant2ExpertsBalancer(m, rank=0)
+    _, out, _ = r2.optimize(0, None, ids, w)
+    assert [place[p] for p in out.flatten().tolist()] == ids.flatten().tolist()      # always a position of the same expert
+    assert out[0, 0].item() != out[1, 0].item()             # tokens 0 and 1 hit different replicas of expert 0
+
+    # ResDis: even deal without loads, all to the replica with room when the other rank is full
+    rd = optim.ResDisExpertsBalancer(m)
+    big = torch.zeros(40, 1, dtype=torch.long)
+    _, out, _ = rd.optimize(0, None, big, torch.ones(40, 1))
+    assert sorted(out.flatten().bincount(minlength=12)[pos0].tolist()) == [20, 20]
+    loads = torch.tensor([1000.0, 10.0, 10.0, 10.0])         # rank 0 is far above the mean: no room there
+    _, out, _ = rd.optimize(0, None, big, torch.ones(40, 1), cluster_status=loads)
+    assert out.flatten().bincount(minlength=12)[pos0[1]].item() == 40
+    capped = optim.ResDisExpertsBalancer(m, max_count=10).optimize(0, None, big, torch.ones(40, 1))[1]
+    assert capped.flatten().bincount(minlength=12)[pos0[0]].item() == 35     # 5 + the 30 beyond the cap
+    rnd = optim.ResDisExpertsBalancer(m, random=True, seed=1).optimize(0, None, big, torch.ones(40, 1))[1]
+    assert set(rnd.flatten().tolist()) == set(pos0)
+
+    # loader: the reference's "<module>.<Class>" names, keyword arguments, unknown names refused
+    opts = optim.create_optimizers([{"ada_router_optimizer.AdaRouter": {"threshold": 0.5}},
+                                    {"token_balance_optimizer.TokenBalance": {"capacity_factor": 1.0}},
+                                    {"heat_optimizer.HEAT_ExpertsBalancer": {"ranks_per_host": 2}},
+                                    {"ResDis_ExpertsBalancer": {"max_count": 16}}], mapping=m, rank=2, num_experts=8)
+    assert [type(o).__name__ for o in opts] == ["AdaRouter", "TokenBalance", "HEATExpertsBalancer", "ResDisExpertsBalancer"]
+    assert opts[2].rank == 2 and opts[1].E == 8
+    w_in = torch.tensor([[0.9, 0.1], [0.5, 0.5], [0.6, 0.4], [0.8, 0.3]])
+    _, i2, w2 = opts[0].optimize(0, None, ids, w_in)
+    assert i2[0, 1].item() == -1 and abs(float(w2[0].sum()) - 1.0) < 1e-6     # AdaRouter dropped the weak choice, mass kept
+    assert i2[1].tolist() == ids[1].tolist() and i2[3, 1].item() == -1
+    _, i3, w3 = opts[1].optimize(0, None, i2, w2)                               # capacity 1 pair per expert at this size
+    kept = i3[i3 >= 0]
+    assert kept.bincount(minlength=8).max().item() == 1 and float(w3[i3 < 0].abs().sum()) == 0.0
+    with pytest.raises(ValueError):
+        optim.create_optimizers([{"NoSuchOptimizer": {}}])
+    m.close()
