@@ -85,7 +85,8 @@ def rope_cos_sin_table(rot_dim, max_pos, base=10000.0, scaling=None, device="cpu
     """[max_pos, rot_dim] fp32 = cos(rot_dim/2) | sin(rot_dim/2).  ``scaling`` may describe YaRN
     (keys factor, original_max_position_embeddings, beta_fast, beta_slow, mscale, mscale_all_dim):
     inverse frequencies are blended and cos/sin are multiplied by the YaRN attention factor
-    (omni/models/common/layers/rotary_embedding.py:375-520)."""
+    (omni/models/common/layers/rotary_embedding.py:375-520); ``type`` linear, llama3 and dynamic are the other
+    variants of that file (:312, :352)."""
     import math
 
     half = rot_dim // 2
@@ -113,6 +114,24 @@ def rope_cos_sin_table(rot_dim, max_pos, base=10000.0, scaling=None, device="cpu
         mscale = ys(factor, scaling.get("mscale", 1.0)) / ys(factor, scaling.get("mscale_all_dim", 0.0))
     elif scaling and scaling.get("type", scaling.get("rope_type")) == "linear":
         inv_freq = inv_freq / float(scaling["factor"])
+    elif scaling and scaling.get("type", scaling.get("rope_type")) == "llama3":
+        # Llama-3.1 extension (reference: rotary_embedding.py:352-373): wavelengths longer than the original context
+        # divided by low_freq_factor are slowed down by `factor`, those shorter than it divided by high_freq_factor
+        # are kept, the band between is interpolated
+        factor = float(scaling.get("factor", 8.0))
+        lo_f, hi_f = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        orig = float(scaling.get("original_max_position_embeddings", 8192))
+        wavelen = 2 * math.pi / inv_freq
+        smooth = ((orig / wavelen - lo_f) / (hi_f - lo_f)).clamp(0, 1)
+        inv_freq = torch.where(wavelen > orig / lo_f, inv_freq / factor,
+                               torch.where(wavelen < orig / hi_f, inv_freq, (1 - smooth) * inv_freq / factor + smooth * inv_freq))
+    elif scaling and scaling.get("type", scaling.get("rope_type")) == "dynamic":
+        # dynamic NTK: the base grows with the table length beyond the original context
+        factor = float(scaling.get("factor", 1.0))
+        orig = int(scaling.get("original_max_position_embeddings", max_pos))
+        if max_pos > orig:
+            nb = base * ((factor * max_pos / orig) - (factor - 1)) ** (rot_dim / (rot_dim - 2))
+            inv_freq = 1.0 / (nb ** (torch.arange(0, half, dtype=torch.float64) * 2 / rot_dim))
     t = torch.arange(max_pos, dtype=torch.float64)
     ang = torch.outer(t, inv_freq)
     return torch.cat([ang.cos() * mscale, ang.sin() * mscale], dim=-1).float().to(device)

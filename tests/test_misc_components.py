@@ -243,3 +243,31 @@ def test_engine_restart_reuses_block_count_placement_and_load_history(tmp_path):
     cold = make(block_size=32, num_kv_blocks=24)     # another block size: the saved state does not apply
     assert cold.kv.num_blocks == 24 and cold.state.get_array("placement_ema") is None
     OmniPlanner.cleanup()
+
+
+def test_rope_scaling_variants():
+    import math
+    from omni_infer_b200.ops.basic import rope_cos_sin_table
+    D, N, base = 64, 64, 10000.0
+    plain = rope_cos_sin_table(D, N, base)
+    inv = 1.0 / (base ** (torch.arange(0, D // 2, dtype=torch.float64) * 2 / D))
+    assert torch.allclose(plain[:, :D // 2], torch.outer(torch.arange(N, dtype=torch.float64), inv).cos().float(), atol=1e-6)
+    lin = rope_cos_sin_table(D, N, base, {"type": "linear", "factor": 4.0})
+    assert torch.allclose(lin[4 * 3], plain[3], atol=1e-5)                       # position 12 of the stretched table = position 3
+    l3 = rope_cos_sin_table(D, N, base, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                         "original_max_position_embeddings": 64})
+    wavelen = 2 * math.pi / inv
+    fast, slow = int((wavelen < 64 / 4.0).nonzero().max()), int((wavelen > 64 / 1.0).nonzero().min())
+    assert torch.allclose(l3[:, fast], plain[:, fast], atol=1e-6)               # short wavelengths untouched
+    assert torch.allclose(l3[8 * 5, slow], plain[5, slow], atol=1e-5)           # long ones slowed down by the factor
+    mid = (fast + slow) // 2
+    ang_mid = torch.acos(l3[1, mid].double().clamp(-1, 1))
+    assert inv[mid] / 8.0 - 1e-9 <= ang_mid <= inv[mid] + 1e-9                  # the band between is interpolated
+    dyn_short = rope_cos_sin_table(D, 32, base, {"type": "dynamic", "factor": 2.0, "original_max_position_embeddings": 32})
+    assert torch.equal(dyn_short, rope_cos_sin_table(D, 32, base))              # within the original context: unchanged
+    dyn_long = rope_cos_sin_table(D, 128, base, {"type": "dynamic", "factor": 2.0, "original_max_position_embeddings": 32})
+    nb = base * ((2.0 * 128 / 32) - 1.0) ** (D / (D - 2))
+    assert torch.allclose(dyn_long[7, 1], torch.tensor(math.cos(7 / nb ** (2 / D)), dtype=torch.float32), atol=1e-6)
+    yarn = rope_cos_sin_table(D, N, base, {"type": "yarn", "factor": 4.0, "original_max_position_embeddings": 16, "mscale": 1.0,
+                                           "mscale_all_dim": 0.0})
+    assert float(yarn[0, 0]) == pytest.approx(0.1 * math.log(4.0) + 1.0, rel=1e-6)    # cos(0) times the attention factor
