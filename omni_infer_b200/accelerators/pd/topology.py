@@ -74,3 +74,63 @@ def merge(*tops: Topology) -> Topology:
             seen.add(key)
             out.instances.append(Instance(**{**asdict(i), "cluster_id": len(out.instances)}))
     return out
+
+
+def main(argv=None) -> int:
+    """Command line of the tool, with the reference's option names (tools/scripts/pd_ranktable_tools.py:43-70):
+
+        python -m omni_infer_b200.accelerators.pd.topology --mode gen --prefill-server-list 0,1 2,3 \
+               --decode-server-list 4,5,6,7 --save-dir tables/
+        python -m omni_infer_b200.accelerators.pd.topology --mode merge --global-ranktable-list a.json b.json --save-dir tables/
+
+    ``gen`` takes one GPU list per instance (all prefill instances must have the same size, and all decode instances:
+    they are the tensor-parallel width) and writes ``global_topology.json`` plus one ``local_<name>.json`` per instance;
+    ``merge`` (also ``merge-local`` / ``merge-all``) concatenates tables into one."""
+    import argparse
+    import os
+
+    ap = argparse.ArgumentParser(description=main.__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--mode", default="gen", choices=["gen", "merge", "merge-local", "merge-all"])
+    ap.add_argument("--api-server", action="store_true", help="accepted for compatibility: every instance has an API server here")
+    ap.add_argument("--prefill-server-list", nargs="*", default=[])
+    ap.add_argument("--decode-server-list", nargs="*", default=[])
+    ap.add_argument("--save-dir", default="./")
+    ap.add_argument("--global-ranktable-list", nargs="*", default=[])
+    ap.add_argument("--local-ranktable-list", nargs="*", default=[])
+    ap.add_argument("--base-api-port", type=int, default=9000)
+    ap.add_argument("--base-control-port", type=int, default=5568)
+    ap.add_argument("--host", default="127.0.0.1")
+    a = ap.parse_args(argv)
+    os.makedirs(a.save_dir, exist_ok=True)
+    if a.mode == "gen":
+        pre = [[int(x) for x in s.split(",") if x != ""] for s in a.prefill_server_list]
+        dec = [[int(x) for x in s.split(",") if x != ""] for s in a.decode_server_list]
+        for name, group in (("prefill", pre), ("decode", dec)):
+            if len({len(g) for g in group}) > 1:
+                raise SystemExit(f"every {name} instance must span the same number of GPUs (its tensor-parallel size)")
+        used = [g for grp in pre + dec for g in grp]
+        if len(used) != len(set(used)):
+            raise SystemExit("a GPU is listed for more than one instance")
+        t = Topology()
+        for i, g in enumerate(pre):
+            t.instances.append(Instance(f"prefill-{i}", "prefill", g, a.base_api_port + i, a.base_control_port + i, a.host, cluster_id=i))
+        for j, g in enumerate(dec):
+            t.instances.append(Instance(f"decode-{j}", "decode", g, a.base_api_port + 100 + j, a.base_control_port + 100 + j, a.host,
+                                        cluster_id=len(pre) + j))
+        t.save(os.path.join(a.save_dir, "global_topology.json"))
+        for inst in t.instances:
+            Topology([inst]).save(os.path.join(a.save_dir, f"local_{inst.name}.json"))
+        print(json.dumps({"instances": len(t.instances), "saved": os.path.join(a.save_dir, "global_topology.json")}))
+        return 0
+    files = list(a.global_ranktable_list) + list(a.local_ranktable_list)
+    if not files:
+        raise SystemExit("merge needs --global-ranktable-list and / or --local-ranktable-list")
+    merged = merge(*[Topology.load(f) for f in files])
+    out = os.path.join(a.save_dir, "global_topology.json")
+    merged.save(out)
+    print(json.dumps({"instances": len(merged.instances), "saved": out}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

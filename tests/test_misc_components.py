@@ -137,6 +137,19 @@ def test_topology_tool(tmp_path):
     assert len(T.merge(a, b).instances) == 2
     with pytest.raises(ValueError):
         T.merge(a, a)
+    # command line with the reference tool's option names
+    d1, d2 = tmp_path / "t1", tmp_path / "t2"
+    assert T.main(["--mode", "gen", "--prefill-server-list", "0,1", "2,3", "--decode-server-list", "4,5,6,7", "--save-dir", str(d1)]) == 0
+    g = T.Topology.load(str(d1 / "global_topology.json"))
+    assert [i.gpus for i in g.instances] == [[0, 1], [2, 3], [4, 5, 6, 7]] and g.instances[2].role == "decode"
+    assert (d1 / "local_prefill-1.json").exists()
+    assert T.main(["--mode", "merge", "--local-ranktable-list", str(d1 / "local_prefill-0.json"), str(d1 / "local_decode-0.json"),
+                   "--save-dir", str(d2)]) == 0
+    assert [i.name for i in T.Topology.load(str(d2 / "global_topology.json")).instances] == ["prefill-0", "decode-0"]
+    with pytest.raises(SystemExit):
+        T.main(["--mode", "gen", "--prefill-server-list", "0,1", "2", "--save-dir", str(d1)])      # unequal TP sizes
+    with pytest.raises(SystemExit):
+        T.main(["--mode", "gen", "--prefill-server-list", "0", "--decode-server-list", "0", "--save-dir", str(d1)])   # GPU used twice
 
 
 def test_kv_manager_failed_allocation_hands_prefix_references_back():
