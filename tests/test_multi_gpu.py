@@ -175,20 +175,18 @@ def test_ep2_fused_and_nccl_match_single_rank():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 or 8 GPUs")
-def test_ep_and_tp_on_all_gpus_match_the_oracle():
-    """The same four prompts on 4 or 8 ranks (experts sharded over all of them; attention data parallel, then tensor
-    parallel): every token checked against the fp32 oracle, first tokens equal to the one-GPU run's."""
+@pytest.mark.parametrize("case,env,port", [("ep-fused", {"EP_BACKEND": "fused"}, 29631), ("ep-nccl", {"EP_BACKEND": "nccl"}, 29632),
+                                           ("tp-fused", {"ATTN_TP": "1", "TP_BACKEND": "fused"}, 29633),
+                                           ("ep-fused-mtp", {"MTP": "1", "EP_BACKEND": "fused"}, 29634)])
+def test_all_gpus_match_the_oracle(case, env, port):
+    """The same four prompts on 4 or 8 ranks (experts sharded over all of them; attention data parallel or tensor
+    parallel; with and without the MTP drafter): every token checked against the fp32 oracle, first tokens equal to the
+    one-GPU run's."""
     world = 8 if torch.cuda.device_count() >= 8 else 4
-    single = _run(1, {}, 0)
-    ep = _run(world, {"EP_BACKEND": "fused"}, 29631)
-    _near_oracle(ep, what=f"EP{world} fused")
-    assert [o[0] for o in ep] == [o[0] for o in single]
-    nccl = _run(world, {"EP_BACKEND": "nccl"}, 29632)
-    _near_oracle(nccl, what=f"EP{world} NCCL")
-    tp = _run(world, {"ATTN_TP": "1", "TP_BACKEND": "fused"}, 29633)
-    _near_oracle(tp, what=f"TP{world} attention + EP{world}")
-    mtp = _run(world, {"MTP": "1", "EP_BACKEND": "fused"}, 29634)
-    _near_oracle(mtp, what=f"EP{world} fused with MTP")
+    outs = _run(world, env, port)
+    _near_oracle(outs, what=f"{case} on {world} GPUs")
+    single = _run(1, {"MTP": env["MTP"]} if "MTP" in env else {}, 0)
+    assert [o[0] for o in outs] == [o[0] for o in single]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
