@@ -306,6 +306,7 @@ struct RelayConn {
   Ticket t;
   std::string rid, tail, pending;
   bool reading = true;
+  double last_activity = 0;   // monotonic seconds of the last byte moved in either direction
   RelayTag up_tag{this, false}, client_tag{this, true};   // what the event loop gets back from epoll
 };
 
@@ -340,6 +341,8 @@ class Relay {
     if (th_.joinable()) th_.join();
     for (auto* c : conns_) finish(c, false);
     conns_.clear();
+    for (auto* c : incoming_) { n_open_++; finish(c, false); }   // handed over but never armed
+    incoming_.clear();
     close(ep_);
     close(wake_);
   }
@@ -405,7 +408,7 @@ class Relay {
       int n = epoll_wait(ep_, evs.data(), (int)evs.size(), 500);
       {
         std::lock_guard<std::mutex> lk(mu_);
-        for (auto* c : incoming_) { conns_.insert(c); n_open_++; arm(c); }
+        for (auto* c : incoming_) { c->last_activity = now_s(); conns_.insert(c); n_open_++; arm(c); }
         incoming_.clear();
       }
       std::vector<RelayConn*> dead;
@@ -415,6 +418,7 @@ class Relay {
         if (tag == nullptr) { uint64_t v; (void)!read(wake_, &v, sizeof(v)); continue; }
         RelayConn* c = tag->c;
         if (is_dead(c)) continue;
+        c->last_activity = now_s();
         if (tag->is_client) {
           if (!flush(c)) { dead.push_back(c); continue; }
           if (c->pending.empty()) {
@@ -445,6 +449,18 @@ class Relay {
         conns_.erase(c);
         finish(c, false);
       }
+      // a stream on which nothing has moved for the upstream time-out is given up (its peer counts a failure)
+      const double now = now_s();
+      if (now - last_sweep_ > 1.0) {
+        last_sweep_ = now;
+        std::vector<RelayConn*> idle;
+        for (auto* c : conns_) if (now - c->last_activity > g_cfg.timeout_s) idle.push_back(c);
+        for (auto* c : idle) {
+          LOG(1, "stream %s idle for %.0f s: closed", c->rid.c_str(), now - c->last_activity);
+          conns_.erase(c);
+          finish(c, true);
+        }
+      }
     }
   }
   int ep_ = -1, wake_ = -1;
@@ -454,6 +470,7 @@ class Relay {
   std::unordered_set<RelayConn*> conns_;
   std::atomic<bool> stopped_{false};
   std::atomic<size_t> n_open_{0};
+  double last_sweep_ = 0;
 };
 static Relay* g_relay = nullptr;
 

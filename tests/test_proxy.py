@@ -199,6 +199,33 @@ def test_many_long_streams_need_no_thread_each(proxy_binary):
         d_srv.shutdown()
 
 
+def test_stalled_stream_is_given_up_after_the_upstream_timeout(proxy_binary):
+    """A decode instance that stops sending in the middle of a stream: the relay closes the stream after the
+    upstream time-out, the client sees the truncated answer end, and the peer's in-flight counters are released."""
+    rec = _Recorder()
+    p_srv, d_srv = _make_server("prefill", rec), _make_server("decode", rec, chunks=3, gap=4.0)
+    port = _free_port()
+    proc = _start_proxy(proxy_binary, port, [p_srv.server_port], [d_srv.server_port], extra=("--timeout", "0.5"))
+    try:
+        t0 = time.time()
+        try:
+            status, text = _post(port, {"prompt": "x", "max_tokens": 3, "stream": True})
+        except Exception as e:                 # a truncated body may also surface as an incomplete read
+            status, text = 200, str(getattr(e, "partial", b""))
+        took = time.time() - t0
+        assert took < 3.5, took                # not the 8 s the stalled server would need
+        assert "[DONE]" not in text and text.count("data: {") <= 2
+        m = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        assert "omni_proxy_open_streams 0" in m
+        assert 'omni_proxy_active_requests{pool="decode",peer="0"} 0' in m
+        assert 'omni_proxy_served_total{pool="decode",peer="0"} 0' in m      # it counts as a failure, not as served
+    finally:
+        proc.terminate()
+        proc.wait(timeout=5)
+        p_srv.shutdown()
+        d_srv.shutdown()
+
+
 def test_prefill_failure_passthrough_and_peer_ejection(proxy_binary):
     rec = _Recorder()
     bad_p, d_srv = _make_server("prefill", rec, fail=True), _make_server("decode", rec)
