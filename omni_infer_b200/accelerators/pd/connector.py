@@ -147,9 +147,12 @@ class TcpTransport:
         if not self.key and host not in ("127.0.0.1", "localhost", "::1"):
             raise ValueError("a kv-transfer endpoint that is not loopback needs an authkey (config 'authkey' or OMNI_KV_AUTHKEY)")
         self.key = self.key or b"omni-pd-loopback"
-        self.listener = Listener((host, int(port)), authkey=self.key)
+        self._addr = (host, int(port))
+        self.listener = Listener(self._addr, authkey=self.key)
         self.worker = worker
         self._stop = False
+        self._out: dict = {}                  # endpoint -> open connection to that peer
+        self._out_lock = threading.Lock()
         threading.Thread(target=self._serve, daemon=True).start()
 
     def _serve(self):
@@ -158,33 +161,74 @@ class TcpTransport:
                 conn = self.listener.accept()
             except OSError:
                 return
-            except Exception:  # noqa: BLE001  (failed handshake of a stranger)
+            except Exception:  # noqa: BLE001  (failed handshake of a stranger, or the wake-up connection of close())
+                if self._stop:
+                    return
                 continue
             threading.Thread(target=self._handle, args=(conn,), daemon=True).start()
 
     def _handle(self, conn):
+        # a peer keeps its connection open and sends one frame per message (the handshake of a new connection costs
+        # two round trips, which would sit on every request's time to first token)
         try:
-            msg = _decode(conn.recv_bytes(1 << 22))
-            self.worker.dispatch(msg)
-        except (EOFError, OSError, ValueError, KeyError) as e:
-            logger.warning("kv control message dropped: %s: %s", type(e).__name__, e)
+            while not self._stop:
+                try:
+                    raw = conn.recv_bytes(1 << 22)
+                except (EOFError, OSError):
+                    return
+                # one thread per message, as before: a cancel must be able to overtake the copy of a push
+                threading.Thread(target=self._dispatch, args=(raw,), daemon=True).start()
         finally:
             conn.close()
 
-    def send(self, endpoint: str, msg: dict) -> bool:
-        from multiprocessing.connection import Client
-        host, port = endpoint.replace("tcp://", "").rsplit(":", 1)
+    def _dispatch(self, raw: bytes) -> None:
         try:
+            self.worker.dispatch(_decode(raw))
+        except (ValueError, KeyError) as e:
+            logger.warning("kv control message dropped: %s: %s", type(e).__name__, e)
+
+    def _connection(self, endpoint: str):
+        from multiprocessing.connection import Client
+        c = self._out.get(endpoint)
+        if c is None:
+            host, port = endpoint.replace("tcp://", "").rsplit(":", 1)
             c = Client((host, int(port)), authkey=self.key)
-            c.send_bytes(_encode(msg))
-            c.close()
-            return True
-        except Exception:  # noqa: BLE001
+            self._out[endpoint] = c
+        return c
+
+    def send(self, endpoint: str, msg: dict) -> bool:
+        frame = _encode(msg)
+        with self._out_lock:
+            for attempt in range(2):            # a cached connection may have been closed by the peer: reconnect once
+                try:
+                    self._connection(endpoint).send_bytes(frame)
+                    return True
+                except Exception:  # noqa: BLE001
+                    c = self._out.pop(endpoint, None)
+                    if c is not None:
+                        try:
+                            c.close()
+                        except OSError:
+                            pass
             return False
 
     def close(self):
         self._stop = True
+        # the accept thread sits in accept(): closing the socket under it would leave the port bound until it returns,
+        # so wake it with a connection of our own first
+        try:
+            import socket
+            socket.create_connection(self._addr, timeout=0.5).close()
+        except OSError:
+            pass
         self.listener.close()
+        with self._out_lock:
+            for c in self._out.values():
+                try:
+                    c.close()
+                except OSError:
+                    pass
+            self._out.clear()
 
 
 # ------------------------------------------------------------------------------------------------ scheduler side

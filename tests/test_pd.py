@@ -155,3 +155,62 @@ def test_wire_format_is_json_and_needs_a_key_off_loopback():
     assert raw.startswith(b"{") and _decode(raw) == msg
     with pytest.raises(ValueError):
         TcpTransport("tcp://10.1.2.3:1", None)
+
+
+def test_tcp_control_channel_keeps_connections_and_reconnects():
+    """Messages between two connectors travel over one kept connection per peer; when the peer went away and came
+    back (a restart), the next message reconnects by itself."""
+    import socket
+    import threading
+    import time
+    from omni_infer_b200.accelerators.pd.connector import TcpTransport
+
+    class Sink:
+        def __init__(self):
+            self.got, self.ev = [], threading.Event()
+
+        def dispatch(self, msg):
+            self.got.append(msg)
+            self.ev.set()
+
+    def port():
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        p = s.getsockname()[1]
+        s.close()
+        return p
+
+    def wait(sink, n):
+        for _ in range(200):
+            if len(sink.got) >= n:
+                return True
+            time.sleep(0.01)
+        return False
+
+    a_sink, b_sink = Sink(), Sink()
+    pa, pb = port(), port()
+    a, b = TcpTransport(f"tcp://127.0.0.1:{pa}", a_sink), TcpTransport(f"tcp://127.0.0.1:{pb}", b_sink)
+    try:
+        for i in range(5):
+            assert a.send(f"tcp://127.0.0.1:{pb}", {"op": "push", "request_id": f"r{i}", "blob": bytes([i]) * 8})
+        assert wait(b_sink, 5) and sorted(m["request_id"] for m in b_sink.got) == [f"r{i}" for i in range(5)]
+        assert b_sink.got[0]["blob"] in [bytes([i]) * 8 for i in range(5)]
+        assert len(a._out) == 1                                    # one connection, reused
+        assert b.send(f"tcp://127.0.0.1:{pa}", {"op": "ack", "request_id": "r0"}) and wait(a_sink, 1)
+        # the peer restarts on the same port: the kept connection is dead, the next send reconnects
+        b.close()
+        time.sleep(0.05)
+        b2_sink = Sink()
+        b2 = TcpTransport(f"tcp://127.0.0.1:{pb}", b2_sink)
+        try:
+            ok = False
+            for _ in range(3):          # the first frame after the restart may still go into the dead socket's buffer
+                ok = a.send(f"tcp://127.0.0.1:{pb}", {"op": "push", "request_id": "after"}) and wait(b2_sink, 1)
+                if ok:
+                    break
+            assert ok and b2_sink.got[-1]["request_id"] == "after"
+        finally:
+            b2.close()
+        assert not a.send("tcp://127.0.0.1:1", {"op": "push"})     # nobody listens there: reported, not raised
+    finally:
+        a.close()
