@@ -12,9 +12,11 @@ One process per GPU.  World ranks are laid out ``[dp][tp]`` (TP fastest).  Group
                  inner position in every stage, ``ep`` is the stage's own ranks (the experts of a stage's layers are
                  sharded over them); without pipeline parallelism ``ep`` is the whole instance
 
-The reference additionally builds local/cross/round/far/near-cross groups for its multi-node
-hierarchical pipelines (omni/adaptors/vllm/distributed/parallel_state.py:349-635); one NVSwitch
-domain has uniform bandwidth, so those collapse to the flat groups above and are not built.
+The reference additionally builds local/cross groups for its multi-node hierarchical pipelines
+(omni/adaptors/vllm/distributed/parallel_state.py:349-635).  One NVSwitch domain has uniform bandwidth, so inside
+one box the flat groups above are used; an instance that spans several boxes passes ``ranks_per_domain`` (or
+``OMNI_RANKS_PER_DOMAIN``) and gets ``local`` / ``cross`` groups plus the two-stage collectives of
+``parallel/hierarchical.py`` in ``ParallelState.hier``.
 """
 from __future__ import annotations
 
@@ -113,6 +115,7 @@ class ParallelState:
     groups: dict = field(default_factory=dict)
     tp_fused: object = None     # TpFusedContext / TpNcclBaseline when attention runs tensor parallel
     step_max_tokens: int = 0    # largest token-row count of any rank in the current step (0 = not agreed)
+    hier: object = None         # HierarchicalGroups when the instance spans more than one NVSwitch domain
 
     @property
     def dp_size(self) -> int:
@@ -160,7 +163,8 @@ def _build(name, all_rank_lists, rank, backend=None) -> GroupCoordinator:
 
 
 def init_distributed(backend: Optional[str] = None, tp_size: int = 1, dense_mlp_tp_size: int = 1,
-                     o_proj_tp_size: int = 1, timeout_s: float = 600.0, pp_size: int = 1) -> ParallelState:
+                     o_proj_tp_size: int = 1, timeout_s: float = 600.0, pp_size: int = 1,
+                     ranks_per_domain: int = 0) -> ParallelState:
     """Join the job described by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT and build
     every group.  ``backend`` defaults to nccl with CUDA, gloo otherwise."""
     import datetime
@@ -202,6 +206,11 @@ def init_distributed(backend: Optional[str] = None, tp_size: int = 1, dense_mlp_
     inner = world // pp_size
     st.groups["pp"] = _build("pp", [allr[i::inner] for i in range(inner)], rank)
     st.groups["ep"] = _build("ep", [allr[s * inner:(s + 1) * inner] for s in range(pp_size)], rank)
+    rpd = int(ranks_per_domain or os.environ.get("OMNI_RANKS_PER_DOMAIN", "0") or 0)
+    if 0 < rpd < world:
+        from .hierarchical import build_hierarchical_groups
+        st.hier = build_hierarchical_groups(world, rank, rpd)
+        st.groups["local"], st.groups["cross"] = st.hier.local, st.hier.cross
     _STATE = st
     return st
 

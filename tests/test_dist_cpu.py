@@ -75,6 +75,63 @@ def test_groups_and_collectives():
     assert set(_spawn(_collectives, 2).values()) == {"ok"}
 
 
+# ---------------------------------------------------------------------------------------------- two-level collectives
+def _hierarchical(rank, world, rpd):
+    from omni_infer_b200.parallel import destroy_distributed, init_distributed
+    from omni_infer_b200.parallel import hierarchical as hc
+    ps = init_distributed(backend="gloo", ranks_per_domain=rpd)
+    hg, flat = ps.hier, ps.group("world")
+    assert hg is not None and hg.ranks_per_domain == rpd and hg.num_domains == world // rpd
+    assert hg.local.ranks == list(range(rank // rpd * rpd, rank // rpd * rpd + rpd))
+    assert hg.cross.ranks == list(range(rank % rpd, world, rpd))
+    assert hg.domain == rank // rpd and hg.local_index == rank % rpd
+    g = torch.Generator().manual_seed(5 + rank)
+    x = torch.randn(3, 10, generator=g)
+    for dim in (0, 1):
+        assert torch.equal(hc.all_gather_two_stage(x, hg, dim), flat.all_gather(x, dim))
+    for chunks in (1, 2, 3):
+        assert torch.equal(hc.all_gather_pipelined(x, hg, chunks), flat.all_gather(x, 0))
+    y = torch.randint(-8, 8, (world * 2, 5, 4), generator=g).float()        # integers: sums are exact in any order
+    want = flat.reduce_scatter(y)
+    assert torch.equal(hc.reduce_scatter_two_stage(y, hg), want)
+    for chunks in (2, 7):
+        assert torch.equal(hc.reduce_scatter_pipelined(y, hg, chunks), want)
+    z = torch.randint(-8, 8, (world * 3 + 1,), generator=g).float()         # element count not divisible by L
+    for t in (y, z):
+        assert torch.equal(hc.all_reduce_two_stage(t.clone(), hg), flat.all_reduce(t.clone()))
+    a = torch.arange(world * 2 * 3, dtype=torch.float32).view(world * 2, 3) + 1000 * rank
+    assert torch.equal(hc.all_to_all_two_stage(a, hg), flat.all_to_all(a))
+    # the process-wide forms pick the two-stage route by themselves
+    assert torch.equal(hc.world_all_gather(x), flat.all_gather(x))
+    assert torch.equal(hc.world_all_gather(x, pipelined_chunks=2), flat.all_gather(x))
+    assert torch.equal(hc.world_reduce_scatter(y), want)
+    assert torch.equal(hc.world_all_reduce(z.clone()), flat.all_reduce(z.clone()))
+    assert torch.equal(hc.world_all_to_all(a), flat.all_to_all(a))
+    assert hc.all_gather_local(x).shape[0] == 3 * rpd and hc.all_gather_cross(x).shape[0] == 3 * (world // rpd)
+    assert hc.reduce_scatter_cross(hc.reduce_scatter_local(
+        y.view(world // rpd, rpd, 2, 5, 4).transpose(0, 1).reshape(world * 2, 5, 4))).equal(want)
+    assert hc.all_to_all_local(torch.arange(rpd * 2.)).shape[0] == rpd * 2
+    destroy_distributed()
+    return "ok"
+
+
+@pytest.mark.parametrize("world,rpd", [(4, 2), (6, 3), (6, 2)])
+def test_two_level_collectives_equal_the_flat_ones(world, rpd):
+    assert set(_spawn(_hierarchical, world, rpd).values()) == {"ok"}
+
+
+def test_one_domain_keeps_the_flat_route():
+    from omni_infer_b200.parallel import hierarchical as hc
+    from omni_infer_b200.parallel.parallel_state import get_parallel_state
+    assert get_parallel_state().hier is None
+    x = torch.arange(6.).view(3, 2)
+    for f in (hc.world_all_gather, hc.world_reduce_scatter, hc.world_all_reduce, hc.world_all_to_all, hc.all_gather_cross,
+              hc.reduce_scatter_cross):
+        assert torch.equal(f(x), x)
+    with pytest.raises(ValueError):
+        hc.build_hierarchical_groups(8, 0, 3)
+
+
 # ---------------------------------------------------------------------------------------------- EP over all-to-all
 def _ep_engine(rank, world):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
