@@ -103,8 +103,10 @@ class ModelRunner:
         cfg = self.model_cfg
         if not self.cfg.attn_tp or ps.world_size == 1:
             return
-        assert getattr(cfg, "is_mla", True) and cfg.architecture.startswith("Deepseek"), \
-            "tensor-parallel attention is wired for the MLA models"
+        assert cfg.architecture.startswith(("Deepseek", "Qwen")), "tensor-parallel attention is wired for the MLA and GQA models"
+        if not cfg.use_mla:
+            from ...layers.gqa import shard_heads
+            shard_heads(cfg.num_attention_heads, cfg.num_key_value_heads, ps.world_size, ps.rank)   # raises if it cannot
         cfg.attn_tp_size, cfg.attn_tp_rank = ps.world_size, ps.rank
         from ...parallel.tp_fused import TpFusedContext, TpNcclBaseline
         grp = ps.group("world").group
@@ -224,8 +226,8 @@ class ModelRunner:
         def one():
             if cfg.use_mla:
                 return zeros(num_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim)
-            return (zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim),
-                    zeros(num_blocks, bs, cfg.num_key_value_heads, cfg.head_dim))
+            return (zeros(num_blocks, bs, cfg.local_kv_heads, cfg.head_dim),
+                    zeros(num_blocks, bs, cfg.local_kv_heads, cfg.head_dim))
 
         self.kv_caches = [one() for _ in range(self.model.num_kv_layers)]
         self.drafter_kv = [[one()] for _ in self.drafters]
@@ -244,7 +246,7 @@ class ModelRunner:
                 self.kv_caches[i] = torch.zeros(num_window_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim, dtype=dt,
                                                 device=self.device)
             else:
-                self.kv_caches[i] = tuple(torch.zeros(num_window_blocks, bs, cfg.num_key_value_heads, cfg.head_dim,
+                self.kv_caches[i] = tuple(torch.zeros(num_window_blocks, bs, cfg.local_kv_heads, cfg.head_dim,
                                                       dtype=dt, device=self.device) for _ in range(2))
         self.graphs = None
 

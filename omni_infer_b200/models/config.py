@@ -92,7 +92,12 @@ class ModelConfig:
     def kv_bytes_per_token(self, elem_bytes: int = 2) -> int:
         if self.use_mla:
             return (self.kv_lora_rank + self.qk_rope_head_dim) * elem_bytes
-        return 2 * self.num_key_value_heads * self.head_dim * elem_bytes
+        return 2 * self.local_kv_heads * self.head_dim * elem_bytes
+
+    @property
+    def local_kv_heads(self) -> int:
+        """K/V heads cached by one rank (all of them unless attention runs tensor parallel)."""
+        return max(1, self.num_key_value_heads // max(1, self.attn_tp_size))
 
     def to_dict(self) -> dict:
         return asdict(self)

@@ -25,6 +25,19 @@ class QwenDecoderLayer(nn.Module):
             self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype=dtype,
                                  quant=cfg.quantization if self.quant else "none", device=device)
 
+    def forward_tp(self, h, residual, md, kv_cache, tp, num_valid):
+        """The same layer on this rank's token rows, attention sharded by heads (GQAAttention.forward_tp)."""
+        if residual is None:
+            residual = h.clone()
+            n = self.input_layernorm(h, quant=self.quant)
+        else:
+            n = self.input_layernorm(h, residual=residual, quant=self.quant)
+        x, xq = (n[0], (n[1], n[2])) if self.quant else (n, None)
+        residual, x = self.self_attn.forward_tp(x, xq, md, kv_cache, residual, self.post_attention_layernorm, tp)
+        xq = ops.quant_fp8_block(x) if self.quant else None
+        out = self.mlp(x, xq=xq, num_valid=num_valid) if self.is_moe else self.mlp(x, xq=xq)
+        return out, residual
+
     def forward(self, h, residual, md, kv_cache):
         if residual is None:
             residual = h.clone()
@@ -60,6 +73,8 @@ class QwenModel(nn.Module):
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
 
     def forward(self, input_ids, md, kv_caches, inputs_embeds=None):
+        if self.cfg.attn_tp_size > 1:
+            return self._forward_tp(input_ids, md, kv_caches, inputs_embeds)
         pp = self.pp
         if pp is None or pp.is_first:
             h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
@@ -72,6 +87,18 @@ class QwenModel(nn.Module):
             pp.send_intermediate(h, residual)
             return h
         return self.norm(h, residual=residual)
+
+
+    def _forward_tp(self, input_ids, md, kv_caches, inputs_embeds=None):
+        """Tensor-parallel attention: every rank sees the same batch, works on its block of the (padded) token rows
+        between the attention blocks, and gathers the final hidden states so that sampling is identical everywhere."""
+        from .deepseek import shard_rows_for_tp
+        tp, h, num_valid, T = shard_rows_for_tp(self.cfg, input_ids, md, self.embed_tokens.weight, inputs_embeds)
+        residual = None
+        for i, layer in enumerate(self.layers):
+            h, residual = layer.forward_tp(h, residual, md, kv_caches[i], tp, num_valid)
+        out = self.norm(h, residual=residual)
+        return tp.all_gather_rows(out.contiguous(), out.shape[0] * tp.world)[:T]
 
 
 class Qwen2ForCausalLM(nn.Module):

@@ -266,9 +266,10 @@ class TpNcclBaseline:
         assert total_rows % self.world == 0
         return total_rows // self.world
 
-    def allgather_gemm(self, x_shard, w, *, total_rows, w_scale=None, x_scale_shard=None, epi="store",
-                       out_dtype=torch.bfloat16):
+    def allgather_gemm(self, x_shard, w, *, total_rows, w_scale=None, x_scale_shard=None, epi="store", out_dtype=None):
         rpr = self.rows_per_rank(total_rows)
+        if out_dtype is None:      # the model's activation type
+            out_dtype = torch.bfloat16 if x_shard.dtype == FP8 else x_shard.dtype
         if x_shard.dtype == FP8:
             xb = torch.empty(total_rows, x_shard.shape[1], dtype=torch.uint8, device=x_shard.device)
             dist.all_gather_into_tensor(xb, x_shard.view(torch.uint8).contiguous(), group=self.group)
@@ -307,7 +308,8 @@ class TpNcclBaseline:
             out = out32
         if residual is not None:
             out = out + residual.float()
-        out = out.to(torch.bfloat16)
+        # the model's activation type: bf16 on the GPU; fp32 models (CPU test sizes) keep fp32 rows
+        out = out.to(residual.dtype if residual is not None else (torch.bfloat16 if x.dtype == FP8 else x.dtype))
         if norm_weight is not None:
             return out, ops.rmsnorm(out, norm_weight, eps)
         return out

@@ -136,6 +136,19 @@ class WeightLoader:
                 }
                 if a in ("q_norm.weight", "k_norm.weight"):
                     return self._store(base + a, None, w, scale, offset)
+                att = layer.self_attn
+                if getattr(att, "tp_world", 1) > 1 and a[:2] in ("q_", "k_", "v_") and a[2:] in ("proj.weight", "proj.bias"):
+                    # tensor-parallel attention: this rank's heads of the checkpoint tensor, into the local merged rows
+                    (s0, s1), rows = att.tp_ckpt_rows(a[0])
+                    if a.endswith("bias"):
+                        self.params[base + "qkv_proj.bias"].data[rows[0]:rows[1]].copy_(w[s0:s1])
+                        self.loaded.add(base + "qkv_proj.bias")
+                        return
+                    if w.dtype == FP8 and scale is not None and s0 % 128 == 0 and s1 % 128 == 0:
+                        w, scale = w[s0:s1], scale[s0 // 128:s1 // 128]
+                    else:
+                        w, scale, offset = _to_float(w, scale, offset)[s0:s1], None, None
+                    return self._store(base + "qkv_proj.weight", base + "qkv_proj.weight_scale", w, scale, offset, rows=rows)
                 bias = {"q_proj.bias": (0, Hq * D), "k_proj.bias": (Hq * D, (Hq + Hkv) * D),
                         "v_proj.bias": ((Hq + Hkv) * D, (Hq + 2 * Hkv) * D)}
                 if a in bias:

@@ -251,11 +251,15 @@ def test_pipeline_layer_ranges():
 
 
 # ---------------------------------------------------------------------------------------------- TP attention
-def _tp_engine(rank, world):
+def _tp_engine(rank, world, model="tiny-deepseek-v3", overrides=None):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
     from omni_infer_b200.engine.request import SamplingParams
-    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", seed=3,
-                                  attn_tp=True, tp_backend="nccl"))
+    eng = EngineCore(EngineConfig(model=model, model_overrides=dict(overrides or {}), block_size=16, num_kv_blocks=32,
+                                  max_model_len=128, device="cpu", seed=3, attn_tp=True, tp_backend="nccl"))
+    if world > 1 and not eng.model_cfg.use_mla:        # every rank caches its own K/V heads only
+        from omni_infer_b200.layers.gqa import shard_heads
+        want = shard_heads(eng.model_cfg.num_attention_heads, eng.model_cfg.num_key_value_heads, world, rank)[1]
+        assert eng.worker.runner.kv_caches[0][0].shape[2] == want
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, 1024, (17 + i,), generator=g).tolist() for i in range(3)]   # 56 rows: not a multiple of 8
     ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in prompts]
@@ -271,6 +275,15 @@ def test_tensor_parallel_attention_matches_single_rank():
     single = _spawn(_tp_engine, 1)[0]
     two = _spawn(_tp_engine, 2)
     assert two[0] == single and two[1] == single
+
+
+@pytest.mark.parametrize("world,overrides", [(2, {}), (2, {"num_key_value_heads": 1}), (4, {})])
+def test_tensor_parallel_gqa_attention_matches_single_rank(world, overrides):
+    """The GQA MoE model with query and K/V heads sharded over the ranks: K/V heads divided (4 q / 2 kv heads on 2 ranks),
+    one K/V head shared by both ranks, and 2 K/V heads replicated over 4 ranks; same tokens as the unsharded model."""
+    single = _spawn(_tp_engine, 1, "tiny-qwen3-moe", overrides)[0]
+    many = _spawn(_tp_engine, world, "tiny-qwen3-moe", overrides)
+    assert all(many[r] == single for r in range(world))
 
 
 # ---------------------------------------------------------------------------------------------- placement across ranks

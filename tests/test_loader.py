@@ -208,3 +208,51 @@ def test_int8_to_e4m3_drift_against_int8_oracle():
             assert e_fp8 < e_int8      # per-128-column scales absorb hot channels that a per-token scale cannot
         else:
             assert e_int8 < e_fp8      # on well-behaved inputs int8 is the finer grid: the cost of converting is real
+
+
+@pytest.mark.parametrize("world,kv_heads,quant", [(2, 2, "none"), (4, 2, "none"), (2, 2, "fp8_block")])
+def test_tensor_parallel_gqa_shards_load_this_ranks_heads(world, kv_heads, quant):
+    """Checkpoint q/k/v/o tensors (and the qkv bias) into a model whose attention is sharded over ``world`` ranks: every
+    rank holds its own query heads, the K/V heads it needs (replicated when there are fewer than ranks), and its
+    columns of o_proj; for an e4m3 checkpoint bytes and scale blocks are taken over unchanged."""
+    over = {"dtype": "float32", "hidden_size": 256, "intermediate_size": 512, "head_dim": 128, "vocab_size": 512,
+            "num_attention_heads": 4, "num_key_value_heads": kv_heads}
+    cfg, src = _fresh("qwen2-small", 1, **over)
+    ckpt = hf_tensors(src, cfg)
+    if quant == "fp8_block":
+        for k in [k for k in ckpt if _is_quantised(k)]:
+            q, s = quant_weight_fp8_block_ref(ckpt[k])
+            ckpt[k], ckpt[k[: -len("weight")] + "weight_scale_inv"] = q, s
+    hq, d = cfg.num_attention_heads, cfg.head_dim
+    pre = "model.layers.1.self_attn."
+    for rank in range(world):
+        _, dst = _fresh("qwen2-small", 2 + rank, **over, attn_tp_size=world, attn_tp_rank=rank, quantization=quant)
+        att = dst.model.layers[1].self_attn
+        hql, hkvl, kv0 = att.Hq, att.Hkv, att.kv_head0
+        assert (hql, hkvl, kv0) == (hq // world, max(1, kv_heads // world), rank * kv_heads // world)
+        assert att.qkv_proj.weight.shape[0] == (hql + 2 * hkvl) * d and att.o_proj.weight.shape[1] == hql * d
+        dst.load_weights([(k, v.clone()) for k, v in ckpt.items()])
+        want_rows = {"q": slice(rank * hql * d, (rank + 1) * hql * d), "k": slice(kv0 * d, (kv0 + hkvl) * d),
+                     "v": slice(kv0 * d, (kv0 + hkvl) * d)}
+        got_rows = {"q": slice(0, hql * d), "k": slice(hql * d, (hql + hkvl) * d), "v": slice((hql + hkvl) * d, None)}
+        w, b = att.qkv_proj.weight, att.qkv_proj.bias
+        for kind in "qkv":
+            full = ckpt[pre + kind + "_proj.weight"]
+            if quant == "fp8_block":
+                assert torch.equal(w[got_rows[kind]].view(torch.uint8), full[want_rows[kind]].view(torch.uint8))
+                sc = ckpt[pre + kind + "_proj.weight_scale_inv"]
+                g0 = got_rows[kind].start // 128
+                n = (want_rows[kind].stop - want_rows[kind].start) // 128
+                assert torch.equal(att.qkv_proj.weight_scale[g0:g0 + n], sc[want_rows[kind].start // 128:want_rows[kind].stop // 128])
+            else:
+                assert torch.equal(w[got_rows[kind]], full[want_rows[kind]])
+            assert torch.equal(b[got_rows[kind]], ckpt[pre + kind + "_proj.bias"][want_rows[kind]])
+        cols = slice(rank * hql * d, (rank + 1) * hql * d)
+        if quant == "fp8_block":
+            assert torch.equal(att.o_proj.weight.view(torch.uint8), ckpt[pre + "o_proj.weight"][:, cols].view(torch.uint8))
+        else:
+            assert torch.equal(att.o_proj.weight, ckpt[pre + "o_proj.weight"][:, cols])
+        # the slice functions that the random initialisation uses pick the same rows of the merged tensor
+        merged = torch.cat([ckpt[pre + k + "_proj.weight"].view(torch.uint8) if quant == "fp8_block" else ckpt[pre + k + "_proj.weight"]
+                            for k in "qkv"], 0)
+        assert torch.equal(att.qkv_proj.weight.tp_slice_fn(merged), w.view(torch.uint8) if quant == "fp8_block" else w)
