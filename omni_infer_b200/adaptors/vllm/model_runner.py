@@ -136,7 +136,9 @@ class ModelRunner:
                 and cfg.hidden_size % 128 == 0 and ps.pp_size == 1):
             from ...parallel.ep_fused import EpContext
             # e4m3 experts: rows are dispatched quantised (1x128 scales); unquantised experts: bf16 rows as they are
-            self.ep_ctx = EpContext(cfg.hidden_size, cfg.num_experts_per_tok, self.cfg.max_num_seqs * self.tpr,
+            # with dedicated shared-expert ranks every token also sends one row per shared piece
+            top_k = cfg.num_experts_per_tok + (moe_layers[0].shared_pieces if moe_layers else 0)
+            self.ep_ctx = EpContext(cfg.hidden_size, top_k, self.cfg.max_num_seqs * self.tpr,
                                     wait_ms=self.cfg.ep_wait_ms, payload="fp8" if cfg.quantization == "fp8_block" else "bf16")
             self.ep_max_tokens = self.ep_ctx.max_tokens
 

@@ -60,9 +60,7 @@ class ConfigUpdater:
         pc = extra.parall_config
         engine_cfg.dense_mlp_tp_size = max(1, int(pc.dense_mlp_tp_size))
         engine_cfg.o_proj_tp_size = max(1, int(pc.o_proj_tp_size))
-        if pc.redundancy_shared_expert_num:
-            logger.warning("redundancy_shared_expert_num=%d: dedicated shared-expert ranks are not built; the shared expert "
-                           "runs on every rank (or sharded over dense_mlp_tp_size)", pc.redundancy_shared_expert_num)
+        engine_cfg.shared_expert_ranks = max(0, int(pc.redundancy_shared_expert_num))
         return engine_cfg
 
 

@@ -32,6 +32,7 @@ class EngineConfig:
     pp_size: int = 1                 # pipeline stages; every stage of a pipeline is given the same requests
     dense_mlp_tp_size: int = 1       # dense MLP layers + shared expert sharded over sub-groups of this size
     o_proj_tp_size: int = 1          # o_proj sharded over sub-groups of this size (attention data parallel)
+    shared_expert_ranks: int = 0     # first N ranks hold only the shared expert, routed experts on the others
     block_size: int = 128
     num_kv_blocks: int = 0
     gpu_memory_utilization: float = 0.9
@@ -63,6 +64,8 @@ class EngineCore:
                  kv_connector_pair=None):
         self.cfg = cfg
         self.model_cfg = model_cfg or get_config(cfg.model, **cfg.model_overrides)
+        if cfg.shared_expert_ranks:
+            self.model_cfg.shared_expert_ranks = int(cfg.shared_expert_ranks)
         rc = RunnerConfig(block_size=cfg.block_size, num_kv_blocks=cfg.num_kv_blocks,
                           gpu_memory_utilization=cfg.gpu_memory_utilization, max_num_seqs=cfg.max_num_seqs,
                           max_model_len=cfg.max_model_len, max_num_batched_tokens=cfg.max_num_batched_tokens,

@@ -8,6 +8,14 @@ omni/models/common/layers/moe/fused_moe/layer.py:169-365).  Expert-parallel data
 * ``nccl``          all-to-all over NCCL: the unfused baseline
 * ``fused``         one dispatch kernel (quantise + NVLink peer stores + counts) and a combine whose reduce
                     reads peer memory (csrc/kernels/ep_dispatch_combine.cu)
+
+Dedicated shared-expert ranks (``cfg.shared_expert_ranks = R``, the reference's ``redundancy_shared_expert_num``,
+omni/models/common/layers/moe/deepseek_moe.py:135-215, 573-600): the first R ranks of the expert-parallel group hold
+no routed experts, only the shared expert; the routed experts are spread over the other ranks.  The shared expert is
+cut along its intermediate dimension into ``n_shared_experts`` pieces of a routed expert's shape (a SwiGLU MLP is a sum
+over such pieces), each piece is an always-selected extra expert with weight 1, and every token sends its row to one of
+the R replicas in turn - so the shared expert travels the same dispatch / grouped GEMM / combine path as the routed
+ones, and no rank spends time on it beside its routed experts.
 """
 from __future__ import annotations
 
@@ -72,10 +80,19 @@ class MoELayer(nn.Module):
         self.planner = planner
         E = cfg.n_routed_experts
         redundant = planner.num_redundant_per_rank if planner is not None else 0
-        assert E % self.ep_size == 0
-        self.slots_per_rank = E // self.ep_size + redundant
+        R = int(getattr(cfg, "shared_expert_ranks", 0) or 0) if (self.ep_size > 1 and cfg.n_shared_experts > 0) else 0
+        if R:
+            if planner is not None:
+                raise ValueError("dedicated shared-expert ranks and the expert placement planner cannot be combined")
+            if not 0 < R < self.ep_size or E % (self.ep_size - R):
+                raise ValueError(f"{R} shared-expert ranks: the {E} routed experts must divide over the other "
+                                 f"{self.ep_size - R} ranks")
+        self.shared_ranks = R
+        self.shared_pieces = cfg.n_shared_experts if R else 0
+        assert E % (self.ep_size - R) == 0
+        self.slots_per_rank = max(E // (self.ep_size - R) + redundant, self.shared_pieces)
         self.num_physical = self.slots_per_rank * self.ep_size
-        self.e_lo = self.ep_rank * self.slots_per_rank
+        self.e_lo = self.ep_rank * self.slots_per_rank          # first physical slot of this rank
         quant = cfg.quantization if cfg.quantization == "fp8_block" else "none"
         self.quant = quant
         H, I = cfg.hidden_size, cfg.moe_intermediate_size
@@ -96,7 +113,7 @@ class MoELayer(nn.Module):
         else:
             self.w13_scale = self.w2_scale = None
         self.shared_experts = None
-        if cfg.n_shared_experts > 0:
+        if cfg.n_shared_experts > 0 and not R:
             if getattr(cfg, "dense_mlp_tp_size", 1) > 1 and getattr(cfg, "attn_tp_size", 1) == 1:
                 # sharded over the mlp_tp sub-group like the dense layers (omni/models/deepseek/deepseek_v3.py:86-136)
                 from .linear import ParallelSwiGLUMLP
@@ -113,6 +130,37 @@ class MoELayer(nn.Module):
             self.routing_bias_override = zipf_router_bias(cfg.n_routed_experts, self.moe_index, **cfg.router_skew)
             if device is not None:
                 self.routing_bias_override = self.routing_bias_override.to(device)
+
+    # ------------------------------------------------------------------ what the local slots hold (no planner)
+    def logical_of_slot(self, slot: int):
+        """Logical routed expert in local slot ``slot``; ``("shared", j)`` for piece j of the shared expert on a
+        shared-expert rank; None for a slot that holds nothing."""
+        R = self.shared_ranks
+        if R and self.ep_rank < R:
+            return ("shared", slot) if slot < self.shared_pieces else None
+        per = self.cfg.n_routed_experts // (self.ep_size - R)
+        return (self.ep_rank - R) * per + slot if slot < per else None
+
+    def local_slots_of(self, expert: int) -> list:
+        """Local slots that hold logical routed expert ``expert`` (none on a shared-expert rank)."""
+        R = self.shared_ranks
+        if R and self.ep_rank < R:
+            return []
+        per = self.cfg.n_routed_experts // (self.ep_size - R)
+        lo = (self.ep_rank - R) * per
+        return [expert - lo] if lo <= expert < lo + per else []
+
+    def _append_shared(self, ids, w):
+        """Physical ids of the routed picks (the routed ranks come after the shared ones) plus one always-selected
+        column per shared piece, on the replica chosen by (row + this rank) mod R.  Padding rows (id -1) stay out."""
+        R, S, ns = self.shared_ranks, self.slots_per_rank, self.shared_pieces
+        T = ids.shape[0]
+        valid = ids[:, :1] >= 0
+        routed = torch.where(ids >= 0, ids + R * S, ids)
+        replica = (torch.arange(T, device=ids.device, dtype=ids.dtype) + self.ep_rank) % R
+        piece = torch.arange(ns, device=ids.device, dtype=ids.dtype)
+        sh = torch.where(valid, replica.view(T, 1) * S + piece.view(1, ns), torch.full((1, 1), -1, dtype=ids.dtype, device=ids.device))
+        return torch.cat([routed, sh], 1).contiguous(), torch.cat([w, torch.ones(T, ns, dtype=w.dtype, device=w.device)], 1).contiguous()
 
     # ------------------------------------------------------------------ routing
     def route(self, x, num_valid=None):
@@ -181,6 +229,8 @@ class MoELayer(nn.Module):
             else:
                 shared = self.shared_experts(x, xq=xq)
         ids, w = self.route(x, num_valid)
+        if self.shared_ranks:
+            ids, w = self._append_shared(ids, w)
         if self.ep_size == 1:
             perm = ops.moe_permute(x, ids, w, self.e_lo, self.slots_per_rank, quant=self.quant == "fp8_block", xq_in=xq)
             t_hint = max(16, (T * k + self.slots_per_rank - 1) // self.slots_per_rank)

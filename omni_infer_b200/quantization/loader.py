@@ -77,10 +77,7 @@ class WeightLoader:
         """Local slots that hold logical expert ``expert`` on this rank (placement pattern aware)."""
         if self.planner is not None:
             return self.planner.local_slots_of(moe.moe_index, expert)
-        per = moe.slots_per_rank
-        if moe.e_lo <= expert < moe.e_lo + per:
-            return [expert - moe.e_lo]
-        return []
+        return moe.local_slots_of(expert)
 
     def _route(self, name: str, w, scale, offset):
         cfg = self.cfg
@@ -177,6 +174,24 @@ class WeightLoader:
             if a == "gate.e_score_correction_bias":
                 return self._store(base + "gate.e_score_correction_bias", None, w, scale, offset)
             ms = re.match(r"shared_experts?\.(gate_proj|up_proj|down_proj)\.weight", a)
+            if ms and getattr(moe, "shared_ranks", 0):
+                # dedicated shared-expert ranks: piece j of the shared expert (a block of its intermediate dimension) goes
+                # to local slot j there; the other ranks hold nothing of it
+                if moe.ep_rank >= moe.shared_ranks:
+                    return
+                I, which = cfg.moe_intermediate_size, ms.group(1)
+                blk = w.dtype == FP8 and scale is not None and I % 128 == 0
+                if not blk:
+                    w, scale, offset = _to_float(w, scale, offset), None, None
+                for j in range(moe.shared_pieces):
+                    if which == "down_proj":
+                        self._store(base + "w2", base + "w2_scale", w[:, j * I:(j + 1) * I],
+                                    scale[:, j * I // 128:(j + 1) * I // 128] if blk else None, None, index=j)
+                    else:
+                        self._store(base + "w13", base + "w13_scale", w[j * I:(j + 1) * I],
+                                    scale[j * I // 128:(j + 1) * I // 128] if blk else None, None,
+                                    rows=(0, I) if which == "gate_proj" else (I, 2 * I), index=j)
+                return
             if ms:
                 I = cfg.moe_intermediate_size * cfg.n_shared_experts
                 mod, rows = {"gate_proj": ("gate_up_proj", (0, I)), "up_proj": ("gate_up_proj", (I, 2 * I)),
@@ -230,6 +245,21 @@ class WeightLoader:
         del self._pending[base]
 
     _expects_offset = False
+
+
+def _draw_shared(moe, pname: str, p, gen, std):
+    """The whole shared-expert tensor (merged gate/up for ``w13``, down for ``w2``) as the random initialisation draws it
+    for a model that keeps the shared expert on every rank; e4m3 models get (bytes, scale blocks)."""
+    cfg = moe.cfg
+    I, H = cfg.moe_intermediate_size * cfg.n_shared_experts, cfg.hidden_size
+    prefix = pname.rsplit(".", 1)[0]
+    which = "gate_up_proj" if pname.endswith("w13") else "down_proj"
+    g = gen(p.device, f"{prefix}.shared_experts.{which}.weight")
+    w = torch.randn((2 * I, H) if which == "gate_up_proj" else (H, I), generator=g, device=g.device, dtype=torch.float32) * std
+    if p.dtype == FP8:
+        assert cfg.moe_intermediate_size % 128 == 0, "e4m3 shared-expert pieces must be aligned to the scale blocks"
+        return quant_weight_fp8_block_ref(w)
+    return w, None
 
 
 def iter_safetensors(model_dir: str):
@@ -321,8 +351,29 @@ def init_random_weights(model, seed: int = 0, std: float = 0.02) -> None:
         if name in expert_params:
             mod = expert_params[name]
             sp = params.get(name + "_scale")
+            shared_full = None
             for slot in range(p.shape[0]):
-                logical = mod.e_lo + slot if mod.planner is None else mod.planner.logical_of_slot(mod.moe_index, slot)
+                logical = mod.logical_of_slot(slot) if mod.planner is None else mod.planner.logical_of_slot(mod.moe_index, slot)
+                if logical is None:
+                    continue                      # an unused slot of a shared-expert rank stays zero
+                if isinstance(logical, tuple):
+                    # piece of the shared expert: draw the tensor the model without shared-expert ranks would hold under
+                    # its name there, quantise it whole, keep this piece
+                    if shared_full is None:
+                        shared_full = _draw_shared(mod, name, p, gen, std)
+                    q, s_ = shared_full
+                    I, j = mod.cfg.moe_intermediate_size, logical[1]
+                    ns = mod.shared_pieces
+                    if name.endswith("w13"):
+                        p[slot].copy_(torch.cat([q[j * I:(j + 1) * I], q[(ns + j) * I:(ns + j + 1) * I]], 0))
+                        if s_ is not None:
+                            sp[slot].copy_(torch.cat([s_[j * I // 128:(j + 1) * I // 128],
+                                                      s_[(ns + j) * I // 128:(ns + j + 1) * I // 128]], 0))
+                    else:
+                        p[slot].copy_(q[:, j * I:(j + 1) * I])
+                        if s_ is not None:
+                            sp[slot].copy_(s_[:, j * I // 128:(j + 1) * I // 128])
+                    continue
                 g = gen(p.device, name, "expert", logical)
                 fill(p[slot], sp[slot] if sp is not None else None, g)
             continue

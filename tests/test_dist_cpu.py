@@ -133,10 +133,22 @@ def test_one_domain_keeps_the_flat_route():
 
 
 # ---------------------------------------------------------------------------------------------- EP over all-to-all
-def _ep_engine(rank, world):
+def _ep_engine(rank, world, shared_ranks=0, overrides=None):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
     from omni_infer_b200.engine.request import SamplingParams
-    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", seed=3))
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", seed=3,
+                                  shared_expert_ranks=shared_ranks, model_overrides=dict(overrides or {})))
+    if shared_ranks and world > 1:
+        moe = eng.worker.runner.model.model.layers[1].mlp
+        assert moe.shared_experts is None and moe.shared_ranks == shared_ranks
+        assert moe.slots_per_rank == 8 // (world - shared_ranks)
+        holds = [moe.logical_of_slot(s) for s in range(moe.slots_per_rank)]
+        if rank < shared_ranks:      # shared pieces first, nothing else; no routed expert lives here
+            assert holds[:moe.shared_pieces] == [("shared", j) for j in range(moe.shared_pieces)]
+            assert all(h is None for h in holds[moe.shared_pieces:]) and not any(moe.local_slots_of(e) for e in range(8))
+            assert float(moe.w13[moe.shared_pieces:].abs().sum()) == 0.0
+        else:
+            assert holds == list(range((rank - shared_ranks) * moe.slots_per_rank, (rank - shared_ranks + 1) * moe.slots_per_rank))
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, 1024, (20,), generator=g).tolist() for _ in range(3)]
     ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in prompts]
@@ -150,6 +162,16 @@ def test_expert_parallel_matches_single_rank():
     single = _spawn(_ep_engine, 1)[0]
     two = _spawn(_ep_engine, 2)
     assert two[0] == single and two[1] == single
+
+
+@pytest.mark.parametrize("world,shared_ranks,overrides", [(2, 1, {}), (3, 1, {}), (4, 2, {}),
+                                                          (3, 1, {"n_shared_experts": 2})])
+def test_dedicated_shared_expert_ranks_match_single_rank(world, shared_ranks, overrides):
+    """The first ranks hold only the shared expert (cut into pieces of a routed expert's shape, each an always-selected
+    extra expert), the others only routed experts: same tokens as the model that runs everything on one rank."""
+    single = _spawn(_ep_engine, 1, 0, overrides)[0]
+    many = _spawn(_ep_engine, world, shared_ranks, overrides)
+    assert all(many[r] == single for r in range(world))
 
 
 def _ep_uneven(rank, world, mode):

@@ -256,3 +256,57 @@ def test_tensor_parallel_gqa_shards_load_this_ranks_heads(world, kv_heads, quant
         merged = torch.cat([ckpt[pre + k + "_proj.weight"].view(torch.uint8) if quant == "fp8_block" else ckpt[pre + k + "_proj.weight"]
                             for k in "qkv"], 0)
         assert torch.equal(att.qkv_proj.weight.tp_slice_fn(merged), w.view(torch.uint8) if quant == "fp8_block" else w)
+
+
+@pytest.mark.parametrize("quant", ["none", "fp8_block"])
+def test_shared_expert_ranks_load_pieces_of_the_shared_expert(quant, monkeypatch):
+    """With dedicated shared-expert ranks the checkpoint's shared expert lands, piece by piece, in the first local slots
+    of a shared rank (and nowhere on the others), routed experts only on the other ranks."""
+    from omni_infer_b200.parallel import parallel_state as pst
+    over = dict(_fp8_cfg(), quantization="none", n_shared_experts=2)
+    cfg_f, src = _fresh("tiny-deepseek-v3", 5, **over)
+    ckpt = hf_tensors(src, cfg_f)
+    if quant == "fp8_block":
+        for k in [k for k in ckpt if _is_quantised(k)]:
+            q, s = quant_weight_fp8_block_ref(ckpt[k])
+            ckpt[k], ckpt[k[: -len("weight")] + "weight_scale_inv"] = q, s
+    I = cfg_f.moe_intermediate_size
+    pre = "model.layers.1.mlp."
+
+    def as_float(name):
+        w = ckpt[name]
+        return dequant_weight_ref(w, ckpt[name[: -len("weight")] + "weight_scale_inv"]) if w.dtype == FP8 else w
+
+    def slot_float(moe, s):
+        if quant == "fp8_block":
+            return dequant_weight_ref(moe.w13[s], moe.w13_scale[s]), dequant_weight_ref(moe.w2[s], moe.w2_scale[s])
+        return moe.w13[s].float(), moe.w2[s].float()
+
+    st = pst.get_parallel_state()
+    for rank in range(3):
+        monkeypatch.setattr(st, "world_size", 3)
+        monkeypatch.setattr(st, "rank", rank)
+        _, dst = _fresh("tiny-deepseek-v3", 6, **{**over, "quantization": quant, "shared_expert_ranks": 1})
+        monkeypatch.setattr(st, "world_size", 1)
+        monkeypatch.setattr(st, "rank", 0)
+        moe = dst.model.layers[1].mlp
+        assert moe.shared_ranks == 1 and moe.slots_per_rank == 4 and moe.shared_experts is None
+        with torch.no_grad():
+            moe.w13.view(torch.uint8).zero_() if quant == "fp8_block" else moe.w13.zero_()
+            moe.w2.view(torch.uint8).zero_() if quant == "fp8_block" else moe.w2.zero_()
+        dst.load_weights([(k, v.clone()) for k, v in ckpt.items()])
+        if rank == 0:
+            g, u, d = (as_float(pre + f"shared_experts.{n}_proj.weight") for n in ("gate", "up", "down"))
+            for j in range(2):
+                w13, w2 = slot_float(moe, j)
+                assert torch.equal(w13, torch.cat([g[j * I:(j + 1) * I], u[j * I:(j + 1) * I]], 0))
+                assert torch.equal(w2, d[:, j * I:(j + 1) * I])
+            for s in (2, 3):
+                assert float(slot_float(moe, s)[0].abs().sum()) == 0.0
+        else:
+            for s in range(4):
+                e = (rank - 1) * 4 + s
+                w13, w2 = slot_float(moe, s)
+                assert torch.equal(w13, torch.cat([as_float(pre + f"experts.{e}.gate_proj.weight"),
+                                                   as_float(pre + f"experts.{e}.up_proj.weight")], 0))
+                assert torch.equal(w2, as_float(pre + f"experts.{e}.down_proj.weight"))
