@@ -47,6 +47,7 @@ class RunnerConfig:
     ep_wait_ms: float = 2000.0                 # bound of every cross-rank wait inside the fused kernels
     attn_tp: bool = False                      # attention heads sharded over all ranks, token-sharded hidden states
     tp_backend: str = "fused"                  # fused | nvls | nccl
+    vocab_parallel: bool = False               # embedding table and LM head sharded by vocabulary rows over all ranks
 
 
 class ModelRunner:
@@ -101,6 +102,13 @@ class ModelRunner:
         reduce-scatter around the attention block run inside the GEMMs (parallel/tp_fused.py)."""
         ps = get_parallel_state()
         cfg = self.model_cfg
+        if self.cfg.vocab_parallel and ps.world_size > 1:
+            # every rank must enter the table / head collectives in every step: true for expert-parallel models (idle
+            # ranks run dummy batches) and for tensor-parallel attention, not for independent dense replicas
+            if ps.pp_size > 1 or not (cfg.is_moe or self.cfg.attn_tp):
+                raise ValueError("vocab_parallel needs ranks that step together (an expert-parallel model or attn_tp) and no "
+                                 "pipeline stages")
+            cfg.vocab_parallel_size, cfg.vocab_parallel_rank = ps.world_size, ps.rank
         if not self.cfg.attn_tp or ps.world_size == 1:
             return
         assert cfg.architecture.startswith(("Deepseek", "Qwen")), "tensor-parallel attention is wired for the MLA and GQA models"
@@ -195,6 +203,8 @@ class ModelRunner:
             h = hidden
             for di, d in enumerate(self.drafters):
                 h = d(ids, md, self.drafter_kv[di], h)
+                if self.model_cfg.vocab_parallel_size > 1:
+                    d.compute_logits(h[:1])      # the sharded head is a collective: join the live ranks' call
 
     def kv_bytes_per_block(self) -> int:
         cfg = self.model_cfg

@@ -33,6 +33,7 @@ class EngineConfig:
     dense_mlp_tp_size: int = 1       # dense MLP layers + shared expert sharded over sub-groups of this size
     o_proj_tp_size: int = 1          # o_proj sharded over sub-groups of this size (attention data parallel)
     shared_expert_ranks: int = 0     # first N ranks hold only the shared expert, routed experts on the others
+    vocab_parallel: bool = False     # embedding table + LM head sharded by vocabulary rows over all ranks
     block_size: int = 128
     num_kv_blocks: int = 0
     gpu_memory_utilization: float = 0.9
@@ -71,7 +72,7 @@ class EngineCore:
                           max_model_len=cfg.max_model_len, max_num_batched_tokens=cfg.max_num_batched_tokens,
                           num_speculative_tokens=cfg.num_speculative_tokens, decode_gear_list=cfg.decode_gear_list,
                           enforce_eager=cfg.enforce_eager, seed=cfg.seed, ep_backend=cfg.ep_backend,
-                          attn_tp=cfg.attn_tp, tp_backend=cfg.tp_backend)
+                          attn_tp=cfg.attn_tp, tp_backend=cfg.tp_backend, vocab_parallel=cfg.vocab_parallel)
         sched_conn = worker_conn = None
         if kv_connector_pair is not None:
             sched_conn, worker_conn = kv_connector_pair

@@ -22,6 +22,9 @@ class ModelConfig:
     # dedicated shared-expert ranks: the first N ranks of the expert-parallel group hold only the shared expert, the routed
     # experts are spread over the others (0 = the shared expert runs on every rank beside its routed experts)
     shared_expert_ranks: int = 0
+    # vocabulary-parallel embedding table and LM head: each rank holds ceil(vocab / size) rows (set by the model runner)
+    vocab_parallel_size: int = 1
+    vocab_parallel_rank: int = 0
     # benchmark aid: {"s": 1.2, "strength": 6.0, "seed": 0} adds a fixed Zipf-shaped bias to every router's logits so that
     # expert popularity is skewed (load-balance stress); None = the router as trained
     router_skew: Optional[dict] = None

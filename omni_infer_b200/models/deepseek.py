@@ -16,6 +16,7 @@ from .. import ops
 from ..layers.common import AttnMetadata, Linear, RMSNorm, SwiGLUMLP, _dtype
 from ..layers.mla import MLAAttention
 from ..layers.moe import MoELayer
+from ..layers.vocab_parallel import embed, lm_logits, make_embedding, make_lm_head
 from .config import ModelConfig
 
 
@@ -87,7 +88,7 @@ def shard_rows_for_tp(cfg, input_ids, md, embed_weight, inputs_embeds=None):
     lo, hi = r * rpr, min(T, (r + 1) * rpr)
     if inputs_embeds is None:
         ids = input_ids[lo:hi] if hi > lo else input_ids[:0]
-        h = ops.embedding(ids, embed_weight)
+        h = embed(ids, embed_weight)
     else:
         h = inputs_embeds[lo:hi] if hi > lo else inputs_embeds[:0]
     if h.shape[0] < rpr:
@@ -108,8 +109,7 @@ class DeepseekModel(nn.Module):
         self.dtype = dtype
         self.cos_sin = ops.rope_cos_sin_table(cfg.qk_rope_head_dim, min(cfg.max_position_embeddings, 163840),
                                               cfg.rope_theta, cfg.rope_scaling, device=device or "cpu")
-        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
-        self.embed_tokens.weight.requires_grad_(False)
+        self.embed_tokens = make_embedding(cfg, dtype, device)
         n = cfg.num_hidden_layers if num_layers is None else num_layers
         # pipeline parallelism: this stage builds its own block of layers, placeholders keep the indices of the others
         from ..parallel.parallel_state import get_parallel_state
@@ -127,7 +127,7 @@ class DeepseekModel(nn.Module):
             return self._forward_tp(input_ids, md, kv_caches, inputs_embeds)
         pp = self.pp
         if pp is None or pp.is_first:
-            h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
+            h = embed(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
             residual = None
         else:
             h, residual = pp.recv_intermediate(input_ids.shape[0], self.cfg.hidden_size, self.dtype, input_ids.device)
@@ -163,7 +163,7 @@ class DeepseekV3ForCausalLM(nn.Module):
         if cfg.tie_word_embeddings:
             self.lm_head = None
         else:
-            self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device)
+            self.lm_head = make_lm_head(cfg, dtype, device)
 
     @property
     def num_kv_layers(self) -> int:
@@ -174,7 +174,7 @@ class DeepseekV3ForCausalLM(nn.Module):
 
     def compute_logits(self, hidden):
         w = self.lm_head.weight if self.lm_head is not None else self.model.embed_tokens.weight
-        return ops.gemm(hidden, w, out_dtype=torch.float32)
+        return lm_logits(hidden, w, same_rows_everywhere=self.cfg.attn_tp_size > 1)
 
     def process_weights_after_loading(self):
         for layer in self.model.layers[self.model.layer_lo:self.model.layer_hi]:

@@ -9,6 +9,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..layers.vocab_parallel import embed
 from ..layers.common import AttnMetadata, Linear, RMSNorm, _dtype
 from .config import ModelConfig
 from .deepseek import DeepseekDecoderLayer
@@ -39,7 +40,7 @@ class DeepseekV3MTP(nn.Module):
         return 1
 
     def forward(self, input_ids, md: AttnMetadata, kv_caches, previous_hidden_states):
-        emb = ops.embedding(input_ids, self._main.model.embed_tokens.weight)
+        emb = embed(input_ids, self._main.model.embed_tokens.weight)
         x = torch.cat([self.enorm(emb), self.hnorm(previous_hidden_states)], dim=-1)
         h = self.eh_proj(x)
         if self.cfg.attn_tp_size > 1:

@@ -8,6 +8,7 @@ from .. import ops
 from ..layers.common import AttnMetadata, Linear, RMSNorm, SwiGLUMLP, _dtype
 from ..layers.gqa import GQAAttention
 from ..layers.moe import MoELayer
+from ..layers.vocab_parallel import embed, lm_logits, make_embedding, make_lm_head
 from .config import ModelConfig
 
 
@@ -60,8 +61,7 @@ class QwenModel(nn.Module):
         self.dtype = dtype
         self.cos_sin = ops.rope_cos_sin_table(cfg.head_dim, min(cfg.max_position_embeddings, 131072), cfg.rope_theta,
                                               cfg.rope_scaling, device=device or "cpu")
-        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
-        self.embed_tokens.weight.requires_grad_(False)
+        self.embed_tokens = make_embedding(cfg, dtype, device)
         from ..parallel.parallel_state import get_parallel_state
         from ..parallel.pipeline import PipelineStage, PPMissingLayer, layer_range
         ps = get_parallel_state()
@@ -77,7 +77,7 @@ class QwenModel(nn.Module):
             return self._forward_tp(input_ids, md, kv_caches, inputs_embeds)
         pp = self.pp
         if pp is None or pp.is_first:
-            h = ops.embedding(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
+            h = embed(input_ids, self.embed_tokens.weight) if inputs_embeds is None else inputs_embeds
             residual = None
         else:
             h, residual = pp.recv_intermediate(input_ids.shape[0], self.cfg.hidden_size, self.dtype, input_ids.device)
@@ -108,8 +108,7 @@ class Qwen2ForCausalLM(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.model = QwenModel(cfg, device=device, planner=planner)
-        self.lm_head = None if cfg.tie_word_embeddings else Linear(cfg.hidden_size, cfg.vocab_size,
-                                                                   dtype=self.model.dtype, device=device)
+        self.lm_head = None if cfg.tie_word_embeddings else make_lm_head(cfg, self.model.dtype, device)
 
     @property
     def num_kv_layers(self):
@@ -120,7 +119,7 @@ class Qwen2ForCausalLM(nn.Module):
 
     def compute_logits(self, hidden):
         w = self.lm_head.weight if self.lm_head is not None else self.model.embed_tokens.weight
-        return ops.gemm(hidden, w, out_dtype=torch.float32)
+        return lm_logits(hidden, w, same_rows_everywhere=self.cfg.attn_tp_size > 1)
 
     def process_weights_after_loading(self):
         pass

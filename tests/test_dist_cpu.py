@@ -174,13 +174,13 @@ def test_dedicated_shared_expert_ranks_match_single_rank(world, shared_ranks, ov
     assert all(many[r] == single for r in range(world))
 
 
-def _ep_uneven(rank, world, mode):
+def _ep_uneven(rank, world, mode, vocab_parallel=False):
     """Data-parallel ranks with different work: rank 0 serves three long requests, rank 1 one short request
     (mode "uneven") or none at all (mode "idle").  With multi-step decode and an MTP drafter the ranks need
     different numbers of model rounds per step; the agreement pads the quieter rank with dummy rounds."""
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
     from omni_infer_b200.engine.request import SamplingParams
-    kw = dict(block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=3)
+    kw = dict(block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=3, vocab_parallel=vocab_parallel)
     if mode != "plain":
         kw.update(num_step=2, num_speculative_tokens=1, model_overrides={"num_nextn_predict_layers": 1})
     eng = EngineCore(EngineConfig(**kw))
@@ -208,6 +208,45 @@ def test_uneven_data_parallel_ranks_stay_in_step(mode):
         assert two[1] == [single[1][:3]]
     else:
         assert two[1] == []
+
+
+def _vp_engine(rank, world, attn_tp, overrides=None):
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", seed=3, attn_tp=attn_tp,
+                                  tp_backend="nccl", vocab_parallel=True, model_overrides=dict(overrides or {})))
+    if world > 1:
+        m = eng.worker.runner.model
+        per = (1024 + world - 1) // world
+        assert m.model.embed_tokens.weight.shape[0] == per and m.lm_head.weight.shape[0] == per
+        if rank == world - 1 and per * world > 1024:     # the rows past the vocabulary are zero
+            assert float(m.lm_head.weight[1024 - per * (world - 1):].abs().sum()) == 0.0
+    g = torch.Generator().manual_seed(11)
+    n = 3 if (attn_tp or rank == 0) else 2               # data-parallel ranks with different numbers of requests
+    prompts = [torch.randint(0, 1024, (17 + i,), generator=g).tolist() for i in range(3)][:n]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in prompts]
+    outs = eng.run_until_done()
+    if dist.is_initialized():
+        dist.barrier()
+    return [outs[i] for i in ids]
+
+
+@pytest.mark.parametrize("world,attn_tp,overrides", [(2, False, {}), (3, False, {"n_routed_experts": 12}), (2, True, {})])
+def test_vocabulary_parallel_table_and_head_match_single_rank(world, attn_tp, overrides):
+    """Embedding table and LM head sharded by vocabulary rows (1024 rows over 3 ranks leaves a short last block): same
+    tokens as one rank, with data-parallel attention (ranks hold different rows) and with tensor-parallel attention."""
+    single = _spawn(_vp_engine, 1, attn_tp, overrides)[0]
+    many = _spawn(_vp_engine, world, attn_tp, overrides)
+    assert many[0] == single
+    assert all(many[r] == single[:len(many[r])] for r in range(1, world))
+
+
+def test_vocabulary_parallel_with_uneven_ranks_and_mtp():
+    """Multi-step decode with a drafter on ranks with different work: the row-count agreement of the sharded table and
+    head keeps the ranks in step, tokens equal the single-rank run."""
+    single = _spawn(_ep_uneven, 1, "uneven")[0]
+    two = _spawn(_ep_uneven, 2, "uneven", True)
+    assert two[0] == single and two[1] == [single[1][:3]]
 
 
 def _subgroup_engine(rank, world, mlp_tp, o_tp):

@@ -310,3 +310,18 @@ def test_shared_expert_ranks_load_pieces_of_the_shared_expert(quant, monkeypatch
                 assert torch.equal(w13, torch.cat([as_float(pre + f"experts.{e}.gate_proj.weight"),
                                                    as_float(pre + f"experts.{e}.up_proj.weight")], 0))
                 assert torch.equal(w2, as_float(pre + f"experts.{e}.down_proj.weight"))
+
+
+def test_vocabulary_parallel_checkpoint_rows():
+    """Each rank keeps its block of the embedding table and the LM head (the last block padded with zero rows)."""
+    cfg, src = _fresh("tiny-deepseek-v3", 7, vocab_size=1000)
+    ckpt = hf_tensors(src, cfg)
+    per = (1000 + 2) // 3
+    for rank in range(3):
+        _, dst = _fresh("tiny-deepseek-v3", 8, vocab_size=1000, vocab_parallel_size=3, vocab_parallel_rank=rank)
+        dst.load_weights([(k, v.clone()) for k, v in ckpt.items()])
+        lo, hi = rank * per, min(1000, (rank + 1) * per)
+        for got, name in ((dst.model.embed_tokens.weight, "model.embed_tokens.weight"), (dst.lm_head.weight, "lm_head.weight")):
+            assert got.shape[0] == per
+            assert torch.equal(got[: hi - lo], ckpt[name][lo:hi])
+            assert float(got[hi - lo:].abs().sum()) == 0.0
