@@ -100,6 +100,8 @@ def main(argv=None) -> int:
     ap.add_argument("--base-api-port", type=int, default=9000)
     ap.add_argument("--base-control-port", type=int, default=5568)
     ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--index-offset", type=int, default=0,
+                    help="first instance number of this call's names (a table per host, merged later, needs distinct names)")
     a = ap.parse_args(argv)
     os.makedirs(a.save_dir, exist_ok=True)
     if a.mode == "gen":
@@ -113,9 +115,11 @@ def main(argv=None) -> int:
             raise SystemExit("a GPU is listed for more than one instance")
         t = Topology()
         for i, g in enumerate(pre):
-            t.instances.append(Instance(f"prefill-{i}", "prefill", g, a.base_api_port + i, a.base_control_port + i, a.host, cluster_id=i))
+            t.instances.append(Instance(f"prefill-{a.index_offset + i}", "prefill", g, a.base_api_port + i, a.base_control_port + i,
+                                        a.host, cluster_id=i))
         for j, g in enumerate(dec):
-            t.instances.append(Instance(f"decode-{j}", "decode", g, a.base_api_port + 100 + j, a.base_control_port + 100 + j, a.host,
+            t.instances.append(Instance(f"decode-{a.index_offset + j}", "decode", g, a.base_api_port + 100 + j,
+                                        a.base_control_port + 100 + j, a.host,
                                         cluster_id=len(pre) + j))
         t.save(os.path.join(a.save_dir, "global_topology.json"))
         for inst in t.instances:

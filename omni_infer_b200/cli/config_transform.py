@@ -86,3 +86,46 @@ def transform_deployment_config(path_or_dict) -> list:
 
 def plan_to_json(procs: list) -> str:
     return json.dumps([asdict(p) for p in procs], indent=1)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# several hosts: the same deployment file as an ansible inventory (reference: omni/cli/config_transform.py:123-354
+# writes omni_infer_inventory.yml with host groups P / D / C and per-host node_rank, kv_rank, ports and devices)
+# ---------------------------------------------------------------------------------------------------------------
+def plan_to_inventory(path_or_dict, user: str = "root", code_path: str = "/workspace/omni_infer_b200",
+                      log_path: str = "/workspace/logs", docker_image: str = "omni-infer-b200:latest") -> dict:
+    """Inventory for ``omni_infer_server.yml``: one host entry per prefill / decode instance and one for the proxy.
+    ``node_rank`` counts the hosts of a group, ``kv_rank`` the instances of a role; ``argv`` / ``env`` are what the
+    local launcher would start, so a host runs exactly the process the single-box plan runs."""
+    cfg = yaml.safe_load(open(path_or_dict)) if isinstance(path_or_dict, str) else dict(path_or_dict)
+    procs = transform_deployment_config(cfg)
+    dep = cfg.get("deployment", {})
+    hosts = {"P": {}, "D": {}, "C": {}}
+    by_name = {p.name: p for p in procs}
+    for role, key in (("prefill", "P"), ("decode", "D")):
+        idx = 0
+        for gname, nodes in (dep.get(role, {}) or {}).items():
+            for node_rank, node in enumerate(nodes):
+                spec = by_name[f"{role}-{gname}-{idx}"]
+                hosts[key][f"{key.lower()}{idx}"] = {
+                    "ansible_host": node.get("ip", "127.0.0.1"), "ansible_user": node.get("user", user),
+                    "role": role, "group": gname, "node_rank": node_rank, "kv_rank": idx, "api_port": spec.api_port,
+                    "devices": spec.env["CUDA_VISIBLE_DEVICES"], "master_port": int(node.get("master_port", 29500 + idx)),
+                    "server_argv": spec.argv, "server_env": spec.env, "log_file": spec.log_file,
+                }
+                idx += 1
+    if "proxy" in by_name:
+        px = dep["proxy"]
+        hosts["C"]["c0"] = {"ansible_host": px.get("ip", "127.0.0.1"), "ansible_user": px.get("user", user), "role": "proxy",
+                            "listen_port": by_name["proxy"].api_port, "proxy_argv": by_name["proxy"].argv,
+                            "log_file": by_name["proxy"].log_file}
+    return {"all": {"vars": {"code_path": code_path, "log_path": log_path, "docker_image": docker_image,
+                             "container_name": "omni_infer_b200", "python": "python3"},
+                    "children": {k: {"hosts": v} for k, v in hosts.items()}}}
+
+
+def write_inventory(path_or_dict, out_path: str, **kw) -> str:
+    inv = plan_to_inventory(path_or_dict, **kw)
+    with open(out_path, "w") as f:
+        yaml.safe_dump(inv, f, sort_keys=False)
+    return out_path

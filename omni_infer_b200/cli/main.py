@@ -8,7 +8,7 @@ import json
 import sys
 import urllib.request
 
-from .config_transform import plan_to_json, transform_deployment_config
+from .config_transform import plan_to_json, transform_deployment_config, write_inventory
 from .launch import Launcher
 
 
@@ -29,6 +29,21 @@ def status(config: str, timeout: float = 30.0) -> int:
         return 1
 
 
+def serve_with_ansible(config: str, dry_run: bool = False, inventory: str = "omni_infer_inventory.yml") -> int:
+    """The reference's ``serve``: inventory from the deployment file, then the playbook (omni/cli/main.py:31-80)."""
+    import os
+    import shutil
+    import subprocess
+    write_inventory(config, inventory)
+    playbook = os.path.join(os.path.dirname(os.path.abspath(__file__)), "omni_infer_server.yml")
+    cmd = ["ansible-playbook", "-i", inventory, playbook]
+    if dry_run or shutil.which("ansible-playbook") is None:
+        print(json.dumps({"inventory": inventory, "command": cmd,
+                          "note": "dry run" if dry_run else "ansible-playbook is not installed: run the command where it is"}))
+        return 0 if dry_run else 1
+    return subprocess.call(cmd)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="omni_cli")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -37,11 +52,21 @@ def main(argv=None) -> int:
     s.add_argument("--dry-run", action="store_true")
     s.add_argument("--log-dir", default="./logs")
     s.add_argument("--restart", action="store_true", help="restart a process that exits instead of stopping everything")
+    s.add_argument("--ansible", action="store_true",
+                   help="several hosts: write the inventory and run the playbook instead of starting local processes")
     st = sub.add_parser("status")
     st.add_argument("--config", required=True)
+    iv = sub.add_parser("inventory", help="write the ansible inventory of a deployment file")
+    iv.add_argument("config")
+    iv.add_argument("-o", "--output", default="omni_infer_inventory.yml")
     a = ap.parse_args(argv)
     if a.cmd == "status":
         return status(a.config)
+    if a.cmd == "inventory":
+        print(write_inventory(a.config, a.output))
+        return 0
+    if a.ansible:
+        return serve_with_ansible(a.config, a.dry_run)
     plan = transform_deployment_config(a.config)
     if a.dry_run:
         print(plan_to_json(plan))

@@ -91,6 +91,78 @@ def test_deployment_transform_and_cli_dry_run(tmp_path, capsys):
     assert env["VLLM_DP_RANK"] == "3" and env["WORLD_SIZE"] == "8"
 
 
+def test_inventory_and_playbook_for_several_hosts(tmp_path, capsys):
+    """The deployment file as an ansible inventory (host groups P / D / C with the process each host runs) and the
+    playbook that uses it: every variable a task reads is an inventory variable or has a default, the tags are the
+    reference's, and the topology step calls the topology tool with options it has."""
+    import os
+    import re
+    from omni_infer_b200.accelerators.pd import topology
+    from omni_infer_b200.cli.config_transform import plan_to_inventory
+    dep = json.loads(json.dumps(DEPLOY))
+    dep["deployment"]["prefill"]["group1"][0]["ip"] = "10.0.0.1"
+    dep["deployment"]["decode"]["group1"][0]["ip"] = "10.0.0.3"
+    inv = plan_to_inventory(dep)
+    groups = inv["all"]["children"]
+    assert list(groups) == ["P", "D", "C"]
+    p0, d0, c0 = groups["P"]["hosts"]["p0"], groups["D"]["hosts"]["d0"], groups["C"]["hosts"]["c0"]
+    assert p0["ansible_host"] == "10.0.0.1" and p0["devices"] == "0,1" and p0["kv_rank"] == 0 and p0["node_rank"] == 0
+    assert groups["P"]["hosts"]["p1"]["kv_rank"] == 1 and groups["P"]["hosts"]["p1"]["node_rank"] == 1
+    assert d0["ansible_host"] == "10.0.0.3" and d0["server_env"]["ROLE"] == "decode" and "--num-speculative-tokens" in d0["server_argv"]
+    assert "10.0.0.1:9000" in " ".join(c0["proxy_argv"]) and c0["listen_port"] == 8080
+    f = tmp_path / "deploy.yml"
+    f.write_text(yaml.safe_dump(dep))
+    out = tmp_path / "inv.yml"
+    assert cli_main.main(["inventory", str(f), "-o", str(out)]) == 0
+    assert yaml.safe_load(out.read_text()) == inv
+    capsys.readouterr()
+    cwd = os.getcwd()
+    os.chdir(tmp_path)
+    try:
+        assert cli_main.main(["serve", str(f), "--ansible", "--dry-run"]) == 0
+    finally:
+        os.chdir(cwd)
+    plan = json.loads(capsys.readouterr().out)
+    assert plan["command"][0] == "ansible-playbook" and plan["command"][-1].endswith("omni_infer_server.yml")
+    # ---- the playbook
+    path = os.path.join(os.path.dirname(cli_main.__file__), "omni_infer_server.yml")
+    text = open(path).read()
+    plays = yaml.safe_load(text)
+    tags = {t for play in plays for t in play["tags"]}
+    assert {"run_docker", "sync_code", "topology", "run_server", "run_proxy", "fetch_log", "stop"} <= tags
+    assert all(play["hosts"] in ("P:D:C", "P:D", "C") for play in plays)
+    known = set(inv["all"]["vars"]) | set(p0) | set(c0) | {"inventory_hostname", "playbook_dir", "health", "k", "v"}
+    used = set()
+    for expr in re.findall(r"{{(.*?)}}|{%(.*?)%}", text):
+        body = expr[0] or expr[1]
+        if "default(" in body:
+            continue
+        body = re.sub(r"'[^']*'", "", body)                       # string literals
+        used |= {w for w in re.findall(r"[A-Za-z_][A-Za-z_0-9]*", body)
+                 if w not in ("if", "else", "for", "in", "endfor", "map", "join", "quote", "items", "status")}
+    assert used <= known, used - known
+    # the topology step's options exist in the tool, and a table per host merges into one
+    opts = set(re.findall(r"(--[a-z-]+)", text[text.index("tags: [topology]"):text.index("tags: [run_server]")]))
+    assert opts <= {"--mode", "--prefill-server-list", "--decode-server-list", "--host", "--base-api-port", "--base-control-port",
+                    "--save-dir", "--global-ranktable-list", "--index-offset"}
+    for name, h in list(groups["P"]["hosts"].items()) + list(groups["D"]["hosts"].items()):
+        role_opt = "--prefill-server-list" if h["role"] == "prefill" else "--decode-server-list"
+        off = 0 if h["role"] == "prefill" else 100
+        assert topology.main(["--mode", "gen", role_opt, h["devices"], "--host", h["ansible_host"], "--index-offset",
+                              str(h["kv_rank"]), "--base-api-port",
+                              str(h["api_port"] - off), "--base-control-port", str(5568 + h["kv_rank"] - off),
+                              "--save-dir", str(tmp_path / name)]) == 0
+    tables = [str(tmp_path / n / "global_topology.json") for n in ("p0", "p1", "d0")]
+    assert topology.main(["--mode", "merge-all", "--global-ranktable-list", *tables, "--save-dir", str(tmp_path / "all")]) == 0
+    merged = topology.Topology.load(str(tmp_path / "all" / "global_topology.json"))
+    assert sorted((i.name, i.host, i.api_port) for i in merged.instances) == [
+        ("decode-0", "10.0.0.3", 9100), ("prefill-0", "10.0.0.1", 9000), ("prefill-1", "127.0.0.1", 9001)]
+    # container image and build script exist and say what they build for
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    assert "deploy/build.sh" in open(os.path.join(root, "deploy", "docker", "Dockerfile")).read()
+    assert "g.build()" in open(os.path.join(root, "deploy", "build.sh")).read()
+
+
 def test_launcher_detects_dead_child(tmp_path):
     from omni_infer_b200.cli.config_transform import ProcessSpec
     procs = [ProcessSpec("sleeper", "decode", ["-c", "import time; time.sleep(30)"]),
