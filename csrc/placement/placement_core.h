@@ -27,6 +27,7 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <set>
 #include <string>
 #include <thread>
 #include <vector>
@@ -418,7 +419,8 @@ class Placement {
   std::condition_variable cv_;
   std::vector<PendingApply> pending_;
   std::vector<ChangeInstruction> last_;
-  int next_stage_ = 0;
+  std::vector<int> stage_used_;                   // staging buffers taken in the current round, per rank (same on all)
+  std::set<std::pair<int, int>> round_touched_;   // (layer, position) changed by an instruction of the current round
   std::atomic<int> rounds_{0}, skipped_{0};
 };
 

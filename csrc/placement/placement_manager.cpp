@@ -227,10 +227,18 @@ int Placement::run_round() {
   }
   last_ = instr;
   int done = 0;
-  next_stage_ = 0;
+  stage_used_.assign((size_t)(dist_ != nullptr ? dist_->world() : mapping_->world()), 0);
+  round_touched_.clear();
   for (const auto& ins : instr) {
-    if (should_stop_) break;
-    if (next_stage_ >= Distribution::QUEUE_SIZE) break;   // staging ring is full: the rest waits for the next round
+    // Every rank must leave this loop at the same instruction (each one starts with a collective), so the test is on
+    // state that is identical everywhere: the staging buffers taken so far on the ranks that would receive.  (The stop
+    // flag is not: a rank asked to stop finishes the round; the threads agree on stopping at the start of the next.)
+    bool full = false;
+    if (ins.type == OperationType::ADD || ins.type == OperationType::SWAP) {
+      full = stage_used_[ins.target_rank] >= Distribution::QUEUE_SIZE;
+      if (ins.type == OperationType::SWAP) full = full || stage_used_[ins.source_rank] >= Distribution::QUEUE_SIZE;
+    }
+    if (full) break;                                      // a staging ring is full: the rest waits for the next round
     if (execute(ins)) ++done; else ++skipped_;
   }
   if (dist_ != nullptr) dist_->barrier();                 // every rank has finished staging this round
@@ -281,9 +289,27 @@ bool Placement::execute(const ChangeInstruction& ins) {
   std::lock_guard<std::mutex> lk(mu_);
   if (ins.type == OperationType::REMOVE) {
     pending_.push_back({ins.layer_idx, sp % S, -1, -1, sp, ins.source_expert_id});
+    round_touched_.insert({ins.layer_idx, sp});
     return true;
   }
-  const bool i_am_src = me == ins.source_rank, i_am_dst = me == ins.target_rank;
+  // A position changed earlier in this round still holds its old bytes (the new ones wait in a staging buffer until
+  // the inference thread applies them), so it cannot be the source of a copy.  A replica of the same expert that is
+  // settled serves instead (same choice on every rank: the mappings are identical); without one the instruction
+  // waits for a later round.  A swap needs both of its positions settled.
+  const auto touched = [&](int pos) { return round_touched_.count({ins.layer_idx, pos}) != 0; };
+  if (ins.type == OperationType::SWAP && (touched(sp) || touched(tp))) return false;
+  if (touched(tp)) return false;
+  int src_pos = sp;
+  if (ins.type == OperationType::ADD && (touched(sp) || mapping_->expert_at(ins.layer_idx, sp) != ins.source_expert_id)) {
+    src_pos = -1;
+    for (int p : mapping_->positions_of(ins.layer_idx, ins.source_expert_id))
+      if (!touched(p)) { src_pos = p; break; }
+    if (src_pos < 0) return false;
+  }
+  const int src_rank = ins.type == OperationType::ADD ? src_pos / S : ins.source_rank;
+  round_touched_.insert({ins.layer_idx, tp});
+  if (ins.type == OperationType::SWAP) round_touched_.insert({ins.layer_idx, sp});
+  const bool i_am_src = me == src_rank, i_am_dst = me == ins.target_rank;
   if (replica_ok) {
     // replacement from the host replica: nothing travels between ranks and no staging buffer is taken; the rank
     // that receives an expert copies it host -> device when the change is applied between two steps
@@ -297,18 +323,24 @@ bool Placement::execute(const ChangeInstruction& ins) {
   }
   int stage = -1;
   if (dist_ != nullptr && (i_am_src || i_am_dst)) {
-    stage = next_stage_;
+    stage = stage_used_[me];
     if (ins.type == OperationType::SWAP) {
       const int my_pos = i_am_src ? sp : tp, peer = i_am_src ? ins.target_rank : ins.source_rank;
       dist_->swap(peer, weights_->tensors(ins.layer_idx, my_pos % S), stage);
+    } else if (i_am_src && i_am_dst) {
+      stage = -1;                                         // cannot happen for a valid plan (one replica per rank)
     } else if (i_am_src) {
-      dist_->send_only(ins.target_rank, weights_->tensors(ins.layer_idx, sp % S));
+      dist_->send_only(ins.target_rank, weights_->tensors(ins.layer_idx, src_pos % S));
       stage = -1;
     } else {
-      dist_->recv_only(ins.source_rank, stage, weights_->expert_bytes());
+      dist_->recv_only(src_rank, stage, weights_->expert_bytes());
     }
   }
-  if (stage >= 0) ++next_stage_;
+  // staging buffers taken by this instruction, counted for every rank (all ranks keep the same table)
+  if (dist_ != nullptr) {
+    ++stage_used_[ins.target_rank];
+    if (ins.type == OperationType::SWAP) ++stage_used_[ins.source_rank];
+  }
   // every rank records the mapping change; only the receivers carry a staging buffer
   if (ins.type == OperationType::SWAP) {
     pending_.push_back({ins.layer_idx, sp % S, i_am_src ? stage : -1, ins.target_expert_id, sp, ins.source_expert_id});

@@ -38,6 +38,22 @@ def test_cpp_static_planner_tests_pass_under_sanitizers(tmp_path):
     _build_and_run(tmp_path, "test_placement_static", "test_placement_static.cpp", "address,undefined")
 
 
+def test_cpp_unit_cases_per_component(tmp_path):
+    """One small case per behaviour of every unit (tensor, mapping, activation, weights + host replica, transports, both
+    balancers, optimizer, manager): 72 cases."""
+    import re
+    run = _build_and_run(tmp_path, "test_placement_units", "test_placement_units.cpp", "address,undefined")
+    m = re.search(r"placement units: (\d+) cases, (\d+) checks, 0 failed", run.stdout)
+    assert m and int(m.group(1)) >= 70 and int(m.group(2)) >= 400, run.stdout
+
+
+def test_cpp_unit_cases_are_race_free_under_thread_sanitizer(tmp_path):
+    """The same cases with ThreadSanitizer: the transports, the shared host replica and the manager (ranks as threads,
+    background rounds, stop) run several threads."""
+    run = _build_and_run(tmp_path, "test_placement_units_tsan", "test_placement_units.cpp", "thread")
+    assert "ThreadSanitizer" not in run.stderr, run.stderr[-3000:]
+
+
 def test_cpp_manager_threads_are_race_free_under_thread_sanitizer(tmp_path):
     """The two-rank round of the manager test runs its ranks as threads over the in-process transport."""
     run = _build_and_run(tmp_path, "test_placement_tsan", "test_placement.cpp", "thread")
