@@ -52,6 +52,7 @@ class Scheduler:
         self.pending_free: dict = {}          # prefill side: blocks kept until the decode side pulled them
         self.finished_recving: set = set()
         self.pull_kv_lock = threading.Lock()  # serialises the fast-path KV pull with schedule()
+        self._capacity_stopped: list = []     # ended by schedule() for lack of KV capacity; reported with the next outputs
         self.stats = {"preemptions": 0, "scheduled_prefill_tokens": 0, "scheduled_decode_tokens": 0, "steps": 0}
 
     # ------------------------------------------------------------------ intake
@@ -134,9 +135,43 @@ class Scheduler:
                     self.waiting.remove(req)
                     self.running.append(req)
 
-        # -- 1. admit waiting requests (prefill)
+        # -- 0. partially prefilled running requests (chunked prefill) go on first: they are older than anything
+        # waiting, and admitting newcomers ahead of them can take the blocks they need to ever finish.  When the
+        # pool is exhausted the last running request is preempted, as in the decode phase.
+        if cfg.enable_chunked_prefill:
+            idx = 0
+            while idx < len(self.running) and budget > 0:
+                req = self.running[idx]
+                rem = req.num_tokens - req.num_computed_tokens
+                if rem <= 1:
+                    idx += 1
+                    continue
+                n = min(rem, budget)
+                ok = False
+                while True:
+                    if self.kv.allocate_slots(req, n) is not None:
+                        ok = True
+                        break
+                    victim = self.running.pop()
+                    if victim is req and self._can_never_fit(req, n):
+                        self._give_up(req)
+                        break
+                    self._preempt(victim)
+                    preempted.append(victim.request_id)
+                    if victim is req:
+                        break
+                if not ok:
+                    break
+                scheduled.append(ScheduledRequest(req, n, True))
+                budget -= n
+                idx += 1
+            scheduled = [s for s in scheduled if s.request in self.running]
+
+        # -- 1. admit waiting requests (prefill); not in a step that had to preempt (the victim heads the queue and
+        # would come straight back)
         skipped: list = []
-        while self.waiting and budget > 0 and len(self.running) + len(scheduled) < cfg.max_num_seqs:
+        while (self.waiting and budget > 0 and not preempted
+               and len(self.running) + len([s for s in scheduled if s.request not in self.running]) < cfg.max_num_seqs):
             req = self.waiting[0]
             if req.status == RequestStatus.WAITING_FOR_REMOTE_KVS:
                 skipped.append(self.waiting.popleft())
@@ -163,9 +198,15 @@ class Scheduler:
             start = max(req.num_computed_tokens, n_cached)
             num_new = req.num_tokens - start
             if num_new > budget:
-                if not cfg.enable_chunked_prefill:
+                if cfg.enable_chunked_prefill:
+                    num_new = budget
+                elif num_new > cfg.max_num_batched_tokens and not scheduled:
+                    # It would not fit an empty step either (a preempted request recomputes its prompt plus what it
+                    # has generated, which may exceed a budget its prompt alone respected): waiting cannot help and it
+                    # would block the queue for ever.  It runs alone in a step of its own size.
+                    pass
+                else:
                     break          # the prompt does not fit this step: stop admitting
-                num_new = budget
             if req.num_computed_tokens == 0 and n_cached:
                 req.num_computed_tokens = n_cached
                 req.num_cached_tokens = n_cached
@@ -181,17 +222,6 @@ class Scheduler:
             budget -= num_new
         for r in reversed(skipped):
             self.waiting.appendleft(r)
-
-        # partially prefilled running requests (chunked prefill) continue before any decode
-        if not scheduled and cfg.enable_chunked_prefill:
-            for req in self.running:
-                rem = req.num_tokens - req.num_computed_tokens
-                if rem > 1 and budget > 0:
-                    n = min(rem, budget)
-                    if self.kv.allocate_slots(req, n) is None:
-                        break
-                    scheduled.append(ScheduledRequest(req, n, True))
-                    budget -= n
 
         if scheduled:
             for s in scheduled:
@@ -219,6 +249,9 @@ class Scheduler:
                     break
                 # out of blocks: preempt the lowest-priority (last) running request
                 victim = self.running.pop()
+                if victim is req and self._can_never_fit(req, n + lookahead):
+                    self._give_up(req)
+                    break
                 self._preempt(victim)
                 preempted.append(victim.request_id)
                 if victim is req:
@@ -238,6 +271,18 @@ class Scheduler:
         if self.connector is not None:
             out.kv_connector_metadata = self.connector.build_connector_meta()
         return out
+
+    def _can_never_fit(self, req: Request, num_new_tokens: int) -> bool:
+        """The request wants more blocks than the whole pool has: preempting it would only bring it back to the same
+        point after a recompute, for ever."""
+        return self.kv.blocks_needed(req.num_computed_tokens + num_new_tokens) > self.kv.num_blocks - 1
+
+    def _give_up(self, req: Request) -> None:
+        """Ends a request that has outgrown the KV pool (it keeps what it has generated; reason: length)."""
+        self.kv.free(req)
+        self._finish(req, RequestStatus.FINISHED_LENGTH_CAPPED)
+        self.stats["kv_capacity_stops"] = self.stats.get("kv_capacity_stops", 0) + 1
+        self._capacity_stopped.append(req)
 
     def _preempt(self, req: Request) -> None:
         self.kv.free(req)
@@ -267,6 +312,10 @@ class Scheduler:
             req = self.pending_free.pop(rid, None)
             if req is not None:
                 self.kv.free(req)          # safe when already freed
+        for req in self._capacity_stopped:
+            results.append(RequestOutput(req.request_id, [], True, FINISH_REASON.get(req.status), None, req.num_prompt_tokens,
+                                         len(req.output_token_ids)))
+        self._capacity_stopped = []
         idx_of = {rid: i for i, rid in enumerate(out.req_ids)}
         for s in sched.scheduled:
             req = s.request

@@ -316,7 +316,7 @@ def test_json_member_surgery_agrees_with_a_full_parser(tmp_path):
     import random
     exe = str(tmp_path / "json_apply")
     res = subprocess.run(["g++", "-O1", "-g", "-std=c++17", "-Wall", "-fsanitize=address,undefined", "-I", SRC, "-o", exe,
-                          os.path.join(SRC, "json_apply.cpp")], capture_output=True, text=True)
+                          os.path.join(SRC, "test_json_apply.cpp")], capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-3000:]
     rnd = random.Random(1234)
     keys = ["model", "prompt", "max_tokens", "stream", "stream_options", "kv_transfer_params", "messages", "temperature", "n",
