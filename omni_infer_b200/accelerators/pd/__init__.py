@@ -48,7 +48,8 @@ def create_connectors(kv_transfer_config: dict, block_size: int = 128, num_specu
     endpoint = c.get("endpoint", f"inproc://{eid}")
     transport = c.get("transport", "inproc" if endpoint.startswith("inproc") else "tcp")
     worker = WorkerConnector(role, eid, endpoint, transport, float(c.get("sync_timeout_s", 20.0)), int(c.get("retries", 3)),
-                             float(c.get("retry_wait_s", 2.0)), authkey=c.get("authkey"))
+                             float(c.get("retry_wait_s", 2.0)), authkey=c.get("authkey"),
+                             handover_ttl_s=float(c.get("handover_ttl_s", 120.0)))
     sched = SchedulerConnector(role, eid, endpoint, block_size, num_speculative_tokens,
                                worker=worker if c.get("async_pull_kv", True) else None)
     return sched, worker

@@ -20,7 +20,10 @@ Robustness: a push request is retried ``retries`` times ``retry_wait_s`` apart a
 scheduler falls back to prefilling it locally.  Every push carries an attempt id: only the acknowledgement of the
 attempt being waited for counts, a producer that does not know the request answers ``nack`` (local prefill at once,
 never a decode on blocks nobody wrote), and a consumer that gives up sends ``cancel`` and frees the blocks only after
-the producer confirmed that nothing of that attempt is being written any more."""
+the producer confirmed that nothing of that attempt is being written any more.  The producer in turn does not keep a
+handed-over request's blocks for ever: it releases them when the consumer cancels or is refused (that request is
+prefilled on the decode side, the blocks are of no use any more) and when nobody has asked for them within
+``handover_ttl_s`` (the client went away, the decode instance died); a push that arrives later is answered ``nack``."""
 from __future__ import annotations
 
 import logging
@@ -269,6 +272,15 @@ class SchedulerConnector:
         self._pending = []
         return meta
 
+    def abandon(self, request_id: str) -> bool:
+        """The scheduler wants to drop a request whose KV is being loaded.  Returns True when a transfer may be writing
+        into its blocks: they must then stay allocated until the request shows up as received or failed."""
+        before = len(self._pending)
+        self._pending = [r for r in self._pending if r.request_id != request_id]
+        if len(self._pending) != before:
+            return False                      # never sent to the worker side: nothing is on its way
+        return self.worker.abandon(request_id) if self.worker is not None else False
+
     def kick(self, meta: ConnectorMetadata) -> None:
         """Fast path: hand the metadata to the worker connector right away instead of with the next step."""
         if self.worker is not None and meta.requests:
@@ -300,9 +312,11 @@ class WorkerConnector:
     SERVED_LIMIT = 4096          # producer: how many served request ids are remembered for re-acknowledgement
 
     def __init__(self, kv_role: str, engine_id: str, endpoint: str, transport: str = "inproc", sync_timeout_s: float = 20.0,
-                 retries: int = 3, retry_wait_s: float = 2.0, authkey=None):
+                 retries: int = 3, retry_wait_s: float = 2.0, authkey=None, handover_ttl_s: float = 120.0):
         self.kv_role, self.engine_id, self.endpoint, self.transport = kv_role, engine_id, endpoint, transport
         self.sync_timeout_s, self.retries, self.retry_wait_s = sync_timeout_s, retries, retry_wait_s
+        self.handover_ttl_s = handover_ttl_s
+        self.expired_handovers = 0         # producer: handed-over requests nobody asked for in time
         self.kv_tensors: list = []
         self._meta: Optional[ConnectorMetadata] = None
         self._lock = threading.Lock()
@@ -311,8 +325,9 @@ class WorkerConnector:
         self._done_send: set = set()
         self._inflight: dict = {}          # consumer: request id -> (ReqMeta, attempt id)
         self._cancel_acked: set = set()    # consumer: (request id, attempt) whose cancel the producer confirmed
+        self._abandoned: set = set()       # consumer: requests the scheduler dropped while their transfer was running
         self._attempts = 0
-        self._expected: set = set()        # producer: requests whose blocks wait to be pushed
+        self._expected: dict = {}          # producer: requests whose blocks wait to be pushed -> time of the hand-over
         self._served: dict = {}            # producer: request id -> attempt id of the push that was served (bounded)
         self._cancelled: set = set()       # producer: (request id, attempt) the consumer gave up on
         self._copying: set = set()         # producer: request ids whose copy is running right now
@@ -356,6 +371,13 @@ class WorkerConnector:
 
     def get_finished(self, finished_req_ids=None):
         with self._lock:
+            if self._expected and self.handover_ttl_s > 0:
+                limit = time.monotonic() - self.handover_ttl_s
+                for rid in [k for k, t in self._expected.items() if t < limit and k not in self._copying]:
+                    del self._expected[rid]
+                    self._done_send.add(rid)
+                    self.expired_handovers += 1
+                    logger.warning("nobody asked for the KV of %s within %.0f s: blocks released", rid, self.handover_ttl_s)
             s, r = self._done_send, self._done_recv
             self._done_send, self._done_recv = set(), set()
         return s, r
@@ -365,9 +387,24 @@ class WorkerConnector:
             f, self._failed_recv = self._failed_recv, set()
         return f
 
+    def abandon(self, request_id: str) -> bool:
+        """Consumer: stop waiting for this request's KV.  True = a transfer is in flight; it is cancelled with the
+        producer and the request is reported as failed (or received, if the copy won the race) once nothing can write
+        into its blocks any more."""
+        with self._lock:
+            if self._meta is not None:
+                n = len(self._meta.requests)
+                self._meta.requests = [r for r in self._meta.requests if r.request_id != request_id]
+                if len(self._meta.requests) != n:
+                    return False              # bound but not started
+            if request_id in self._inflight:
+                self._abandoned.add(request_id)
+                return True
+        return False
+
     def expect_pull(self, request_id: str) -> None:
         with self._lock:
-            self._expected.add(request_id)
+            self._expected[request_id] = time.monotonic()
 
     # -- message plumbing
     def dispatch(self, msg: dict) -> None:
@@ -410,11 +447,18 @@ class WorkerConnector:
             self._send(r.remote_host, msg)
             # the last send waits out the whole synchronisation timeout, earlier ones one retry interval
             wait_until = deadline if n == self.retries else min(deadline, time.monotonic() + self.retry_wait_s)
+            dropped = False
             while time.monotonic() < wait_until:
                 if not self._still_waiting(r.request_id, attempt):
+                    with self._lock:
+                        self._abandoned.discard(r.request_id)
                     return                       # acknowledged, or refused by the producer
+                with self._lock:
+                    dropped = r.request_id in self._abandoned
+                if dropped:
+                    break
                 time.sleep(0.002)
-            if time.monotonic() >= deadline:
+            if dropped or time.monotonic() >= deadline:
                 break
             logger.warning("kv push for %s not acknowledged, retry %d", r.request_id, n + 1)
         # Give up.  A push that is still on its way must not land in blocks that were handed to another request:
@@ -435,7 +479,12 @@ class WorkerConnector:
             if cur is not None and cur[1] == attempt:
                 del self._inflight[r.request_id]
                 self._failed_recv.add(r.request_id)
-        logger.error("kv push for %s abandoned after %.1fs", r.request_id, self.sync_timeout_s)
+            was_dropped = r.request_id in self._abandoned
+            self._abandoned.discard(r.request_id)
+        if was_dropped:
+            logger.info("kv push for %s cancelled: the request was dropped", r.request_id)
+        else:
+            logger.error("kv push for %s abandoned after %.1fs", r.request_id, self.sync_timeout_s)
 
     def handle_ack(self, msg: dict) -> None:
         """Only the acknowledgement of the attempt that is being waited for counts: duplicates, strangers and late
@@ -493,6 +542,9 @@ class WorkerConnector:
                 peer = self._peer_cache(msg)
             except LookupError as e:
                 logger.warning("push request for %s refused: %s", rid, e)
+                with self._lock:                 # the consumer prefills it itself now: the blocks are of no use here
+                    if self._expected.pop(rid, None) is not None:
+                        self._done_send.add(rid)
                 self._send(msg["reply_to"], {"op": "nack", "request_id": rid, "attempt": attempt})
                 return
             if isinstance(peer, PeerCacheView):
@@ -505,7 +557,7 @@ class WorkerConnector:
             with self._lock:
                 self._copying.discard(rid)
         with self._lock:
-            self._expected.discard(rid)
+            self._expected.pop(rid, None)
             self._done_send.add(rid)
             self._served[rid] = attempt
             while len(self._served) > self.SERVED_LIMIT:
@@ -526,6 +578,10 @@ class WorkerConnector:
                 if rid not in self._copying:
                     break
             time.sleep(0.001)
+        with self._lock:
+            # the consumer gave the transfer up and prefills the request itself: nobody will ask for these blocks again
+            if rid not in self._copying and self._expected.pop(rid, None) is not None:
+                self._done_send.add(rid)
         self._send(msg["reply_to"], {"op": "cancel_ack", "request_id": rid, "attempt": attempt})
 
     def close(self) -> None:

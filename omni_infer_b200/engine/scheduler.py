@@ -52,6 +52,7 @@ class Scheduler:
         self.pending_free: dict = {}          # prefill side: blocks kept until the decode side pulled them
         self.finished_recving: set = set()
         self.pull_kv_lock = threading.Lock()  # serialises the fast-path KV pull with schedule()
+        self._aborting: dict = {}             # dropped while their KV transfer ran: finished when it has concluded
         self._capacity_stopped: list = []     # ended by schedule() for lack of KV capacity; reported with the next outputs
         self.stats = {"preemptions": 0, "scheduled_prefill_tokens": 0, "scheduled_decode_tokens": 0, "steps": 0}
 
@@ -67,7 +68,14 @@ class Scheduler:
 
     def abort_request(self, request_id: str) -> None:
         req = self.requests.get(request_id)
-        if req is None or req.is_finished:
+        if req is None or req.is_finished or request_id in self._aborting:
+            return
+        if (req.status == RequestStatus.WAITING_FOR_REMOTE_KVS and req.block_ids and self.connector is not None
+                and self.connector.abandon(request_id)):
+            # A producer may be writing into these blocks right now.  Freeing them here would hand them to another
+            # request while the copy still lands in them: the request ends when the transfer has been cancelled (it
+            # then shows up as failed) or has completed.
+            self._aborting[request_id] = req
             return
         self._finish(req, RequestStatus.FINISHED_ABORTED)
         if req in self.running:
@@ -123,6 +131,10 @@ class Scheduler:
             for req in list(self.waiting):
                 if req.status == RequestStatus.WAITING_FOR_REMOTE_KVS and req.request_id in self.finished_recving:
                     self.finished_recving.discard(req.request_id)
+                    if self._aborting.pop(req.request_id, None) is not None:
+                        self.waiting.remove(req)          # dropped meanwhile: the copy is over, the blocks can go
+                        self._finish(req, RequestStatus.FINISHED_ABORTED)
+                        continue
                     params = req.kv_transfer_params or {}
                     if params.get("prefilled_token") is not None and not req.output_token_ids:
                         req.output_token_ids.append(int(params["prefilled_token"]))   # reuse P's first token
@@ -302,6 +314,13 @@ class Scheduler:
         for rid in getattr(out, "failed_recving", None) or ():
             # the remote KV never arrived: give the blocks back and prefill the prompt on this instance
             req = self.requests.get(rid)
+            if req is not None and self._aborting.pop(rid, None) is not None:
+                try:
+                    self.waiting.remove(req)
+                except ValueError:
+                    pass
+                self._finish(req, RequestStatus.FINISHED_ABORTED)
+                continue
             if req is not None and req.status == RequestStatus.WAITING_FOR_REMOTE_KVS:
                 self.kv.free(req)
                 req.status = RequestStatus.WAITING

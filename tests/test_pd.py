@@ -92,6 +92,47 @@ def test_transfer_that_never_completes_falls_back_to_local_prefill():
     outs = _run_pd(P, D, prompts, 5)
     assert D.scheduler.stats.get("kv_fallbacks", 0) == 2
     assert [outs[f"r{i}"] for i in range(2)] == want
+    # the consumer's cancel told the producer that nobody will come for these blocks: they are free again
+    for _ in range(50):
+        P.step()
+        if not P.scheduler.pending_free:
+            break
+        time.sleep(0.01)
+    assert not P.scheduler.pending_free and P.scheduler.kv.num_free_blocks == 47
+
+
+def test_producer_releases_blocks_that_nobody_asks_for():
+    """The client went away after the prefill (or the decode instance died): the hand-over expires, the blocks are
+    freed, and a push request that arrives afterwards is refused, so the late consumer prefills the prompt itself."""
+    prompts = _prompts(2)
+    want = _mixed_reference(prompts, 4)
+    P = _engine("kv_producer", "p9")
+    conn = P.worker.runner.kv_connector
+    conn.handover_ttl_s = 0.3
+    handoff = {}
+    for i, p in enumerate(prompts):
+        P.add_request(p, SamplingParams(max_tokens=1), request_id=f"r{i}", kv_transfer_params={"do_remote_decode": True})
+    while P.scheduler.has_unfinished:
+        for out in P.step():
+            if out.finished:
+                handoff[out.request_id] = out.kv_transfer_params
+    assert len(P.scheduler.pending_free) == 2 and P.scheduler.kv.num_free_blocks < 47
+    t0 = time.time()
+    while P.scheduler.pending_free and time.time() - t0 < 5.0:
+        P.step()
+        time.sleep(0.02)
+    assert not P.scheduler.pending_free and P.scheduler.kv.num_free_blocks == 47 and conn.expired_handovers == 2
+    D = _engine("kv_consumer", "d9")
+    for i, p in enumerate(prompts):
+        D.add_request(p, SamplingParams(max_tokens=4), request_id=f"r{i}", kv_transfer_params=dict(handoff[f"r{i}"]))
+    outs = {}
+    t0 = time.time()
+    while D.has_unfinished and time.time() - t0 < 30.0:
+        for out in D.step():
+            outs.setdefault(out.request_id, []).extend(out.new_token_ids)
+        time.sleep(0.001)
+    assert D.scheduler.stats.get("kv_fallbacks", 0) == 2
+    assert [outs[f"r{i}"] for i in range(2)] == want
 
 
 def test_unknown_request_is_refused_and_prefilled_locally():
@@ -214,3 +255,41 @@ def test_tcp_control_channel_keeps_connections_and_reconnects():
         assert not a.send("tcp://127.0.0.1:1", {"op": "push"})     # nobody listens there: reported, not raised
     finally:
         a.close()
+
+
+def test_request_dropped_during_its_kv_transfer_keeps_its_blocks_until_the_transfer_is_over():
+    """A client that disconnects while the decode instance waits for the KV: the blocks must not return to the pool
+    while a producer could still write into them.  The transfer is cancelled with the producer, the request then ends
+    as aborted with its blocks freed on both sides, and a request that was not dropped is unaffected."""
+    prompts = _prompts(2)
+    want = _mixed_reference(prompts, 4)
+    P = _engine("kv_producer", "p10")
+    D = _engine("kv_consumer", "d10", sync_timeout_s=3.0, retries=3, retry_wait_s=0.3)
+    handoff = {}
+    for i, p in enumerate(prompts):
+        P.add_request(p, SamplingParams(max_tokens=1), request_id=f"r{i}", kv_transfer_params={"do_remote_decode": True})
+    while P.scheduler.has_unfinished:
+        for out in P.step():
+            if out.finished:
+                handoff[out.request_id] = out.kv_transfer_params
+    InProcessHub.drop_next = 1                 # r0's first push request is lost: its transfer is "on the way" for a while
+    D.add_request(prompts[0], SamplingParams(max_tokens=4), request_id="r0", kv_transfer_params=dict(handoff["r0"]))
+    D.step()
+    r0 = D.scheduler.requests["r0"]
+    assert r0.status.name == "WAITING_FOR_REMOTE_KVS" and r0.block_ids
+    held = list(r0.block_ids)
+    D.abort("r0")
+    assert not r0.is_finished and r0.block_ids == held and all(D.scheduler.kv.ref[b] == 1 for b in held)
+    D.abort("r0")                              # twice is harmless
+    D.add_request(prompts[1], SamplingParams(max_tokens=4), request_id="r1", kv_transfer_params=dict(handoff["r1"]))
+    outs = {}
+    t0 = time.time()
+    while (D.has_unfinished or P.scheduler.pending_free) and time.time() - t0 < 20.0:
+        for out in D.step():
+            outs.setdefault(out.request_id, []).extend(out.new_token_ids)
+        P.step()
+        time.sleep(0.002)
+    assert r0.status.name == "FINISHED_ABORTED" and not r0.block_ids and "r0" not in outs
+    assert outs["r1"] == want[1]
+    assert D.scheduler.kv.num_free_blocks == 47 and not D.scheduler._aborting
+    assert P.scheduler.kv.num_free_blocks == 47 and not P.scheduler.pending_free
