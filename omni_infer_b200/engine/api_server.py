@@ -42,9 +42,10 @@ class AsyncEngine:
         self.lock = threading.Lock()
         self.inbox: queue.Queue = queue.Queue()
         self._stop = False
+        self.stats = {"requests": 0, "tokens": 0, "started": time.time(), "failed_steps": 0}
+        self.failed_in_a_row = 0          # engine steps that raised, since the last one that did not
         self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
-        self.stats = {"requests": 0, "tokens": 0, "started": time.time()}
 
     def submit(self, prompt_ids, sampling, request_id, kv_transfer_params=None) -> queue.Queue:
         q: queue.Queue = queue.Queue()
@@ -56,6 +57,14 @@ class AsyncEngine:
 
     def abort(self, request_id):
         self.inbox.put(("abort", request_id))
+
+    UNHEALTHY_AFTER = 3
+
+    @property
+    def healthy(self) -> bool:
+        """False after several engine steps in a row have failed (a lost device or peer): ``/health`` then answers 503
+        so that the proxy takes this instance out of rotation instead of feeding it requests that will fail."""
+        return self.failed_in_a_row < self.UNHEALTHY_AFTER
 
     def _loop(self):
         eng = self.engine
@@ -80,11 +89,22 @@ class AsyncEngine:
                 outs = eng.step()
             except Exception as e:  # noqa: BLE001  (a failed step must not kill the serving thread)
                 logger.exception("engine step failed: %s", e)
+                self.stats["failed_steps"] += 1
+                self.failed_in_a_row += 1
                 with self.lock:
-                    for q in self.queues.values():
-                        q.put(None)
+                    failed = list(self.queues.items())
                     self.queues.clear()
+                for rid, q in failed:
+                    # out of the scheduler too: the same batch must not be run (and fail) again for ever
+                    try:
+                        eng.abort(rid)
+                    except Exception:  # noqa: BLE001
+                        logger.exception("could not drop %s after the failed step", rid)
+                    q.put(None)
+                if self.failed_in_a_row >= self.UNHEALTHY_AFTER:
+                    time.sleep(0.2)         # nothing works: do not spin
                 continue
+            self.failed_in_a_row = 0
             for o in outs:
                 self.stats["tokens"] += len(o.new_token_ids)
                 with self.lock:
@@ -118,8 +138,25 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
             self.end_headers()
             self.wfile.write(body)
 
+        def _client_gone(self) -> bool:
+            """True when the peer has closed its side (no request is pipelined behind a pending one here, so readable +
+            zero bytes means end of stream)."""
+            import select
+            import socket
+            try:
+                r, _, _ = select.select([self.connection], [], [], 0)
+                if not r:
+                    return False
+                return self.connection.recv(1, socket.MSG_PEEK | socket.MSG_DONTWAIT) == b""
+            except (BlockingIOError, InterruptedError):
+                return False
+            except OSError:
+                return True
+
         def do_GET(self):
             if self.path == "/health":
+                if not aeng.healthy:
+                    return self._json(503, {"status": "engine steps are failing", "failed_steps": aeng.stats["failed_steps"]})
                 return self._json(200, {"status": "ok"})
             if self.path == "/metrics":
                 s, e = aeng.stats, aeng.engine
@@ -155,10 +192,24 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                                  if hasattr(tok.tokenizer, "apply_chat_template") else str(body.get("messages")))
             else:
                 p = body.get("prompt", "")
-                ids = list(p) if isinstance(p, list) and p and isinstance(p[0], int) else tok.encode(p if isinstance(p, str) else str(p))
-            sp = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
-                                temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
-                                top_p=float(body.get("top_p", 1.0) or 1.0), ignore_eos=bool(body.get("ignore_eos", False)))
+                if isinstance(p, list) and all(isinstance(t, int) and not isinstance(t, bool) for t in p):
+                    ids = list(p)                       # token ids as they are (an empty list is an empty prompt)
+                else:
+                    ids = tok.encode(p if isinstance(p, str) else str(p))
+            try:
+                sp = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
+                                    temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
+                                    top_p=float(body.get("top_p", 1.0) or 1.0), ignore_eos=bool(body.get("ignore_eos", False)))
+                if sp.max_tokens < 1 or sp.temperature < 0 or not 0 < sp.top_p <= 1 or sp.top_k < 0:
+                    raise ValueError("max_tokens >= 1, temperature >= 0, 0 < top_p <= 1 and top_k >= 0 are required")
+            except (TypeError, ValueError) as e:
+                return self._json(400, {"error": f"invalid sampling parameters: {e}"})
+            if not ids:
+                return self._json(400, {"error": "empty prompt"})
+            limit = aeng.engine.cfg.max_model_len
+            if len(ids) >= limit:
+                return self._json(400, {"error": f"the prompt has {len(ids)} tokens; this model's context holds {limit} "
+                                                 f"including the completion"})
             rid = self.headers.get("X-Request-Id") or ("cmpl-" + uuid.uuid4().hex)
             timeline.emit("Get request in api server", rid, role=aeng.engine.role)
             q = aeng.submit(ids, sp, rid, kvp)
@@ -181,10 +232,24 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                 self.send_header("Connection", "close")
                 self.end_headers()
             try:
+                last_output = last_probe = time.monotonic()
                 while True:
-                    o = q.get(timeout=600)
+                    now = time.monotonic()
+                    if now - last_probe >= 0.5:           # also while outputs keep coming (a non-streaming reply
+                        last_probe = now                  # writes nothing until the end)
+                        if self._client_gone():
+                            raise BrokenPipeError("the client closed the connection")
+                    try:
+                        o = q.get(timeout=0.5)
+                    except queue.Empty:
+                        if time.monotonic() - last_output >= 600:
+                            raise
+                        continue
+                    last_output = time.monotonic()
                     if o is None:
                         raise RuntimeError("engine failure")
+                    if o.finished and o.finish_reason == "ignored":
+                        raise RuntimeError("the request does not fit this instance (prompt longer than the context or the KV pool)")
                     if not out_ids and o.new_token_ids:
                         timeline.emit("First token out of api server", rid, role=aeng.engine.role)
                     out_ids += o.new_token_ids
@@ -215,7 +280,10 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                 resp["choices"][0] = {"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": final.finish_reason}
             if final.kv_transfer_params:
                 resp["kv_transfer_params"] = final.kv_transfer_params
-            self._json(200, resp)
+            try:
+                self._json(200, resp)
+            except (BrokenPipeError, ConnectionResetError):
+                self.close_connection = True          # the client left just before the answer: nothing to tell anybody
 
     return Handler
 

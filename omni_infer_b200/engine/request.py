@@ -45,7 +45,7 @@ class RequestStatus(enum.IntEnum):
 
 
 FINISH_REASON = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH_CAPPED: "length",
-                 RequestStatus.FINISHED_ABORTED: "abort", RequestStatus.FINISHED_IGNORED: "length"}
+                 RequestStatus.FINISHED_ABORTED: "abort", RequestStatus.FINISHED_IGNORED: "ignored"}
 
 
 @dataclass

@@ -203,6 +203,7 @@ class Scheduler:
                     self.kv.blocks_needed(req.num_prompt_tokens + 1) > self.kv.num_blocks - 1:
                 self.waiting.popleft()
                 self._finish(req, RequestStatus.FINISHED_IGNORED)
+                self._capacity_stopped.append(req)     # nobody else would tell the client: reported with the next outputs
                 continue
             computed_blocks, n_cached = ([], 0)
             if req.num_computed_tokens == 0 and not req.block_ids:

@@ -50,6 +50,84 @@ def test_api_server_completions_and_stream():
         InProcessHub.reset()
 
 
+def _status(port, path, body):
+    import urllib.error
+    req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=30) as r:
+            return r.status, json.loads(r.read().decode())
+    except urllib.error.HTTPError as e:
+        return e.code, json.loads(e.read().decode() or "{}")
+
+
+def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_failing_engine():
+    import socket
+    import urllib.error
+    cfg = EngineConfig(block_size=16, num_kv_blocks=8, max_model_len=64, device="cpu")
+    srv, aeng = serve(cfg, "127.0.0.1", 0, block=False)
+    port = srv.server_port
+    eng = aeng.engine
+    try:
+        # ---- input that cannot be served is answered at once, not after a time-out
+        assert _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": "many"})[0] == 400
+        assert _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 4, "top_p": 1.5})[0] == 400
+        assert _status(port, "/v1/completions", {"prompt": [], "max_tokens": 4})[0] == 400
+        code, err = _status(port, "/v1/completions", {"prompt": list(range(70)), "max_tokens": 4})
+        assert code == 400 and "context" in err["error"]
+        # a prompt that fits the context but not the KV pool (7 usable blocks of 16 tokens) is ended by the scheduler,
+        # and the client hears about it
+        big = EngineConfig(block_size=16, num_kv_blocks=4, max_model_len=128, device="cpu")
+        srv2, aeng2 = serve(big, "127.0.0.1", 0, block=False)
+        try:
+            t0 = time.time()
+            code, err = _status(srv2.server_port, "/v1/completions", {"prompt": list(range(100)), "max_tokens": 4})
+            assert code == 500 and "does not fit" in err["error"] and time.time() - t0 < 10
+            assert _status(srv2.server_port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 2})[0] == 200
+        finally:
+            srv2.shutdown()
+            aeng2.stop()
+        # ---- a client that goes away while its (non-streaming) request runs: the request is dropped from the engine
+        real_step = eng.step
+        eng.step = lambda: (time.sleep(0.05), real_step())[1]          # slow the engine down a little
+        s = socket.create_connection(("127.0.0.1", port))
+        body = json.dumps({"prompt": [5, 6, 7], "max_tokens": 60, "ignore_eos": True}).encode()
+        s.sendall(b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: "
+                  + str(len(body)).encode() + b"\r\n\r\n" + body)
+        for _ in range(100):
+            if eng.scheduler.num_running:
+                break
+            time.sleep(0.02)
+        assert eng.scheduler.num_running == 1
+        s.close()
+        for _ in range(200):
+            if not eng.has_unfinished:
+                break
+            time.sleep(0.02)
+        req = next(iter(eng.scheduler.requests.values()))
+        assert not eng.has_unfinished and req.status.name == "FINISHED_ABORTED" and len(req.output_token_ids) < 60
+        eng.step = real_step
+        # ---- an engine whose steps fail: requests get an error, are dropped, and /health turns 503 until a step works
+        assert urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=5).status == 200
+
+        def broken():
+            raise RuntimeError("device lost")
+        eng.step = broken
+        for _ in range(aeng.UNHEALTHY_AFTER):
+            code, err = _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 4})
+            assert code == 500 and "engine failure" in err["error"]
+        assert not eng.scheduler.running and not eng.scheduler.waiting          # nothing left to fail again
+        with pytest.raises(urllib.error.HTTPError) as ei:
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=5)
+        assert ei.value.code == 503
+        eng.step = real_step
+        assert _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 2})[0] == 200
+        assert urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=5).status == 200
+    finally:
+        srv.shutdown()
+        aeng.stop()
+
+
 def test_tokenizer_pool_offloads_long_prompts():
     pool = TokenizerPool(None, vocab_size=300, workers=1, threshold=10, enabled=True)
     try:
