@@ -9,7 +9,8 @@
 //        the original body; a prefill status >= 300 is passed through to the client        (:106-345)
 //     4. the request goes to a decode instance; its response (SSE stream or JSON) is relayed as it arrives while
 //        a body filter feeds token counters to the balancer      (pd_score...c:292-356, weighted_least_active...c:167-243)
-//   Failed connects eject the peer for --fail-timeout seconds and the request is retried on another peer.
+//   Failed connects and 5xx answers eject the peer for --fail-timeout seconds and the request is retried on another
+//   peer (nothing has reached the client at that point); when every attempt fails the last answer is passed through.
 //   GET /health answers 200, GET /metrics lists per-peer load in Prometheus text format.
 //
 // Concurrency: an epoll accept loop feeds a pool of worker threads (blocking sockets with poll timeouts).  With
@@ -264,7 +265,7 @@ static std::string build_prefill_body(const std::string& body) {
 static bool run_prefill(const HttpMessage& req, const std::string& body, HttpMessage& out) {
   const int64_t len = (int64_t)req.body.size();
   g_lb_decode->prefill_started(len);
-  bool ok = false;
+  bool ok = false, have_error_response = false;
   for (int attempt = 0; attempt <= g_cfg.retries && !ok; ++attempt) {
     Ticket t = g_lb_prefill->get_peer(len, now_s());
     int up = connect_to(g_cfg.prefill[t.peer], g_cfg.connect_timeout_s);
@@ -285,11 +286,21 @@ static bool run_prefill(const HttpMessage& req, const std::string& body, HttpMes
                      read_body_all(up, resp, rest, g_cfg.timeout_s);
     close(up);
     if (got) timeline("Proxy got prefill response", req.header("X-Request-Id"));
-    g_lb_prefill->free_peer(t, !got, now_s());
+    // An instance that answers 5xx is reachable but not serving (its engine fails, it is out of memory): that counts
+    // against it like a refused connection, and the request, which has produced nothing yet, goes to another peer.
+    // If every attempt ends that way the last answer is passed through to the client.
+    const bool server_error = got && resp.status >= 500;
+    g_lb_prefill->free_peer(t, !got || server_error, now_s());
+    if (server_error) {
+      LOG(1, "prefill peer %d answered %d", t.peer, resp.status);
+      out = resp;
+      have_error_response = true;
+      continue;
+    }
     if (got) { out = resp; ok = true; }
   }
   g_lb_decode->prefill_finished(len);
-  return ok;
+  return ok || have_error_response;
 }
 
 // ------------------------------------------------------------------------------------------------ stream relay
@@ -306,6 +317,7 @@ struct RelayConn {
   Ticket t;
   std::string rid, tail, pending;
   bool reading = true;
+  bool server_error = false;  // the upstream answered 5xx: relayed, but counted against the peer
   double last_activity = 0;   // monotonic seconds of the last byte moved in either direction
   RelayTag up_tag{this, false}, client_tag{this, true};   // what the event loop gets back from epoll
 };
@@ -385,7 +397,7 @@ class Relay {
     close(c->up);
     shutdown(c->client, SHUT_RDWR);
     close(c->client);
-    g_lb_decode->free_peer(c->t, failed, now_s());
+    g_lb_decode->free_peer(c->t, failed || c->server_error, now_s());
     timeline("Proxy finished request", c->rid);
     n_open_--;
     delete c;
@@ -503,9 +515,19 @@ static bool run_decode(int client, const HttpMessage& req, const std::string& bo
       g_lb_decode->free_peer(t, true, now_s());
       continue;
     }
+    // "HTTP/1.1 5xx": the instance is up but cannot serve.  Nothing has been sent to the client yet, so another
+    // instance gets the request; the last attempt's answer is relayed as it is.  Either way it counts as a failure.
+    const bool server_error = n >= 12 && memcmp(buf, "HTTP/1.", 7) == 0 && buf[8] == ' ' && buf[9] == '5';
+    if (server_error && attempt < g_cfg.retries) {
+      LOG(1, "decode peer %d answered 5xx", t.peer);
+      close(up);
+      g_lb_decode->free_peer(t, true, now_s());
+      continue;
+    }
     timeline("Proxy relays first decode bytes", req.header("X-Request-Id"));
     RelayConn* c = new RelayConn();
     c->up = up; c->client = client; c->t = t; c->rid = req.header("X-Request-Id");
+    c->server_error = server_error;
     scan_counters(*c, buf, (size_t)n);
     if (!send_all(client, buf, (size_t)n, g_cfg.timeout_s)) {   // the client is already gone
       close(up);

@@ -87,6 +87,13 @@ def _make_server(kind, rec, fail=False, chunks=3, gap=0.02):
                 self.send_header("Content-Length", str(len(out)))
                 self.end_headers()
                 self.wfile.write(out)
+            elif fail:
+                out = json.dumps({"error": "decode boom"}).encode()
+                self.send_response(503)
+                self.send_header("Content-Type", "application/json")
+                self.send_header("Content-Length", str(len(out)))
+                self.end_headers()
+                self.wfile.write(out)
             else:
                 self.send_response(200)
                 self.send_header("Content-Type", "text/event-stream")
@@ -257,6 +264,46 @@ def test_prefill_failure_passthrough_and_peer_ejection(proxy_binary):
         proc.wait(timeout=5)
         for s in (p_srv, d_ok, d_srv):
             s.shutdown()
+
+
+def test_instances_that_answer_5xx_are_retried_elsewhere_and_ejected(proxy_binary):
+    """An instance whose engine fails still accepts connections and answers 500 / 503.  Each leg moves on to another
+    instance (nothing has reached the client yet), the failing one is ejected like an unreachable one, and the client
+    gets a normal answer."""
+    rec = _Recorder()
+    bad_p, good_p = _make_server("prefill", rec, fail=True), _make_server("prefill", rec)
+    bad_d, good_d = _make_server("decode", rec, fail=True), _make_server("decode", rec)
+    port = _free_port()
+    proc = _start_proxy(proxy_binary, port, [bad_p.server_port, good_p.server_port], [bad_d.server_port, good_d.server_port],
+                        extra=("--decode-lb", "round_robin", "--prefill-lb", "round_robin"))
+    try:
+        for _ in range(4):
+            status, text = _post(port, {"prompt": "x", "max_tokens": 4})
+            assert status == 200 and "t2" in text and "boom" not in text
+        metrics = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=2).read().decode()
+        assert 'omni_proxy_peer_up{pool="prefill",peer="0"} 0' in metrics and 'omni_proxy_peer_up{pool="decode",peer="0"} 0' in metrics
+        assert 'omni_proxy_served_total{pool="prefill",peer="1"} 4' in metrics
+        assert 'omni_proxy_served_total{pool="decode",peer="1"} 4' in metrics
+        # each failing instance was tried once, then left alone while it is ejected
+        assert sum(1 for k, _, b in rec.requests if k == "prefill") <= 4 + 1 + 1
+    finally:
+        proc.terminate()
+        proc.wait(timeout=5)
+        for srv in (bad_p, good_p, bad_d, good_d):
+            srv.shutdown()
+    # when every decode instance fails, the last answer reaches the client
+    rec2 = _Recorder()
+    p_srv, only_bad = _make_server("prefill", rec2), _make_server("decode", rec2, fail=True)
+    port = _free_port()
+    proc = _start_proxy(proxy_binary, port, [p_srv.server_port], [only_bad.server_port])
+    try:
+        status, text = _post(port, {"prompt": "x", "max_tokens": 4})
+        assert status == 503 and "decode boom" in text
+    finally:
+        proc.terminate()
+        proc.wait(timeout=5)
+        p_srv.shutdown()
+        only_bad.shutdown()
 
 
 def test_proxy_under_thread_sanitizer_serves_concurrent_requests(tmp_path):
