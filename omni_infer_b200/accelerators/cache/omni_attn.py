@@ -108,19 +108,38 @@ class OmniAttnState:
     def is_compressed(self, layer_idx: int) -> bool:
         return layer_idx < len(self.pattern) and bool(self.pattern[layer_idx])
 
-    # ---- prefill: where each prompt token goes in the window (or -1)
-    def prefill_slots(self, window_blocks: list, start: int, n: int, prompt_len: int) -> list:
-        bs, st, rt = self.block_size, self.cfg.sink * self.block_size, self.cfg.recent * self.block_size
+    # ---- prefill: where each token goes in the window (or -1)
+    def window_position(self, p: int, prompt_len: int):
+        """Window position that the token at sequence position ``p`` is written to, or None for a prompt token that is
+        not kept.  Prompt tokens follow the prefill rule, generated ones the decode ring."""
+        st, rt = self.cfg.sink * self.block_size, self.cfg.recent * self.block_size
         cap = st + rt
+        if p >= prompt_len:
+            return compute_omni_attn_metadata_ref(p + 1, prompt_len, self.block_size, self.cfg.sink, self.cfg.recent)[0]
+        if prompt_len <= cap or p < st:
+            return p
+        if p >= prompt_len - rt:
+            return st + (p - (prompt_len - rt))
+        return None
+
+    def prefill_slots(self, window_blocks: list, start: int, n: int, prompt_len: int, total_len: Optional[int] = None) -> list:
+        """Slots of the tokens ``[start, start + n)`` of a prefill over ``total_len`` tokens (default: the prompt).  A
+        request that was preempted recomputes its prompt *and* what it had generated (``total_len > prompt_len``); the
+        generated tokens then go where the decode steps had put them, and a token whose window entry a later one of the
+        same prefill takes is not written at all (the scatter has no order), so that the window ends up as the decode
+        steps had left it."""
+        bs = self.block_size
+        total = prompt_len if total_len is None else max(total_len, prompt_len)
+        last_writer = {}
+        if total > prompt_len:
+            for p in range(total):
+                w = self.window_position(p, prompt_len)
+                if w is not None:
+                    last_writer[w] = p
         out = []
         for p in range(start, start + n):
-            if prompt_len <= cap:
-                w = p
-            elif p < st:
-                w = p
-            elif p >= prompt_len - rt:
-                w = st + (p - (prompt_len - rt))
-            else:
+            w = self.window_position(p, prompt_len)
+            if w is None or (last_writer and last_writer.get(w) != p):
                 out.append(-1)
                 continue
             out.append(window_blocks[w // bs] * bs + w % bs)

@@ -343,7 +343,7 @@ class ModelRunner:
             for s in so.scheduled:
                 r = s.request
                 oslots += self.omni.prefill_slots(r.omni_block_ids, r.num_computed_tokens, s.num_scheduled_tokens,
-                                                  r.num_prompt_tokens)
+                                                  r.num_prompt_tokens, total_len=r.num_tokens)
             md.omni = {"pattern": self.omni.pattern, "slot_mapping": self._to_dev(oslots, torch.int64)}
         return self._to_dev(ids, torch.int64), md
 

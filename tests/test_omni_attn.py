@@ -72,3 +72,84 @@ def test_engine_with_omni_attention():
     # beyond the window the compressed layer forgets the middle: still runs, output may differ
     long_out, _ = run(True, 80, prompts[:1])
     assert len(long_out[0]) == 80
+
+
+def test_window_holds_sink_and_most_recent_tokens_whatever_the_history():
+    """Replay of the writes into one request's window (64 entries: 16 sink + 48 recent): prefill of any prompt length,
+    decode steps, and a recompute after a preemption (prompt + generated tokens in one or several prefill chunks).  At
+    every point the window must hold the first 16 tokens and the most recent ones, each exactly once."""
+    import random
+    bs, sink, recent = 16, 1, 3
+    st_, rt, cap = 16, 48, 64
+    state = OmniAttnState(OmniAttnConfig(sink, recent, 0.2, [0, 1]), bs)
+    blocks = [7, 3, 9, 5]                                   # window blocks in any order
+
+    def where(slot):
+        return blocks.index(slot // bs) * bs + slot % bs
+
+    def expect(window, L):
+        held = sorted(v for v in window if v is not None)
+        want = list(range(L)) if L <= cap else list(range(st_)) + list(range(L - rt, L))
+        assert held == want, (L, held[:20], want[:20])
+
+    rnd = random.Random(3)
+    for prompt_len in [1, 5, 16, 17, 63, 64, 65, 80, 111, 112, 113, 200]:
+        for n_gen_before_preempt in [0, 1, 7, 49, 130]:
+            window = [None] * cap
+            # ---- first life: prefill the prompt (in two chunks), then decode
+            cut = rnd.randint(0, prompt_len)
+            for start, n in ((0, cut), (cut, prompt_len - cut)):
+                for i, s in enumerate(state.prefill_slots(blocks, start, n, prompt_len)):
+                    if s >= 0:
+                        window[where(s)] = start + i
+            expect(window, prompt_len)
+            L = prompt_len
+            for _ in range(n_gen_before_preempt):
+                L += 1
+                pos, eff = compute_omni_attn_metadata_ref(L, prompt_len, bs, sink, recent)
+                window[pos] = L - 1
+                assert eff == min(L, cap)
+                expect(window, L)
+            # ---- preempted: the window is lost; prompt + generated tokens are prefilled again, in chunks
+            redo = [None] * cap
+            total = L
+            pieces, at = [], 0
+            while at < total:
+                n = rnd.randint(1, max(1, total // 2))
+                pieces.append((at, min(n, total - at)))
+                at += pieces[-1][1]
+            rnd.shuffle(pieces)                              # a scatter has no order: neither may the result depend on it
+            for start, n in pieces:
+                slots = state.prefill_slots(blocks, start, n, prompt_len, total_len=total)
+                assert len(slots) == n
+                for i, s in enumerate(slots):
+                    if s >= 0:
+                        assert redo[where(s)] is None, "two tokens of one prefill were sent to the same window entry"
+                        redo[where(s)] = start + i
+            assert redo == window, (prompt_len, n_gen_before_preempt)
+            # ---- and decoding goes on from there
+            for _ in range(60):
+                L += 1
+                pos, _ = compute_omni_attn_metadata_ref(L, prompt_len, bs, sink, recent)
+                redo[pos] = L - 1
+                expect(redo, L)
+
+
+def test_engine_with_omni_attention_survives_preemption():
+    """A KV pool so small that running requests are preempted and recomputed while Omni-Attention is on and the
+    sequences (80 tokens) have outgrown the 64-token window: the recompute rebuilds the window as the decode steps had
+    left it, so the tokens equal those of a run that never preempts."""
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1024, (20,), generator=g).tolist() for _ in range(3)]
+
+    def run(num_blocks):
+        e = EngineCore(EngineConfig(block_size=16, num_kv_blocks=num_blocks, max_model_len=256, device="cpu", max_num_seqs=4,
+                                    enable_omni_attn=True, omni_attn_config={"sink": 1, "recent": 3, "pattern": [0, 1]}))
+        ids = [e.add_request(p, SamplingParams(max_tokens=60)) for p in prompts]
+        outs = e.run_until_done()
+        return [outs[i] for i in ids], e
+
+    roomy, _ = run(64)
+    tight, eng = run(13)                                    # 12 usable blocks for 3 x 80 tokens: somebody has to go
+    assert eng.scheduler.stats["preemptions"] > 0
+    assert tight == roomy
