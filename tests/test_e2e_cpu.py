@@ -107,3 +107,37 @@ def test_qwen_models_match_their_fp32_oracle(name, over):
     outs = llm.generate(prompts, SamplingParams(max_tokens=6))
     for p, o in zip(prompts, outs):
         assert o == ref.greedy(p, 6)
+
+
+COMBOS = [
+    dict(num_kv_blocks=12, enable_prefix_caching=True, enable_chunked_prefill=True, max_num_batched_tokens=24),
+    dict(num_kv_blocks=12, num_step=3, enable_prefix_caching=True),
+    dict(num_kv_blocks=14, num_speculative_tokens=1, num_step=2, mtp=True),
+    dict(num_kv_blocks=14, num_speculative_tokens=1, enable_chunked_prefill=True, max_num_batched_tokens=20, mtp=True),
+    dict(num_kv_blocks=13, async_schedule=True, num_step=2),
+    dict(num_kv_blocks=13, num_speculative_tokens=1, num_step=2, enable_prefix_caching=True, async_schedule=True, mtp=True),
+]
+
+
+COMBOS += [dict(c, model="tiny-qwen3-moe") for c in COMBOS if not c.get("mtp")]
+
+
+@pytest.mark.parametrize("combo", COMBOS, ids=lambda c: "-".join(f"{k}={v}" for k, v in c.items()))
+def test_feature_combinations_under_memory_pressure_match_the_plain_engine(combo):
+    """Features that each pass alone, together and with a KV pool small enough to force preemption and recompute:
+    prefix cache + chunked prefill, multi-step, MTP drafts, asynchronous scheduling.  Greedy output must not change."""
+    combo = dict(combo)
+    model = combo.pop("model", "tiny-deepseek-v3")
+    over = {"num_nextn_predict_layers": 1} if combo.pop("mtp", False) else {}
+    g = torch.Generator().manual_seed(9)
+    shared = torch.randint(0, 1024, (32,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 1024, (int(n),), generator=g).tolist() for n in (3, 9, 17)]
+    prompts += [torch.randint(0, 1024, (int(n),), generator=g).tolist() for n in (21, 40)]
+    base = LLM(model, block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu", model_overrides=over)
+    want = base.generate(prompts, SamplingParams(max_tokens=18))
+    llm = LLM(model, block_size=16, max_model_len=128, device="cpu", max_num_seqs=4, model_overrides=over, **combo)
+    got = llm.generate(prompts, SamplingParams(max_tokens=18))
+    assert got == want
+    st = llm.engine.scheduler.stats
+    assert st["preemptions"] > 0, st                     # the pool really was too small
+    assert llm.engine.kv.num_free_blocks == combo["num_kv_blocks"] - 1
