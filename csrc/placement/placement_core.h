@@ -396,6 +396,10 @@ class Placement {
   // the selector.  Returns the number of experts replaced.
   int do_placement_optimizer();
   int rounds() const { return rounds_; }
+  // Rounds whose changes are complete on every rank (published after the round's closing barrier) and wait to be, or
+  // have been, applied.  Ranks apply a round in the same inference step: the embedding process exchanges this counter
+  // (minimum over the ranks) and calls do_placement_optimizer() when the minimum has moved past what it has applied.
+  int ready_rounds() const { return ready_rounds_; }
   int skipped_instructions() const { return skipped_; }
   std::vector<ChangeInstruction> last_instructions() const;
   // the balancer's moving average of position loads: saved at shutdown and restored at start so that a restart does
@@ -417,11 +421,12 @@ class Placement {
   std::mutex mu_;
   std::mutex ema_mu_;   // the optimizer's history: a round updates it, snapshot / restore read and write it
   std::condition_variable cv_;
-  std::vector<PendingApply> pending_;
+  std::vector<PendingApply> pending_;   // complete rounds, visible to the inference thread
+  std::vector<PendingApply> staged_;    // the round in progress
   std::vector<ChangeInstruction> last_;
   std::vector<int> stage_used_;                   // staging buffers taken in the current round, per rank (same on all)
   std::set<std::pair<int, int>> round_touched_;   // (layer, position) changed by an instruction of the current round
-  std::atomic<int> rounds_{0}, skipped_{0};
+  std::atomic<int> rounds_{0}, skipped_{0}, ready_rounds_{0};
 };
 
 }  // namespace omni_placement

@@ -181,7 +181,7 @@ void Placement::loop() {
     {
       // the previous round must have been applied by the inference thread before new data is staged
       std::unique_lock<std::mutex> lk(mu_);
-      cv_.wait(lk, [&] { return should_stop_ || pending_.empty(); });
+      cv_.wait(lk, [&] { return should_stop_ || pending_.empty(); });   // (staged_ is empty between rounds)
     }
     // The threads of all ranks leave together: a round is a sequence of collectives, so a thread that simply
     // returned when its own rank asked it to stop would leave the others blocked in the next one (and their stop()
@@ -226,6 +226,10 @@ int Placement::run_round() {
     instr = optimizer_->optimize();
   }
   last_ = instr;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    staged_.clear();                                      // leftovers of a round that ended in an exception
+  }
   int done = 0;
   stage_used_.assign((size_t)(dist_ != nullptr ? dist_->world() : mapping_->world()), 0);
   round_touched_.clear();
@@ -242,6 +246,16 @@ int Placement::run_round() {
     if (execute(ins)) ++done; else ++skipped_;
   }
   if (dist_ != nullptr) dist_->barrier();                 // every rank has finished staging this round
+  {
+    // Only now may the inference thread see the round: before the barrier another rank could still be waiting for
+    // bytes this round sends it, and a rank that applied (and re-routed tokens to) a replica whose holder has not
+    // received it yet would read an empty slot.  The apply step itself is agreed between the ranks by the caller
+    // (ready_rounds() of every rank, see do_placement_optimizer).
+    std::lock_guard<std::mutex> lk(mu_);
+    pending_.insert(pending_.end(), staged_.begin(), staged_.end());
+    staged_.clear();
+    ++ready_rounds_;
+  }
   ++rounds_;
   return done;
 }
@@ -288,7 +302,7 @@ bool Placement::execute(const ChangeInstruction& ins) {
   // 3. data movement into the staging ring (only the ranks involved)
   std::lock_guard<std::mutex> lk(mu_);
   if (ins.type == OperationType::REMOVE) {
-    pending_.push_back({ins.layer_idx, sp % S, -1, -1, sp, ins.source_expert_id});
+    staged_.push_back({ins.layer_idx, sp % S, -1, -1, sp, ins.source_expert_id});
     round_touched_.insert({ins.layer_idx, sp});
     return true;
   }
@@ -314,10 +328,10 @@ bool Placement::execute(const ChangeInstruction& ins) {
     // replacement from the host replica: nothing travels between ranks and no staging buffer is taken; the rank
     // that receives an expert copies it host -> device when the change is applied between two steps
     if (ins.type == OperationType::SWAP) {
-      pending_.push_back({ins.layer_idx, sp % S, -1, ins.target_expert_id, sp, ins.source_expert_id, i_am_src});
-      pending_.push_back({ins.layer_idx, tp % S, -1, ins.source_expert_id, tp, ins.target_expert_id, i_am_dst});
+      staged_.push_back({ins.layer_idx, sp % S, -1, ins.target_expert_id, sp, ins.source_expert_id, i_am_src});
+      staged_.push_back({ins.layer_idx, tp % S, -1, ins.source_expert_id, tp, ins.target_expert_id, i_am_dst});
     } else {
-      pending_.push_back({ins.layer_idx, tp % S, -1, ins.source_expert_id, tp, ins.target_expert_id, i_am_dst});
+      staged_.push_back({ins.layer_idx, tp % S, -1, ins.source_expert_id, tp, ins.target_expert_id, i_am_dst});
     }
     return true;
   }
@@ -343,10 +357,10 @@ bool Placement::execute(const ChangeInstruction& ins) {
   }
   // every rank records the mapping change; only the receivers carry a staging buffer
   if (ins.type == OperationType::SWAP) {
-    pending_.push_back({ins.layer_idx, sp % S, i_am_src ? stage : -1, ins.target_expert_id, sp, ins.source_expert_id});
-    pending_.push_back({ins.layer_idx, tp % S, i_am_dst ? stage : -1, ins.source_expert_id, tp, ins.target_expert_id});
+    staged_.push_back({ins.layer_idx, sp % S, i_am_src ? stage : -1, ins.target_expert_id, sp, ins.source_expert_id});
+    staged_.push_back({ins.layer_idx, tp % S, i_am_dst ? stage : -1, ins.source_expert_id, tp, ins.target_expert_id});
   } else {
-    pending_.push_back({ins.layer_idx, tp % S, i_am_dst ? stage : -1, ins.source_expert_id, tp, ins.target_expert_id});
+    staged_.push_back({ins.layer_idx, tp % S, i_am_dst ? stage : -1, ins.source_expert_id, tp, ins.target_expert_id});
   }
   return true;
 }
@@ -485,6 +499,7 @@ int omni_pl_placement_run_round(void* p) {
 }
 int omni_pl_do_placement_optimizer(void* p) { return ((Placement*)p)->do_placement_optimizer(); }
 int omni_pl_placement_rounds(void* p) { return ((Placement*)p)->rounds(); }
+int omni_pl_placement_ready_rounds(void* p) { return ((Placement*)p)->ready_rounds(); }
 int omni_pl_placement_skipped(void* p) { return ((Placement*)p)->skipped_instructions(); }
 int omni_pl_placement_last_instructions(void* p, int* out, int max_n) {
   auto v = ((Placement*)p)->last_instructions();

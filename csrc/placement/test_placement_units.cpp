@@ -13,6 +13,7 @@
 #include <numeric>
 #include <stdexcept>
 #include <string>
+#include <chrono>
 #include <thread>
 #include <vector>
 
@@ -993,6 +994,43 @@ TEST(manager_disagreeing_ranks_skip_the_instruction) {
   // the next round, with honest tuples, goes through
   c.counts[0][0] += 1000;
   CHECK(c.round() >= 1 && c.held(1, 2) == 0.f && c.maps[0]->expert_at(0, 5) == 0);
+}
+
+// a transport whose closing barrier of the round waits for the test's signal
+class HeldBarrier : public FakeDistribution {
+ public:
+  using FakeDistribution::FakeDistribution;
+  std::atomic<bool> release{false};
+  std::atomic<int> at_barrier{0};
+  void barrier() override {
+    ++at_barrier;
+    while (!release.load()) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    FakeDistribution::barrier();
+  }
+};
+
+TEST(manager_shows_a_round_to_the_inference_thread_only_when_every_rank_has_staged_it) {
+  Cluster c(2, 4);
+  c.counts[0] = {1000, 10, 0};
+  c.counts[1] = {10, 10, 0};
+  // rank 1 gets the held transport (it is the receiver of the replica of expert 0)
+  auto* held = new HeldBarrier(c.hub, 1, c.ws[1]->expert_bytes());
+  c.dists[1].reset(held);
+  c.pls[1].reset(new Placement(c.maps[1].get(), c.ws[1].get(), c.acts[1].get(), held, 10, 3600.0));
+  std::thread t0([&] { c.pls[0]->run_round(); });
+  std::thread t1([&] { c.pls[1]->run_round(); });
+  for (int i = 0; i < 2000 && held->at_barrier.load() == 0; ++i) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+  CHECK(held->at_barrier.load() == 1);               // rank 1 has received the expert and stands before the barrier
+  // both inference threads look for work now: there is none yet, although the bytes are already in rank 1's staging
+  CHECK(c.pls[0]->ready_rounds() == 0 && c.pls[1]->ready_rounds() == 0);
+  CHECK(c.pls[0]->do_placement_optimizer() == 0 && c.pls[1]->do_placement_optimizer() == 0);
+  CHECK(c.maps[0]->expert_at(0, 5) == -1 && c.maps[0]->selector(0, 0) == 0 && c.held(1, 2) == -1.f);
+  held->release = true;
+  t0.join();
+  t1.join();
+  CHECK(c.pls[0]->ready_rounds() == 1 && c.pls[1]->ready_rounds() == 1);
+  CHECK(c.pls[0]->do_placement_optimizer() == 0 && c.pls[1]->do_placement_optimizer() == 1);
+  CHECK(c.maps[0]->expert_at(0, 5) == 0 && c.maps[1]->selector(0, 0) == 5 && c.held(1, 2) == 0.f && c.views_agree());
 }
 
 TEST(manager_history_survives_a_restart) {

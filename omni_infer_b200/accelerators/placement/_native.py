@@ -50,6 +50,7 @@ def lib():
             ("omni_pl_placement_run_round", ci, [vp]),
             ("omni_pl_do_placement_optimizer", ci, [vp]),
             ("omni_pl_placement_rounds", ci, [vp]),
+            ("omni_pl_placement_ready_rounds", ci, [vp]),
             ("omni_pl_placement_skipped", ci, [vp]),
             ("omni_pl_placement_last_instructions", ci, [vp, vp, ci]),
             ("omni_pl_weights_init_shm", ci, [vp, ctypes.c_char_p, ci, ci]),

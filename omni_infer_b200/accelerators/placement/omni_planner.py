@@ -4,9 +4,10 @@
 * ``selector(layer)`` - int32 device row mapping logical to physical expert ids; the router kernel applies it
   (the reference does ``F.embedding(topk_ids, expert_mapping)`` in ``plan``).
 * ``activation_counts(layer)`` - int64 device row incremented by the router kernel per physical position.
-* ``place_experts()`` - called by the runner before every step: every ``apply_interval`` steps the ranks agree
-  (MIN over the host group) on whether a staged re-placement round is complete everywhere and, if so, apply it at
-  the same step boundary (weights copied from staging, selector refreshed).
+* ``place_experts(min_ready)`` - called by the runner before every step, right after the ranks' per-step agreement on
+  the host group, which also carries the minimum over the ranks of ``ready_rounds()``: a re-placement round is applied
+  (weights copied from staging, selector refreshed) in the step in which every rank has it complete, by all ranks at
+  that same step boundary.
 * ``init_dram_weights(model)`` - registers the expert tensors (w13 / w2 and their scales) of every local slot.
 * ``start_dynamic_optimize_expert_load_balance()`` - starts the C++ background thread.
 
@@ -74,6 +75,7 @@ class OmniPlanner(metaclass=_Singleton):
         self.sent_counts = torch.zeros(num_moe_layers, self.num_positions, dtype=torch.int64, device=self.device)
         self.local_counts = torch.zeros(num_moe_layers, self.slots_per_rank, dtype=torch.int64, device=self.device)
         self._step = 0
+        self._applied_round = 0      # placement rounds applied so far (compared with ready_rounds of all ranks)
         self.applied_total = 0    # experts replaced since start (all rounds)
         self._weights = self._act = self._dist = self._placement = None
         self._keep = []          # ctypes callbacks must outlive the C++ objects
@@ -348,12 +350,24 @@ class OmniPlanner(metaclass=_Singleton):
         self.sync_activation_counts()
         return nat.lib().omni_pl_placement_run_round(self._ensure_placement())
 
-    def place_experts(self) -> int:
-        """Between steps: keep the collector's input fresh and apply a staged round when every rank has one."""
+    def ready_rounds(self) -> int:
+        """Placement rounds that are complete on this rank (staged on every rank, published after the round's barrier)."""
+        return int(nat.lib().omni_pl_placement_ready_rounds(self._placement)) if self._placement else 0
+
+    def place_experts(self, min_ready: Optional[int] = None) -> int:
+        """Between steps: keep the collector's input fresh and apply a finished round.  ``min_ready`` = the smallest
+        ``ready_rounds()`` of any rank, exchanged by the caller: a round is applied when every rank has it complete, by
+        all of them in the same step.  Without it (one rank, or a caller that steps all ranks itself) the rank goes by
+        its own counter."""
         self._step += 1
-        if self._placement is None or self._step % self.apply_interval:
+        if self._placement is None:
             return 0
-        self.sync_activation_counts()
+        if self._step % self.apply_interval == 0:
+            self.sync_activation_counts()
+        ready = self.ready_rounds() if min_ready is None else int(min_ready)
+        if ready <= self._applied_round:
+            return 0
+        self._applied_round = ready
         return self.apply_pending()
 
     def apply_pending(self) -> int:

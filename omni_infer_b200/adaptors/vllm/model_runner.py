@@ -161,7 +161,10 @@ class ModelRunner:
         if ps.world_size == 1 or not self.model_cfg.is_moe:
             return None
         import torch.distributed as dist
-        t = torch.tensor([num_tokens, rounds, 1 if has_work else 0], dtype=torch.int64)
+        # fourth value: minus the number of placement rounds this rank has complete, so that the MAX gives the minimum
+        # over the ranks - a round is applied in the step in which every rank has it (see _place_experts)
+        ready = self.planner.ready_rounds() if self.planner is not None else 0
+        t = torch.tensor([num_tokens, rounds, 1 if has_work else 0, -ready], dtype=torch.int64)
         work = dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ps.group("cpu").group, async_op=True)
         return t, work
 
@@ -171,6 +174,7 @@ class ModelRunner:
         model rounds all ranks run.  ``peers_busy`` tells the engine loop whether any rank still has requests."""
         ps = get_parallel_state()
         if handle is None:
+            self._place_experts(None)
             self.peers_busy = False
             self._ep_fused_now = getattr(self, "ep_ctx", None) is not None
             ps.step_max_tokens = 0
@@ -178,6 +182,7 @@ class ModelRunner:
         t, work = handle
         work.wait()
         max_tokens, max_rounds, any_work = int(t[0]), int(t[1]), bool(int(t[2]))
+        self._place_experts(-int(t[3]))
         self.peers_busy = any_work
         ps.step_max_tokens = max_tokens        # layers sharded over a sub-group pad their rows to this
         ctx = getattr(self, "ep_ctx", None)
@@ -186,6 +191,14 @@ class ModelRunner:
         for m in getattr(self, "_moe_layers", ()):
             m.ep_ctx = ctx if fused else None
         return max(rounds, max_rounds)
+
+    def _place_experts(self, min_ready) -> None:
+        """Between two steps, right after the ranks' agreement: apply the expert moves of a finished placement round.
+        ``min_ready`` is the smallest number of complete rounds on any rank, so every rank applies a round in the same
+        step; a rank that switched its selector to a replica before the holder has copied the weights in would send
+        tokens to an empty slot.  (One rank alone passes None and goes by its own counter.)"""
+        if self.planner is not None:
+            self.planner.place_experts(min_ready)
 
     def _agree_ep_path(self, num_tokens: int, rounds: int = 1, has_work: bool = True) -> int:
         return self._agree_finish(self._agree_start(num_tokens, rounds, has_work), rounds)
@@ -474,8 +487,6 @@ class ModelRunner:
                 fin_send, fin_recv = self.kv_connector.get_finished(so.finished_req_ids)
                 failed = self.kv_connector.take_failed()
             return ModelRunnerOutput([], [[]], None, fin_send, fin_recv, failed)
-        if self.planner is not None:
-            self.planner.place_experts()
         reqs = [s.request for s in so.scheduled]
         if so.is_prefill:
             out = self._run_prefill(so, reqs)

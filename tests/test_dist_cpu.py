@@ -387,6 +387,47 @@ def _placement_round_replica(rank, world):
     return _placement_round(rank, world, host_replica=f"/omni_pytest_replica_{os.getppid()}")
 
 
+def _background_placement_engine(rank, world, dynamic):
+    """Decode while the planner's own thread runs placement rounds every 50 ms and the runner applies them between
+    steps: skewed routing makes the balancer move experts all the time."""
+    import time as _t
+    from omni_infer_b200.accelerators.placement import OmniPlanner
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    pc = {"max_redundant_per_rank": 2, "enable_dynamic": True, "period_s": 0.05, "apply_interval": 1} if dynamic else None
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=64, max_model_len=160, device="cpu", seed=3,
+                                  placement_config=pc, model_overrides={"router_skew": {"s": 1.2, "strength": 6.0, "seed": 0}}))
+    g = torch.Generator().manual_seed(11 + rank)            # different requests on every rank
+    prompts = [torch.randint(0, 1024, (20 + i,), generator=g).tolist() for i in range(3)]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=70, ignore_eos=True)) for p in prompts]
+    outs = {}
+    for _ in range(400):
+        if not eng.has_unfinished and not eng.peers_busy:
+            break
+        for r in eng.step():
+            outs.setdefault(r.request_id, []).extend(r.new_token_ids)
+        if dynamic:
+            _t.sleep(0.01)                                   # give the background rounds time to happen during the run
+    planner = eng.worker.runner.planner
+    applied = planner.applied_total if planner is not None else 0
+    rounds = planner.ready_rounds() if planner is not None else 0
+    if dist.is_initialized():
+        dist.barrier()
+    if planner is not None:
+        OmniPlanner.cleanup()
+    return {"outs": [outs[i] for i in ids], "applied": applied, "rounds": rounds}
+
+
+def test_background_placement_rounds_never_change_the_tokens():
+    """Experts are copied and re-routed between steps while requests decode.  A rank that re-routed to a replica before
+    its holder had the weights would compute with an empty expert: every token must equal the run without placement."""
+    plain = _spawn(_background_placement_engine, 2, False)
+    moved = _spawn(_background_placement_engine, 2, True)
+    assert moved[0]["applied"] + moved[1]["applied"] > 0 and moved[0]["rounds"] >= 2
+    for r in range(2):
+        assert moved[r]["outs"] == plain[r]["outs"], r
+
+
 def test_dynamic_placement_round_moves_a_hot_expert():
     out = _spawn(_placement_round, 2)
     r0, r1 = out[0], out[1]
