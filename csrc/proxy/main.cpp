@@ -62,6 +62,7 @@ struct Config {
   double timeout_s = 600.0, connect_timeout_s = 3.0;
   int log_level = 1;
   bool timeline = false;   // one "<<<Action" line per request stage on stderr, in the engine's format
+  long long max_body_bytes = 64ll << 20;   // larger request bodies are refused with 413
 };
 
 static Config g_cfg;
@@ -567,7 +568,37 @@ static void handle_connection(int client) {
   HttpMessage req;
   if (!read_head(client, req, rest, 30.0)) { close(client); return; }
   const std::string cl = req.header("Content-Length");
-  if (!cl.empty() && !read_exact(client, req.body, (size_t)atoll(cl.c_str()), rest, 60.0)) { close(client); return; }
+  if (!cl.empty()) {
+    // the length is the client's claim: refuse what is not a number or more than a request can reasonably be, instead
+    // of buffering whatever arrives
+    char* end = nullptr;
+    errno = 0;
+    const long long n = strtoll(cl.c_str(), &end, 10);
+    if (end == cl.c_str() || *end != '\0' || errno != 0 || n < 0) {
+      send_simple(client, 400, "Bad Request", "{\"error\":\"invalid Content-Length\"}");
+      close(client);
+      return;
+    }
+    if (n > g_cfg.max_body_bytes) {
+      send_simple(client, 413, "Payload Too Large", "{\"error\":\"request body too large\"}");
+      close(client);
+      return;
+    }
+    if (!read_exact(client, req.body, (size_t)n, rest, 60.0)) { close(client); return; }
+  } else if (strcasecmp(req.header("Transfer-Encoding").c_str(), "chunked") == 0) {
+    // a chunked request body is put together here and forwarded with a Content-Length
+    if (!read_body_all(client, req, rest, 60.0) || (long long)req.body.size() > g_cfg.max_body_bytes) {
+      send_simple(client, 400, "Bad Request", "{\"error\":\"unreadable chunked body\"}");
+      close(client);
+      return;
+    }
+    req.remove_header("Transfer-Encoding");
+  }
+  if (req.method.empty() || req.path.empty() || req.path[0] != '/') {
+    send_simple(client, 400, "Bad Request", "{\"error\":\"malformed request line\"}");
+    close(client);
+    return;
+  }
   if (req.method == "GET" && req.path == "/health") { send_simple(client, 200, "OK", "{\"status\":\"ok\"}"); close(client); return; }
   if (req.method == "GET" && req.path == "/metrics") { send_simple(client, 200, "OK", metrics_text(), "text/plain; version=0.0.4"); close(client); return; }
   if (req.header("X-Request-Id").empty()) req.set_header("X-Request-Id", make_request_id());
@@ -712,6 +743,7 @@ int main(int argc, char** argv) {
     else if (a == "--workers") g_cfg.workers = std::max(1, atoi(val().c_str()));
     else if (a == "--threads") g_cfg.threads = std::max(1, atoi(val().c_str()));
     else if (a == "--retries") g_cfg.retries = atoi(val().c_str());
+    else if (a == "--max-body-mb") g_cfg.max_body_bytes = (long long)(atof(val().c_str()) * (1 << 20));
     else if (a == "--timeout") g_cfg.timeout_s = atof(val().c_str());
     else if (a == "--log-level") g_cfg.log_level = atoi(val().c_str());
     else if (a == "--timeline") g_cfg.timeline = true;

@@ -117,12 +117,12 @@ def proxy_binary():
     return str(pb())
 
 
-def _start_proxy(binary, port, prefill_ports, decode_ports, extra=()):
+def _start_proxy(binary, port, prefill_ports, decode_ports, extra=(), capture=False):
     cmd = [binary, "--listen", f"127.0.0.1:{port}", "--decode-servers", ",".join(f"127.0.0.1:{p}" for p in decode_ports),
            "--log-level", "0", "--fail-timeout", "30", *extra]
     if prefill_ports:
         cmd += ["--prefill-servers", ",".join(f"127.0.0.1:{p}" for p in prefill_ports)]
-    proc = subprocess.Popen(cmd)
+    proc = subprocess.Popen(cmd, stderr=subprocess.PIPE if capture else None)
     for _ in range(100):
         try:
             urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=0.5).read()
@@ -304,6 +304,84 @@ def test_instances_that_answer_5xx_are_retried_elsewhere_and_ejected(proxy_binar
         proc.wait(timeout=5)
         p_srv.shutdown()
         only_bad.shutdown()
+
+
+def test_malformed_requests_are_refused_and_the_proxy_stays_up(tmp_path):
+    """The proxy built with AddressSanitizer + UBSan, fed request lines, headers and lengths that are not what it
+    expects: each gets a 4xx (or the connection closed), none brings it down, and a normal request still works after."""
+    import socket
+    exe = str(tmp_path / "omni_proxy_asan")
+    srcs = [os.path.join(SRC, f) for f in ("main.cpp", "lb.cpp")]
+    res = subprocess.run(["g++", "-O1", "-g", "-std=c++17", "-pthread", "-fsanitize=address,undefined", "-I", SRC, "-o", exe, *srcs],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    rec = _Recorder()
+    p_srv, d_srv = _make_server("prefill", rec), _make_server("decode", rec)
+    port = _free_port()
+    proc = _start_proxy(exe, port, [p_srv.server_port], [d_srv.server_port], extra=("--max-body-mb", "1"), capture=True)
+
+    def raw(data: bytes, read=True, timeout=5.0):
+        s = socket.create_connection(("127.0.0.1", port), timeout=timeout)
+        try:
+            s.sendall(data)
+            if not read:
+                return b""
+            s.settimeout(timeout)
+            out = b""
+            try:
+                while True:
+                    chunk = s.recv(65536)
+                    if not chunk:
+                        break
+                    out += chunk
+            except socket.timeout:
+                pass
+            return out
+        finally:
+            s.close()
+
+    def status(resp: bytes) -> int:
+        return int(resp.split(b" ", 2)[1]) if resp.startswith(b"HTTP/1.") else 0
+
+    try:
+        body = b'{"prompt": "x", "max_tokens": 4}'
+        post = b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\n"
+        assert status(raw(post + b"Content-Length: -5\r\n\r\n" + body)) == 400
+        assert status(raw(post + b"Content-Length: 12abc\r\n\r\n" + body)) == 400
+        assert status(raw(post + b"Content-Length: 99999999999999999999\r\n\r\n" + body)) == 400
+        assert status(raw(post + b"Content-Length: 5000000\r\n\r\n" + body)) == 413          # more than --max-body-mb
+        assert status(raw(b"\r\n\r\n")) in (0, 400)        # nothing to answer to: closed
+        assert status(raw(b"GARBAGE\r\n\r\n")) == 400
+        assert status(raw(b"POST nopath HTTP/1.1\r\nContent-Length: 0\r\n\r\n")) == 400
+        raw(b"\x00\xff\xfe" * 1000 + b"\r\n\r\n")                                           # binary noise
+        raw(b"POST /v1/completions HTTP/1.1\r\n" + b"X-Pad: " + b"a" * 200000 + b"\r\n\r\n")     # a very long header
+        raw(post + b"Content-Length: 100\r\n\r\n" + body, read=False)                            # body shorter than announced, then gone
+        # not JSON at all: forwarded as it is (the instance decides), the proxy itself does not care
+        r = raw(post + b"Content-Length: 9\r\n\r\nnot json!")
+        assert status(r) in (200, 400, 500, 502)
+        # a chunked request body is put together and forwarded with a length
+        chunked = post + b"Transfer-Encoding: chunked\r\n\r\n" + b"10\r\n" + body[:16] + b"\r\n" + \
+            hex(len(body) - 16)[2:].encode() + b"\r\n" + body[16:] + b"\r\n0\r\n\r\n"
+        r = raw(chunked)
+        assert status(r) == 200 and b"t2" in r
+        sent = [b for k, h, b in rec.requests if k == "prefill"][-1]
+        assert sent["prompt"] == "x" and sent["max_tokens"] == 1
+        # and plain traffic is unaffected
+        st, text = _post(port, {"prompt": "x", "max_tokens": 4})
+        assert st == 200 and "t2" in text
+        assert urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2).status == 200
+        assert proc.poll() is None
+    finally:
+        proc.terminate()
+        try:
+            _, err = proc.communicate(timeout=10)
+        except Exception:  # noqa: BLE001
+            proc.kill()
+            err = b""
+        p_srv.shutdown()
+        d_srv.shutdown()
+    err = err.decode() if isinstance(err, bytes) else (err or "")
+    assert "AddressSanitizer" not in err and "runtime error" not in err, err[-3000:]
 
 
 def test_proxy_under_thread_sanitizer_serves_concurrent_requests(tmp_path):
