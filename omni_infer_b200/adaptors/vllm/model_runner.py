@@ -48,6 +48,10 @@ class RunnerConfig:
     attn_tp: bool = False                      # attention heads sharded over all ranks, token-sharded hidden states
     tp_backend: str = "fused"                  # fused | nvls | nccl
     vocab_parallel: bool = False               # embedding table and LM head sharded by vocabulary rows over all ranks
+    # how long a rank waits for its peers in the per-step host agreement once serving has begun (start-up, where ranks
+    # may be minutes apart, uses the process group's own limit): a peer that has died or stopped stepping then ends
+    # this rank's step with an error instead of holding it for the group's ten minutes
+    agree_timeout_s: float = float(os.environ.get("OMNI_AGREE_TIMEOUT_S", "120"))
 
 
 class ModelRunner:
@@ -67,6 +71,7 @@ class ModelRunner:
         self._bt_width = (cfg.max_model_len + cfg.block_size - 1) // cfg.block_size + 1
         self.step_times: list = []
         self.omni = None
+        self._agreements_done = 0      # per-step host agreements completed (the first ones belong to start-up)
 
     # ------------------------------------------------------------------ model / cache set-up
     def load_model(self, weights=None, seed: Optional[int] = 0) -> None:
@@ -180,7 +185,18 @@ class ModelRunner:
             ps.step_max_tokens = 0
             return rounds
         t, work = handle
-        work.wait()
+        if self._agreements_done and self.cfg.agree_timeout_s > 0:
+            import datetime
+            try:
+                ok = work.wait(timeout=datetime.timedelta(seconds=self.cfg.agree_timeout_s))
+            except RuntimeError as e:
+                raise RuntimeError(f"a peer rank did not join the step agreement within {self.cfg.agree_timeout_s:.0f} s "
+                                   f"(it has died or stopped stepping): {e}") from e
+            if ok is False:
+                raise RuntimeError(f"a peer rank did not join the step agreement within {self.cfg.agree_timeout_s:.0f} s")
+        else:
+            work.wait()
+        self._agreements_done += 1
         max_tokens, max_rounds, any_work = int(t[0]), int(t[1]), bool(int(t[2]))
         self._place_experts(-int(t[3]))
         self.peers_busy = any_work

@@ -461,6 +461,39 @@ def _absent_peer(rank, world):
         return "detected: " + type(e).__name__
 
 
+def _peer_stops_stepping(rank, world):
+    import time as _t
+    os.environ["OMNI_AGREE_TIMEOUT_S"] = "1.5"
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", seed=3))
+    eng.add_request(list(range(1, 20)), SamplingParams(max_tokens=200 if rank == 0 else 3, ignore_eos=True))
+    if rank == 1:
+        for _ in range(6):
+            eng.step()                      # a few steps with its peer, then this rank stops stepping (a stuck host thread)
+        _t.sleep(6.0)
+        return "stopped"
+    t0, steps = _t.time(), 0
+    try:
+        while eng.has_unfinished and _t.time() - t0 < 30:
+            eng.step()
+            steps += 1
+        return f"no error after {steps} steps"
+    except RuntimeError as e:
+        return f"detected after {_t.time() - t0:.1f}s and {steps} steps: {str(e)[:60]}"
+
+
+def test_a_peer_that_stops_stepping_ends_the_step_with_an_error():
+    """Host-side failure detection in serving: the per-step agreement waits a bounded time for the peers (1.5 s here),
+    then the step fails with a message that says so - the API server turns that into errors for its clients and, when
+    it persists, into an unhealthy instance - instead of waiting out the process group's ten minutes."""
+    out = _spawn(_peer_stops_stepping, 2)
+    assert out[1] == "stopped"
+    assert out[0].startswith("detected") and "did not join the step agreement" in out[0], out[0]
+    waited = float(out[0].split()[2].rstrip("s"))
+    assert waited < 6.0
+
+
 def test_missing_rank_is_reported_not_hung():
     out = _spawn(_absent_peer, 2)
     assert out[1] == "absent" and out[0].startswith("detected")
