@@ -5,6 +5,7 @@ byte-level fallback is used (token = byte value mod vocab), which keeps the serv
 from __future__ import annotations
 
 import os
+import threading
 from concurrent.futures import ProcessPoolExecutor
 from typing import Optional
 
@@ -56,7 +57,14 @@ class TokenizerPool:
         n = int(os.environ.get("TOKENIZER_WORKER_NUM", "4")) if workers is None else workers
         aff = os.environ.get("TOKENIZER_AFFINITY_CORES", "") if affinity is None else affinity
         cores = self._parse_cores(aff)
-        self.pool = ProcessPoolExecutor(n, initializer=_init_worker, initargs=(path, vocab_size, cores)) if self.enabled else None
+        self._pool_args = (n, path, vocab_size, cores)
+        self.pool_restarts = 0
+        self._replace_lock = threading.Lock()
+        self.pool = self._new_pool() if self.enabled else None
+
+    def _new_pool(self) -> ProcessPoolExecutor:
+        n, path, vocab_size, cores = self._pool_args
+        return ProcessPoolExecutor(n, initializer=_init_worker, initargs=(path, vocab_size, cores))
 
     @staticmethod
     def _parse_cores(spec: str) -> set:
@@ -71,7 +79,20 @@ class TokenizerPool:
 
     def encode(self, text: str) -> list:
         if self.pool is not None and len(text) >= self.threshold:
-            return self.pool.submit(_encode, text).result()
+            from concurrent.futures.process import BrokenProcessPool
+            pool = self.pool
+            try:
+                return pool.submit(_encode, text).result()
+            except BrokenProcessPool:
+                # a worker died (killed for memory, say): every later submit would fail too.  This prompt is tokenised
+                # here, and the pool is replaced for the next ones (once, however many threads notice).
+                with self._replace_lock:
+                    if self.pool is pool:
+                        try:
+                            pool.shutdown(wait=False, cancel_futures=True)
+                        finally:
+                            self.pool = self._new_pool()
+                            self.pool_restarts += 1
         return list(self.tokenizer.encode(text))
 
     def decode(self, ids) -> str:

@@ -150,6 +150,24 @@ DEPLOY = {
 }
 
 
+def test_tokenizer_pool_survives_a_dead_worker():
+    import os
+    import signal
+    pool = TokenizerPool(None, vocab_size=1024, workers=1, threshold=8, enabled=True)
+    try:
+        text = "a fairly long prompt " * 4
+        want = pool.tokenizer.encode(text)
+        assert pool.encode(text) == want
+        (pid,) = list(pool.pool._processes)                  # the one worker
+        os.kill(pid, signal.SIGKILL)
+        time.sleep(0.2)
+        assert pool.encode(text) == want                     # tokenised here, pool replaced
+        assert pool.pool_restarts == 1
+        assert pool.encode(text) == want and pool.pool_restarts == 1      # and the new pool works
+    finally:
+        pool.shutdown()
+
+
 def test_deployment_transform_and_cli_dry_run(tmp_path, capsys):
     procs = transform_deployment_config(DEPLOY)
     assert [p.role for p in procs] == ["prefill", "prefill", "decode", "proxy"]
