@@ -37,7 +37,11 @@ def fingerprint(model_cfg, engine_cfg, world: int = 1) -> dict:
             "world": int(world), "tp": g(engine_cfg, "tp_size", 1), "pp": g(engine_cfg, "pp_size", 1),
             "block_size": g(engine_cfg, "block_size"), "max_model_len": g(engine_cfg, "max_model_len"),
             "max_num_seqs": g(engine_cfg, "max_num_seqs"), "gpu_memory_utilization": g(engine_cfg, "gpu_memory_utilization", None),
-            "num_speculative_tokens": g(engine_cfg, "num_speculative_tokens", 0)}
+            "num_speculative_tokens": g(engine_cfg, "num_speculative_tokens", 0),
+            # options that change what a rank holds (K/V heads, vocabulary rows, expert slots, window pool)
+            "attn_tp": bool(g(engine_cfg, "attn_tp", False)), "vocab_parallel": bool(g(engine_cfg, "vocab_parallel", False)),
+            "shared_expert_ranks": int(g(engine_cfg, "shared_expert_ranks", 0) or 0),
+            "omni_attn": bool(g(engine_cfg, "enable_omni_attn", False))}
 
 
 class StateDir:
