@@ -221,3 +221,109 @@ class ParallelSwiGLUMLP(nn.Module):
         if g.world_size > 1:
             y = g.reduce_scatter(y)[:T]
         return y
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Sequence-sharded ("flash-comm") family: between the blocks every rank keeps only its rows of the hidden states;
+# a column-parallel layer gathers the rows on the way in, a row-parallel layer scatters the sums on the way out, so the
+# residual stream, the norms and everything else elementwise run on 1/W of the tokens
+# (reference: RowParallelFlashCommLinear / ColumnParallelFlashCommLinear / QKVParallelFlashCommLinear /
+# MergedColumnParallelFlashCommLinear, omni/models/common/layers/linear.py:955-1245; used by qwen/qwen2.py).
+# ---------------------------------------------------------------------------------------------------------------
+class RowParallelLinearWithReduceScatter(RowParallelLinear):
+    """Row-parallel linear whose partial sums are reduce-scattered over token rows (reference: linear.py:587)."""
+
+    def __init__(self, in_features: int, out_features: int, group: GroupCoordinator, **kw):
+        kw.pop("reduce", None)
+        super().__init__(in_features, out_features, group, reduce="reduce_scatter", **kw)
+
+
+class RowParallelLinearCross(RowParallelLinear):
+    """Row-parallel linear over the cross group of an instance that spans several NVSwitch domains (one rank per
+    domain with the same local index); inside one domain it is the plain layer over the given group
+    (reference: RowParallelLinearCross, linear.py:764)."""
+
+    def __init__(self, in_features: int, out_features: int, group: Optional[GroupCoordinator] = None, **kw):
+        ps = get_parallel_state()
+        if group is None:
+            group = ps.group("cross") if getattr(ps, "hier", None) is not None else ps.group("world")
+        super().__init__(in_features, out_features, group, **kw)
+
+
+class ColumnParallelFlashCommLinear(Linear):
+    """Output features sharded over the group; the input arrives sharded by token rows and is all-gathered first
+    (``gather_input=False`` for an input that is already whole)."""
+
+    def __init__(self, in_features: int, out_features: int, group: GroupCoordinator, *, gather_input: bool = True,
+                 bias: bool = False, dtype=torch.bfloat16, quant: str = "none", device=None):
+        W, r = group.world_size, group.rank_in_group
+        assert out_features % W == 0
+        super().__init__(in_features, out_features // W, bias=bias, dtype=dtype, quant=quant, device=device)
+        self.group, self.gather_input = group, gather_input
+        if W > 1:
+            _mark_rows(self, out_features, r, W, out_features // W)
+            if self.bias is not None:
+                u = out_features // W
+                self.bias.tp_slice_fn = lambda full: full[r * u:(r + 1) * u]
+                self.bias.tp_full_shape = (out_features,)
+
+    def forward(self, x, xq=None):
+        if self.gather_input and self.group.world_size > 1:
+            x, xq = self.group.all_gather(x), None
+        return Linear.forward(self, x, xq=xq)
+
+
+class MergedColumnParallelFlashCommLinear(MergedColumnParallelLinear):
+    """Merged column-parallel projections (gate / up) of a row-sharded input."""
+
+    def __init__(self, in_features: int, part_sizes: list, group: GroupCoordinator, *, gather_input: bool = True, **kw):
+        super().__init__(in_features, part_sizes, group, **kw)
+        self.gather_input = gather_input
+
+    def forward(self, x, xq=None):
+        if self.gather_input and self.group.world_size > 1:
+            x, xq = self.group.all_gather(x), None
+        return Linear.forward(self, x, xq=xq)
+
+
+class RowParallelFlashCommLinear(RowParallelLinear):
+    """Input features sharded over the group; the sums go back to row shards (``reduce="reduce_scatter"``, the
+    default) or stay whole on every rank (``"all_reduce"``, for the last layer before something that needs all rows)."""
+
+    def __init__(self, in_features: int, out_features: int, group: GroupCoordinator, *, reduce: str = "reduce_scatter", **kw):
+        super().__init__(in_features, out_features, group, reduce=reduce, **kw)
+
+
+class QKVParallelFlashCommLinear(Linear):
+    """Merged q / k / v projection with the heads sharded over the group: query heads divide, K/V heads divide when
+    there are enough of them and are otherwise held by every rank whose query heads read them; row-sharded input."""
+
+    def __init__(self, hidden: int, head_dim: int, num_heads: int, num_kv_heads: int, group: GroupCoordinator, *,
+                 gather_input: bool = True, bias: bool = False, dtype=torch.bfloat16, quant: str = "none", device=None):
+        from .gqa import shard_heads
+        W, r = group.world_size, group.rank_in_group
+        hq, hkv, kv0 = shard_heads(num_heads, num_kv_heads, W, r)
+        D = head_dim
+        super().__init__(hidden, (hq + 2 * hkv) * D, bias=bias, dtype=dtype, quant=quant, device=device)
+        self.group, self.gather_input = group, gather_input
+        self.num_heads, self.num_kv_heads, self.head_dim = hq, hkv, D
+        if W > 1:
+            offs = (0, num_heads * D, (num_heads + num_kv_heads) * D)
+            blocks = [(offs[0] + r * hq * D, offs[0] + (r + 1) * hq * D), (offs[1] + kv0 * D, offs[1] + (kv0 + hkv) * D),
+                      (offs[2] + kv0 * D, offs[2] + (kv0 + hkv) * D)]
+            self.weight.tp_slice_fn = lambda full: torch.cat([full[a:b] for a, b in blocks], 0)
+            self.weight.tp_full_shape = ((num_heads + 2 * num_kv_heads) * D, hidden)
+            if self.weight_scale is not None:
+                assert D % 128 == 0, "e4m3 head shards must align to the 128x128 scale blocks"
+                self.weight_scale.tp_slice_fn = lambda full: torch.cat([full[a // 128:b // 128] for a, b in blocks], 0)
+            if self.bias is not None:
+                self.bias.tp_slice_fn = lambda full: torch.cat([full[a:b] for a, b in blocks], 0)
+                self.bias.tp_full_shape = ((num_heads + 2 * num_kv_heads) * D,)
+
+    def forward(self, x, xq=None):
+        """Returns (q, k, v) of this rank's heads for all rows."""
+        if self.gather_input and self.group.world_size > 1:
+            x, xq = self.group.all_gather(x), None
+        y = Linear.forward(self, x, xq=xq)
+        D = self.head_dim
+        return torch.split(y, [self.num_heads * D, self.num_kv_heads * D, self.num_kv_heads * D], dim=-1)

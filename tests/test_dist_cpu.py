@@ -132,6 +132,76 @@ def test_one_domain_keeps_the_flat_route():
         hc.build_hierarchical_groups(8, 0, 3)
 
 
+# ---------------------------------------------------------------------------------------------- linear family
+def _linear_family(rank, world):
+    """Every parallel linear against the dense product with the whole weight: shards cut by the layers' own slice
+    functions, inputs sharded by token rows where the layer expects that."""
+    from omni_infer_b200.layers import linear as L
+    from omni_infer_b200.parallel import destroy_distributed, init_distributed
+    ps = init_distributed(backend="gloo")
+    g = ps.group("world")
+    gen = torch.Generator().manual_seed(5)                       # same numbers on every rank
+    T, H, N = 4 * world, 32, 24 * world
+    x = torch.randn(T, H, generator=gen)
+    rows = slice(rank * T // world, (rank + 1) * T // world)
+
+    def fill(layer, full_w, full_b=None):
+        with torch.no_grad():
+            layer.weight.copy_(layer.weight.tp_slice_fn(full_w) if world > 1 else full_w)
+            if full_b is not None:
+                layer.bias.copy_(layer.bias.tp_slice_fn(full_b) if world > 1 else full_b)
+
+    kw = dict(dtype=torch.float32)
+    close = lambda a, b: torch.allclose(a, b, atol=1e-4, rtol=1e-4)      # noqa: E731
+    # column parallel, rows gathered on the way in
+    w, b = torch.randn(N, H, generator=gen), torch.randn(N, generator=gen)
+    col = L.ColumnParallelFlashCommLinear(H, N, g, bias=True, **kw)
+    fill(col, w, b)
+    cols = slice(rank * N // world, (rank + 1) * N // world)
+    assert close(col(x[rows].contiguous()), (x @ w.t() + b)[:, cols])
+    # merged gate / up
+    w2 = torch.randn(2 * N, H, generator=gen)
+    mer = L.MergedColumnParallelFlashCommLinear(H, [N, N], g, **kw)
+    fill(mer, w2)
+    full = x @ w2.t()
+    assert close(mer(x[rows].contiguous()), torch.cat([full[:, :N][:, cols], full[:, N:][:, cols]], 1))
+    # row parallel: scatter back to row shards, or keep whole
+    w3 = torch.randn(H, N, generator=gen)
+    xin = torch.randn(T, N, generator=gen)
+    for cls, red in ((L.RowParallelFlashCommLinear, "reduce_scatter"), (L.RowParallelLinearWithReduceScatter, "reduce_scatter"),
+                     (L.RowParallelFlashCommLinear, "all_reduce"), (L.RowParallelLinearCross, "all_reduce")):
+        row = cls(N, H, g, reduce=red, **kw) if cls is not L.RowParallelLinearWithReduceScatter else cls(N, H, g, **kw)
+        fill(row, w3)
+        want = xin @ w3.t()
+        got = row(xin[:, cols].contiguous())
+        assert close(got, want[rows] if row.reduce == "reduce_scatter" else want), cls.__name__
+    assert L.RowParallelLinearCross(N, H, None, **kw).group is g                 # one domain: the world group
+    # q / k / v with 4 query and 2 K/V heads (divided on 2 ranks, shared pairwise on 4)
+    D, hq, hkv = 8, 4, 2
+    wq = torch.randn((hq + 2 * hkv) * D, H, generator=gen)
+    qkv = L.QKVParallelFlashCommLinear(H, D, hq, hkv, g, **kw)
+    fill(qkv, wq)
+    q, k, v = qkv(x[rows].contiguous())
+    full = x @ wq.t()
+    hql, hkvl, kv0 = hq // world, max(1, hkv // world), rank * hkv // world
+    assert close(q, full[:, rank * hql * D:(rank + 1) * hql * D])
+    assert close(k, full[:, hq * D + kv0 * D: hq * D + (kv0 + hkvl) * D])
+    assert close(v, full[:, (hq + hkv) * D + kv0 * D:(hq + hkv) * D + (kv0 + hkvl) * D])
+    # a whole block in the sequence-sharded form: gather -> column -> row -> scatter equals the dense block on my rows
+    blk_in = L.ColumnParallelFlashCommLinear(H, N, g, **kw)
+    blk_out = L.RowParallelFlashCommLinear(N, H, g, **kw)
+    fill(blk_in, w)
+    fill(blk_out, w3)
+    assert close(blk_out(torch.relu(blk_in(x[rows].contiguous()))), (torch.relu(x @ w.t()) @ w3.t())[rows])
+    destroy_distributed()
+    return "ok"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_parallel_linear_family_equals_the_dense_product(world):
+    assert set(_spawn(_linear_family, world).values()) == {"ok"}
+
+
 # ---------------------------------------------------------------------------------------------- EP over all-to-all
 def _ep_engine(rank, world, shared_ranks=0, overrides=None):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
