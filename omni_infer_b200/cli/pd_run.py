@@ -21,9 +21,12 @@ from .launch import Launcher, dp_rank_env, port_free
 
 logger = logging.getLogger("omni_infer_b200.pd_run")
 
-IGNORED = ("global_rank_table_path", "rank_table_path", "hcc_intra_roce_enable", "hcc_intra_pcie_enable",
-           "hccl_op_expansion_mode", "hccl_buffsize", "kv_buffer_device", "vllm_use_v1", "vllm_worker_multiproc_method",
-           "gloo_socket_ifname", "tp_socket_ifname", "local_decode_server_ip_list", "global_decode_server_ip_list")
+IGNORED = ("hcc_intra_roce_enable", "hcc_intra_pcie_enable", "hccl_op_expansion_mode", "hccl_buffsize", "kv_buffer_device",
+           "vllm_use_v1", "vllm_worker_multiproc_method", "local_decode_server_ip_list", "global_decode_server_ip_list",
+           "enable_expert_parallel")
+# options of the reference's script that have a counterpart here: option -> environment variable of the servers
+MAPPED = {"gloo_socket_ifname": "GLOO_SOCKET_IFNAME", "tp_socket_ifname": "NCCL_SOCKET_IFNAME",
+          "global_rank_table_path": "OMNI_TOPOLOGY", "rank_table_path": "OMNI_LOCAL_TOPOLOGY"}
 
 
 def parse(argv=None):
@@ -69,8 +72,8 @@ def parse(argv=None):
     ap.add_argument("--extra-args", default="")
     ap.add_argument("--additional-config", "--additional-args", dest="additional_config", default="")
     ap.add_argument("--vllm-enable-mc2", type=int, default=1, help="fused NVLink dispatch/combine on decode (role of VLLM_ENABLE_MC2)")
-    for name in IGNORED:
-        ap.add_argument("--" + name.replace("_", "-"), default=None, help=argparse.SUPPRESS)
+    for name in IGNORED + tuple(MAPPED):
+        ap.add_argument("--" + name.replace("_", "-"), default=None, nargs="?", const="1", help=argparse.SUPPRESS)
     ap.add_argument("--dry-run", action="store_true")
     return ap.parse_args(argv)
 
@@ -115,6 +118,9 @@ def build_plan(a) -> list:
                     "MODEL_EXTRA_CFG_PATH": a.model_extra_cfg_path, "OMNI_USE_FUSED_EP": str(a.vllm_enable_mc2),
                     "OMNI_KV_CONTROL_PORT": str(a.kv_control_port), "VLLM_LOGGING_LEVEL": a.vllm_logging_level,
                     "SERVED_MODEL_NAME": a.served_model_name, "GPU_UTIL": str(a.gpu_util)})
+        for name, var in MAPPED.items():
+            if getattr(a, name) is not None:
+                env[var] = str(getattr(a, name))
         if devices:
             per = max(1, len(devices) // a.num_servers)
             env["CUDA_VISIBLE_DEVICES"] = ",".join(devices[i * per:(i + 1) * per] or devices[-per:])
