@@ -47,9 +47,13 @@ def create_connectors(kv_transfer_config: dict, block_size: int = 128, num_specu
     eid = c.get("engine_id", f"engine-{next(_ids)}")
     endpoint = c.get("endpoint", f"inproc://{eid}")
     transport = c.get("transport", "inproc" if endpoint.startswith("inproc") else "tcp")
+    from .topology import from_env
+    topo = from_env()
     worker = WorkerConnector(role, eid, endpoint, transport, float(c.get("sync_timeout_s", 20.0)), int(c.get("retries", 3)),
                              float(c.get("retry_wait_s", 2.0)), authkey=c.get("authkey"),
-                             handover_ttl_s=float(c.get("handover_ttl_s", 120.0)))
+                             handover_ttl_s=float(c.get("handover_ttl_s", 120.0)),
+                             known_producers=topo.control_endpoints("prefill") | topo.control_endpoints("mixed") if topo else None,
+                             known_consumers=topo.control_endpoints("decode") | topo.control_endpoints("mixed") if topo else None)
     sched = SchedulerConnector(role, eid, endpoint, block_size, num_speculative_tokens,
                                worker=worker if c.get("async_pull_kv", True) else None)
     return sched, worker

@@ -312,10 +312,15 @@ class WorkerConnector:
     SERVED_LIMIT = 4096          # producer: how many served request ids are remembered for re-acknowledgement
 
     def __init__(self, kv_role: str, engine_id: str, endpoint: str, transport: str = "inproc", sync_timeout_s: float = 20.0,
-                 retries: int = 3, retry_wait_s: float = 2.0, authkey=None, handover_ttl_s: float = 120.0):
+                 retries: int = 3, retry_wait_s: float = 2.0, authkey=None, handover_ttl_s: float = 120.0,
+                 known_producers=None, known_consumers=None):
         self.kv_role, self.engine_id, self.endpoint, self.transport = kv_role, engine_id, endpoint, transport
         self.sync_timeout_s, self.retries, self.retry_wait_s = sync_timeout_s, retries, retry_wait_s
         self.handover_ttl_s = handover_ttl_s
+        # with a deployment table (accelerators/pd/topology.py) KV is only asked from, and pushed to, instances it lists
+        self.known_producers = set(known_producers) if known_producers else None
+        self.known_consumers = set(known_consumers) if known_consumers else None
+        self.refused_strangers = 0
         self.expired_handovers = 0         # producer: handed-over requests nobody asked for in time
         self.kv_tensors: list = []
         self._meta: Optional[ConnectorMetadata] = None
@@ -442,6 +447,16 @@ class WorkerConnector:
                "dst_blocks": r.local_block_ids, "reply_to": self.endpoint, "consumer": self.engine_id}
         if self.transport != "inproc":
             msg["cache"] = self.cache_descriptor()
+        if self.known_producers is not None and r.remote_host not in self.known_producers:
+            # the hand-over names an endpoint that is not a prefill instance of this deployment: nothing is asked of it
+            logger.warning("kv for %s offered by %s, which the deployment table does not list: prefilling locally",
+                           r.request_id, r.remote_host)
+            with self._lock:
+                self.refused_strangers += 1
+                if self._inflight.get(r.request_id, (None, None))[1] == attempt:
+                    del self._inflight[r.request_id]
+                    self._failed_recv.add(r.request_id)
+            return
         deadline = time.monotonic() + self.sync_timeout_s
         for n in range(self.retries + 1):
             self._send(r.remote_host, msg)
@@ -520,6 +535,12 @@ class WorkerConnector:
 
     def handle_push_request(self, msg: dict) -> None:
         rid, attempt = msg["request_id"], msg.get("attempt")
+        if self.known_consumers is not None and msg.get("reply_to") not in self.known_consumers:
+            logger.warning("push request for %s from %s, which the deployment table does not list: refused", rid, msg.get("reply_to"))
+            with self._lock:
+                self.refused_strangers += 1
+            self._send(msg["reply_to"], {"op": "nack", "request_id": rid, "attempt": attempt})
+            return
         with self._lock:
             if (rid, attempt) in self._cancelled:
                 return                           # the consumer already gave this attempt up

@@ -30,6 +30,10 @@ class Topology:
     def by_role(self, role: str) -> list:
         return [i for i in self.instances if i.role == role]
 
+    def control_endpoints(self, role=None) -> set:
+        """Control endpoints of the instances (of one role): who a KV exchange may come from or go to."""
+        return {i.control_endpoint for i in self.instances if role is None or i.role == role}
+
     def to_json(self) -> str:
         return json.dumps({"instances": [asdict(i) for i in self.instances]}, indent=1)
 
@@ -44,6 +48,21 @@ class Topology:
 
     def save(self, path: str) -> None:
         Path(path).write_text(self.to_json())
+
+
+def from_env(var: str = "OMNI_TOPOLOGY"):
+    """The deployment's table named by the environment (set by the launchers and the playbook), or None.  An unreadable
+    file is reported and treated as absent: the table restricts who may exchange KV, it is not needed to run."""
+    import logging
+    import os
+    path = os.environ.get(var, "")
+    if not path:
+        return None
+    try:
+        return Topology.load(path)
+    except (OSError, ValueError, TypeError, KeyError) as e:
+        logging.getLogger("omni_infer_b200.pd").warning("topology file %s is unreadable (%s): not used", path, e)
+        return None
 
 
 def generate(n_prefill: int, n_decode: int, gpus_per_prefill: int = 1, gpus_per_decode: int = 1, base_api_port: int = 9000,

@@ -107,7 +107,9 @@ def plan_to_inventory(path_or_dict, user: str = "root", code_path: str = "/works
         for gname, nodes in (dep.get(role, {}) or {}).items():
             for node_rank, node in enumerate(nodes):
                 spec = by_name[f"{role}-{gname}-{idx}"]
+                kv = json.loads(spec.argv[spec.argv.index("--kv-transfer-config") + 1])
                 hosts[key][f"{key.lower()}{idx}"] = {
+                    "control_port": int(kv["endpoint"].rsplit(":", 1)[1]),      # where this instance's KV control listens
                     "ansible_host": node.get("ip", "127.0.0.1"), "ansible_user": node.get("user", user),
                     "role": role, "group": gname, "node_rank": node_rank, "kv_rank": idx, "api_port": spec.api_port,
                     "devices": spec.env["CUDA_VISIBLE_DEVICES"], "master_port": int(node.get("master_port", 29500 + idx)),

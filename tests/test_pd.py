@@ -293,3 +293,47 @@ def test_request_dropped_during_its_kv_transfer_keeps_its_blocks_until_the_trans
     assert outs["r1"] == want[1]
     assert D.scheduler.kv.num_free_blocks == 47 and not D.scheduler._aborting
     assert P.scheduler.kv.num_free_blocks == 47 and not P.scheduler.pending_free
+
+
+def test_deployment_table_limits_who_exchanges_kv(tmp_path, monkeypatch):
+    """With a deployment table in force a decode instance asks only listed prefill instances for KV and a prefill
+    instance pushes only to listed decode instances; anything else is prefilled locally."""
+    from omni_infer_b200.accelerators.pd.topology import Instance, Topology, from_env
+    table = tmp_path / "global_topology.json"
+    Topology([Instance("prefill-0", "prefill", [0], 9000, 1, host="p11"), Instance("decode-0", "decode", [1], 9100, 2, host="d11")]).save(str(table))
+    monkeypatch.setenv("OMNI_TOPOLOGY", str(table))
+    assert from_env().control_endpoints("prefill") == {"tcp://p11:1"}
+    prompts = _prompts(2)
+    want = _mixed_reference(prompts, 4)
+
+    def engines(p_name, d_name):
+        InProcessHub.reset()
+        P, D = _engine("kv_producer", p_name), _engine("kv_consumer", d_name)
+        return P, D
+
+    # (the engines read the table at start; the endpoints of this test are "inproc://<name>", so each case states who
+    # is listed)
+    # listed on both sides: KV travels
+    P, D = engines("p11", "d11")
+    assert D.worker.runner.kv_connector.known_producers == {"tcp://p11:1"}        # what the table said
+    for eng in (P, D):
+        c = eng.worker.runner.kv_connector
+        c.known_producers, c.known_consumers = {"inproc://p11"}, {"inproc://d11"}
+    outs = _run_pd(P, D, prompts, 4)
+    assert [outs[f"r{i}"] for i in range(2)] == want and D.scheduler.stats.get("kv_fallbacks", 0) == 0
+    # the decode instance does not know this prefill instance: it asks nothing of it and prefills itself
+    P, D = engines("p12", "d12")
+    D.worker.runner.kv_connector.known_producers = {"inproc://somebody-else"}
+    outs = _run_pd(P, D, prompts, 4)
+    assert [outs[f"r{i}"] for i in range(2)] == want
+    assert D.scheduler.stats.get("kv_fallbacks", 0) == 2 and D.worker.runner.kv_connector.refused_strangers == 2
+    # the prefill instance does not know this decode instance: refused, prefilled locally
+    P, D = engines("p13", "d13")
+    D.worker.runner.kv_connector.known_producers = {"inproc://p13"}
+    P.worker.runner.kv_connector.known_consumers = {"inproc://somebody-else"}
+    outs = _run_pd(P, D, prompts, 4)
+    assert [outs[f"r{i}"] for i in range(2)] == want
+    assert D.scheduler.stats.get("kv_fallbacks", 0) == 2 and P.worker.runner.kv_connector.refused_strangers == 2
+    # an unreadable table is not fatal
+    table.write_text("{not json")
+    assert from_env() is None

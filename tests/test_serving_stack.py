@@ -246,13 +246,18 @@ def test_inventory_and_playbook_for_several_hosts(tmp_path, capsys):
         off = 0 if h["role"] == "prefill" else 100
         assert topology.main(["--mode", "gen", role_opt, h["devices"], "--host", h["ansible_host"], "--index-offset",
                               str(h["kv_rank"]), "--base-api-port",
-                              str(h["api_port"] - off), "--base-control-port", str(5568 + h["kv_rank"] - off),
+                              str(h["api_port"] - off), "--base-control-port", str(h["control_port"] - off),
                               "--save-dir", str(tmp_path / name)]) == 0
     tables = [str(tmp_path / n / "global_topology.json") for n in ("p0", "p1", "d0")]
     assert topology.main(["--mode", "merge-all", "--global-ranktable-list", *tables, "--save-dir", str(tmp_path / "all")]) == 0
     merged = topology.Topology.load(str(tmp_path / "all" / "global_topology.json"))
     assert sorted((i.name, i.host, i.api_port) for i in merged.instances) == [
         ("decode-0", "10.0.0.3", 9100), ("prefill-0", "10.0.0.1", 9000), ("prefill-1", "127.0.0.1", 9001)]
+    # the table's control endpoints are the ones the servers listen on (the connectors only talk to listed instances)
+    listening = set()
+    for h in list(groups["P"]["hosts"].values()) + list(groups["D"]["hosts"].values()):
+        listening.add(json.loads(h["server_argv"][h["server_argv"].index("--kv-transfer-config") + 1])["endpoint"])
+    assert merged.control_endpoints() == listening and len(listening) == 3
     # container image and build script exist and say what they build for
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     assert "deploy/build.sh" in open(os.path.join(root, "deploy", "docker", "Dockerfile")).read()
