@@ -40,6 +40,17 @@ def _spawn(fn, world, *args):
     return out
 
 
+_ONE_RANK: dict = {}
+
+
+def _single(fn, *args):
+    """Result of a one-rank run, computed once per (function, arguments): several cases compare against the same one."""
+    key = (fn.__name__, repr(args))
+    if key not in _ONE_RANK:
+        _ONE_RANK[key] = _spawn(fn, 1, *args)[0]
+    return _ONE_RANK[key]
+
+
 def _entry(fn, rank, world, port, q, args):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
@@ -229,7 +240,7 @@ def _ep_engine(rank, world, shared_ranks=0, overrides=None):
 
 
 def test_expert_parallel_matches_single_rank():
-    single = _spawn(_ep_engine, 1)[0]
+    single = _single(_ep_engine)
     two = _spawn(_ep_engine, 2)
     assert two[0] == single and two[1] == single
 
@@ -239,7 +250,7 @@ def test_expert_parallel_matches_single_rank():
 def test_dedicated_shared_expert_ranks_match_single_rank(world, shared_ranks, overrides):
     """The first ranks hold only the shared expert (cut into pieces of a routed expert's shape, each an always-selected
     extra expert), the others only routed experts: same tokens as the model that runs everything on one rank."""
-    single = _spawn(_ep_engine, 1, 0, overrides)[0]
+    single = _single(_ep_engine, 0, overrides)
     many = _spawn(_ep_engine, world, shared_ranks, overrides)
     assert all(many[r] == single for r in range(world))
 
@@ -271,7 +282,7 @@ def _ep_uneven(rank, world, mode, vocab_parallel=False):
 @pytest.mark.parametrize("mode", ["uneven", "idle"])
 def test_uneven_data_parallel_ranks_stay_in_step(mode):
     """Neither rank waits for an exchange its peer never joins, and the busy rank's tokens equal a single-rank run."""
-    single = _spawn(_ep_uneven, 1, mode)[0]
+    single = _single(_ep_uneven, mode)
     two = _spawn(_ep_uneven, 2, mode)
     assert two[0] == single
     if mode == "uneven":
@@ -305,7 +316,7 @@ def _vp_engine(rank, world, attn_tp, overrides=None):
 def test_vocabulary_parallel_table_and_head_match_single_rank(world, attn_tp, overrides):
     """Embedding table and LM head sharded by vocabulary rows (1024 rows over 3 ranks leaves a short last block): same
     tokens as one rank, with data-parallel attention (ranks hold different rows) and with tensor-parallel attention."""
-    single = _spawn(_vp_engine, 1, attn_tp, overrides)[0]
+    single = _single(_vp_engine, attn_tp, overrides)
     many = _spawn(_vp_engine, world, attn_tp, overrides)
     assert many[0] == single
     assert all(many[r] == single[:len(many[r])] for r in range(1, world))
@@ -314,7 +325,7 @@ def test_vocabulary_parallel_table_and_head_match_single_rank(world, attn_tp, ov
 def test_vocabulary_parallel_with_uneven_ranks_and_mtp():
     """Multi-step decode with a drafter on ranks with different work: the row-count agreement of the sharded table and
     head keeps the ranks in step, tokens equal the single-rank run."""
-    single = _spawn(_ep_uneven, 1, "uneven")[0]
+    single = _single(_ep_uneven, "uneven")
     two = _spawn(_ep_uneven, 2, "uneven", True)
     assert two[0] == single and two[1] == [single[1][:3]]
 
@@ -338,7 +349,7 @@ def _subgroup_engine(rank, world, mlp_tp, o_tp):
 
 @pytest.mark.parametrize("mlp_tp,o_tp", [(2, 1), (1, 2), (2, 2)])
 def test_dense_mlp_and_o_proj_subgroups_match_single_rank(mlp_tp, o_tp):
-    single = _spawn(_subgroup_engine, 1, 1, 1)[0]
+    single = _single(_subgroup_engine, 1, 1)
     two = _spawn(_subgroup_engine, 2, mlp_tp, o_tp)
     assert two[0] == single and two[1] == [single[1]]
 
@@ -365,7 +376,7 @@ def _pp_engine(rank, world, model):
 
 @pytest.mark.parametrize("model", ["tiny-deepseek-v3", "tiny-qwen3-moe"])
 def test_pipeline_parallel_matches_single_rank(model):
-    single = _spawn(_pp_engine, 1, model)[0]
+    single = _single(_pp_engine, model)
     two = _spawn(_pp_engine, 2, model)
     assert two[0] == single and two[1] == single
 
@@ -403,7 +414,7 @@ def _tp_engine(rank, world, model="tiny-deepseek-v3", overrides=None):
 def test_tensor_parallel_attention_matches_single_rank():
     """Heads sharded over two ranks, hidden states sharded by token rows between layers (library collectives on CPU):
     same tokens as the unsharded model."""
-    single = _spawn(_tp_engine, 1)[0]
+    single = _single(_tp_engine)
     two = _spawn(_tp_engine, 2)
     assert two[0] == single and two[1] == single
 
@@ -412,7 +423,7 @@ def test_tensor_parallel_attention_matches_single_rank():
 def test_tensor_parallel_gqa_attention_matches_single_rank(world, overrides):
     """The GQA MoE model with query and K/V heads sharded over the ranks: K/V heads divided (4 q / 2 kv heads on 2 ranks),
     one K/V head shared by both ranks, and 2 K/V heads replicated over 4 ranks; same tokens as the unsharded model."""
-    single = _spawn(_tp_engine, 1, "tiny-qwen3-moe", overrides)[0]
+    single = _single(_tp_engine, "tiny-qwen3-moe", overrides)
     many = _spawn(_tp_engine, world, "tiny-qwen3-moe", overrides)
     assert all(many[r] == single for r in range(world))
 
@@ -469,7 +480,7 @@ def _background_placement_engine(rank, world, dynamic):
                                   placement_config=pc, model_overrides={"router_skew": {"s": 1.2, "strength": 6.0, "seed": 0}}))
     g = torch.Generator().manual_seed(11 + rank)            # different requests on every rank
     prompts = [torch.randint(0, 1024, (20 + i,), generator=g).tolist() for i in range(3)]
-    ids = [eng.add_request(p, SamplingParams(max_tokens=70, ignore_eos=True)) for p in prompts]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=40, ignore_eos=True)) for p in prompts]
     outs = {}
     for _ in range(400):
         if not eng.has_unfinished and not eng.peers_busy:
