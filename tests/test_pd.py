@@ -12,7 +12,7 @@ from omni_infer_b200.engine.request import SamplingParams
 
 
 def _engine(role, name, **kw):
-    cfg = EngineConfig(block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=0,
+    cfg = EngineConfig(block_size=16, num_kv_blocks=kw.pop("num_kv_blocks", 48), max_model_len=160, device="cpu", seed=0,
                        kv_transfer_config={"kv_role": role, "engine_id": name, "endpoint": f"inproc://{name}",
                                            "sync_timeout_s": kw.pop("sync_timeout_s", 5.0), "retries": kw.pop("retries", 3),
                                            "retry_wait_s": kw.pop("retry_wait_s", 0.2)}, **kw)
@@ -71,6 +71,8 @@ def test_pd_matches_single_instance_and_frees_producer_blocks():
         P.step()
     assert P.kv.num_free_blocks == free_before and not P.scheduler.pending_free
     assert D.scheduler.stats.get("kv_fallbacks", 0) == 0
+    if d_kw.get("num_kv_blocks"):
+        assert D.scheduler.stats["preemptions"] > 0        # a request whose KV came from the prefill side was recomputed here
 
 
 def test_dropped_push_request_is_retried_and_duplicate_acks_ignored():
@@ -337,3 +339,39 @@ def test_deployment_table_limits_who_exchanges_kv(tmp_path, monkeypatch):
     # an unreadable table is not fatal
     table.write_text("{not json")
     assert from_env() is None
+
+
+@pytest.mark.parametrize("p_kw,d_kw,mtp", [
+    (dict(enable_prefix_caching=True), dict(num_step=3), False),
+    (dict(enable_chunked_prefill=True, max_num_batched_tokens=24), dict(async_schedule=True), False),
+    (dict(enable_prefix_caching=True, enable_chunked_prefill=True, max_num_batched_tokens=32), dict(num_step=2, num_speculative_tokens=1), True),
+    (dict(), dict(num_kv_blocks=11, num_speculative_tokens=1), True),
+], ids=["prefix+multistep", "chunked+async", "prefix+chunked+mtp+multistep", "mtp+tight-decode-pool"])
+def test_pd_with_engine_features_on_both_sides(p_kw, d_kw, mtp):
+    """Prefill and decode instances with different engine options (prefix cache and chunked prefill on the prefill side;
+    multi-step, drafts, asynchronous scheduling and a KV pool small enough to preempt on the decode side): the tokens
+    equal those of one plain instance, and both sides end with every block free."""
+    over = {"num_nextn_predict_layers": 1} if mtp else {}
+    g = torch.Generator().manual_seed(21)
+    shared = torch.randint(0, 1024, (32,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 1024, (int(n),), generator=g).tolist() for n in (5, 11)]
+    prompts.append(torch.randint(0, 1024, (40,), generator=g).tolist())
+    E = EngineCore(EngineConfig(block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=0, model_overrides=over))
+    ids = [E.add_request(p, SamplingParams(max_tokens=12)) for p in prompts]
+    ref = E.run_until_done()
+    want = [ref[i] for i in ids]
+    P = _engine("kv_producer", "p20", model_overrides=over, **p_kw)
+    D = _engine("kv_consumer", "d20", model_overrides=over, **d_kw)
+    outs = _run_pd(P, D, prompts, 12)
+    assert [outs[f"r{i}"] for i in range(3)] == want
+    for _ in range(50):
+        P.step()
+        if not P.scheduler.pending_free:
+            break
+        time.sleep(0.01)
+    assert not P.scheduler.pending_free
+    assert P.scheduler.kv.num_free_blocks == P.scheduler.kv.num_blocks - 1
+    assert D.scheduler.kv.num_free_blocks == D.scheduler.kv.num_blocks - 1
+    assert D.scheduler.stats.get("kv_fallbacks", 0) == 0
+    if d_kw.get("num_kv_blocks"):
+        assert D.scheduler.stats["preemptions"] > 0        # a request whose KV came from the prefill side was recomputed here
