@@ -46,6 +46,10 @@ class ReqMeta:
     remote_block_ids: list
     remote_host: str
     remote_engine_id: str = ""
+    # Omni-Attention on the decode instance: the request's window blocks for the compressed layers and what decides
+    # which prompt tokens go where in them
+    window_block_ids: list = field(default_factory=list)
+    prompt_len: int = 0
 
 
 @dataclass
@@ -264,7 +268,9 @@ class SchedulerConnector:
         p = req.kv_transfer_params or {}
         n_blocks = (len(req.prompt_token_ids) + self.block_size - 1) // self.block_size
         self._pending.append(ReqMeta(req.request_id, list(req.block_ids[:n_blocks]), list(p["remote_block_ids"][:n_blocks]),
-                                     p["remote_host"], p.get("remote_engine_id", "")))
+                                     p["remote_host"], p.get("remote_engine_id", ""),
+                                     window_block_ids=list(getattr(req, "omni_block_ids", None) or []),
+                                     prompt_len=len(req.prompt_token_ids)))
         p["do_remote_prefill"] = False        # handled: a fallback re-schedule prefills locally
 
     def build_connector_meta(self) -> ConnectorMetadata:
@@ -337,6 +343,8 @@ class WorkerConnector:
         self._cancelled: set = set()       # producer: (request id, attempt) the consumer gave up on
         self._copying: set = set()         # producer: request ids whose copy is running right now
         self._peer_views: dict = {}        # producer: consumer endpoint -> cache view
+        self.compressed_idx: list = []     # consumer with Omni-Attention: flat indices of the window-cache tensors
+        self.omni_spec = None              # consumer with Omni-Attention: sink / recent / block size of a window
         self._tcp = None
         if transport == "inproc":
             InProcessHub.register(endpoint, self)
@@ -344,13 +352,23 @@ class WorkerConnector:
             self._tcp = TcpTransport(endpoint, self, authkey)
 
     # -- set-up
-    def register_kv_caches(self, kv_caches) -> None:
+    def register_kv_caches(self, kv_caches, compressed_layers=None) -> None:
+        """``compressed_layers``: indices (into ``kv_caches``) of the layers whose cache is a pool of per-request
+        windows (Omni-Attention on a decode instance) rather than the paged cache."""
         self.kv_tensors = flatten_cache(kv_caches)
+        comp, flat = set(compressed_layers or ()), 0
+        self.compressed_idx = []
+        for li, c in enumerate(kv_caches):
+            n = len(c) if isinstance(c, (tuple, list)) else 1
+            if li in comp:
+                self.compressed_idx += list(range(flat, flat + n))
+            flat += n
 
     def cache_descriptor(self) -> dict:
         """What a producer needs to write into this cache from another process (CUDA IPC handles)."""
         t0 = self.kv_tensors[0]
-        desc = {"block_bytes": t0[0].numel() * t0.element_size(), "num_blocks": t0.shape[0], "n_tensors": len(self.kv_tensors)}
+        desc = {"block_bytes": t0[0].numel() * t0.element_size(), "num_blocks": t0.shape[0], "n_tensors": len(self.kv_tensors),
+                "num_blocks_per_tensor": [int(t.shape[0]) for t in self.kv_tensors]}
         if t0.is_cuda:
             from ...parallel.symmetric_heap import export_ipc_handles
             desc["ipc"] = export_ipc_handles(self.kv_tensors)
@@ -447,6 +465,10 @@ class WorkerConnector:
                "dst_blocks": r.local_block_ids, "reply_to": self.endpoint, "consumer": self.engine_id}
         if self.transport != "inproc":
             msg["cache"] = self.cache_descriptor()
+        if self.omni_spec is not None and self.compressed_idx and r.window_block_ids:
+            sp = self.omni_spec
+            msg["omni"] = {"sink": sp.sink, "recent": sp.recent, "block_size": sp.block_size, "prompt_len": r.prompt_len,
+                           "dst_window": list(r.window_block_ids), "compressed": list(self.compressed_idx)}
         if self.known_producers is not None and r.remote_host not in self.known_producers:
             # the hand-over names an endpoint that is not a prefill instance of this deployment: nothing is asked of it
             logger.warning("kv for %s offered by %s, which the deployment table does not list: prefilling locally",
@@ -531,6 +553,7 @@ class WorkerConnector:
                 raise LookupError("the consumer's cache is not shareable between processes (no device IPC handles)")
             from ...parallel.symmetric_heap import open_ipc_handles
             self._peer_views[key] = PeerCacheView(open_ipc_handles(d["ipc"]), d["block_bytes"], d["num_blocks"])
+            self._peer_views[key].num_blocks_per_tensor = d.get("num_blocks_per_tensor")
         return self._peer_views[key]
 
     def handle_push_request(self, msg: dict) -> None:
@@ -560,6 +583,8 @@ class WorkerConnector:
             return
         try:
             try:
+                if msg.get("omni") and self.compressed_idx:
+                    raise LookupError("a prefill instance with Omni-Attention has no full cache to send from")
                 peer = self._peer_cache(msg)
             except LookupError as e:
                 logger.warning("push request for %s refused: %s", rid, e)
@@ -568,7 +593,9 @@ class WorkerConnector:
                         self._done_send.add(rid)
                 self._send(msg["reply_to"], {"op": "nack", "request_id": rid, "attempt": attempt})
                 return
-            if isinstance(peer, PeerCacheView):
+            if msg.get("omni"):
+                self._push_omni(peer, msg)
+            elif isinstance(peer, PeerCacheView):
                 push_blocks_cuda(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
             else:
                 push_blocks_torch(self.kv_tensors, peer, msg["src_blocks"], msg["dst_blocks"])
@@ -584,6 +611,44 @@ class WorkerConnector:
             while len(self._served) > self.SERVED_LIMIT:
                 self._served.pop(next(iter(self._served)))
         self._send(msg["reply_to"], {"op": "ack", "request_id": rid, "attempt": attempt})
+
+    def _push_omni(self, peer, msg: dict) -> None:
+        """Transfer to a decode instance that runs Omni-Attention (reference: OmniBiGroupDataDistManager.pull_kv,
+        omni/accelerators/cache/pd.py:81-123).  Full layers get the request's blocks as usual.  Compressed layers get
+        only what their window keeps - the first ``sink`` blocks' worth of tokens and the most recent ones - token by
+        token at the window positions the decode instance computes for a prompt of this length, so that its first step
+        finds the window exactly as its own prefill would have left it."""
+        from ..cache.omni_attn import OmniAttnConfig, OmniAttnState
+        om = msg["omni"]
+        bs, n_prompt = int(om["block_size"]), int(om["prompt_len"])
+        comp = [int(i) for i in om["compressed"]]
+        full = [i for i in range(len(self.kv_tensors)) if i not in set(comp)]
+        src_blocks, dst_blocks, window = msg["src_blocks"], msg["dst_blocks"], om["dst_window"]
+        st = OmniAttnState(OmniAttnConfig(int(om["sink"]), int(om["recent"]), 0.0, [1]), bs)
+        src_slots, dst_slots = [], []
+        for p in range(min(n_prompt, len(src_blocks) * bs)):
+            w = st.window_position(p, n_prompt)
+            if w is not None:
+                src_slots.append(src_blocks[p // bs] * bs + p % bs)
+                dst_slots.append(window[w // bs] * bs + w % bs)
+        if isinstance(peer, PeerCacheView):
+            per = getattr(peer, "num_blocks_per_tensor", None) or [peer.num_blocks] * len(peer.ptrs)
+            if full:
+                push_blocks_cuda([self.kv_tensors[i] for i in full],
+                                 PeerCacheView([peer.ptrs[i] for i in full], peer.block_bytes, per[full[0]]), src_blocks, dst_blocks)
+            if comp and src_slots:
+                # the same copy kernel with one token as the unit: the caches seen as [slots, token bytes]
+                toks = [self.kv_tensors[i].view(-1, *self.kv_tensors[i].shape[2:]) for i in comp]
+                push_blocks_cuda(toks, PeerCacheView([peer.ptrs[i] for i in comp], peer.block_bytes // bs, per[comp[0]] * bs),
+                                 src_slots, dst_slots)
+            return
+        if full:
+            push_blocks_torch([self.kv_tensors[i] for i in full], [peer[i] for i in full], src_blocks, dst_blocks)
+        if comp and src_slots:
+            push_blocks_torch([self.kv_tensors[i].view(-1, *self.kv_tensors[i].shape[2:]) for i in comp],
+                              [peer[i].view(-1, *peer[i].shape[2:]) for i in comp], src_slots, dst_slots)
+        if self.kv_tensors and self.kv_tensors[0].is_cuda:
+            torch.cuda.synchronize()
 
     def handle_cancel(self, msg: dict) -> None:
         rid, attempt = msg["request_id"], msg.get("attempt")

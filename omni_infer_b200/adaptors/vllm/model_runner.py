@@ -280,16 +280,29 @@ class ModelRunner:
         cfg, bs = self.model_cfg, self.cfg.block_size
         self.omni = state
         dt = self.model.model.dtype
+        ipc = (self.kv_connector is not None and getattr(self.kv_connector, "transport", "inproc") != "inproc"
+               and self.device.type == "cuda")
+
+        def zeros(*shape):
+            if ipc:     # a prefill instance in another process writes the transferred windows through CUDA IPC
+                from ...parallel.symmetric_heap import alloc_ipc_tensor
+                return alloc_ipc_tensor(shape, dt)
+            return torch.zeros(*shape, dtype=dt, device=self.device)
+
+        compressed = []
         for i in range(self.model.num_kv_layers):
             if not state.is_compressed(i):
                 continue
+            compressed.append(i)
             if cfg.use_mla:
-                self.kv_caches[i] = torch.zeros(num_window_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim, dtype=dt,
-                                                device=self.device)
+                self.kv_caches[i] = zeros(num_window_blocks, bs, cfg.kv_lora_rank + cfg.qk_rope_head_dim)
             else:
-                self.kv_caches[i] = tuple(torch.zeros(num_window_blocks, bs, cfg.local_kv_heads, cfg.head_dim,
-                                                      dtype=dt, device=self.device) for _ in range(2))
+                self.kv_caches[i] = tuple(zeros(num_window_blocks, bs, cfg.local_kv_heads, cfg.head_dim) for _ in range(2))
         self.graphs = None
+        if self.kv_connector is not None:
+            # the connector keeps the cache tensors: tell it about the new ones and which layers they belong to
+            self.kv_connector.register_kv_caches(self.kv_caches + [k[0] for k in self.drafter_kv], compressed_layers=compressed)
+            self.kv_connector.omni_spec = state.spec
 
     # ------------------------------------------------------------------ gears / graphs
     def gear_list(self) -> list:

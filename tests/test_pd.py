@@ -375,3 +375,31 @@ def test_pd_with_engine_features_on_both_sides(p_kw, d_kw, mtp):
     assert D.scheduler.stats.get("kv_fallbacks", 0) == 0
     if d_kw.get("num_kv_blocks"):
         assert D.scheduler.stats["preemptions"] > 0        # a request whose KV came from the prefill side was recomputed here
+
+
+@pytest.mark.parametrize("prompt_len", [40, 64, 65, 100, 128])
+def test_pd_into_a_decode_instance_with_omni_attention(prompt_len):
+    """The decode instance keeps, for compressed layers, a 64-token window per request (16 sink + 48 recent).  The
+    prefill instance sends full blocks for the full layers and, for the compressed ones, only the tokens the window
+    keeps, at the window positions: the decode instance then generates exactly what one Omni-Attention instance that
+    prefilled the prompt itself generates."""
+    g = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, 1024, (prompt_len + d,), generator=g).tolist() for d in (0, 3)]
+    omni = dict(enable_omni_attn=True, omni_attn_config={"sink": 1, "recent": 3, "pattern": [0, 1]})
+    base = dict(block_size=16, num_kv_blocks=64, max_model_len=256, device="cpu", seed=0, max_num_seqs=4)
+    E = EngineCore(EngineConfig(**base, **omni))
+    ids = [E.add_request(p, SamplingParams(max_tokens=20)) for p in prompts]
+    ref = E.run_until_done()
+    want = [ref[i] for i in ids]
+
+    def engine(role, name, **kw):
+        return EngineCore(EngineConfig(**base, kv_transfer_config={"kv_role": role, "engine_id": name, "endpoint": f"inproc://{name}",
+                                                                   "sync_timeout_s": 5.0, "retries": 3, "retry_wait_s": 0.2}, **kw))
+
+    P, D = engine("kv_producer", "p30"), engine("kv_consumer", "d30", **omni)
+    conn = D.worker.runner.kv_connector
+    assert conn.compressed_idx == [1] and conn.omni_spec.capacity_tokens == 64
+    outs = _run_pd(P, D, prompts, 20)
+    assert [outs[f"r{i}"] for i in range(2)] == want
+    assert D.scheduler.stats.get("kv_fallbacks", 0) == 0                     # the KV really came from the prefill instance
+    assert len(D.kv.window_free) == 4 * 4 and D.kv.num_free_blocks == 63
