@@ -71,8 +71,6 @@ def test_pd_matches_single_instance_and_frees_producer_blocks():
         P.step()
     assert P.kv.num_free_blocks == free_before and not P.scheduler.pending_free
     assert D.scheduler.stats.get("kv_fallbacks", 0) == 0
-    if d_kw.get("num_kv_blocks"):
-        assert D.scheduler.stats["preemptions"] > 0        # a request whose KV came from the prefill side was recomputed here
 
 
 def test_dropped_push_request_is_retried_and_duplicate_acks_ignored():
