@@ -53,6 +53,7 @@ def _single(fn, *args):
 
 def _entry(fn, rank, world, port, q, args):
     sys.path.insert(0, ROOT)
+    torch.set_num_threads(1)        # several ranks share the cores; the models are tiny
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NO_GPU_MOCK="1")
     try:
@@ -480,7 +481,7 @@ def _background_placement_engine(rank, world, dynamic):
                                   placement_config=pc, model_overrides={"router_skew": {"s": 1.2, "strength": 6.0, "seed": 0}}))
     g = torch.Generator().manual_seed(11 + rank)            # different requests on every rank
     prompts = [torch.randint(0, 1024, (20 + i,), generator=g).tolist() for i in range(3)]
-    ids = [eng.add_request(p, SamplingParams(max_tokens=40, ignore_eos=True)) for p in prompts]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=80, ignore_eos=True)) for p in prompts]
     outs = {}
     for _ in range(400):
         if not eng.has_unfinished and not eng.peers_busy:
@@ -488,7 +489,7 @@ def _background_placement_engine(rank, world, dynamic):
         for r in eng.step():
             outs.setdefault(r.request_id, []).extend(r.new_token_ids)
         if dynamic:
-            _t.sleep(0.01)                                   # give the background rounds time to happen during the run
+            _t.sleep(0.02)                                   # give the background rounds time to happen during the run
     planner = eng.worker.runner.planner
     applied = planner.applied_total if planner is not None else 0
     rounds = planner.ready_rounds() if planner is not None else 0
