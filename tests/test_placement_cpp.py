@@ -13,16 +13,44 @@ SRC = os.path.join(ROOT, "csrc", "placement")
 CORE = ("placement_mapping.cpp", "placement_balancer.cpp", "placement_static.cpp", "placement_manager.cpp")
 
 
-def _build_and_run(tmp_path, name, test_source, sanitizer):
-    exe = str(tmp_path / name)
-    srcs = [os.path.join(SRC, f) for f in (*CORE, test_source)]
-    cmd = ["g++", "-O1", "-g", "-std=c++17", "-Wall", "-pthread", f"-fsanitize={sanitizer}", "-I", SRC, "-o", exe] + srcs
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0 and "sanitize" in res.stderr:
+_CORE_OBJECTS: dict = {}       # sanitizer -> (object files, flags) compiled once per test session
+
+
+def _core_objects(sanitizer):
+    """The library's sources compiled once per sanitizer; every test binary links against the same objects."""
+    if sanitizer in _CORE_OBJECTS:
+        return _CORE_OBJECTS[sanitizer]
+    import tempfile
+    out_dir = tempfile.mkdtemp(prefix=f"omni_placement_{sanitizer.replace(',', '_')}_")
+    flags = ["-O1", "-g", "-std=c++17", "-Wall", "-pthread", f"-fsanitize={sanitizer}"]
+    probe = subprocess.run(["g++", *flags, "-x", "c++", "-", "-o", os.path.join(out_dir, "probe")], input="int main(){return 0;}",
+                           capture_output=True, text=True)
+    if probe.returncode != 0:
         if sanitizer == "thread":
-            pytest.skip("-fsanitize=thread is not available with this compiler")
-        cmd = [c for c in cmd if not c.startswith("-fsanitize")]
-        res = subprocess.run(cmd, capture_output=True, text=True)
+            _CORE_OBJECTS[sanitizer] = None
+            return None
+        flags = [f for f in flags if not f.startswith("-fsanitize")]
+    objs = []
+    procs = []
+    for f in CORE:
+        o = os.path.join(out_dir, f.replace(".cpp", ".o"))
+        procs.append((f, subprocess.Popen(["g++", *flags, "-I", SRC, "-c", os.path.join(SRC, f), "-o", o],
+                                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+        objs.append(o)
+    for f, pr in procs:
+        _, err = pr.communicate()
+        assert pr.returncode == 0, f + "\n" + err[-3000:]
+    _CORE_OBJECTS[sanitizer] = (objs, flags)
+    return _CORE_OBJECTS[sanitizer]
+
+
+def _build_and_run(tmp_path, name, test_source, sanitizer):
+    core = _core_objects(sanitizer)
+    if core is None:
+        pytest.skip("-fsanitize=thread is not available with this compiler")
+    objs, flags = core
+    exe = str(tmp_path / name)
+    res = subprocess.run(["g++", *flags, "-I", SRC, "-o", exe, os.path.join(SRC, test_source), *objs], capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-3000:]
     run = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert run.returncode == 0 and "ALL PASSED" in run.stdout, run.stdout + run.stderr[-3000:]
