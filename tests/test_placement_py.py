@@ -271,3 +271,38 @@ def test_token_level_optimizers():
     with pytest.raises(ValueError):
         optim.create_optimizers([{"NoSuchOptimizer": {}}])
     m.close()
+
+
+def test_shipped_configuration_patterns_and_guideline(tmp_path):
+    """The configuration file that ships with the package loads with the reference's keys, the base patterns are
+    valid for their model shapes, and the commands of the guideline exist in the pattern tool."""
+    import os
+    import re
+    import numpy as np
+    import yaml
+    from omni_infer_b200.accelerators.placement import OmniPlanner, pattern_tool
+    from omni_infer_b200.models.config import tiny_deepseek_v3
+    here = os.path.dirname(pattern_tool.__file__)
+    cfg_path = os.path.join(here, "config.yaml")
+    cfg = yaml.safe_load(open(cfg_path))
+    assert {"pattern_path", "max_moe_layer_num", "enable_dynamic", "max_redundant_per_expert", "max_redundant_per_rank",
+            "enable_dump", "dump_dir"} <= set(cfg)
+    assert cfg["max_moe_layer_num"] == 58 and cfg["max_redundant_per_expert"] == 10 and cfg["max_redundant_per_rank"] == 1
+    pl = OmniPlanner.from_config({"config_path": cfg_path}, tiny_deepseek_v3())
+    try:
+        assert pl.num_redundant_per_rank == 1 and pl.layers == 1 and not pl.enable_dynamic
+    finally:
+        OmniPlanner.cleanup()
+    for name, (world, layers, experts) in {"DSV3_baseline_58_layers_8_ranks.npy": (8, 58, 256),
+                                           "Qwen3_30B_A3B_baseline_48_layers_8_ranks.npy": (8, 48, 128)}.items():
+        pat = np.load(os.path.join(here, "patterns", "base_patterns", name))
+        assert pat.shape == (world, layers, experts) and set(np.unique(pat)) == {0, 1}
+        assert (pat.sum(0) == 1).all() and (pat.sum(2) == experts // world).all()      # every expert once, ranks even
+    guide = open(os.path.join(here, "Guideline.md")).read()
+    for sub in re.findall(r"pattern_tool (\\w[\\w-]*)", guide) + re.findall(r"`([a-z-]+)`(?=[,)]| run)", guide):
+        if sub in ("logs-to-csv", "generate", "check", "analyse", "plan", "pipeline"):
+            with pytest.raises(SystemExit) as ei:
+                pattern_tool.main([sub, "--help"])
+            assert ei.value.code == 0
+    for flag in re.findall(r"(--[a-z][a-z-]+)", guide):
+        assert flag in open(pattern_tool.__file__).read(), flag
