@@ -264,6 +264,19 @@ def test_inventory_and_playbook_for_several_hosts(tmp_path, capsys):
     assert "g.build()" in open(os.path.join(root, "deploy", "build.sh")).read()
 
 
+def test_shipped_deployment_file_describes_a_runnable_plan(capsys):
+    import os
+    path = os.path.join(os.path.dirname(cli_main.__file__), "omni_infer_deployment.yml")
+    procs = transform_deployment_config(path)
+    assert [p.role for p in procs] == ["prefill"] * 4 + ["decode"] * 4 + ["proxy"]
+    assert sorted(p.env["CUDA_VISIBLE_DEVICES"] for p in procs[:8]) == [str(i) for i in range(8)]     # every GPU once
+    assert len({p.api_port for p in procs}) == 9
+    ends = [json.loads(p.argv[p.argv.index("--kv-transfer-config") + 1])["endpoint"] for p in procs[:8]]
+    assert len(set(ends)) == 8
+    assert cli_main.main(["serve", path, "--dry-run"]) == 0
+    assert len(json.loads(capsys.readouterr().out)) == 9
+
+
 def test_launcher_detects_dead_child(tmp_path):
     from omni_infer_b200.cli.config_transform import ProcessSpec
     procs = [ProcessSpec("sleeper", "decode", ["-c", "import time; time.sleep(30)"]),
