@@ -284,3 +284,25 @@ def test_rope_scaling_variants():
     yarn = rope_cos_sin_table(D, N, base, {"type": "yarn", "factor": 4.0, "original_max_position_embeddings": 16, "mscale": 1.0,
                                            "mscale_all_dim": 0.0})
     assert float(yarn[0, 0]) == pytest.approx(0.1 * math.log(4.0) + 1.0, rel=1e-6)    # cos(0) times the attention factor
+
+
+def test_shipped_model_extra_configs_load():
+    """The sample ``MODEL_EXTRA_CFG_PATH`` files of the package load through the same reader as a user's and reach the
+    engine configuration (reference: tests/test_config/*.json)."""
+    import glob
+    import os
+    from omni_infer_b200 import config as oc
+    from omni_infer_b200.adaptors.vllm.platform import ConfigUpdater
+    from omni_infer_b200.engine.engine_core import EngineConfig
+    root = os.path.join(os.path.dirname(oc.__file__), "configs")
+    files = sorted(glob.glob(os.path.join(root, "*.json")))
+    assert [os.path.basename(f) for f in files] == ["decode_ep8.json", "decode_ep8_placement.json", "prefill_ep8.json"]
+    for f in files:
+        extra = oc.load_model_extra_config(f)
+        assert extra.parall_config.dp_size == 8
+    dec = oc.load_model_extra_config(files[0])
+    assert dec.operator_opt_config.moe_dispatch_combine and dec.operator_opt_config.decode_gear_list == [256]
+    pre = oc.load_model_extra_config(files[2])
+    assert pre.parall_config.dense_mlp_tp_size == 4 and not pre.operator_opt_config.moe_dispatch_combine
+    pl = oc.load_model_extra_config(files[1])
+    assert pl.operator_opt_config.use_omni_placement and pl.operator_opt_config.omni_placement_config_path.endswith("config.yaml")
