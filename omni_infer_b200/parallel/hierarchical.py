@@ -184,6 +184,36 @@ def reduce_scatter_pipelined(x: torch.Tensor, hg: HierarchicalGroups, chunks: in
     return torch.cat(outs, dim=1).view(n, *x.shape[1:])
 
 
+def all_gather_round_pipelined(x: torch.Tensor, hg: HierarchicalGroups) -> torch.Tensor:
+    """All-gather over the world for a power-of-two number of domains (2, 4, 8 hosts) as rounds of pairwise exchanges:
+    in round ``k`` every rank swaps its own shard with the rank of the same local index in domain ``d xor k``, and the
+    fan-out of what arrived inside the domain (a local all-gather) is started at once, so it runs while the next
+    round's exchange is on the wire.  Every link between two domains carries exactly one shard per rank and round, no
+    rank ever waits on a collective that spans all domains (the reference's three-round pairwise pipelines for four
+    nodes, omni/adaptors/vllm/distributed/communication_op.py:173-266).  Result: blocks in world-rank order, dim 0."""
+    H, L = hg.num_domains, hg.ranks_per_domain
+    if H & (H - 1):
+        raise ValueError("the pairwise rounds need a power-of-two number of domains")
+    x = x.contiguous()
+    d = hg.domain
+    got = {d: hg.local.all_gather(x, 0, async_op=True)}            # own domain's rows: fan-out starts first
+    for k in range(1, H):
+        peer = d ^ k
+        recv = torch.empty_like(x)
+        if hg.cross.world_size > 1:
+            ops = [dist.P2POp(dist.isend, x, hg.cross.ranks[peer], hg.cross.group),
+                   dist.P2POp(dist.irecv, recv, hg.cross.ranks[peer], hg.cross.group)]
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        got[peer] = hg.local.all_gather(recv, 0, async_op=True)    # overlaps the next round's exchange
+    parts = []
+    for h in range(H):
+        out, work = got[h]
+        _wait(work)
+        parts.append(out)                                           # [L * n, ...]: domain h's ranks in local order
+    return torch.cat(parts, 0)
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # free functions over the process-wide state (the names the reference's model code calls); flat when the instance
 # sits in one domain

@@ -111,6 +111,11 @@ def _hierarchical(rank, world, rpd):
     z = torch.randint(-8, 8, (world * 3 + 1,), generator=g).float()         # element count not divisible by L
     for t in (y, z):
         assert torch.equal(hc.all_reduce_two_stage(t.clone(), hg), flat.all_reduce(t.clone()))
+    if (world // rpd) & (world // rpd - 1) == 0:           # power-of-two domains: the pairwise rounds
+        assert torch.equal(hc.all_gather_round_pipelined(x, hg), flat.all_gather(x, 0))
+    else:
+        with pytest.raises(ValueError):
+            hc.all_gather_round_pipelined(x, hg)
     a = torch.arange(world * 2 * 3, dtype=torch.float32).view(world * 2, 3) + 1000 * rank
     assert torch.equal(hc.all_to_all_two_stage(a, hg), flat.all_to_all(a))
     # the process-wide forms pick the two-stage route by themselves
@@ -127,7 +132,7 @@ def _hierarchical(rank, world, rpd):
     return "ok"
 
 
-@pytest.mark.parametrize("world,rpd", [(4, 2), (6, 3), (6, 2)])
+@pytest.mark.parametrize("world,rpd", [(4, 2), (6, 3), (6, 2), (8, 2)])
 def test_two_level_collectives_equal_the_flat_ones(world, rpd):
     assert set(_spawn(_hierarchical, world, rpd).values()) == {"ok"}
 
