@@ -23,7 +23,7 @@ logger = logging.getLogger("omni_infer_b200.pd_run")
 
 IGNORED = ("hcc_intra_roce_enable", "hcc_intra_pcie_enable", "hccl_op_expansion_mode", "hccl_buffsize", "kv_buffer_device",
            "vllm_use_v1", "vllm_worker_multiproc_method", "local_decode_server_ip_list", "global_decode_server_ip_list",
-           "enable_expert_parallel")
+           "enable_expert_parallel", "head", "num_gpus")
 # options of the reference's script that have a counterpart here: option -> environment variable of the servers
 MAPPED = {"gloo_socket_ifname": "GLOO_SOCKET_IFNAME", "tp_socket_ifname": "NCCL_SOCKET_IFNAME",
           "global_rank_table_path": "OMNI_TOPOLOGY", "rank_table_path": "OMNI_LOCAL_TOPOLOGY"}
@@ -74,8 +74,17 @@ def parse(argv=None):
     ap.add_argument("--vllm-enable-mc2", type=int, default=1, help="fused NVLink dispatch/combine on decode (role of VLLM_ENABLE_MC2)")
     for name in IGNORED + tuple(MAPPED):
         ap.add_argument("--" + name.replace("_", "-"), default=None, nargs="?", const="1", help=argparse.SUPPRESS)
+    ap.add_argument("--address", default=None,
+                    help="host:port of the first node of an instance that spans several nodes (the reference passes its Ray "
+                         "head address here); becomes the rendezvous address of the ranks")
     ap.add_argument("--dry-run", action="store_true")
-    return ap.parse_args(argv)
+    a = ap.parse_args(argv)
+    if a.address:
+        host, _, port = a.address.partition(":")
+        a.master_ip = host or a.master_ip
+        if port.isdigit():
+            a.master_port = int(port)
+    return a
 
 
 def build_plan(a) -> list:
