@@ -52,6 +52,15 @@ def check_blocks(sched: Scheduler, kv: KVCacheManager):
         assert b in kv.block_hash and kv.hash_to_block.get(kv.block_hash[b]) == b
     for h, b in kv.hash_to_block.items():
         assert kv.block_hash.get(b) == h
+    if hasattr(kv, "window_free"):                      # Omni-Attention: the pool of per-request windows
+        held_w = [b for r in sched.requests.values() for b in (getattr(r, "omni_block_ids", None) or [])]
+        assert len(held_w) == len(set(held_w)) and not (set(held_w) & set(kv.window_free))
+        assert len(kv.window_free) == len(set(kv.window_free))
+        assert set(held_w) | set(kv.window_free) == set(range(1, kv.num_window_blocks))
+        n = kv.spec.blocks_per_request
+        for r in sched.requests.values():
+            w = getattr(r, "omni_block_ids", None) or []
+            assert len(w) in (0, n) and (len(w) == n) == bool(r.block_ids), r.request_id
     # finished requests own nothing unless a hand-over is pending
     for r in sched.requests.values():
         if r.is_finished and r.request_id not in sched.pending_free:
@@ -96,6 +105,8 @@ CASES = [
     dict(blocks=20, bs=4, seqs=4, budget=32, chunked=False, prefix=False, num_step=1, spec=2),
     dict(blocks=24, bs=4, seqs=5, budget=28, chunked=True, prefix=True, num_step=2, spec=1),
     dict(blocks=40, bs=8, seqs=8, budget=64, chunked=True, prefix=True, num_step=2, spec=3),
+    dict(blocks=16, bs=4, seqs=4, budget=32, chunked=False, prefix=False, num_step=1, spec=0, omni_windows=3),
+    dict(blocks=30, bs=4, seqs=6, budget=24, chunked=True, prefix=False, num_step=2, spec=0, omni_windows=2),
 ]
 
 
@@ -103,7 +114,13 @@ CASES = [
 @pytest.mark.parametrize("seed", [0, 1, 2])
 def test_random_traffic_keeps_outputs_and_block_accounting_right(case, seed):
     rnd = random.Random(1000 * seed + case["blocks"])
-    kv = KVCacheManager(case["blocks"], case["bs"], enable_prefix_caching=case["prefix"])
+    if case.get("omni_windows"):
+        # two pools: paged blocks plus a fixed window (1 sink + 3 recent blocks) per request; room for only a few windows
+        from omni_infer_b200.accelerators.cache import OmniAttentionSpec, OmniKVCacheManager
+        spec = OmniAttentionSpec(case["bs"], 1, 3)
+        kv = OmniKVCacheManager(case["blocks"], case["bs"], spec, num_window_blocks=case["omni_windows"] * 4 + 1)
+    else:
+        kv = KVCacheManager(case["blocks"], case["bs"], enable_prefix_caching=case["prefix"])
     cfg = SchedulerConfig(max_num_seqs=case["seqs"], max_num_batched_tokens=case["budget"], max_model_len=64,
                           num_speculative_tokens=case["spec"], num_step=case["num_step"], enable_chunked_prefill=case["chunked"])
     sched = Scheduler(cfg, kv)
@@ -176,6 +193,8 @@ def test_random_traffic_keeps_outputs_and_block_accounting_right(case, seed):
     assert finished >= 20
     if case["blocks"] <= 16:
         assert sched.stats["preemptions"] > 0 or case["prefix"]     # the small pools really were under pressure
+    if case.get("omni_windows"):
+        assert len(kv.window_free) == kv.num_window_blocks - 1
 
 
 def test_a_preempted_request_longer_than_the_step_budget_is_not_stuck():
