@@ -164,7 +164,9 @@ class Scheduler:
                     if self.kv.allocate_slots(req, n) is not None:
                         ok = True
                         break
-                    victim = self.running.pop()
+                    vi, victim = self._pop_victim()
+                    if vi < idx:
+                        idx -= 1
                     if victim is req and self._can_never_fit(req, n):
                         self._give_up(req)
                         break
@@ -261,7 +263,9 @@ class Scheduler:
                     ok = True
                     break
                 # out of blocks: preempt the lowest-priority (last) running request
-                victim = self.running.pop()
+                vi, victim = self._pop_victim()
+                if vi < idx:
+                    idx -= 1
                 if victim is req and self._can_never_fit(req, n + lookahead):
                     self._give_up(req)
                     break
@@ -285,6 +289,15 @@ class Scheduler:
             out.kv_connector_metadata = self.connector.build_connector_meta()
         return out
 
+    def _pop_victim(self):
+        """(index, request) of the running request that gives way when the KV pool is exhausted: the last one admitted,
+        or with the priority policy the one of lowest priority (largest value, latest arrival among equals), as in the
+        reference's scheduler (omni/adaptors/vllm/worker/npu_schedule.py:111-359)."""
+        i = len(self.running) - 1
+        if self.cfg.policy == "priority":
+            i = max(range(len(self.running)), key=lambda k: (self.running[k].priority, self.running[k].arrival_time))
+        return i, self.running.pop(i)
+
     def _can_never_fit(self, req: Request, num_new_tokens: int) -> bool:
         """The request wants more blocks than the whole pool has: preempting it would only bring it back to the same
         point after a recompute, for ever."""
@@ -304,7 +317,10 @@ class Scheduler:
         req.spec_token_ids = []
         req.num_preemptions += 1
         self.stats["preemptions"] += 1
-        self.waiting.appendleft(req)
+        if self.cfg.policy == "priority":      # back into its place by priority, not ahead of more urgent requests
+            self.waiting = deque(sorted(list(self.waiting) + [req], key=lambda r: (r.priority, r.arrival_time)))
+        else:
+            self.waiting.appendleft(req)
 
     # ------------------------------------------------------------------ results
     def update_from_output(self, sched: SchedulerOutput, out: ModelRunnerOutput) -> list:

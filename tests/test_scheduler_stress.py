@@ -270,3 +270,47 @@ def test_a_request_that_outgrows_the_whole_pool_ends_instead_of_recomputing_for_
     assert seen["big"][-1].finished and seen["big"][-1].finish_reason == "length"
     assert small.output_token_ids == expected_output(small.prompt_token_ids, 2)
     assert sched.stats.get("kv_capacity_stops") == 1 and kv.num_free_blocks == 5
+
+
+def test_priority_policy_preempts_the_least_urgent_request():
+    """With the priority policy the request that gives way when the KV pool runs out is the least urgent running one
+    (largest priority value; the latest arrival among equals), not simply the last admitted, and it goes back into the
+    queue at its place rather than ahead of more urgent waiting requests."""
+    kv = KVCacheManager(10, 4)                          # 9 usable blocks
+    cfg = SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=64, policy="priority")
+    sched = Scheduler(cfg, kv)
+    rnd = random.Random(0)
+    # three requests of 8 prompt tokens (2 blocks each): urgent (0), background (5), normal (1) - admitted in that order
+    reqs = {}
+    for name, prio, t in (("urgent", 0, 1.0), ("background", 5, 2.0), ("normal", 1, 3.0)):
+        r = Request(name, list(range(8)), SamplingParams(max_tokens=20, ignore_eos=True), priority=prio, arrival_time=t)
+        reqs[name] = r
+        sched.add_request(r)
+    preempted_order = []
+    for _ in range(40):
+        so = sched.schedule()
+        preempted_order += list(so.preempted_req_ids)
+        if so.scheduled:
+            sched.update_from_output(so, fake_runner(so, rnd, 0))
+        check_blocks(sched, kv)
+        if len(preempted_order) >= 1:
+            break
+    assert preempted_order[0] == "background"           # not "normal", which was admitted last
+    # a more urgent request arrives while "background" waits: it is served first
+    late = Request("late-urgent", list(range(8)), SamplingParams(max_tokens=2, ignore_eos=True), priority=0, arrival_time=9.0)
+    sched.add_request(late)
+    assert [r.request_id for r in sched.waiting] == ["late-urgent", "background"]
+    done = {}
+    for _ in range(400):
+        if not sched.has_unfinished:
+            break
+        so = sched.schedule()
+        if so.scheduled:
+            for ro in sched.update_from_output(so, fake_runner(so, rnd, 0)):
+                if ro.finished:
+                    done[ro.request_id] = len(done)
+        check_blocks(sched, kv)
+    assert set(done) == {"urgent", "background", "normal", "late-urgent"}
+    assert done["late-urgent"] < done["background"]
+    for r in list(reqs.values()) + [late]:
+        assert r.output_token_ids == expected_output(r.prompt_token_ids, r.sampling.max_tokens)
