@@ -47,11 +47,11 @@ class AsyncEngine:
         self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
 
-    def submit(self, prompt_ids, sampling, request_id, kv_transfer_params=None) -> queue.Queue:
+    def submit(self, prompt_ids, sampling, request_id, kv_transfer_params=None, priority: int = 0) -> queue.Queue:
         q: queue.Queue = queue.Queue()
         with self.lock:
             self.queues[request_id] = q
-        self.inbox.put((prompt_ids, sampling, request_id, kv_transfer_params))
+        self.inbox.put((prompt_ids, sampling, request_id, kv_transfer_params, priority))
         self.stats["requests"] += 1
         return q
 
@@ -75,7 +75,7 @@ class AsyncEngine:
                     if item[0] == "abort":
                         eng.abort(item[1])
                     else:
-                        eng.add_request(item[0], item[1], item[2], item[3])
+                        eng.add_request(item[0], item[1], item[2], item[3], priority=item[4])
             except queue.Empty:
                 pass
             if not eng.has_unfinished:
@@ -212,7 +212,11 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                                                  f"including the completion"})
             rid = self.headers.get("X-Request-Id") or ("cmpl-" + uuid.uuid4().hex)
             timeline.emit("Get request in api server", rid, role=aeng.engine.role)
-            q = aeng.submit(ids, sp, rid, kvp)
+            try:
+                priority = int(body.get("priority", 0) or 0)       # used by the priority scheduling policy
+            except (TypeError, ValueError):
+                return self._json(400, {"error": "priority must be an integer"})
+            q = aeng.submit(ids, sp, rid, kvp, priority)
             stream = bool(body.get("stream", False))
             created = int(time.time())
             n_prompt, out_ids, final = len(ids), [], None
@@ -328,12 +332,13 @@ def main(argv=None) -> int:
     ap.add_argument("--model-overrides", default=None, help="JSON of model-config fields to override (e.g. fewer layers)")
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--enable-chunked-prefill", action="store_true")
+    ap.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"])
     a = ap.parse_args(argv)
     cfg = EngineConfig(model=a.model, device=a.device, max_num_seqs=a.max_num_seqs, max_model_len=a.max_model_len,
                        max_num_batched_tokens=a.max_num_batched_tokens, block_size=a.block_size, num_kv_blocks=a.num_kv_blocks,
                        num_speculative_tokens=a.num_speculative_tokens, tp_size=a.tensor_parallel_size,
                        enforce_eager=a.enforce_eager, gpu_memory_utilization=a.gpu_memory_utilization,
-                       enable_chunked_prefill=a.enable_chunked_prefill,
+                       enable_chunked_prefill=a.enable_chunked_prefill, scheduling_policy=a.scheduling_policy,
                        model_overrides=json.loads(a.model_overrides) if a.model_overrides else {},
                        kv_transfer_config=json.loads(a.kv_transfer_config) if a.kv_transfer_config else None)
     if a.additional_config:

@@ -34,6 +34,7 @@ class EngineConfig:
     o_proj_tp_size: int = 1          # o_proj sharded over sub-groups of this size (attention data parallel)
     shared_expert_ranks: int = 0     # first N ranks hold only the shared expert, routed experts on the others
     vocab_parallel: bool = False     # embedding table + LM head sharded by vocabulary rows over all ranks
+    scheduling_policy: str = "fcfs"  # fcfs | priority (smaller value first; decides admission order and who is preempted)
     block_size: int = 128
     num_kv_blocks: int = 0
     gpu_memory_utilization: float = 0.9
@@ -119,7 +120,7 @@ class EngineCore:
         sc = SchedulerConfig(max_num_seqs=cfg.max_num_seqs, max_num_batched_tokens=cfg.max_num_batched_tokens,
                              max_model_len=cfg.max_model_len, num_speculative_tokens=cfg.num_speculative_tokens,
                              num_step=cfg.num_step, async_schedule=cfg.async_schedule,
-                             enable_chunked_prefill=cfg.enable_chunked_prefill)
+                             enable_chunked_prefill=cfg.enable_chunked_prefill, policy=cfg.scheduling_policy)
         self.scheduler = Scheduler(sc, self.kv, connector=sched_conn)
         self._ids = itertools.count()
         from ..parallel import get_parallel_state

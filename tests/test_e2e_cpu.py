@@ -141,3 +141,22 @@ def test_feature_combinations_under_memory_pressure_match_the_plain_engine(combo
     st = llm.engine.scheduler.stats
     assert st["preemptions"] > 0, st                     # the pool really was too small
     assert llm.engine.kv.num_free_blocks == combo["num_kv_blocks"] - 1
+
+
+def test_priority_scheduling_serves_urgent_requests_first():
+    """``scheduling_policy="priority"``: with room for one sequence at a time, requests finish in priority order however
+    they arrived, and the tokens are those of the plain engine."""
+    prompts = _prompts(3, 20, seed=5)
+    base = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu")
+    want = base.generate(prompts, SamplingParams(max_tokens=6))
+    eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu", max_num_seqs=1,
+                                  scheduling_policy="priority"))
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6), priority=pr) for p, pr in zip(prompts, (2, 0, 1))]
+    order, outs = [], {}
+    while eng.has_unfinished:
+        for r in eng.step():
+            outs.setdefault(r.request_id, []).extend(r.new_token_ids)
+            if r.finished:
+                order.append(r.request_id)
+    assert order == [ids[1], ids[2], ids[0]]
+    assert [outs[i] for i in ids] == want
