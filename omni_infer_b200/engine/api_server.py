@@ -199,7 +199,16 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
             try:
                 sp = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
                                     temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
-                                    top_p=float(body.get("top_p", 1.0) or 1.0), ignore_eos=bool(body.get("ignore_eos", False)))
+                                    top_p=float(body.get("top_p", 1.0) or 1.0), ignore_eos=bool(body.get("ignore_eos", False)),
+                                    stop_token_ids=tuple(int(t) for t in (body.get("stop_token_ids") or ())),
+                                    seed=None if body.get("seed") is None else int(body["seed"]),
+                                    repetition_penalty=float(body.get("repetition_penalty", 1.0) or 1.0),
+                                    presence_penalty=float(body.get("presence_penalty", 0.0) or 0.0),
+                                    frequency_penalty=float(body.get("frequency_penalty", 0.0) or 0.0))
+                stop = body.get("stop") or []
+                stop = [stop] if isinstance(stop, str) else [str(x) for x in stop]
+                if sp.repetition_penalty <= 0:
+                    raise ValueError("repetition_penalty must be positive")
                 if sp.max_tokens < 1 or sp.temperature < 0 or not 0 < sp.top_p <= 1 or sp.top_k < 0:
                     raise ValueError("max_tokens >= 1, temperature >= 0, 0 < top_p <= 1 and top_k >= 0 are required")
             except (TypeError, ValueError) as e:
@@ -220,6 +229,7 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
             stream = bool(body.get("stream", False))
             created = int(time.time())
             n_prompt, out_ids, final = len(ids), [], None
+            sent_text, final_text, final_reason = "", None, None
 
             def chunk_obj(text, finish):
                 usage = {"prompt_tokens": n_prompt, "completion_tokens": len(out_ids), "total_tokens": n_prompt + len(out_ids)}
@@ -257,8 +267,35 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                     if not out_ids and o.new_token_ids:
                         timeline.emit("First token out of api server", rid, role=aeng.engine.role)
                     out_ids += o.new_token_ids
+                    stopped = None
+                    if stop and o.new_token_ids:
+                        # stop strings are matched on the text so far (they may straddle tokens); the text ends before
+                        # the first one and the request is dropped from the engine
+                        text_so_far = tok.decode(out_ids)
+                        cuts = [text_so_far.find(x) for x in stop if x and x in text_so_far]
+                        if cuts:
+                            stopped = text_so_far[:min(cuts)]
+                    if stopped is not None:
+                        aeng.abort(rid)
+                        if stream:
+                            tail = stopped[len(sent_text):] if stopped.startswith(sent_text) else ""
+                            self.wfile.write(("data: " + json.dumps(chunk_obj(tail, "stop")) + "\n\n").encode())
+                            self.wfile.flush()
+                        final = o
+                        final_text, final_reason = stopped, "stop"
+                        break
                     if stream and (o.new_token_ids or o.finished):
-                        self.wfile.write(("data: " + json.dumps(chunk_obj(tok.decode(o.new_token_ids), o.finish_reason if o.finished else None)) + "\n\n").encode())
+                        # incremental detokenisation: what the whole output reads as now, minus what was sent; a
+                        # character whose bytes have not all arrived yet is held back until it is complete
+                        full = tok.decode(out_ids)
+                        stable = full if o.finished else full.rstrip("\ufffd")
+                        if stop and not o.finished:
+                            # the end of the text may be the beginning of a stop string: not sent until that is settled
+                            hold = max((n for x in stop for n in range(1, len(x)) if stable.endswith(x[:n])), default=0)
+                            stable = stable[:len(stable) - hold]
+                        piece = stable[len(sent_text):] if stable.startswith(sent_text) else tok.decode(o.new_token_ids)
+                        sent_text += piece
+                        self.wfile.write(("data: " + json.dumps(chunk_obj(piece, o.finish_reason if o.finished else None)) + "\n\n").encode())
                         self.wfile.flush()
                     if o.finished:
                         final = o
@@ -277,11 +314,12 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                 self.wfile.flush()
                 self.close_connection = True
                 return
-            text = tok.decode(out_ids)
-            resp = chunk_obj(text, final.finish_reason)
+            text = tok.decode(out_ids) if final_text is None else final_text
+            reason = final_reason or final.finish_reason
+            resp = chunk_obj(text, reason)
             resp["object"] = "chat.completion" if chat else "text_completion"
             if chat:
-                resp["choices"][0] = {"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": final.finish_reason}
+                resp["choices"][0] = {"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}
             if final.kv_transfer_params:
                 resp["kv_transfer_params"] = final.kv_transfer_params
             try:

@@ -128,6 +128,47 @@ def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_f
         aeng.stop()
 
 
+def test_api_sampling_parameters_and_stop_strings():
+    """Penalties, seeds and stop token ids reach the sampler, and stop strings end a request at the text level: the
+    answer stops before the string, in both response forms."""
+    cfg = EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu")
+    srv, aeng = serve(cfg, "127.0.0.1", 0, block=False)
+    port = srv.server_port
+    try:
+        plain = json.loads(_post(port, "/v1/completions", {"prompt": "hello world", "max_tokens": 12}))
+        text = plain["choices"][0]["text"]
+        assert plain["usage"]["completion_tokens"] == 12 and len(text) >= 6
+        # a strong repetition penalty changes the greedy continuation
+        pen = json.loads(_post(port, "/v1/completions", {"prompt": "hello world", "max_tokens": 12, "repetition_penalty": 50.0}))
+        assert pen["choices"][0]["text"] != text
+        # stop token id = the third generated token of the plain run: two tokens come back
+        from omni_infer_b200.engine.tokenizer_pool import ByteTokenizer
+        ids = ByteTokenizer(1024).encode(text)
+        # (the byte tokenizer maps characters to ids one to one for ASCII; otherwise take the ids from the engine)
+        req = next(r for r in aeng.engine.scheduler.requests.values() if len(r.output_token_ids) == 12 and r.sampling.repetition_penalty == 1.0)
+        third = req.output_token_ids[2]
+        short = json.loads(_post(port, "/v1/completions", {"prompt": "hello world", "max_tokens": 12, "stop_token_ids": [third]}))
+        assert short["usage"]["completion_tokens"] <= 3 and short["choices"][0]["finish_reason"] == "stop"
+        # stop string taken from the middle of the plain answer
+        needle = text[4:6]
+        cut = json.loads(_post(port, "/v1/completions", {"prompt": "hello world", "max_tokens": 12, "stop": needle}))
+        assert cut["choices"][0]["text"] == text[:text.find(needle)] and cut["choices"][0]["finish_reason"] == "stop"
+        streamed = _post(port, "/v1/completions", {"prompt": "hello world", "max_tokens": 12, "stop": [needle], "stream": True})
+        chunks = [json.loads(l[6:]) for l in streamed.splitlines() if l.startswith("data: {")]
+        assert "".join(c["choices"][0]["text"] for c in chunks) == text[:text.find(needle)]
+        assert chunks[-1]["choices"][0]["finish_reason"] == "stop" and "[DONE]" in streamed
+        for _ in range(100):
+            if not aeng.engine.has_unfinished:
+                break
+            time.sleep(0.02)
+        assert not aeng.engine.has_unfinished            # the stopped requests left the engine
+        assert _status(port, "/v1/completions", {"prompt": "x", "max_tokens": 2, "repetition_penalty": -1})[0] == 400
+        assert _status(port, "/v1/completions", {"prompt": "x", "max_tokens": 2, "priority": "soon"})[0] == 400
+    finally:
+        srv.shutdown()
+        aeng.stop()
+
+
 def test_tokenizer_pool_offloads_long_prompts():
     pool = TokenizerPool(None, vocab_size=300, workers=1, threshold=10, enabled=True)
     try:
