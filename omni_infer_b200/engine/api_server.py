@@ -122,7 +122,20 @@ class AsyncEngine:
             logging.getLogger("omni_infer_b200.api_server").exception("could not write the state directory")
 
 
-def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
+def _make_parsers(reasoning_parser: Optional[str], tool_call_parser: Optional[str]):
+    """Parser objects for the chat endpoint by name (the host engine's ``--reasoning-parser`` / ``--tool-call-parser``)."""
+    known_r, known_t = {}, {}
+    from ..models.pangu.reasoning import PanguReasoningParser
+    from ..models.pangu.tool_parser import PanguToolParser
+    known_r["pangu"], known_t["pangu"] = PanguReasoningParser, PanguToolParser
+    if reasoning_parser and reasoning_parser not in known_r:
+        raise ValueError(f"unknown reasoning parser {reasoning_parser!r} (known: {sorted(known_r)})")
+    if tool_call_parser and tool_call_parser not in known_t:
+        raise ValueError(f"unknown tool-call parser {tool_call_parser!r} (known: {sorted(known_t)})")
+    return (known_r[reasoning_parser]() if reasoning_parser else None, known_t[tool_call_parser]() if tool_call_parser else None)
+
+
+def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoning=None, tools=None):
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
         timeout = 120           # keep-alive
@@ -230,6 +243,7 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
             created = int(time.time())
             n_prompt, out_ids, final = len(ids), [], None
             sent_text, final_text, final_reason = "", None, None
+            saw_tool_call, content_seen = False, ""
 
             def chunk_obj(text, finish):
                 usage = {"prompt_tokens": n_prompt, "completion_tokens": len(out_ids), "total_tokens": n_prompt + len(out_ids)}
@@ -294,8 +308,24 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
                             hold = max((n for x in stop for n in range(1, len(x)) if stable.endswith(x[:n])), default=0)
                             stable = stable[:len(stable) - hold]
                         piece = stable[len(sent_text):] if stable.startswith(sent_text) else tok.decode(o.new_token_ids)
+                        obj = chunk_obj(piece, o.finish_reason if o.finished else None)
+                        if chat and (reasoning is not None or tools is not None):
+                            # the delta is split into reasoning / content / tool calls; markers never reach the client
+                            delta = {"content": piece} if piece else {}
+                            if reasoning is not None:
+                                delta = reasoning.extract_reasoning_content_streaming(sent_text, piece) or {}
+                            if tools is not None and delta.get("content"):
+                                c = delta.pop("content")
+                                t = tools.extract_tool_calls_streaming(content_seen, c) or {}
+                                content_seen += c             # what the tool parser has been shown so far
+                                delta.update(t)
+                                if t.get("tool_calls"):
+                                    saw_tool_call = True
+                            obj["choices"][0]["delta"] = delta
+                            if o.finished and saw_tool_call:
+                                obj["choices"][0]["finish_reason"] = "tool_calls"
                         sent_text += piece
-                        self.wfile.write(("data: " + json.dumps(chunk_obj(piece, o.finish_reason if o.finished else None)) + "\n\n").encode())
+                        self.wfile.write(("data: " + json.dumps(obj) + "\n\n").encode())
                         self.wfile.flush()
                     if o.finished:
                         final = o
@@ -319,7 +349,15 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
             resp = chunk_obj(text, reason)
             resp["object"] = "chat.completion" if chat else "text_completion"
             if chat:
-                resp["choices"][0] = {"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}
+                message = {"role": "assistant", "content": text}
+                if reasoning is not None:
+                    message["reasoning_content"], message["content"] = reasoning.extract_reasoning_content(text)
+                if tools is not None and message["content"]:
+                    ex = tools.extract_tool_calls(message["content"])
+                    if ex.tools_called:
+                        message["content"], message["tool_calls"] = ex.content, [c.to_dict() for c in ex.tool_calls]
+                        reason = "tool_calls"
+                resp["choices"][0] = {"index": 0, "message": message, "finish_reason": reason}
             if final.kv_transfer_params:
                 resp["kv_transfer_params"] = final.kv_transfer_params
             try:
@@ -331,11 +369,12 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str):
 
 
 def serve(engine_cfg: EngineConfig, host: str = "0.0.0.0", port: int = 8000, tokenizer: Optional[str] = None,
-          model_cfg=None, block: bool = True):
+          model_cfg=None, block: bool = True, reasoning_parser: Optional[str] = None, tool_call_parser: Optional[str] = None):
+    reasoning, tools = _make_parsers(reasoning_parser, tool_call_parser)
     engine = EngineCore(engine_cfg, model_cfg=model_cfg)
     aeng = AsyncEngine(engine)
     tok = TokenizerPool(tokenizer, vocab_size=engine.model_cfg.vocab_size)
-    srv = ThreadingHTTPServer((host, port), make_handler(aeng, tok, engine.model_cfg.name or engine_cfg.model))
+    srv = ThreadingHTTPServer((host, port), make_handler(aeng, tok, engine.model_cfg.name or engine_cfg.model, reasoning, tools))
     srv.daemon_threads = True
     if block:
         try:
@@ -371,6 +410,9 @@ def main(argv=None) -> int:
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--enable-chunked-prefill", action="store_true")
     ap.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"])
+    ap.add_argument("--reasoning-parser", default=None, help="split chat answers into reasoning and content (pangu)")
+    ap.add_argument("--tool-call-parser", default=None, help="turn tool-call blocks of chat answers into tool_calls (pangu)")
+    ap.add_argument("--enable-auto-tool-choice", action="store_true", help="accepted for compatibility: tool calls are parsed whenever a parser is set")
     a = ap.parse_args(argv)
     cfg = EngineConfig(model=a.model, device=a.device, max_num_seqs=a.max_num_seqs, max_model_len=a.max_model_len,
                        max_num_batched_tokens=a.max_num_batched_tokens, block_size=a.block_size, num_kv_blocks=a.num_kv_blocks,
@@ -382,7 +424,7 @@ def main(argv=None) -> int:
     if a.additional_config:
         from ..adaptors.vllm.platform import ConfigUpdater
         ConfigUpdater.update_engine_config(cfg, json.loads(a.additional_config))
-    serve(cfg, a.host, a.port, a.tokenizer)
+    serve(cfg, a.host, a.port, a.tokenizer, reasoning_parser=a.reasoning_parser, tool_call_parser=a.tool_call_parser)
     return 0
 
 

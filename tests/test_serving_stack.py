@@ -169,6 +169,66 @@ def test_api_sampling_parameters_and_stop_strings():
         aeng.stop()
 
 
+def test_chat_endpoint_splits_reasoning_content_and_tool_calls():
+    """The chat endpoint with ``--reasoning-parser pangu --tool-call-parser pangu``: a scripted model answer with a
+    chain of thought, an answer and a tool call comes back as reasoning_content / content / tool_calls, whole and
+    streamed (the markers never reach the client, also when they arrive split over several tokens)."""
+    import queue
+    import threading
+    from http.server import ThreadingHTTPServer
+    from types import SimpleNamespace
+    from omni_infer_b200.engine.api_server import _make_parsers, make_handler
+    from omni_infer_b200.engine.request import RequestOutput
+    script = '[unused16]the user wants weather[unused17]Let me check. [unused11]get_weather|{"city": "Paris"}[unused12]'
+    data = list(script.encode())
+
+    class FakeEngine:
+        stats = {"requests": 0, "tokens": 0, "failed_steps": 0}
+        healthy = True
+        engine = SimpleNamespace(role="mixed", cfg=SimpleNamespace(max_model_len=4096))
+
+        def submit(self, ids, sp, rid, kvp=None, priority=0):
+            q = queue.Queue()
+            for i in range(0, len(data), 3):               # three bytes per step: markers are split across steps
+                chunk = data[i:i + 3]
+                last = i + 3 >= len(data)
+                q.put(RequestOutput(rid, chunk, last, "stop" if last else None, None, len(ids), i + len(chunk)))
+            return q
+
+        def abort(self, rid):
+            pass
+
+    with pytest.raises(ValueError):
+        _make_parsers("nope", None)
+    reasoning, tools = _make_parsers("pangu", "pangu")
+    tok = TokenizerPool(None, vocab_size=1024)
+    srv = ThreadingHTTPServer(("127.0.0.1", 0), make_handler(FakeEngine(), tok, "m", reasoning, tools))
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    port = srv.server_port
+    try:
+        body = {"messages": [{"role": "user", "content": "weather in Paris?"}], "max_tokens": 200}
+        r = json.loads(_post(port, "/v1/chat/completions", body))
+        msg = r["choices"][0]["message"]
+        assert msg["reasoning_content"] == "the user wants weather" and msg["content"] == "Let me check."
+        assert msg["tool_calls"][0]["function"] == {"name": "get_weather", "arguments": '{"city": "Paris"}'}
+        assert r["choices"][0]["finish_reason"] == "tool_calls"
+        text = _post(port, "/v1/chat/completions", dict(body, stream=True))
+        chunks = [json.loads(l[6:]) for l in text.splitlines() if l.startswith("data: {")]
+        deltas = [c["choices"][0]["delta"] for c in chunks]
+        assert "".join(d.get("reasoning_content", "") for d in deltas) == "the user wants weather"
+        assert "".join(d.get("content", "") for d in deltas).strip() == "Let me check."
+        calls = [t for d in deltas for t in d.get("tool_calls", [])]
+        assert len(calls) == 1 and calls[0]["function"]["name"] == "get_weather" and calls[0]["index"] == 0
+        assert "unused" not in "".join(json.dumps(d) for d in deltas)
+        assert chunks[-1]["choices"][0]["finish_reason"] == "tool_calls"
+        # the plain completions endpoint is not touched by the parsers
+        r = json.loads(_post(port, "/v1/completions", {"prompt": "x", "max_tokens": 200}))
+        assert r["choices"][0]["text"] == script
+    finally:
+        srv.shutdown()
+        tok.shutdown()
+
+
 def test_tokenizer_pool_offloads_long_prompts():
     pool = TokenizerPool(None, vocab_size=300, workers=1, threshold=10, enabled=True)
     try:
