@@ -37,6 +37,11 @@ def _lazy():
 def register_model() -> dict:
     """Entry point name kept from the reference's ``vllm.general_plugins`` hook."""
     _lazy()
+    try:      # the response parsers of the Pangu models, under the name "pangu" in the host engine's parser managers
+        from .pangu.host_engine import register_with_host_engine
+        register_with_host_engine()
+    except Exception:  # noqa: BLE001  (no host engine: the in-repo API server has its own wiring)
+        pass
     if os.environ.get("PROFILING_NAMELIST"):
         from ..utils.profiler_patches import apply_patches
         apply_patches(os.environ["PROFILING_NAMELIST"])

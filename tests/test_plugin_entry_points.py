@@ -78,3 +78,32 @@ def test_check_and_update_config_on_a_host_engine_config(dist_info):
 def test_cli_script_entry(dist_info):
     eps = {e.name: e for e in md.entry_points(group="console_scripts")}
     assert eps["omni_cli"].load().__module__ == "omni_infer_b200.cli.main"
+
+
+def test_pangu_parsers_register_with_the_host_engine():
+    """``register_model`` (the general-plugins hook) also puts the Pangu reasoning and tool-call parsers under the name
+    ``pangu`` into the host engine's parser managers, and the adapters speak the managers' interface."""
+    pytest.importorskip("vllm")
+    from omni_infer_b200.models.pangu.host_engine import (PanguHostReasoningParser, PanguHostToolParser,
+                                                          register_with_host_engine)
+    done = register_with_host_engine()
+    if done["reasoning"]:
+        from vllm.reasoning import ReasoningParserManager
+        assert ReasoningParserManager.get_reasoning_parser("pangu") is PanguHostReasoningParser
+    if done["tool"]:
+        from vllm.tool_parsers import ToolParserManager
+        assert ToolParserManager.get_tool_parser("pangu") is PanguHostToolParser
+    assert done["reasoning"] or done["tool"]
+
+    class Tok:
+        def get_vocab(self):
+            return {"[unused16]": 7, "[unused17]": 8, "a": 1}
+
+    r = PanguHostReasoningParser(Tok())
+    assert r.extract_reasoning("[unused16]think[unused17]answer", None) == ("think", "answer")
+    assert r.is_reasoning_end([1, 8, 1]) and not r.is_reasoning_end([1, 1]) and r.extract_content_ids([1, 8, 1, 1]) == [1, 1]
+    d = r.extract_reasoning_streaming("[unused16]thi", "[unused16]think", "nk")
+    assert (getattr(d, "reasoning", None) or (d.get("reasoning_content") if isinstance(d, dict) else None)) == "nk"
+    t = PanguHostToolParser(Tok())
+    ex = t.extract_tool_calls('ok [unused11]f|{"a": 1}[unused12]', None)
+    assert ex.tools_called and ex.tool_calls[0].function.name == "f" if hasattr(ex.tool_calls[0], "function") else ex.tool_calls[0].name == "f"
