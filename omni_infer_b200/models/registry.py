@@ -40,6 +40,8 @@ def register_model() -> dict:
     try:      # the response parsers of the Pangu models, under the name "pangu" in the host engine's parser managers
         from .pangu.host_engine import register_with_host_engine
         register_with_host_engine()
+        from ..quantization.host_engine import register_with_host_engine as register_quantization
+        register_quantization()
     except Exception:  # noqa: BLE001  (no host engine: the in-repo API server has its own wiring)
         pass
     if os.environ.get("PROFILING_NAMELIST"):

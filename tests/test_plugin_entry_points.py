@@ -107,3 +107,17 @@ def test_pangu_parsers_register_with_the_host_engine():
     t = PanguHostToolParser(Tok())
     ex = t.extract_tool_calls('ok [unused11]f|{"a": 1}[unused12]', None)
     assert ex.tools_called and ex.tool_calls[0].function.name == "f" if hasattr(ex.tool_calls[0], "function") else ex.tool_calls[0].name == "f"
+
+
+def test_quantisation_name_registers_with_the_host_engine():
+    pytest.importorskip("vllm")
+    from omni_infer_b200.quantization.host_engine import NAME, register_with_host_engine
+    if not register_with_host_engine():
+        pytest.skip("the host engine's quantisation registry is not importable here")
+    from vllm.model_executor.layers.quantization import QUANTIZATION_METHODS, get_quantization_config
+    assert NAME in QUANTIZATION_METHODS
+    cls = get_quantization_config(NAME)
+    cfg = cls.from_config({"config_groups": {"group_0": {"weights": {"num_bits": 8}}}, "ignore": ["lm_head"]})
+    assert cfg.get_name() == NAME and cfg.inner.name == "w8a8_int8" and cfg.inner.ignore == ["lm_head"]
+    assert cls.get_config_filenames() == ["quant_model_description.json"] and cls.get_min_capability() == 100
+    assert register_with_host_engine()                  # a second call is harmless
