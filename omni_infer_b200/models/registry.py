@@ -44,6 +44,12 @@ def register_model() -> dict:
         register_quantization()
     except Exception:  # noqa: BLE001  (no host engine: the in-repo API server has its own wiring)
         pass
+    try:      # architecture names -> these classes in the host engine's model registry (lazy form: nothing is imported)
+        from vllm import ModelRegistry
+        for arch, cls in _REGISTRY.items():
+            ModelRegistry.register_model(arch, f"{cls.__module__}:{cls.__qualname__}")
+    except Exception:  # noqa: BLE001
+        pass
     if os.environ.get("PROFILING_NAMELIST"):
         from ..utils.profiler_patches import apply_patches
         apply_patches(os.environ["PROFILING_NAMELIST"])

@@ -57,6 +57,11 @@ def test_host_engine_loader_sees_the_plugins(dist_info):
     assert {"b200_optimized_models", "kv_connectors"} <= set(general)
     models = general["b200_optimized_models"]()
     assert {"DeepseekV3ForCausalLM", "DeepseekV2ForCausalLM", "Qwen2ForCausalLM", "DeepSeekMTPModel"} <= set(models)
+    from vllm import ModelRegistry
+    import vllm.model_executor.models.registry as host_registry
+    lazy = ModelRegistry.models["DeepseekV3ForCausalLM"]         # the host's entry now names this package's class
+    assert getattr(lazy, "module_name", "").startswith("omni_infer_b200.models") and lazy.class_name == "DeepseekV3ForCausalLM"
+    assert "Qwen3MoeForCausalLM" in ModelRegistry.get_supported_archs() and host_registry is not None
     conns = general["kv_connectors"]()
     assert "B200PeerPushConnectorV1" in conns and "AscendHcclConnectorV1" in conns
     from omni_infer_b200.accelerators.pd import get_connector_class
