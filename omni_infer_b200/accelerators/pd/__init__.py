@@ -24,7 +24,8 @@ def register() -> dict:
         from vllm.distributed.kv_transfer.kv_connector.factory import KVConnectorFactory
         for name in (CONNECTOR_NAME, *COMPAT_NAMES):
             if name not in getattr(KVConnectorFactory, "_registry", {}):
-                KVConnectorFactory.register_connector(name, mod, cls)
+                # the host engine gets the class that speaks its connector interface and delegates to this package's pair
+                KVConnectorFactory.register_connector(name, "omni_infer_b200.accelerators.pd.host_engine", "B200PeerPushConnectorV1")
     except Exception:  # noqa: BLE001  (no host engine: the in-repo engine uses create_connectors directly)
         pass
     return {name: mod for name in _REGISTERED}

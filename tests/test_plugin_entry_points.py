@@ -126,3 +126,61 @@ def test_quantisation_name_registers_with_the_host_engine():
     assert cfg.get_name() == NAME and cfg.inner.name == "w8a8_int8" and cfg.inner.ignore == ["lm_head"]
     assert cls.get_config_filenames() == ["quant_model_description.json"] and cls.get_min_capability() == 100
     assert register_with_host_engine()                  # a second call is harmless
+
+
+def test_connector_class_for_the_host_engine_delegates_to_the_pair():
+    """The class the host engine's connector factory loads: one object per role over this package's connector pair; a
+    prefill-role and a decode-role object move a request's blocks between two caches through the factory's interface."""
+    pytest.importorskip("vllm")
+    import time
+    from types import SimpleNamespace
+    import torch
+    from vllm.distributed.kv_transfer.kv_connector.factory import KVConnectorFactory
+    from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorBase_V1, KVConnectorRole
+    from omni_infer_b200.accelerators import pd
+    from omni_infer_b200.engine.request import Request, RequestStatus, SamplingParams
+    pd.register()
+    pd.InProcessHub.reset()
+    loader = KVConnectorFactory._registry["B200PeerPushConnectorV1"]
+    cls = loader()
+    assert issubclass(cls, KVConnectorBase_V1) and cls.__name__ == "B200PeerPushConnectorV1"
+    assert KVConnectorFactory._registry["AscendHcclConnectorV1"]() is cls
+
+    def make(role_name, name):
+        vc = SimpleNamespace(kv_transfer_config={"kv_role": role_name, "engine_id": name, "endpoint": f"inproc://{name}",
+                                                 "sync_timeout_s": 5.0, "retries": 2, "retry_wait_s": 0.2},
+                             cache_config=SimpleNamespace(block_size=4), speculative_config=None)
+        return cls(vc, KVConnectorRole.WORKER, None)
+
+    P, D = make("kv_producer", "hp"), make("kv_consumer", "hd")
+    p_cache = {"layer0": torch.arange(8 * 4 * 2, dtype=torch.float32).view(8, 4, 2)}
+    d_cache = {"layer0": torch.zeros(8, 4, 2)}
+    P.register_kv_caches(p_cache)
+    D.register_kv_caches(d_cache)
+    # prefill side: a request that ended at its token cap hands blocks 2 and 3 over
+    done = Request("r", list(range(7)), SamplingParams(max_tokens=1), status=RequestStatus.FINISHED_LENGTH_CAPPED, output_token_ids=[5])
+    delay, params = P.request_finished(done, [2, 3])
+    assert delay and params["remote_block_ids"] == [2, 3] and params["prefilled_token"] == 5
+    # decode side: the scheduler reserves blocks 5 and 6 and asks for the load
+    req = Request("r", list(range(7)), SamplingParams(max_tokens=4), kv_transfer_params=dict(params))
+    n, is_async = D.get_num_new_matched_tokens(req, 0)
+    assert (n, is_async) == (8, True)
+    req.block_ids = [5, 6]
+    D.update_state_after_alloc(req, SimpleNamespace(get_block_ids=lambda: [[5, 6]]), n)
+    meta = D.build_connector_meta(None)
+    D.bind_connector_metadata(meta)
+    D.start_load_kv(None)
+    sent = received = None
+    for _ in range(200):
+        s, r = D.get_finished(set())
+        received = received or r
+        s2, _ = P.get_finished(set())
+        sent = sent or s2
+        if sent and received:
+            break
+        time.sleep(0.01)
+    assert received == {"r"} and sent == {"r"}
+    assert torch.equal(d_cache["layer0"][5:7], p_cache["layer0"][2:4]) and float(d_cache["layer0"][:5].abs().sum()) == 0
+    P.shutdown()
+    D.shutdown()
+    pd.InProcessHub.reset()
