@@ -160,3 +160,40 @@ def test_priority_scheduling_serves_urgent_requests_first():
                 order.append(r.request_id)
     assert order == [ids[1], ids[2], ids[0]]
     assert [outs[i] for i in ids] == want
+
+
+@pytest.mark.parametrize("seed,kw,mtp", [
+    (0, dict(num_kv_blocks=14, enable_prefix_caching=True, enable_chunked_prefill=True, max_num_batched_tokens=32), False),
+    (1, dict(num_kv_blocks=16, num_step=3, scheduling_policy="priority"), False),
+    (2, dict(num_kv_blocks=18, num_speculative_tokens=1, num_step=2, enable_prefix_caching=True), True),
+    (3, dict(num_kv_blocks=16, async_schedule=True, enable_chunked_prefill=True, max_num_batched_tokens=24), False),
+])
+def test_random_arrivals_through_the_whole_engine(seed, kw, mtp):
+    """Requests of random lengths arriving at random steps (some with a shared prefix, some with priorities) through
+    scheduler, block manager, input preparation and the model under a small KV pool: every request's tokens equal what
+    it gets when it is served alone by a plain engine."""
+    import random
+    rnd = random.Random(seed)
+    over = {"num_nextn_predict_layers": 1} if mtp else {}
+    g = torch.Generator().manual_seed(100 + seed)
+    shared = torch.randint(0, 1024, (32,), generator=g).tolist()
+    jobs = []
+    for i in range(10):
+        body = torch.randint(0, 1024, (rnd.randint(1, 40),), generator=g).tolist()
+        prompt = (shared[: rnd.choice([0, 16, 32])] + body)[:60]
+        jobs.append((rnd.randint(0, 25), prompt, rnd.randint(1, 14), rnd.randint(0, 2)))
+    base = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu", model_overrides=over)
+    want = [base.generate([p], SamplingParams(max_tokens=n))[0] for _, p, n, _ in jobs]
+    eng = EngineCore(EngineConfig(block_size=16, max_model_len=128, device="cpu", max_num_seqs=4, model_overrides=over, **kw))
+    pending = sorted(range(len(jobs)), key=lambda i: jobs[i][0])
+    ids, outs, step = {}, {}, 0
+    while pending or eng.has_unfinished:
+        while pending and jobs[pending[0]][0] <= step:
+            i = pending.pop(0)
+            ids[i] = eng.add_request(jobs[i][1], SamplingParams(max_tokens=jobs[i][2]), priority=jobs[i][3])
+        for r in eng.step():
+            outs.setdefault(r.request_id, []).extend(r.new_token_ids)
+        step += 1
+        assert step < 3000
+    assert [outs[ids[i]] for i in range(len(jobs))] == want
+    assert eng.kv.num_free_blocks == kw["num_kv_blocks"] - 1
