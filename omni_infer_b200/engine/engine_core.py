@@ -127,6 +127,7 @@ class EngineCore:
         self._world = get_parallel_state().world_size
         self._pool = ThreadPoolExecutor(max_workers=1) if cfg.async_schedule else None
         self._inflight = None
+        self._deferred_aborts: list = []
         self.metrics = {"steps": 0, "prefill_steps": 0, "decode_steps": 0, "generated_tokens": 0}
 
     # ------------------------------------------------------------------ intake
@@ -155,6 +156,12 @@ class EngineCore:
         return rid
 
     def abort(self, request_id: str) -> None:
+        """Drops a request.  While a round is being executed on the worker thread (asynchronous scheduling) the runner
+        reads the requests of that round - their block lists, their token counts - so the drop waits until the round's
+        results have been applied; the request takes part in at most that one more round."""
+        if self._inflight is not None:
+            self._deferred_aborts.append(request_id)
+            return
         self.scheduler.abort_request(request_id)
 
     @property
@@ -188,6 +195,10 @@ class EngineCore:
         out = fut.result()
         res = self.scheduler.update_from_output(so, out)
         self._account(so, res)
+        self._inflight = None
+        for rid in self._deferred_aborts:          # nothing is executing now: requests may change
+            self.scheduler.abort_request(rid)
+        self._deferred_aborts = []
         nxt = self.scheduler.schedule()
         if not nxt.empty or nxt.kv_connector_metadata is not None and self.scheduler.has_unfinished:
             self._inflight = (nxt, self._pool.submit(self.worker.execute_model, nxt))

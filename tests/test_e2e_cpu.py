@@ -197,3 +197,28 @@ def test_random_arrivals_through_the_whole_engine(seed, kw, mtp):
         assert step < 3000
     assert [outs[ids[i]] for i in range(len(jobs))] == want
     assert eng.kv.num_free_blocks == kw["num_kv_blocks"] - 1
+
+
+def test_abort_while_a_round_is_executing_under_async_scheduling():
+    """With asynchronous scheduling a round runs on the worker thread while the caller may drop requests.  Dropping a
+    request of the executing round used to free its blocks under the runner's feet; it now takes effect once the round's
+    results are in.  The other requests are unaffected and nothing leaks."""
+    prompts = _prompts(3, 30, seed=7)
+    base = LLM("tiny-deepseek-v3", block_size=16, num_kv_blocks=64, max_model_len=128, device="cpu")
+    want = base.generate(prompts, SamplingParams(max_tokens=10))
+    for drop_at in range(1, 8):
+        eng = EngineCore(EngineConfig(block_size=16, num_kv_blocks=32, max_model_len=128, device="cpu", async_schedule=True,
+                                      enable_chunked_prefill=True, max_num_batched_tokens=24))
+        ids = [eng.add_request(p, SamplingParams(max_tokens=10)) for p in prompts]
+        outs, step = {}, 0
+        while eng.has_unfinished:
+            if step == drop_at:
+                eng.abort(ids[1])                         # a round is in flight at this point
+            for r in eng.step():
+                outs.setdefault(r.request_id, []).extend(r.new_token_ids)
+            step += 1
+            assert step < 500
+        assert outs[ids[0]] == want[0] and outs[ids[2]] == want[2]
+        assert outs.get(ids[1], []) == want[1][:len(outs.get(ids[1], []))]
+        assert eng.scheduler.requests[ids[1]].status.name == "FINISHED_ABORTED"
+        assert eng.kv.num_free_blocks == 31
