@@ -53,7 +53,7 @@ class Scheduler:
         self.finished_recving: set = set()
         self.pull_kv_lock = threading.Lock()  # serialises the fast-path KV pull with schedule()
         self._aborting: dict = {}             # dropped while their KV transfer ran: finished when it has concluded
-        self._capacity_stopped: list = []     # ended by schedule() for lack of KV capacity; reported with the next outputs
+        self._capacity_stopped: list = []     # (request, new tokens) ended inside schedule(): reported with the next outputs
         self.stats = {"preemptions": 0, "scheduled_prefill_tokens": 0, "scheduled_decode_tokens": 0, "steps": 0}
 
     # ------------------------------------------------------------------ intake
@@ -137,7 +137,15 @@ class Scheduler:
                         continue
                     params = req.kv_transfer_params or {}
                     if params.get("prefilled_token") is not None and not req.output_token_ids:
-                        req.output_token_ids.append(int(params["prefilled_token"]))   # reuse P's first token
+                        # reuse the prefill instance's first token; it counts like any sampled token, so it can end the
+                        # request (token cap of one, end-of-sequence, a stop id) before anything is decoded here
+                        first: list = []
+                        self._append(req, [int(params["prefilled_token"])], first)
+                        if req.is_finished:
+                            self.waiting.remove(req)
+                            self.kv.free(req)
+                            self._capacity_stopped.append((req, first))
+                            continue
                         req._emit_prefilled = True
                     req.num_computed_tokens = req.num_tokens - 1
                     if cfg.num_speculative_tokens:
@@ -205,7 +213,7 @@ class Scheduler:
                     self.kv.blocks_needed(req.num_prompt_tokens + 1) > self.kv.num_blocks - 1:
                 self.waiting.popleft()
                 self._finish(req, RequestStatus.FINISHED_IGNORED)
-                self._capacity_stopped.append(req)     # nobody else would tell the client: reported with the next outputs
+                self._capacity_stopped.append((req, []))     # nobody else would tell the client: reported with the next outputs
                 continue
             computed_blocks, n_cached = ([], 0)
             if req.num_computed_tokens == 0 and not req.block_ids:
@@ -308,7 +316,7 @@ class Scheduler:
         self.kv.free(req)
         self._finish(req, RequestStatus.FINISHED_LENGTH_CAPPED)
         self.stats["kv_capacity_stops"] = self.stats.get("kv_capacity_stops", 0) + 1
-        self._capacity_stopped.append(req)
+        self._capacity_stopped.append((req, []))
 
     def _preempt(self, req: Request) -> None:
         self.kv.free(req)
@@ -348,9 +356,9 @@ class Scheduler:
             req = self.pending_free.pop(rid, None)
             if req is not None:
                 self.kv.free(req)          # safe when already freed
-        for req in self._capacity_stopped:
-            results.append(RequestOutput(req.request_id, [], True, FINISH_REASON.get(req.status), None, req.num_prompt_tokens,
-                                         len(req.output_token_ids)))
+        for req, toks in self._capacity_stopped:
+            results.append(RequestOutput(req.request_id, list(toks), True, FINISH_REASON.get(req.status), None,
+                                         req.num_prompt_tokens, len(req.output_token_ids)))
         self._capacity_stopped = []
         idx_of = {rid: i for i, rid in enumerate(out.req_ids)}
         for s in sched.scheduled:

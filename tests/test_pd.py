@@ -401,3 +401,34 @@ def test_pd_into_a_decode_instance_with_omni_attention(prompt_len):
     assert [outs[f"r{i}"] for i in range(2)] == want
     assert D.scheduler.stats.get("kv_fallbacks", 0) == 0                     # the KV really came from the prefill instance
     assert len(D.kv.window_free) == 4 * 4 and D.kv.num_free_blocks == 63
+
+
+def test_the_reused_prefill_token_counts_towards_the_stop_conditions():
+    """The decode instance takes its first token from the prefill instance.  That token is an output token like any
+    other: a request with ``max_tokens = 1``, or one whose first token is a stop id, ends with it instead of decoding
+    one more."""
+    prompts = _prompts(2, 30, seed=8)
+    want = _mixed_reference(prompts, 5)
+    P, D = _engine("kv_producer", "p40"), _engine("kv_consumer", "d40")
+    handoff = {}
+    for i, p in enumerate(prompts):
+        P.add_request(p, SamplingParams(max_tokens=1), request_id=f"r{i}", kv_transfer_params={"do_remote_decode": True})
+    while P.scheduler.has_unfinished:
+        for out in P.step():
+            if out.finished:
+                handoff[out.request_id] = out.kv_transfer_params
+    D.add_request(prompts[0], SamplingParams(max_tokens=1), request_id="r0", kv_transfer_params=dict(handoff["r0"]))
+    D.add_request(prompts[1], SamplingParams(max_tokens=5, stop_token_ids=(want[1][0],)), request_id="r1",
+                  kv_transfer_params=dict(handoff["r1"]))
+    outs, reasons = {}, {}
+    t0 = time.time()
+    while (D.has_unfinished or P.scheduler.pending_free) and time.time() - t0 < 20:
+        for out in D.step():
+            outs.setdefault(out.request_id, []).extend(out.new_token_ids)
+            if out.finished:
+                reasons[out.request_id] = out.finish_reason
+        P.step()
+        time.sleep(0.001)
+    assert outs == {"r0": want[0][:1], "r1": want[1][:1]}
+    assert reasons == {"r0": "length", "r1": "stop"}
+    assert D.scheduler.kv.num_free_blocks == 47 and P.scheduler.kv.num_free_blocks == 47
