@@ -13,6 +13,12 @@ def apply_omni_attn_patch(engine, config: dict, is_kv_consumer: bool = True) -> 
     runner = engine.worker.runner
     if runner.tpr != 1:
         raise ValueError("Omni-Attention is not combined with speculative decoding here")
+    if engine.cfg.enable_chunked_prefill or engine.cfg.enable_prefix_caching:
+        # A later chunk (or a request that starts from cached blocks) attends over what earlier tokens left in the cache.
+        # A compressed layer keeps only its window of them, so the result would differ from a prefill that sees the whole
+        # prompt at once - which is what the layer pattern was chosen for.  The reference runs Omni-Attention on decode
+        # instances, whose prompts are prefilled elsewhere (omni/accelerators/cache/__init__.py:28-69).
+        raise ValueError("Omni-Attention cannot be combined with chunked prefill or prefix caching")
     n_layers = runner.model.num_kv_layers
     cfg = OmniAttnConfig.from_dict(config, n_layers)
     state = OmniAttnState(cfg, engine.cfg.block_size)

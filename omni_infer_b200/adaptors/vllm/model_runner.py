@@ -460,8 +460,9 @@ class ModelRunner:
             nb = self.omni.spec.blocks_per_request
             wt = [list(s.request.omni_block_ids) for s in so.scheduled] + [[0] * nb] * (padded - B)
             pl = [s.request.num_prompt_tokens for s in so.scheduled] + [0] * (padded - B)
-            om = self.omni.decode_metadata(d_seq, self._to_dev(pl, torch.int32), self._to_dev(wt, torch.int32))
-            om["pattern"] = self.omni.pattern
+            pl_dev = self._to_dev(pl, torch.int32)
+            om = self.omni.decode_metadata(d_seq, pl_dev, self._to_dev(wt, torch.int32))
+            om["pattern"], om["prompt_lens"] = self.omni.pattern, pl_dev
             md.omni = om
         return d64[:n], md
 
@@ -610,6 +611,9 @@ class ModelRunner:
                     ops.step_advance(md.positions, md.seq_lens, md.slot_mapping, md.block_table, self.cfg.block_size, 1)
                     md.q_seq_lens = md.seq_lens
                     md.max_seq_len += 1
+                    if md.omni is not None:      # the windows of the compressed layers move on with the sequence
+                        nxt = self.omni.decode_metadata(md.seq_lens, md.omni["prompt_lens"], md.omni["block_table"])
+                        md.omni = dict(md.omni, **nxt)
                     ids = toks
                 continue
             # ---- MTP: verify the drafts, then draft again from the last accepted position

@@ -153,3 +153,26 @@ def test_engine_with_omni_attention_survives_preemption():
     tight, eng = run(13)                                    # 12 usable blocks for 3 x 80 tokens: somebody has to go
     assert eng.scheduler.stats["preemptions"] > 0
     assert tight == roomy
+
+
+def test_omni_attention_with_multi_step_rounds_and_async_scheduling():
+    """Several model steps per scheduling round: the windows of the compressed layers have to move on with every step of
+    the round, not once per round.  Sequences grow past the window; tokens equal the one-step-per-round run."""
+    import pytest
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (20, 61, 90)]
+    omni = dict(enable_omni_attn=True, omni_attn_config={"sink": 1, "recent": 2, "pattern": [1, 0]})
+
+    def run(**kw):
+        e = EngineCore(EngineConfig(block_size=16, num_kv_blocks=64, max_model_len=256, device="cpu", max_num_seqs=4, **omni, **kw))
+        ids = [e.add_request(p, SamplingParams(max_tokens=40)) for p in prompts]
+        outs = e.run_until_done()
+        return [outs[i] for i in ids]
+
+    want = run()
+    assert run(num_step=3) == want
+    assert run(num_step=2, async_schedule=True) == want
+    # what cannot be combined is refused at start, not discovered as an index error later
+    for bad in (dict(enable_chunked_prefill=True), dict(enable_prefix_caching=True)):
+        with pytest.raises(ValueError):
+            EngineCore(EngineConfig(block_size=16, num_kv_blocks=64, max_model_len=256, device="cpu", **omni, **bad))
