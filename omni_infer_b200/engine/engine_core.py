@@ -166,18 +166,17 @@ class EngineCore:
 
     @property
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished or self._inflight is not None
+        # an empty round in flight (an idle rank keeping step with its peers) is not work of this rank
+        return self.scheduler.has_unfinished or (self._inflight is not None and not self._inflight[0].empty)
 
     # ------------------------------------------------------------------ stepping
     def step(self) -> list:
         if self.cfg.async_schedule:
             return self.step_async()
         so = self.scheduler.schedule()
-        if so.empty and self._world > 1:
-            # data-parallel ranks step together: an idle rank runs a padded dummy batch so that the
-            # expert-parallel exchanges of the busy ranks find their peer
-            self.worker.execute_dummy_batch()
-        out = self.worker.execute_model(so)
+        # data-parallel ranks step together: an idle rank runs a padded dummy batch so that the
+        # expert-parallel exchanges of the busy ranks find their peer
+        out = self._execute(so)
         res = self.scheduler.update_from_output(so, out)
         self._account(so, res)
         return res
@@ -189,7 +188,7 @@ class EngineCore:
         results: list = []
         if self._inflight is None:
             so = self.scheduler.schedule()
-            self._inflight = (so, self._pool.submit(self.worker.execute_model, so))
+            self._inflight = (so, self._pool.submit(self._execute, so))
             return results
         so, fut = self._inflight
         out = fut.result()
@@ -200,11 +199,18 @@ class EngineCore:
             self.scheduler.abort_request(rid)
         self._deferred_aborts = []
         nxt = self.scheduler.schedule()
-        if not nxt.empty or nxt.kv_connector_metadata is not None and self.scheduler.has_unfinished:
-            self._inflight = (nxt, self._pool.submit(self.worker.execute_model, nxt))
+        # with several data-parallel ranks an idle rank keeps executing (dummy batches): its peers' exchanges need it
+        if not nxt.empty or self._world > 1 or nxt.kv_connector_metadata is not None and self.scheduler.has_unfinished:
+            self._inflight = (nxt, self._pool.submit(self._execute, nxt))
         else:
             self._inflight = None
         return res
+
+    def _execute(self, so):
+        """One round on the worker; a rank with nothing scheduled still takes part in the step of its peers."""
+        if so.empty and self._world > 1:
+            self.worker.execute_dummy_batch()
+        return self.worker.execute_model(so)
 
     def _account(self, so, res) -> None:
         self.metrics["steps"] += 1

@@ -268,7 +268,9 @@ def _ep_uneven(rank, world, mode, vocab_parallel=False):
     from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
     from omni_infer_b200.engine.request import SamplingParams
     kw = dict(block_size=16, num_kv_blocks=48, max_model_len=160, device="cpu", seed=3, vocab_parallel=vocab_parallel)
-    if mode != "plain":
+    if mode == "async":
+        kw.update(async_schedule=True, num_step=2)
+    elif mode != "plain":
         kw.update(num_step=2, num_speculative_tokens=1, model_overrides={"num_nextn_predict_layers": 1})
     eng = EngineCore(EngineConfig(**kw))
     g = torch.Generator().manual_seed(11)
@@ -283,6 +285,14 @@ def _ep_uneven(rank, world, mode, vocab_parallel=False):
     if dist.is_initialized():
         dist.barrier()
     return [outs[i] for i in ids]
+
+
+def test_uneven_ranks_with_asynchronous_scheduling():
+    """Asynchronous scheduling on two data-parallel ranks with different work: the rank that runs dry keeps executing
+    dummy rounds on its worker thread, so the busy rank's exchanges always find their peer, and both leave together."""
+    single = _single(_ep_uneven, "async")
+    two = _spawn(_ep_uneven, 2, "async")
+    assert two[0] == single and two[1] == [single[1][:3]]
 
 
 @pytest.mark.parametrize("mode", ["uneven", "idle"])
