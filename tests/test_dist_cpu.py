@@ -444,6 +444,63 @@ def test_tensor_parallel_gqa_attention_matches_single_rank(world, overrides):
     assert all(many[r] == single for r in range(world))
 
 
+# ---------------------------------------------------------------------------------------------- everything at once
+def _mixed_features_engine(rank, world, case):
+    """Ranks with different requests and a KV pool that forces preemption, with the engine options of ``case`` on."""
+    import random
+    from omni_infer_b200.engine.engine_core import EngineConfig, EngineCore
+    from omni_infer_b200.engine.request import SamplingParams
+    case = dict(case)
+    mtp, attn_tp = case.pop("mtp", False), case.pop("attn_tp", False)
+    over = {"num_nextn_predict_layers": 1} if mtp else {}
+    if world == 1:                                    # the baseline: plain options, roomy pool, one request at a time
+        kw = dict(num_kv_blocks=64)
+    else:
+        kw = dict(case, attn_tp=attn_tp, tp_backend="nccl", **({"num_speculative_tokens": 1} if mtp else {}))
+    eng = EngineCore(EngineConfig(block_size=16, max_model_len=128, device="cpu", seed=3, max_num_seqs=4, model_overrides=over, **kw))
+
+    def jobs_of(r):
+        r = 0 if attn_tp else r                       # tensor-parallel attention: every rank serves the same requests
+        g, jr = torch.Generator().manual_seed(77 + r), random.Random(5 + r)
+        shared = torch.randint(0, 1024, (32,), generator=g).tolist()
+        return [((shared[: jr.choice([0, 16, 32])] + torch.randint(0, 1024, (jr.randint(1, 40),), generator=g).tolist())[:60],
+                 jr.randint(1, 12)) for _ in range(jr.randint(1, 5))]
+
+    if world == 1:
+        table = {}
+        for r in range(4):
+            table[r] = []
+            for p, n in jobs_of(r):
+                i = eng.add_request(p, SamplingParams(max_tokens=n))
+                table[r].append(eng.run_until_done()[i])
+        return table
+    jobs = jobs_of(rank)
+    ids = [eng.add_request(p, SamplingParams(max_tokens=n)) for p, n in jobs]
+    outs = eng.run_until_done(max_steps=5000)
+    leak = eng.kv.num_free_blocks != kw["num_kv_blocks"] - 1
+    if dist.is_initialized():
+        dist.barrier()
+    return {"outs": [outs[i] for i in ids], "leak": leak, "preemptions": eng.scheduler.stats["preemptions"]}
+
+
+@pytest.mark.parametrize("world,case", [
+    (2, dict(num_kv_blocks=9, enable_prefix_caching=True, enable_chunked_prefill=True, max_num_batched_tokens=24, num_step=3,
+             async_schedule=True)),
+    (4, dict(num_kv_blocks=10, num_step=3, mtp=True, attn_tp=True, vocab_parallel=True)),
+    (2, dict(num_kv_blocks=9, enable_chunked_prefill=True, max_num_batched_tokens=24, num_step=2, mtp=True, vocab_parallel=True)),
+], ids=["dp2-async-chunked-prefix-multistep", "tp4-mtp-multistep-vocab-parallel", "dp2-mtp-chunked-vocab-parallel"])
+def test_engine_options_together_on_several_ranks(world, case):
+    """The engine options that each have their own test, together, on ranks with different work and KV pools small
+    enough to preempt: every request gets the tokens it gets when served alone by a plain one-rank engine."""
+    base_key = {k: case[k] for k in ("mtp", "attn_tp") if k in case}
+    want = _single(_mixed_features_engine, base_key)
+    got = _spawn(_mixed_features_engine, world, case)
+    for r in range(world):
+        assert got[r]["outs"] == (want[0] if case.get("attn_tp") else want[r]), r
+        assert not got[r]["leak"]
+    assert sum(got[r]["preemptions"] for r in range(world)) > 0
+
+
 # ---------------------------------------------------------------------------------------------- placement across ranks
 def _placement_round(rank, world, host_replica=""):
     from omni_infer_b200.accelerators.placement import OmniPlanner
