@@ -11,6 +11,7 @@
 #include <fstream>
 #include <functional>
 #include <numeric>
+#include <random>
 #include <stdexcept>
 #include <string>
 #include <chrono>
@@ -1031,6 +1032,40 @@ TEST(manager_shows_a_round_to_the_inference_thread_only_when_every_rank_has_stag
   CHECK(c.pls[0]->ready_rounds() == 1 && c.pls[1]->ready_rounds() == 1);
   CHECK(c.pls[0]->do_placement_optimizer() == 0 && c.pls[1]->do_placement_optimizer() == 1);
   CHECK(c.maps[0]->expert_at(0, 5) == 0 && c.maps[1]->selector(0, 0) == 5 && c.held(1, 2) == 0.f && c.views_agree());
+}
+
+TEST(manager_random_traffic_keeps_every_rank_consistent) {
+  // random clusters and random load, several rounds each: after every round all ranks hold the same placement, every
+  // expert has a replica, a slot's bytes are those of the expert the placement names, and every rank's selector points
+  // at a position that holds the expert it is asked for
+  std::mt19937 rng(1234);
+  for (int trial = 0; trial < 12; ++trial) {
+    const int W = 2 + (int)(rng() % 3), per = 1 + (int)(rng() % 3), L = 1 + (int)(rng() % 4), E = W * per;
+    Cluster c(W, E, L);
+    for (int round = 0; round < 5; ++round) {
+      for (int r = 0; r < W; ++r)
+        for (int l = 0; l < L; ++l)
+          for (int s = 0; s < c.S; ++s) {
+            const int e = c.maps[0]->expert_at(l, r * c.S + s);
+            const bool hot = e >= 0 && (int)(rng() % 4) == 0;
+            c.counts[r][l * c.S + s] += e < 0 ? 0 : (hot ? 500 + (int64_t)(rng() % 2000) : (int64_t)(rng() % 60));
+          }
+      c.round();
+      CHECK(c.views_agree());
+      for (int l = 0; l < L; ++l) {
+        for (int e = 0; e < E; ++e) CHECK(c.maps[0]->redundant_count(l, e) >= 1);
+        for (int r = 0; r < W; ++r) {
+          for (int s = 0; s < c.S; ++s) {
+            const int e = c.maps[0]->expert_at(l, r * c.S + s);
+            if (e >= 0) CHECK(c.held(r, s, l) == float(100 * l + e));
+          }
+          for (int e = 0; e < E; ++e) CHECK(c.maps[r]->expert_at(l, c.maps[r]->selector(l, e)) == e);
+        }
+      }
+      // instructions may be put off (a source that changed in the same round, a full staging ring), but by all ranks alike
+      for (int r = 1; r < W; ++r) CHECK(c.pls[r]->skipped_instructions() == c.pls[0]->skipped_instructions());
+    }
+  }
 }
 
 TEST(manager_history_survives_a_restart) {
