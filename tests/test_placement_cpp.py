@@ -68,7 +68,7 @@ def test_cpp_static_planner_tests_pass_under_sanitizers(tmp_path):
 
 def test_cpp_unit_cases_per_component(tmp_path):
     """One small case per behaviour of every unit (tensor, mapping, activation, weights + host replica, transports, both
-    balancers, optimizer, manager): 72 cases."""
+    balancers, optimizer, manager)."""
     import re
     run = _build_and_run(tmp_path, "test_placement_units", "test_placement_units.cpp", "address,undefined")
     m = re.search(r"placement units: (\d+) cases, (\d+) checks, 0 failed", run.stdout)
