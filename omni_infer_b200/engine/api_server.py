@@ -47,16 +47,28 @@ class AsyncEngine:
         self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
 
-    def submit(self, prompt_ids, sampling, request_id, kv_transfer_params=None, priority: int = 0) -> queue.Queue:
+    def submit(self, prompt_ids, sampling, request_id, kv_transfer_params=None, priority: int = 0) -> Optional[queue.Queue]:
         q: queue.Queue = queue.Queue()
         with self.lock:
+            if request_id in self.queues:
+                return None
             self.queues[request_id] = q
         self.inbox.put((prompt_ids, sampling, request_id, kv_transfer_params, priority))
         self.stats["requests"] += 1
         return q
 
     def abort(self, request_id):
+        """Called by the request's own handler once it has stopped reading: an aborted request produces no finished
+        output, so its queue is dropped here and not by the loop."""
+        with self.lock:
+            self.queues.pop(request_id, None)
         self.inbox.put(("abort", request_id))
+
+    def _fail(self, request_id):
+        with self.lock:
+            q = self.queues.pop(request_id, None)
+        if q is not None:
+            q.put(None)
 
     UNHEALTHY_AFTER = 3
 
@@ -68,16 +80,27 @@ class AsyncEngine:
 
     def _loop(self):
         eng = self.engine
+        held: list = []
         while not self._stop:
             try:
                 while True:
                     item = self.inbox.get_nowait() if (eng.has_unfinished or eng._world > 1) else self.inbox.get(timeout=0.05)
                     if item[0] == "abort":
                         eng.abort(item[1])
+                    elif item[2] in eng.scheduler.requests and not eng.scheduler.requests[item[2]].is_finished:
+                        # the id of a request that has been dropped but takes part in the round being executed (a client
+                        # that retries at once under its old id): the new one is taken in after that round
+                        if item[2] in eng._deferred_aborts:
+                            held.append(item)
+                        else:
+                            self._fail(item[2])
                     else:
                         eng.add_request(item[0], item[1], item[2], item[3], priority=item[4])
             except queue.Empty:
                 pass
+            for item in held:
+                self.inbox.put(item)
+            held = []
             if not eng.has_unfinished:
                 if eng._world == 1:
                     continue
@@ -120,6 +143,20 @@ class AsyncEngine:
             self.engine.save_state()
         except Exception:                      # shutting down: a state file that cannot be written must not hang it
             logging.getLogger("omni_infer_b200.api_server").exception("could not write the state directory")
+
+
+class _QuietServer(ThreadingHTTPServer):
+    """A client that hangs up between requests is routine for a server behind a proxy: one log line, not a stack trace."""
+    daemon_threads = True
+    request_queue_size = 128
+
+    def handle_error(self, request, client_address):
+        import sys
+        e = sys.exc_info()[1]
+        if isinstance(e, (ConnectionError, TimeoutError)):
+            logger.debug("client %s went away: %s", client_address, e)
+            return
+        super().handle_error(request, client_address)
 
 
 def _make_parsers(reasoning_parser: Optional[str], tool_call_parser: Optional[str]):
@@ -210,7 +247,10 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoni
                 else:
                     ids = tok.encode(p if isinstance(p, str) else str(p))
             try:
-                sp = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
+                want = body.get("max_tokens") if body.get("max_tokens") is not None else body.get("max_completion_tokens")
+                if isinstance(want, bool) or (want is not None and int(want) != want):
+                    raise ValueError("max_tokens must be an integer")
+                sp = SamplingParams(max_tokens=16 if want is None else int(want),
                                     temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
                                     top_p=float(body.get("top_p", 1.0) or 1.0), ignore_eos=bool(body.get("ignore_eos", False)),
                                     stop_token_ids=tuple(int(t) for t in (body.get("stop_token_ids") or ())),
@@ -239,6 +279,8 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoni
             except (TypeError, ValueError):
                 return self._json(400, {"error": "priority must be an integer"})
             q = aeng.submit(ids, sp, rid, kvp, priority)
+            if q is None:       # a client-chosen id that is still in flight: answering on the first one's queue would mix them
+                return self._json(409, {"error": f"request id {rid!r} is already in flight"})
             stream = bool(body.get("stream", False))
             created = int(time.time())
             n_prompt, out_ids, final = len(ids), [], None
@@ -374,7 +416,7 @@ def serve(engine_cfg: EngineConfig, host: str = "0.0.0.0", port: int = 8000, tok
     engine = EngineCore(engine_cfg, model_cfg=model_cfg)
     aeng = AsyncEngine(engine)
     tok = TokenizerPool(tokenizer, vocab_size=engine.model_cfg.vocab_size)
-    srv = ThreadingHTTPServer((host, port), make_handler(aeng, tok, engine.model_cfg.name or engine_cfg.model, reasoning, tools))
+    srv = _QuietServer((host, port), make_handler(aeng, tok, engine.model_cfg.name or engine_cfg.model, reasoning, tools))
     srv.daemon_threads = True
     if block:
         try:

@@ -49,12 +49,15 @@ class Scheduler:
         self.running: list = []
         self.requests: dict = {}
         self.finished_req_ids: set = set()
+        self._finished_order: deque = deque() # finished requests still listed in ``requests``, oldest first
         self.pending_free: dict = {}          # prefill side: blocks kept until the decode side pulled them
         self.finished_recving: set = set()
         self.pull_kv_lock = threading.Lock()  # serialises the fast-path KV pull with schedule()
         self._aborting: dict = {}             # dropped while their KV transfer ran: finished when it has concluded
         self._capacity_stopped: list = []     # (request, new tokens) ended inside schedule(): reported with the next outputs
         self.stats = {"preemptions": 0, "scheduled_prefill_tokens": 0, "scheduled_decode_tokens": 0, "steps": 0}
+
+    KEEP_FINISHED = 1024
 
     # ------------------------------------------------------------------ intake
     def add_request(self, req: Request) -> None:
@@ -425,6 +428,13 @@ class Scheduler:
         req.finish_time = _t.monotonic()
         req.record("Finish request")
         self.finished_req_ids.add(req.request_id)
+        # finished requests stay readable for a while (callers look their outputs up after the last step), but not for
+        # ever: a server lives for millions of requests
+        self._finished_order.append(req)
+        while len(self._finished_order) > self.KEEP_FINISHED:
+            old = self._finished_order.popleft()
+            if self.requests.get(old.request_id) is old:
+                del self.requests[old.request_id]
         if status in (RequestStatus.FINISHED_ABORTED, RequestStatus.FINISHED_IGNORED):
             self.kv.free(req)
 

@@ -314,3 +314,33 @@ def test_priority_policy_preempts_the_least_urgent_request():
     assert done["late-urgent"] < done["background"]
     for r in list(reqs.values()) + [late]:
         assert r.output_token_ids == expected_output(r.prompt_token_ids, r.sampling.max_tokens)
+
+
+def test_the_table_of_finished_requests_is_bounded():
+    """Finished requests stay in ``requests`` for callers that read an output after the last step, but only the latest
+    ``KEEP_FINISHED`` of them: a server's table must not grow with every request it has ever served."""
+    kv = KVCacheManager(16, 4)
+    sched = Scheduler(SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=64), kv)
+    sched.KEEP_FINISHED = 5
+    rnd = random.Random(0)
+    for i in range(20):
+        sched.add_request(Request(f"r{i}", [1 + i, 2, 3], SamplingParams(max_tokens=2, ignore_eos=True)))
+        if i == 7:
+            sched.abort_request("r7")                     # dropped requests age out the same way
+    for _ in range(60):
+        if not sched.has_unfinished:
+            break
+        so = sched.schedule()
+        sched.update_from_output(so, fake_runner(so, rnd, 0))
+        check_blocks(sched, kv)
+    assert not sched.has_unfinished and len(sched.requests) == 5 and "r19" in sched.requests and "r7" not in sched.requests
+    assert kv.num_free_blocks == kv.num_blocks - 1
+    # an id that has aged out (or merely finished) can be used again without touching the old record
+    again = Request("r19", [9, 9], SamplingParams(max_tokens=1, ignore_eos=True))
+    sched.add_request(again)
+    for _ in range(10):
+        if not sched.has_unfinished:
+            break
+        so = sched.schedule()
+        sched.update_from_output(so, fake_runner(so, rnd, 0))
+    assert sched.requests["r19"] is again and again.output_token_ids == expected_output([9, 9], 1)

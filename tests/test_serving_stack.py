@@ -61,6 +61,17 @@ def _status(port, path, body):
         return e.code, json.loads(e.read().decode() or "{}")
 
 
+def _status_id(port, body, rid):
+    import urllib.error
+    req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json", "X-Request-Id": rid})
+    try:
+        with urllib.request.urlopen(req, timeout=30) as r:
+            return r.status, json.loads(r.read().decode())
+    except urllib.error.HTTPError as e:
+        return e.code, json.loads(e.read().decode() or "{}")
+
+
 def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_failing_engine():
     import socket
     import urllib.error
@@ -73,6 +84,8 @@ def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_f
         assert _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": "many"})[0] == 400
         assert _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 4, "top_p": 1.5})[0] == 400
         assert _status(port, "/v1/completions", {"prompt": [], "max_tokens": 4})[0] == 400
+        for bad in (0, -3, 2.5, True):                     # zero is not "use the default"
+            assert _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": bad})[0] == 400, bad
         code, err = _status(port, "/v1/completions", {"prompt": list(range(70)), "max_tokens": 4})
         assert code == 400 and "context" in err["error"]
         # a prompt that fits the context but not the KV pool (7 usable blocks of 16 tokens) is ended by the scheduler,
@@ -106,6 +119,20 @@ def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_f
             time.sleep(0.02)
         req = next(iter(eng.scheduler.requests.values()))
         assert not eng.has_unfinished and req.status.name == "FINISHED_ABORTED" and len(req.output_token_ids) < 60
+        assert not aeng.queues                              # the output queue of the dropped request went with it
+        # ---- a request id that is still in flight is refused; once that request has ended the id can be used again
+        import threading
+        first = {}
+        t = threading.Thread(target=lambda: first.update(r=_status_id(port, {"prompt": [5, 6], "max_tokens": 30, "ignore_eos": True}, "same")))
+        t.start()
+        for _ in range(100):
+            if "same" in aeng.queues:
+                break
+            time.sleep(0.02)
+        assert _status_id(port, {"prompt": [5, 6], "max_tokens": 2}, "same")[0] == 409
+        t.join()
+        assert first["r"][0] == 200 and first["r"][1]["usage"]["completion_tokens"] == 30
+        assert _status_id(port, {"prompt": [5, 6], "max_tokens": 2}, "same")[0] == 200
         eng.step = real_step
         # ---- an engine whose steps fail: requests get an error, are dropped, and /health turns 503 until a step works
         assert urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=5).status == 200
