@@ -6,4 +6,4 @@ heap, fused collectives), ``engine`` (scheduler / KV manager / engine core / API
 ``adaptors`` (platform, worker, model runner), ``quantization``, ``accelerators`` (PD
 disaggregation, Omni-Attention KV compression, OmniPlacement, global proxy launcher), ``cli``.
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"

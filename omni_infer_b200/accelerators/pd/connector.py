@@ -443,6 +443,8 @@ class WorkerConnector:
         elif op == "cancel_ack":
             with self._lock:
                 self._cancel_acked.add((msg["request_id"], msg.get("attempt")))
+                if len(self._cancel_acked) > self.SERVED_LIMIT:      # confirmations that came after their wait had ended
+                    self._cancel_acked.pop()
 
     def _send(self, endpoint: str, msg: dict) -> bool:
         if self.transport == "inproc":

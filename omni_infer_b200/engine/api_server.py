@@ -212,21 +212,48 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoni
                 s, e = aeng.stats, aeng.engine
                 text = (f"omni_requests_total {s['requests']}\nomni_generated_tokens_total {s['tokens']}\n"
                         f"omni_running_requests {e.scheduler.num_running}\nomni_waiting_requests {e.scheduler.num_waiting}\n"
-                        f"omni_kv_cache_usage {e.kv.usage:.4f}\nomni_preemptions_total {e.scheduler.stats['preemptions']}\n").encode()
+                        f"omni_kv_cache_usage {e.kv.usage:.4f}\nomni_preemptions_total {e.scheduler.stats['preemptions']}\n"
+                        f"omni_failed_steps_total {s['failed_steps']}\nomni_engine_healthy {int(aeng.healthy)}\n"
+                        f"omni_engine_steps_total {e.metrics['steps']}\n").encode()
                 self.send_response(200)
                 self.send_header("Content-Type", "text/plain; version=0.0.4")
                 self.send_header("Content-Length", str(len(text)))
                 self.end_headers()
                 self.wfile.write(text)
                 return
+            if self.path == "/v1/models":
+                return self._json(200, {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "omni_infer_b200",
+                                                                    "max_model_len": aeng.engine.cfg.max_model_len}]})
+            if self.path == "/version":
+                from .. import __version__
+                return self._json(200, {"version": __version__})
             self._json(404, {"error": "not found"})
 
         def do_POST(self):
-            n = int(self.headers.get("Content-Length", "0"))
+            try:
+                n = int(self.headers.get("Content-Length", "0"))
+                if n < 0:
+                    raise ValueError
+            except ValueError:
+                self.close_connection = True            # where the body ends is unknown: nothing more is read here
+                return self._json(400, {"error": "bad Content-Length"})
             try:
                 body = json.loads(self.rfile.read(n) or b"{}")
-            except json.JSONDecodeError:
+            except (json.JSONDecodeError, UnicodeDecodeError):
                 return self._json(400, {"error": "invalid JSON"})
+            if not isinstance(body, dict):
+                return self._json(400, {"error": "the request body must be a JSON object"})
+            if self.path == "/tokenize":
+                text = body.get("prompt")
+                if not isinstance(text, str):
+                    return self._json(400, {"error": "prompt must be a string"})
+                ids = tok.encode(text)
+                return self._json(200, {"tokens": ids, "count": len(ids), "max_model_len": aeng.engine.cfg.max_model_len})
+            if self.path == "/detokenize":
+                ids = body.get("tokens")
+                if not isinstance(ids, list) or not all(isinstance(t, int) and not isinstance(t, bool) for t in ids):
+                    return self._json(400, {"error": "tokens must be a list of integers"})
+                return self._json(200, {"prompt": tok.decode(ids)})
             if self.path in ("/start_profile", "/stop_profile"):
                 aeng.engine.worker.profile(self.path == "/start_profile")
                 return self._json(200, {"status": "ok"})

@@ -88,6 +88,23 @@ def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_f
             assert _status(port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": bad})[0] == 400, bad
         code, err = _status(port, "/v1/completions", {"prompt": list(range(70)), "max_tokens": 4})
         assert code == 400 and "context" in err["error"]
+        # ---- a body that is not an object, or whose length is not a number, is refused without a stack trace
+        assert _status(port, "/v1/completions", [1, 2, 3])[0] == 400
+        bad_len = socket.create_connection(("127.0.0.1", port))
+        bad_len.sendall(b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Length: many\r\n\r\n{}")
+        assert bad_len.recv(200).split(b"\r\n")[0].endswith(b"400 Bad Request")
+        bad_len.close()
+        # ---- the small endpoints clients and load generators ask first
+        models = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=5).read())
+        assert models["data"][0]["id"] and models["data"][0]["max_model_len"] == 64
+        import omni_infer_b200
+        assert json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/version", timeout=5).read())["version"] == omni_infer_b200.__version__
+        code, t = _status(port, "/tokenize", {"prompt": "héllo"})
+        assert code == 200 and t["count"] == len(t["tokens"]) == 6
+        assert _status(port, "/detokenize", {"tokens": t["tokens"]}) == (200, {"prompt": "héllo"})
+        assert _status(port, "/detokenize", {"tokens": "abc"})[0] == 400 and _status(port, "/tokenize", {"prompt": 5})[0] == 400
+        metrics = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        assert "omni_engine_healthy 1" in metrics and "omni_failed_steps_total 0" in metrics
         # a prompt that fits the context but not the KV pool (7 usable blocks of 16 tokens) is ended by the scheduler,
         # and the client hears about it
         big = EngineConfig(block_size=16, num_kv_blocks=4, max_model_len=128, device="cpu")
