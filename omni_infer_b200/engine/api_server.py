@@ -103,10 +103,14 @@ class AsyncEngine:
             held = []
             if not eng.has_unfinished:
                 if eng._world == 1:
-                    continue
+                    if not eng.scheduler.pending_free:
+                        continue
+                    # a prefill instance that has gone idle still holds the blocks of its last hand-overs: it keeps
+                    # stepping (slowly) so that they are released when the decode side has fetched them or their time is up
+                    time.sleep(0.02)
                 # several data-parallel ranks share the expert-parallel exchanges: an idle rank keeps stepping (dummy
                 # batches) so that busy peers never wait for it; when the whole group was idle it paces itself
-                if not eng.peers_busy:
+                elif not eng.peers_busy:
                     time.sleep(0.002)
             try:
                 outs = eng.step()

@@ -555,3 +555,29 @@ def test_request_timeline_joins_proxy_prefill_and_decode(tmp_path):
     assert "request tl-req-1" in text and "p50" in text
     assert timeline.main([str(proxy_log), str(eng_log), "--json", str(tmp_path / "s.json")]) == 0
     assert json.load(open(tmp_path / "s.json"))["requests"] == 1
+
+
+def test_an_idle_prefill_server_releases_handed_over_blocks_without_new_traffic():
+    """A prefill instance keeps a finished prompt's blocks for the decode side.  When the decode side never comes (its
+    client hung up) they are released when the hand-over's time is up - also on a server that receives nothing else:
+    its loop keeps stepping while hand-overs are outstanding."""
+    from omni_infer_b200.accelerators.pd import InProcessHub
+    InProcessHub.reset()
+    cfg = EngineConfig(block_size=16, num_kv_blocks=8, max_model_len=64, device="cpu",
+                       kv_transfer_config={"kv_role": "kv_producer", "engine_id": "idle-p", "endpoint": "inproc://idle-p",
+                                           "handover_ttl_s": 0.5})
+    srv, aeng = serve(cfg, "127.0.0.1", 0, block=False)
+    eng = aeng.engine
+    try:
+        code, out = _status(srv.server_port, "/v1/completions", {"prompt": list(range(1, 30)), "max_tokens": 1})
+        assert code == 200 and out["kv_transfer_params"]["remote_block_ids"]
+        assert eng.scheduler.pending_free and eng.kv.num_free_blocks < eng.kv.num_blocks - 1
+        for _ in range(100):
+            if not eng.scheduler.pending_free:
+                break
+            time.sleep(0.05)
+        assert not eng.scheduler.pending_free and eng.kv.num_free_blocks == eng.kv.num_blocks - 1
+    finally:
+        srv.shutdown()
+        aeng.stop()
+        InProcessHub.reset()
