@@ -95,7 +95,11 @@ class AsyncEngine:
                         else:
                             self._fail(item[2])
                     else:
-                        eng.add_request(item[0], item[1], item[2], item[3], priority=item[4])
+                        try:
+                            eng.add_request(item[0], item[1], item[2], item[3], priority=item[4])
+                        except Exception:  # noqa: BLE001  (one request the engine refuses must not end the serving thread)
+                            logger.exception("the engine refused request %s", item[2])
+                            self._fail(item[2])
             except queue.Empty:
                 pass
             for item in held:
@@ -265,18 +269,41 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoni
             if not chat and self.path != "/v1/completions":
                 return self._json(404, {"error": "not found"})
             kvp = body.get("kv_transfer_params")
+            if kvp is not None and not isinstance(kvp, dict):
+                return self._json(400, {"error": "kv_transfer_params must be an object"})
+            if (body.get("n") or 1) != 1 or body.get("logprobs") or body.get("top_logprobs"):
+                return self._json(400, {"error": "n > 1 and logprobs are not supported"})
+
+            def token_list(v):
+                return isinstance(v, list) and all(isinstance(t, int) and not isinstance(t, bool) for t in v)
             # decode instance: reuse the prompt ids produced by the prefill instance
             if kvp and kvp.get("prompt_token_ids"):
+                if not token_list(kvp["prompt_token_ids"]):
+                    return self._json(400, {"error": "kv_transfer_params.prompt_token_ids must be a list of integers"})
                 ids = list(kvp["prompt_token_ids"])
             elif chat:
-                ids = tok.encode(tok.tokenizer.apply_chat_template(body.get("messages", []), add_generation_prompt=True)
-                                 if hasattr(tok.tokenizer, "apply_chat_template") else str(body.get("messages")))
+                msgs = body.get("messages")
+                if not isinstance(msgs, list) or not all(isinstance(m, dict) for m in msgs):
+                    return self._json(400, {"error": "messages must be a list of objects"})
+                # content given as a list of parts: the text parts, joined
+                msgs = [dict(m, content="".join(str(c.get("text", "")) for c in m["content"] if isinstance(c, dict)))
+                        if isinstance(m.get("content"), list) else m for m in msgs]
+                ids = tok.encode(tok.tokenizer.apply_chat_template(msgs, add_generation_prompt=True)
+                                 if hasattr(tok.tokenizer, "apply_chat_template") else str(msgs))
             else:
-                p = body.get("prompt", "")
-                if isinstance(p, list) and all(isinstance(t, int) and not isinstance(t, bool) for t in p):
+                p = body.get("prompt")
+                if isinstance(p, list) and len(p) == 1 and isinstance(p[0], (str, list)):
+                    p = p[0]                            # a batch of one
+                if token_list(p):
                     ids = list(p)                       # token ids as they are (an empty list is an empty prompt)
+                elif isinstance(p, str):
+                    ids = tok.encode(p)
                 else:
-                    ids = tok.encode(p if isinstance(p, str) else str(p))
+                    return self._json(400, {"error": "prompt must be a string or a list of token ids (one prompt per request)"})
+            vocab = getattr(getattr(aeng.engine, "model_cfg", None), "vocab_size", None)
+            if vocab is not None and any(t < 0 or t >= vocab for t in ids):
+                # the embedding lookup trusts its indices: an id outside the table must never reach the device
+                return self._json(400, {"error": f"token ids must lie in [0, {vocab})"})
             try:
                 want = body.get("max_tokens") if body.get("max_tokens") is not None else body.get("max_completion_tokens")
                 if isinstance(want, bool) or (want is not None and int(want) != want):

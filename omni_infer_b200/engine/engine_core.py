@@ -146,6 +146,10 @@ class EngineCore:
     def add_request(self, prompt_token_ids, sampling: Optional[SamplingParams] = None, request_id: Optional[str] = None,
                     kv_transfer_params: Optional[dict] = None, priority: int = 0) -> str:
         rid = request_id or f"req-{next(self._ids)}"
+        vocab = self.model_cfg.vocab_size
+        if any(not 0 <= int(t) < vocab for t in prompt_token_ids):
+            # the embedding lookup trusts its indices: an id outside the table must never reach the device
+            raise ValueError(f"prompt token ids must lie in [0, {vocab})")
         req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), priority=priority,
                       eos_token_id=self.cfg.eos_token_id, kv_transfer_params=kv_transfer_params, role=self.role)
         if not self.scheduler.try_pull_kv_fast_path(req):

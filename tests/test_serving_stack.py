@@ -94,6 +94,20 @@ def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_f
         bad_len.sendall(b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Length: many\r\n\r\n{}")
         assert bad_len.recv(200).split(b"\r\n")[0].endswith(b"400 Bad Request")
         bad_len.close()
+        # ---- shapes the server does not serve are refused, not guessed at; token ids outside the table never reach the model
+        for body in ({"prompt": ["a", "b"]}, {"prompt": None}, {"prompt": [[1, 2], [3]]}, {"prompt": [1, 2], "n": 2},
+                     {"prompt": [1, 2], "logprobs": 5}, {"prompt": [1, -5]}, {"prompt": [1, 10 ** 9]},
+                     {"prompt": [1, 2], "kv_transfer_params": "x"}, {"prompt": "x", "kv_transfer_params": {"prompt_token_ids": [1, 10 ** 9]}}):
+            assert _status(port, "/v1/completions", body)[0] == 400, body
+        for body in ({"messages": "hi"}, {"messages": [1, 2]}):
+            assert _status(port, "/v1/chat/completions", body)[0] == 400, body
+        assert _status(port, "/v1/completions", {"prompt": ["one prompt"], "max_tokens": 1})[0] == 200      # a batch of one
+        parts = {"messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}], "max_tokens": 1}
+        plain = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 1}
+        a, b = _status(port, "/v1/chat/completions", parts), _status(port, "/v1/chat/completions", plain)
+        assert a[0] == b[0] == 200 and a[1]["usage"]["prompt_tokens"] == b[1]["usage"]["prompt_tokens"]
+        with pytest.raises(ValueError):
+            eng.add_request([1, 5000])
         # ---- the small endpoints clients and load generators ask first
         models = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=5).read())
         assert models["data"][0]["id"] and models["data"][0]["max_model_len"] == 64
@@ -134,7 +148,7 @@ def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_f
             if not eng.has_unfinished:
                 break
             time.sleep(0.02)
-        req = next(iter(eng.scheduler.requests.values()))
+        req = list(eng.scheduler.requests.values())[-1]              # the one whose client went away
         assert not eng.has_unfinished and req.status.name == "FINISHED_ABORTED" and len(req.output_token_ids) < 60
         assert not aeng.queues                              # the output queue of the dropped request went with it
         # ---- a request id that is still in flight is refused; once that request has ended the id can be used again
