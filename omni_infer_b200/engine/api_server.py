@@ -301,7 +301,7 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoni
                 else:
                     return self._json(400, {"error": "prompt must be a string or a list of token ids (one prompt per request)"})
             vocab = getattr(getattr(aeng.engine, "model_cfg", None), "vocab_size", None)
-            if vocab is not None and any(t < 0 or t >= vocab for t in ids):
+            if vocab is not None and ids and (min(ids) < 0 or max(ids) >= vocab):
                 # the embedding lookup trusts its indices: an id outside the table must never reach the device
                 return self._json(400, {"error": f"token ids must lie in [0, {vocab})"})
             try:

@@ -147,10 +147,11 @@ class EngineCore:
                     kv_transfer_params: Optional[dict] = None, priority: int = 0) -> str:
         rid = request_id or f"req-{next(self._ids)}"
         vocab = self.model_cfg.vocab_size
-        if any(not 0 <= int(t) < vocab for t in prompt_token_ids):
+        prompt_token_ids = list(prompt_token_ids)
+        if prompt_token_ids and not (min(prompt_token_ids) >= 0 and max(prompt_token_ids) < vocab):
             # the embedding lookup trusts its indices: an id outside the table must never reach the device
             raise ValueError(f"prompt token ids must lie in [0, {vocab})")
-        req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), priority=priority,
+        req = Request(rid, prompt_token_ids, sampling or SamplingParams(), priority=priority,
                       eos_token_id=self.cfg.eos_token_id, kv_transfer_params=kv_transfer_params, role=self.role)
         if not self.scheduler.try_pull_kv_fast_path(req):
             self.scheduler.add_request(req)
