@@ -440,6 +440,12 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoni
                 return
             timeline.emit("Finish response in api server", rid, role=aeng.engine.role)
             if stream:
+                opts = body.get("stream_options")
+                if isinstance(opts, dict) and opts.get("include_usage"):
+                    # the closing chunk load generators count tokens from: no choices, the totals of the request
+                    last = chunk_obj("", None)
+                    last["choices"] = []
+                    self.wfile.write(("data: " + json.dumps(last) + "\n\n").encode())
                 self.wfile.write(b"data: [DONE]\n\n")
                 self.wfile.flush()
                 self.close_connection = True

@@ -37,13 +37,18 @@ def test_api_server_completions_and_stream():
         chunks = [json.loads(l[6:]) for l in text.splitlines() if l.startswith("data: {")]
         assert chunks[-1]["output_num_token"] == 4 and chunks[-1]["usage"]["total_tokens"] == chunks[-1]["prompt_num_token"] + 4
         assert "[DONE]" in text and chunks[-1]["choices"][0]["finish_reason"] == "length"
+        # a client that asks for it gets a closing chunk without choices that carries the request's totals
+        text = _post(port, "/v1/completions", {"prompt": "hi", "max_tokens": 3, "stream": True, "stream_options": {"include_usage": True}})
+        chunks = [json.loads(l[6:]) for l in text.splitlines() if l.startswith("data: {")]
+        assert chunks[-1]["choices"] == [] and chunks[-1]["usage"] == {"prompt_tokens": 2, "completion_tokens": 3, "total_tokens": 5}
+        assert chunks[-2]["choices"][0]["finish_reason"] == "length" and text.rstrip().endswith("[DONE]")
         # prefill leg of a PD request: one token, hand-off parameters in the response
         r = json.loads(_post(port, "/v1/completions", {"prompt": [1, 2, 3, 4, 5], "max_tokens": 1,
                                                        "kv_transfer_params": {"do_remote_decode": True}}))
         kv = r["kv_transfer_params"]
         assert kv["prompt_token_ids"] == [1, 2, 3, 4, 5] and kv["remote_block_ids"] and kv["prefilled_token"] is not None
         m = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
-        assert "omni_requests_total 3" in m
+        assert "omni_requests_total 4" in m
     finally:
         srv.shutdown()
         aeng.stop()
