@@ -237,7 +237,28 @@ def make_handler(aeng: AsyncEngine, tok: TokenizerPool, model_name: str, reasoni
                 return self._json(200, {"version": __version__})
             self._json(404, {"error": "not found"})
 
+        def send_response(self, code, message=None):
+            self._answered = True
+            super().send_response(code, message)
+
         def do_POST(self):
+            """A fault in the handler itself is answered with a 500 when no answer has been started (a client must not be
+            left with a connection that closes without a word), and logged either way."""
+            self._answered = False
+            try:
+                return self._post()
+            except (ConnectionError, TimeoutError):
+                raise
+            except Exception as e:  # noqa: BLE001
+                logger.exception("request handler failed: %s", e)
+                self.close_connection = True
+                if not self._answered:
+                    try:
+                        self._json(500, {"error": f"internal error: {type(e).__name__}"})
+                    except OSError:
+                        pass
+
+        def _post(self):
             try:
                 n = int(self.headers.get("Content-Length", "0"))
                 if n < 0:

@@ -113,6 +113,16 @@ def test_api_server_refuses_bad_input_drops_disconnected_clients_and_reports_a_f
         assert a[0] == b[0] == 200 and a[1]["usage"]["prompt_tokens"] == b[1]["usage"]["prompt_tokens"]
         with pytest.raises(ValueError):
             eng.add_request([1, 5000])
+        # ---- a fault inside the handler itself is answered (500), and the server goes on serving
+        real_submit = aeng.submit
+
+        def boom(*a, **k):
+            raise KeyError("boom")
+        aeng.submit = boom
+        code, err = _status(port, "/v1/completions", {"prompt": [1, 2], "max_tokens": 2})
+        assert code == 500 and "KeyError" in err["error"]
+        aeng.submit = real_submit
+        assert _status(port, "/v1/completions", {"prompt": [1, 2], "max_tokens": 2})[0] == 200
         # ---- the small endpoints clients and load generators ask first
         models = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=5).read())
         assert models["data"][0]["id"] and models["data"][0]["max_model_len"] == 64
